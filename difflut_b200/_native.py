@@ -1,0 +1,130 @@
+"""ctypes binding of the C ABI declared in `include/difflut_b200.h`.
+
+There is no CPU fallback: if the shared library is missing, `lib()` raises.  Every wrapper
+passes raw device pointers plus the current CUDA stream and turns a negative return code
+into RuntimeError (the reference's bindings raise RuntimeError through TORCH_CHECK,
+difflut/nodes/cuda/efd_cuda.cpp:18-40).
+"""
+
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "_lib", "libdifflut_b200.so")
+
+# signature strings: p = pointer, l = int64, i = int, f = float, d = double; the trailing
+# stream argument is implicit for every entry marked with a final 's'.
+SIGNATURES = {
+    "dl_thermo_rows": "ppplll s",
+    "dl_thermo_pack_t": "pppllll s",
+    "dl_thermo_pack_rows": "ppplll s",
+    "dl_pack_rows_to_t": "pplllf s",
+    "dl_f32_rows_to_t": "pplll s",
+    "dl_f32_t_to_rows": "pplll s",
+    "dl_bits_t_to_rows": "pplll s",
+    "dl_bits_rows_to_t": "ppllll s",
+    "dl_gather_rows": "pppllll s",
+    "dl_gather_rows_bwd": "ppppllll s",
+    "dl_dwn_prepare": "pppllff s",
+    "dl_dwn_prepare_full": "ppllff s",
+    "dl_dwn_fwd_bits_t": "ppppLLL s".replace("L", "l"),
+    "dl_dwn_fwd_vals_t": "ppppplll s",
+    "dl_dwn_bwd_tables_t": "ppplfpplll s",
+    "dl_dwn_bwd_input_t": "pplfpppplll s",
+    "dl_dwn_mapped_fwd": "pppllll i s".replace(" i", "i"),
+    "dl_dwn_mapped_bwd": "pppppllll s",
+    "dl_prob_fwd_t": "pppfpllll s",
+    "dl_prob_fwd_groupsum_t": "pppfpppllllfl s",
+    "dl_prob_bwd_t": "pppfplfpplllll s",
+    "dl_seg_sum_t": "ppppll s",
+    "dl_groupsum_rows": "ppllLf s".replace("L", "l"),
+    "dl_groupsum_rows_bwd": "ppllLf s".replace("L", "l"),
+    "dl_groupsum_t": "ppllfl s",
+    "dl_dwn_fwd_groupsum_t": "ppppplllfl s",
+    "dl_popcount_groupsum_t": "ppllll s",
+    "dl_ce_t": "pppppllll s",
+    "dl_adam_step": "ppppplfffff s",
+}
+
+_CT = {"p": ctypes.c_void_p, "l": ctypes.c_int64, "i": ctypes.c_int, "f": ctypes.c_float, "d": ctypes.c_double}
+
+_lib = None
+
+
+def lib():
+    """Load the shared library once; raise (never fall back) when it is absent."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"difflut_b200: CUDA library not found at {LIB_PATH}. Build it with "
+            "`python -m difflut_b200.build` (needs nvcc, targets sm_100a). There is no CPU fallback."
+        )
+    handle = ctypes.CDLL(LIB_PATH)
+    for name, sig in SIGNATURES.items():
+        fn = getattr(handle, name)
+        sig = sig.replace(" ", "")
+        args = [_CT[c] for c in sig if c != "s"]
+        if sig.endswith("s"):
+            args.append(ctypes.c_void_p)
+        fn.argtypes = args
+        fn.restype = ctypes.c_int
+    handle.dl_version.restype = ctypes.c_int
+    handle.dl_error_string.restype = ctypes.c_char_p
+    handle.dl_error_string.argtypes = [ctypes.c_int]
+    handle.dl_padded_batch.restype = ctypes.c_int64
+    handle.dl_padded_batch.argtypes = [ctypes.c_int64]
+    handle.dl_dwn_groupsum_splits.restype = ctypes.c_int64
+    handle.dl_dwn_groupsum_splits.argtypes = [ctypes.c_int64, ctypes.c_int64]
+    handle.dl_prob_groupsum_splits.restype = ctypes.c_int64
+    handle.dl_prob_groupsum_splits.argtypes = [ctypes.c_int64, ctypes.c_int64]
+    _lib = handle
+    return _lib
+
+
+def available() -> bool:
+    return os.path.exists(LIB_PATH)
+
+
+def padded_batch(B: int) -> int:
+    return (int(B) + 127) // 128 * 128
+
+
+def _ptr(a):
+    if a is None:
+        return None
+    if isinstance(a, torch.Tensor):
+        if not a.is_cuda:
+            raise RuntimeError("difflut_b200 kernels take CUDA tensors only (no CPU fallback)")
+        if not a.is_contiguous():
+            raise RuntimeError("difflut_b200 kernels take contiguous tensors")
+        return a.data_ptr()
+    return int(a)
+
+
+def call(name: str, *args, stream=None):
+    """Invoke C-ABI entry `name`; tensors become device pointers, the stream is appended."""
+    handle = lib()
+    fn = getattr(handle, name)
+    sig = SIGNATURES[name].replace(" ", "")
+    kinds = [c for c in sig if c != "s"]
+    if len(kinds) != len(args):
+        raise TypeError(f"{name}: expected {len(kinds)} arguments, got {len(args)}")
+    conv = []
+    for kind, a in zip(kinds, args):
+        if kind == "p":
+            conv.append(_ptr(a))
+        elif kind in ("l", "i"):
+            conv.append(int(a))
+        else:
+            conv.append(float(a))
+    if sig.endswith("s"):
+        if stream is None:
+            stream = torch.cuda.current_stream().cuda_stream
+        conv.append(stream)
+    code = fn(*conv)
+    if code != 0:
+        raise RuntimeError(f"{name} failed: {handle.dl_error_string(code).decode()} (code {code})")

@@ -1,0 +1,41 @@
+// Shared helpers for the difflut_b200 kernels (sm_100a).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/difflut_b200.h"
+
+#define DL_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Every entry point validates on the host, launches on the caller's stream and reports
+// launch-time errors through cudaPeekAtLastError (no synchronisation, no allocation).
+#define DL_REQUIRE(cond)                \
+    do {                                \
+        if (!(cond)) return DL_ERR_ARG; \
+    } while (0)
+
+#define DL_REQUIRE_ALIGNED(p, a)                                              \
+    do {                                                                      \
+        if ((reinterpret_cast<uintptr_t>(p) % (a)) != 0) return DL_ERR_ALIGN; \
+    } while (0)
+
+static inline int dl_launch_status() {
+    return cudaPeekAtLastError() == cudaSuccess ? DL_OK : DL_ERR_LAUNCH;
+}
+
+static inline cudaStream_t dl_cast(dl_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+static inline int64_t dl_ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+static inline int64_t dl_min64(int64_t a, int64_t b) { return a < b ? a : b; }
+__device__ __forceinline__ int64_t dl_ceil_div_dev(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// Number of streaming multiprocessors the grids are sized for (B200: 148).
+constexpr int DL_NUM_SMS = 148;
+
+__device__ __forceinline__ uint32_t dl_lane() { return threadIdx.x & 31u; }
+
+// Spread the 4 low bits of `nib` to the least-significant bit of each byte:
+// bit q -> bit 8q.  (1 + 2^7 + 2^14 + 2^21 places every product term on a distinct bit.)
+__device__ __forceinline__ uint32_t dl_spread_nibble(uint32_t nib) {
+    return (nib * 0x00204081u) & 0x01010101u;
+}

@@ -1,0 +1,229 @@
+// Thermometer encoder and layout-change kernels.
+//
+// The reference encoder (difflut/encoder/thermometer.py:89-116) writes one fp32 per bit.  The
+// kernels here compare once and either write that fp32 tensor (API-exact) or ballot the
+// results of 32 samples into one word of the packed feature-major layout the LUT kernels read.
+#include "common.cuh"
+
+namespace {
+
+constexpr int TILE_F = 32;    // features per CTA tile
+constexpr int TILE_B = 256;   // samples per CTA tile (8 words per feature row)
+constexpr int PACK_THREADS = 256;
+
+// x rows (B,F) -> packed feature-major bits.  MODE 0: bit = x > thr[f][t] (T bits per feature);
+// MODE 1: bit = x >= scalar threshold (T == 1).
+template <int MODE>
+__global__ void __launch_bounds__(PACK_THREADS)
+pack_t_kernel(const float* __restrict__ x, const float* __restrict__ thr, float scalar_thr,
+              uint32_t* __restrict__ bits_t, int64_t B, int64_t F, int T, int64_t Wp) {
+    __shared__ float tile[TILE_B][TILE_F + 1];
+    const int64_t f0 = (int64_t)blockIdx.y * TILE_F;
+    const int64_t b0 = (int64_t)blockIdx.x * TILE_B;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // coalesced load: one warp reads 32 consecutive features of one sample row
+    for (int r = warp; r < TILE_B; r += PACK_THREADS / 32) {
+        const int64_t b = b0 + r, f = f0 + lane;
+        tile[r][lane] = (b < B && f < F) ? x[b * F + f] : 0.0f;
+    }
+    __syncthreads();
+    // warp w owns word w of the tile: lane = sample inside the word
+    const int64_t b = b0 + warp * 32 + lane;
+    const bool valid = b < B;
+    const int64_t word = (b0 >> 5) + warp;
+    for (int f = 0; f < TILE_F; ++f) {
+        if (f0 + f >= F) break;
+        const float v = tile[warp * 32 + lane][f];
+        if (MODE == 0) {
+            for (int t = 0; t < T; ++t) {
+                const float th = __ldg(&thr[(f0 + f) * T + t]);
+                const uint32_t w = __ballot_sync(0xffffffffu, valid && (v > th));
+                if (lane == 0 && word < Wp) bits_t[((f0 + f) * T + t) * Wp + word] = w;
+            }
+        } else {
+            const uint32_t w = __ballot_sync(0xffffffffu, valid && (v >= scalar_thr));
+            if (lane == 0 && word < Wp) bits_t[(f0 + f) * Wp + word] = w;
+        }
+    }
+}
+
+// rows in, fp32 rows out: out[b, f*T+t] = x[b,f] > thr[f,t]
+__global__ void thermo_rows_kernel(const float* __restrict__ x, const float* __restrict__ thr,
+                                   float* __restrict__ out, int64_t B, int64_t F, int T) {
+    const int64_t total = B * F * T;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t c = i % (F * T), b = i / (F * T);
+        const int64_t f = c / T;
+        out[i] = (x[b * F + f] > __ldg(&thr[c])) ? 1.0f : 0.0f;
+    }
+}
+
+// rows in, packed rows out: one warp per (sample, word); lane = column inside the word
+__global__ void thermo_pack_rows_kernel(const float* __restrict__ x, const float* __restrict__ thr,
+                                        uint32_t* __restrict__ bits, int64_t B, int64_t F, int T,
+                                        int64_t Wr) {
+    const int64_t C = F * T;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    for (int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < B * Wr; w += nwarps) {
+        const int64_t b = w / Wr, c = (w % Wr) * 32 + lane;
+        bool bit = false;
+        if (c < C) bit = x[b * F + c / T] > __ldg(&thr[c]);
+        const uint32_t word = __ballot_sync(0xffffffffu, bit);
+        if (lane == 0) bits[w] = word;
+    }
+}
+
+// fp32 rows (B,F) -> feature-major [F][Bp] through a 32x32 shared tile; padding written as 0.
+__global__ void __launch_bounds__(256)
+rows_to_t_kernel(const float* __restrict__ rows, float* __restrict__ t, int64_t B, int64_t F,
+                 int64_t Bp) {
+    __shared__ float tile[32][33];
+    const int64_t f0 = (int64_t)blockIdx.y * 32, b0 = (int64_t)blockIdx.x * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (int r = ty; r < 32; r += 8) {
+        const int64_t b = b0 + r, f = f0 + tx;
+        tile[r][tx] = (b < B && f < F) ? rows[b * F + f] : 0.0f;
+    }
+    __syncthreads();
+    for (int r = ty; r < 32; r += 8) {
+        const int64_t f = f0 + r, b = b0 + tx;
+        if (f < F && b < Bp) t[f * Bp + b] = tile[tx][r];
+    }
+}
+
+__global__ void __launch_bounds__(256)
+t_to_rows_kernel(const float* __restrict__ t, float* __restrict__ rows, int64_t B, int64_t F,
+                 int64_t Bp) {
+    __shared__ float tile[32][33];
+    const int64_t f0 = (int64_t)blockIdx.y * 32, b0 = (int64_t)blockIdx.x * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (int r = ty; r < 32; r += 8) {
+        const int64_t f = f0 + r, b = b0 + tx;
+        tile[r][tx] = (f < F && b < Bp) ? t[f * Bp + b] : 0.0f;
+    }
+    __syncthreads();
+    for (int r = ty; r < 32; r += 8) {
+        const int64_t b = b0 + r, f = f0 + tx;
+        if (b < B && f < F) rows[b * F + f] = tile[tx][r];
+    }
+}
+
+// bits_t [F][Wp] -> fp32 rows (B,F) of {0,1}: CTA tile = 32 features x 32 samples (one word each)
+__global__ void __launch_bounds__(256)
+bits_t_to_rows_kernel(const uint32_t* __restrict__ bits_t, float* __restrict__ rows, int64_t B,
+                      int64_t F, int64_t Wp) {
+    __shared__ uint32_t words[32];
+    const int64_t f0 = (int64_t)blockIdx.y * 32, w = blockIdx.x;
+    if (threadIdx.x < 32) {
+        const int64_t f = f0 + threadIdx.x;
+        words[threadIdx.x] = f < F ? bits_t[f * Wp + w] : 0u;
+    }
+    __syncthreads();
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (int r = ty; r < 32; r += 8) {
+        const int64_t b = w * 32 + r, f = f0 + tx;
+        if (b < B && f < F) rows[b * F + f] = (float)((words[tx] >> r) & 1u);
+    }
+}
+
+// packed rows (B, Wr) -> packed feature-major [F][Wp]: 32x32 bit-matrix transpose per warp.
+// Lane r holds word (sample 32*wb + r, column word wc); after the transpose lane c holds the
+// 32 samples of column 32*wc + c.
+__global__ void __launch_bounds__(256)
+bits_rows_to_t_kernel(const uint32_t* __restrict__ bits_rows, uint32_t* __restrict__ bits_t,
+                      int64_t B, int64_t F, int64_t Wr, int64_t Wp) {
+    const int lane = threadIdx.x & 31;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int64_t Wc = (F + 31) / 32;
+    for (int64_t tile = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; tile < Wp * Wc;
+         tile += nwarps) {
+        const int64_t wb = tile / Wc, wc = tile % Wc;
+        const int64_t b = wb * 32 + lane;
+        const uint32_t mine = (b < B) ? bits_rows[b * Wr + wc] : 0u;
+        uint32_t outw = 0;
+        // column c of the tile = ballot of bit c over the 32 lanes (samples)
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+            const uint32_t col = __ballot_sync(0xffffffffu, (mine >> c) & 1u);
+            if (lane == c) outw = col;
+        }
+        const int64_t f = wc * 32 + lane;
+        if (f < F) bits_t[f * Wp + wb] = outw;
+    }
+}
+
+}  // namespace
+
+DL_EXPORT int dl_thermo_rows(const float* x, const float* thr, float* out, int64_t B, int64_t F,
+                             int64_t T, dl_stream_t stream) {
+    DL_REQUIRE(x && thr && out && B > 0 && F > 0 && T > 0);
+    const int64_t total = B * F * T;
+    const int blocks = (int)dl_min64(dl_ceil_div(total, 256), (int64_t)DL_NUM_SMS * 16);
+    thermo_rows_kernel<<<blocks, 256, 0, dl_cast(stream)>>>(x, thr, out, B, F, (int)T);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_thermo_pack_t(const float* x, const float* thr, uint32_t* bits_t, int64_t B,
+                               int64_t F, int64_t T, int64_t Bp, dl_stream_t stream) {
+    DL_REQUIRE(x && thr && bits_t && B > 0 && F > 0 && T > 0);
+    DL_REQUIRE(Bp >= B && Bp % DL_BATCH_ALIGN == 0);
+    dim3 grid((unsigned)dl_ceil_div(Bp, TILE_B), (unsigned)dl_ceil_div(F, TILE_F));
+    pack_t_kernel<0><<<grid, PACK_THREADS, 0, dl_cast(stream)>>>(x, thr, 0.f, bits_t, B, F, (int)T,
+                                                                Bp / 32);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_thermo_pack_rows(const float* x, const float* thr, uint32_t* bits, int64_t B,
+                                  int64_t F, int64_t T, dl_stream_t stream) {
+    DL_REQUIRE(x && thr && bits && B > 0 && F > 0 && T > 0);
+    const int64_t Wr = dl_ceil_div(F * T, 32);
+    const int blocks = (int)dl_min64(dl_ceil_div(B * Wr * 32, 256), (int64_t)DL_NUM_SMS * 16);
+    thermo_pack_rows_kernel<<<blocks, 256, 0, dl_cast(stream)>>>(x, thr, bits, B, F, (int)T, Wr);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_pack_rows_to_t(const float* x, uint32_t* bits_t, int64_t B, int64_t F, int64_t Bp,
+                                float threshold, dl_stream_t stream) {
+    DL_REQUIRE(x && bits_t && B > 0 && F > 0);
+    DL_REQUIRE(Bp >= B && Bp % DL_BATCH_ALIGN == 0);
+    dim3 grid((unsigned)dl_ceil_div(Bp, TILE_B), (unsigned)dl_ceil_div(F, TILE_F));
+    pack_t_kernel<1><<<grid, PACK_THREADS, 0, dl_cast(stream)>>>(x, nullptr, threshold, bits_t, B, F,
+                                                                1, Bp / 32);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_f32_rows_to_t(const float* rows, float* t, int64_t B, int64_t F, int64_t Bp,
+                               dl_stream_t stream) {
+    DL_REQUIRE(rows && t && B > 0 && F > 0 && Bp >= B && Bp % DL_BATCH_ALIGN == 0);
+    dim3 grid((unsigned)(Bp / 32), (unsigned)dl_ceil_div(F, 32));
+    rows_to_t_kernel<<<grid, 256, 0, dl_cast(stream)>>>(rows, t, B, F, Bp);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_f32_t_to_rows(const float* t, float* rows, int64_t B, int64_t F, int64_t Bp,
+                               dl_stream_t stream) {
+    DL_REQUIRE(rows && t && B > 0 && F > 0 && Bp >= B && Bp % DL_BATCH_ALIGN == 0);
+    dim3 grid((unsigned)dl_ceil_div(B, 32), (unsigned)dl_ceil_div(F, 32));
+    t_to_rows_kernel<<<grid, 256, 0, dl_cast(stream)>>>(t, rows, B, F, Bp);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_bits_t_to_rows(const uint32_t* bits_t, float* rows, int64_t B, int64_t F, int64_t Bp,
+                                dl_stream_t stream) {
+    DL_REQUIRE(rows && bits_t && B > 0 && F > 0 && Bp >= B && Bp % DL_BATCH_ALIGN == 0);
+    dim3 grid((unsigned)dl_ceil_div(B, 32), (unsigned)dl_ceil_div(F, 32));
+    bits_t_to_rows_kernel<<<grid, 256, 0, dl_cast(stream)>>>(bits_t, rows, B, F, Bp / 32);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_bits_rows_to_t(const uint32_t* bits_rows, uint32_t* bits_t, int64_t B, int64_t F,
+                                int64_t Wr, int64_t Bp, dl_stream_t stream) {
+    DL_REQUIRE(bits_rows && bits_t && B > 0 && F > 0 && Bp >= B && Bp % DL_BATCH_ALIGN == 0);
+    DL_REQUIRE(Wr * 32 >= F);
+    const int64_t tiles = (Bp / 32) * dl_ceil_div(F, 32);
+    const int blocks = (int)dl_min64(dl_ceil_div(tiles * 32, 256), (int64_t)DL_NUM_SMS * 16);
+    bits_rows_to_t_kernel<<<blocks, 256, 0, dl_cast(stream)>>>(bits_rows, bits_t, B, F, Wr, Bp / 32);
+    return dl_launch_status();
+}

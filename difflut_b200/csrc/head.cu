@@ -1,0 +1,188 @@
+// GroupSum, cross-entropy and Adam: the small kernels after the last LUT layer.
+#include "common.cuh"
+
+namespace {
+
+// rows: one warp per (sample, class); lanes stride over the class's contiguous columns.
+__global__ void groupsum_rows_kernel(const float* __restrict__ x, float* __restrict__ out, int64_t B,
+                                     int64_t F, int k, int64_t gsz, float inv_tau) {
+    const int lane = threadIdx.x & 31;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < B * k; w += nwarps) {
+        const int64_t b = w / k, c = w - b * k;
+        const int64_t c0 = c * gsz;
+        int64_t c1 = c0 + gsz;
+        if (c1 > F) c1 = F;
+        float acc = 0.f;
+        for (int64_t col = c0 + lane; col < c1; col += 32) acc += x[b * F + col];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) out[w] = acc * inv_tau;
+    }
+}
+
+__global__ void groupsum_rows_bwd_kernel(const float* __restrict__ gout, float* __restrict__ gx,
+                                         int64_t B, int64_t F, int k, int64_t gsz, float inv_tau) {
+    const int64_t total = B * F;
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total;
+         t += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t b = t / F, col = t - b * F;
+        gx[t] = gout[b * k + col / gsz] * inv_tau;
+    }
+}
+
+// feature-major: thread per (class, sample); rows of the class are read coalesced.
+__global__ void groupsum_t_kernel(const float* __restrict__ vals_t, float* __restrict__ logits_t,
+                                  int64_t F, int k, int64_t gsz, float inv_tau, int64_t Bp) {
+    const int64_t total = (int64_t)k * Bp;
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total;
+         t += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t c = t / Bp, b = t - c * Bp;
+        int64_t r1 = (c + 1) * gsz;
+        if (r1 > F) r1 = F;
+        float acc = 0.f;
+        for (int64_t r = c * gsz; r < r1; ++r) acc += vals_t[r * Bp + b];
+        logits_t[t] = acc * inv_tau;
+    }
+}
+
+// softmax cross-entropy, thread per sample
+__global__ void ce_t_kernel(const float* __restrict__ logits_t, const int32_t* __restrict__ labels,
+                            float* __restrict__ dlogits_t, float* __restrict__ loss_rows, int64_t B,
+                            float inv_bg, int k, int64_t Bp) {
+    for (int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; b < Bp;
+         b += (int64_t)gridDim.x * blockDim.x) {
+        if (b >= B) {
+            for (int c = 0; c < k; ++c) dlogits_t[c * Bp + b] = 0.f;
+            loss_rows[b] = 0.f;
+            continue;
+        }
+        float mx = -INFINITY;
+        for (int c = 0; c < k; ++c) mx = fmaxf(mx, logits_t[c * Bp + b]);
+        float sum = 0.f;
+        for (int c = 0; c < k; ++c) sum += expf(logits_t[c * Bp + b] - mx);
+        const float lse = mx + logf(sum);
+        const int y = labels[b];
+        const float inv = 1.0f / sum;
+        for (int c = 0; c < k; ++c) {
+            const float p = expf(logits_t[c * Bp + b] - mx) * inv;
+            dlogits_t[c * Bp + b] = (p - (c == y ? 1.f : 0.f)) * inv_bg;
+        }
+        loss_rows[b] = lse - logits_t[(int64_t)y * Bp + b];
+    }
+}
+
+// single CTA, fixed-order tree: reproducible
+__global__ void __launch_bounds__(1024)
+loss_sum_kernel(const float* __restrict__ loss_rows, float* __restrict__ loss, int64_t Bp, float inv_bg) {
+    __shared__ double part[1024];
+    double acc = 0.0;
+    for (int64_t b = threadIdx.x; b < Bp; b += 1024) acc += (double)loss_rows[b];
+    part[threadIdx.x] = acc;
+    __syncthreads();
+    for (int s = 512; s > 0; s >>= 1) {
+        if (threadIdx.x < s) part[threadIdx.x] += part[threadIdx.x + s];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) loss[0] = (float)(part[0] * (double)inv_bg);
+}
+
+__global__ void adam_advance_kernel(double* state, double b1, double b2) {
+    state[0] *= b1;
+    state[1] *= b2;
+}
+
+__global__ void adam_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
+                            float* __restrict__ v, const double* __restrict__ state, int64_t count,
+                            float lr, float b1, float b2, float eps, float gscale) {
+    // bias corrections in double, as the host-side optimiser computes them
+    const double bc1 = 1.0 - state[0];
+    const double bc2 = 1.0 - state[1];
+    const float step_size = (float)((double)lr / bc1);
+    const float bc2_sqrt = (float)sqrt(bc2);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const float gi = g[i] * gscale;
+        const float mi = m[i] + (gi - m[i]) * (1.0f - b1);
+        const float vi = v[i] * b2 + (1.0f - b2) * gi * gi;
+        m[i] = mi;
+        v[i] = vi;
+        const float denom = sqrtf(vi) / bc2_sqrt + eps;
+        p[i] = p[i] - step_size * (mi / denom);
+    }
+}
+
+}  // namespace
+
+DL_EXPORT int dl_groupsum_rows(const float* x, float* out, int64_t B, int64_t F, int64_t k, float tau,
+                               dl_stream_t stream) {
+    DL_REQUIRE(x && out && B > 0 && F > 0 && k > 0 && tau > 0.f);
+    const int64_t gsz = dl_ceil_div(F, k);
+    const int64_t blocks = dl_min64(dl_ceil_div(B * k * 32, 256), (int64_t)DL_NUM_SMS * 32);
+    groupsum_rows_kernel<<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(x, out, B, F, (int)k, gsz, 1.0f / tau);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_groupsum_rows_bwd(const float* gout, float* gx, int64_t B, int64_t F, int64_t k,
+                                   float tau, dl_stream_t stream) {
+    DL_REQUIRE(gout && gx && B > 0 && F > 0 && k > 0 && tau > 0.f);
+    const int64_t gsz = dl_ceil_div(F, k);
+    const int64_t blocks = dl_min64(dl_ceil_div(B * F, 256), (int64_t)DL_NUM_SMS * 32);
+    groupsum_rows_bwd_kernel<<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(gout, gx, B, F, (int)k, gsz,
+                                                                          1.0f / tau);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_groupsum_t(const float* vals_t, float* logits_t, int64_t F, int64_t k, float tau,
+                            int64_t Bp, dl_stream_t stream) {
+    DL_REQUIRE(vals_t && logits_t && F > 0 && k > 0 && tau > 0.f && Bp > 0);
+    const int64_t gsz = dl_ceil_div(F, k);
+    const int64_t blocks = dl_min64(dl_ceil_div(k * Bp, 128), (int64_t)DL_NUM_SMS * 32);
+    groupsum_t_kernel<<<(unsigned)blocks, 128, 0, dl_cast(stream)>>>(vals_t, logits_t, F, (int)k, gsz,
+                                                                   1.0f / tau, Bp);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_ce_t(const float* logits_t, const int32_t* labels, float* dlogits_t, float* loss_rows,
+                      float* loss, int64_t B, int64_t B_global, int64_t k, int64_t Bp,
+                      dl_stream_t stream) {
+    DL_REQUIRE(logits_t && labels && dlogits_t && loss_rows && loss);
+    DL_REQUIRE(B > 0 && B_global >= B && k > 0 && Bp >= B);
+    const float inv_bg = (float)(1.0 / (double)B_global);
+    const int64_t blocks = dl_min64(dl_ceil_div(Bp, 128), (int64_t)DL_NUM_SMS * 8);
+    ce_t_kernel<<<(unsigned)blocks, 128, 0, dl_cast(stream)>>>(logits_t, labels, dlogits_t, loss_rows, B,
+                                                             inv_bg, (int)k, Bp);
+    if (cudaPeekAtLastError() != cudaSuccess) return DL_ERR_LAUNCH;
+    loss_sum_kernel<<<1, 1024, 0, dl_cast(stream)>>>(loss_rows, loss, Bp, inv_bg);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_adam_step(float* p, const float* g, float* m, float* v, double* state, int64_t count,
+                           float lr, float beta1, float beta2, float eps, float gscale,
+                           dl_stream_t stream) {
+    DL_REQUIRE(p && g && m && v && state && count > 0);
+    adam_advance_kernel<<<1, 1, 0, dl_cast(stream)>>>(state, (double)beta1, (double)beta2);
+    if (cudaPeekAtLastError() != cudaSuccess) return DL_ERR_LAUNCH;
+    const int64_t blocks = dl_min64(dl_ceil_div(count, 256), (int64_t)DL_NUM_SMS * 16);
+    adam_kernel<<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(p, g, m, v, state, count, lr, beta1, beta2,
+                                                             eps, gscale);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_version(void) { return 100; }
+
+DL_EXPORT const char* dl_error_string(int code) {
+    switch (code) {
+        case DL_OK: return "ok";
+        case DL_ERR_ARG: return "invalid argument (null pointer or inconsistent sizes)";
+        case DL_ERR_UNSUPPORTED: return "unsupported node input count for this entry point";
+        case DL_ERR_LAUNCH: return "CUDA reported an error at kernel launch";
+        case DL_ERR_ALIGN: return "pointer or stride is not aligned as documented";
+        case DL_ERR_TOO_LARGE: return "size exceeds a documented fixed capacity";
+        default: return "unknown error code";
+    }
+}
+
+DL_EXPORT int64_t dl_padded_batch(int64_t B) {
+    return B <= 0 ? 0 : dl_ceil_div(B, DL_BATCH_ALIGN) * DL_BATCH_ALIGN;
+}

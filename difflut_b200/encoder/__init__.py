@@ -1,0 +1,6 @@
+"""Encoders of the hot path: the thermometer encoder and its base class."""
+
+from .base_encoder import BaseEncoder
+from .thermometer import ThermometerEncoder
+
+__all__ = ["BaseEncoder", "ThermometerEncoder"]

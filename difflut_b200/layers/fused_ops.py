@@ -1,0 +1,212 @@
+"""Layer-granular autograd functions: gather + node arithmetic in one pass over feature-major data.
+
+The reference runs a Python loop over N node modules on a materialised (B, N, n) tensor
+(difflut/layers/random_layer.py:306-340).  Here a layer is one forward kernel and, in backward,
+one table-gradient kernel plus one input-gradient kernel; rows <-> feature-major transposes sit
+at the API edge only.  `ConnectionPlan` holds the device-side index structures of a layer.
+"""
+
+from typing import Optional
+
+import torch
+
+from .. import _native
+
+
+class ConnectionPlan:
+    """Device copies of a fixed (N, n) index map: int32 map per virtual node and its inverse (CSR).
+
+    A node with O outputs appears as O consecutive virtual nodes sharing one map row, so the
+    same kernels serve output_dim > 1.  `inv_ptr` (F+1) / `inv_ent` list, per input feature, the
+    flat positions v*n+i that read it (sorted, so the backward sums in a fixed order).
+    """
+
+    def __init__(self, mapping: torch.Tensor, input_size: int, out_dim: int, device: torch.device):
+        m = mapping.to(device=device, dtype=torch.int64)
+        self.N, self.n = int(m.shape[0]), int(m.shape[1])
+        self.O = int(out_dim)
+        self.input_size = int(input_size)
+        if m.numel() and (int(m.min()) < 0 or int(m.max()) >= input_size):
+            raise ValueError("mapping indices out of range for input_size")
+        self.map_nodes = m.to(torch.int32).contiguous()  # (N, n)
+        mv = m.repeat_interleave(self.O, dim=0) if self.O > 1 else m
+        self.map_virtual = mv.to(torch.int32).contiguous()  # (N*O, n)
+        self.inv_ptr_virtual, self.inv_ent_virtual = self._invert(mv, input_size)
+        if self.O > 1:
+            self.inv_ptr_nodes, self.inv_ent_nodes = self._invert(m, input_size)
+        else:
+            self.inv_ptr_nodes, self.inv_ent_nodes = self.inv_ptr_virtual, self.inv_ent_virtual
+        self.device = device
+
+    @staticmethod
+    def _invert(m: torch.Tensor, input_size: int):
+        flat = m.reshape(-1)
+        order = torch.argsort(flat, stable=True)
+        counts = torch.bincount(flat, minlength=input_size)
+        ptr = torch.zeros(input_size + 1, dtype=torch.int64, device=m.device)
+        ptr[1:] = torch.cumsum(counts, 0)
+        return ptr.to(torch.int32).contiguous(), order.to(torch.int32).contiguous()
+
+
+def _rows_to_t(rows: torch.Tensor, Bp: int) -> torch.Tensor:
+    B, F = rows.shape
+    t = torch.empty(F, Bp, device=rows.device, dtype=torch.float32)
+    _native.call("dl_f32_rows_to_t", rows, t, B, F, Bp)
+    return t
+
+
+def _t_to_rows(t: torch.Tensor, B: int) -> torch.Tensor:
+    F, Bp = t.shape
+    rows = torch.empty(B, F, device=t.device, dtype=torch.float32)
+    _native.call("dl_f32_t_to_rows", t, rows, B, F, Bp)
+    return rows
+
+
+class DWNLayerFunction(torch.autograd.Function):
+    """RandomLayer(+DWN) training forward/backward: x (B, I) rows, tables (N, O, 2^n) -> (B, N*O).
+
+    Counterpart of EFDFusedFunction (difflut/nodes/dwn_node.py:232-316) with per-node tables.
+    """
+
+    @staticmethod
+    def forward(ctx, x, tables, plan: ConnectionPlan, alpha: float, beta: float):
+        x = x.contiguous().float()
+        tables = tables.contiguous().float()
+        B, I = x.shape
+        NO, n = plan.N * plan.O, plan.n
+        Bp = _native.padded_batch(B)
+        with torch.cuda.device(x.device):
+            bits = torch.empty(I, Bp // 32, device=x.device, dtype=torch.int32)
+            _native.call("dl_pack_rows_to_t", x, bits, B, I, Bp, 0.5)
+            out_t = torch.empty(NO, Bp, device=x.device, dtype=torch.float32)
+            _native.call("dl_dwn_fwd_vals_t", bits, plan.map_virtual, tables, out_t, None, NO, n, Bp)
+            out = _t_to_rows(out_t, B)
+        ctx.save_for_backward(bits, tables)
+        ctx.plan, ctx.alpha, ctx.beta, ctx.B = plan, float(alpha), float(beta), B
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        bits, tables = ctx.saved_tensors
+        plan, B = ctx.plan, ctx.B
+        NO, n, I = plan.N * plan.O, plan.n, plan.input_size
+        Bp = bits.shape[1] * 32
+        need_x, need_t = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        gx = gt = None
+        with torch.cuda.device(g.device):
+            g_t = _rows_to_t(g.contiguous().float(), Bp)
+            addr = torch.empty(NO, Bp, device=g.device, dtype=torch.uint8) if need_x else None
+            gt = torch.empty_like(tables)
+            # the table-gradient kernel also produces the addresses the input-gradient kernel reads
+            _native.call("dl_dwn_bwd_tables_t", bits, plan.map_virtual, g_t, 1, 1.0, gt, addr, NO, n, Bp)
+            if need_x:
+                efd = torch.empty(NO, n, 32, device=g.device, dtype=torch.float32)
+                _native.call("dl_dwn_prepare", tables, efd, None, NO, n, ctx.alpha, ctx.beta)
+                gx_t = torch.empty(I, Bp, device=g.device, dtype=torch.float32)
+                _native.call("dl_dwn_bwd_input_t", addr, g_t, 1, 1.0, efd, plan.inv_ptr_virtual,
+                             plan.inv_ent_virtual, gx_t, I, n, Bp)
+                gx = _t_to_rows(gx_t, B)
+        return gx, (gt if need_t else None), None, None, None
+
+
+def dwn_layer_eval(x: torch.Tensor, tables: torch.Tensor, plan: ConnectionPlan) -> torch.Tensor:
+    """Eval forward on {0,1} inputs: bit-sliced hard LUTs, fp32 {0,1} rows out (dwn_node.py:457-483)."""
+    x = x.contiguous().float()
+    tables = tables.detach().contiguous().float()
+    B, I = x.shape
+    NO, n = plan.N * plan.O, plan.n
+    Bp = _native.padded_batch(B)
+    with torch.cuda.device(x.device):
+        bits = torch.empty(I, Bp // 32, device=x.device, dtype=torch.int32)
+        _native.call("dl_pack_rows_to_t", x, bits, B, I, Bp, 0.5)
+        masks = torch.empty(NO, device=x.device, dtype=torch.int64)
+        _native.call("dl_dwn_prepare", tables, None, masks, NO, n, 0.0, 0.0)
+        out_bits = torch.empty(NO, Bp // 32, device=x.device, dtype=torch.int32)
+        _native.call("dl_dwn_fwd_bits_t", bits, plan.map_virtual, masks, out_bits, NO, n, Bp)
+        out = torch.empty(B, NO, device=x.device, dtype=torch.float32)
+        _native.call("dl_bits_t_to_rows", out_bits, out, B, NO, Bp)
+    return out
+
+
+class ProbLayerFunction(torch.autograd.Function):
+    """RandomLayer(+Probabilistic) training forward/backward; optional fused GroupSum.
+
+    x (B, I) rows, raw (N, 2^n, O).  With `k` set the function returns the GroupSum logits
+    (B, k) instead of the node outputs, without writing the (B, N*O) tensor.
+    """
+
+    @staticmethod
+    def forward(ctx, x, raw, plan: ConnectionPlan, temperature: float, k: Optional[int], tau: float):
+        x = x.contiguous().float()
+        raw = raw.contiguous().float()
+        B, I = x.shape
+        N, n, O = plan.N, plan.n, plan.O
+        Bp = _native.padded_batch(B)
+        with torch.cuda.device(x.device):
+            x_t = _rows_to_t(x, Bp)
+            if k is None:
+                out_t = torch.empty(N * O, Bp, device=x.device, dtype=torch.float32)
+                _native.call("dl_prob_fwd_t", x_t, plan.map_nodes, raw, temperature, out_t, N, n, O, Bp)
+                out = _t_to_rows(out_t, B)
+            else:
+                S = _native.lib().dl_prob_groupsum_splits(N * O, k)
+                partial = torch.empty(k * S, Bp, device=x.device, dtype=torch.float32)
+                logits_t = torch.empty(k, Bp, device=x.device, dtype=torch.float32)
+                _native.call("dl_prob_fwd_groupsum_t", x_t, plan.map_nodes, raw, temperature, None, partial,
+                             logits_t, N, n, O, k, tau, Bp)
+                out = _t_to_rows(logits_t, B)
+        ctx.save_for_backward(x_t, raw)
+        ctx.plan, ctx.temperature, ctx.k, ctx.tau, ctx.B = plan, float(temperature), k, float(tau), B
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        x_t, raw = ctx.saved_tensors
+        plan, B, k = ctx.plan, ctx.B, ctx.k
+        N, n, O, I = plan.N, plan.n, plan.O, plan.input_size
+        Bp = x_t.shape[1]
+        need_x, need_r = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        gx = None
+        with torch.cuda.device(g.device):
+            g_t = _rows_to_t(g.contiguous().float(), Bp)
+            if k is None:
+                gdiv, gscale = 1, 1.0
+            else:
+                gdiv, gscale = (N * O + k - 1) // k, 1.0 / ctx.tau
+            graw = torch.empty_like(raw)
+            gxm_t = torch.empty(N * n, Bp, device=g.device, dtype=torch.float32) if need_x else None
+            _native.call("dl_prob_bwd_t", x_t, plan.map_nodes, raw, ctx.temperature, g_t, gdiv, gscale, graw,
+                         gxm_t, N, n, O, B, Bp)
+            if need_x:
+                gx_t = torch.empty(I, Bp, device=g.device, dtype=torch.float32)
+                _native.call("dl_seg_sum_t", gxm_t, plan.inv_ptr_nodes, plan.inv_ent_nodes, gx_t, I, Bp)
+                gx = _t_to_rows(gx_t, B)
+        return gx, (graw if need_r else None), None, None, None, None
+
+
+class GatherFunction(torch.autograd.Function):
+    """x (B, I) -> (B, N, n): the materialised mapping `get_mapping` returns.
+
+    Counterpart of MappingFunction (difflut/layers/random_layer.py:34-100); the backward is a
+    segmented sum over the inverse map instead of fp32 atomics.
+    """
+
+    @staticmethod
+    def forward(ctx, x, plan: ConnectionPlan):
+        x = x.contiguous().float()
+        B, I = x.shape
+        out = torch.empty(B, plan.N, plan.n, device=x.device, dtype=torch.float32)
+        with torch.cuda.device(x.device):
+            _native.call("dl_gather_rows", x, plan.map_nodes, out, B, I, plan.N, plan.n)
+        ctx.plan, ctx.B = plan, B
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        plan, B = ctx.plan, ctx.B
+        g = g.contiguous().float()
+        gx = torch.empty(B, plan.input_size, device=g.device, dtype=torch.float32)
+        with torch.cuda.device(g.device):
+            _native.call("dl_gather_rows_bwd", g, plan.inv_ptr_nodes, plan.inv_ent_nodes, gx, B,
+                         plan.input_size, plan.N, plan.n)
+        return gx, None

@@ -1,0 +1,276 @@
+"""Fused execution of an encoder -> RandomLayer(DWN) x L -> GroupSum classifier.
+
+The per-layer API (`RandomLayer.forward`) is exact to the reference's tensors: fp32 rows in and
+out of every layer.  A DWN layer only looks at `input >= 0.5`, so between layers one bit per
+activation is enough; this module runs the same kernels on that representation end to end:
+
+  forward   thermometer compare-and-pack -> bit-sliced hard LUT layers -> last layer fused with
+            GroupSum (logits), one kernel per layer, activations bit-packed feature-major;
+  backward  cross-entropy, then per layer one table-gradient kernel (lane-private histograms)
+            and one input-gradient kernel (segmented pull over the inverse map using the
+            per-step EFD transform); gradients are fp32 feature-major;
+  update    table gradients of all layers live in ONE flat buffer which is all-reduced (NCCL,
+            data parallel over the batch) and consumed by one fused Adam kernel.
+
+The parameters are the layers' own `luts` tensors (re-pointed into the flat buffer), so the
+API objects and this executor always see the same tables.  Equivalent reference code: user
+model + loop as in examples/demo_probabilistic_random.py:111-178 with DWN nodes.
+"""
+
+from typing import List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from . import _native
+from .distributed import allreduce_sum_
+from .encoder.thermometer import ThermometerEncoder
+from .layers.random_layer import RandomLayer
+from .utils.modules import GroupSum
+
+
+class DWNNetwork:
+    def __init__(self, encoder: ThermometerEncoder, layers: Sequence[RandomLayer], groupsum: GroupSum,
+                 lr: float = 1e-2, betas=(0.9, 0.999), eps: float = 1e-8,
+                 process_group: Optional["dist.ProcessGroup"] = None, distributed: Optional[bool] = None):
+        if not encoder.is_fitted:
+            raise RuntimeError("DWNNetwork needs a fitted encoder")
+        if groupsum.use_randperm:
+            raise ValueError("DWNNetwork does not support GroupSum(use_randperm=True)")
+        for l in layers:
+            if l._stacked != "dwn" or l.n > 6 or l.output_dim_per_node != 1:
+                raise ValueError("DWNNetwork takes RandomLayer(DWNNode) layers with n <= 6 and output_dim 1")
+        self.encoder, self.layers, self.groupsum = encoder, list(layers), groupsum
+        self.device = self.layers[0].luts.device
+        if self.device.type != "cuda":
+            raise RuntimeError("DWNNetwork needs its layers on a CUDA device (no CPU fallback)")
+        self.lr, self.betas, self.eps = float(lr), (float(betas[0]), float(betas[1])), float(eps)
+        self.k, self.tau = int(groupsum.k), float(groupsum.tau)
+        self.group = process_group
+        if distributed is None:
+            distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(process_group) > 1
+        self.distributed = bool(distributed)
+        self.world = dist.get_world_size(process_group) if self.distributed else 1
+
+        thr = encoder.thresholds.reshape(-1, encoder.num_bits)
+        self.thr = thr.to(device=self.device, dtype=torch.float32).contiguous()
+        self.F, self.T = int(self.thr.shape[0]), int(encoder.num_bits)
+        sizes_in = [self.F * self.T] + [l.output_size for l in self.layers[:-1]]
+        for l, i in zip(self.layers, sizes_in):
+            if l.input_size != i:
+                raise ValueError(f"layer input_size {l.input_size} does not match the {i} features feeding it")
+        self.n = [l.n for l in self.layers]
+        self.N = [l.output_size for l in self.layers]
+        self.I = sizes_in
+        self.L = [2 ** n for n in self.n]
+
+        # one flat buffer for all tables / gradients / Adam moments; the layers' parameters view it
+        counts = [N * L for N, L in zip(self.N, self.L)]
+        self.offsets = [0]
+        for c in counts:
+            self.offsets.append(self.offsets[-1] + c)
+        total = self.offsets[-1]
+        self.flat = torch.empty(total, device=self.device, dtype=torch.float32)
+        self.flat_grad = torch.zeros(total, device=self.device, dtype=torch.float32)
+        self.exp_avg = torch.zeros(total, device=self.device, dtype=torch.float32)
+        self.exp_avg_sq = torch.zeros(total, device=self.device, dtype=torch.float32)
+        self.adam_state = torch.ones(2, device=self.device, dtype=torch.float64)
+        self.tables, self.grads = [], []
+        for li, l in enumerate(self.layers):
+            sl = slice(self.offsets[li], self.offsets[li + 1])
+            view = self.flat[sl].view(self.N[li], 1, self.L[li])
+            view.copy_(l.luts.data)
+            l.luts.data = view
+            gview = self.flat_grad[sl].view(self.N[li], 1, self.L[li])
+            l.luts.grad = gview
+            self.tables.append(view)
+            self.grads.append(gview)
+        self.plans = [l._plan(self.device) for l in self.layers]
+        self.alpha = [l.alpha for l in self.layers]
+        self.beta = [l.beta for l in self.layers]
+        self.masks = [torch.empty(N, device=self.device, dtype=torch.int64) for N in self.N]
+        self.efd = [torch.empty(N, n, 32, device=self.device, dtype=torch.float32) if li > 0 else None
+                    for li, (N, n) in enumerate(zip(self.N, self.n))]
+        self.gsz = (self.N[-1] + self.k - 1) // self.k
+        self.splits = int(_native.lib().dl_dwn_groupsum_splits(self.N[-1], self.k))
+        self._B = None
+        self._graph = None
+        self.step_count = 0
+
+    # ------------------------------------------------------------------ buffers
+    def _ensure_buffers(self, B: int) -> None:
+        if self._B == B:
+            return
+        dev = self.device
+        Bp = _native.padded_batch(B)
+        Wp = Bp // 32
+        self.Bp = Bp
+        self.bits = [torch.empty(self.I[0], Wp, device=dev, dtype=torch.int32)]
+        for N in self.N[:-1]:
+            self.bits.append(torch.empty(N, Wp, device=dev, dtype=torch.int32))
+        self.last_bits = torch.empty(self.N[-1], Wp, device=dev, dtype=torch.int32)
+        # gradient w.r.t. the output of layer li (li < last), produced by layer li+1's backward
+        self.gact = [torch.empty(N, Bp, device=dev, dtype=torch.float32) for N in self.N[:-1]]
+        self.addr = [None] + [torch.empty(N, Bp, device=dev, dtype=torch.uint8) for N in self.N[1:]]
+        self.partial = torch.empty(self.k * self.splits, Bp, device=dev, dtype=torch.float32)
+        self.logits_t = torch.empty(self.k, Bp, device=dev, dtype=torch.float32)
+        self.dlogits_t = torch.empty(self.k, Bp, device=dev, dtype=torch.float32)
+        self.loss_rows = torch.empty(Bp, device=dev, dtype=torch.float32)
+        self.loss = torch.zeros(1, device=dev, dtype=torch.float32)
+        self.x_static = torch.empty(B, self.F, device=dev, dtype=torch.float32)
+        self.y_static = torch.empty(B, device=dev, dtype=torch.int32)
+        self._B = B
+        self._graph = None
+
+    # ------------------------------------------------------------------ kernels
+    def _prepare_tables(self, need_efd: bool) -> None:
+        last = len(self.layers) - 1
+        for li in range(len(self.layers)):
+            efd = self.efd[li] if (need_efd and li > 0) else None
+            masks = self.masks[li] if li < last or not need_efd else None
+            if efd is None and masks is None:
+                continue
+            _native.call("dl_dwn_prepare", self.tables[li], efd, masks, self.N[li], self.n[li],
+                         self.alpha[li], self.beta[li])
+
+    def _forward(self, x: torch.Tensor, B: int) -> None:
+        Bp = self.Bp
+        _native.call("dl_thermo_pack_t", x, self.thr, self.bits[0], B, self.F, self.T, Bp)
+        last = len(self.layers) - 1
+        for li in range(last):
+            _native.call("dl_dwn_fwd_bits_t", self.bits[li], self.plans[li].map_nodes, self.masks[li],
+                         self.bits[li + 1], self.N[li], self.n[li], Bp)
+        _native.call("dl_dwn_fwd_groupsum_t", self.bits[last], self.plans[last].map_nodes, self.tables[last],
+                     self.partial, self.logits_t, self.N[last], self.n[last], self.k, self.tau, Bp)
+
+    def _backward(self) -> None:
+        Bp = self.Bp
+        last = len(self.layers) - 1
+        for li in range(last, -1, -1):
+            if li == last:
+                g, gdiv, gscale = self.dlogits_t, self.gsz, 1.0 / self.tau
+            else:
+                g, gdiv, gscale = self.gact[li], 1, 1.0
+            _native.call("dl_dwn_bwd_tables_t", self.bits[li], self.plans[li].map_nodes, g, gdiv, gscale,
+                         self.grads[li], self.addr[li], self.N[li], self.n[li], Bp)
+            if li > 0:
+                _native.call("dl_dwn_bwd_input_t", self.addr[li], g, gdiv, gscale, self.efd[li],
+                             self.plans[li].inv_ptr_nodes, self.plans[li].inv_ent_nodes, self.gact[li - 1],
+                             self.I[li], self.n[li], Bp)
+
+    def _step_body(self, B: int, B_global: int) -> None:
+        self._prepare_tables(need_efd=True)
+        self._forward(self.x_static, B)
+        _native.call("dl_ce_t", self.logits_t, self.y_static, self.dlogits_t, self.loss_rows, self.loss,
+                     B, B_global, self.k, self.Bp)
+        self._backward()
+        if self.distributed:
+            # sum of per-rank gradients of the GLOBAL-mean loss (dl_ce_t divides by B_global)
+            allreduce_sum_(self.flat_grad, self.group)
+        _native.call("dl_adam_step", self.flat, self.flat_grad, self.exp_avg, self.exp_avg_sq, self.adam_state,
+                     self.flat.numel(), self.lr, self.betas[0], self.betas[1], self.eps, 1.0)
+
+    # ------------------------------------------------------------------ public API
+    KERNELS_PER_STEP_NOTE = "prepare xL, pack, fwd xL(+reduce), ce x2, bwd tables xL, bwd input x(L-1), adam x2"
+
+    def kernel_launches_per_step(self) -> int:
+        L = len(self.layers)
+        return L + 1 + (L - 1) + 2 + 2 + L + (L - 1) + 2
+
+    def train_step(self, x: torch.Tensor, labels: torch.Tensor, use_graph: bool = False) -> torch.Tensor:
+        """One optimisation step on this rank's shard (x (B, F) fp32, labels (B,) integer).
+
+        Returns the 1-element device tensor holding this rank's share of the global mean loss
+        (sum over ranks = global mean).  With `use_graph` the step is captured once per batch
+        size into a CUDA graph and replayed.
+        """
+        B = int(x.shape[0])
+        with torch.cuda.device(self.device):
+            self._ensure_buffers(B)
+            self.x_static.copy_(x, non_blocking=True)
+            self.y_static.copy_(labels, non_blocking=True)
+            B_global = B * self.world
+            if not use_graph:
+                self._step_body(B, B_global)
+            else:
+                if self._graph is None:
+                    self._capture(B, B_global)
+                self._graph.replay()
+        self.step_count += 1
+        return self.loss
+
+    def _capture(self, B: int, B_global: int) -> None:
+        # run once eagerly on a side stream (warms NCCL and the allocator), restoring the state after
+        snap = (self.flat.clone(), self.exp_avg.clone(), self.exp_avg_sq.clone(), self.adam_state.clone())
+        s = torch.cuda.Stream(device=self.device)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self._step_body(B, B_global)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize(self.device)
+        self.flat.copy_(snap[0]); self.exp_avg.copy_(snap[1]); self.exp_avg_sq.copy_(snap[2])
+        self.adam_state.copy_(snap[3])
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._step_body(B, B_global)
+        self._graph = graph
+
+    @torch.no_grad()
+    def logits(self, x: torch.Tensor) -> torch.Tensor:
+        """Training-mode logits (B, k) fp32 = GroupSum(last layer's raw table values)."""
+        B = int(x.shape[0])
+        with torch.cuda.device(self.device):
+            self._ensure_buffers(B)
+            self._prepare_tables(need_efd=False)
+            self._forward(x.contiguous().float(), B)
+            out = torch.empty(B, self.k, device=self.device, dtype=torch.float32)
+            _native.call("dl_f32_t_to_rows", self.logits_t, out, B, self.k, self.Bp)
+        return out
+
+    @torch.no_grad()
+    def hard_counts(self, x: Optional[torch.Tensor] = None, packed_rows: Optional[torch.Tensor] = None,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Eval-mode class counts (B, k) int32 of the binarised network (every table >= 0.5).
+
+        Input is either raw features x (B, F) fp32 or thermometer bits already packed as rows
+        (B, ceil(F*T/32)) int32 with bit c%32 of word c//32 = encoded column c.
+        """
+        with torch.cuda.device(self.device):
+            if packed_rows is not None:
+                B = int(packed_rows.shape[0])
+                self._ensure_buffers(B)
+                _native.call("dl_bits_rows_to_t", packed_rows, self.bits[0], B, self.I[0],
+                             packed_rows.shape[1], self.Bp)
+            else:
+                B = int(x.shape[0])
+                self._ensure_buffers(B)
+                _native.call("dl_thermo_pack_t", x.contiguous().float(), self.thr, self.bits[0], B, self.F,
+                             self.T, self.Bp)
+            for li in range(len(self.layers)):
+                _native.call("dl_dwn_prepare", self.tables[li], None, self.masks[li], self.N[li], self.n[li], 0.0, 0.0)
+            cur = self.bits[0]
+            for li in range(len(self.layers)):
+                nxt = self.bits[li + 1] if li + 1 < len(self.layers) else self.last_bits
+                _native.call("dl_dwn_fwd_bits_t", cur, self.plans[li].map_nodes, self.masks[li], nxt,
+                             self.N[li], self.n[li], self.Bp)
+                cur = nxt
+            if out is None:
+                out = torch.empty(B, self.k, device=self.device, dtype=torch.int32)
+            _native.call("dl_popcount_groupsum_t", cur, out, self.N[-1], self.k, B, self.Bp)
+        return out
+
+    def algorithmic_bytes_per_step(self, B: int) -> int:
+        """HBM bytes one training step must move in this (bit-packed) mode: per sample
+        encoder 4F + FT/8; hidden layer forward I/8 + N/8, last layer forward I/8 + 4k;
+        backward per layer 4N (0 for the last: its gradient is the k logits' gradient) + I/8
+        + 4I (0 for the first layer); per step tables read (forward, transform) and gradient
+        written, index maps, and Adam's 7 passes over the tables."""
+        per_sample = 4 * self.F + self.I[0] / 8
+        last = len(self.layers) - 1
+        for li in range(len(self.layers)):
+            per_sample += self.I[li] / 8 + (4 * self.k if li == last else self.N[li] / 8)
+            per_sample += (4 * self.k if li == last else 4 * self.N[li]) + self.I[li] / 8
+            per_sample += 4 * self.I[li] if li > 0 else 0
+        table_bytes = 4 * self.flat.numel()
+        per_step = 3 * table_bytes + 7 * table_bytes + sum(2 * 4 * N * n for N, n in zip(self.N, self.n))
+        return int(per_sample * B + per_step)

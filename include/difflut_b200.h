@@ -1,0 +1,226 @@
+/*
+ * difflut_b200 — C ABI of the B200 (sm_100a) kernels for DiffLUT's LUT-network hot path.
+ *
+ * Conventions for every entry point
+ *   - plain pointers and sizes; all pointers are DEVICE pointers unless a comment says host;
+ *   - the caller allocates every input, output and scratch buffer; nothing here allocates,
+ *     synchronises or keeps state (exception: the one function documented as such);
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*), in stream order;
+ *   - the return value is DL_OK or a negative DL_ERR_* code; the Python shim raises
+ *     RuntimeError from it (the reference's bindings raise RuntimeError via TORCH_CHECK,
+ *     difflut/nodes/cuda/efd_cuda.cpp:18-40).
+ *
+ * Layouts
+ *   "rows"   row-major (B, F) fp32 — the reference's tensor layout at every API edge.
+ *   "t"      feature-major: fp32 [F][Bp] or bit-packed uint32 [F][Bp/32] where bit (b%32) of
+ *            word b/32 of row f is sample b of feature f.  Bp = dl_padded_batch(B) (multiple of
+ *            128); padded samples hold 0 bits / 0.0 gradients.
+ *   tables   DWN: (N, 2^n) fp32, entry index = LUT address, address bit i = node input slot i
+ *            (LSB first; difflut/nodes/dwn_node.py:147-153).  A node with several outputs is
+ *            passed as several rows that share one row of the index map.
+ *   map      (N, n) int32 indices into the layer input (difflut/layers/random_layer.py:195-256).
+ */
+#ifndef DIFFLUT_B200_H
+#define DIFFLUT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* dl_stream_t; /* cudaStream_t */
+
+enum {
+    DL_OK = 0,
+    DL_ERR_ARG = -1,         /* null pointer, non-positive size, inconsistent sizes      */
+    DL_ERR_UNSUPPORTED = -2, /* n outside the supported range of this entry point         */
+    DL_ERR_LAUNCH = -3,      /* cudaPeekAtLastError reported a failure after the launch   */
+    DL_ERR_ALIGN = -4,       /* a pointer or stride misses the documented alignment       */
+    DL_ERR_TOO_LARGE = -5    /* size beyond a documented fixed capacity                   */
+};
+
+#define DL_BATCH_ALIGN 128 /* samples; Bp is a multiple of this */
+#define DL_MAX_FAST_N 6    /* n <= 6: tables are 64-bit words / 32-lane shuffles */
+
+int dl_version(void);
+const char* dl_error_string(int code);
+int64_t dl_padded_batch(int64_t B);
+
+/* ------------------------------------------------------------------ thermometer encoder
+ * Replaces ThermometerEncoder.encode (difflut/encoder/thermometer.py:89-116):
+ * bit[b, f*T+i] = x[b,f] > thr[f,i] (strict).                                              */
+
+/* rows in, rows out: out (B, F*T) fp32 {0,1} — the reference's exact output tensor. */
+int dl_thermo_rows(const float* x, const float* thr, float* out, int64_t B, int64_t F, int64_t T,
+                   dl_stream_t stream);
+/* rows in, packed feature-major out: bits_t [F*T][Bp/32]. */
+int dl_thermo_pack_t(const float* x, const float* thr, uint32_t* bits_t, int64_t B, int64_t F,
+                     int64_t T, int64_t Bp, dl_stream_t stream);
+/* rows in, packed row-major out: bits (B, ceil(F*T/32)) uint32, bit (c%32) of word c/32. */
+int dl_thermo_pack_rows(const float* x, const float* thr, uint32_t* bits, int64_t B, int64_t F,
+                        int64_t T, dl_stream_t stream);
+
+/* ------------------------------------------------------------------ layout changes
+ * No counterpart in the reference (it keeps fp32 rows everywhere).                         */
+
+/* x (B, F) fp32 rows -> bits_t [F][Bp/32] with bit = x >= threshold (DWN uses 0.5,
+ * difflut/nodes/dwn_node.py:147). */
+int dl_pack_rows_to_t(const float* x, uint32_t* bits_t, int64_t B, int64_t F, int64_t Bp,
+                      float threshold, dl_stream_t stream);
+/* fp32 rows (B, F) <-> fp32 feature-major [F][Bp]; padding columns are written as 0. */
+int dl_f32_rows_to_t(const float* rows, float* t, int64_t B, int64_t F, int64_t Bp,
+                     dl_stream_t stream);
+int dl_f32_t_to_rows(const float* t, float* rows, int64_t B, int64_t F, int64_t Bp,
+                     dl_stream_t stream);
+/* bits_t [F][Bp/32] -> fp32 rows (B, F) of {0,1}. */
+int dl_bits_t_to_rows(const uint32_t* bits_t, float* rows, int64_t B, int64_t F, int64_t Bp,
+                      dl_stream_t stream);
+/* packed rows (B, Wr) uint32 (bit c%32 of word c/32 = column c) -> bits_t [F][Bp/32]. */
+int dl_bits_rows_to_t(const uint32_t* bits_rows, uint32_t* bits_t, int64_t B, int64_t F,
+                      int64_t Wr, int64_t Bp, dl_stream_t stream);
+
+/* ------------------------------------------------------------------ RandomLayer gather
+ * Replaces mapping_cuda.forward / .backward (difflut/layers/cuda/mapping_cuda.cpp:69-74,
+ * kernels difflut/layers/cuda/mapping_cuda_kernel.cu:30-56,136-162):
+ * out[b,j,i] = x[b, map[j,i]];  backward gx[b,f] = sum over (j,i) with map[j,i]==f.
+ * The backward is a segmented sum over the inverse map (CSR: inv_ptr (F+1), inv_ent holds
+ * j*n+i), so it is atomics-free and reproducible.                                          */
+int dl_gather_rows(const float* x, const int32_t* map, float* out, int64_t B, int64_t F, int64_t N,
+                   int64_t n, dl_stream_t stream);
+int dl_gather_rows_bwd(const float* g, const int32_t* inv_ptr, const int32_t* inv_ent, float* gx,
+                       int64_t B, int64_t F, int64_t N, int64_t n, dl_stream_t stream);
+
+/* ------------------------------------------------------------------ DWN node, feature-major path
+ * Together these replace the per-node efd_cuda.forward / .backward calls of a whole layer
+ * (difflut/nodes/cuda/efd_cuda.cpp:22-45) and the layer-wide efd_fused_cuda.forward /
+ * .backward (difflut/nodes/cuda/efd_fused_cuda.cpp:19-34).  n <= DL_MAX_FAST_N.            */
+
+/* Once per step: tables (N, 2^n) -> efd_t (N, n, 32) and masks (N) uint64.
+ * efd_t[j,i,a'] = alpha * sum_k sgn(k_i) * tables[j,k] * beta^popc((a^k) & ~(1<<i)) where a'
+ * is the address a with bit i removed (the value does not depend on bit i;
+ * difflut/nodes/dwn_node.py:195-227).  Rows a' >= 2^(n-1) are zero.
+ * masks[j] bit a = tables[j,a] >= 0.5 (difflut/nodes/dwn_node.py:481).
+ * Either output pointer may be null. */
+int dl_dwn_prepare(const float* tables, float* efd_t, uint64_t* masks, int64_t N, int64_t n,
+                   float alpha, float beta, dl_stream_t stream);
+
+/* Hard forward on packed bits: out_bits_t[j] = masks[j] looked up at the address formed from
+ * rows map[j,0..n-1] of in_bits_t, 32 samples per word at a time (bit-sliced). */
+int dl_dwn_fwd_bits_t(const uint32_t* in_bits_t, const int32_t* map, const uint64_t* masks,
+                      uint32_t* out_bits_t, int64_t N, int64_t n, int64_t Bp, dl_stream_t stream);
+
+/* Training forward: out_t[j][b] = tables[j, addr(b,j)] (raw value, no clamp;
+ * difflut/nodes/dwn_node.py:158).  addr_t [N][Bp] uint8 is optional (null = not written). */
+int dl_dwn_fwd_vals_t(const uint32_t* in_bits_t, const int32_t* map, const float* tables,
+                      float* out_t, uint8_t* addr_t, int64_t N, int64_t n, int64_t Bp,
+                      dl_stream_t stream);
+
+/* Table gradient: gt[j,e] = sum over samples with addr(b,j)==e of g(b,j)
+ * (difflut/nodes/dwn_node.py:190-192).  g(b,j) = gscale * g_t[(j / gdiv)][b]: gdiv = 1 reads
+ * an [N][Bp] gradient; gdiv = group size reads the [k][Bp] gradient of a following GroupSum
+ * without materialising its broadcast.  Overwrites gt.  Also writes addr_t [N][Bp] (the
+ * addresses the input-gradient kernel consumes) when addr_t is not null.  Lane-private
+ * histograms, fixed summation order: run-to-run reproducible. */
+int dl_dwn_bwd_tables_t(const uint32_t* in_bits_t, const int32_t* map, const float* g_t,
+                        int64_t gdiv, float gscale, float* gt, uint8_t* addr_t, int64_t N,
+                        int64_t n, int64_t Bp, dl_stream_t stream);
+
+/* Input gradient (EFD): gx_t[f][b] = sum over (j,i) with map[j,i]==f of
+ * g(b,j) * efd_t[j,i,addr(b,j) without bit i]  (difflut/nodes/dwn_node.py:194-227 followed by
+ * the gather's scatter-add, difflut/layers/random_layer.py:301-302), as a segmented sum over
+ * the inverse map (inv_ptr (F+1), inv_ent = j*n+i, the same CSR dl_gather_rows_bwd takes).
+ * Overwrites gx_t. */
+int dl_dwn_bwd_input_t(const uint8_t* addr_t, const float* g_t, int64_t gdiv, float gscale,
+                       const float* efd_t, const int32_t* inv_ptr, const int32_t* inv_ent,
+                       float* gx_t, int64_t F, int64_t n, int64_t Bp, dl_stream_t stream);
+
+/* ------------------------------------------------------------------ DWN node, materialised-input path
+ * Replaces efd_cuda.forward(input, luts) / .backward(input, luts, grad_output, alpha, beta)
+ * (difflut/nodes/cuda/efd_cuda.cpp:22-45) for N nodes at once on inputs that are already
+ * mapped: xm (B, N, n) fp32 rows (what get_mapping returns,
+ * difflut/layers/random_layer.py:258-304 / learnable_layer.py:392-413).
+ * tables (N, O, L), out (B, N, O), L = 2^n, n <= 16.                                        */
+int dl_dwn_mapped_fwd(const float* xm, const float* tables, float* out, int64_t B, int64_t N,
+                      int64_t n, int64_t O, int eval_mode, dl_stream_t stream);
+/* gxm (B,N,n) and gt (N,O,L) are overwritten.  efd_full (N, O, L, n) is the full transform
+ * written by dl_dwn_prepare_full (caller-provided scratch). */
+int dl_dwn_prepare_full(const float* tables, float* efd_full, int64_t NO, int64_t n, float alpha,
+                        float beta, dl_stream_t stream);
+int dl_dwn_mapped_bwd(const float* xm, const float* g, const float* efd_full, float* gxm,
+                      float* gt, int64_t B, int64_t N, int64_t n, int64_t O, dl_stream_t stream);
+
+/* ------------------------------------------------------------------ Probabilistic node
+ * Replaces probabilistic_cuda.forward(input, raw_weights, temperature) / .backward(...)
+ * (difflut/nodes/cuda/probabilistic_cuda.cpp:44-49) for a whole layer, fused with the
+ * RandomLayer gather.  Parity target is the reference's PyTorch path
+ * (difflut/nodes/probabilistic_node.py:263-300, backward = autograd): no input clamping, input
+ * gradient by the product rule (finite at x in {0,1}).
+ * x_t [F][Bp] fp32; raw (N, 2^n, O) fp32 (the reference's per-node (2^n, O) tables stacked);
+ * outputs are indexed by the virtual node v = j*O + o.  n <= DL_MAX_FAST_N.                  */
+int dl_prob_fwd_t(const float* x_t, const int32_t* map, const float* raw, float temperature,
+                  float* out_t, int64_t N, int64_t n, int64_t O, int64_t Bp, dl_stream_t stream);
+/* Forward fused with the following GroupSum (difflut/utils/modules.py:116-163):
+ * logits_t [k][Bp] = (1/tau) * class sums.  `partial` is caller-provided scratch of
+ * k*dl_prob_groupsum_splits(N*O,k)*Bp floats; out_t [N*O][Bp] is optional (null = not written). */
+int64_t dl_prob_groupsum_splits(int64_t NO, int64_t k);
+int dl_prob_fwd_groupsum_t(const float* x_t, const int32_t* map, const float* raw, float temperature,
+                           float* out_t, float* partial, float* logits_t, int64_t N, int64_t n,
+                           int64_t O, int64_t k, float tau, int64_t Bp, dl_stream_t stream);
+/* Backward: graw (N, 2^n, O) (overwritten) and gxm_t [N*n][Bp], the gradient w.r.t. each node's
+ * mapped input slot, summed over the node's outputs (overwritten).  g(b,v) = gscale *
+ * g_t[v / gdiv][b] as for the DWN kernels.  Either output may be null. */
+int dl_prob_bwd_t(const float* x_t, const int32_t* map, const float* raw, float temperature,
+                  const float* g_t, int64_t gdiv, float gscale, float* graw, float* gxm_t, int64_t N,
+                  int64_t n, int64_t O, int64_t B, int64_t Bp, dl_stream_t stream);
+/* gx_t[f][b] = sum over the inverse-map entries e of feature f of src_t[inv_ent[e]][b]: the
+ * scatter-add of the gather (difflut/layers/cuda/mapping_cuda_kernel.cu:136-162) as an
+ * atomics-free segmented sum in the feature-major layout. */
+int dl_seg_sum_t(const float* src_t, const int32_t* inv_ptr, const int32_t* inv_ent, float* gx_t,
+                 int64_t F, int64_t Bp, dl_stream_t stream);
+
+/* ------------------------------------------------------------------ GroupSum / loss / optimiser
+ * GroupSum.forward (difflut/utils/modules.py:116-163): zero-pad F to a multiple of k, class c
+ * sums the contiguous block of g = ceil(F/k) columns, divided by tau.                      */
+int dl_groupsum_rows(const float* x, float* out, int64_t B, int64_t F, int64_t k, float tau,
+                     dl_stream_t stream);
+int dl_groupsum_rows_bwd(const float* gout, float* gx, int64_t B, int64_t F, int64_t k, float tau,
+                         dl_stream_t stream);
+/* feature-major: vals_t [F][Bp] -> logits_t [k][Bp]. */
+int dl_groupsum_t(const float* vals_t, float* logits_t, int64_t F, int64_t k, float tau, int64_t Bp,
+                  dl_stream_t stream);
+/* Fused last layer: logits_t[c][b] = (1/tau) * sum_{j in class c} tables[j, addr(b,j)].
+ * `partial` is caller-provided scratch of k*splits*Bp floats (splits from
+ * dl_dwn_groupsum_splits); each CTA sums one slice of a class in a fixed order and a second
+ * pass adds the slices, so the result is reproducible. */
+int64_t dl_dwn_groupsum_splits(int64_t N, int64_t k);
+int dl_dwn_fwd_groupsum_t(const uint32_t* in_bits_t, const int32_t* map, const float* tables,
+                          float* partial, float* logits_t, int64_t N, int64_t n, int64_t k,
+                          float tau, int64_t Bp, dl_stream_t stream);
+
+/* Mean cross-entropy over `B_global` samples of which this call holds B (user code in the
+ * reference: nn.CrossEntropyLoss, e.g. tests/test_layers/test_convolutional_learning.py:85-111).
+ * logits_t [k][Bp]; labels (B) int32; writes dlogits_t [k][Bp] = (softmax - onehot)/B_global
+ * (0 in padding), loss_rows [Bp] per-sample losses and loss[0] = sum(loss_rows)/B_global. */
+int dl_ce_t(const float* logits_t, const int32_t* labels, float* dlogits_t, float* loss_rows,
+            float* loss, int64_t B, int64_t B_global, int64_t k, int64_t Bp, dl_stream_t stream);
+
+/* torch.optim.Adam step (no weight decay / amsgrad) over a flat fp32 tensor.  `state` is a
+ * device array of 2 doubles {beta1^t, beta2^t}, initialised to {1, 1}; every call multiplies
+ * them on the device first (so a captured CUDA graph can be replayed step after step).
+ * g is multiplied by gscale before use (1/world after a sum all-reduce). */
+int dl_adam_step(float* p, const float* g, float* m, float* v, double* state, int64_t count,
+                 float lr, float beta1, float beta2, float eps, float gscale, dl_stream_t stream);
+
+/* ------------------------------------------------------------------ bit-packed hard-LUT inference
+ * The per-layer kernel is dl_dwn_fwd_bits_t.  Class counts of the last layer's packed outputs:
+ * counts (B, k) int32, counts[b,c] = number of nodes of class c (contiguous blocks of ceil(N/k))
+ * whose output bit is 1 = GroupSum(k, tau=1) of the reference's eval-mode outputs
+ * (difflut/nodes/dwn_node.py:457-483, difflut/utils/modules.py:158-163).                   */
+int dl_popcount_groupsum_t(const uint32_t* bits_t, int32_t* counts, int64_t N, int64_t k, int64_t B,
+                           int64_t Bp, dl_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DIFFLUT_B200_H */

@@ -1,0 +1,441 @@
+"""GPU parity: every CUDA path, called through the public API (which calls the C ABI), against the
+golden fixtures produced by the reference and against the CPU oracle on seeded inputs.
+
+Bars: bit-exact for bits, addresses (observable through exact table values), index maps and hard
+outputs; rtol 1e-5 (+ small atol for near-zero sums) for fp32 outputs; rtol 1e-4 where fp32
+summation order differs over long reductions (gradients summed over the batch).
+"""
+
+import warnings
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import difflut_oracle as O
+
+pytestmark = pytest.mark.gpu
+warnings.simplefilter("ignore")
+
+
+def T(a):
+    return torch.from_numpy(np.asarray(a))
+
+
+@pytest.fixture(scope="module")
+def dev():
+    return torch.device("cuda", 0)
+
+
+def _layer(dev, I, N, n, O_, node, mapping, extra=None):
+    from difflut_b200.layers import RandomLayer
+    from difflut_b200.nodes import NodeConfig
+
+    cfg = NodeConfig(input_dim=n, output_dim=O_, extra_params=extra or {})
+    return RandomLayer(I, N, node, cfg, seed=0, mapping_indices=mapping).to(dev)
+
+
+# ------------------------------------------------------------------------------ encoder
+def test_thermometer_bits_exact(golden, dev):
+    from difflut_b200.encoder import ThermometerEncoder
+
+    g = golden("thermometer")
+    for nb in (1, 3, 8):
+        enc = ThermometerEncoder(num_bits=nb).fit(T(g[f"x_fit_T{nb}"]))
+        assert torch.equal(enc.thresholds, T(g[f"thr_T{nb}"]))
+        x = T(g[f"x_T{nb}"]).to(dev)
+        bits = enc.to(dev).encode(x)
+        assert bits.dtype == torch.float32 and bits.shape == (x.shape[0], x.shape[1] * nb)
+        assert np.array_equal(bits.cpu().numpy().astype(np.uint8), g[f"bits_T{nb}"])
+        packed_t = enc.encode_packed_t(x).cpu().numpy().view(np.uint32)
+        ref_t = O.pack_bits_feature_major(T(g[f"bits_T{nb}"]).float())
+        assert np.array_equal(packed_t[:, : ref_t.shape[1]], ref_t)
+        assert not packed_t[:, ref_t.shape[1]:].any(), "padding words must be zero"
+        packed_r = enc.encode_packed(x).cpu().numpy().view(np.uint32)
+        assert np.array_equal(packed_r, O.pack_bits_row_major(T(g[f"bits_T{nb}"]).float()))
+        enc3 = ThermometerEncoder(num_bits=nb, flatten=False).fit(T(g[f"x_fit_T{nb}"])).to(dev)
+        assert enc3.encode(x).shape == (x.shape[0], x.shape[1], nb)
+
+
+def test_thermometer_unfitted_raises(dev):
+    from difflut_b200.encoder import ThermometerEncoder
+
+    with pytest.raises(RuntimeError):
+        ThermometerEncoder(num_bits=2).encode(torch.rand(3, 4, device=dev))
+
+
+def test_layout_round_trips(dev):
+    from difflut_b200 import _native
+
+    gen = torch.Generator().manual_seed(1)
+    for B, F in ((1, 1), (37, 45), (300, 70), (129, 33)):
+        Bp = _native.padded_batch(B)
+        x = torch.rand(B, F, generator=gen).to(dev)
+        t = torch.full((F, Bp), 7.0, device=dev)
+        _native.call("dl_f32_rows_to_t", x, t, B, F, Bp)
+        assert torch.equal(t[:, :B].t(), x) and not t[:, B:].any()
+        back = torch.empty_like(x)
+        _native.call("dl_f32_t_to_rows", t, back, B, F, Bp)
+        assert torch.equal(back, x)
+        bits = torch.empty(F, Bp // 32, device=dev, dtype=torch.int32)
+        _native.call("dl_pack_rows_to_t", x, bits, B, F, Bp, 0.5)
+        ref = O.pack_bits_feature_major((x.cpu() >= 0.5).float())
+        got = bits.cpu().numpy().view(np.uint32)
+        assert np.array_equal(got[:, : ref.shape[1]], ref) and not got[:, ref.shape[1]:].any()
+        rows = torch.empty(B, F, device=dev)
+        _native.call("dl_bits_t_to_rows", bits, rows, B, F, Bp)
+        assert torch.equal(rows, (x >= 0.5).float())
+        pr = torch.from_numpy(O.pack_bits_row_major((x.cpu() >= 0.5).float()).view(np.int32)).to(dev)
+        bits2 = torch.empty_like(bits)
+        _native.call("dl_bits_rows_to_t", pr, bits2, B, F, pr.shape[1], Bp)
+        assert torch.equal(bits2, bits)
+
+
+# ------------------------------------------------------------------------------ DWN
+@pytest.mark.parametrize("tag", ["n6", "n4o2", "n2"])
+def test_dwn_layer_matches_reference(golden, dev, tag):
+    from difflut_b200.nodes import DWNNode
+
+    g = golden("dwn_layer")
+    x, idx, tab = T(g[f"{tag}_x"]), T(g[f"{tag}_map"]), T(g[f"{tag}_tables"])
+    N, O_, L = tab.shape
+    n = int(np.log2(L))
+    layer = _layer(dev, x.shape[1], N, n, O_, DWNNode, idx)
+    with torch.no_grad():
+        layer.luts.copy_(tab.to(dev))
+    assert torch.equal(layer._mapping_indices.cpu(), idx)
+    xg = x.to(dev).requires_grad_(True)
+    layer.train()
+    y = layer(xg)
+    assert torch.equal(y.cpu(), T(g[f"{tag}_y"])), "table values must be exact (addresses bit-exact)"
+    y.backward(T(g[f"{tag}_gy"]).to(dev))
+    torch.testing.assert_close(xg.grad.cpu(), T(g[f"{tag}_gx"]), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(layer.luts.grad.cpu(), T(g[f"{tag}_gtables"]), rtol=1e-5, atol=1e-6)
+    layer.eval()
+    ye = layer((x >= 0.5).float().to(dev))
+    assert np.array_equal(ye.cpu().numpy().astype(np.uint8), g[f"{tag}_y_eval"])
+    # the materialised path (get_mapping + node arithmetic) gives the same numbers
+    layer.train()
+    xg2 = x.to(dev).requires_grad_(True)
+    y2 = layer._run_nodes(layer.get_mapping(xg2))
+    assert torch.equal(y2, y)
+    y2.backward(T(g[f"{tag}_gy"]).to(dev))
+    torch.testing.assert_close(xg2.grad.cpu(), T(g[f"{tag}_gx"]), rtol=1e-5, atol=1e-6)
+    # per-node views: node(node_input) equals the layer's column
+    node = layer.nodes[1]
+    yn = node(layer.get_mapping(x.to(dev))[:, 1, :])
+    assert torch.equal(yn, y.detach().reshape(x.shape[0], N, O_)[:, 1, :])
+
+
+@pytest.mark.parametrize("n,O_", [(1, 1), (3, 2), (6, 1), (8, 1), (10, 2)])
+def test_dwn_standalone_node_vs_oracle(dev, n, O_):
+    from difflut_b200.nodes import DWNNode
+
+    gen = torch.Generator().manual_seed(n)
+    B = 50
+    x = torch.rand(B, n, generator=gen)
+    node = DWNNode(input_dim=n, output_dim=O_).to(dev)
+    tab = torch.randn(O_, 2 ** n, generator=gen)
+    with torch.no_grad():
+        node.luts.copy_(tab.to(dev))
+    xg = x.to(dev).requires_grad_(True)
+    node.train()
+    y = node(xg)
+    y_ref = O.dwn_forward(x.unsqueeze(1), tab.unsqueeze(0)).squeeze(1)
+    assert torch.equal(y.cpu(), y_ref)
+    gy = torch.randn(B, O_, generator=gen)
+    y.backward(gy.to(dev))
+    alpha, beta = 0.5 * 0.75 ** (n - 1), 0.25 / 0.75
+    gxm, gl = O.dwn_backward(x.unsqueeze(1), tab.unsqueeze(0), gy.unsqueeze(1), alpha, beta)
+    torch.testing.assert_close(xg.grad.cpu(), gxm.squeeze(1), rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(node.luts.grad.cpu(), gl.squeeze(0), rtol=1e-5, atol=1e-6)
+    node.eval()
+    xb = (x >= 0.5).float()
+    ye = node(xb.to(dev))
+    assert torch.equal(ye.cpu(), O.dwn_forward_eval(xb.unsqueeze(1), tab.unsqueeze(0)).squeeze(1))
+
+
+def test_dwn_residual_tables_pass_bit0(golden, dev):
+    from difflut_b200.nodes import DWNNode
+
+    node = DWNNode(input_dim=6, output_dim=1).to(dev).eval()
+    with torch.no_grad():
+        node.luts.copy_(T(golden("dwn_layer")["residual_tables"]).to(dev))
+    a = torch.arange(64)
+    pats = ((a[:, None] >> torch.arange(6)) & 1).float().to(dev)
+    assert torch.equal(node(pats)[:, 0], pats[:, 0])
+    import itertools
+
+    assert node.export_bitstream() == [p[0] for p in itertools.product([0, 1], repeat=6)]
+
+
+def test_dwn_config1_full_size_vs_oracle(dev):
+    """BASELINE config 1: B=256 x 784, T=3, 2000 nodes, multinomial map, loss = sum of outputs."""
+    from difflut_b200.encoder import ThermometerEncoder
+    from difflut_b200.layers import RandomLayer
+    from difflut_b200.nodes import DWNNode, NodeConfig
+
+    gen = torch.Generator().manual_seed(0)
+    x = torch.rand(256, 784, generator=gen)
+    enc = ThermometerEncoder(num_bits=3).fit(x)
+    layer = RandomLayer(2352, 2000, DWNNode, NodeConfig(input_dim=6, output_dim=1), seed=0,
+                        ensure_full_input_coverage=False).to(dev)
+    tab = torch.randn(2000, 1, 64, generator=gen)
+    with torch.no_grad():
+        layer.luts.copy_(tab.to(dev))
+    bits_ref = O.thermometer_encode(x, O.thermometer_thresholds(x, 3))
+    bits = enc.to(dev)(x.to(dev))
+    assert torch.equal(bits.cpu(), bits_ref)
+    idx = O.random_mapping(2352, 2000, 6, 0, False)
+    assert torch.equal(layer._mapping_indices.cpu(), idx)
+    bg = bits.clone().requires_grad_(True)
+    y = layer(bg)
+    xm = O.gather_mapping(bits_ref, idx)
+    assert torch.equal(y.cpu(), O.dwn_forward(xm, tab).reshape(256, -1))
+    y.sum().backward()
+    gxm, gl = O.dwn_backward(xm, tab, torch.ones(256, 2000, 1), 0.5 * 0.75 ** 5, 0.25 / 0.75)
+    torch.testing.assert_close(layer.luts.grad.cpu(), gl, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(bg.grad.cpu(), O.gather_mapping_backward(gxm, idx, 2352), rtol=1e-4, atol=1e-6)
+
+
+# ------------------------------------------------------------------------------ probabilistic
+def test_prob_layer_matches_reference(golden, dev):
+    from difflut_b200.nodes import ProbabilisticNode
+    from difflut_b200.utils import GroupSum
+
+    g = golden("prob_layer")
+    x, idx, raw = T(g["x"]), T(g["map"]), T(g["raw"])
+    layer = _layer(dev, x.shape[1], raw.shape[0], 6, 1, ProbabilisticNode, idx)
+    with torch.no_grad():
+        layer.raw_weights.copy_(raw.to(dev))
+    layer.train()
+    xg = x.to(dev).requires_grad_(True)
+    y = layer(xg)
+    torch.testing.assert_close(y.cpu(), T(g["y"]), rtol=1e-5, atol=1e-6)
+    logits = GroupSum(k=10, tau=1.0, use_randperm=False)(y)
+    torch.testing.assert_close(logits.cpu(), T(g["logits"]), rtol=1e-5, atol=1e-5)
+    loss = torch.nn.functional.cross_entropy(logits, T(g["labels"]).to(dev))
+    loss.backward()
+    torch.testing.assert_close(loss.detach().cpu(), T(g["loss"]), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(xg.grad.cpu(), T(g["gx"]), rtol=1e-4, atol=1e-7)
+    torch.testing.assert_close(layer.raw_weights.grad.cpu(), T(g["graw"]), rtol=1e-4, atol=1e-7)
+    # fused with GroupSum: same logits and gradients without the (B, N) tensor
+    layer.raw_weights.grad = None
+    xg2 = x.to(dev).requires_grad_(True)
+    logits2 = layer.forward_groupsum(xg2, 10, 1.0)
+    torch.testing.assert_close(logits2.cpu(), T(g["logits"]), rtol=1e-5, atol=1e-5)
+    torch.nn.functional.cross_entropy(logits2, T(g["labels"]).to(dev)).backward()
+    torch.testing.assert_close(xg2.grad.cpu(), T(g["gx"]), rtol=1e-4, atol=1e-7)
+    torch.testing.assert_close(layer.raw_weights.grad.cpu(), T(g["graw"]), rtol=1e-4, atol=1e-7)
+    layer.eval()
+    ye = layer((x >= 0.5).float().to(dev))
+    assert np.array_equal(ye.cpu().numpy().astype(np.uint8), g["y_eval"])
+
+
+def test_prob_layer_temperature_multi_output(golden, dev):
+    from difflut_b200.nodes import ProbabilisticNode
+
+    g = golden("prob_layer")
+    x, idx, raw = T(g["t_x"]), T(g["t_map"]), T(g["t_raw"])
+    layer = _layer(dev, x.shape[1], raw.shape[0], 3, 2, ProbabilisticNode, idx, {"temperature": 0.5})
+    with torch.no_grad():
+        layer.raw_weights.copy_(raw.to(dev))
+    layer.train()
+    xg = x.to(dev).requires_grad_(True)
+    y = layer(xg)
+    torch.testing.assert_close(y.cpu(), T(g["t_y"]), rtol=1e-5, atol=1e-6)
+    y.backward(T(g["t_gy"]).to(dev))
+    torch.testing.assert_close(xg.grad.cpu(), T(g["t_gx"]), rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(layer.raw_weights.grad.cpu(), T(g["t_graw"]), rtol=1e-4, atol=1e-6)
+    # standalone node on mapped inputs
+    node = ProbabilisticNode(input_dim=3, output_dim=2, temperature=0.5).to(dev)
+    with torch.no_grad():
+        node.raw_weights.copy_(raw[0].to(dev))
+    xm = O.gather_mapping(x, idx)[:, 0, :]
+    out = node(xm.to(dev))
+    torch.testing.assert_close(out.cpu(), T(g["t_y"]).reshape(x.shape[0], -1, 2)[:, 0, :], rtol=1e-5, atol=1e-6)
+
+
+def test_prob_edge_inputs_finite(dev):
+    """x exactly 0 or 1: the product-rule gradient stays finite (the reference's autograd path)."""
+    from difflut_b200.nodes import ProbabilisticNode
+
+    node = ProbabilisticNode(input_dim=6, output_dim=1).to(dev)
+    x = torch.tensor([[0.0, 1.0, 0.0, 1.0, 0.5, 0.0], [1.0] * 6, [0.0] * 6], device=dev, requires_grad=True)
+    y = node(x)
+    y.sum().backward()
+    xr = x.detach().cpu().requires_grad_(True)
+    yr = O.prob_forward(xr.unsqueeze(1), node.raw_weights.detach().cpu().unsqueeze(0), 1.0)
+    yr.sum().backward()
+    assert torch.isfinite(x.grad).all()
+    torch.testing.assert_close(y.detach().cpu(), yr.detach().reshape(3, 1), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(x.grad.cpu(), xr.grad, rtol=1e-4, atol=1e-6)
+
+
+# ------------------------------------------------------------------------------ learnable
+def test_learnable_layer_matches_reference(golden, dev):
+    from difflut_b200.layers import LearnableLayer
+    from difflut_b200.nodes import DWNNode, NodeConfig
+
+    g = golden("learnable_layer")
+    x, W, tab = T(g["x"]), T(g["W"]), T(g["tables"])
+    layer = LearnableLayer(x.shape[1], tab.shape[0], DWNNode, NodeConfig(input_dim=6, output_dim=1)).to(dev)
+    with torch.no_grad():
+        layer.mapping.W.copy_(W.to(dev))
+        layer.luts.copy_(tab.to(dev))
+    layer.train()
+    xg = x.to(dev).requires_grad_(True)
+    m = layer.get_mapping(xg)
+    torch.testing.assert_close(m.detach().cpu(), T(g["m"]), rtol=1e-2, atol=1e-4)
+    y = layer(xg)
+    # soft selections close to 0.5 could flip an address under a low-precision GEMM; the fixture has none
+    torch.testing.assert_close(y.cpu(), T(g["y"]), rtol=1e-5, atol=1e-6)
+    y.backward(T(g["gy"]).to(dev))
+    torch.testing.assert_close(layer.luts.grad.cpu(), T(g["gtables"]), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(xg.grad.cpu(), T(g["gx"]), rtol=1e-2, atol=1e-5)
+    torch.testing.assert_close(layer.mapping.W.grad.cpu(), T(g["gW"]), rtol=1e-2, atol=1e-6)
+    layer.eval()
+    assert np.array_equal(layer.get_mapping_matrix().cpu().numpy(), g["hard_idx"])
+    ye = layer(x.to(dev))
+    assert np.array_equal(ye.cpu().numpy().astype(np.uint8), g["y_eval"])
+    layer.update_tau(500)
+    assert abs(layer.tau - float(g["tau_500"][0])) < 1e-12
+
+
+# ------------------------------------------------------------------------------ GroupSum
+def test_groupsum_known_answers(golden, dev):
+    from difflut_b200.utils import GroupSum
+
+    g = golden("groupsum")
+    x = T(g["x"]).to(dev).requires_grad_(True)
+    out = GroupSum(k=4, tau=2.0, use_randperm=False)(x)
+    torch.testing.assert_close(out.cpu(), T(g["k4_tau2"]), rtol=1e-6, atol=1e-6)
+    out.sum().backward()
+    assert torch.allclose(x.grad, torch.full_like(x.grad, 0.5))
+    out1 = GroupSum(k=1, tau=1.0, use_randperm=False)(x.detach())
+    torch.testing.assert_close(out1.cpu(), T(g["k1_tau1"]), rtol=1e-6, atol=1e-6)
+    ones = torch.ones(3, 12, device=dev)
+    assert torch.equal(GroupSum(k=4, tau=1.0, use_randperm=False)(ones), torch.full((3, 4), 3.0, device=dev))
+    with pytest.raises(ValueError):
+        GroupSum(k=2, tau=1.0, use_randperm=False)(torch.ones(3, device=dev))
+
+
+# ------------------------------------------------------------------------------ fused network
+def _build_net3(g, dev, lr=1e-2):
+    from difflut_b200.encoder import ThermometerEncoder
+    from difflut_b200.layers import RandomLayer
+    from difflut_b200.network import DWNNetwork
+    from difflut_b200.nodes import DWNNode, NodeConfig
+    from difflut_b200.utils import GroupSum
+
+    x = T(g["x"])
+    k, tau = int(g["k_tau"][0]), float(g["k_tau"][1])
+    enc = ThermometerEncoder(num_bits=4).fit(x)
+    layers, I = [], x.shape[1] * 4
+    for li, N in enumerate(g["sizes"].tolist()):
+        l = RandomLayer(I, N, DWNNode, NodeConfig(input_dim=6, output_dim=1), seed=li).to(dev)
+        assert torch.equal(l._mapping_indices.cpu(), T(g[f"map{li}"])), "seeded map must equal the reference's"
+        with torch.no_grad():
+            l.luts.copy_(T(g[f"tables{li}"]).to(dev))
+        layers.append(l)
+        I = N
+    return DWNNetwork(enc, layers, GroupSum(k=k, tau=tau, use_randperm=False), lr=lr), layers, enc
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_dwn_net3_two_adam_steps_match_reference(golden, dev, use_graph):
+    g = golden("dwn_net3")
+    net, layers, enc = _build_net3(g, dev)
+    x, labels = T(g["x"]).to(dev), T(g["labels"]).to(dev)
+    for step in range(2):
+        logits = net.logits(x)
+        torch.testing.assert_close(logits.cpu(), T(g[f"logits_step{step}"]), rtol=1e-5, atol=1e-5)
+        loss = net.train_step(x, labels, use_graph=use_graph)
+        torch.testing.assert_close(loss.cpu()[0], T(g[f"loss_step{step}"]), rtol=1e-5, atol=1e-6)
+        for li in range(3):
+            torch.testing.assert_close(layers[li].luts.grad.cpu(), T(g[f"gtables{li}_step{step}"]), rtol=1e-4, atol=1e-7)
+            torch.testing.assert_close(layers[li].luts.detach().cpu(), T(g[f"tables{li}_after{step}"]), rtol=1e-5, atol=2e-6)
+    counts = net.hard_counts(x)
+    assert np.array_equal(counts.cpu().numpy(), g["eval_counts"])
+    packed = enc.to(dev).encode_packed(x)
+    assert torch.equal(net.hard_counts(packed_rows=packed), counts)
+
+
+def test_layer_api_equals_fused_network(golden, dev):
+    """The per-layer fp32 API and the bit-packed executor compute the same logits and table gradients."""
+    from difflut_b200.utils import GroupSum
+
+    g = golden("dwn_net3")
+    net, layers, enc = _build_net3(g, dev)
+    x, labels = T(g["x"]).to(dev), T(g["labels"]).to(dev)
+    k, tau = int(g["k_tau"][0]), float(g["k_tau"][1])
+    h = enc.to(dev)(x)
+    for l in layers:
+        l.train()
+        l.luts.grad = None
+        h = l(h)
+    logits = GroupSum(k=k, tau=tau, use_randperm=False)(h)
+    torch.testing.assert_close(logits.cpu(), T(g["logits_step0"]), rtol=1e-5, atol=1e-5)
+    torch.nn.functional.cross_entropy(logits, labels).backward()
+    for li in range(3):
+        torch.testing.assert_close(layers[li].luts.grad.cpu(), T(g[f"gtables{li}_step0"]), rtol=1e-4, atol=1e-7)
+
+
+def test_full_size_properties(dev):
+    """Config-4 shapes (B=8192, 6272 -> 16000 -> 8000 -> 4000): size-independent properties.
+
+    (1) two runs are bit-identical (no atomics anywhere); (2) per node the table gradient sums to
+    the sum of the node's output gradient (a checksum of the histogram); (3) the hard path equals
+    thresholding the training path's table values for the first layer (bit-sliced LUT vs lookup).
+    """
+    from difflut_b200 import _native
+    from difflut_b200.layers.fused_ops import ConnectionPlan
+    from difflut_b200.layers.random_layer import draw_random_mapping
+
+    gen = torch.Generator().manual_seed(0)
+    B, I, N = 8192, 6272, 16000
+    Bp = _native.padded_batch(B)
+    bits_rows = (torch.rand(B, I, generator=gen) > 0.5).float().to(dev)
+    bits = torch.empty(I, Bp // 32, device=dev, dtype=torch.int32)
+    _native.call("dl_pack_rows_to_t", bits_rows, bits, B, I, Bp, 0.5)
+    plan = ConnectionPlan(draw_random_mapping(I, N, 6, 0, True), I, 1, dev)
+    tab = torch.randn(N, 64, generator=gen).to(dev)
+    g_t = torch.randn(N, Bp, generator=gen).to(dev)
+    g_t[:, B:] = 0
+    outs = []
+    for _ in range(2):
+        gt = torch.empty(N, 64, device=dev)
+        addr = torch.empty(N, Bp, device=dev, dtype=torch.uint8)
+        _native.call("dl_dwn_bwd_tables_t", bits, plan.map_nodes, g_t, 1, 1.0, gt, addr, N, 6, Bp)
+        efd = torch.empty(N, 6, 32, device=dev)
+        _native.call("dl_dwn_prepare", tab, efd, None, N, 6, 0.1, 1 / 3)
+        gx = torch.empty(I, Bp, device=dev)
+        _native.call("dl_dwn_bwd_input_t", addr, g_t, 1, 1.0, efd, plan.inv_ptr_nodes, plan.inv_ent_nodes, gx, I, 6, Bp)
+        outs.append((gt, gx, addr))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    torch.testing.assert_close(outs[0][0].sum(1), g_t.sum(1), rtol=1e-3, atol=1e-2)
+    vals = torch.empty(N, Bp, device=dev)
+    _native.call("dl_dwn_fwd_vals_t", bits, plan.map_nodes, tab, vals, None, N, 6, Bp)
+    masks = torch.empty(N, device=dev, dtype=torch.int64)
+    _native.call("dl_dwn_prepare", tab, None, masks, N, 6, 0.0, 0.0)
+    hard = torch.empty(N, Bp // 32, device=dev, dtype=torch.int32)
+    _native.call("dl_dwn_fwd_bits_t", bits, plan.map_nodes, masks, hard, N, 6, Bp)
+    hard_rows = torch.empty(B, N, device=dev)
+    _native.call("dl_bits_t_to_rows", hard, hard_rows, B, N, Bp)
+    assert torch.equal(hard_rows, (vals[:, :B].t() >= 0.5).float())
+    # addresses agree with a direct computation on a slice of nodes
+    sl = slice(0, 64)
+    ref_addr = O.dwn_addresses(O.gather_mapping(bits_rows.cpu(), plan.map_nodes.cpu()[sl]))
+    assert torch.equal(outs[0][2][sl, :B].t().cpu().long(), ref_addr)
+
+
+def test_error_codes(dev):
+    from difflut_b200 import _native
+
+    a = torch.zeros(4, device=dev)
+    with pytest.raises(RuntimeError, match="invalid argument"):
+        _native.call("dl_f32_rows_to_t", a, a, 1, 4, 100)  # Bp not a multiple of 128
+    with pytest.raises(RuntimeError, match="unsupported"):
+        _native.call("dl_dwn_prepare", a, a, None, 1, 9, 0.1, 0.3)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        _native.call("dl_f32_rows_to_t", torch.zeros(4), a, 1, 4, 128)
