@@ -1,0 +1,393 @@
+"""Benchmark of the DWN training hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (BASELINE config "3-layer DWN classifier"): 784 uniform features -> 8-threshold
+thermometer (6272 bits) -> RandomLayer+DWN 16000 / 8000 / 4000 (n=6) -> GroupSum(10, tau=33)
+-> cross-entropy -> Adam(lr=1e-2); global batch 8192 split over the ranks (data parallel,
+table gradients all-reduced).  Synthetic seeded data, random tables.  One JSON line on rank 0.
+
+For N > 1 launch under `python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N`;
+a plain `python bench.py --gpus N` re-launches itself that way.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+import warnings
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+SIZES = (16000, 8000, 4000)
+FEATURES, THERMO_BITS, CLASSES, TAU, GLOBAL_BATCH, LR = 784, 8, 10, 33.0, 8192, 1e-2
+METRIC = "train samples/s (fwd+bwd) 3-layer n=6 DWN"
+WORKLOAD = "dwn3_16000-8000-4000_n6_T8_globalbatch8192_adam"
+
+
+def _config(extra=None):
+    cfg = {"workload": WORKLOAD, "global_batch": GLOBAL_BATCH, "features": FEATURES, "thermometer_bits": THERMO_BITS,
+           "layers": list(SIZES), "n": 6, "classes": CLASSES, "tau": TAU, "optimizer": "adam lr=1e-2"}
+    cfg.update(extra or {})
+    return cfg
+
+
+# ------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples `nvidia-smi` SM clocks and throttle reasons of one GPU while a region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.samples.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                mx.append(float(s[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, s[2:]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------ CPU baseline (oracle)
+def _oracle_step_time(sample_rows: int, threads: int, repeats: int = 1):
+    """Seconds for one fwd+bwd of the full-width network on `sample_rows` samples with the CPU oracle."""
+    import torch
+
+    from oracle import difflut_oracle as O
+
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    x = torch.rand(sample_rows, FEATURES, generator=g)
+    labels = torch.randint(0, CLASSES, (sample_rows,), generator=g)
+    thr = O.thermometer_thresholds(x, THERMO_BITS)
+    maps, tabs, I = [], [], FEATURES * THERMO_BITS
+    for li, N in enumerate(SIZES):
+        maps.append(O.random_mapping(I, N, 6, li, True))
+        tabs.append(torch.randn(N, 1, 64, generator=g))
+        I = N
+    alpha, beta = 0.5 * 0.75 ** 5, 0.25 / 0.75
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        bits = O.thermometer_encode(x, thr)
+        logits, acts = O.dwn_network_forward(bits, maps, tabs, CLASSES, TAU)
+        lg = logits.clone().requires_grad_(True)
+        torch.nn.functional.cross_entropy(lg, labels).backward()
+        O.dwn_network_backward(acts, maps, tabs, lg.grad, CLASSES, TAU, alpha, beta)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return best
+
+
+def cpu_baseline(sample_rows: int = 1024):
+    import torch
+
+    threads = os.cpu_count() or 1
+    threads = min(threads, 64)
+    dt = _oracle_step_time(sample_rows, threads, repeats=3)
+    return {"value": sample_rows / dt, "unit": "samples/s", "cores": threads, "kind": "port",
+            "sample": f"one fwd+bwd of the full 16000/8000/4000 network on {sample_rows} samples "
+                      f"(vectorised torch-CPU oracle, best of 3, {dt:.2f} s each)"}
+
+
+def run_reference_arm(args):
+    """`--impl reference`: the reference's algorithm on the host cores (oracle port: the reference is a
+    Python package that is not present on the benchmark machine), bounded sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+
+    threads = min(os.cpu_count() or 1, 64)
+    rows = 512
+    for _ in range(min(args.warmup, 1)):
+        _oracle_step_time(rows, threads)
+    times = [_oracle_step_time(rows, threads) for _ in range(max(1, min(args.steps, 10)))]
+    dt = sum(times) / len(times)
+    value = rows / dt
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": args.gpus,
+        "steps": len(times), "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": _config({"sample_rows_per_step": rows}),
+        "cpu_baseline": {"value": value, "unit": "samples/s", "cores": threads, "kind": "port",
+                         "sample": f"{rows} samples per step through the full-width network, torch-CPU oracle"},
+        "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------ GPU arm
+def build_network(device, rank, world, fused_backward=True):
+    import torch
+
+    from difflut_b200.encoder import ThermometerEncoder
+    from difflut_b200.layers import RandomLayer
+    from difflut_b200.network import DWNNetwork
+    from difflut_b200.nodes import DWNNode, NodeConfig
+    from difflut_b200.utils import GroupSum
+
+    g = torch.Generator().manual_seed(0)
+    x = torch.rand(GLOBAL_BATCH, FEATURES, generator=g)
+    labels = torch.randint(0, CLASSES, (GLOBAL_BATCH,), generator=g)
+    enc = ThermometerEncoder(num_bits=THERMO_BITS).fit(x)
+    layers, I = [], FEATURES * THERMO_BITS
+    for li, N in enumerate(SIZES):
+        layer = RandomLayer(I, N, DWNNode, NodeConfig(input_dim=6, output_dim=1), seed=li)
+        with torch.no_grad():
+            layer.luts.copy_(torch.randn(N, 1, 64, generator=g))
+        layers.append(layer.to(device))
+        I = N
+    net = DWNNetwork(enc, layers, GroupSum(k=CLASSES, tau=TAU, use_randperm=False), lr=LR,
+                     fused_backward=fused_backward)
+    from difflut_b200.distributed import shard_rows
+
+    lo, hi = shard_rows(GLOBAL_BATCH, rank, world)
+    return net, x[lo:hi].contiguous(), labels[lo:hi].contiguous()
+
+
+def profile_kernels(net, B, B_global, iters=3):
+    """Per-kernel CUDA-event timings of one training step (ms, averaged over `iters` steps)."""
+    import torch
+
+    from difflut_b200 import _native
+
+    records = []
+    real_call = _native.call
+
+    def timed_call(name, *a, **kw):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        real_call(name, *a, **kw)
+        e.record()
+        records.append((name, a, s, e))
+
+    import difflut_b200.network as netmod
+
+    totals = {}
+    try:
+        netmod._native.call = timed_call
+        for _ in range(iters):
+            records.clear()
+            net._step_body(B, B_global)
+            torch.cuda.synchronize()
+            for name, a, s, e in records:
+                d = totals.setdefault(name, {"ms": 0.0, "launches": 0})
+                d["ms"] += s.elapsed_time(e)
+                d["launches"] += 1
+    finally:
+        netmod._native.call = real_call
+    for d in totals.values():
+        d["ms"] /= iters
+        d["launches"] //= iters
+    return totals
+
+
+def kernel_algorithmic_bytes(net, name):
+    """Algorithmic HBM bytes of all launches of `name` in one step (inputs read once, outputs written once)."""
+    Bp, k = net.Bp, net.k
+    last = len(net.layers) - 1
+    total = 0
+    for li in range(len(net.layers)):
+        N, I, n = net.N[li], net.I[li], net.n[li]
+        g_rows = k if li == last else N
+        if name == "dl_dwn_bwd_tables_t":
+            total += 4 * g_rows * Bp + I * Bp // 8 + (N * Bp if li > 0 else 0) + 4 * N * 64 + 4 * N * n
+        elif name == "dl_dwn_bwd_input_t" and li > 0:
+            total += N * Bp + 4 * g_rows * Bp + 4 * N * n * 32 + 4 * I * Bp + 4 * (I + 1) + 4 * N * n
+        elif name == "dl_dwn_bwd_fused_t":
+            G = net.groups
+            total += I * Bp // 8 + 4 * N * 64 * G + 4 * N * n  # own input bits, partial table gradients, map
+            if li == last:
+                total += 4 * k * Bp + N * Bp  # logits gradient in, addresses out
+            else:
+                up = li + 1
+                total += (4 * k * Bp if up == last else 4 * net.N[up] * Bp) + net.N[up] * Bp  # gradient + addresses above
+                total += 4 * net.N[up] * net.n[up] * 32 + 4 * net.N[up] * net.n[up] + 4 * (N + 1)  # efd, inverse map
+                if li > 0:
+                    total += 4 * N * Bp + N * Bp  # own output gradient and addresses for the layer below
+        elif name == "dl_dwn_fwd_bits_t" and li < last:
+            total += I * Bp // 8 + N * Bp // 8 + 8 * N + 4 * N * n
+        elif name == "dl_dwn_fwd_groupsum_t" and li == last:
+            total += I * Bp // 8 + 4 * k * Bp + 4 * N * 64 + 4 * N * n
+    return total
+
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    warnings.simplefilter("ignore")
+    from difflut_b200.distributed import init_from_env, max_over_ranks
+
+    rank, world, local = init_from_env()
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    net, x_cpu, y_cpu = build_network(device, rank, world, fused_backward=not args.unfused_backward)
+    B = x_cpu.shape[0]
+    x_dev, y_dev = x_cpu.to(device), y_cpu.to(device)
+    x_pin, y_pin = x_cpu.pin_memory(), y_cpu.to(torch.int32).pin_memory()
+    loss_pin = torch.zeros(1).pin_memory()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)  # > 126 MB L2
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    use_graph = not args.no_graph
+
+    def timed(step_fn, steps):
+        """Sum of per-step CUDA-event durations with an L2 flush between steps; max over ranks."""
+        pairs = []
+        barrier()
+        for _ in range(steps):
+            flush.zero_()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            step_fn()
+            e.record()
+            pairs.append((s, e))
+        barrier()
+        ms = sum(s.elapsed_time(e) for s, e in pairs)
+        return max_over_ranks(ms, device=device)
+
+    def step_resident():
+        net.train_step(x_dev, y_dev, use_graph=use_graph)
+
+    def step_e2e():
+        net.train_step(x_pin, y_pin, use_graph=use_graph)
+        loss_pin.copy_(net.loss, non_blocking=True)
+
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    barrier()
+    with ClockSampler(local) as clocks:
+        ms_total = timed(step_resident, args.steps)
+        # keep the sampler alive for at least a few samples on very short runs
+        if ms_total < 500:
+            t_end = time.time() + 0.5
+            while time.time() < t_end:
+                step_resident()
+            torch.cuda.synchronize()
+    clock_summary = clocks.summary()
+    for _ in range(3):
+        step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+
+    ms_per_step = ms_total / args.steps
+    value = GLOBAL_BATCH / (ms_per_step * 1e-3)
+    e2e_value = GLOBAL_BATCH / (ms_e2e / args.steps * 1e-3)
+
+    line = None
+    if rank == 0:
+        # live per-kernel timings (eager launches with events around each) for the roofline object
+        prof = profile_kernels(net, B, GLOBAL_BATCH)
+        top = max(prof.items(), key=lambda kv: kv[1]["ms"])
+        top_name, top_info = top
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+            peak, peak_src = float(peaks["hbm_gbs"]), "measured"
+        except Exception:
+            peak, peak_src = 6650.0, "fallback"
+        alg = kernel_algorithmic_bytes(net, top_name)
+        achieved = alg / (top_info["ms"] * 1e-3) / 1e9 if top_info["ms"] > 0 else 0.0
+        step_alg = net.algorithmic_bytes_per_step(B)
+        roofline = {
+            "bound": "hbm", "kernel": top_name, "launches_per_step": top_info["launches"],
+            "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
+            "frac": achieved / peak, "traffic": None,
+            "algorithmic_bytes_per_launch_set": alg, "kernel_ms_per_step": top_info["ms"],
+            "step_achieved_gbs": step_alg / (ms_per_step * 1e-3) / 1e9 * (1 if world == 1 else 1),
+            "step_algorithmic_bytes": step_alg,
+            "per_kernel_ms": {k: round(v["ms"], 4) for k, v in sorted(prof.items(), key=lambda kv: -kv[1]["ms"])},
+        }
+        cpu = cpu_baseline() if (world == 1 and not args.no_cpu_baseline) else None
+        line = {
+            "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": _config({"per_gpu_batch": B, "parallelism": f"dp{world}", "mode": "bit-packed activations between layers, fp32 gradients",
+                               "cuda_graph": use_graph, "l2": "256 MB flush between timed steps"}),
+            "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": int(x_pin.numel() * 4 + y_pin.numel() * 4) * world,
+                    "d2h_bytes_per_step": 4 * world},
+            "gpu_launches": net.kernel_launches_per_step() * args.steps,
+            "clocks": clock_summary, "roofline": roofline,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    barrier()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--global-batch", type=int, default=8192,
+                    help="override the global batch (profiling on a small case; the default is the benchmark workload)")
+    ap.add_argument("--unfused-backward", action="store_true", help="separate table / input gradient kernels")
+    args = ap.parse_args()
+    globals()["GLOBAL_BATCH"] = args.global_batch
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+    if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29511"),
+               os.path.abspath(__file__)] + sys.argv[1:]
+        raise SystemExit(subprocess.call(cmd))
+    run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -33,6 +33,8 @@ SIGNATURES = {
     "dl_dwn_fwd_vals_t": "ppppplll s",
     "dl_dwn_bwd_tables_t": "ppplfpplll s",
     "dl_dwn_bwd_input_t": "pplfpppplll s",
+    "dl_dwn_bwd_fused_t": "pplfplpppppppllll s",
+    "dl_sum_groups": "pplll s",
     "dl_dwn_mapped_fwd": "pppllll i s".replace(" i", "i"),
     "dl_dwn_mapped_bwd": "pppppllll s",
     "dl_prob_fwd_t": "pppfpllll s",
@@ -79,6 +81,8 @@ def lib():
     handle.dl_padded_batch.argtypes = [ctypes.c_int64]
     handle.dl_dwn_groupsum_splits.restype = ctypes.c_int64
     handle.dl_dwn_groupsum_splits.argtypes = [ctypes.c_int64, ctypes.c_int64]
+    handle.dl_dwn_bwd_groups.restype = ctypes.c_int64
+    handle.dl_dwn_bwd_groups.argtypes = [ctypes.c_int64]
     handle.dl_prob_groupsum_splits.restype = ctypes.c_int64
     handle.dl_prob_groupsum_splits.argtypes = [ctypes.c_int64, ctypes.c_int64]
     _lib = handle

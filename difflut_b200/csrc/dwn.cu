@@ -13,40 +13,63 @@ namespace {
 // per-step table preparation
 // ------------------------------------------------------------------------------------------
 
-// One CTA per node (grid-stride).  Threads (i, a') with i < n, a' < 2^(n-1) evaluate the
-// reference's inner sum over k directly, in double, with sign and beta^hamming weights.
-__global__ void __launch_bounds__(192)
+// One warp per node j (8 warps per CTA), looping over the slots i.  The 2^n table values sit two per lane (address
+// = lane and lane+32) and go through the separable transform one address bit at a time: bit i
+// becomes the difference (v1 - v0), every other bit b becomes v + beta * partner, where the
+// partner differs in bit b only (a lane shuffle for bits 0..4, the lane's other register for bit
+// 5).  The result does not depend on bit i of the address, so the entries with bit i = 0 are
+// compacted into efd_t[j][i][0..2^(n-1)).  The same warp ballots the >= 0.5 masks.
+__global__ void __launch_bounds__(256)
 dwn_prepare_kernel(const float* __restrict__ tables, float* __restrict__ efd_t,
-                   uint64_t* __restrict__ masks, int64_t N, int n, float alpha, float beta) {
-    __shared__ float lut[64];
-    __shared__ double bpow[8];
+                   uint64_t* __restrict__ masks, int N, int n, float alpha, float beta) {
+    const int lane = threadIdx.x & 31;
     const int L = 1 << n;
-    if (threadIdx.x < 8) bpow[threadIdx.x] = pow((double)beta, (double)threadIdx.x);
-    for (int64_t j = blockIdx.x; j < N; j += gridDim.x) {
-        __syncthreads();
-        if (threadIdx.x < L) lut[threadIdx.x] = tables[j * L + threadIdx.x];
-        __syncthreads();
-        if (masks != nullptr && threadIdx.x < 32) {
-            const int lane = threadIdx.x;
-            const uint32_t lo = __ballot_sync(0xffffffffu, lane < L && lut[lane] >= 0.5f);
-            const uint32_t hi = __ballot_sync(0xffffffffu, lane + 32 < L && lut[(lane + 32) & 63] >= 0.5f);
+    const int nwarps = (gridDim.x * blockDim.x) >> 5;
+    for (int j = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; j < N; j += nwarps) {
+        const float t_lo = lane < L ? __ldg(tables + (int64_t)j * L + lane) : 0.f;
+        const float t_hi = lane + 32 < L ? __ldg(tables + (int64_t)j * L + lane + 32) : 0.f;
+        if (masks != nullptr) {
+            const uint32_t lo = __ballot_sync(0xffffffffu, lane < L && t_lo >= 0.5f);
+            const uint32_t hi = __ballot_sync(0xffffffffu, lane + 32 < L && t_hi >= 0.5f);
             if (lane == 0) masks[j] = ((uint64_t)hi << 32) | lo;
         }
-        if (efd_t != nullptr) {
-            const int i = threadIdx.x >> 5, a5 = threadIdx.x & 31;
-            if (i < n) {
-                double acc = 0.0;
-                if (a5 < (L >> 1)) {
-                    const int low = (1 << i) - 1;
-                    const int a = ((a5 & ~low) << 1) | (a5 & low);  // bit i of a is 0
-                    const int keep = (L - 1) & ~(1 << i);
-                    for (int k = 0; k < L; ++k) {
-                        const int ham = __popc((a ^ k) & keep);
-                        const double term = (double)lut[k] * bpow[ham];
-                        acc += ((k >> i) & 1) ? term : -term;
-                    }
+        if (efd_t == nullptr) continue;
+        for (int i = 0; i < n; ++i) {
+            float lo = alpha * t_lo, hi = alpha * t_hi;
+            for (int b = 0; b < n && b < 5; ++b) {
+                const float plo = __shfl_xor_sync(0xffffffffu, lo, 1 << b);
+                const float phi = __shfl_xor_sync(0xffffffffu, hi, 1 << b);
+                if (b == i) {
+                    const bool one = (lane >> b) & 1;
+                    lo = one ? lo - plo : plo - lo;
+                    hi = one ? hi - phi : phi - hi;
+                } else {
+                    lo = fmaf(beta, plo, lo);
+                    hi = fmaf(beta, phi, hi);
                 }
-                efd_t[(j * n + i) * 32 + a5] = (float)((double)alpha * acc);
+            }
+            if (n == 6) {
+                const float l0 = lo, h0 = hi;
+                if (i == 5) {
+                    lo = h0 - l0;
+                    hi = h0 - l0;
+                } else {
+                    lo = fmaf(beta, h0, l0);
+                    hi = fmaf(beta, l0, h0);
+                }
+            }
+            // compact: keep addresses whose bit i is 0 and drop that bit
+            float* dst = efd_t + ((int64_t)j * n + i) * 32;
+            const int low = (1 << i) - 1;
+            if (i == 5) {
+                dst[lane] = lo;
+            } else {
+                if (lane < L && !((lane >> i) & 1)) {
+                    const int a5 = ((lane >> (i + 1)) << i) | (lane & low);
+                    dst[a5] = lo;
+                    if (n == 6) dst[a5 + 16] = hi;
+                }
+                if (n < 6 && lane >= (L >> 1)) dst[lane] = 0.f;  // rows beyond 2^(n-1) are defined as zero
             }
         }
     }
@@ -119,28 +142,26 @@ struct MuxTree<0, BASE> {
     }
 };
 
-// Work item = (node j, group of 4 words).  Q = Wp/4 groups per node; items are numbered with the
-// word group fastest so a warp reads contiguous 512-byte segments of each input row.
+// Thread (x = group of 4 words, y = node): consecutive x read contiguous 16-byte pieces of each
+// input row; nodes and word groups are walked with grid-stride loops (no index division).
 template <int NIN>
 __global__ void __launch_bounds__(256)
 dwn_fwd_bits_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __restrict__ map,
-                    const uint64_t* __restrict__ masks, uint32_t* __restrict__ out_bits, int64_t N,
-                    int64_t Wp) {
-    const int64_t Q = Wp >> 2;
-    const int64_t total = N * Q;
-    for (int64_t item = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; item < total;
-         item += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t j = item / Q, q = item - j * Q;
+                    const uint64_t* __restrict__ masks, uint32_t* __restrict__ out_bits, int N, int Q) {
+    const int64_t Wp = (int64_t)Q << 2;
+    for (int j = blockIdx.y * blockDim.y + threadIdx.y; j < N; j += gridDim.y * blockDim.y) {
         const uint64_t m = __ldg(&masks[j]);
-        uint4 x[NIN];
+        int64_t base[NIN];
 #pragma unroll
-        for (int i = 0; i < NIN; ++i) {
-            const int64_t row = __ldg(&map[j * NIN + i]);
-            x[i] = __ldg(reinterpret_cast<const uint4*>(in_bits + row * Wp) + q);
+        for (int i = 0; i < NIN; ++i) base[i] = (int64_t)__ldg(&map[j * NIN + i]) * Wp;
+        for (int q = blockIdx.x * blockDim.x + threadIdx.x; q < Q; q += gridDim.x * blockDim.x) {
+            uint4 x[NIN];
+#pragma unroll
+            for (int i = 0; i < NIN; ++i) x[i] = __ldg(reinterpret_cast<const uint4*>(in_bits + base[i]) + q);
+            uint4 o;
+            MuxTree<NIN - 1, 0>::eval((uint32_t)m, (uint32_t)(m >> 32), x, o);
+            reinterpret_cast<uint4*>(out_bits + (int64_t)j * Wp)[q] = o;
         }
-        uint4 o;
-        MuxTree<NIN - 1, 0>::eval((uint32_t)m, (uint32_t)(m >> 32), x, o);
-        reinterpret_cast<uint4*>(out_bits + j * Wp)[q] = o;
     }
 }
 
@@ -164,7 +185,7 @@ __device__ __forceinline__ uint32_t addr4(const uint32_t* __restrict__ in_bits, 
     return packed;
 }
 
-// Training forward, one warp per (node, 128-sample chunk); lane = 4 consecutive samples.
+// Training forward, one warp per node; lane = 4 consecutive samples of each 128-sample chunk.
 __global__ void __launch_bounds__(256)
 dwn_fwd_vals_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __restrict__ map,
                     const float* __restrict__ tables, float* __restrict__ out_t,
@@ -173,22 +194,23 @@ dwn_fwd_vals_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __restr
     const int64_t C = Bp >> 7, Wp = Bp >> 5;
     const int L = 1 << n;
     const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-    for (int64_t item = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; item < N * C;
-         item += nwarps) {
-        const int64_t j = item / C, c = item - j * C;
+    // warp w of the grid walks nodes w, w + nwarps, ...; all chunks of a node stay in one warp
+    for (int64_t j = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; j < N; j += nwarps) {
         int32_t rows[DL_MAX_FAST_N];
 #pragma unroll
         for (int i = 0; i < DL_MAX_FAST_N; ++i) rows[i] = i < n ? __ldg(&map[j * n + i]) : 0;
-        const int64_t b = (c << 7) + lane * 4;
-        const uint32_t a = addr4(in_bits, rows, n, Wp, b);
         const float* tj = tables + j * L;
-        float4 o;
-        o.x = __ldg(tj + (a & 0xFF));
-        o.y = __ldg(tj + ((a >> 8) & 0xFF));
-        o.z = __ldg(tj + ((a >> 16) & 0xFF));
-        o.w = __ldg(tj + (a >> 24));
-        *reinterpret_cast<float4*>(out_t + j * Bp + b) = o;
-        if (addr_t != nullptr) *reinterpret_cast<uint32_t*>(addr_t + j * Bp + b) = a;
+        for (int64_t c = 0; c < C; ++c) {
+            const int64_t b = (c << 7) + lane * 4;
+            const uint32_t a = addr4(in_bits, rows, n, Wp, b);
+            float4 o;
+            o.x = __ldg(tj + (a & 0xFF));
+            o.y = __ldg(tj + ((a >> 8) & 0xFF));
+            o.z = __ldg(tj + ((a >> 16) & 0xFF));
+            o.w = __ldg(tj + (a >> 24));
+            *reinterpret_cast<float4*>(out_t + j * Bp + b) = o;
+            if (addr_t != nullptr) *reinterpret_cast<uint32_t*>(addr_t + j * Bp + b) = a;
+        }
     }
 }
 
@@ -203,8 +225,8 @@ dwn_fwd_groupsum_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __r
     const int L = 1 << n;
     const int64_t b = ((int64_t)blockIdx.x * 4 + warp) * 128 + lane * 4;
     if (b >= Bp) return;
-    const int64_t cls = blockIdx.y / S, s = blockIdx.y % S;
-    const int64_t per = dl_ceil_div_dev(gsz, S);
+    const int64_t cls = blockIdx.y / (unsigned)S, s = blockIdx.y % (unsigned)S;
+    const int64_t per = (gsz + S - 1) / S;
     const int64_t j0 = cls * gsz + s * per;
     int64_t j1 = j0 + per;
     if (j1 > (cls + 1) * gsz) j1 = (cls + 1) * gsz;
@@ -262,7 +284,7 @@ dwn_bwd_tables_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __res
         for (int i = 0; i < DL_MAX_FAST_N; ++i) rows[i] = i < n ? __ldg(&map[j * n + i]) : 0;
 #pragma unroll 8
         for (int e = 0; e < 64; ++e) hist[e][lane] = 0.f;
-        const float* grow = g_t + (j / gdiv) * Bp;
+        const float* grow = g_t + (gdiv == 1 ? j : (int64_t)((uint32_t)j / (uint32_t)gdiv)) * Bp;
         for (int64_t c = 0; c < C; ++c) {
             const int64_t b = (c << 7) + lane * 4;
             const uint32_t a = addr4(in_bits, rows, n, Wp, b);
@@ -298,18 +320,23 @@ dwn_bwd_input_kernel(const uint8_t* __restrict__ addr_t, const float* __restrict
     const int lane = threadIdx.x & 31;
     const int64_t C = Bp >> 7;
     const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-    for (int64_t item = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; item < F * C;
-         item += nwarps) {
-        const int64_t f = item / C, c = item - f * C;
+    // all warps sweep the features of one 1024-sample slab before moving on, so the slab of g_t /
+    // addr_t they share stays in L2; within a slab a warp owns a feature (no index division)
+    const int64_t G = (C + 7) >> 3;
+    const uint32_t ugdiv = (uint32_t)gdiv;
+    for (int64_t cg = 0; cg < G; ++cg)
+    for (int64_t f = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; f < F; f += nwarps)
+    for (int64_t c = cg << 3; c < ((cg + 1) << 3) && c < C; ++c) {
         const int64_t b = (c << 7) + lane * 4;
         const int e0 = __ldg(&inv_ptr[f]), e1 = __ldg(&inv_ptr[f + 1]);
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int e = e0; e < e1; ++e) {
             const int ent = __ldg(&inv_ent[e]);
-            const int j = ent / n, i = ent - j * n;
-            const float tv = __ldg(efd_t + (int64_t)ent * 32 + lane);
+            const int j = ent >> 3, i = ent & 7;
+            const float tv = __ldg(efd_t + ((int64_t)j * n + i) * 32 + lane);
             const uint32_t a = __ldg(reinterpret_cast<const uint32_t*>(addr_t + (int64_t)j * Bp + b));
-            const float4 g = __ldg(reinterpret_cast<const float4*>(g_t + (int64_t)(j / gdiv) * Bp + b));
+            const int64_t grow = ugdiv == 1 ? j : (int64_t)((uint32_t)j / ugdiv);
+            const float4 g = __ldg(reinterpret_cast<const float4*>(g_t + grow * Bp + b));
             const uint32_t low = (1u << i) - 1u;
             // drop bit i of every byte: keep the bits below i, shift the bits above i down by one
             const uint32_t lowm = low * 0x01010101u;
@@ -321,6 +348,167 @@ dwn_bwd_input_kernel(const uint8_t* __restrict__ addr_t, const float* __restrict
         }
         acc.x *= gscale; acc.y *= gscale; acc.z *= gscale; acc.w *= gscale;
         *reinterpret_cast<float4*>(gx_t + f * Bp + b) = acc;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// fused backward of one layer: output gradient (pulled from the layer above) + table gradient
+// ------------------------------------------------------------------------------------------
+
+constexpr int FUSED_CG = 8;  // 128-sample chunks per work item (1024 samples)
+
+// One warp per (1024-sample group cg, node f of THIS layer).  Step 1 forms the gradient w.r.t. the
+// node's output for the 8 chunks of the group: either read directly (DIRECT: g_up rows, e.g. the
+// GroupSum gradient) or pulled from the layer above through the inverse map, exactly as
+// dwn_bwd_input_kernel does.  Step 2 forms the node's own addresses from its input bits and adds
+// the gradients into a lane-private histogram, which is written as one partial table gradient per
+// (group, node); the caller sums the groups in order (dl_sum_groups).  The output gradient and the
+// addresses are stored only when the layer below needs them, so for the first layer its
+// [N][Bp] fp32 gradient never reaches HBM.
+constexpr int FUSED_MAX_REG_CONTRIB = 4;  // inverse-map entries of a node kept in registers
+
+// T-table lookups of 4 samples: the lane index of each shuffle is the sample's address without
+// bit i (a shuffle takes its source lane modulo 32, so the bytes above need no masking).
+__device__ __forceinline__ void efd_accumulate(float4& acc, const float4 g, const uint32_t a, const uint32_t lowm,
+                                               const float tv) {
+    const uint32_t a5 = (a & lowm) | ((a >> 1) & ~lowm & 0x7F7F7F7Fu);
+    acc.x = fmaf(g.x, __shfl_sync(0xffffffffu, tv, a5), acc.x);
+    acc.y = fmaf(g.y, __shfl_sync(0xffffffffu, tv, a5 >> 8), acc.y);
+    acc.z = fmaf(g.z, __shfl_sync(0xffffffffu, tv, a5 >> 16), acc.z);
+    acc.w = fmaf(g.w, __shfl_sync(0xffffffffu, tv, a5 >> 24), acc.w);
+}
+
+template <bool DIRECT>
+__global__ void __launch_bounds__(HIST_WARPS * 32, 6)
+dwn_bwd_fused_kernel(const uint8_t* __restrict__ addr_up, const float* __restrict__ g_up, int64_t gdiv_up,
+                     float gscale_up, const float* __restrict__ efd_up, int n_up,
+                     const int32_t* __restrict__ inv_ptr, const int32_t* __restrict__ inv_ent,
+                     const uint32_t* __restrict__ in_bits, const int32_t* __restrict__ map,
+                     float* __restrict__ g_out, uint8_t* __restrict__ addr_out,
+                     float* __restrict__ gt_partial, int64_t group_stride, int64_t N, int n, int64_t Bp) {
+    __shared__ __align__(16) float hist_all[HIST_WARPS][64 * 32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* hist = hist_all[warp];      // hist[e * 32 + lane]: bin e, private to the lane
+    float* mine = hist + lane;
+    const int64_t C = Bp >> 7, Wp = Bp >> 5;
+    const int64_t G = (C + FUSED_CG - 1) / FUSED_CG;
+    const int L = 1 << n;
+    const int64_t nwarps = (int64_t)gridDim.x * HIST_WARPS;
+    const uint32_t ugdiv = (uint32_t)gdiv_up;
+    const int src_lane = lane >> 3;          // which of a chunk's 4 words holds this lane's samples
+    const int sh = (lane & 7) * 4;           // bit offset of its 4 samples inside that word
+    for (int64_t cg = 0; cg < G; ++cg)
+    for (int64_t f = (int64_t)blockIdx.x * HIST_WARPS + warp; f < N; f += nwarps) {
+        const int64_t b0 = cg * (FUSED_CG * 128) + lane * 4;
+        // this node's input words for the whole group: lane w holds word w of each input row
+        uint32_t words[DL_MAX_FAST_N];
+#pragma unroll
+        for (int i = 0; i < DL_MAX_FAST_N; ++i) {
+            words[i] = 0u;
+            if (i < n) {
+                const int64_t w = cg * (FUSED_CG * 4) + lane;
+                if (w < Wp) words[i] = __ldg(in_bits + (int64_t)__ldg(&map[f * n + i]) * Wp + w);
+            }
+        }
+        // inverse-map entries of this node: the first few stay in registers for all chunks
+        int e0 = 0, cnt = 0;
+        float tv_r[FUSED_MAX_REG_CONTRIB];
+        uint32_t lowm_r[FUSED_MAX_REG_CONTRIB];
+        const uint8_t* arow_r[FUSED_MAX_REG_CONTRIB];
+        const float* grow_r[FUSED_MAX_REG_CONTRIB];
+        const float* grow_direct = nullptr;
+        if (DIRECT) {
+            grow_direct = g_up + (ugdiv == 1 ? f : (int64_t)((uint32_t)f / ugdiv)) * Bp;
+        } else {
+            e0 = __ldg(&inv_ptr[f]);
+            cnt = __ldg(&inv_ptr[f + 1]) - e0;
+#pragma unroll
+            for (int k = 0; k < FUSED_MAX_REG_CONTRIB; ++k) {
+                tv_r[k] = 0.f; lowm_r[k] = 0u; arow_r[k] = addr_up; grow_r[k] = g_up;
+                if (k < cnt) {
+                    const int ent = __ldg(&inv_ent[e0 + k]);
+                    const int j = ent >> 3, i = ent & 7;
+                    tv_r[k] = __ldg(efd_up + ((int64_t)j * n_up + i) * 32 + lane);
+                    lowm_r[k] = ((1u << i) - 1u) * 0x01010101u;
+                    arow_r[k] = addr_up + (int64_t)j * Bp;
+                    grow_r[k] = g_up + (ugdiv == 1 ? (int64_t)j : (int64_t)((uint32_t)j / ugdiv)) * Bp;
+                }
+            }
+        }
+        // zero the 64 x 32 histogram: 16 conflict-free 16-byte stores per lane
+#pragma unroll
+        for (int it = 0; it < 16; ++it)
+            *reinterpret_cast<float4*>(hist + (it * 32 + lane) * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+        __syncwarp();
+#pragma unroll 2
+        for (int c = 0; c < FUSED_CG; ++c) {
+            const int64_t b = b0 + c * 128;
+            if (b >= Bp) break;  // Bp is a multiple of 128: uniform over the warp
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (DIRECT) {
+                acc = __ldg(reinterpret_cast<const float4*>(grow_direct + b));
+            } else {
+#pragma unroll
+                for (int k = 0; k < FUSED_MAX_REG_CONTRIB; ++k) {
+                    if (k < cnt) {
+                        const uint32_t a = __ldg(reinterpret_cast<const uint32_t*>(arow_r[k] + b));
+                        const float4 g = __ldg(reinterpret_cast<const float4*>(grow_r[k] + b));
+                        efd_accumulate(acc, g, a, lowm_r[k], tv_r[k]);
+                    }
+                }
+                for (int k = FUSED_MAX_REG_CONTRIB; k < cnt; ++k) {  // rare: more readers than registers
+                    const int ent = __ldg(&inv_ent[e0 + k]);
+                    const int j = ent >> 3, i = ent & 7;
+                    const float tv = __ldg(efd_up + ((int64_t)j * n_up + i) * 32 + lane);
+                    const uint32_t a = __ldg(reinterpret_cast<const uint32_t*>(addr_up + (int64_t)j * Bp + b));
+                    const int64_t gr = ugdiv == 1 ? (int64_t)j : (int64_t)((uint32_t)j / ugdiv);
+                    const float4 g = __ldg(reinterpret_cast<const float4*>(g_up + gr * Bp + b));
+                    efd_accumulate(acc, g, a, ((1u << i) - 1u) * 0x01010101u, tv);
+                }
+            }
+            acc.x *= gscale_up; acc.y *= gscale_up; acc.z *= gscale_up; acc.w *= gscale_up;
+            // own addresses: fetch the word of this lane's samples from the lane that loaded it
+            uint32_t a = 0;
+#pragma unroll
+            for (int i = 0; i < DL_MAX_FAST_N; ++i) {
+                if (i < n) {
+                    const uint32_t t = __shfl_sync(0xffffffffu, words[i], c * 4 + src_lane) >> sh;
+                    a |= dl_spread_nibble(t & 0xFu) << i;
+                }
+            }
+            if (g_out != nullptr) *reinterpret_cast<float4*>(g_out + f * Bp + b) = acc;
+            if (addr_out != nullptr) *reinterpret_cast<uint32_t*>(addr_out + f * Bp + b) = a;
+            mine[(a & 0xFF) * 32] += acc.x;
+            mine[((a >> 8) & 0xFF) * 32] += acc.y;
+            mine[((a >> 16) & 0xFF) * 32] += acc.z;
+            mine[(a >> 24) * 32] += acc.w;
+        }
+        __syncwarp();
+        // sum the 32 lane copies of bins `lane` and `lane + 32`: rotated 16-byte reads, conflict-free
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const int col = ((r + lane) & 7) * 4;
+            const float4 u = *reinterpret_cast<const float4*>(hist + lane * 32 + col);
+            const float4 v = *reinterpret_cast<const float4*>(hist + (lane + 32) * 32 + col);
+            s0 += (u.x + u.y) + (u.z + u.w);
+            s1 += (v.x + v.y) + (v.z + v.w);
+        }
+        float* dst = gt_partial + cg * group_stride + f * L;
+        if (lane < L) dst[lane] = s0;
+        if (lane + 32 < L) dst[lane + 32] = s1;
+        __syncwarp();
+    }
+}
+
+// out[i] = sum over groups g (in order) of partial[g*stride + i]
+__global__ void sum_groups_kernel(const float* __restrict__ partial, float* __restrict__ out, int64_t count,
+                                  int64_t stride, int G) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        float acc = 0.f;
+        for (int g = 0; g < G; ++g) acc += partial[(int64_t)g * stride + i];
+        out[i] = acc;
     }
 }
 
@@ -432,8 +620,9 @@ DL_EXPORT int dl_dwn_prepare(const float* tables, float* efd_t, uint64_t* masks,
                              float alpha, float beta, dl_stream_t stream) {
     DL_REQUIRE(tables && N > 0 && (efd_t || masks));
     if (n < 1 || n > DL_MAX_FAST_N) return DL_ERR_UNSUPPORTED;
-    const int blocks = (int)(N < (int64_t)DL_NUM_SMS * 16 ? N : (int64_t)DL_NUM_SMS * 16);
-    dwn_prepare_kernel<<<blocks, 192, 0, dl_cast(stream)>>>(tables, efd_t, masks, N, (int)n, alpha, beta);
+    DL_REQUIRE(N < ((int64_t)1 << 30));
+    const int blocks = grid_for(N * 32, 256);
+    dwn_prepare_kernel<<<blocks, 256, 0, dl_cast(stream)>>>(tables, efd_t, masks, (int)N, (int)n, alpha, beta);
     return dl_launch_status();
 }
 
@@ -454,16 +643,27 @@ DL_EXPORT int dl_dwn_fwd_bits_t(const uint32_t* in_bits_t, const int32_t* map, c
     DL_REQUIRE_ALIGNED(in_bits_t, 16);
     DL_REQUIRE_ALIGNED(out_bits_t, 16);
     if (n < 1 || n > DL_MAX_FAST_N) return DL_ERR_UNSUPPORTED;
-    const int64_t Wp = Bp / 32;
-    const int blocks = grid_for(N * (Wp / 4), 256);
+    DL_REQUIRE(N < ((int64_t)1 << 30) && Bp < ((int64_t)1 << 36));
+    const int Q = (int)(Bp / 128);
+    int bx = 1;
+    while (bx < Q && bx < 256) bx <<= 1;
+    const int by = 256 / bx;
+    dim3 block(bx, by);
+    int64_t gx = dl_ceil_div(Q, bx), gy = dl_ceil_div(N, by);
+    const int64_t cap = (int64_t)DL_NUM_SMS * 32;
+    if (gx > cap) gx = cap;
+    if (gx * gy > cap) gy = cap / gx > 0 ? cap / gx : 1;
+    if (gy > 65535) gy = 65535;
+    dim3 grid((unsigned)gx, (unsigned)gy);
     cudaStream_t s = dl_cast(stream);
+    const int Ni = (int)N;
     switch (n) {
-        case 1: dwn_fwd_bits_kernel<1><<<blocks, 256, 0, s>>>(in_bits_t, map, masks, out_bits_t, N, Wp); break;
-        case 2: dwn_fwd_bits_kernel<2><<<blocks, 256, 0, s>>>(in_bits_t, map, masks, out_bits_t, N, Wp); break;
-        case 3: dwn_fwd_bits_kernel<3><<<blocks, 256, 0, s>>>(in_bits_t, map, masks, out_bits_t, N, Wp); break;
-        case 4: dwn_fwd_bits_kernel<4><<<blocks, 256, 0, s>>>(in_bits_t, map, masks, out_bits_t, N, Wp); break;
-        case 5: dwn_fwd_bits_kernel<5><<<blocks, 256, 0, s>>>(in_bits_t, map, masks, out_bits_t, N, Wp); break;
-        default: dwn_fwd_bits_kernel<6><<<blocks, 256, 0, s>>>(in_bits_t, map, masks, out_bits_t, N, Wp); break;
+        case 1: dwn_fwd_bits_kernel<1><<<grid, block, 0, s>>>(in_bits_t, map, masks, out_bits_t, Ni, Q); break;
+        case 2: dwn_fwd_bits_kernel<2><<<grid, block, 0, s>>>(in_bits_t, map, masks, out_bits_t, Ni, Q); break;
+        case 3: dwn_fwd_bits_kernel<3><<<grid, block, 0, s>>>(in_bits_t, map, masks, out_bits_t, Ni, Q); break;
+        case 4: dwn_fwd_bits_kernel<4><<<grid, block, 0, s>>>(in_bits_t, map, masks, out_bits_t, Ni, Q); break;
+        case 5: dwn_fwd_bits_kernel<5><<<grid, block, 0, s>>>(in_bits_t, map, masks, out_bits_t, Ni, Q); break;
+        default: dwn_fwd_bits_kernel<6><<<grid, block, 0, s>>>(in_bits_t, map, masks, out_bits_t, Ni, Q); break;
     }
     return dl_launch_status();
 }
@@ -475,7 +675,7 @@ DL_EXPORT int dl_dwn_fwd_vals_t(const uint32_t* in_bits_t, const int32_t* map, c
     DL_REQUIRE_ALIGNED(out_t, 16);
     if (addr_t) DL_REQUIRE_ALIGNED(addr_t, 4);
     if (n < 1 || n > DL_MAX_FAST_N) return DL_ERR_UNSUPPORTED;
-    const int blocks = grid_for(N * (Bp / 128) * 32, 256);
+    const int blocks = grid_for(N * 32, 256);
     dwn_fwd_vals_kernel<<<blocks, 256, 0, dl_cast(stream)>>>(in_bits_t, map, tables, out_t, addr_t, N,
                                                             (int)n, Bp);
     return dl_launch_status();
@@ -532,9 +732,60 @@ DL_EXPORT int dl_dwn_bwd_input_t(const uint8_t* addr_t, const float* g_t, int64_
     DL_REQUIRE_ALIGNED(g_t, 16);
     DL_REQUIRE_ALIGNED(gx_t, 16);
     if (n < 1 || n > DL_MAX_FAST_N) return DL_ERR_UNSUPPORTED;
-    const int blocks = grid_for(F * (Bp / 128) * 32, 256);
+    const int64_t want = dl_ceil_div(F * 32, 256);
+    const int blocks = (int)(want < (int64_t)DL_NUM_SMS * 5 ? want : (int64_t)DL_NUM_SMS * 5);
     dwn_bwd_input_kernel<<<blocks, 256, 0, dl_cast(stream)>>>(addr_t, g_t, gdiv, gscale, efd_t, inv_ptr,
                                                              inv_ent, gx_t, F, (int)n, Bp);
+    return dl_launch_status();
+}
+
+DL_EXPORT int64_t dl_dwn_bwd_groups(int64_t Bp) {
+    return Bp <= 0 ? 0 : dl_ceil_div(Bp / 128, FUSED_CG);
+}
+
+DL_EXPORT int dl_dwn_bwd_fused_t(const uint8_t* addr_up, const float* g_up, int64_t gdiv_up, float gscale_up,
+                                 const float* efd_up, int64_t n_up, const int32_t* inv_ptr,
+                                 const int32_t* inv_ent, const uint32_t* in_bits_t, const int32_t* map,
+                                 float* g_out, uint8_t* addr_out, float* gt_partial, int64_t group_stride,
+                                 int64_t N, int64_t n, int64_t Bp, dl_stream_t stream) {
+    DL_REQUIRE(g_up && in_bits_t && map && gt_partial && N > 0 && gdiv_up > 0);
+    DL_REQUIRE(Bp > 0 && Bp % DL_BATCH_ALIGN == 0 && group_stride >= N * ((int64_t)1 << n));
+    DL_REQUIRE_ALIGNED(g_up, 16);
+    if (g_out) DL_REQUIRE_ALIGNED(g_out, 16);
+    if (addr_out) DL_REQUIRE_ALIGNED(addr_out, 4);
+    if (n < 1 || n > DL_MAX_FAST_N) return DL_ERR_UNSUPPORTED;
+    const bool direct = (inv_ptr == nullptr);
+    if (!direct) {
+        DL_REQUIRE(addr_up && efd_up && inv_ent);
+        DL_REQUIRE_ALIGNED(addr_up, 4);
+        if (n_up < 1 || n_up > DL_MAX_FAST_N) return DL_ERR_UNSUPPORTED;
+    }
+    DL_REQUIRE(N < ((int64_t)1 << 28) && gdiv_up < ((int64_t)1 << 31));
+    // persistent grid: only as many CTAs as are resident at once (6 per SM), so that the
+    // grid-stride loops really sweep all nodes of one 1024-sample slab before the next slab
+    const int64_t cap = (int64_t)DL_NUM_SMS * 6;
+    const int64_t blocks64 = dl_ceil_div(N, HIST_WARPS);
+    const unsigned blocks = (unsigned)(blocks64 < cap ? blocks64 : cap);
+    cudaStream_t s = dl_cast(stream);
+    // ask for the largest shared-memory carve-out so that 6 CTAs (6 x 32 KB of histograms) fit per SM
+    cudaFuncSetAttribute(dwn_bwd_fused_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    cudaFuncSetAttribute(dwn_bwd_fused_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    if (direct)
+        dwn_bwd_fused_kernel<true><<<blocks, HIST_WARPS * 32, 0, s>>>(nullptr, g_up, gdiv_up, gscale_up, nullptr, 1,
+                                                                      nullptr, nullptr, in_bits_t, map, g_out,
+                                                                      addr_out, gt_partial, group_stride, N, (int)n, Bp);
+    else
+        dwn_bwd_fused_kernel<false><<<blocks, HIST_WARPS * 32, 0, s>>>(addr_up, g_up, gdiv_up, gscale_up, efd_up,
+                                                                       (int)n_up, inv_ptr, inv_ent, in_bits_t, map,
+                                                                       g_out, addr_out, gt_partial, group_stride, N,
+                                                                       (int)n, Bp);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_sum_groups(const float* partial, float* out, int64_t count, int64_t stride, int64_t groups,
+                            dl_stream_t stream) {
+    DL_REQUIRE(partial && out && count > 0 && stride >= count && groups > 0);
+    sum_groups_kernel<<<grid_for(count, 256), 256, 0, dl_cast(stream)>>>(partial, out, count, stride, (int)groups);
     return dl_launch_status();
 }
 

@@ -18,7 +18,8 @@ class ConnectionPlan:
 
     A node with O outputs appears as O consecutive virtual nodes sharing one map row, so the
     same kernels serve output_dim > 1.  `inv_ptr` (F+1) / `inv_ent` list, per input feature, the
-    flat positions v*n+i that read it (sorted, so the backward sums in a fixed order).
+    flat positions v*n+i that read it (sorted, so the backward sums in a fixed order);
+    `inv_ent8` holds the same entries packed as (v << 3) | i.
     """
 
     def __init__(self, mapping: torch.Tensor, input_size: int, out_dim: int, device: torch.device):
@@ -32,6 +33,9 @@ class ConnectionPlan:
         mv = m.repeat_interleave(self.O, dim=0) if self.O > 1 else m
         self.map_virtual = mv.to(torch.int32).contiguous()  # (N*O, n)
         self.inv_ptr_virtual, self.inv_ent_virtual = self._invert(mv, input_size)
+        # the DWN kernels take entries packed as (v << 3) | i instead of v*n + i
+        flat = self.inv_ent_virtual.to(torch.int64)
+        self.inv_ent8_virtual = (((flat // self.n) << 3) | (flat % self.n)).to(torch.int32).contiguous()
         if self.O > 1:
             self.inv_ptr_nodes, self.inv_ent_nodes = self._invert(m, input_size)
         else:
@@ -104,7 +108,7 @@ class DWNLayerFunction(torch.autograd.Function):
                 _native.call("dl_dwn_prepare", tables, efd, None, NO, n, ctx.alpha, ctx.beta)
                 gx_t = torch.empty(I, Bp, device=g.device, dtype=torch.float32)
                 _native.call("dl_dwn_bwd_input_t", addr, g_t, 1, 1.0, efd, plan.inv_ptr_virtual,
-                             plan.inv_ent_virtual, gx_t, I, n, Bp)
+                             plan.inv_ent8_virtual, gx_t, I, n, Bp)
                 gx = _t_to_rows(gx_t, B)
         return gx, (gt if need_t else None), None, None, None
 

@@ -32,7 +32,8 @@ from .utils.modules import GroupSum
 class DWNNetwork:
     def __init__(self, encoder: ThermometerEncoder, layers: Sequence[RandomLayer], groupsum: GroupSum,
                  lr: float = 1e-2, betas=(0.9, 0.999), eps: float = 1e-8,
-                 process_group: Optional["dist.ProcessGroup"] = None, distributed: Optional[bool] = None):
+                 process_group: Optional["dist.ProcessGroup"] = None, distributed: Optional[bool] = None,
+                 fused_backward: bool = True):
         if not encoder.is_fitted:
             raise RuntimeError("DWNNetwork needs a fitted encoder")
         if groupsum.use_randperm:
@@ -47,6 +48,7 @@ class DWNNetwork:
         self.lr, self.betas, self.eps = float(lr), (float(betas[0]), float(betas[1])), float(eps)
         self.k, self.tau = int(groupsum.k), float(groupsum.tau)
         self.group = process_group
+        self.fused_backward = bool(fused_backward)
         if distributed is None:
             distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(process_group) > 1
         self.distributed = bool(distributed)
@@ -109,8 +111,13 @@ class DWNNetwork:
         for N in self.N[:-1]:
             self.bits.append(torch.empty(N, Wp, device=dev, dtype=torch.int32))
         self.last_bits = torch.empty(self.N[-1], Wp, device=dev, dtype=torch.int32)
-        # gradient w.r.t. the output of layer li (li < last), produced by layer li+1's backward
-        self.gact = [torch.empty(N, Bp, device=dev, dtype=torch.float32) for N in self.N[:-1]]
+        # gradient w.r.t. the output of layer li (li < last), produced by layer li+1's backward; the
+        # fused backward never materialises it for the first layer
+        self.gact = [torch.empty(N, Bp, device=dev, dtype=torch.float32)
+                     if (li > 0 or not self.fused_backward) else None for li, N in enumerate(self.N[:-1])]
+        self.groups = int(_native.lib().dl_dwn_bwd_groups(Bp))
+        self.gt_partial = (torch.empty(self.groups, self.flat.numel(), device=dev, dtype=torch.float32)
+                           if self.fused_backward else None)
         self.addr = [None] + [torch.empty(N, Bp, device=dev, dtype=torch.uint8) for N in self.N[1:]]
         self.partial = torch.empty(self.k * self.splits, Bp, device=dev, dtype=torch.float32)
         self.logits_t = torch.empty(self.k, Bp, device=dev, dtype=torch.float32)
@@ -144,6 +151,8 @@ class DWNNetwork:
                      self.partial, self.logits_t, self.N[last], self.n[last], self.k, self.tau, Bp)
 
     def _backward(self) -> None:
+        if self.fused_backward:
+            return self._backward_fused()
         Bp = self.Bp
         last = len(self.layers) - 1
         for li in range(last, -1, -1):
@@ -155,8 +164,31 @@ class DWNNetwork:
                          self.grads[li], self.addr[li], self.N[li], self.n[li], Bp)
             if li > 0:
                 _native.call("dl_dwn_bwd_input_t", self.addr[li], g, gdiv, gscale, self.efd[li],
-                             self.plans[li].inv_ptr_nodes, self.plans[li].inv_ent_nodes, self.gact[li - 1],
+                             self.plans[li].inv_ptr_virtual, self.plans[li].inv_ent8_virtual, self.gact[li - 1],
                              self.I[li], self.n[li], Bp)
+
+    def _backward_fused(self) -> None:
+        """One kernel per layer (top down) + one ordered sum of the per-1024-sample partial gradients."""
+        Bp = self.Bp
+        last = len(self.layers) - 1
+        total = self.flat.numel()
+        for li in range(last, -1, -1):
+            partial = self.gt_partial[0, self.offsets[li]:]
+            if li == last:
+                _native.call("dl_dwn_bwd_fused_t", None, self.dlogits_t, self.gsz, 1.0 / self.tau, None, 1, None, None,
+                             self.bits[li], self.plans[li].map_nodes, None, self.addr[li], partial, total,
+                             self.N[li], self.n[li], Bp)
+                continue
+            up = li + 1
+            if up == last:
+                g_up, gdiv, gscale = self.dlogits_t, self.gsz, 1.0 / self.tau
+            else:
+                g_up, gdiv, gscale = self.gact[up], 1, 1.0
+            _native.call("dl_dwn_bwd_fused_t", self.addr[up], g_up, gdiv, gscale, self.efd[up], self.n[up],
+                         self.plans[up].inv_ptr_virtual, self.plans[up].inv_ent8_virtual, self.bits[li],
+                         self.plans[li].map_nodes, self.gact[li] if li > 0 else None,
+                         self.addr[li] if li > 0 else None, partial, total, self.N[li], self.n[li], Bp)
+        _native.call("dl_sum_groups", self.gt_partial, self.flat_grad, total, total, self.groups)
 
     def _step_body(self, B: int, B_global: int) -> None:
         self._prepare_tables(need_efd=True)
@@ -175,7 +207,8 @@ class DWNNetwork:
 
     def kernel_launches_per_step(self) -> int:
         L = len(self.layers)
-        return L + 1 + (L - 1) + 2 + 2 + L + (L - 1) + 2
+        backward = (L + 1) if self.fused_backward else (L + (L - 1))
+        return L + 1 + (L - 1) + 2 + 2 + backward + 2
 
     def train_step(self, x: torch.Tensor, labels: torch.Tensor, use_graph: bool = False) -> torch.Tensor:
         """One optimisation step on this rank's shard (x (B, F) fp32, labels (B,) integer).
@@ -269,8 +302,16 @@ class DWNNetwork:
         last = len(self.layers) - 1
         for li in range(len(self.layers)):
             per_sample += self.I[li] / 8 + (4 * self.k if li == last else self.N[li] / 8)
-            per_sample += (4 * self.k if li == last else 4 * self.N[li]) + self.I[li] / 8
-            per_sample += 4 * self.I[li] if li > 0 else 0
+            # backward: read the gradient of this layer's output (the k logit gradients for the last
+            # layer; never materialised for the first layer in fused mode), re-read the input bits,
+            # write the gradient of the input (not for the first layer)
+            if li == last:
+                per_sample += 4 * self.k
+            elif li > 0 or not self.fused_backward:
+                per_sample += 4 * self.N[li]
+            per_sample += self.I[li] / 8
+            if li > 1 or (li == 1 and not self.fused_backward):
+                per_sample += 4 * self.I[li]
         table_bytes = 4 * self.flat.numel()
         per_step = 3 * table_bytes + 7 * table_bytes + sum(2 * 4 * N * n for N, n in zip(self.N, self.n))
         return int(per_sample * B + per_step)

@@ -129,11 +129,30 @@ int dl_dwn_bwd_tables_t(const uint32_t* in_bits_t, const int32_t* map, const flo
 /* Input gradient (EFD): gx_t[f][b] = sum over (j,i) with map[j,i]==f of
  * g(b,j) * efd_t[j,i,addr(b,j) without bit i]  (difflut/nodes/dwn_node.py:194-227 followed by
  * the gather's scatter-add, difflut/layers/random_layer.py:301-302), as a segmented sum over
- * the inverse map (inv_ptr (F+1), inv_ent = j*n+i, the same CSR dl_gather_rows_bwd takes).
- * Overwrites gx_t. */
+ * the inverse map: inv_ptr (F+1) and inv_ent8, whose entries are (j << 3) | i.  Overwrites gx_t. */
 int dl_dwn_bwd_input_t(const uint8_t* addr_t, const float* g_t, int64_t gdiv, float gscale,
                        const float* efd_t, const int32_t* inv_ptr, const int32_t* inv_ent,
                        float* gx_t, int64_t F, int64_t n, int64_t Bp, dl_stream_t stream);
+
+/* Fused backward of one layer of a stack (same arithmetic as dl_dwn_bwd_input_t of the layer
+ * above followed by dl_dwn_bwd_tables_t of this layer, in one pass).  One warp handles 1024
+ * samples of one node f of THIS layer: it forms d(loss)/d(out[f]) either by reading it
+ * (inv_ptr == NULL: g(b,f) = gscale_up * g_up[f / gdiv_up][b], e.g. a GroupSum gradient) or by
+ * pulling it from the layer above (addr_up [N_up][Bp], g_up, efd_up (N_up, n_up, 32) and the
+ * inverse map of the layer above over this layer's nodes, entries (j << 3) | i), then forms this layer's addresses
+ * from in_bits_t / map and accumulates the table gradient.  g_out [N][Bp] and addr_out [N][Bp]
+ * are written only if not NULL (the first layer of a stack needs neither).
+ * gt_partial is caller-provided scratch: dl_dwn_bwd_groups(Bp) slabs of `group_stride` floats
+ * (slab g holds the table gradient of samples [1024 g, 1024 (g+1)) at offset f*2^n); sum them
+ * with dl_sum_groups, which adds the slabs in order (reproducible).                          */
+int64_t dl_dwn_bwd_groups(int64_t Bp);
+int dl_dwn_bwd_fused_t(const uint8_t* addr_up, const float* g_up, int64_t gdiv_up, float gscale_up,
+                       const float* efd_up, int64_t n_up, const int32_t* inv_ptr,
+                       const int32_t* inv_ent, const uint32_t* in_bits_t, const int32_t* map,
+                       float* g_out, uint8_t* addr_out, float* gt_partial, int64_t group_stride,
+                       int64_t N, int64_t n, int64_t Bp, dl_stream_t stream);
+int dl_sum_groups(const float* partial, float* out, int64_t count, int64_t stride, int64_t groups,
+                  dl_stream_t stream);
 
 /* ------------------------------------------------------------------ DWN node, materialised-input path
  * Replaces efd_cuda.forward(input, luts) / .backward(input, luts, grad_output, alpha, beta)

@@ -321,7 +321,7 @@ def test_groupsum_known_answers(golden, dev):
 
 
 # ------------------------------------------------------------------------------ fused network
-def _build_net3(g, dev, lr=1e-2):
+def _build_net3(g, dev, lr=1e-2, fused_backward=True):
     from difflut_b200.encoder import ThermometerEncoder
     from difflut_b200.layers import RandomLayer
     from difflut_b200.network import DWNNetwork
@@ -339,13 +339,14 @@ def _build_net3(g, dev, lr=1e-2):
             l.luts.copy_(T(g[f"tables{li}"]).to(dev))
         layers.append(l)
         I = N
-    return DWNNetwork(enc, layers, GroupSum(k=k, tau=tau, use_randperm=False), lr=lr), layers, enc
+    net = DWNNetwork(enc, layers, GroupSum(k=k, tau=tau, use_randperm=False), lr=lr, fused_backward=fused_backward)
+    return net, layers, enc
 
 
-@pytest.mark.parametrize("use_graph", [False, True])
-def test_dwn_net3_two_adam_steps_match_reference(golden, dev, use_graph):
+@pytest.mark.parametrize("use_graph,fused", [(False, True), (True, True), (False, False)])
+def test_dwn_net3_two_adam_steps_match_reference(golden, dev, use_graph, fused):
     g = golden("dwn_net3")
-    net, layers, enc = _build_net3(g, dev)
+    net, layers, enc = _build_net3(g, dev, fused_backward=fused)
     x, labels = T(g["x"]).to(dev), T(g["labels"]).to(dev)
     for step in range(2):
         logits = net.logits(x)
@@ -410,7 +411,7 @@ def test_full_size_properties(dev):
         efd = torch.empty(N, 6, 32, device=dev)
         _native.call("dl_dwn_prepare", tab, efd, None, N, 6, 0.1, 1 / 3)
         gx = torch.empty(I, Bp, device=dev)
-        _native.call("dl_dwn_bwd_input_t", addr, g_t, 1, 1.0, efd, plan.inv_ptr_nodes, plan.inv_ent_nodes, gx, I, 6, Bp)
+        _native.call("dl_dwn_bwd_input_t", addr, g_t, 1, 1.0, efd, plan.inv_ptr_virtual, plan.inv_ent8_virtual, gx, I, 6, Bp)
         outs.append((gt, gx, addr))
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
     torch.testing.assert_close(outs[0][0].sum(1), g_t.sum(1), rtol=1e-3, atol=1e-2)
@@ -439,3 +440,43 @@ def test_error_codes(dev):
         _native.call("dl_dwn_prepare", a, a, None, 1, 9, 0.1, 0.3)
     with pytest.raises(RuntimeError, match="CUDA tensors only"):
         _native.call("dl_f32_rows_to_t", torch.zeros(4), a, 1, 4, 128)
+
+
+def test_fused_backward_equals_separate_kernels_multi_group(dev):
+    """B = 2500 (three 1024-sample groups, ragged tail): the fused per-layer backward and the separate
+    table / input gradient kernels give the same table gradients; both match the oracle."""
+    from difflut_b200.encoder import ThermometerEncoder
+    from difflut_b200.layers import RandomLayer
+    from difflut_b200.network import DWNNetwork
+    from difflut_b200.nodes import DWNNode, NodeConfig
+    from difflut_b200.utils import GroupSum
+
+    gen = torch.Generator().manual_seed(3)
+    B, F, Tb, k, tau = 2500, 16, 4, 5, 2.0
+    sizes = [96, 50, 33]  # 33 is not a multiple of k: the last class is short
+    x = torch.rand(B, F, generator=gen)
+    labels = torch.randint(0, k, (B,), generator=gen)
+    grads = {}
+    tabs0 = [torch.randn(N, 1, 64, generator=gen) for N in sizes]
+    for fused in (True, False):
+        enc = ThermometerEncoder(num_bits=Tb).fit(x)
+        layers, I = [], F * Tb
+        for li, N in enumerate(sizes):
+            l = RandomLayer(I, N, DWNNode, NodeConfig(input_dim=6, output_dim=1), seed=10 + li).to(dev)
+            with torch.no_grad():
+                l.luts.copy_(tabs0[li].to(dev))
+            layers.append(l)
+            I = N
+        net = DWNNetwork(enc, layers, GroupSum(k=k, tau=tau, use_randperm=False), lr=1e-3, fused_backward=fused)
+        net.train_step(x.to(dev), labels.to(dev))
+        grads[fused] = [gr.cpu().clone() for gr in net.grads]
+        maps = [l._mapping_indices.cpu() for l in layers]
+    for a, b in zip(grads[True], grads[False]):
+        torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-7)
+    bits = O.thermometer_encode(x, O.thermometer_thresholds(x, Tb))
+    logits, acts = O.dwn_network_forward(bits, maps, tabs0, k, tau)
+    lg = logits.clone().requires_grad_(True)
+    torch.nn.functional.cross_entropy(lg, labels).backward()
+    ref = O.dwn_network_backward(acts, maps, tabs0, lg.grad, k, tau, 0.5 * 0.75 ** 5, 0.25 / 0.75)
+    for a, r in zip(grads[True], ref):
+        torch.testing.assert_close(a, r, rtol=1e-4, atol=1e-7)
