@@ -378,8 +378,87 @@ __device__ __forceinline__ void efd_accumulate(float4& acc, const float4 g, cons
     acc.w = fmaf(g.w, __shfl_sync(0xffffffffu, tv, a5 >> 24), acc.w);
 }
 
+// Data one chunk needs from the layer above: CNT (address word, gradient float4) pairs, or one
+// gradient float4 in DIRECT mode.  Loads are issued unconditionally (no branch between them) so that
+// they overlap; the next chunk's loads are issued before the current chunk is consumed.
+template <int CNT>
+struct ChunkData {
+    uint32_t a[CNT > 0 ? CNT : 1];
+    float4 g[CNT > 0 ? CNT : 1];
+};
+
+template <bool DIRECT, int CNT>
+__device__ __forceinline__ void load_chunk(ChunkData<CNT>& d, int c, const float* __restrict__ gdir,
+                                           const uint8_t* const (&ap)[FUSED_MAX_REG_CONTRIB],
+                                           const float* const (&gp)[FUSED_MAX_REG_CONTRIB]) {
+    if (DIRECT) {
+        d.g[0] = __ldg(reinterpret_cast<const float4*>(gdir + c * 128));
+    } else {
+#pragma unroll
+        for (int k = 0; k < CNT; ++k) {
+            d.a[k] = __ldg(reinterpret_cast<const uint32_t*>(ap[k] + c * 128));
+            d.g[k] = __ldg(reinterpret_cast<const float4*>(gp[k] + c * 128));
+        }
+    }
+}
+
+// The chunks of one (group, node) item for a node with exactly CNT readers held in registers
+// (`extra` further readers, if any, are walked generically).
+template <bool DIRECT, int CNT>
+__device__ __forceinline__ void fused_chunks(
+    int valid_chunks, int n, int extra, int src_lane, int sh, float gscale, const uint32_t (&words)[DL_MAX_FAST_N],
+    const float* __restrict__ gdir, const uint8_t* const (&ap)[FUSED_MAX_REG_CONTRIB],
+    const float* const (&gp)[FUSED_MAX_REG_CONTRIB], const float (&tv)[FUSED_MAX_REG_CONTRIB],
+    const uint32_t (&lowm)[FUSED_MAX_REG_CONTRIB], const int32_t* __restrict__ inv_ent, int e_tail,
+    const uint8_t* __restrict__ addr_up, const float* __restrict__ g_up, const float* __restrict__ efd_up,
+    int n_up, uint32_t ugdiv, int64_t Bp, int64_t b0, float* __restrict__ go, uint8_t* __restrict__ ao,
+    float* __restrict__ mine) {
+    ChunkData<CNT> cur;
+    load_chunk<DIRECT, CNT>(cur, 0, gdir, ap, gp);
+#pragma unroll 2
+    for (int c = 0; c < FUSED_CG; ++c) {
+        if (c >= valid_chunks) break;
+        ChunkData<CNT> nxt = cur;
+        if (c + 1 < valid_chunks) load_chunk<DIRECT, CNT>(nxt, c + 1, gdir, ap, gp);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (DIRECT) {
+            acc = cur.g[0];
+            acc.x *= gscale; acc.y *= gscale; acc.z *= gscale; acc.w *= gscale;
+        } else {
+#pragma unroll
+            for (int k = 0; k < CNT; ++k) efd_accumulate(acc, cur.g[k], cur.a[k], lowm[k], tv[k]);
+            for (int k = 0; k < extra; ++k) {  // rare: more readers than registers
+                const int ent = __ldg(&inv_ent[e_tail + k]);
+                const int j = ent >> 3, i = ent & 7;
+                const float t = gscale * __ldg(efd_up + ((int64_t)j * n_up + i) * 32 + (threadIdx.x & 31));
+                const int64_t b = b0 + c * 128;
+                const uint32_t a = __ldg(reinterpret_cast<const uint32_t*>(addr_up + (int64_t)j * Bp + b));
+                const int64_t gr = ugdiv == 1 ? (int64_t)j : (int64_t)((uint32_t)j / ugdiv);
+                const float4 g = __ldg(reinterpret_cast<const float4*>(g_up + gr * Bp + b));
+                efd_accumulate(acc, g, a, ((1u << i) - 1u) * 0x01010101u, t);
+            }
+        }
+        // own addresses: fetch the word of this lane's samples from the lane that loaded it
+        uint32_t a = 0;
+#pragma unroll
+        for (int i = 0; i < DL_MAX_FAST_N; ++i) {
+            if (i < n) {
+                const uint32_t t = __shfl_sync(0xffffffffu, words[i], c * 4 + src_lane) >> sh;
+                a |= dl_spread_nibble(t & 0xFu) << i;
+            }
+        }
+        if (go != nullptr) *reinterpret_cast<float4*>(go + c * 128) = acc;
+        if (ao != nullptr) *reinterpret_cast<uint32_t*>(ao + c * 128) = a;
+        mine[(a & 0xFF) * 32] += acc.x;
+        mine[((a >> 8) & 0xFF) * 32] += acc.y;
+        mine[((a >> 16) & 0xFF) * 32] += acc.z;
+        mine[(a >> 24) * 32] += acc.w;
+        cur = nxt;
+    }
+}
+
 template <bool DIRECT>
-__global__ void __launch_bounds__(HIST_WARPS * 32, 6)
+__global__ void __launch_bounds__(HIST_WARPS * 32, 5)
 dwn_bwd_fused_kernel(const uint8_t* __restrict__ addr_up, const float* __restrict__ g_up, int64_t gdiv_up,
                      float gscale_up, const float* __restrict__ efd_up, int n_up,
                      const int32_t* __restrict__ inv_ptr, const int32_t* __restrict__ inv_ent,
@@ -397,107 +476,84 @@ dwn_bwd_fused_kernel(const uint8_t* __restrict__ addr_up, const float* __restric
     const uint32_t ugdiv = (uint32_t)gdiv_up;
     const int src_lane = lane >> 3;          // which of a chunk's 4 words holds this lane's samples
     const int sh = (lane & 7) * 4;           // bit offset of its 4 samples inside that word
-    for (int64_t cg = 0; cg < G; ++cg)
-    for (int64_t f = (int64_t)blockIdx.x * HIST_WARPS + warp; f < N; f += nwarps) {
-        const int64_t b0 = cg * (FUSED_CG * 128) + lane * 4;
-        // this node's input words for the whole group: lane w holds word w of each input row
-        uint32_t words[DL_MAX_FAST_N];
-#pragma unroll
-        for (int i = 0; i < DL_MAX_FAST_N; ++i) {
-            words[i] = 0u;
-            if (i < n) {
-                const int64_t w = cg * (FUSED_CG * 4) + lane;
-                if (w < Wp) words[i] = __ldg(in_bits + (int64_t)__ldg(&map[f * n + i]) * Wp + w);
-            }
-        }
-        // inverse-map entries of this node: the first few stay in registers for all chunks
-        int e0 = 0, cnt = 0;
-        float tv_r[FUSED_MAX_REG_CONTRIB];
-        uint32_t lowm_r[FUSED_MAX_REG_CONTRIB];
-        const uint8_t* arow_r[FUSED_MAX_REG_CONTRIB];
-        const float* grow_r[FUSED_MAX_REG_CONTRIB];
-        const float* grow_direct = nullptr;
-        if (DIRECT) {
-            grow_direct = g_up + (ugdiv == 1 ? f : (int64_t)((uint32_t)f / ugdiv)) * Bp;
-        } else {
-            e0 = __ldg(&inv_ptr[f]);
-            cnt = __ldg(&inv_ptr[f + 1]) - e0;
-#pragma unroll
-            for (int k = 0; k < FUSED_MAX_REG_CONTRIB; ++k) {
-                tv_r[k] = 0.f; lowm_r[k] = 0u; arow_r[k] = addr_up; grow_r[k] = g_up;
-                if (k < cnt) {
-                    const int ent = __ldg(&inv_ent[e0 + k]);
-                    const int j = ent >> 3, i = ent & 7;
-                    tv_r[k] = __ldg(efd_up + ((int64_t)j * n_up + i) * 32 + lane);
-                    lowm_r[k] = ((1u << i) - 1u) * 0x01010101u;
-                    arow_r[k] = addr_up + (int64_t)j * Bp;
-                    grow_r[k] = g_up + (ugdiv == 1 ? (int64_t)j : (int64_t)((uint32_t)j / ugdiv)) * Bp;
-                }
-            }
-        }
-        // zero the 64 x 32 histogram: 16 conflict-free 16-byte stores per lane
-#pragma unroll
-        for (int it = 0; it < 16; ++it)
-            *reinterpret_cast<float4*>(hist + (it * 32 + lane) * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
-        __syncwarp();
-#pragma unroll 2
-        for (int c = 0; c < FUSED_CG; ++c) {
-            const int64_t b = b0 + c * 128;
-            if (b >= Bp) break;  // Bp is a multiple of 128: uniform over the warp
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (DIRECT) {
-                acc = __ldg(reinterpret_cast<const float4*>(grow_direct + b));
-            } else {
-#pragma unroll
-                for (int k = 0; k < FUSED_MAX_REG_CONTRIB; ++k) {
-                    if (k < cnt) {
-                        const uint32_t a = __ldg(reinterpret_cast<const uint32_t*>(arow_r[k] + b));
-                        const float4 g = __ldg(reinterpret_cast<const float4*>(grow_r[k] + b));
-                        efd_accumulate(acc, g, a, lowm_r[k], tv_r[k]);
-                    }
-                }
-                for (int k = FUSED_MAX_REG_CONTRIB; k < cnt; ++k) {  // rare: more readers than registers
-                    const int ent = __ldg(&inv_ent[e0 + k]);
-                    const int j = ent >> 3, i = ent & 7;
-                    const float tv = __ldg(efd_up + ((int64_t)j * n_up + i) * 32 + lane);
-                    const uint32_t a = __ldg(reinterpret_cast<const uint32_t*>(addr_up + (int64_t)j * Bp + b));
-                    const int64_t gr = ugdiv == 1 ? (int64_t)j : (int64_t)((uint32_t)j / ugdiv);
-                    const float4 g = __ldg(reinterpret_cast<const float4*>(g_up + gr * Bp + b));
-                    efd_accumulate(acc, g, a, ((1u << i) - 1u) * 0x01010101u, tv);
-                }
-            }
-            acc.x *= gscale_up; acc.y *= gscale_up; acc.z *= gscale_up; acc.w *= gscale_up;
-            // own addresses: fetch the word of this lane's samples from the lane that loaded it
-            uint32_t a = 0;
+    for (int64_t cg = 0; cg < G; ++cg) {
+        const int64_t left = C - cg * FUSED_CG;
+        const int valid_chunks = left < FUSED_CG ? (int)left : FUSED_CG;
+        for (int64_t f = (int64_t)blockIdx.x * HIST_WARPS + warp; f < N; f += nwarps) {
+            const int64_t b0 = cg * (FUSED_CG * 128) + lane * 4;
+            // this node's input words for the whole group: lane w holds word w of each input row
+            uint32_t words[DL_MAX_FAST_N];
 #pragma unroll
             for (int i = 0; i < DL_MAX_FAST_N; ++i) {
+                words[i] = 0u;
                 if (i < n) {
-                    const uint32_t t = __shfl_sync(0xffffffffu, words[i], c * 4 + src_lane) >> sh;
-                    a |= dl_spread_nibble(t & 0xFu) << i;
+                    const int64_t w = cg * (FUSED_CG * 4) + lane;
+                    if (w < Wp) words[i] = __ldg(in_bits + (int64_t)__ldg(&map[f * n + i]) * Wp + w);
                 }
             }
-            if (g_out != nullptr) *reinterpret_cast<float4*>(g_out + f * Bp + b) = acc;
-            if (addr_out != nullptr) *reinterpret_cast<uint32_t*>(addr_out + f * Bp + b) = a;
-            mine[(a & 0xFF) * 32] += acc.x;
-            mine[((a >> 8) & 0xFF) * 32] += acc.y;
-            mine[((a >> 16) & 0xFF) * 32] += acc.z;
-            mine[(a >> 24) * 32] += acc.w;
-        }
-        __syncwarp();
-        // sum the 32 lane copies of bins `lane` and `lane + 32`: rotated 16-byte reads, conflict-free
-        float s0 = 0.f, s1 = 0.f;
+            // inverse-map entries of this node: the first few stay in registers for all chunks; the
+            // output-gradient scale is folded into their EFD values
+            int e0 = 0, cnt = 0;
+            float tv_r[FUSED_MAX_REG_CONTRIB];
+            uint32_t lowm_r[FUSED_MAX_REG_CONTRIB];
+            const uint8_t* ap[FUSED_MAX_REG_CONTRIB];
+            const float* gp[FUSED_MAX_REG_CONTRIB];
+            const float* gdir = nullptr;
+            if (DIRECT) {
+                gdir = g_up + (ugdiv == 1 ? f : (int64_t)((uint32_t)f / ugdiv)) * Bp + b0;
+            } else {
+                e0 = __ldg(&inv_ptr[f]);
+                cnt = __ldg(&inv_ptr[f + 1]) - e0;
 #pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            const int col = ((r + lane) & 7) * 4;
-            const float4 u = *reinterpret_cast<const float4*>(hist + lane * 32 + col);
-            const float4 v = *reinterpret_cast<const float4*>(hist + (lane + 32) * 32 + col);
-            s0 += (u.x + u.y) + (u.z + u.w);
-            s1 += (v.x + v.y) + (v.z + v.w);
+                for (int k = 0; k < FUSED_MAX_REG_CONTRIB; ++k) {
+                    tv_r[k] = 0.f; lowm_r[k] = 0u; ap[k] = addr_up; gp[k] = g_up;
+                    if (k < cnt) {
+                        const int ent = __ldg(&inv_ent[e0 + k]);
+                        const int j = ent >> 3, i = ent & 7;
+                        tv_r[k] = gscale_up * __ldg(efd_up + ((int64_t)j * n_up + i) * 32 + lane);
+                        lowm_r[k] = ((1u << i) - 1u) * 0x01010101u;
+                        ap[k] = addr_up + (int64_t)j * Bp + b0;
+                        gp[k] = g_up + (ugdiv == 1 ? (int64_t)j : (int64_t)((uint32_t)j / ugdiv)) * Bp + b0;
+                    }
+                }
+            }
+            float* go = g_out != nullptr ? g_out + f * Bp + b0 : nullptr;
+            uint8_t* ao = addr_out != nullptr ? addr_out + f * Bp + b0 : nullptr;
+            // zero the 64 x 32 histogram: 16 conflict-free 16-byte stores per lane
+#pragma unroll
+            for (int it = 0; it < 16; ++it)
+                *reinterpret_cast<float4*>(hist + (it * 32 + lane) * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+            __syncwarp();
+#define DL_FUSED_ARGS(extra_) valid_chunks, n, extra_, src_lane, sh, gscale_up, words, gdir, ap, gp, tv_r, lowm_r, \
+                              inv_ent, e0 + FUSED_MAX_REG_CONTRIB, addr_up, g_up, efd_up, n_up, ugdiv, Bp, b0, go, ao, mine
+            if (DIRECT) {
+                fused_chunks<true, 0>(DL_FUSED_ARGS(0));
+            } else {
+                switch (cnt) {  // uniform over the warp
+                    case 0: fused_chunks<false, 0>(DL_FUSED_ARGS(0)); break;
+                    case 1: fused_chunks<false, 1>(DL_FUSED_ARGS(0)); break;
+                    case 2: fused_chunks<false, 2>(DL_FUSED_ARGS(0)); break;
+                    case 3: fused_chunks<false, 3>(DL_FUSED_ARGS(0)); break;
+                    default: fused_chunks<false, 4>(DL_FUSED_ARGS(cnt - FUSED_MAX_REG_CONTRIB)); break;
+                }
+            }
+#undef DL_FUSED_ARGS
+            __syncwarp();
+            // sum the 32 lane copies of bins `lane` and `lane + 32`: rotated 16-byte reads, conflict-free
+            float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                const int col = ((r + lane) & 7) * 4;
+                const float4 u = *reinterpret_cast<const float4*>(hist + lane * 32 + col);
+                const float4 v = *reinterpret_cast<const float4*>(hist + (lane + 32) * 32 + col);
+                s0 += (u.x + u.y) + (u.z + u.w);
+                s1 += (v.x + v.y) + (v.z + v.w);
+            }
+            float* dst = gt_partial + cg * group_stride + f * L;
+            if (lane < L) dst[lane] = s0;
+            if (lane + 32 < L) dst[lane + 32] = s1;
+            __syncwarp();
         }
-        float* dst = gt_partial + cg * group_stride + f * L;
-        if (lane < L) dst[lane] = s0;
-        if (lane + 32 < L) dst[lane + 32] = s1;
-        __syncwarp();
     }
 }
 
@@ -761,9 +817,10 @@ DL_EXPORT int dl_dwn_bwd_fused_t(const uint8_t* addr_up, const float* g_up, int6
         if (n_up < 1 || n_up > DL_MAX_FAST_N) return DL_ERR_UNSUPPORTED;
     }
     DL_REQUIRE(N < ((int64_t)1 << 28) && gdiv_up < ((int64_t)1 << 31));
-    // persistent grid: only as many CTAs as are resident at once (6 per SM), so that the
+    // persistent grid: only as many CTAs as are resident at once, so that the
     // grid-stride loops really sweep all nodes of one 1024-sample slab before the next slab
-    const int64_t cap = (int64_t)DL_NUM_SMS * 6;
+    // (5 per SM: the register budget of the software-pipelined loads)
+    const int64_t cap = (int64_t)DL_NUM_SMS * 5;
     const int64_t blocks64 = dl_ceil_div(N, HIST_WARPS);
     const unsigned blocks = (unsigned)(blocks64 < cap ? blocks64 : cap);
     cudaStream_t s = dl_cast(stream);

@@ -90,9 +90,19 @@ class DWNNetwork:
         self.plans = [l._plan(self.device) for l in self.layers]
         self.alpha = [l.alpha for l in self.layers]
         self.beta = [l.beta for l in self.layers]
-        self.masks = [torch.empty(N, device=self.device, dtype=torch.int64) for N in self.N]
-        self.efd = [torch.empty(N, n, 32, device=self.device, dtype=torch.float32) if li > 0 else None
-                    for li, (N, n) in enumerate(zip(self.N, self.n))]
+        # per-step derived tables of all layers in one buffer each (layers are slices): when every
+        # layer has the same n / alpha / beta, one kernel launch prepares the whole network
+        nodes_total = sum(self.N)
+        self.uniform = len(set(self.n)) == 1 and len(set(self.alpha)) == 1 and len(set(self.beta)) == 1
+        self.masks_all = torch.empty(nodes_total, device=self.device, dtype=torch.int64)
+        self.efd_all = torch.empty(sum(N * n * 32 for N, n in zip(self.N, self.n)), device=self.device,
+                                   dtype=torch.float32)
+        self.masks, self.efd, node_off, efd_off = [], [], 0, 0
+        for N, n in zip(self.N, self.n):
+            self.masks.append(self.masks_all[node_off:node_off + N])
+            self.efd.append(self.efd_all[efd_off:efd_off + N * n * 32].view(N, n, 32))
+            node_off += N
+            efd_off += N * n * 32
         self.gsz = (self.N[-1] + self.k - 1) // self.k
         self.splits = int(_native.lib().dl_dwn_groupsum_splits(self.N[-1], self.k))
         self._B = None
@@ -131,14 +141,14 @@ class DWNNetwork:
 
     # ------------------------------------------------------------------ kernels
     def _prepare_tables(self, need_efd: bool) -> None:
-        last = len(self.layers) - 1
+        """EFD transform tables (for the backward) and >= 0.5 masks (for the hard forward) of this step."""
+        if self.uniform:
+            _native.call("dl_dwn_prepare", self.flat, self.efd_all if need_efd else None, self.masks_all,
+                         sum(self.N), self.n[0], self.alpha[0], self.beta[0])
+            return
         for li in range(len(self.layers)):
-            efd = self.efd[li] if (need_efd and li > 0) else None
-            masks = self.masks[li] if li < last or not need_efd else None
-            if efd is None and masks is None:
-                continue
-            _native.call("dl_dwn_prepare", self.tables[li], efd, masks, self.N[li], self.n[li],
-                         self.alpha[li], self.beta[li])
+            _native.call("dl_dwn_prepare", self.tables[li], self.efd[li] if need_efd else None, self.masks[li],
+                         self.N[li], self.n[li], self.alpha[li], self.beta[li])
 
     def _forward(self, x: torch.Tensor, B: int) -> None:
         Bp = self.Bp
@@ -208,7 +218,8 @@ class DWNNetwork:
     def kernel_launches_per_step(self) -> int:
         L = len(self.layers)
         backward = (L + 1) if self.fused_backward else (L + (L - 1))
-        return L + 1 + (L - 1) + 2 + 2 + backward + 2
+        prepare = 1 if self.uniform else L
+        return prepare + 1 + (L - 1) + 2 + 2 + backward + 2
 
     def train_step(self, x: torch.Tensor, labels: torch.Tensor, use_graph: bool = False) -> torch.Tensor:
         """One optimisation step on this rank's shard (x (B, F) fp32, labels (B,) integer).
@@ -279,8 +290,7 @@ class DWNNetwork:
                 self._ensure_buffers(B)
                 _native.call("dl_thermo_pack_t", x.contiguous().float(), self.thr, self.bits[0], B, self.F,
                              self.T, self.Bp)
-            for li in range(len(self.layers)):
-                _native.call("dl_dwn_prepare", self.tables[li], None, self.masks[li], self.N[li], self.n[li], 0.0, 0.0)
+            self._prepare_tables(need_efd=False)
             cur = self.bits[0]
             for li in range(len(self.layers)):
                 nxt = self.bits[li + 1] if li + 1 < len(self.layers) else self.last_bits
