@@ -365,7 +365,7 @@ constexpr int FUSED_CG = 8;  // 128-sample chunks per work item (1024 samples)
 // (group, node); the caller sums the groups in order (dl_sum_groups).  The output gradient and the
 // addresses are stored only when the layer below needs them, so for the first layer its
 // [N][Bp] fp32 gradient never reaches HBM.
-constexpr int FUSED_MAX_REG_CONTRIB = 4;  // inverse-map entries of a node kept in registers
+constexpr int FUSED_MAX_REG_CONTRIB = 3;  // inverse-map entries of a node kept in registers
 
 // T-table lookups of 4 samples: the lane index of each shuffle is the sample's address without
 // bit i (a shuffle takes its source lane modulo 32, so the bytes above need no masking).
@@ -402,9 +402,60 @@ __device__ __forceinline__ void load_chunk(ChunkData<CNT>& d, int c, const float
     }
 }
 
-// The chunks of one (group, node) item for a node with exactly CNT readers held in registers
-// (`extra` further readers, if any, are walked generically).
-template <bool DIRECT, int CNT>
+// Everything chunk c does once its data is in registers: output gradient, own addresses, stores,
+// histogram update.  NIN is the compile-time node input count (0 = use the runtime value n).
+template <bool DIRECT, int CNT, int NIN>
+__device__ __forceinline__ void consume_chunk(
+    const ChunkData<CNT>& d, int c, int n, int extra, int src_lane, int sh, float gscale,
+    const uint32_t (&words)[DL_MAX_FAST_N], const float (&tv)[FUSED_MAX_REG_CONTRIB],
+    const uint32_t (&lowm)[FUSED_MAX_REG_CONTRIB], const int32_t* __restrict__ inv_ent, int e_tail,
+    const uint8_t* __restrict__ addr_up, const float* __restrict__ g_up, const float* __restrict__ efd_up,
+    int n_up, uint32_t ugdiv, int64_t Bp, int64_t b0, float* __restrict__ go, uint8_t* __restrict__ ao,
+    float* __restrict__ mine) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (DIRECT) {
+        acc = d.g[0];
+        acc.x *= gscale; acc.y *= gscale; acc.z *= gscale; acc.w *= gscale;
+    } else {
+#pragma unroll
+        for (int k = 0; k < CNT; ++k) efd_accumulate(acc, d.g[k], d.a[k], lowm[k], tv[k]);
+        for (int k = 0; k < extra; ++k) {  // rare: more readers than registers
+            const int ent = __ldg(&inv_ent[e_tail + k]);
+            const int j = ent >> 3, i = ent & 7;
+            const float t = gscale * __ldg(efd_up + ((int64_t)j * n_up + i) * 32 + (threadIdx.x & 31));
+            const int64_t b = b0 + c * 128;
+            const uint32_t a = __ldg(reinterpret_cast<const uint32_t*>(addr_up + (int64_t)j * Bp + b));
+            const int64_t gr = ugdiv == 1 ? (int64_t)j : (int64_t)((uint32_t)j / ugdiv);
+            const float4 g = __ldg(reinterpret_cast<const float4*>(g_up + gr * Bp + b));
+            efd_accumulate(acc, g, a, ((1u << i) - 1u) * 0x01010101u, t);
+        }
+    }
+    // own addresses: fetch the word of this lane's samples from the lane that loaded it
+    uint32_t a = 0;
+#pragma unroll
+    for (int i = 0; i < DL_MAX_FAST_N; ++i) {
+        if (NIN > 0 ? i < NIN : i < n) {
+            const uint32_t t = __shfl_sync(0xffffffffu, words[i], c * 4 + src_lane) >> sh;
+            a |= dl_spread_nibble(t & 0xFu) << i;
+        }
+    }
+    if (go != nullptr) *reinterpret_cast<float4*>(go + c * 128) = acc;
+    if (ao != nullptr) *reinterpret_cast<uint32_t*>(ao + c * 128) = a;
+    // bin e of this lane lives at float offset e*32: byte offset e << 7
+    char* base = reinterpret_cast<char*>(mine);
+    *reinterpret_cast<float*>(base + ((a << 7) & 0x1F80u)) += acc.x;
+    *reinterpret_cast<float*>(base + ((a >> 1) & 0x1F80u)) += acc.y;
+    *reinterpret_cast<float*>(base + ((a >> 9) & 0x1F80u)) += acc.z;
+    *reinterpret_cast<float*>(base + ((a >> 17) & 0x1F80u)) += acc.w;
+}
+
+#define DL_CONSUME_ARGS n, extra, src_lane, sh, gscale, words, tv, lowm, inv_ent, e_tail, addr_up, g_up, efd_up, \
+                        n_up, ugdiv, Bp, b0, go, ao, mine
+
+// The chunks of one (group, node) item for a node with exactly CNT readers held in registers.
+// FULL: all 8 chunks exist; they are processed as 4 unrolled pairs with two register buffers
+// (ping-pong), so the loads of chunk c+1 fly while chunk c is consumed and nothing is copied.
+template <bool DIRECT, int CNT, int NIN, bool FULL>
 __device__ __forceinline__ void fused_chunks(
     int valid_chunks, int n, int extra, int src_lane, int sh, float gscale, const uint32_t (&words)[DL_MAX_FAST_N],
     const float* __restrict__ gdir, const uint8_t* const (&ap)[FUSED_MAX_REG_CONTRIB],
@@ -413,59 +464,36 @@ __device__ __forceinline__ void fused_chunks(
     const uint8_t* __restrict__ addr_up, const float* __restrict__ g_up, const float* __restrict__ efd_up,
     int n_up, uint32_t ugdiv, int64_t Bp, int64_t b0, float* __restrict__ go, uint8_t* __restrict__ ao,
     float* __restrict__ mine) {
-    ChunkData<CNT> cur;
-    load_chunk<DIRECT, CNT>(cur, 0, gdir, ap, gp);
-#pragma unroll 2
-    for (int c = 0; c < FUSED_CG; ++c) {
-        if (c >= valid_chunks) break;
-        ChunkData<CNT> nxt = cur;
-        if (c + 1 < valid_chunks) load_chunk<DIRECT, CNT>(nxt, c + 1, gdir, ap, gp);
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (DIRECT) {
-            acc = cur.g[0];
-            acc.x *= gscale; acc.y *= gscale; acc.z *= gscale; acc.w *= gscale;
-        } else {
+    if (FULL) {
+        ChunkData<CNT> even, odd;
+        load_chunk<DIRECT, CNT>(even, 0, gdir, ap, gp);
 #pragma unroll
-            for (int k = 0; k < CNT; ++k) efd_accumulate(acc, cur.g[k], cur.a[k], lowm[k], tv[k]);
-            for (int k = 0; k < extra; ++k) {  // rare: more readers than registers
-                const int ent = __ldg(&inv_ent[e_tail + k]);
-                const int j = ent >> 3, i = ent & 7;
-                const float t = gscale * __ldg(efd_up + ((int64_t)j * n_up + i) * 32 + (threadIdx.x & 31));
-                const int64_t b = b0 + c * 128;
-                const uint32_t a = __ldg(reinterpret_cast<const uint32_t*>(addr_up + (int64_t)j * Bp + b));
-                const int64_t gr = ugdiv == 1 ? (int64_t)j : (int64_t)((uint32_t)j / ugdiv);
-                const float4 g = __ldg(reinterpret_cast<const float4*>(g_up + gr * Bp + b));
-                efd_accumulate(acc, g, a, ((1u << i) - 1u) * 0x01010101u, t);
-            }
+        for (int c = 0; c < FUSED_CG; c += 2) {
+            load_chunk<DIRECT, CNT>(odd, c + 1, gdir, ap, gp);
+            consume_chunk<DIRECT, CNT, NIN>(even, c, DL_CONSUME_ARGS);
+            if (c + 2 < FUSED_CG) load_chunk<DIRECT, CNT>(even, c + 2, gdir, ap, gp);
+            consume_chunk<DIRECT, CNT, NIN>(odd, c + 1, DL_CONSUME_ARGS);
         }
-        // own addresses: fetch the word of this lane's samples from the lane that loaded it
-        uint32_t a = 0;
-#pragma unroll
-        for (int i = 0; i < DL_MAX_FAST_N; ++i) {
-            if (i < n) {
-                const uint32_t t = __shfl_sync(0xffffffffu, words[i], c * 4 + src_lane) >> sh;
-                a |= dl_spread_nibble(t & 0xFu) << i;
-            }
+    } else {
+        for (int c = 0; c < valid_chunks; ++c) {
+            ChunkData<CNT> d;
+            load_chunk<DIRECT, CNT>(d, c, gdir, ap, gp);
+            consume_chunk<DIRECT, CNT, NIN>(d, c, DL_CONSUME_ARGS);
         }
-        if (go != nullptr) *reinterpret_cast<float4*>(go + c * 128) = acc;
-        if (ao != nullptr) *reinterpret_cast<uint32_t*>(ao + c * 128) = a;
-        mine[(a & 0xFF) * 32] += acc.x;
-        mine[((a >> 8) & 0xFF) * 32] += acc.y;
-        mine[((a >> 16) & 0xFF) * 32] += acc.z;
-        mine[(a >> 24) * 32] += acc.w;
-        cur = nxt;
     }
 }
+#undef DL_CONSUME_ARGS
 
-template <bool DIRECT>
+template <bool DIRECT, int NIN>
 __global__ void __launch_bounds__(HIST_WARPS * 32, 5)
 dwn_bwd_fused_kernel(const uint8_t* __restrict__ addr_up, const float* __restrict__ g_up, int64_t gdiv_up,
                      float gscale_up, const float* __restrict__ efd_up, int n_up,
                      const int32_t* __restrict__ inv_ptr, const int32_t* __restrict__ inv_ent,
                      const uint32_t* __restrict__ in_bits, const int32_t* __restrict__ map,
                      float* __restrict__ g_out, uint8_t* __restrict__ addr_out,
-                     float* __restrict__ gt_partial, int64_t group_stride, int64_t N, int n, int64_t Bp) {
+                     float* __restrict__ gt_partial, int64_t group_stride, int64_t N, int n_rt, int64_t Bp) {
     __shared__ __align__(16) float hist_all[HIST_WARPS][64 * 32];
+    const int n = NIN > 0 ? NIN : n_rt;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float* hist = hist_all[warp];      // hist[e * 32 + lane]: bin e, private to the lane
     float* mine = hist + lane;
@@ -526,16 +554,24 @@ dwn_bwd_fused_kernel(const uint8_t* __restrict__ addr_up, const float* __restric
             __syncwarp();
 #define DL_FUSED_ARGS(extra_) valid_chunks, n, extra_, src_lane, sh, gscale_up, words, gdir, ap, gp, tv_r, lowm_r, \
                               inv_ent, e0 + FUSED_MAX_REG_CONTRIB, addr_up, g_up, efd_up, n_up, ugdiv, Bp, b0, go, ao, mine
-            if (DIRECT) {
-                fused_chunks<true, 0>(DL_FUSED_ARGS(0));
-            } else {
-                switch (cnt) {  // uniform over the warp
-                    case 0: fused_chunks<false, 0>(DL_FUSED_ARGS(0)); break;
-                    case 1: fused_chunks<false, 1>(DL_FUSED_ARGS(0)); break;
-                    case 2: fused_chunks<false, 2>(DL_FUSED_ARGS(0)); break;
-                    case 3: fused_chunks<false, 3>(DL_FUSED_ARGS(0)); break;
-                    default: fused_chunks<false, 4>(DL_FUSED_ARGS(cnt - FUSED_MAX_REG_CONTRIB)); break;
+            if (valid_chunks == FUSED_CG) {
+                if (DIRECT) {
+                    fused_chunks<true, 0, NIN, true>(DL_FUSED_ARGS(0));
+                } else {
+                    switch (cnt) {  // uniform over the warp
+                        case 0: fused_chunks<false, 0, NIN, true>(DL_FUSED_ARGS(0)); break;
+                        case 1: fused_chunks<false, 1, NIN, true>(DL_FUSED_ARGS(0)); break;
+                        case 2: fused_chunks<false, 2, NIN, true>(DL_FUSED_ARGS(0)); break;
+                        default: fused_chunks<false, 3, NIN, true>(DL_FUSED_ARGS(cnt - FUSED_MAX_REG_CONTRIB)); break;
+                    }
                 }
+            } else if (DIRECT) {
+                fused_chunks<true, 0, NIN, false>(DL_FUSED_ARGS(0));
+            } else {
+                // ragged last group: one generic body, every reader walked through the inverse map
+                fused_chunks<false, 0, NIN, false>(valid_chunks, n, cnt, src_lane, sh, gscale_up, words, gdir, ap, gp,
+                                                   tv_r, lowm_r, inv_ent, e0, addr_up, g_up, efd_up, n_up, ugdiv, Bp,
+                                                   b0, go, ao, mine);
             }
 #undef DL_FUSED_ARGS
             __syncwarp();
@@ -824,18 +860,20 @@ DL_EXPORT int dl_dwn_bwd_fused_t(const uint8_t* addr_up, const float* g_up, int6
     const int64_t blocks64 = dl_ceil_div(N, HIST_WARPS);
     const unsigned blocks = (unsigned)(blocks64 < cap ? blocks64 : cap);
     cudaStream_t s = dl_cast(stream);
-    // ask for the largest shared-memory carve-out so that 6 CTAs (6 x 32 KB of histograms) fit per SM
-    cudaFuncSetAttribute(dwn_bwd_fused_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    cudaFuncSetAttribute(dwn_bwd_fused_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    if (direct)
-        dwn_bwd_fused_kernel<true><<<blocks, HIST_WARPS * 32, 0, s>>>(nullptr, g_up, gdiv_up, gscale_up, nullptr, 1,
-                                                                      nullptr, nullptr, in_bits_t, map, g_out,
-                                                                      addr_out, gt_partial, group_stride, N, (int)n, Bp);
-    else
-        dwn_bwd_fused_kernel<false><<<blocks, HIST_WARPS * 32, 0, s>>>(addr_up, g_up, gdiv_up, gscale_up, efd_up,
-                                                                       (int)n_up, inv_ptr, inv_ent, in_bits_t, map,
-                                                                       g_out, addr_out, gt_partial, group_stride, N,
-                                                                       (int)n, Bp);
+#define DL_LAUNCH_FUSED(D, NN)                                                                                        \
+    do {                                                                                                              \
+        /* largest shared-memory carve-out, so that 5 CTAs (5 x 32 KB of histograms) fit per SM */                    \
+        cudaFuncSetAttribute(dwn_bwd_fused_kernel<D, NN>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);        \
+        dwn_bwd_fused_kernel<D, NN><<<blocks, HIST_WARPS * 32, 0, s>>>(                                                \
+            addr_up, g_up, gdiv_up, gscale_up, efd_up, (int)n_up, inv_ptr, inv_ent, in_bits_t, map, g_out, addr_out,   \
+            gt_partial, group_stride, N, (int)n, Bp);                                                                  \
+    } while (0)
+    if (direct) {
+        if (n == 6) DL_LAUNCH_FUSED(true, 6); else DL_LAUNCH_FUSED(true, 0);
+    } else {
+        if (n == 6) DL_LAUNCH_FUSED(false, 6); else DL_LAUNCH_FUSED(false, 0);
+    }
+#undef DL_LAUNCH_FUSED
     return dl_launch_status();
 }
 
