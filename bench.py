@@ -325,10 +325,11 @@ def run_gpu_arm(args):
     value = GLOBAL_BATCH / (ms_per_step * 1e-3)
     e2e_value = GLOBAL_BATCH / (ms_e2e / args.steps * 1e-3)
 
+    # live per-kernel timings (eager launches with events around each) for the roofline object; the
+    # step contains the gradient all-reduce, so every rank runs it
+    prof = profile_kernels(net, B, GLOBAL_BATCH)
     line = None
     if rank == 0:
-        # live per-kernel timings (eager launches with events around each) for the roofline object
-        prof = profile_kernels(net, B, GLOBAL_BATCH)
         top = max(prof.items(), key=lambda kv: kv[1]["ms"])
         top_name, top_info = top
         try:

@@ -145,7 +145,7 @@ struct MuxTree<0, BASE> {
 // Thread (x = group of 4 words, y = node): consecutive x read contiguous 16-byte pieces of each
 // input row; nodes and word groups are walked with grid-stride loops (no index division).
 template <int NIN>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 dwn_fwd_bits_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __restrict__ map,
                     const uint64_t* __restrict__ masks, uint32_t* __restrict__ out_bits, int N, int Q) {
     const int64_t Wp = (int64_t)Q << 2;
@@ -214,8 +214,10 @@ dwn_fwd_vals_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __restr
     }
 }
 
-// Last layer fused with GroupSum: CTA (x = 512-sample tile, y = class*S + slice); each warp
-// walks the nodes of its slice and keeps 4 running sums per lane.
+// Last layer fused with GroupSum.  One warp per (1024-sample group, class*S + slice): it walks the
+// nodes of its slice; for each node lane w loads word w of the node's 6 input rows (coalesced), the
+// 8 chunks of the group get their words by shuffle, and 32 running sums (8 chunks x 4 samples) stay
+// in registers.  The next node's words are loaded before the current node is consumed.
 __global__ void __launch_bounds__(128)
 dwn_fwd_groupsum_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __restrict__ map,
                         const float* __restrict__ tables, float* __restrict__ partial, int64_t N,
@@ -223,27 +225,55 @@ dwn_fwd_groupsum_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __r
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t Wp = Bp >> 5;
     const int L = 1 << n;
-    const int64_t b = ((int64_t)blockIdx.x * 4 + warp) * 128 + lane * 4;
-    if (b >= Bp) return;
+    const int64_t grp = (int64_t)blockIdx.x * 4 + warp;  // 1024-sample group
+    if (grp * 1024 >= Bp) return;
     const int64_t cls = blockIdx.y / (unsigned)S, s = blockIdx.y % (unsigned)S;
     const int64_t per = (gsz + S - 1) / S;
     const int64_t j0 = cls * gsz + s * per;
     int64_t j1 = j0 + per;
     if (j1 > (cls + 1) * gsz) j1 = (cls + 1) * gsz;
     if (j1 > N) j1 = N;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int64_t j = j0; j < j1; ++j) {
-        int32_t rows[DL_MAX_FAST_N];
+    const int64_t w = grp * 32 + lane;
+    const bool wvalid = w < Wp;
+    const int src_lane = lane >> 3, sh = (lane & 7) * 4;
+    float4 acc[8];
 #pragma unroll
-        for (int i = 0; i < DL_MAX_FAST_N; ++i) rows[i] = i < n ? __ldg(&map[j * n + i]) : 0;
-        const uint32_t a = addr4(in_bits, rows, n, Wp, b);
+    for (int c = 0; c < 8; ++c) acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+    uint32_t nxt[DL_MAX_FAST_N];
+#pragma unroll
+    for (int i = 0; i < DL_MAX_FAST_N; ++i)
+        nxt[i] = (i < n && j0 < j1 && wvalid) ? __ldg(in_bits + (int64_t)__ldg(&map[j0 * n + i]) * Wp + w) : 0u;
+    for (int64_t j = j0; j < j1; ++j) {
+        uint32_t words[DL_MAX_FAST_N];
+#pragma unroll
+        for (int i = 0; i < DL_MAX_FAST_N; ++i) words[i] = nxt[i];
+        if (j + 1 < j1) {
+#pragma unroll
+            for (int i = 0; i < DL_MAX_FAST_N; ++i)
+                nxt[i] = (i < n && wvalid) ? __ldg(in_bits + (int64_t)__ldg(&map[(j + 1) * n + i]) * Wp + w) : 0u;
+        }
         const float* tj = tables + j * L;
-        acc.x += __ldg(tj + (a & 0xFF));
-        acc.y += __ldg(tj + ((a >> 8) & 0xFF));
-        acc.z += __ldg(tj + ((a >> 16) & 0xFF));
-        acc.w += __ldg(tj + (a >> 24));
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            uint32_t a = 0;
+#pragma unroll
+            for (int i = 0; i < DL_MAX_FAST_N; ++i) {
+                if (i < n) {
+                    const uint32_t t = __shfl_sync(0xffffffffu, words[i], c * 4 + src_lane) >> sh;
+                    a |= dl_spread_nibble(t & 0xFu) << i;
+                }
+            }
+            acc[c].x += __ldg(tj + (a & 0xFF));
+            acc[c].y += __ldg(tj + ((a >> 8) & 0xFF));
+            acc[c].z += __ldg(tj + ((a >> 16) & 0xFF));
+            acc[c].w += __ldg(tj + (a >> 24));
+        }
     }
-    *reinterpret_cast<float4*>(partial + (int64_t)blockIdx.y * Bp + b) = acc;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        const int64_t b = grp * 1024 + c * 128 + lane * 4;
+        if (b < Bp) *reinterpret_cast<float4*>(partial + (int64_t)blockIdx.y * Bp + b) = acc[c];
+    }
 }
 
 __global__ void groupsum_reduce_kernel(const float* __restrict__ partial, float* __restrict__ logits_t,
@@ -776,9 +806,9 @@ DL_EXPORT int dl_dwn_fwd_vals_t(const uint32_t* in_bits_t, const int32_t* map, c
 DL_EXPORT int64_t dl_dwn_groupsum_splits(int64_t N, int64_t k) {
     if (N <= 0 || k <= 0) return 1;
     const int64_t gsz = dl_ceil_div(N, k);
-    int64_t s = gsz / 32;
+    int64_t s = gsz / 8;  // about 8 nodes per slice: enough warps even for one 1024-sample group
     if (s < 1) s = 1;
-    if (s > 16) s = 16;
+    if (s > 64) s = 64;
     return s;
 }
 
@@ -792,7 +822,7 @@ DL_EXPORT int dl_dwn_fwd_groupsum_t(const uint32_t* in_bits_t, const int32_t* ma
     const int S = (int)dl_dwn_groupsum_splits(N, k);
     const int64_t gsz = dl_ceil_div(N, k);
     DL_REQUIRE(k * S <= 65535);
-    dim3 grid((unsigned)dl_ceil_div(Bp, 512), (unsigned)(k * S));
+    dim3 grid((unsigned)dl_ceil_div(Bp, 4096), (unsigned)(k * S));
     dwn_fwd_groupsum_kernel<<<grid, 128, 0, dl_cast(stream)>>>(in_bits_t, map, tables, partial, N, (int)n,
                                                               gsz, S, Bp);
     if (cudaPeekAtLastError() != cudaSuccess) return DL_ERR_LAUNCH;

@@ -12,7 +12,9 @@ constexpr int TILE_B = 256;   // samples per CTA tile (8 words per feature row)
 constexpr int PACK_THREADS = 256;
 
 // x rows (B,F) -> packed feature-major bits.  MODE 0: bit = x > thr[f][t] (T bits per feature);
-// MODE 1: bit = x >= scalar threshold (T == 1).
+// MODE 1: bit = x >= scalar threshold (T == 1).  A CTA stages a 256-sample x 32-feature tile in
+// shared memory (coalesced row reads), then each warp takes 4 features: for every threshold it
+// ballots the 8 words of the tile and lanes 0..7 store them as one 32-byte piece of the output row.
 template <int MODE>
 __global__ void __launch_bounds__(PACK_THREADS)
 pack_t_kernel(const float* __restrict__ x, const float* __restrict__ thr, float scalar_thr,
@@ -22,27 +24,33 @@ pack_t_kernel(const float* __restrict__ x, const float* __restrict__ thr, float 
     const int64_t b0 = (int64_t)blockIdx.x * TILE_B;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // coalesced load: one warp reads 32 consecutive features of one sample row
+#pragma unroll 8
     for (int r = warp; r < TILE_B; r += PACK_THREADS / 32) {
         const int64_t b = b0 + r, f = f0 + lane;
         tile[r][lane] = (b < B && f < F) ? x[b * F + f] : 0.0f;
     }
     __syncthreads();
-    // warp w owns word w of the tile: lane = sample inside the word
-    const int64_t b = b0 + warp * 32 + lane;
-    const bool valid = b < B;
-    const int64_t word = (b0 >> 5) + warp;
-    for (int f = 0; f < TILE_F; ++f) {
-        if (f0 + f >= F) break;
-        const float v = tile[warp * 32 + lane][f];
-        if (MODE == 0) {
-            for (int t = 0; t < T; ++t) {
-                const float th = __ldg(&thr[(f0 + f) * T + t]);
-                const uint32_t w = __ballot_sync(0xffffffffu, valid && (v > th));
-                if (lane == 0 && word < Wp) bits_t[((f0 + f) * T + t) * Wp + word] = w;
+    const int64_t word0 = b0 >> 5;
+    for (int fl = warp * 4; fl < warp * 4 + 4; ++fl) {
+        const int64_t f = f0 + fl;
+        if (f >= F) break;  // uniform over the warp
+        float v[8];
+        bool valid[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            v[k] = tile[k * 32 + lane][fl];
+            valid[k] = b0 + k * 32 + lane < B;
+        }
+        for (int t = 0; t < T; ++t) {
+            const float th = MODE == 0 ? __ldg(&thr[f * T + t]) : scalar_thr;
+            uint32_t mine = 0;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const bool bit = valid[k] && (MODE == 0 ? v[k] > th : v[k] >= th);
+                const uint32_t w = __ballot_sync(0xffffffffu, bit);
+                if (lane == k) mine = w;
             }
-        } else {
-            const uint32_t w = __ballot_sync(0xffffffffu, valid && (v >= scalar_thr));
-            if (lane == 0 && word < Wp) bits_t[(f0 + f) * Wp + word] = w;
+            if (lane < 8 && word0 + lane < Wp) bits_t[(f * T + t) * Wp + word0 + lane] = mine;
         }
     }
 }

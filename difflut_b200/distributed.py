@@ -5,6 +5,7 @@ blocks; every rank holds the full tables and index maps; the only exchange per s
 all-reduce of the flat table-gradient buffer.  Inference shards rows with no communication.
 """
 
+import datetime
 import os
 from typing import Optional, Tuple
 
@@ -12,10 +13,11 @@ import torch
 import torch.distributed as dist
 
 
-def init_from_env(backend: Optional[str] = None) -> Tuple[int, int, int]:
+def init_from_env(backend: Optional[str] = None, timeout_s: float = 180.0) -> Tuple[int, int, int]:
     """Initialise the default process group from RANK / WORLD_SIZE / LOCAL_RANK / MASTER_*.
 
-    Returns (rank, world, local_rank).  Without WORLD_SIZE > 1 nothing is initialised.
+    Returns (rank, world, local_rank).  Without WORLD_SIZE > 1 nothing is initialised.  A collective
+    that a rank never joins ends with an error after `timeout_s` instead of waiting forever.
     """
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -25,9 +27,10 @@ def init_from_env(backend: Optional[str] = None) -> Tuple[int, int, int]:
             backend = "nccl" if torch.cuda.is_available() else "gloo"
         if backend == "nccl":
             torch.cuda.set_device(local)
-            dist.init_process_group(backend, device_id=torch.device("cuda", local))
+            dist.init_process_group(backend, device_id=torch.device("cuda", local),
+                                    timeout=datetime.timedelta(seconds=timeout_s))
         else:
-            dist.init_process_group(backend)
+            dist.init_process_group(backend, timeout=datetime.timedelta(seconds=timeout_s))
     elif torch.cuda.is_available():
         torch.cuda.set_device(local)
     return rank, world, local
