@@ -265,6 +265,9 @@ def run_gpu_arm(args):
     from difflut_b200.distributed import init_from_env, max_over_ranks
 
     rank, world, local = init_from_env()
+    trace = (lambda msg: print(f"[bench rank {rank}] {msg}", file=sys.stderr, flush=True)) \
+        if os.environ.get("DIFFLUT_BENCH_TRACE") else (lambda msg: None)
+    trace("process group ready")
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     device = torch.device("cuda", local)
@@ -305,21 +308,26 @@ def run_gpu_arm(args):
         net.train_step(x_pin, y_pin, use_graph=use_graph)
         loss_pin.copy_(net.loss, non_blocking=True)
 
-    for _ in range(max(args.warmup, 3)):
+    trace("network built")
+    for i in range(max(args.warmup, 3)):
         step_resident()
+        trace(f"warm-up step {i} enqueued")
     barrier()
+    trace("warm-up done")
     with ClockSampler(local) as clocks:
         ms_total = timed(step_resident, args.steps)
         # keep the sampler alive for at least a few samples on very short runs
         if ms_total < 500:
-            t_end = time.time() + 0.5
-            while time.time() < t_end:
+            # same count on every rank (ms_total is already the max over ranks): the step holds a collective
+            for _ in range(int(500.0 / max(ms_total / args.steps, 1e-3)) + 1):
                 step_resident()
             torch.cuda.synchronize()
     clock_summary = clocks.summary()
+    trace("resident timing done")
     for _ in range(3):
         step_e2e()
     ms_e2e = timed(step_e2e, args.steps)
+    trace("e2e timing done")
 
     ms_per_step = ms_total / args.steps
     value = GLOBAL_BATCH / (ms_per_step * 1e-3)
@@ -328,6 +336,7 @@ def run_gpu_arm(args):
     # live per-kernel timings (eager launches with events around each) for the roofline object; the
     # step contains the gradient all-reduce, so every rank runs it
     prof = profile_kernels(net, B, GLOBAL_BATCH)
+    trace("kernel profile done")
     line = None
     if rank == 0:
         top = max(prof.items(), key=lambda kv: kv[1]["ms"])
@@ -365,8 +374,15 @@ def run_gpu_arm(args):
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
     barrier()
+    trace("finished")
     if world > 1:
-        dist.destroy_process_group()
+        # drop the captured graph (it references NCCL work) before leaving; the communicator is not
+        # torn down collectively: a rank that is slow to get here must not keep the others waiting
+        net._graph = None
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():
