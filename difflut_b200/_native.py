@@ -45,6 +45,7 @@ SIGNATURES = {
     "dl_groupsum_rows_bwd": "ppllLf s".replace("L", "l"),
     "dl_groupsum_t": "ppllfl s",
     "dl_dwn_fwd_groupsum_t": "ppppplllfl s",
+    "dl_dwn_fwd_groupsum_noalloc_t": "ppppllLfl s".replace("L", "l"),
     "dl_popcount_groupsum_t": "ppllll s",
     "dl_ce_t": "pppppllll s",
     "dl_adam_step": "ppppplfffff s",

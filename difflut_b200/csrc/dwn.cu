@@ -5,6 +5,8 @@
 // coalesced row segment.  Per sample the EFD backward is one address, one histogram update and
 // n lookups in the per-step transform table `efd_t` instead of the reference's 2^n-term loop
 // (difflut/nodes/dwn_node.py:195-227).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace {
@@ -730,6 +732,34 @@ __global__ void dwn_mapped_bwd_tables_atomic_kernel(const float* __restrict__ xm
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// built-in scratch for the entry point that must not allocate
+// ------------------------------------------------------------------------------------------
+
+// 16 MiB of device memory owned by the library itself (every GPU that loads it holds this until the
+// process exits).  Host code never uses the symbol as a pointer: `static_scratch_address` asks the
+// runtime for the symbol's device address once per device and caches it.
+constexpr int64_t STATIC_SCRATCH_FLOATS = DL_STATIC_SCRATCH_BYTES / 4;
+static __device__ __align__(256) float dl_static_scratch[STATIC_SCRATCH_FLOATS];
+
+constexpr int MAX_DEVICES = 64;
+std::mutex g_scratch_mutex;
+float* g_scratch_address[MAX_DEVICES] = {nullptr};
+
+// Device address of dl_static_scratch on the CURRENT device (looked up on first use per device).
+int static_scratch_address(float** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return DL_ERR_LAUNCH;
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (g_scratch_address[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, dl_static_scratch) != cudaSuccess || p == nullptr) return DL_ERR_LAUNCH;
+        g_scratch_address[dev] = static_cast<float*>(p);
+    }
+    *out = g_scratch_address[dev];
+    return DL_OK;
+}
+
 int grid_for(int64_t threads_needed, int block) {
     const int64_t blocks = dl_ceil_div(threads_needed, block);
     const int64_t cap = (int64_t)DL_NUM_SMS * 32;
@@ -829,6 +859,20 @@ DL_EXPORT int dl_dwn_fwd_groupsum_t(const uint32_t* in_bits_t, const int32_t* ma
     groupsum_reduce_kernel<<<grid_for(k * Bp, 256), 256, 0, dl_cast(stream)>>>(partial, logits_t, (int)k, S,
                                                                             1.0f / tau, Bp);
     return dl_launch_status();
+}
+
+DL_EXPORT int dl_dwn_fwd_groupsum_noalloc_t(const uint32_t* in_bits_t, const int32_t* map, const float* tables,
+                                            float* logits_t, int64_t N, int64_t n, int64_t k, float tau, int64_t Bp,
+                                            dl_stream_t stream) {
+    DL_REQUIRE(N > 0 && k > 0 && Bp > 0);
+    const int64_t need = k * dl_dwn_groupsum_splits(N, k) * Bp;
+    if (need > STATIC_SCRATCH_FLOATS) return DL_ERR_TOO_LARGE;
+    float* scratch = nullptr;
+    const int rc = static_scratch_address(&scratch);
+    if (rc != DL_OK) return rc;
+    // every partial sum the reduction pass reads is written by the first pass of this same call, so
+    // what an earlier call left in the scratch does not matter and nothing needs clearing
+    return dl_dwn_fwd_groupsum_t(in_bits_t, map, tables, scratch, logits_t, N, n, k, tau, Bp, stream);
 }
 
 DL_EXPORT int dl_dwn_bwd_tables_t(const uint32_t* in_bits_t, const int32_t* map, const float* g_t,

@@ -42,6 +42,7 @@ enum {
 
 #define DL_BATCH_ALIGN 128 /* samples; Bp is a multiple of this */
 #define DL_MAX_FAST_N 6    /* n <= 6: tables are 64-bit words / 32-lane shuffles */
+#define DL_STATIC_SCRATCH_BYTES (16 << 20) /* built-in scratch of dl_dwn_fwd_groupsum_noalloc_t */
 
 int dl_version(void);
 const char* dl_error_string(int code);
@@ -216,6 +217,25 @@ int64_t dl_dwn_groupsum_splits(int64_t N, int64_t k);
 int dl_dwn_fwd_groupsum_t(const uint32_t* in_bits_t, const int32_t* map, const float* tables,
                           float* partial, float* logits_t, int64_t N, int64_t n, int64_t k,
                           float tau, int64_t Bp, dl_stream_t stream);
+
+/* Same result as dl_dwn_fwd_groupsum_t, for hosts that may not allocate device memory.  It has no
+ * counterpart in the reference.  Some callers of this library cannot hand it a scratch buffer:
+ * an inference server whose device memory was carved up at start-up and belongs to another
+ * component, a latency-critical thread that must not pay for cudaMalloc's device-wide
+ * synchronisation, or a plain C host with no caching allocator at all.  For them the partial class
+ * sums live in a fixed array inside the library (DL_STATIC_SCRATCH_BYTES = 16 MiB, resident on
+ * every GPU that loads the library until the process exits); the caller passes only inputs and
+ * the logits output.  Limit: k * dl_dwn_groupsum_splits(N, k) * Bp * 4 bytes must fit in that
+ * array (the 4000-node, 10-class, 8192-sample case needs 15.6 MiB); anything larger returns
+ * DL_ERR_TOO_LARGE and launches nothing.  The first call on a device looks up the array's device
+ * address (cudaGetSymbolAddress) and caches it per device; make that first call before starting
+ * any stream capture.  No cudaMalloc / cudaFree or other allocating routine is called.  All calls
+ * on one GPU share the one array: calls whose kernels can overlap on the GPU (different streams,
+ * no ordering between them) race on it and must be serialised by the caller.  Nothing in the
+ * array has to be zero on entry - each call overwrites every element it later reads. */
+int dl_dwn_fwd_groupsum_noalloc_t(const uint32_t* in_bits_t, const int32_t* map, const float* tables,
+                                  float* logits_t, int64_t N, int64_t n, int64_t k, float tau,
+                                  int64_t Bp, dl_stream_t stream);
 
 /* Mean cross-entropy over `B_global` samples of which this call holds B (user code in the
  * reference: nn.CrossEntropyLoss, e.g. tests/test_layers/test_convolutional_learning.py:85-111).
