@@ -1,0 +1,211 @@
+"""Host-side behaviour of the reference-compatible API (no GPU): registry, configs, validation,
+index maps, stacked layers with node views, reference-format state dicts."""
+
+import hashlib
+import warnings
+
+import numpy as np
+import pytest
+import torch
+
+warnings.simplefilter("ignore")
+
+import difflut_b200 as difflut  # noqa: E402
+from difflut_b200.encoder import ThermometerEncoder  # noqa: E402
+from difflut_b200.layers import LayerConfig, LearnableLayer, RandomLayer  # noqa: E402
+from difflut_b200.nodes import DWNNode, NodeConfig, ProbabilisticNode  # noqa: E402
+from difflut_b200.utils import GroupSum  # noqa: E402
+from difflut_b200.utils.warnings import DefaultValueWarning  # noqa: E402
+
+
+def test_registry_names_and_errors():
+    R = difflut.REGISTRY
+    assert R.get_node("dwn") is DWNNode and R.get_node("probabilistic") is ProbabilisticNode
+    assert R.get_layer("random") is RandomLayer and R.get_layer("learnable") is LearnableLayer
+    assert R.get_encoder("thermometer") is ThermometerEncoder
+    with pytest.raises(ValueError, match="not found"):
+        R.get_node("nope")
+    with pytest.raises(ValueError):
+        R.get_initializer("nope")
+    assert set(R.list_all()) == {"nodes", "layers", "convolutional_layers", "encoders", "initializers", "regularizers"}
+
+
+def test_registry_decorators_and_suffix_aliases():
+    R = difflut.registry.Registry()
+
+    @R.register_initializer()
+    def my_init(param, **kw):
+        param.fill_(1.0)
+
+    @R.register_regularizer("L2_regularizer")
+    def l2(node):
+        return node.luts.pow(2).sum()
+
+    assert R.get_initializer("my") is my_init and R.get_initializer("MY_INIT") is my_init
+    assert R.get_regularizer("l2") is l2
+    with pytest.warns(UserWarning):
+        R.register_node("x")(int)
+        R.register_node("x")(float)
+    assert R.build_node("x") == 0.0
+
+
+def test_node_config_to_dict():
+    cfg = NodeConfig(input_dim=6, output_dim=1, extra_params={"alpha": 0.1})
+    assert cfg.to_dict() == {"input_dim": 6, "output_dim": 1, "alpha": 0.1}
+    c2 = cfg.copy()
+    c2.extra_params["alpha"] = 0.2
+    assert cfg.extra_params["alpha"] == 0.1
+
+
+def test_layer_config_validation():
+    with pytest.raises(ValueError):
+        LayerConfig(flip_probability=1.5)
+    with pytest.raises(ValueError):
+        LayerConfig(grad_stabilization="bogus")
+    with pytest.raises(TypeError):
+        RandomLayer(10, 4, DWNNode, NodeConfig(input_dim=2, output_dim=1), layer_config={"flip_probability": 0.1})
+    assert "default" in repr(LayerConfig())
+
+
+def test_validation_errors_match_reference_types():
+    with pytest.raises(ValueError):
+        RandomLayer(0, 4, DWNNode, NodeConfig(input_dim=2, output_dim=1))
+    with pytest.raises(ValueError):
+        RandomLayer(10, -1, DWNNode, NodeConfig(input_dim=2, output_dim=1))
+    with pytest.raises(ValueError):
+        DWNNode(input_dim=0, output_dim=1)
+    with pytest.raises(TypeError):
+        DWNNode(input_dim=2, output_dim=1, init_fn="not callable")
+    with pytest.raises(ValueError):
+        GroupSum(k=0, tau=1.0, use_randperm=False)
+    with pytest.raises(ValueError):
+        GroupSum(k=2, tau=-1.0, use_randperm=False)
+    layer = RandomLayer(10, 4, DWNNode, NodeConfig(input_dim=2, output_dim=1))
+    with pytest.raises(ValueError):
+        layer(torch.zeros(3, 11))
+    with pytest.raises(ValueError):
+        layer(torch.zeros(3, 10, 1))
+    with pytest.raises(ValueError):
+        layer(torch.zeros(0, 10))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        layer(torch.zeros(3, 10))  # valid shape, but there is no CPU path
+    with pytest.raises(RuntimeError):
+        ThermometerEncoder(num_bits=2).encode(torch.zeros(2, 2))
+
+
+def test_default_value_warnings():
+    with pytest.warns(DefaultValueWarning):
+        DWNNode(input_dim=3, output_dim=1)  # alpha / beta defaults
+    with pytest.warns(DefaultValueWarning):
+        GroupSum()
+
+
+def test_index_maps_equal_reference(golden):
+    g = golden("index_maps")
+    for name in ("c1", "cov_rem", "cov_exact", "small_in", "n4"):
+        I, N, n, seed, cov = (int(v) for v in g[name + "_args"])
+        from difflut_b200.layers.random_layer import draw_random_mapping
+
+        before = torch.get_rng_state()
+        draw_random_mapping(I, N, n, seed, bool(cov))
+        assert torch.equal(before, torch.get_rng_state()), "drawing the map must not disturb the global RNG"
+        layer = RandomLayer(I, N, DWNNode, NodeConfig(input_dim=n, output_dim=1), seed=seed,
+                            ensure_full_input_coverage=bool(cov))
+        assert np.array_equal(layer._mapping_indices.numpy(), g[name])
+        assert layer.get_mapping_matrix().dtype == torch.int64
+    for name, I, N, seed in (("c4_l1", 6272, 16000, 0), ("c4_l2", 16000, 8000, 1), ("c4_l3", 8000, 4000, 2)):
+        layer = RandomLayer(I, N, DWNNode, NodeConfig(input_dim=6, output_dim=1), seed=seed)
+        digest = np.frombuffer(hashlib.sha256(layer._mapping_indices.numpy().tobytes()).digest(), dtype=np.uint8)
+        assert np.array_equal(digest, g[name + "_sha256"])
+    given = torch.arange(12).reshape(3, 4)
+    layer = RandomLayer(20, 3, DWNNode, NodeConfig(input_dim=4, output_dim=1), mapping_indices=given)
+    assert torch.equal(layer._mapping_indices.long(), given) and layer._mapping_indices.dtype == torch.int16
+
+
+def test_stacked_layer_structure_and_node_views():
+    calls = []
+
+    def init_fn(param, **kw):
+        calls.append((tuple(param.shape), kw.get("input_dim")))
+        param.fill_(0.25)
+
+    layer = RandomLayer(40, 7, DWNNode, NodeConfig(input_dim=4, output_dim=2, init_fn=init_fn), seed=1)
+    assert layer.n == 4 and layer.output_dim_per_node == 2 and layer.output_size == 7
+    assert len(calls) == 7 and calls[0] == ((2, 16), 4)  # per node, reference-shaped, input_dim injected
+    assert layer.luts.shape == (7, 2, 16) and bool((layer.luts == 0.25).all())
+    assert len(layer.nodes) == 7
+    node = layer.nodes[3]
+    assert isinstance(node, DWNNode) and node.luts.shape == (2, 16) and node.num_inputs == 4 and node.output_dim == 2
+    with torch.no_grad():
+        node.luts.fill_(2.0)  # a view: the layer sees the edit
+    assert bool((layer.luts[3] == 2.0).all()) and bool((layer.luts[2] == 0.25).all())
+    assert [nd.input_dim for nd in layer.nodes][:2] == [4, 4] and len(layer.nodes[-2:]) == 2
+    names = [n for n, _ in layer.named_parameters()]
+    assert names == ["luts"]
+    assert float(layer.regularization()) == 0.0
+    reg_layer = RandomLayer(40, 3, DWNNode, NodeConfig(input_dim=4, output_dim=1,
+                            regularizers={"l2": [lambda nd: nd.luts.pow(2).sum(), 0.5, {}]}), seed=1)
+    assert float(reg_layer.regularization()) == pytest.approx(0.5 * float(reg_layer.luts.pow(2).sum()), rel=1e-5)
+    p = RandomLayer(40, 5, ProbabilisticNode, NodeConfig(input_dim=3, output_dim=2, extra_params={"temperature": 0.5}))
+    assert p.raw_weights.shape == (5, 8, 2) and p.nodes[0].raw_weights.shape == (8, 2)
+    assert float(p.nodes[0].temperature) == 0.5 and p.nodes[0].binary_combinations.shape == (8, 3)
+
+
+def test_state_dict_uses_reference_keys_and_round_trips():
+    layer = RandomLayer(30, 4, DWNNode, NodeConfig(input_dim=3, output_dim=1), seed=2)
+    sd = layer.state_dict()
+    assert set(sd) == {"_mapping_indices"} | {f"nodes.{i}.{k}" for i in range(4) for k in ("luts", "alpha", "beta")}
+    assert sd["nodes.2.luts"].shape == (1, 8) and sd["_mapping_indices"].dtype == torch.int16
+    other = RandomLayer(30, 4, DWNNode, NodeConfig(input_dim=3, output_dim=1), seed=9)
+    other.load_state_dict(sd)
+    assert torch.equal(other.luts, layer.luts) and torch.equal(other._mapping_indices, layer._mapping_indices)
+    # the stacked layout loads too
+    third = RandomLayer(30, 4, DWNNode, NodeConfig(input_dim=3, output_dim=1), seed=9)
+    third.load_state_dict({"_mapping_indices": layer._mapping_indices, "luts": layer.luts.detach()})
+    assert torch.equal(third.luts, layer.luts)
+    p = RandomLayer(30, 2, ProbabilisticNode, NodeConfig(input_dim=3, output_dim=1), seed=2)
+    psd = p.state_dict()
+    assert {"nodes.0.raw_weights", "nodes.1.temperature", "nodes.0.binary_combinations"} <= set(psd)
+    q = RandomLayer(30, 2, ProbabilisticNode, NodeConfig(input_dim=3, output_dim=1), seed=2)
+    q.load_state_dict(psd)
+    assert torch.equal(q.raw_weights, p.raw_weights)
+
+
+def test_learnable_layer_host_logic():
+    layer = LearnableLayer(16, 3, DWNNode, NodeConfig(input_dim=2, output_dim=1), tau=0.5, tau_start=1.0,
+                           tau_min=0.01, tau_decay_iters=100.0, use_cuda_soft=False)
+    assert layer.tau == 1.0 and layer.mapping.W.shape == (6, 16)  # tau argument is ignored, as in the reference
+    layer.update_tau(100)
+    assert layer.tau == pytest.approx(0.1) and layer.mapping.tau == layer.tau
+    layer.update_tau(10_000)
+    assert layer.tau == 0.01
+    assert layer.get_mapping_matrix().shape == (3, 2)
+    layer.eval()
+    idx = layer.mapping.hard_indices()
+    assert torch.equal(idx.long(), torch.argmax(layer.mapping.W, -1))
+    layer.train()
+    assert layer.mapping._cache_valid is False
+
+
+def test_thermometer_fit_host_side(golden):
+    g = golden("thermometer")
+    enc = ThermometerEncoder(num_bits=3)
+    assert not enc.is_fitted
+    assert enc.fit(torch.from_numpy(g["x_fit_T3"])) is enc and enc.is_fitted
+    assert torch.equal(enc.thresholds, torch.from_numpy(g["thr_T3"]))
+    assert "thresholds" not in enc.state_dict()
+    assert torch.equal(enc.get_thresholds(torch.from_numpy(g["x_fit_T3"])), enc.thresholds)
+    assert repr(enc) == "ThermometerEncoder(num_bits=3, flatten=True)"
+
+
+def test_mixin_helpers_on_cpu():
+    layer = RandomLayer(8, 2, DWNNode, NodeConfig(input_dim=2, output_dim=1),
+                        layer_config=LayerConfig(flip_probability=0.5, grad_stabilization="layerwise"))
+    x = torch.zeros(64, 8)
+    flipped = layer._apply_bit_flip(x)
+    assert 0 < float(flipped.mean()) < 1 and set(flipped.unique().tolist()) <= {0.0, 1.0}
+    g = torch.randn(16, 2) * 10
+    out = layer._apply_gradient_stabilization(g)
+    assert float(out.pow(2).mean()) == pytest.approx(1.0, rel=1e-3)
+    layer.eval()
+    assert layer._apply_bit_flip(x) is x
