@@ -28,6 +28,10 @@ if ROOT not in sys.path:
 SIZES = (16000, 8000, 4000)
 FEATURES, THERMO_BITS, CLASSES, TAU, GLOBAL_BATCH, LR = 784, 8, 10, 33.0, 8192, 1e-2
 METRIC = "train samples/s (fwd+bwd) 3-layer n=6 DWN"
+# dram__bytes_read.sum + dram__bytes_write.sum of the three dl_dwn_bwd_fused_t launches of one step at
+# per-GPU batch 8192, from one ncu capture (profiles/dwn_bwd_fused_kernel_c4_B8192.txt); the traffic is
+# proportional to the batch (every term but the 7 MB of tables scales with it), so other batches scale it
+NCU_TRAFFIC_BWD_FUSED_B8192 = 831.5e6
 WORKLOAD = "dwn3_16000-8000-4000_n6_T8_globalbatch8192_adam"
 
 
@@ -352,7 +356,8 @@ def run_gpu_arm(args):
         roofline = {
             "bound": "hbm", "kernel": top_name, "launches_per_step": top_info["launches"],
             "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
-            "frac": achieved / peak, "traffic": None,
+            "frac": achieved / peak,
+            "traffic": (NCU_TRAFFIC_BWD_FUSED_B8192 * B / 8192.0) if top_name == "dl_dwn_bwd_fused_t" else None,
             "algorithmic_bytes_per_launch_set": alg, "kernel_ms_per_step": top_info["ms"],
             "step_achieved_gbs": step_alg / (ms_per_step * 1e-3) / 1e9 * (1 if world == 1 else 1),
             "step_algorithmic_bytes": step_alg,
