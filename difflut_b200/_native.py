@@ -41,6 +41,11 @@ SIGNATURES = {
     "dl_prob_fwd_groupsum_t": "pppfpppllllfl s",
     "dl_prob_bwd_t": "pppfplfpplllll s",
     "dl_seg_sum_t": "ppppll s",
+    "dl_gemm_bf16_tn": "ppplllp s",
+    "dl_softmax_rows_bf16": "pfpplll s",
+    "dl_softmax_bwd_rows": "ppfpll s",
+    "dl_f32_to_bf16": "ppplllI s".replace("I", "i"),
+    "dl_bf16_transpose": "ppllll s",
     "dl_groupsum_rows": "ppllLf s".replace("L", "l"),
     "dl_groupsum_rows_bwd": "ppllLf s".replace("L", "l"),
     "dl_groupsum_t": "ppllfl s",

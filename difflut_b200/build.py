@@ -45,7 +45,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
             subprocess.run(cmd, check=True)
         objs.append(obj)
     if force or _stale(LIB_PATH, objs):
-        cmd = [nvcc, "-shared", "-o", LIB_PATH] + objs + ["-lcuda"]
+        cmd = [nvcc, "-shared", "-o", LIB_PATH] + objs
         subprocess.run(cmd, check=True)
     return LIB_PATH
 

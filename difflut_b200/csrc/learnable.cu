@@ -1,0 +1,427 @@
+// LearnableLayer soft connectivity: row softmax + a tcgen05 / TMA tensor-core GEMM.
+//
+// The reference computes `x @ softmax(W/tau, -1).T` with F.softmax + torch.matmul
+// (difflut/layers/learnable_layer.py:253-255) and lets autograd produce the two backward GEMMs.
+// Here the three contractions run on one kernel, C[M,N] (fp32) = A[M,K] * B[N,K]^T with bf16
+// operands: TMA (cp.async.bulk.tensor) stages 128x64 / 256x64 operand tiles in 128-byte-swizzled
+// shared memory, one elected thread issues tcgen05.mma (kind::f16, fp32 accumulator in tensor
+// memory), and four epilogue warps read the accumulator back with tcgen05.ld.
+// No cluster, no multicast.  Every wait on an mbarrier is bounded: when a wait runs out the kernel
+// records where it gave up in `status` and leaves (after freeing its tensor memory).
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;          // accumulator rows = TMEM lanes
+constexpr int BN = 256;          // accumulator columns = TMEM columns
+constexpr int BK = 64;           // 64 bf16 = 128 bytes: one swizzle row
+constexpr int UMMA_K = 16;       // K per tcgen05.mma for 16-bit operands
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;   // 16 KB
+constexpr int B_BYTES = BN * BK * 2;   // 32 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int GEMM_THREADS = 192;      // warp 0: TMA, warp 1: MMA, warps 2..5: epilogue
+constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;  // every wait gives up after about one second
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+// Bounded wait on a phase parity; false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    const long long start = clock64();
+    for (uint32_t it = 0;; ++it) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if ((it & 63u) == 63u && clock64() - start > WAIT_LIMIT_CYCLES) return false;
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major bf16 tile whose rows are 128 bytes, 128-byte swizzle:
+// start address >> 4, stride between 8-row groups = 1024 bytes, descriptor version 1, layout 2.
+__device__ __forceinline__ uint64_t umma_desc_k_major_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;                   // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024u >> 4) << 32;        // stride byte offset
+    d |= (uint64_t)1 << 46;                   // descriptor version
+    d |= (uint64_t)2 << 61;                   // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor: D = f32, A = B = bf16, both K-major, N and M of the tile.
+__device__ __forceinline__ uint32_t umma_idesc_bf16(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+// status[0] = 0 ok, otherwise (role << 8 | stage) of the wait that gave up
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    float* __restrict__ C, int M, int N, int K, int* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    // the swizzled tiles need 1024-byte alignment
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_ready = empty + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_m = blockIdx.y, tile_n = blockIdx.x;
+    const int kblocks = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(acc_ready, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // tensor memory for the 128 x 256 fp32 accumulator
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)BN)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < kblocks; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t use = kb / STAGES;
+                if (use > 0 && !mbar_wait(&empty[s], (use - 1) & 1)) {
+                    atomicCAS(status, 0, (1 << 8) | s);
+                    break;
+                }
+                uint8_t* a_dst = tiles + s * STAGE_BYTES;
+                uint8_t* b_dst = a_dst + A_BYTES;
+                mbar_expect_tx(&full[s], STAGE_BYTES);
+                tma_load_2d(a_dst, &map_a, &full[s], kb * BK, tile_m * BM);
+                tma_load_2d(b_dst, &map_b, &full[s], kb * BK, tile_n * BN);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_bf16(BM, BN);
+            bool ok = true;
+            for (int kb = 0; kb < kblocks && ok; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t use = kb / STAGES;
+                if (!mbar_wait(&full[s], use & 1)) {
+                    atomicCAS(status, 0, (2 << 8) | s);
+                    ok = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = smem_u32(tiles + s * STAGE_BYTES);
+                const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    // inside the 128-byte swizzle row the next 16 elements start 32 bytes further
+                    const uint64_t adesc = umma_desc_k_major_sw128(a_addr + k * UMMA_K * 2);
+                    const uint64_t bdesc = umma_desc_k_major_sw128(b_addr + k * UMMA_K * 2);
+                    umma_bf16(tmem_base, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(&empty[s]);  // the stage is free again once these MMAs have read it
+            }
+            umma_commit(acc_ready);      // arrives when every MMA issued so far has finished
+        }
+    } else {
+        // epilogue: warp w may read TMEM lanes 32*(w%4) .. +31; one accumulator row per thread
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const int64_t grow = (int64_t)tile_m * BM + row;
+        const bool ok = mbar_wait(acc_ready, 0);
+        if (!ok && lane == 0) atomicCAS(status, 0, (3 << 8));
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+                      "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+                      "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+                      "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                    : "r"(taddr)
+                    : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (grow < M) {
+                    const int64_t gcol = (int64_t)tile_n * BN + c0;
+                    float* dst = C + grow * N + gcol;
+                    if (gcol + 32 <= N && (N & 3) == 0) {
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            reinterpret_cast<float4*>(dst)[q] =
+                                make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                            __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 32; ++q)
+                            if (gcol + q < N) dst[q] = __uint_as_float(r[q]);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN)
+                     : "memory");
+    }
+}
+
+// bf16 [rows][cols] row-major tensor map with a (box_rows x 64) box and 128-byte swizzle
+int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int box_rows) {
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    // the driver entry point is looked up through the runtime, so the library itself does not link
+    // against libcuda and still loads on a machine without a driver
+    typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static encode_fn encode = nullptr;
+    if (encode == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+            fn == nullptr)
+            return DL_ERR_LAUNCH;
+        encode = reinterpret_cast<encode_fn>(fn);
+    }
+    const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return rc == CUDA_SUCCESS ? DL_OK : DL_ERR_ARG;
+}
+
+// ------------------------------------------------------------------------------------------
+// softmax rows, conversions
+// ------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ float block_reduce(float v, float* scratch, bool is_max) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float u = __shfl_xor_sync(0xffffffffu, v, o);
+        v = is_max ? fmaxf(v, u) : v + u;
+    }
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    const int nw = blockDim.x >> 5;
+    float r = is_max ? -INFINITY : 0.f;
+    for (int w = 0; w < nw; ++w) r = is_max ? fmaxf(r, scratch[w]) : r + scratch[w];
+    return r;
+}
+
+// one CTA per row: S = softmax(W / tau) written as bf16 hi (+ optional lo = bf16(S - hi))
+__global__ void __launch_bounds__(256)
+softmax_rows_kernel(const float* __restrict__ W, float inv_tau, __nv_bfloat16* __restrict__ S_hi,
+                    __nv_bfloat16* __restrict__ S_lo, int64_t ld_out, int64_t I) {
+    __shared__ float scratch[8];
+    const int64_t row = blockIdx.x;
+    const float* w = W + row * I;
+    float mx = -INFINITY;
+    for (int64_t i = threadIdx.x; i < I; i += blockDim.x) mx = fmaxf(mx, w[i] * inv_tau);
+    mx = block_reduce(mx, scratch, true);
+    float sum = 0.f;
+    for (int64_t i = threadIdx.x; i < I; i += blockDim.x) sum += expf(w[i] * inv_tau - mx);
+    sum = block_reduce(sum, scratch, false);
+    const float inv = 1.0f / sum;
+    for (int64_t i = threadIdx.x; i < I; i += blockDim.x) {
+        const float s = expf(w[i] * inv_tau - mx) * inv;
+        const __nv_bfloat16 hi = __float2bfloat16(s);
+        S_hi[row * ld_out + i] = hi;
+        if (S_lo != nullptr) S_lo[row * ld_out + i] = __float2bfloat16(s - __bfloat162float(hi));
+    }
+}
+
+// gW[row] = S * (gS - sum(gS * S)) / tau with S recomputed from W in fp32
+__global__ void __launch_bounds__(256)
+softmax_bwd_rows_kernel(const float* __restrict__ W, const float* __restrict__ gS, float inv_tau,
+                        float* __restrict__ gW, int64_t I) {
+    __shared__ float scratch[8];
+    const int64_t row = blockIdx.x;
+    const float* w = W + row * I;
+    const float* g = gS + row * I;
+    float mx = -INFINITY;
+    for (int64_t i = threadIdx.x; i < I; i += blockDim.x) mx = fmaxf(mx, w[i] * inv_tau);
+    mx = block_reduce(mx, scratch, true);
+    float sum = 0.f, dot = 0.f;
+    for (int64_t i = threadIdx.x; i < I; i += blockDim.x) {
+        const float e = expf(w[i] * inv_tau - mx);
+        sum += e;
+        dot += e * g[i];
+    }
+    sum = block_reduce(sum, scratch, false);
+    dot = block_reduce(dot, scratch, false);
+    const float inv = 1.0f / sum;
+    const float mean = dot * inv;
+    for (int64_t i = threadIdx.x; i < I; i += blockDim.x) {
+        const float s = expf(w[i] * inv_tau - mx) * inv;
+        gW[row * I + i] = s * (g[i] - mean) * inv_tau;
+    }
+}
+
+// fp32 (rows, cols) -> bf16, written at dst[r * ld + c] (or transposed: dst[c * ld + r]); optional
+// residual lo = bf16(x - hi) written at the same place of dst_lo
+__global__ void __launch_bounds__(256)
+to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, __nv_bfloat16* __restrict__ dst_lo,
+               int64_t rows, int64_t cols, int64_t ld, bool transpose) {
+    __shared__ float tile[32][33];
+    const int64_t c0 = (int64_t)blockIdx.x * 32, r0 = (int64_t)blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (int r = ty; r < 32; r += 8) {
+        const int64_t rr = r0 + r, cc = c0 + tx;
+        tile[r][tx] = (rr < rows && cc < cols) ? src[rr * cols + cc] : 0.f;
+    }
+    __syncthreads();
+    for (int r = ty; r < 32; r += 8) {
+        float v;
+        int64_t off;
+        bool ok;
+        if (!transpose) {
+            const int64_t rr = r0 + r, cc = c0 + tx;
+            v = tile[r][tx]; off = rr * ld + cc; ok = rr < rows && cc < cols;
+        } else {
+            const int64_t cc = c0 + r, rr = r0 + tx;
+            v = tile[tx][r]; off = cc * ld + rr; ok = rr < rows && cc < cols;
+        }
+        if (ok) {
+            const __nv_bfloat16 hi = __float2bfloat16(v);
+            dst[off] = hi;
+            if (dst_lo != nullptr) dst_lo[off] = __float2bfloat16(v - __bfloat162float(hi));
+        }
+    }
+}
+
+// bf16 (rows, cols) with row pitch ld_src -> transposed bf16 (cols, rows) with row pitch ld_dst
+__global__ void __launch_bounds__(256)
+bf16_transpose_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst, int64_t rows,
+                      int64_t cols, int64_t ld_src, int64_t ld_dst) {
+    __shared__ __nv_bfloat16 tile[64][66];
+    const int64_t c0 = (int64_t)blockIdx.x * 64, r0 = (int64_t)blockIdx.y * 64;
+    const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+    for (int r = ty; r < 64; r += 4) {
+        const int64_t rr = r0 + r, cc = c0 + tx;
+        tile[r][tx] = (rr < rows && cc < cols) ? src[rr * ld_src + cc] : __float2bfloat16(0.f);
+    }
+    __syncthreads();
+    for (int c = ty; c < 64; c += 4) {
+        const int64_t cc = c0 + c, rr = r0 + tx;
+        if (cc < cols && rr < rows) dst[cc * ld_dst + rr] = tile[tx][c];
+    }
+}
+
+}  // namespace
+
+DL_EXPORT int dl_gemm_bf16_tn(const void* A, const void* B, float* C, int64_t M, int64_t N, int64_t K,
+                              int* status, dl_stream_t stream) {
+    DL_REQUIRE(A && B && C && status && M > 0 && N > 0 && K > 0);
+    DL_REQUIRE(M < ((int64_t)1 << 31) && N < ((int64_t)1 << 31) && K < ((int64_t)1 << 31));
+    DL_REQUIRE_ALIGNED(A, 16);
+    DL_REQUIRE_ALIGNED(B, 16);
+    DL_REQUIRE_ALIGNED(C, 16);
+    if (K % 8 != 0) return DL_ERR_ALIGN;  // tensor-map row pitch must be a multiple of 16 bytes
+    CUtensorMap map_a, map_b;
+    int rc = make_map(&map_a, A, M, K, BM);
+    if (rc != DL_OK) return rc;
+    rc = make_map(&map_b, B, N, K, BN);
+    if (rc != DL_OK) return rc;
+    cudaFuncSetAttribute(gemm_bf16_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    const int64_t gx = dl_ceil_div(N, BN), gy = dl_ceil_div(M, BM);
+    DL_REQUIRE(gy <= 65535);
+    dim3 grid((unsigned)gx, (unsigned)gy);
+    gemm_bf16_tn_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, dl_cast(stream)>>>(map_a, map_b, C, (int)M, (int)N, (int)K,
+                                                                           status);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_softmax_rows_bf16(const float* W, float tau, void* S_hi, void* S_lo, int64_t ld_out, int64_t M,
+                                   int64_t I, dl_stream_t stream) {
+    DL_REQUIRE(W && S_hi && M > 0 && I > 0 && tau > 0.f && ld_out >= I);
+    softmax_rows_kernel<<<(unsigned)M, 256, 0, dl_cast(stream)>>>(W, 1.0f / tau, static_cast<__nv_bfloat16*>(S_hi),
+                                                                 static_cast<__nv_bfloat16*>(S_lo), ld_out, I);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_softmax_bwd_rows(const float* W, const float* gS, float tau, float* gW, int64_t M, int64_t I,
+                                  dl_stream_t stream) {
+    DL_REQUIRE(W && gS && gW && M > 0 && I > 0 && tau > 0.f);
+    softmax_bwd_rows_kernel<<<(unsigned)M, 256, 0, dl_cast(stream)>>>(W, gS, 1.0f / tau, gW, I);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_f32_to_bf16(const float* src, void* dst_hi, void* dst_lo, int64_t rows, int64_t cols, int64_t ld,
+                             int transpose, dl_stream_t stream) {
+    DL_REQUIRE(src && dst_hi && rows > 0 && cols > 0 && ld >= (transpose ? rows : cols));
+    dim3 grid((unsigned)dl_ceil_div(cols, 32), (unsigned)dl_ceil_div(rows, 32));
+    DL_REQUIRE(grid.y <= 65535);
+    to_bf16_kernel<<<grid, 256, 0, dl_cast(stream)>>>(src, static_cast<__nv_bfloat16*>(dst_hi),
+                                                     static_cast<__nv_bfloat16*>(dst_lo), rows, cols, ld, transpose != 0);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_bf16_transpose(const void* src, void* dst, int64_t rows, int64_t cols, int64_t ld_src,
+                                int64_t ld_dst, dl_stream_t stream) {
+    DL_REQUIRE(src && dst && rows > 0 && cols > 0 && ld_src >= cols && ld_dst >= rows);
+    dim3 grid((unsigned)dl_ceil_div(cols, 64), (unsigned)dl_ceil_div(rows, 64));
+    DL_REQUIRE(grid.y <= 65535);
+    bf16_transpose_kernel<<<grid, 256, 0, dl_cast(stream)>>>(static_cast<const __nv_bfloat16*>(src),
+                                                            static_cast<__nv_bfloat16*>(dst), rows, cols, ld_src, ld_dst);
+    return dl_launch_status();
+}

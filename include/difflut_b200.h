@@ -199,6 +199,32 @@ int dl_prob_bwd_t(const float* x_t, const int32_t* map, const float* raw, float 
 int dl_seg_sum_t(const float* src_t, const int32_t* inv_ptr, const int32_t* inv_ent, float* gx_t,
                  int64_t F, int64_t Bp, dl_stream_t stream);
 
+/* ------------------------------------------------------------------ LearnableLayer soft connectivity
+ * Training path of LearnableMappingModule.forward: softmax(W / tau, dim=-1) followed by
+ * x @ S^T (difflut/layers/learnable_layer.py:253-255, which calls F.softmax + torch.matmul), and
+ * the two GEMMs + softmax backward autograd derives from it.                                */
+
+/* C (M, N) fp32 = A (M, K) * B (N, K)^T, A and B bf16 row-major (K contiguous), fp32 accumulation in
+ * tensor memory (tcgen05.mma fed by TMA).  K must be a multiple of 8.  `status` is one int32 in
+ * device memory that the caller zeroes: it stays 0 on success; a non-zero value ((role << 8) |
+ * stage) means a bounded wait inside the kernel ran out and C is not valid. */
+int dl_gemm_bf16_tn(const void* A, const void* B, float* C, int64_t M, int64_t N, int64_t K, int* status,
+                    dl_stream_t stream);
+/* S = softmax(W / tau) per row of W (M, I), written as bf16 at S_hi[r*ld_out + i]; S_lo (optional)
+ * receives bf16(S - S_hi) so that S_hi + S_lo carries 16 mantissa bits. */
+int dl_softmax_rows_bf16(const float* W, float tau, void* S_hi, void* S_lo, int64_t ld_out, int64_t M,
+                         int64_t I, dl_stream_t stream);
+/* gW = S * (gS - rowsum(gS * S)) / tau, S recomputed from W in fp32. */
+int dl_softmax_bwd_rows(const float* W, const float* gS, float tau, float* gW, int64_t M, int64_t I,
+                        dl_stream_t stream);
+/* fp32 (rows, cols) -> bf16 at dst[r*ld + c], or transposed at dst[c*ld + r]; dst_lo (optional)
+ * receives the bf16 residual. */
+int dl_f32_to_bf16(const float* src, void* dst_hi, void* dst_lo, int64_t rows, int64_t cols, int64_t ld,
+                   int transpose, dl_stream_t stream);
+/* bf16 (rows, cols) with row pitch ld_src -> bf16 (cols, rows) with row pitch ld_dst. */
+int dl_bf16_transpose(const void* src, void* dst, int64_t rows, int64_t cols, int64_t ld_src,
+                      int64_t ld_dst, dl_stream_t stream);
+
 /* ------------------------------------------------------------------ GroupSum / loss / optimiser
  * GroupSum.forward (difflut/utils/modules.py:116-163): zero-pad F to a multiple of k, class c
  * sums the contiguous block of g = ceil(F/k) columns, divided by tau.                      */

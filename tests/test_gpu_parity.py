@@ -292,8 +292,10 @@ def test_learnable_layer_matches_reference(golden, dev):
     torch.testing.assert_close(y.cpu(), T(g["y"]), rtol=1e-5, atol=1e-6)
     y.backward(T(g["gy"]).to(dev))
     torch.testing.assert_close(layer.luts.grad.cpu(), T(g["gtables"]), rtol=1e-5, atol=1e-6)
-    torch.testing.assert_close(xg.grad.cpu(), T(g["gx"]), rtol=1e-2, atol=1e-5)
-    torch.testing.assert_close(layer.mapping.W.grad.cpu(), T(g["gW"]), rtol=1e-2, atol=1e-6)
+    # the backward GEMMs run on bf16 operands: 1e-2 of the gradient's scale
+    gx_ref, gW_ref = T(g["gx"]), T(g["gW"])
+    torch.testing.assert_close(xg.grad.cpu(), gx_ref, rtol=1e-2, atol=1e-2 * float(gx_ref.abs().max()))
+    torch.testing.assert_close(layer.mapping.W.grad.cpu(), gW_ref, rtol=1e-2, atol=1e-2 * float(gW_ref.abs().max()))
     layer.eval()
     assert np.array_equal(layer.get_mapping_matrix().cpu().numpy(), g["hard_idx"])
     ye = layer(x.to(dev))
@@ -480,3 +482,48 @@ def test_fused_backward_equals_separate_kernels_multi_group(dev):
     ref = O.dwn_network_backward(acts, maps, tabs0, lg.grad, k, tau, 0.5 * 0.75 ** 5, 0.25 / 0.75)
     for a, r in zip(grads[True], ref):
         torch.testing.assert_close(a, r, rtol=1e-4, atol=1e-7)
+
+
+# ------------------------------------------------------------------------------ tensor-core GEMM
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 320), (300, 500, 200), (1000, 777, 4096)])
+def test_gemm_bf16_tn_matches_fp32_matmul(dev, M, N, K):
+    """C = A B^T with bf16 operands, fp32 accumulation: equal to an fp32 matmul of the same bf16 values
+    up to summation order (1e-5 relative to the row scale)."""
+    from difflut_b200 import _native
+
+    gen = torch.Generator().manual_seed(M + N + K)
+    A = torch.randn(M, K, generator=gen).to(dev).to(torch.bfloat16)
+    B = torch.randn(N, K, generator=gen).to(dev).to(torch.bfloat16)
+    C = torch.full((M, N), float("nan"), device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    _native.call("dl_gemm_bf16_tn", A, B, C, M, N, K, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, "a bounded wait inside the kernel ran out"
+    ref = A.float() @ B.float().t()
+    torch.testing.assert_close(C, ref, rtol=1e-4, atol=1e-4 * float(K) ** 0.5)
+
+
+def test_soft_select_matches_fp32_reference(dev):
+    from difflut_b200.layers.soft_select import soft_select
+
+    gen = torch.Generator().manual_seed(0)
+    B, I, M = 200, 300, 90
+    x = torch.rand(B, I, generator=gen).to(dev).requires_grad_(True)
+    W = (torch.randn(M, I, generator=gen) * 0.5).to(dev).requires_grad_(True)
+    gy = torch.randn(B, M, generator=gen).to(dev)
+    for tau in (1.0, 0.3):
+        xr = x.detach().clone().requires_grad_(True)
+        Wr = W.detach().clone().requires_grad_(True)
+        ref = torch.matmul(xr, torch.softmax(Wr / tau, dim=-1).t())
+        ref.backward(gy)
+        x.grad = W.grad = None
+        out = soft_select(x, W, tau)  # three-way split: 16 mantissa bits in the forward
+        torch.testing.assert_close(out, ref.detach(), rtol=2e-5, atol=2e-5)
+        out.backward(gy)
+        torch.testing.assert_close(x.grad, xr.grad, rtol=1e-2, atol=1e-2 * float(xr.grad.abs().max()))
+        torch.testing.assert_close(W.grad, Wr.grad, rtol=1e-2, atol=1e-2 * float(Wr.grad.abs().max()))
+        plain = soft_select(x.detach(), W.detach(), tau, splits=1)
+        torch.testing.assert_close(plain, ref.detach(), rtol=1e-2, atol=1e-2)
+    xb = (torch.rand(64, I, generator=gen) > 0.5).float().to(dev)  # binary inputs: two pieces are exact enough
+    out2 = soft_select(xb, W.detach(), 1.0, splits=2)
+    torch.testing.assert_close(out2, xb @ torch.softmax(W.detach(), -1).t(), rtol=2e-5, atol=2e-5)
