@@ -106,38 +106,45 @@ class DWNNetwork:
         self.gsz = (self.N[-1] + self.k - 1) // self.k
         self.splits = int(_native.lib().dl_dwn_groupsum_splits(self.N[-1], self.k))
         self._B = None
+        self._train_B = None
         self._graph = None
         self.step_count = 0
+        self.infer_chunk = 1 << 18  # hard inference walks large batches in pieces of this many samples
 
     # ------------------------------------------------------------------ buffers
-    def _ensure_buffers(self, B: int) -> None:
-        if self._B == B:
-            return
+    def _ensure_buffers(self, B: int, training: bool = True) -> None:
+        """Activation buffers for a batch of B samples; gradient-side buffers only when training."""
         dev = self.device
-        Bp = _native.padded_batch(B)
-        Wp = Bp // 32
-        self.Bp = Bp
-        self.bits = [torch.empty(self.I[0], Wp, device=dev, dtype=torch.int32)]
-        for N in self.N[:-1]:
-            self.bits.append(torch.empty(N, Wp, device=dev, dtype=torch.int32))
-        self.last_bits = torch.empty(self.N[-1], Wp, device=dev, dtype=torch.int32)
-        # gradient w.r.t. the output of layer li (li < last), produced by layer li+1's backward; the
-        # fused backward never materialises it for the first layer
-        self.gact = [torch.empty(N, Bp, device=dev, dtype=torch.float32)
-                     if (li > 0 or not self.fused_backward) else None for li, N in enumerate(self.N[:-1])]
-        self.groups = int(_native.lib().dl_dwn_bwd_groups(Bp))
-        self.gt_partial = (torch.empty(self.groups, self.flat.numel(), device=dev, dtype=torch.float32)
-                           if self.fused_backward else None)
-        self.addr = [None] + [torch.empty(N, Bp, device=dev, dtype=torch.uint8) for N in self.N[1:]]
-        self.partial = torch.empty(self.k * self.splits, Bp, device=dev, dtype=torch.float32)
-        self.logits_t = torch.empty(self.k, Bp, device=dev, dtype=torch.float32)
-        self.dlogits_t = torch.empty(self.k, Bp, device=dev, dtype=torch.float32)
-        self.loss_rows = torch.empty(Bp, device=dev, dtype=torch.float32)
-        self.loss = torch.zeros(1, device=dev, dtype=torch.float32)
-        self.x_static = torch.empty(B, self.F, device=dev, dtype=torch.float32)
-        self.y_static = torch.empty(B, device=dev, dtype=torch.int32)
-        self._B = B
-        self._graph = None
+        if self._B != B:
+            Bp = _native.padded_batch(B)
+            Wp = Bp // 32
+            self.Bp = Bp
+            self.bits = [torch.empty(self.I[0], Wp, device=dev, dtype=torch.int32)]
+            for N in self.N[:-1]:
+                self.bits.append(torch.empty(N, Wp, device=dev, dtype=torch.int32))
+            self.last_bits = torch.empty(self.N[-1], Wp, device=dev, dtype=torch.int32)
+            self.partial = torch.empty(self.k * self.splits, Bp, device=dev, dtype=torch.float32)
+            self.logits_t = torch.empty(self.k, Bp, device=dev, dtype=torch.float32)
+            self._B = B
+            self._train_B = None
+            self._graph = None
+        if training and self._train_B != B:
+            Bp = self.Bp
+            # gradient w.r.t. the output of layer li (li < last), produced by layer li+1's backward; the
+            # fused backward never materialises it for the first layer
+            self.gact = [torch.empty(N, Bp, device=dev, dtype=torch.float32)
+                         if (li > 0 or not self.fused_backward) else None for li, N in enumerate(self.N[:-1])]
+            self.groups = int(_native.lib().dl_dwn_bwd_groups(Bp))
+            self.gt_partial = (torch.empty(self.groups, self.flat.numel(), device=dev, dtype=torch.float32)
+                               if self.fused_backward else None)
+            self.addr = [None] + [torch.empty(N, Bp, device=dev, dtype=torch.uint8) for N in self.N[1:]]
+            self.dlogits_t = torch.empty(self.k, Bp, device=dev, dtype=torch.float32)
+            self.loss_rows = torch.empty(Bp, device=dev, dtype=torch.float32)
+            self.loss = torch.zeros(1, device=dev, dtype=torch.float32)
+            self.x_static = torch.empty(B, self.F, device=dev, dtype=torch.float32)
+            self.y_static = torch.empty(B, device=dev, dtype=torch.int32)
+            self._train_B = B
+            self._graph = None
 
     # ------------------------------------------------------------------ kernels
     def _prepare_tables(self, need_efd: bool) -> None:
@@ -264,7 +271,7 @@ class DWNNetwork:
         """Training-mode logits (B, k) fp32 = GroupSum(last layer's raw table values)."""
         B = int(x.shape[0])
         with torch.cuda.device(self.device):
-            self._ensure_buffers(B)
+            self._ensure_buffers(B, training=False)
             self._prepare_tables(need_efd=False)
             self._forward(x.contiguous().float(), B)
             out = torch.empty(B, self.k, device=self.device, dtype=torch.float32)
@@ -279,27 +286,28 @@ class DWNNetwork:
         Input is either raw features x (B, F) fp32 or thermometer bits already packed as rows
         (B, ceil(F*T/32)) int32 with bit c%32 of word c//32 = encoded column c.
         """
+        src = packed_rows if packed_rows is not None else x.contiguous().float()
+        B_total = int(src.shape[0])
         with torch.cuda.device(self.device):
-            if packed_rows is not None:
-                B = int(packed_rows.shape[0])
-                self._ensure_buffers(B)
-                _native.call("dl_bits_rows_to_t", packed_rows, self.bits[0], B, self.I[0],
-                             packed_rows.shape[1], self.Bp)
-            else:
-                B = int(x.shape[0])
-                self._ensure_buffers(B)
-                _native.call("dl_thermo_pack_t", x.contiguous().float(), self.thr, self.bits[0], B, self.F,
-                             self.T, self.Bp)
-            self._prepare_tables(need_efd=False)
-            cur = self.bits[0]
-            for li in range(len(self.layers)):
-                nxt = self.bits[li + 1] if li + 1 < len(self.layers) else self.last_bits
-                _native.call("dl_dwn_fwd_bits_t", cur, self.plans[li].map_nodes, self.masks[li], nxt,
-                             self.N[li], self.n[li], self.Bp)
-                cur = nxt
             if out is None:
-                out = torch.empty(B, self.k, device=self.device, dtype=torch.int32)
-            _native.call("dl_popcount_groupsum_t", cur, out, self.N[-1], self.k, B, self.Bp)
+                out = torch.empty(B_total, self.k, device=self.device, dtype=torch.int32)
+            self._prepare_tables(need_efd=False)
+            for lo in range(0, B_total, self.infer_chunk):
+                hi = min(lo + self.infer_chunk, B_total)
+                B = hi - lo
+                self._ensure_buffers(B, training=False)
+                piece = src[lo:hi]
+                if packed_rows is not None:
+                    _native.call("dl_bits_rows_to_t", piece, self.bits[0], B, self.I[0], piece.shape[1], self.Bp)
+                else:
+                    _native.call("dl_thermo_pack_t", piece, self.thr, self.bits[0], B, self.F, self.T, self.Bp)
+                cur = self.bits[0]
+                for li in range(len(self.layers)):
+                    nxt = self.bits[li + 1] if li + 1 < len(self.layers) else self.last_bits
+                    _native.call("dl_dwn_fwd_bits_t", cur, self.plans[li].map_nodes, self.masks[li], nxt,
+                                 self.N[li], self.n[li], self.Bp)
+                    cur = nxt
+                _native.call("dl_popcount_groupsum_t", cur, out[lo:hi], self.N[-1], self.k, B, self.Bp)
         return out
 
     def algorithmic_bytes_per_step(self, B: int) -> int:
