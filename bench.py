@@ -426,7 +426,7 @@ def run_infer(args):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     enc = net.encoder.to(device)
     results = []
-    for logb in (14, 16, 18, 20, 22):
+    for logb in ((14, 16, 18) if args.small else (14, 16, 18, 20, 22)):
         Bg = 1 << logb
         lo, hi = shard_rows(Bg, rank, world)
         B = hi - lo
@@ -520,7 +520,7 @@ def run_learnable(args):
 
     device = torch.device("cuda", 0)
     g = torch.Generator().manual_seed(0)
-    B, I, N = 4096, 4096, 16000
+    B, I, N = (2048, 4096, 4000) if args.small else (4096, 4096, 16000)
     x = torch.bernoulli(torch.full((B, I), 0.5), generator=g).to(device)
     layer = LearnableLayer(I, N, DWNNode, NodeConfig(input_dim=6, output_dim=1), tau=1.0, tau_start=1.0, tau_min=1e-4,
                            tau_decay_iters=1000.0, use_cuda_soft=False).to(device)
@@ -539,7 +539,7 @@ def run_learnable(args):
     print(json.dumps({"metric": "train samples/s (fwd+bwd) LearnableLayer 4096 -> 16000 DWN n=6",
                       "value": B / (ms * 1e-3), "unit": "samples/s", "n_gpus": 1, "steps": max(2, args.steps // 4),
                       "warmup": 2, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-                      "dtype": "bf16", "data": "synthetic", "config": {"workload": "learnable_B4096_in4096_N16000_n6"},
+                      "dtype": "bf16", "data": "synthetic", "config": {"workload": f"learnable_B{B}_in{I}_N{N}_n6"},
                       "roofline": {"bound": "tensor", "achieved": gemm_flops / (ms * 1e-3) / 1e12, "peak": 1643.8,
                                    "unit": "TFLOP/s", "frac": gemm_flops / (ms * 1e-3) / 1e12 / 1643.8, "traffic": None,
                                    "note": "whole step (softmax, conversions, DWN kernels included) against the GEMM flops"}}),
@@ -554,6 +554,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="train", choices=["train", "infer", "prob", "learnable"],
                     help="train = the benchmark contract's workload; the others are secondary measurements")
+    ap.add_argument("--small", action="store_true", help="reduced sizes of the secondary workloads (for ncu captures)")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--global-batch", type=int, default=8192,

@@ -145,21 +145,21 @@ struct MuxTree<0, BASE> {
 };
 
 // Thread (x = group of 4 words, y = node): consecutive x read contiguous 16-byte pieces of each
-// input row; nodes and word groups are walked with grid-stride loops (no index division).
+// input row.  Node tiles are the fast grid dimension and word-group tiles the slow one, so the CTAs
+// resident at any time work on one slab of the batch (its input rows stay in L2 while all nodes
+// gather from them); both are walked with grid-stride loops (no index division).
 template <int NIN>
 __global__ void __launch_bounds__(256, 2)
 dwn_fwd_bits_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __restrict__ map,
                     const uint64_t* __restrict__ masks, uint32_t* __restrict__ out_bits, int N, int Q) {
     const int64_t Wp = (int64_t)Q << 2;
-    for (int j = blockIdx.y * blockDim.y + threadIdx.y; j < N; j += gridDim.y * blockDim.y) {
-        const uint64_t m = __ldg(&masks[j]);
-        int64_t base[NIN];
-#pragma unroll
-        for (int i = 0; i < NIN; ++i) base[i] = (int64_t)__ldg(&map[j * NIN + i]) * Wp;
-        for (int q = blockIdx.x * blockDim.x + threadIdx.x; q < Q; q += gridDim.x * blockDim.x) {
+    for (int q = blockIdx.y * blockDim.x + threadIdx.x; q < Q; q += gridDim.y * blockDim.x) {
+        for (int j = blockIdx.x * blockDim.y + threadIdx.y; j < N; j += gridDim.x * blockDim.y) {
+            const uint64_t m = __ldg(&masks[j]);
             uint4 x[NIN];
 #pragma unroll
-            for (int i = 0; i < NIN; ++i) x[i] = __ldg(reinterpret_cast<const uint4*>(in_bits + base[i]) + q);
+            for (int i = 0; i < NIN; ++i)
+                x[i] = __ldg(reinterpret_cast<const uint4*>(in_bits + (int64_t)__ldg(&map[j * NIN + i]) * Wp) + q);
             uint4 o;
             MuxTree<NIN - 1, 0>::eval((uint32_t)m, (uint32_t)(m >> 32), x, o);
             reinterpret_cast<uint4*>(out_bits + (int64_t)j * Wp)[q] = o;
@@ -801,12 +801,11 @@ DL_EXPORT int dl_dwn_fwd_bits_t(const uint32_t* in_bits_t, const int32_t* map, c
     while (bx < Q && bx < 256) bx <<= 1;
     const int by = 256 / bx;
     dim3 block(bx, by);
-    int64_t gx = dl_ceil_div(Q, bx), gy = dl_ceil_div(N, by);
-    const int64_t cap = (int64_t)DL_NUM_SMS * 32;
-    if (gx > cap) gx = cap;
-    if (gx * gy > cap) gy = cap / gx > 0 ? cap / gx : 1;
-    if (gy > 65535) gy = 65535;
-    dim3 grid((unsigned)gx, (unsigned)gy);
+    int64_t gq = dl_ceil_div(Q, bx), gn = dl_ceil_div(N, by);
+    if (gq > 65535) gq = 65535;
+    const int64_t cap = (int64_t)DL_NUM_SMS * 64;
+    if (gn > cap) gn = cap;
+    dim3 grid((unsigned)gn, (unsigned)gq);
     cudaStream_t s = dl_cast(stream);
     const int Ni = (int)N;
     switch (n) {

@@ -136,29 +136,40 @@ bits_t_to_rows_kernel(const uint32_t* __restrict__ bits_t, float* __restrict__ r
     }
 }
 
-// packed rows (B, Wr) -> packed feature-major [F][Wp]: 32x32 bit-matrix transpose per warp.
-// Lane r holds word (sample 32*wb + r, column word wc); after the transpose lane c holds the
-// 32 samples of column 32*wc + c.
+// packed rows (B, Wr) -> packed feature-major [F][Wp].  A CTA takes 512 samples x 8 column words
+// (256 features): the 512 x 8 input words are read with 32-byte row pieces into shared memory,
+// every warp transposes 32x32 bit tiles with ballots (lane r holds sample r's word, ballot of bit c
+// = the 32 samples of feature c), and the 256 x 16 output words leave as 64-byte row pieces.
 __global__ void __launch_bounds__(256)
 bits_rows_to_t_kernel(const uint32_t* __restrict__ bits_rows, uint32_t* __restrict__ bits_t,
                       int64_t B, int64_t F, int64_t Wr, int64_t Wp) {
-    const int lane = threadIdx.x & 31;
-    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-    const int64_t Wc = (F + 31) / 32;
-    for (int64_t tile = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; tile < Wp * Wc;
-         tile += nwarps) {
-        const int64_t wb = tile / Wc, wc = tile % Wc;
-        const int64_t b = wb * 32 + lane;
-        const uint32_t mine = (b < B) ? bits_rows[b * Wr + wc] : 0u;
+    __shared__ uint32_t in_tile[512][9];     // +1 word padding: a warp reads one column conflict-free
+    __shared__ uint32_t out_tile[256][17];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t wc0 = (int64_t)blockIdx.y * 8;      // first column word
+    const int64_t b0 = (int64_t)blockIdx.x * 512;     // first sample
+    for (int idx = threadIdx.x; idx < 512 * 8; idx += 256) {
+        const int r = idx >> 3, cw = idx & 7;
+        const int64_t b = b0 + r, wc = wc0 + cw;
+        in_tile[r][cw] = (b < B && wc < Wr) ? __ldg(bits_rows + b * Wr + wc) : 0u;
+    }
+    __syncthreads();
+    // 8 column words x 16 sample words = 128 tiles; warp w takes column word w
+    for (int sw = 0; sw < 16; ++sw) {
+        const uint32_t mine = in_tile[sw * 32 + lane][warp];
         uint32_t outw = 0;
-        // column c of the tile = ballot of bit c over the 32 lanes (samples)
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
             const uint32_t col = __ballot_sync(0xffffffffu, (mine >> c) & 1u);
             if (lane == c) outw = col;
         }
-        const int64_t f = wc * 32 + lane;
-        if (f < F) bits_t[f * Wp + wb] = outw;
+        out_tile[warp * 32 + lane][sw] = outw;
+    }
+    __syncthreads();
+    const int64_t wb0 = b0 >> 5;
+    for (int row = warp; row < 256; row += 8) {
+        const int64_t f = wc0 * 32 + row;
+        if (lane < 16 && f < F && wb0 + lane < Wp) bits_t[f * Wp + wb0 + lane] = out_tile[row][lane];
     }
 }
 
@@ -230,8 +241,8 @@ DL_EXPORT int dl_bits_rows_to_t(const uint32_t* bits_rows, uint32_t* bits_t, int
                                 int64_t Wr, int64_t Bp, dl_stream_t stream) {
     DL_REQUIRE(bits_rows && bits_t && B > 0 && F > 0 && Bp >= B && Bp % DL_BATCH_ALIGN == 0);
     DL_REQUIRE(Wr * 32 >= F);
-    const int64_t tiles = (Bp / 32) * dl_ceil_div(F, 32);
-    const int blocks = (int)dl_min64(dl_ceil_div(tiles * 32, 256), (int64_t)DL_NUM_SMS * 16);
-    bits_rows_to_t_kernel<<<blocks, 256, 0, dl_cast(stream)>>>(bits_rows, bits_t, B, F, Wr, Bp / 32);
+    dim3 grid((unsigned)dl_ceil_div(Bp, 512), (unsigned)dl_ceil_div(dl_ceil_div(F, 32), 8));
+    DL_REQUIRE(grid.y <= 65535);
+    bits_rows_to_t_kernel<<<grid, 256, 0, dl_cast(stream)>>>(bits_rows, bits_t, B, F, Wr, Bp / 32);
     return dl_launch_status();
 }
