@@ -138,8 +138,7 @@ bits_t_to_rows_kernel(const uint32_t* __restrict__ bits_t, float* __restrict__ r
 
 // packed rows (B, Wr) -> packed feature-major [F][Wp].  A CTA takes 512 samples x 8 column words
 // (256 features): the 512 x 8 input words are read with 32-byte row pieces into shared memory,
-// every warp transposes 32x32 bit tiles with ballots (lane r holds sample r's word, ballot of bit c
-// = the 32 samples of feature c), and the 256 x 16 output words leave as 64-byte row pieces.
+// every warp transposes 32x32 bit tiles with five shuffle rounds, and the 256 x 16 output words leave as 64-byte row pieces.
 __global__ void __launch_bounds__(256)
 bits_rows_to_t_kernel(const uint32_t* __restrict__ bits_rows, uint32_t* __restrict__ bits_t,
                       int64_t B, int64_t F, int64_t Wr, int64_t Wp) {
@@ -156,13 +155,24 @@ bits_rows_to_t_kernel(const uint32_t* __restrict__ bits_rows, uint32_t* __restri
     __syncthreads();
     // 8 column words x 16 sample words = 128 tiles; warp w takes column word w
     for (int sw = 0; sw < 16; ++sw) {
-        const uint32_t mine = in_tile[sw * 32 + lane][warp];
-        uint32_t outw = 0;
+        // 32x32 bit transpose across the warp: five rounds of swapping off-diagonal blocks with the
+        // lane that differs in bit j of its index (lane r starts with sample r's word and ends with
+        // the 32 samples of feature r)
+        uint32_t v = in_tile[sw * 32 + lane][warp];
+        uint32_t m = 0x0000FFFFu;
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-            const uint32_t col = __ballot_sync(0xffffffffu, (mine >> c) & 1u);
-            if (lane == c) outw = col;
+        for (int j = 16; j > 0; j >>= 1) {
+            const uint32_t p = __shfl_xor_sync(0xffffffffu, v, j);
+            if ((lane & j) == 0) {
+                const uint32_t t = ((v >> j) ^ p) & m;
+                v ^= t << j;
+            } else {
+                const uint32_t t = ((p >> j) ^ v) & m;
+                v ^= t;
+            }
+            m ^= m << (j >> 1);
         }
+        const uint32_t outw = v;
         out_tile[warp * 32 + lane][sw] = outw;
     }
     __syncthreads();

@@ -107,7 +107,17 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile_m = blockIdx.y, tile_n = blockIdx.x;
+    // 1-D grid; the operand with fewer row tiles is the fast index, so CTAs that run together share the
+    // tiles of the large operand's current row block and the small operand is re-read from L2
+    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+    int tile_m, tile_n;
+    if (tiles_m <= tiles_n) {
+        tile_m = blockIdx.x % tiles_m;
+        tile_n = blockIdx.x / tiles_m;
+    } else {
+        tile_n = blockIdx.x % tiles_n;
+        tile_m = blockIdx.x / tiles_n;
+    }
     const int kblocks = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -384,8 +394,8 @@ DL_EXPORT int dl_gemm_bf16_tn(const void* A, const void* B, float* C, int64_t M,
     if (rc != DL_OK) return rc;
     cudaFuncSetAttribute(gemm_bf16_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
     const int64_t gx = dl_ceil_div(N, BN), gy = dl_ceil_div(M, BM);
-    DL_REQUIRE(gy <= 65535);
-    dim3 grid((unsigned)gx, (unsigned)gy);
+    DL_REQUIRE(gx * gy < ((int64_t)1 << 31));
+    dim3 grid((unsigned)(gx * gy));
     gemm_bf16_tn_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, dl_cast(stream)>>>(map_a, map_b, C, (int)M, (int)N, (int)K,
                                                                            status);
     return dl_launch_status();
