@@ -54,6 +54,7 @@ SIGNATURES = {
     "dl_popcount_groupsum_t": "ppllll s",
     "dl_ce_t": "pppppllll s",
     "dl_adam_step": "ppppplfffff s",
+    "dl_adam_step_groups": "pplLppppLfffff s".replace("L", "l"),
 }
 
 _CT = {"p": ctypes.c_void_p, "l": ctypes.c_int64, "i": ctypes.c_int, "f": ctypes.c_float, "d": ctypes.c_double}

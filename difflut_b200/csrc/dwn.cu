@@ -21,9 +21,11 @@ namespace {
 // partner differs in bit b only (a lane shuffle for bits 0..4, the lane's other register for bit
 // 5).  The result does not depend on bit i of the address, so the entries with bit i = 0 are
 // compacted into efd_t[j][i][0..2^(n-1)).  The same warp ballots the >= 0.5 masks.
+template <int NIN>  // compile-time n (loops fully unrolled), or 0 to use the runtime value
 __global__ void __launch_bounds__(256)
 dwn_prepare_kernel(const float* __restrict__ tables, float* __restrict__ efd_t,
-                   uint64_t* __restrict__ masks, int N, int n, float alpha, float beta) {
+                   uint64_t* __restrict__ masks, int N, int n_rt, float alpha, float beta) {
+    const int n = NIN > 0 ? NIN : n_rt;
     const int lane = threadIdx.x & 31;
     const int L = 1 << n;
     const int nwarps = (gridDim.x * blockDim.x) >> 5;
@@ -36,9 +38,13 @@ dwn_prepare_kernel(const float* __restrict__ tables, float* __restrict__ efd_t,
             if (lane == 0) masks[j] = ((uint64_t)hi << 32) | lo;
         }
         if (efd_t == nullptr) continue;
-        for (int i = 0; i < n; ++i) {
+#pragma unroll
+        for (int i = 0; i < (NIN > 0 ? NIN : DL_MAX_FAST_N); ++i) {
+            if (i >= n) break;
             float lo = alpha * t_lo, hi = alpha * t_hi;
-            for (int b = 0; b < n && b < 5; ++b) {
+#pragma unroll
+            for (int b = 0; b < 5; ++b) {
+                if (b >= n) break;
                 const float plo = __shfl_xor_sync(0xffffffffu, lo, 1 << b);
                 const float phi = __shfl_xor_sync(0xffffffffu, hi, 1 << b);
                 if (b == i) {
@@ -774,7 +780,10 @@ DL_EXPORT int dl_dwn_prepare(const float* tables, float* efd_t, uint64_t* masks,
     if (n < 1 || n > DL_MAX_FAST_N) return DL_ERR_UNSUPPORTED;
     DL_REQUIRE(N < ((int64_t)1 << 30));
     const int blocks = grid_for(N * 32, 256);
-    dwn_prepare_kernel<<<blocks, 256, 0, dl_cast(stream)>>>(tables, efd_t, masks, (int)N, (int)n, alpha, beta);
+    if (n == 6)
+        dwn_prepare_kernel<6><<<blocks, 256, 0, dl_cast(stream)>>>(tables, efd_t, masks, (int)N, 6, alpha, beta);
+    else
+        dwn_prepare_kernel<0><<<blocks, 256, 0, dl_cast(stream)>>>(tables, efd_t, masks, (int)N, (int)n, alpha, beta);
     return dl_launch_status();
 }
 

@@ -112,6 +112,31 @@ __global__ void adam_kernel(float* __restrict__ p, const float* __restrict__ g, 
     }
 }
 
+// Adam step whose gradient is the ordered sum of `groups` partial-gradient slabs; the summed
+// gradient is also written to g_out (it is the .grad users read)
+__global__ void adam_groups_kernel(float* __restrict__ p, const float* __restrict__ partial, int64_t stride,
+                                   int groups, float* __restrict__ g_out, float* __restrict__ m,
+                                   float* __restrict__ v, const double* __restrict__ state, int64_t count, float lr,
+                                   float b1, float b2, float eps, float gscale) {
+    const double bc1 = 1.0 - state[0];
+    const double bc2 = 1.0 - state[1];
+    const float step_size = (float)((double)lr / bc1);
+    const float bc2_sqrt = (float)sqrt(bc2);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        float acc = 0.f;
+        for (int g = 0; g < groups; ++g) acc += partial[(int64_t)g * stride + i];
+        g_out[i] = acc;
+        const float gi = acc * gscale;
+        const float mi = m[i] + (gi - m[i]) * (1.0f - b1);
+        const float vi = v[i] * b2 + (1.0f - b2) * gi * gi;
+        m[i] = mi;
+        v[i] = vi;
+        const float denom = sqrtf(vi) / bc2_sqrt + eps;
+        p[i] = p[i] - step_size * (mi / denom);
+    }
+}
+
 }  // namespace
 
 DL_EXPORT int dl_groupsum_rows(const float* x, float* out, int64_t B, int64_t F, int64_t k, float tau,
@@ -166,6 +191,18 @@ DL_EXPORT int dl_adam_step(float* p, const float* g, float* m, float* v, double*
     const int64_t blocks = dl_min64(dl_ceil_div(count, 256), (int64_t)DL_NUM_SMS * 16);
     adam_kernel<<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(p, g, m, v, state, count, lr, beta1, beta2,
                                                              eps, gscale);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_adam_step_groups(float* p, const float* partial, int64_t stride, int64_t groups, float* g_out,
+                                  float* m, float* v, double* state, int64_t count, float lr, float beta1,
+                                  float beta2, float eps, float gscale, dl_stream_t stream) {
+    DL_REQUIRE(p && partial && g_out && m && v && state && count > 0 && groups > 0 && stride >= count);
+    adam_advance_kernel<<<1, 1, 0, dl_cast(stream)>>>(state, (double)beta1, (double)beta2);
+    if (cudaPeekAtLastError() != cudaSuccess) return DL_ERR_LAUNCH;
+    const int64_t blocks = dl_min64(dl_ceil_div(count, 256), (int64_t)DL_NUM_SMS * 16);
+    adam_groups_kernel<<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(p, partial, stride, (int)groups, g_out, m, v,
+                                                                    state, count, lr, beta1, beta2, eps, gscale);
     return dl_launch_status();
 }
 

@@ -108,6 +108,7 @@ class DWNNetwork:
         self._B = None
         self._train_B = None
         self._graph = None
+        self._side = None
         self.step_count = 0
         self.infer_chunk = 1 << 18  # hard inference walks large batches in pieces of this many samples
 
@@ -147,15 +148,17 @@ class DWNNetwork:
             self._graph = None
 
     # ------------------------------------------------------------------ kernels
-    def _prepare_tables(self, need_efd: bool) -> None:
+    def _prepare_tables(self, need_efd: bool, need_masks: bool = True) -> None:
         """EFD transform tables (for the backward) and >= 0.5 masks (for the hard forward) of this step."""
+        if not (need_efd or need_masks):
+            return
         if self.uniform:
-            _native.call("dl_dwn_prepare", self.flat, self.efd_all if need_efd else None, self.masks_all,
-                         sum(self.N), self.n[0], self.alpha[0], self.beta[0])
+            _native.call("dl_dwn_prepare", self.flat, self.efd_all if need_efd else None,
+                         self.masks_all if need_masks else None, sum(self.N), self.n[0], self.alpha[0], self.beta[0])
             return
         for li in range(len(self.layers)):
-            _native.call("dl_dwn_prepare", self.tables[li], self.efd[li] if need_efd else None, self.masks[li],
-                         self.N[li], self.n[li], self.alpha[li], self.beta[li])
+            _native.call("dl_dwn_prepare", self.tables[li], self.efd[li] if need_efd else None,
+                         self.masks[li] if need_masks else None, self.N[li], self.n[li], self.alpha[li], self.beta[li])
 
     def _forward(self, x: torch.Tensor, B: int) -> None:
         Bp = self.Bp
@@ -205,27 +208,47 @@ class DWNNetwork:
                          self.plans[up].inv_ptr_virtual, self.plans[up].inv_ent8_virtual, self.bits[li],
                          self.plans[li].map_nodes, self.gact[li] if li > 0 else None,
                          self.addr[li] if li > 0 else None, partial, total, self.N[li], self.n[li], Bp)
-        _native.call("dl_sum_groups", self.gt_partial, self.flat_grad, total, total, self.groups)
+        if self.distributed:
+            _native.call("dl_sum_groups", self.gt_partial, self.flat_grad, total, total, self.groups)
 
     def _step_body(self, B: int, B_global: int) -> None:
-        self._prepare_tables(need_efd=True)
+        # the EFD transform is only needed by the backward: it runs on a side stream next to the forward
+        main = torch.cuda.current_stream()
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.device)
+            self._fork, self._join = torch.cuda.Event(), torch.cuda.Event()
+        self._fork.record(main)
+        self._side.wait_event(self._fork)
+        with torch.cuda.stream(self._side):
+            self._prepare_tables(need_efd=True, need_masks=False)
+            self._join.record(self._side)
+        self._prepare_tables(need_efd=False, need_masks=True)
         self._forward(self.x_static, B)
         _native.call("dl_ce_t", self.logits_t, self.y_static, self.dlogits_t, self.loss_rows, self.loss,
                      B, B_global, self.k, self.Bp)
+        main.wait_event(self._join)
         self._backward()
+        count = self.flat.numel()
+        if self.fused_backward and not self.distributed:
+            # no exchange between the backward and the update: sum the partial gradients inside Adam
+            _native.call("dl_adam_step_groups", self.flat, self.gt_partial, count, self.groups, self.flat_grad,
+                         self.exp_avg, self.exp_avg_sq, self.adam_state, count, self.lr, self.betas[0], self.betas[1],
+                         self.eps, 1.0)
+            return
         if self.distributed:
             # sum of per-rank gradients of the GLOBAL-mean loss (dl_ce_t divides by B_global)
             allreduce_sum_(self.flat_grad, self.group)
         _native.call("dl_adam_step", self.flat, self.flat_grad, self.exp_avg, self.exp_avg_sq, self.adam_state,
-                     self.flat.numel(), self.lr, self.betas[0], self.betas[1], self.eps, 1.0)
+                     count, self.lr, self.betas[0], self.betas[1], self.eps, 1.0)
 
     # ------------------------------------------------------------------ public API
     KERNELS_PER_STEP_NOTE = "prepare xL, pack, fwd xL(+reduce), ce x2, bwd tables xL, bwd input x(L-1), adam x2"
 
     def kernel_launches_per_step(self) -> int:
         L = len(self.layers)
-        backward = (L + 1) if self.fused_backward else (L + (L - 1))
-        prepare = 1 if self.uniform else L
+        fused_adam = self.fused_backward and not self.distributed
+        backward = (L + (0 if fused_adam else 1)) if self.fused_backward else (L + (L - 1))
+        prepare = 2 * (1 if self.uniform else L)
         return prepare + 1 + (L - 1) + 2 + 2 + backward + 2
 
     def train_step(self, x: torch.Tensor, labels: torch.Tensor, use_graph: bool = False) -> torch.Tensor:

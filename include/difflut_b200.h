@@ -276,6 +276,12 @@ int dl_ce_t(const float* logits_t, const int32_t* labels, float* dlogits_t, floa
  * g is multiplied by gscale before use (1/world after a sum all-reduce). */
 int dl_adam_step(float* p, const float* g, float* m, float* v, double* state, int64_t count,
                  float lr, float beta1, float beta2, float eps, float gscale, dl_stream_t stream);
+/* The same step with the gradient given as `groups` partial slabs of `stride` floats (what
+ * dl_dwn_bwd_fused_t writes): g = sum of the slabs in order, also stored to g_out.  Replaces
+ * dl_sum_groups + dl_adam_step when no all-reduce sits between them. */
+int dl_adam_step_groups(float* p, const float* partial, int64_t stride, int64_t groups, float* g_out,
+                        float* m, float* v, double* state, int64_t count, float lr, float beta1,
+                        float beta2, float eps, float gscale, dl_stream_t stream);
 
 /* ------------------------------------------------------------------ bit-packed hard-LUT inference
  * The per-layer kernel is dl_dwn_fwd_bits_t.  Class counts of the last layer's packed outputs:
