@@ -28,6 +28,7 @@ if ROOT not in sys.path:
 SIZES = (16000, 8000, 4000)
 FEATURES, THERMO_BITS, CLASSES, TAU, GLOBAL_BATCH, LR = 784, 8, 10, 33.0, 8192, 1e-2
 METRIC = "train samples/s (fwd+bwd) 3-layer n=6 DWN"
+SCALING = "strong"
 # dram__bytes_read.sum + dram__bytes_write.sum of the three dl_dwn_bwd_fused_t launches of one step at
 # per-GPU batch 8192, from one ncu capture (profiles/dwn_bwd_fused_kernel_c4_B8192.txt); the traffic is
 # proportional to the batch (every term but the 7 MB of tables scales with it), so other batches scale it
@@ -367,7 +368,7 @@ def run_gpu_arm(args):
         line = {
             "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "scaling": SCALING, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": _config({"per_gpu_batch": B, "parallelism": f"dp{world}", "mode": "bit-packed activations between layers, fp32 gradients",
                                "cuda_graph": use_graph, "l2": "256 MB flush between timed steps"}),
             "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": int(x_pin.numel() * 4 + y_pin.numel() * 4) * world,
@@ -559,9 +560,13 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--global-batch", type=int, default=8192,
                     help="override the global batch (profiling on a small case; the default is the benchmark workload)")
+    ap.add_argument("--per-gpu-batch", type=int, default=0,
+                    help="weak-scaling variant: this many samples per GPU (global batch = N x this); the default "
+                         "keeps the benchmark's fixed global batch (strong scaling)")
     ap.add_argument("--unfused-backward", action="store_true", help="separate table / input gradient kernels")
     args = ap.parse_args()
-    globals()["GLOBAL_BATCH"] = args.global_batch
+    globals()["GLOBAL_BATCH"] = args.per_gpu_batch * args.gpus if args.per_gpu_batch > 0 else args.global_batch
+    globals()["SCALING"] = "weak" if args.per_gpu_batch > 0 else "strong"
     if args.impl == "reference":
         run_reference_arm(args)
         return

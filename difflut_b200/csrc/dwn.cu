@@ -222,19 +222,20 @@ dwn_fwd_vals_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __restr
     }
 }
 
-// Last layer fused with GroupSum.  One warp per (1024-sample group, class*S + slice): it walks the
-// nodes of its slice; for each node lane w loads word w of the node's 6 input rows (coalesced), the
-// 8 chunks of the group get their words by shuffle, and 32 running sums (8 chunks x 4 samples) stay
-// in registers.  The next node's words are loaded before the current node is consumed.
+// Last layer fused with GroupSum.  One CTA per (1024-sample group, class*S + slice); its 4 warps
+// share the slice's nodes (warp w takes nodes w, w+4, ...) and add their sums through shared memory
+// in a fixed order.  For each node lane w loads word w of the node's 6 input rows (coalesced), the 8
+// chunks of the group get their words by shuffle, and 32 running sums (8 chunks x 4 samples) stay
+// in registers; the next node's words are loaded before the current node is consumed.
 __global__ void __launch_bounds__(128)
 dwn_fwd_groupsum_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __restrict__ map,
                         const float* __restrict__ tables, float* __restrict__ partial, int64_t N,
                         int n, int64_t gsz, int S, int64_t Bp) {
+    __shared__ float4 red[3][8][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t Wp = Bp >> 5;
     const int L = 1 << n;
-    const int64_t grp = (int64_t)blockIdx.x * 4 + warp;  // 1024-sample group
-    if (grp * 1024 >= Bp) return;
+    const int64_t grp = blockIdx.x;  // 1024-sample group
     const int64_t cls = blockIdx.y / (unsigned)S, s = blockIdx.y % (unsigned)S;
     const int64_t per = (gsz + S - 1) / S;
     const int64_t j0 = cls * gsz + s * per;
@@ -248,17 +249,18 @@ dwn_fwd_groupsum_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __r
 #pragma unroll
     for (int c = 0; c < 8; ++c) acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
     uint32_t nxt[DL_MAX_FAST_N];
+    const int64_t jfirst = j0 + warp;
 #pragma unroll
     for (int i = 0; i < DL_MAX_FAST_N; ++i)
-        nxt[i] = (i < n && j0 < j1 && wvalid) ? __ldg(in_bits + (int64_t)__ldg(&map[j0 * n + i]) * Wp + w) : 0u;
-    for (int64_t j = j0; j < j1; ++j) {
+        nxt[i] = (i < n && jfirst < j1 && wvalid) ? __ldg(in_bits + (int64_t)__ldg(&map[jfirst * n + i]) * Wp + w) : 0u;
+    for (int64_t j = jfirst; j < j1; j += 4) {
         uint32_t words[DL_MAX_FAST_N];
 #pragma unroll
         for (int i = 0; i < DL_MAX_FAST_N; ++i) words[i] = nxt[i];
-        if (j + 1 < j1) {
+        if (j + 4 < j1) {
 #pragma unroll
             for (int i = 0; i < DL_MAX_FAST_N; ++i)
-                nxt[i] = (i < n && wvalid) ? __ldg(in_bits + (int64_t)__ldg(&map[(j + 1) * n + i]) * Wp + w) : 0u;
+                nxt[i] = (i < n && wvalid) ? __ldg(in_bits + (int64_t)__ldg(&map[(j + 4) * n + i]) * Wp + w) : 0u;
         }
         const float* tj = tables + j * L;
 #pragma unroll
@@ -277,10 +279,22 @@ dwn_fwd_groupsum_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __r
             acc[c].w += __ldg(tj + (a >> 24));
         }
     }
+    if (warp > 0) {
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-        const int64_t b = grp * 1024 + c * 128 + lane * 4;
-        if (b < Bp) *reinterpret_cast<float4*>(partial + (int64_t)blockIdx.y * Bp + b) = acc[c];
+        for (int c = 0; c < 8; ++c) red[warp - 1][c][lane] = acc[c];
+    }
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+#pragma unroll
+            for (int o = 0; o < 3; ++o) {
+                const float4 v = red[o][c][lane];
+                acc[c].x += v.x; acc[c].y += v.y; acc[c].z += v.z; acc[c].w += v.w;
+            }
+            const int64_t b = grp * 1024 + c * 128 + lane * 4;
+            if (b < Bp) *reinterpret_cast<float4*>(partial + (int64_t)blockIdx.y * Bp + b) = acc[c];
+        }
     }
 }
 
@@ -860,7 +874,7 @@ DL_EXPORT int dl_dwn_fwd_groupsum_t(const uint32_t* in_bits_t, const int32_t* ma
     const int S = (int)dl_dwn_groupsum_splits(N, k);
     const int64_t gsz = dl_ceil_div(N, k);
     DL_REQUIRE(k * S <= 65535);
-    dim3 grid((unsigned)dl_ceil_div(Bp, 4096), (unsigned)(k * S));
+    dim3 grid((unsigned)dl_ceil_div(Bp, 1024), (unsigned)(k * S));
     dwn_fwd_groupsum_kernel<<<grid, 128, 0, dl_cast(stream)>>>(in_bits_t, map, tables, partial, N, (int)n,
                                                               gsz, S, Bp);
     if (cudaPeekAtLastError() != cudaSuccess) return DL_ERR_LAUNCH;

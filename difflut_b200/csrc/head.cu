@@ -92,6 +92,15 @@ __global__ void adam_advance_kernel(double* state, double b1, double b2) {
     state[1] *= b2;
 }
 
+__device__ __forceinline__ float adam_update(float p, float gi, float& m, float& v, float step_size, float bc2_sqrt,
+                                             float b1, float b2, float eps) {
+    m = m + (gi - m) * (1.0f - b1);
+    v = v * b2 + (1.0f - b2) * gi * gi;
+    const float denom = sqrtf(v) / bc2_sqrt + eps;
+    return p - step_size * (m / denom);
+}
+
+// four elements per thread (16-byte accesses); the tail is handled element-wise
 __global__ void adam_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
                             float* __restrict__ v, const double* __restrict__ state, int64_t count,
                             float lr, float b1, float b2, float eps, float gscale) {
@@ -100,16 +109,23 @@ __global__ void adam_kernel(float* __restrict__ p, const float* __restrict__ g, 
     const double bc2 = 1.0 - state[1];
     const float step_size = (float)((double)lr / bc1);
     const float bc2_sqrt = (float)sqrt(bc2);
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count;
+    const int64_t quads = count >> 2;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < quads;
          i += (int64_t)gridDim.x * blockDim.x) {
-        const float gi = g[i] * gscale;
-        const float mi = m[i] + (gi - m[i]) * (1.0f - b1);
-        const float vi = v[i] * b2 + (1.0f - b2) * gi * gi;
-        m[i] = mi;
-        v[i] = vi;
-        const float denom = sqrtf(vi) / bc2_sqrt + eps;
-        p[i] = p[i] - step_size * (mi / denom);
+        float4 pp = reinterpret_cast<float4*>(p)[i], mm = reinterpret_cast<float4*>(m)[i];
+        float4 vv = reinterpret_cast<float4*>(v)[i];
+        const float4 gg = reinterpret_cast<const float4*>(g)[i];
+        pp.x = adam_update(pp.x, gg.x * gscale, mm.x, vv.x, step_size, bc2_sqrt, b1, b2, eps);
+        pp.y = adam_update(pp.y, gg.y * gscale, mm.y, vv.y, step_size, bc2_sqrt, b1, b2, eps);
+        pp.z = adam_update(pp.z, gg.z * gscale, mm.z, vv.z, step_size, bc2_sqrt, b1, b2, eps);
+        pp.w = adam_update(pp.w, gg.w * gscale, mm.w, vv.w, step_size, bc2_sqrt, b1, b2, eps);
+        reinterpret_cast<float4*>(p)[i] = pp;
+        reinterpret_cast<float4*>(m)[i] = mm;
+        reinterpret_cast<float4*>(v)[i] = vv;
     }
+    for (int64_t i = (quads << 2) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count;
+         i += (int64_t)gridDim.x * blockDim.x)
+        p[i] = adam_update(p[i], g[i] * gscale, m[i], v[i], step_size, bc2_sqrt, b1, b2, eps);
 }
 
 // Adam step whose gradient is the ordered sum of `groups` partial-gradient slabs; the summed
@@ -186,9 +202,13 @@ DL_EXPORT int dl_adam_step(float* p, const float* g, float* m, float* v, double*
                            float lr, float beta1, float beta2, float eps, float gscale,
                            dl_stream_t stream) {
     DL_REQUIRE(p && g && m && v && state && count > 0);
+    DL_REQUIRE_ALIGNED(p, 16);
+    DL_REQUIRE_ALIGNED(g, 16);
+    DL_REQUIRE_ALIGNED(m, 16);
+    DL_REQUIRE_ALIGNED(v, 16);
     adam_advance_kernel<<<1, 1, 0, dl_cast(stream)>>>(state, (double)beta1, (double)beta2);
     if (cudaPeekAtLastError() != cudaSuccess) return DL_ERR_LAUNCH;
-    const int64_t blocks = dl_min64(dl_ceil_div(count, 256), (int64_t)DL_NUM_SMS * 16);
+    const int64_t blocks = dl_min64(dl_ceil_div(dl_ceil_div(count, 4), 256), (int64_t)DL_NUM_SMS * 16);
     adam_kernel<<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(p, g, m, v, state, count, lr, beta1, beta2,
                                                              eps, gscale);
     return dl_launch_status();

@@ -46,11 +46,14 @@ def shard_rows(total_rows: int, rank: int, world: int) -> Tuple[int, int]:
     return start, start + base + (1 if rank < extra else 0)
 
 
-def allreduce_sum_(flat: torch.Tensor, group=None) -> torch.Tensor:
-    """In-place sum all-reduce of a flat gradient buffer (no-op outside a process group)."""
+def allreduce_sum_(flat: torch.Tensor, group=None, async_op: bool = False):
+    """In-place sum all-reduce of a flat gradient buffer (no-op outside a process group).
+
+    Returns the tensor, or with `async_op` the work handle to `wait()` on (None when nothing ran)."""
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
-        dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
-    return flat
+        work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
+        return work if async_op else flat
+    return None if async_op else flat
 
 
 def max_over_ranks(value: float, device=None) -> float:

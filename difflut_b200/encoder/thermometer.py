@@ -101,3 +101,37 @@ class ThermometerEncoder(BaseEncoder):
 
     def __repr__(self) -> str:
         return f"ThermometerEncoder(num_bits={self.num_bits}, flatten={self.flatten})"
+
+
+@register_encoder("gaussian_thermometer")
+class GaussianThermometerEncoder(ThermometerEncoder):
+    """Thresholds at Gaussian quantiles of each feature: mean + icdf(i/(T+1)) * std.
+
+    Only `fit` differs from ThermometerEncoder (difflut/encoder/thermometer.py:131-166); encoding
+    runs the same compare-and-pack kernels.
+    """
+
+    def _compute_thresholds(self, x: torch.Tensor) -> torch.Tensor:
+        q = torch.arange(1, self.num_bits + 1, device=x.device).float() / (self.num_bits + 1)
+        skews = torch.distributions.Normal(0, 1).icdf(q)
+        mean, std = x.mean(dim=0), x.std(dim=0)
+        return torch.stack([k * std + mean for k in skews], dim=-1)
+
+    def __repr__(self) -> str:
+        return f"GaussianThermometerEncoder(num_bits={self.num_bits}, flatten={self.flatten})"
+
+
+@register_encoder("distributive_thermometer")
+class DistributiveThermometerEncoder(ThermometerEncoder):
+    """Thresholds at empirical quantiles of each feature: sorted column value at index
+    int(S * i / (T+1)) (difflut/encoder/thermometer.py:169-205)."""
+
+    def _compute_thresholds(self, x: torch.Tensor) -> torch.Tensor:
+        ordered = torch.sort(x, dim=0)[0]
+        S = ordered.shape[0]
+        idx = torch.tensor([int(S * i / (self.num_bits + 1)) for i in range(1, self.num_bits + 1)], device=x.device)
+        picked = ordered[idx]  # (T, features...)
+        return picked.permute(*range(1, picked.ndim), 0)
+
+    def __repr__(self) -> str:
+        return f"DistributiveThermometerEncoder(num_bits={self.num_bits}, flatten={self.flatten})"

@@ -188,28 +188,38 @@ class DWNNetwork:
                              self.I[li], self.n[li], Bp)
 
     def _backward_fused(self) -> None:
-        """One kernel per layer (top down) + one ordered sum of the per-1024-sample partial gradients."""
+        """One kernel per layer (top down).  Each kernel leaves one partial table gradient per 1024-sample
+        group; on one GPU Adam sums them itself, under data parallelism each layer's gradient is summed
+        and its all-reduce started right away, so it travels while the layers below are still computed."""
         Bp = self.Bp
         last = len(self.layers) - 1
         total = self.flat.numel()
+        # with a single group the "partial" gradient is the gradient: write it in place
+        direct = self.distributed and self.groups == 1
+        self._pending = []
         for li in range(last, -1, -1):
-            partial = self.gt_partial[0, self.offsets[li]:]
+            partial = self.flat_grad[self.offsets[li]:] if direct else self.gt_partial[0, self.offsets[li]:]
             if li == last:
                 _native.call("dl_dwn_bwd_fused_t", None, self.dlogits_t, self.gsz, 1.0 / self.tau, None, 1, None, None,
                              self.bits[li], self.plans[li].map_nodes, None, self.addr[li], partial, total,
                              self.N[li], self.n[li], Bp)
-                continue
-            up = li + 1
-            if up == last:
-                g_up, gdiv, gscale = self.dlogits_t, self.gsz, 1.0 / self.tau
             else:
-                g_up, gdiv, gscale = self.gact[up], 1, 1.0
-            _native.call("dl_dwn_bwd_fused_t", self.addr[up], g_up, gdiv, gscale, self.efd[up], self.n[up],
-                         self.plans[up].inv_ptr_virtual, self.plans[up].inv_ent8_virtual, self.bits[li],
-                         self.plans[li].map_nodes, self.gact[li] if li > 0 else None,
-                         self.addr[li] if li > 0 else None, partial, total, self.N[li], self.n[li], Bp)
-        if self.distributed:
-            _native.call("dl_sum_groups", self.gt_partial, self.flat_grad, total, total, self.groups)
+                up = li + 1
+                if up == last:
+                    g_up, gdiv, gscale = self.dlogits_t, self.gsz, 1.0 / self.tau
+                else:
+                    g_up, gdiv, gscale = self.gact[up], 1, 1.0
+                _native.call("dl_dwn_bwd_fused_t", self.addr[up], g_up, gdiv, gscale, self.efd[up], self.n[up],
+                             self.plans[up].inv_ptr_virtual, self.plans[up].inv_ent8_virtual, self.bits[li],
+                             self.plans[li].map_nodes, self.gact[li] if li > 0 else None,
+                             self.addr[li] if li > 0 else None, partial, total, self.N[li], self.n[li], Bp)
+            if self.distributed:
+                lo, hi = self.offsets[li], self.offsets[li + 1]
+                grad = self.flat_grad[lo:hi]
+                if not direct:
+                    _native.call("dl_sum_groups", self.gt_partial[0, lo:], grad, hi - lo, total, self.groups)
+                # sum of per-rank gradients of the GLOBAL-mean loss (dl_ce_t divides by B_global)
+                self._pending.append(allreduce_sum_(grad, self.group, async_op=True))
 
     def _step_body(self, B: int, B_global: int) -> None:
         # the EFD transform is only needed by the backward: it runs on a side stream next to the forward
@@ -236,8 +246,13 @@ class DWNNetwork:
                          self.eps, 1.0)
             return
         if self.distributed:
-            # sum of per-rank gradients of the GLOBAL-mean loss (dl_ce_t divides by B_global)
-            allreduce_sum_(self.flat_grad, self.group)
+            if self.fused_backward:
+                for work in self._pending:  # the per-layer all-reduces started during the backward
+                    if work is not None:
+                        work.wait()
+                self._pending = []
+            else:
+                allreduce_sum_(self.flat_grad, self.group)
         _native.call("dl_adam_step", self.flat, self.flat_grad, self.exp_avg, self.exp_avg_sq, self.adam_state,
                      count, self.lr, self.betas[0], self.betas[1], self.eps, 1.0)
 
@@ -247,7 +262,8 @@ class DWNNetwork:
     def kernel_launches_per_step(self) -> int:
         L = len(self.layers)
         fused_adam = self.fused_backward and not self.distributed
-        backward = (L + (0 if fused_adam else 1)) if self.fused_backward else (L + (L - 1))
+        sums = 0 if (fused_adam or (self.distributed and getattr(self, "groups", 2) == 1)) else (L if self.distributed else 1)
+        backward = (L + sums) if self.fused_backward else (L + (L - 1))
         prepare = 2 * (1 if self.uniform else L)
         return prepare + 1 + (L - 1) + 2 + 2 + backward + 2
 

@@ -55,6 +55,16 @@ def main():
         out[f"x_T{T}"] = _np(xt)
         out[f"thr_T{T}"] = _np(enc.thresholds)
         out[f"bits_T{T}"] = _np(enc.encode(xt)).astype(np.uint8)
+    from difflut.encoder import DistributiveThermometerEncoder, GaussianThermometerEncoder
+
+    g = torch.Generator().manual_seed(77)
+    xv = torch.randn(90, 13, generator=g) * 2 + 1
+    xq = torch.randn(25, 13, generator=g) * 2 + 1
+    for tag, cls in (("gauss", GaussianThermometerEncoder), ("distr", DistributiveThermometerEncoder)):
+        enc = cls(num_bits=4).fit(xv)
+        out[f"{tag}_thr"] = _np(enc.thresholds)
+        out[f"{tag}_bits"] = _np(enc.encode(xq)).astype(np.uint8)
+    out["variant_x_fit"], out["variant_x"] = _np(xv), _np(xq)
     np.savez_compressed(os.path.join(HERE, "thermometer.npz"), **out)
 
     # ---------------------------------------------------------------- index maps

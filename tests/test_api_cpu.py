@@ -209,3 +209,15 @@ def test_mixin_helpers_on_cpu():
     assert float(out.pow(2).mean()) == pytest.approx(1.0, rel=1e-3)
     layer.eval()
     assert layer._apply_bit_flip(x) is x
+
+
+def test_thermometer_fit_variants_match_reference(golden):
+    from difflut_b200.encoder import DistributiveThermometerEncoder, GaussianThermometerEncoder
+
+    g = golden("thermometer")
+    x = torch.from_numpy(g["variant_x_fit"])
+    for tag, cls in (("gauss", GaussianThermometerEncoder), ("distr", DistributiveThermometerEncoder)):
+        enc = cls(num_bits=4).fit(x)
+        assert torch.equal(enc.thresholds, torch.from_numpy(g[f"{tag}_thr"]))
+    assert difflut.REGISTRY.get_encoder("gaussian_thermometer") is GaussianThermometerEncoder
+    assert difflut.REGISTRY.get_encoder("distributive_thermometer") is DistributiveThermometerEncoder

@@ -57,6 +57,16 @@ def test_thermometer_bits_exact(golden, dev):
         assert enc3.encode(x).shape == (x.shape[0], x.shape[1], nb)
 
 
+def test_thermometer_fit_variants_bits_exact(golden, dev):
+    from difflut_b200.encoder import DistributiveThermometerEncoder, GaussianThermometerEncoder
+
+    g = golden("thermometer")
+    x_fit, x = T(g["variant_x_fit"]), T(g["variant_x"]).to(dev)
+    for tag, cls in (("gauss", GaussianThermometerEncoder), ("distr", DistributiveThermometerEncoder)):
+        enc = cls(num_bits=4).fit(x_fit).to(dev)
+        assert np.array_equal(enc.encode(x).cpu().numpy().astype(np.uint8), g[f"{tag}_bits"])
+
+
 def test_thermometer_unfitted_raises(dev):
     from difflut_b200.encoder import ThermometerEncoder
 
