@@ -27,12 +27,9 @@ static inline cudaStream_t dl_cast(dl_stream_t s) { return reinterpret_cast<cuda
 
 static inline int64_t dl_ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 static inline int64_t dl_min64(int64_t a, int64_t b) { return a < b ? a : b; }
-__device__ __forceinline__ int64_t dl_ceil_div_dev(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 // Number of streaming multiprocessors the grids are sized for (B200: 148).
 constexpr int DL_NUM_SMS = 148;
-
-__device__ __forceinline__ uint32_t dl_lane() { return threadIdx.x & 31u; }
 
 // Spread the 4 low bits of `nib` to the least-significant bit of each byte:
 // bit q -> bit 8q.  (1 + 2^7 + 2^14 + 2^21 places every product term on a distinct bit.)

@@ -17,7 +17,7 @@ API objects and this executor always see the same tables.  Equivalent reference 
 model + loop as in examples/demo_probabilistic_random.py:111-178 with DWN nodes.
 """
 
-from typing import List, Optional, Sequence
+from typing import Optional, Sequence
 
 import torch
 import torch.distributed as dist
@@ -257,8 +257,6 @@ class DWNNetwork:
                      count, self.lr, self.betas[0], self.betas[1], self.eps, 1.0)
 
     # ------------------------------------------------------------------ public API
-    KERNELS_PER_STEP_NOTE = "prepare xL, pack, fwd xL(+reduce), ce x2, bwd tables xL, bwd input x(L-1), adam x2"
-
     def kernel_launches_per_step(self) -> int:
         L = len(self.layers)
         fused_adam = self.fused_backward and not self.distributed
