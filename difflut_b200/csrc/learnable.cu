@@ -5,7 +5,8 @@
 // Here the three contractions run on one kernel, C[M,N] (fp32) = A[M,K] * B[N,K]^T with bf16
 // operands: TMA (cp.async.bulk.tensor) stages 128x64 / 256x64 operand tiles in 128-byte-swizzled
 // shared memory, one elected thread issues tcgen05.mma (kind::f16, fp32 accumulator in tensor
-// memory), and four epilogue warps read the accumulator back with tcgen05.ld.
+// memory), and four epilogue warps read the accumulator back with tcgen05.ld.  CTAs are persistent
+// and the accumulator is double-buffered, so the epilogue of a tile overlaps the next tile's MMAs.
 // No cluster, no multicast.  Every wait on an mbarrier is bounded: when a wait runs out the kernel
 // records where it gave up in `status` and leaves (after freeing its tensor memory).
 #include <cuda.h>
@@ -38,8 +39,8 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");
 }
-// Bounded wait on a phase parity; false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Bounded wait on a phase parity; false when the limit ran out or another role of the CTA gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     const uint32_t addr = smem_u32(bar);
     const long long start = clock64();
     for (uint32_t it = 0;; ++it) {
@@ -52,8 +53,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
             : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
-        if ((it & 63u) == 63u && clock64() - start > WAIT_LIMIT_CYCLES) return false;
+        if ((it & 63u) == 63u && (*abort_flag != 0 || clock64() - start > WAIT_LIMIT_CYCLES)) return false;
     }
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
@@ -94,7 +98,11 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                  : "memory");
 }
 
-// status[0] = 0 ok, otherwise (role << 8 | stage) of the wait that gave up
+// Persistent kernel: each CTA (one per SM) walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  The
+// accumulator is double-buffered in tensor memory (2 x 256 columns), so the epilogue warps drain
+// tile t while the MMA thread already accumulates tile t+1; the TMA / MMA stage ring runs across
+// tile boundaries without draining.
+// status[0] = 0 ok, otherwise (role << 8 | stage) of the wait that gave up.
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     float* __restrict__ C, int M, int N, int K, int* __restrict__ status) {
@@ -103,21 +111,17 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);
     uint64_t* empty = full + STAGES;
-    uint64_t* acc_ready = empty + STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+    uint64_t* acc_full = empty + STAGES;    // [2] MMA -> epilogue
+    uint64_t* acc_empty = acc_full + 2;     // [2] epilogue -> MMA (one arrival per epilogue warp)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // 1-D grid; the operand with fewer row tiles is the fast index, so CTAs that run together share the
+    // the operand with fewer row tiles is the fast tile index, so CTAs that run together share the
     // tiles of the large operand's current row block and the small operand is re-read from L2
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
-    int tile_m, tile_n;
-    if (tiles_m <= tiles_n) {
-        tile_m = blockIdx.x % tiles_m;
-        tile_n = blockIdx.x / tiles_m;
-    } else {
-        tile_n = blockIdx.x % tiles_n;
-        tile_m = blockIdx.x / tiles_n;
-    }
+    const int total_tiles = tiles_m * tiles_n;
+    const bool m_fast = tiles_m <= tiles_n;
     const int kblocks = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -125,12 +129,16 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
-        mbar_init(acc_ready, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);
+        }
+        *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {  // tensor memory for the 128 x 256 fp32 accumulator
+    if (warp == 1) {  // all 512 columns of tensor memory: two 128 x 256 fp32 accumulators
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                     "r"((uint32_t)BN)
+                     "r"((uint32_t)(2 * BN))
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -141,59 +149,87 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < kblocks; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t use = kb / STAGES;
-                if (use > 0 && !mbar_wait(&empty[s], (use - 1) & 1)) {
-                    atomicCAS(status, 0, (1 << 8) | s);
-                    break;
+            uint32_t kc = 0;  // k-blocks issued so far, over all tiles
+            for (int tile = blockIdx.x; tile < total_tiles && *abort_flag == 0; tile += gridDim.x) {
+                const int tile_m = m_fast ? tile % tiles_m : tile / tiles_n;
+                const int tile_n = m_fast ? tile / tiles_m : tile % tiles_n;
+                for (int kb = 0; kb < kblocks; ++kb, ++kc) {
+                    const int s = kc % STAGES;
+                    const uint32_t use = kc / STAGES;
+                    if (use > 0 && !mbar_wait(&empty[s], (use - 1) & 1, abort_flag)) {
+                        atomicCAS(status, 0, (1 << 8) | s);
+                        *abort_flag = 1;
+                        break;
+                    }
+                    uint8_t* a_dst = tiles + s * STAGE_BYTES;
+                    uint8_t* b_dst = a_dst + A_BYTES;
+                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_a, &full[s], kb * BK, tile_m * BM);
+                    tma_load_2d(b_dst, &map_b, &full[s], kb * BK, tile_n * BN);
                 }
-                uint8_t* a_dst = tiles + s * STAGE_BYTES;
-                uint8_t* b_dst = a_dst + A_BYTES;
-                mbar_expect_tx(&full[s], STAGE_BYTES);
-                tma_load_2d(a_dst, &map_a, &full[s], kb * BK, tile_m * BM);
-                tma_load_2d(b_dst, &map_b, &full[s], kb * BK, tile_n * BN);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_bf16(BM, BN);
-            bool ok = true;
-            for (int kb = 0; kb < kblocks && ok; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t use = kb / STAGES;
-                if (!mbar_wait(&full[s], use & 1)) {
-                    atomicCAS(status, 0, (2 << 8) | s);
-                    ok = false;
+            uint32_t kc = 0, it = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && *abort_flag == 0; tile += gridDim.x, ++it) {
+                const uint32_t buf = it & 1, useb = it >> 1;
+                if (useb > 0 && !mbar_wait(&acc_empty[buf], (useb - 1) & 1, abort_flag)) {
+                    atomicCAS(status, 0, (4 << 8) | buf);
+                    *abort_flag = 1;
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_addr = smem_u32(tiles + s * STAGE_BYTES);
-                const uint32_t b_addr = a_addr + A_BYTES;
+                const uint32_t tmem_d = tmem_base + buf * BN;
+                bool ok = true;
+                for (int kb = 0; kb < kblocks; ++kb, ++kc) {
+                    const int s = kc % STAGES;
+                    const uint32_t use = kc / STAGES;
+                    if (!mbar_wait(&full[s], use & 1, abort_flag)) {
+                        atomicCAS(status, 0, (2 << 8) | s);
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = smem_u32(tiles + s * STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    // inside the 128-byte swizzle row the next 16 elements start 32 bytes further
-                    const uint64_t adesc = umma_desc_k_major_sw128(a_addr + k * UMMA_K * 2);
-                    const uint64_t bdesc = umma_desc_k_major_sw128(b_addr + k * UMMA_K * 2);
-                    umma_bf16(tmem_base, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // inside the 128-byte swizzle row the next 16 elements start 32 bytes further
+                        const uint64_t adesc = umma_desc_k_major_sw128(a_addr + k * UMMA_K * 2);
+                        const uint64_t bdesc = umma_desc_k_major_sw128(b_addr + k * UMMA_K * 2);
+                        umma_bf16(tmem_d, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty[s]);  // the stage is free again once these MMAs have read it
                 }
-                umma_commit(&empty[s]);  // the stage is free again once these MMAs have read it
+                if (!ok) break;
+                umma_commit(&acc_full[buf]);  // arrives when every MMA of this tile has finished
             }
-            umma_commit(acc_ready);      // arrives when every MMA issued so far has finished
         }
     } else {
         // epilogue: warp w may read TMEM lanes 32*(w%4) .. +31; one accumulator row per thread
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
-        const int64_t grow = (int64_t)tile_m * BM + row;
-        const bool ok = mbar_wait(acc_ready, 0);
-        if (!ok && lane == 0) atomicCAS(status, 0, (3 << 8));
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok) {
+        uint32_t it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+            const int tile_m = m_fast ? tile % tiles_m : tile / tiles_n;
+            const int tile_n = m_fast ? tile / tiles_m : tile % tiles_n;
+            const uint32_t buf = it & 1, useb = it >> 1;
+            const int64_t grow = (int64_t)tile_m * BM + row;
+            if (!mbar_wait(&acc_full[buf], useb & 1, abort_flag)) {
+                if (lane == 0) {
+                    atomicCAS(status, 0, (3 << 8) | buf);
+                    *abort_flag = 1;
+                }
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
-                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN + (uint32_t)c0;
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                     "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -222,12 +258,16 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     }
                 }
             }
+            // this warp has read its quarter of the buffer: hand it back to the MMA thread
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN))
                      : "memory");
     }
 }
@@ -395,7 +435,7 @@ DL_EXPORT int dl_gemm_bf16_tn(const void* A, const void* B, float* C, int64_t M,
     cudaFuncSetAttribute(gemm_bf16_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
     const int64_t gx = dl_ceil_div(N, BN), gy = dl_ceil_div(M, BM);
     DL_REQUIRE(gx * gy < ((int64_t)1 << 31));
-    dim3 grid((unsigned)(gx * gy));
+    dim3 grid((unsigned)dl_min64(gx * gy, DL_NUM_SMS));
     gemm_bf16_tn_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, dl_cast(stream)>>>(map_a, map_b, C, (int)M, (int)N, (int)K,
                                                                            status);
     return dl_launch_status();
