@@ -81,7 +81,36 @@ class DWNMappedFunction(torch.autograd.Function):
         return gxm, gt, None, None
 
 
+_IDENTITY_PLANS = {}
+FEATURE_MAJOR_MIN_NODES = 64  # below this the row-major kernels are cheaper than two transposes
+
+
+def _identity_plan(N: int, n: int, out_dim: int, device):
+    """Connection plan in which node j reads columns j*n .. j*n+n-1 of a (B, N*n) tensor."""
+    from ..layers.fused_ops import ConnectionPlan
+
+    key = (N, n, out_dim, str(device))
+    if key not in _IDENTITY_PLANS:
+        if len(_IDENTITY_PLANS) > 16:
+            _IDENTITY_PLANS.clear()
+        mapping = torch.arange(N * n).view(N, n)
+        _IDENTITY_PLANS[key] = ConnectionPlan(mapping, N * n, out_dim, torch.device(device))
+    return _IDENTITY_PLANS[key]
+
+
 def dwn_mapped_forward(xm, tables, alpha, beta):
+    """Training forward of N nodes on mapped inputs xm (B, N, n) -> (B, N, O) with autograd.
+
+    Wide layers with n <= 6 treat the mapped tensor as N*n input features under the identity map and
+    run the feature-major layer kernels (coalesced, shuffle-based EFD look-ups, no atomics); small
+    cases and n > 6 use the row-major kernels."""
+    B, N, n = xm.shape
+    if n <= 6 and N >= FEATURE_MAJOR_MIN_NODES:
+        from ..layers.fused_ops import DWNLayerFunction
+
+        plan = _identity_plan(N, n, tables.shape[1], xm.device)
+        out = DWNLayerFunction.apply(xm.reshape(B, N * n), tables, plan, alpha, beta)
+        return out.reshape(B, N, tables.shape[1])
     return DWNMappedFunction.apply(xm, tables, alpha, beta)
 
 

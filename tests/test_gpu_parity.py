@@ -537,3 +537,34 @@ def test_soft_select_matches_fp32_reference(dev):
     xb = (torch.rand(64, I, generator=gen) > 0.5).float().to(dev)  # binary inputs: two pieces are exact enough
     out2 = soft_select(xb, W.detach(), 1.0, splits=2)
     torch.testing.assert_close(out2, xb @ torch.softmax(W.detach(), -1).t(), rtol=2e-5, atol=2e-5)
+
+
+def test_wide_materialised_path_equals_fused_layer(dev):
+    """(B, N, n) mapped inputs with N >= 64 go through the feature-major kernels under the identity map:
+    same outputs and gradients as the fused layer forward, and as the oracle."""
+    from difflut_b200.layers import RandomLayer
+    from difflut_b200.nodes import DWNNode, NodeConfig
+
+    gen = torch.Generator().manual_seed(11)
+    B, I, N = 150, 70, 96
+    layer = RandomLayer(I, N, DWNNode, NodeConfig(input_dim=6, output_dim=2), seed=5).to(dev).train()
+    tab = torch.randn(N, 2, 64, generator=gen)
+    with torch.no_grad():
+        layer.luts.copy_(tab.to(dev))
+    x = torch.rand(B, I, generator=gen)
+    gy = torch.randn(B, N * 2, generator=gen).to(dev)
+    xa = x.to(dev).requires_grad_(True)
+    ya = layer(xa)
+    ya.backward(gy)
+    ga, gta = xa.grad.clone(), layer.luts.grad.clone()
+    layer.luts.grad = None
+    xb = x.to(dev).requires_grad_(True)
+    yb = layer._run_nodes(layer.get_mapping(xb))
+    assert torch.equal(ya, yb)
+    yb.backward(gy)
+    torch.testing.assert_close(xb.grad, ga, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(layer.luts.grad, gta, rtol=1e-5, atol=1e-6)
+    xm = O.gather_mapping(x, layer._mapping_indices.cpu())
+    gxm, gl = O.dwn_backward(xm, tab, gy.cpu().reshape(B, N, 2), layer.alpha, layer.beta)
+    torch.testing.assert_close(gta.cpu(), gl, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(ga.cpu(), O.gather_mapping_backward(gxm, layer._mapping_indices.cpu(), I), rtol=1e-4, atol=1e-6)
