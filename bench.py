@@ -262,7 +262,22 @@ def kernel_algorithmic_bytes(net, name):
     return total
 
 
+class StdoutGuard:
+    """Keeps stdout for the one JSON line: while active, file descriptor 1 points at stderr, so that
+    libraries that print to stdout (NCCL's version banner) cannot add lines to it."""
+
+    def __init__(self):
+        sys.stdout.flush()
+        self.saved = os.dup(1)
+        os.dup2(2, 1)
+
+    def emit(self, text: str) -> None:
+        sys.stdout.flush()
+        os.write(self.saved, (text + "\n").encode())
+
+
 def run_gpu_arm(args):
+    guard = StdoutGuard()
     import torch
     import torch.distributed as dist
 
@@ -404,7 +419,7 @@ def run_gpu_arm(args):
         }
         if cpu is not None:
             line["cpu_baseline"] = cpu
-        print(json.dumps(line), flush=True)
+        guard.emit(json.dumps(line))
     barrier()
     trace("finished")
     if world > 1:
@@ -573,13 +588,54 @@ def run_learnable(args):
           flush=True)
 
 
+def run_train_layers(args):
+    """The same 3-layer DWN training step through the per-layer drop-in API: ThermometerEncoder ->
+    RandomLayer x3 -> GroupSum -> torch cross-entropy -> autograd -> torch.optim.Adam (fp32 rows between layers)."""
+    import torch
+
+    warnings.simplefilter("ignore")
+    from difflut_b200.encoder import ThermometerEncoder
+    from difflut_b200.layers import RandomLayer
+    from difflut_b200.nodes import DWNNode, NodeConfig
+    from difflut_b200.utils import GroupSum
+
+    device = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(0)
+    x = torch.rand(GLOBAL_BATCH, FEATURES, generator=g)
+    labels = torch.randint(0, CLASSES, (GLOBAL_BATCH,), generator=g).to(device)
+    enc = ThermometerEncoder(num_bits=THERMO_BITS).fit(x).to(device)
+    layers, I = [], FEATURES * THERMO_BITS
+    for li, N in enumerate(SIZES):
+        layer = RandomLayer(I, N, DWNNode, NodeConfig(input_dim=6, output_dim=1), seed=li)
+        with torch.no_grad():
+            layer.luts.copy_(torch.randn(N, 1, 64, generator=g))
+        layers.append(layer.to(device))
+        I = N
+    model = torch.nn.Sequential(*layers, GroupSum(k=CLASSES, tau=TAU, use_randperm=False)).train()
+    opt = torch.optim.Adam(model.parameters(), lr=LR)
+    xd = x.to(device)
+
+    def step():
+        opt.zero_grad(set_to_none=True)
+        loss = torch.nn.functional.cross_entropy(model(enc(xd)), labels)
+        loss.backward()
+        opt.step()
+
+    ms = _time_gpu(step, args.steps, max(args.warmup, 3), torch.empty(256 << 20, dtype=torch.uint8, device=device))
+    print(json.dumps({"metric": METRIC + " (per-layer API)", "value": GLOBAL_BATCH / (ms * 1e-3), "unit": "samples/s",
+                      "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+                      "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                      "data": "synthetic", "config": _config({"mode": "layer API: fp32 rows between layers, torch autograd + Adam"})}),
+          flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="train", choices=["train", "infer", "prob", "learnable"],
+    ap.add_argument("--workload", default="train", choices=["train", "train-layers", "infer", "prob", "learnable"],
                     help="train = the benchmark contract's workload; the others are secondary measurements")
     ap.add_argument("--small", action="store_true", help="reduced sizes of the secondary workloads (for ncu captures)")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
@@ -607,6 +663,8 @@ def main():
         run_prob(args)
     elif args.workload == "learnable":
         run_learnable(args)
+    elif args.workload == "train-layers":
+        run_train_layers(args)
     else:
         run_gpu_arm(args)
 
