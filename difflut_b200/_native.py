@@ -28,33 +28,35 @@ SIGNATURES = {
     "dl_gather_rows": "pppllll s",
     "dl_gather_rows_bwd": "ppppllll s",
     "dl_dwn_prepare": "pppllff s",
+    "dl_dwn_prepare_weighted": "pppllfp s",
     "dl_dwn_prepare_full": "ppllff s",
-    "dl_dwn_fwd_bits_t": "ppppLLL s".replace("L", "l"),
+    "dl_dwn_fwd_bits_t": "pppplll s",
     "dl_dwn_fwd_vals_t": "ppppplll s",
     "dl_dwn_bwd_tables_t": "ppplfpplll s",
     "dl_dwn_bwd_input_t": "pplfpppplll s",
     "dl_dwn_bwd_fused_t": "pplfplpppppppllll s",
     "dl_sum_groups": "pplll s",
-    "dl_dwn_mapped_fwd": "pppllll i s".replace(" i", "i"),
+    "dl_dwn_mapped_fwd": "ppplllli s",
     "dl_dwn_mapped_bwd": "pppppllll s",
     "dl_prob_fwd_t": "pppfpllll s",
     "dl_prob_fwd_groupsum_t": "pppfpppllllfl s",
     "dl_prob_bwd_t": "pppfplfpplllll s",
+    "dl_hybrid_bwd_t": "pppplfpplllll s",
     "dl_seg_sum_t": "ppppll s",
     "dl_gemm_bf16_tn": "ppplllp s",
     "dl_softmax_rows_bf16": "pfpplll s",
     "dl_softmax_bwd_rows": "ppfpll s",
-    "dl_f32_to_bf16": "ppplllI s".replace("I", "i"),
+    "dl_f32_to_bf16": "pppllli s",
     "dl_bf16_transpose": "ppllll s",
-    "dl_groupsum_rows": "ppllLf s".replace("L", "l"),
-    "dl_groupsum_rows_bwd": "ppllLf s".replace("L", "l"),
+    "dl_groupsum_rows": "pplllf s",
+    "dl_groupsum_rows_bwd": "pplllf s",
     "dl_groupsum_t": "ppllfl s",
     "dl_dwn_fwd_groupsum_t": "ppppplllfl s",
-    "dl_dwn_fwd_groupsum_noalloc_t": "ppppllLfl s".replace("L", "l"),
+    "dl_dwn_fwd_groupsum_noalloc_t": "pppplllfl s",
     "dl_popcount_groupsum_t": "ppllll s",
     "dl_ce_t": "pppppllll s",
     "dl_adam_step": "ppppplfffff s",
-    "dl_adam_step_groups": "pplLppppLfffff s".replace("L", "l"),
+    "dl_adam_step_groups": "ppllpppplfffff s",
 }
 
 _CT = {"p": ctypes.c_void_p, "l": ctypes.c_int64, "i": ctypes.c_int, "f": ctypes.c_float, "d": ctypes.c_double}
@@ -114,6 +116,12 @@ def _ptr(a):
             raise RuntimeError("difflut_b200 kernels take contiguous tensors")
         return a.data_ptr()
     return int(a)
+
+
+def host_floats(values):
+    """ctypes float array for entry points that take a small HOST array; pass `ctypes.addressof(arr)`
+    (keep `arr` alive until the call returns)."""
+    return (ctypes.c_float * len(values))(*[float(v) for v in values])
 
 
 def call(name: str, *args, stream=None):

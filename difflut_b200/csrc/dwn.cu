@@ -83,6 +83,48 @@ dwn_prepare_kernel(const float* __restrict__ tables, float* __restrict__ efd_t,
     }
 }
 
+// Transform with an arbitrary weight per Hamming distance (e.g. 1/(h+1) of the gradient-stabilised
+// DWN variant, difflut/nodes/dwn_stable_node.py:170-202), which is not separable: thread (i, a') of a
+// CTA evaluates the 2^n-term sum directly.  One CTA per node.
+struct HammingWeights {
+    float w[DL_MAX_FAST_N];
+};
+
+__global__ void __launch_bounds__(192)
+dwn_prepare_weighted_kernel(const float* __restrict__ tables, float* __restrict__ efd_t,
+                            uint64_t* __restrict__ masks, int N, int n, float scale, HammingWeights hw) {
+    __shared__ float lut[64];
+    const int L = 1 << n;
+    for (int j = blockIdx.x; j < N; j += gridDim.x) {
+        __syncthreads();
+        if (threadIdx.x < 64) lut[threadIdx.x] = threadIdx.x < L ? __ldg(tables + (int64_t)j * L + threadIdx.x) : 0.f;
+        __syncthreads();
+        if (masks != nullptr && threadIdx.x < 32) {
+            const int lane = threadIdx.x;
+            const uint32_t lo = __ballot_sync(0xffffffffu, lane < L && lut[lane] >= 0.5f);
+            const uint32_t hi = __ballot_sync(0xffffffffu, lane + 32 < L && lut[lane + 32] >= 0.5f);
+            if (lane == 0) masks[j] = ((uint64_t)hi << 32) | lo;
+        }
+        if (efd_t == nullptr) continue;
+        const int i = threadIdx.x >> 5, a5 = threadIdx.x & 31;
+        if (i < n) {
+            // slowly decaying weights leave a heavily cancelling +- sum: accumulate it in double (the
+            // reference sums in Python floats, dwn_stable_node.py:178-200); this kernel is off the hot loop
+            double acc = 0.0;
+            if (a5 < (L >> 1)) {
+                const int low = (1 << i) - 1;
+                const int a = ((a5 & ~low) << 1) | (a5 & low);  // address with bit i = 0
+                const int keep = (L - 1) & ~(1 << i);
+                for (int k = 0; k < L; ++k) {
+                    const double term = (double)lut[k] * (double)hw.w[__popc((a ^ k) & keep)];
+                    acc += ((k >> i) & 1) ? term : -term;
+                }
+            }
+            efd_t[((int64_t)j * n + i) * 32 + a5] = (float)((double)scale * acc);
+        }
+    }
+}
+
 // General n: separable butterfly.  One CTA per (virtual node v, input slot i); the slab
 // efd_full[v][i][0..L) starts as a copy of the table and is transformed in place along every
 // address bit: bit i -> (v1 - v0) in both halves, other bits -> (v0 + beta v1, beta v0 + v1).
@@ -798,6 +840,18 @@ DL_EXPORT int dl_dwn_prepare(const float* tables, float* efd_t, uint64_t* masks,
         dwn_prepare_kernel<6><<<blocks, 256, 0, dl_cast(stream)>>>(tables, efd_t, masks, (int)N, 6, alpha, beta);
     else
         dwn_prepare_kernel<0><<<blocks, 256, 0, dl_cast(stream)>>>(tables, efd_t, masks, (int)N, (int)n, alpha, beta);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_dwn_prepare_weighted(const float* tables, float* efd_t, uint64_t* masks, int64_t N, int64_t n,
+                                      float scale, const float* hamming_weights_host, dl_stream_t stream) {
+    DL_REQUIRE(tables && N > 0 && (efd_t || masks) && hamming_weights_host);
+    if (n < 1 || n > DL_MAX_FAST_N) return DL_ERR_UNSUPPORTED;
+    DL_REQUIRE(N < ((int64_t)1 << 30));
+    HammingWeights hw;
+    for (int h = 0; h < DL_MAX_FAST_N; ++h) hw.w[h] = h < n ? hamming_weights_host[h] : 0.f;
+    const int blocks = (int)dl_min64(N, (int64_t)DL_NUM_SMS * 16);
+    dwn_prepare_weighted_kernel<<<blocks, 192, 0, dl_cast(stream)>>>(tables, efd_t, masks, (int)N, (int)n, scale, hw);
     return dl_launch_status();
 }
 

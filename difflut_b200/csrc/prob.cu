@@ -89,7 +89,11 @@ __global__ void prob_groupsum_reduce_kernel(const float* __restrict__ partial, f
 // gradient accumulators live in registers.  Phase A expands g top-down into g*P_a (table
 // gradient); phase B runs the tree bottom-up keeping the per-level differences and then walks it
 // top-down for d/dx_i.  gxm_t[(j*n+i)][b] receives the input gradient of slot i (summed over o).
-template <int NIN>
+// HYBRID (difflut/nodes/hybrid_node.py:173-224): `raw` holds the table values themselves in the DWN
+// layout (N, O, 2^n), the table gradient is sum_b g*P_a with no sigmoid factor and is written in that
+// layout, and d/dx_i carries the reference's factor x(1-x) / (x(1-x) + 1e-8), which makes the input
+// gradient vanish at x in {0, 1}.
+template <int NIN, bool HYBRID>
 __global__ void __launch_bounds__(128)
 prob_bwd_kernel(const float* __restrict__ x_t, const int32_t* __restrict__ map,
                 const float* __restrict__ raw, float inv_t, const float* __restrict__ g_t,
@@ -106,7 +110,8 @@ prob_bwd_kernel(const float* __restrict__ x_t, const int32_t* __restrict__ map,
         for (int i = 0; i < NIN; ++i) rows[i] = __ldg(map + j * NIN + i);
         for (int o = 0; o < O; ++o) {
             __syncwarp();
-            for (int a = lane; a < L; a += 32) w[a] = prob_weight(raw, j, o, O, L, a, inv_t);
+            for (int a = lane; a < L; a += 32)
+                w[a] = HYBRID ? __ldg(raw + (j * O + o) * L + a) : prob_weight(raw, j, o, O, L, a, inv_t);
             __syncwarp();
             float acc[L];
 #pragma unroll
@@ -161,6 +166,10 @@ prob_bwd_kernel(const float* __restrict__ x_t, const int32_t* __restrict__ map,
                         float dx = 0.f;
 #pragma unroll
                         for (int k = 0; k < cnt; ++k) dx = fmaf(q[k], d[off + k], dx);
+                        if (HYBRID) {
+                            const float t = x[lvl] * (1.f - x[lvl]);
+                            dx *= t / (t + 1e-8f);
+                        }
                         float* dst = gxm_t + (j * NIN + lvl) * Bp + b;
                         if (o == 0) *dst = dx; else *dst += dx;
                         if (lvl > 0) {
@@ -183,8 +192,12 @@ prob_bwd_kernel(const float* __restrict__ x_t, const int32_t* __restrict__ map,
 #pragma unroll
                     for (int sh = 16; sh > 0; sh >>= 1) s += __shfl_xor_sync(0xffffffffu, s, sh);
                     if (lane == (a & 31)) {
-                        const float sg = w[a];
-                        graw[(j * L + a) * O + o] = s * sg * (1.f - sg) * inv_t;
+                        if (HYBRID) {
+                            graw[(j * O + o) * L + a] = s;
+                        } else {
+                            const float sg = w[a];
+                            graw[(j * L + a) * O + o] = s * sg * (1.f - sg) * inv_t;
+                        }
                     }
                 }
             }
@@ -280,6 +293,23 @@ DL_EXPORT int dl_prob_fwd_groupsum_t(const float* x_t, const int32_t* map, const
     return dl_launch_status();
 }
 
+template <bool HYBRID>
+static int launch_prob_bwd(const float* x_t, const int32_t* map, const float* raw, float inv_t, const float* g_t,
+                           int64_t gdiv, float gscale, float* graw, float* gxm_t, int64_t N, int64_t n, int64_t O,
+                           int64_t B, int64_t Bp, cudaStream_t s) {
+    const int64_t blocks = dl_min64(dl_ceil_div(N, 4), (int64_t)DL_NUM_SMS * 16);
+    const unsigned gb = (unsigned)blocks;
+    switch (n) {
+        case 1: prob_bwd_kernel<1, HYBRID><<<gb, 128, 0, s>>>(x_t, map, raw, inv_t, g_t, gdiv, gscale, graw, gxm_t, N, (int)O, B, Bp); break;
+        case 2: prob_bwd_kernel<2, HYBRID><<<gb, 128, 0, s>>>(x_t, map, raw, inv_t, g_t, gdiv, gscale, graw, gxm_t, N, (int)O, B, Bp); break;
+        case 3: prob_bwd_kernel<3, HYBRID><<<gb, 128, 0, s>>>(x_t, map, raw, inv_t, g_t, gdiv, gscale, graw, gxm_t, N, (int)O, B, Bp); break;
+        case 4: prob_bwd_kernel<4, HYBRID><<<gb, 128, 0, s>>>(x_t, map, raw, inv_t, g_t, gdiv, gscale, graw, gxm_t, N, (int)O, B, Bp); break;
+        case 5: prob_bwd_kernel<5, HYBRID><<<gb, 128, 0, s>>>(x_t, map, raw, inv_t, g_t, gdiv, gscale, graw, gxm_t, N, (int)O, B, Bp); break;
+        default: prob_bwd_kernel<6, HYBRID><<<gb, 128, 0, s>>>(x_t, map, raw, inv_t, g_t, gdiv, gscale, graw, gxm_t, N, (int)O, B, Bp); break;
+    }
+    return dl_launch_status();
+}
+
 DL_EXPORT int dl_prob_bwd_t(const float* x_t, const int32_t* map, const float* raw, float temperature,
                             const float* g_t, int64_t gdiv, float gscale, float* graw, float* gxm_t,
                             int64_t N, int64_t n, int64_t O, int64_t B, int64_t Bp, dl_stream_t stream) {
@@ -287,18 +317,18 @@ DL_EXPORT int dl_prob_bwd_t(const float* x_t, const int32_t* map, const float* r
     DL_REQUIRE(B > 0 && Bp >= B && Bp % DL_BATCH_ALIGN == 0);
     if (n < 1 || n > DL_MAX_FAST_N) return DL_ERR_UNSUPPORTED;
     const float inv_t = 1.0f / fmaxf(temperature, 1e-6f);
-    const int64_t blocks = dl_min64(dl_ceil_div(N, 4), (int64_t)DL_NUM_SMS * 16);
-    cudaStream_t s = dl_cast(stream);
-    const unsigned gb = (unsigned)blocks;
-    switch (n) {
-        case 1: prob_bwd_kernel<1><<<gb, 128, 0, s>>>(x_t, map, raw, inv_t, g_t, gdiv, gscale, graw, gxm_t, N, (int)O, B, Bp); break;
-        case 2: prob_bwd_kernel<2><<<gb, 128, 0, s>>>(x_t, map, raw, inv_t, g_t, gdiv, gscale, graw, gxm_t, N, (int)O, B, Bp); break;
-        case 3: prob_bwd_kernel<3><<<gb, 128, 0, s>>>(x_t, map, raw, inv_t, g_t, gdiv, gscale, graw, gxm_t, N, (int)O, B, Bp); break;
-        case 4: prob_bwd_kernel<4><<<gb, 128, 0, s>>>(x_t, map, raw, inv_t, g_t, gdiv, gscale, graw, gxm_t, N, (int)O, B, Bp); break;
-        case 5: prob_bwd_kernel<5><<<gb, 128, 0, s>>>(x_t, map, raw, inv_t, g_t, gdiv, gscale, graw, gxm_t, N, (int)O, B, Bp); break;
-        default: prob_bwd_kernel<6><<<gb, 128, 0, s>>>(x_t, map, raw, inv_t, g_t, gdiv, gscale, graw, gxm_t, N, (int)O, B, Bp); break;
-    }
-    return dl_launch_status();
+    return launch_prob_bwd<false>(x_t, map, raw, inv_t, g_t, gdiv, gscale, graw, gxm_t, N, n, O, B, Bp,
+                                  dl_cast(stream));
+}
+
+DL_EXPORT int dl_hybrid_bwd_t(const float* x_t, const int32_t* map, const float* tables, const float* g_t,
+                              int64_t gdiv, float gscale, float* gtables, float* gxm_t, int64_t N, int64_t n,
+                              int64_t O, int64_t B, int64_t Bp, dl_stream_t stream) {
+    DL_REQUIRE(x_t && map && tables && g_t && (gtables || gxm_t) && N > 0 && O > 0 && gdiv > 0);
+    DL_REQUIRE(B > 0 && Bp >= B && Bp % DL_BATCH_ALIGN == 0);
+    if (n < 1 || n > DL_MAX_FAST_N) return DL_ERR_UNSUPPORTED;
+    return launch_prob_bwd<true>(x_t, map, tables, 1.0f, g_t, gdiv, gscale, gtables, gxm_t, N, n, O, B, Bp,
+                                 dl_cast(stream));
 }
 
 DL_EXPORT int dl_seg_sum_t(const float* src_t, const int32_t* inv_ptr, const int32_t* inv_ent, float* gx_t,

@@ -2,9 +2,9 @@
 
 The reference layer owns `nn.ModuleList([node_type(...) for _ in range(N)])` and loops over
 it (difflut/layers/base_layer.py:342-576).  Here, when `node_type` is one of the package's
-own DWN / Probabilistic nodes, the layer owns ONE stacked parameter (`luts (N, O, 2^n)` or
-`raw_weights (N, 2^n, O)`) and runs one kernel per pass; `layer.nodes` is a lazy sequence of
-node views so that `layer.nodes[i].luts`, `len(layer.nodes)`, per-node calls, initializers and
+own DWN / DWNStable / Hybrid / Probabilistic nodes, the layer owns ONE stacked parameter (`luts (N, O, 2^n)`,
+`raw_luts (N, O, 2^n)` (+ `gradient_scale (N,)` for DWNStable), or `raw_weights (N, 2^n, O)`) and runs one kernel
+per pass; `layer.nodes` is a lazy sequence of node views so that `layer.nodes[i].luts`, `len(layer.nodes)`, per-node calls, initializers and
 regularizers keep working, and the state dict is written with the reference's per-node keys
 (`nodes.{i}.luts` ...).  Any other node class keeps the reference structure (a ModuleList,
 the gather kernel and a per-node loop), which is API compatibility, not a second backend.
@@ -19,6 +19,8 @@ import torch.nn as nn
 
 from ..nodes.base_node import validate_node_dims, validate_regularizers
 from ..nodes.dwn_node import DWNNode, MAX_DWN_INPUT_DIM, default_alpha, default_beta
+from ..nodes.dwn_stable_node import DWNStableNode, MAX_DWN_STABLE_INPUT_DIM
+from ..nodes.hybrid_node import HybridNode, MAX_HYBRID_INPUT_DIM
 from ..nodes.node_config import NodeConfig
 from ..nodes.probabilistic_node import ProbabilisticNode
 from ..utils.warnings import warn_default_value
@@ -163,6 +165,12 @@ class BaseLUTLayer(ABC, LUTLayerMixin, nn.Module):
         if node_type is DWNNode:
             self._stacked = "dwn"
             self._init_stacked_dwn(**kwargs)
+        elif node_type is DWNStableNode:
+            self._stacked = "dwn_stable"
+            self._init_stacked_dwn_stable(**kwargs)
+        elif node_type is HybridNode:
+            self._stacked = "hybrid"
+            self._init_stacked_hybrid(**kwargs)
         elif node_type is ProbabilisticNode:
             self._stacked = "probabilistic"
             self._init_stacked_prob(**kwargs)
@@ -217,6 +225,34 @@ class BaseLUTLayer(ABC, LUTLayerMixin, nn.Module):
         self._init_rows(self.luts.data, "luts")
         self.nodes = _NodeViews(self)
 
+    def _init_stacked_dwn_stable(self, input_dim=None, output_dim=None, use_cuda=True, regularizers=None,
+                                 gradient_scale=1.25, init_fn=None, init_kwargs=None):
+        self._common_node_args(input_dim, output_dim, regularizers, init_fn, init_kwargs)
+        if self.n > MAX_DWN_STABLE_INPUT_DIM:
+            raise ValueError(f"DWNStableNode supports input_dim <= {MAX_DWN_STABLE_INPUT_DIM}, got {self.n}")
+        self.gradient_scale = nn.Parameter(torch.full((self.output_size,), float(gradient_scale)))
+        self.raw_luts = nn.Parameter(torch.randn(self.output_size, self.output_dim_per_node, 2 ** self.n) * 0.1)
+        self._init_rows(self.raw_luts.data, "raw_luts")
+        self.nodes = _NodeViews(self)
+
+    def _init_stacked_hybrid(self, input_dim=None, output_dim=None, use_cuda=True, regularizers=None, init_fn=None,
+                             init_kwargs=None):
+        self._common_node_args(input_dim, output_dim, regularizers, init_fn, init_kwargs)
+        if self.n > MAX_HYBRID_INPUT_DIM:
+            raise ValueError(f"HybridNode supports input_dim <= {MAX_HYBRID_INPUT_DIM}, got {self.n}")
+        self.raw_luts = nn.Parameter(torch.randn(self.output_size, self.output_dim_per_node, 2 ** self.n) * 0.1)
+        self._init_rows(self.raw_luts.data, "raw_luts")
+        self.nodes = _NodeViews(self)
+
+    def stable_tables(self) -> torch.Tensor:
+        """sigmoid(raw_luts) (N, O, 2^n) of a DWNStable / Hybrid layer (dwn_stable_node.py:310-316,
+        hybrid_node.py:308-314)."""
+        return torch.sigmoid(self.raw_luts)
+
+    def stable_scales(self) -> torch.Tensor:
+        """One backward scale per virtual node (N*O,), detached: the reference reads it with .item()."""
+        return self.gradient_scale.detach().float().repeat_interleave(self.output_dim_per_node)
+
     def _init_stacked_prob(self, input_dim=None, output_dim=None, init_fn=None, init_kwargs=None,
                            regularizers=None, temperature=1.0, eval_mode="expectation", use_cuda=True):
         self._common_node_args(input_dim, output_dim, regularizers, init_fn, init_kwargs)
@@ -239,6 +275,18 @@ class BaseLUTLayer(ABC, LUTLayerMixin, nn.Module):
                 destination[f"{prefix}nodes.{i}.alpha"] = torch.tensor(self.alpha, dtype=torch.float32, device=dev)
                 destination[f"{prefix}nodes.{i}.beta"] = torch.tensor(self.beta, dtype=torch.float32, device=dev)
                 destination[f"{prefix}nodes.{i}.luts"] = stacked[i]
+        elif self._stacked == "dwn_stable":
+            stacked = destination.pop(prefix + "raw_luts")
+            scales = destination.pop(prefix + "gradient_scale")
+            for i in range(self.output_size):
+                destination[f"{prefix}nodes.{i}.gradient_scale"] = scales[i]
+                destination[f"{prefix}nodes.{i}.raw_luts"] = stacked[i]
+        elif self._stacked == "hybrid":
+            stacked = destination.pop(prefix + "raw_luts")
+            patterns = HybridNode.binary_patterns(self.n, stacked.device)
+            for i in range(self.output_size):
+                destination[f"{prefix}nodes.{i}.raw_luts"] = stacked[i]
+                destination[f"{prefix}nodes.{i}.binary_combinations"] = patterns
         else:
             stacked = destination.pop(prefix + "raw_weights")
             dev = stacked.device
@@ -251,7 +299,8 @@ class BaseLUTLayer(ABC, LUTLayerMixin, nn.Module):
     def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys,
                               error_msgs):
         if self._stacked is not None:
-            name = "luts" if self._stacked == "dwn" else "raw_weights"
+            name = {"dwn": "luts", "dwn_stable": "raw_luts", "hybrid": "raw_luts",
+                    "probabilistic": "raw_weights"}[self._stacked]
             first = f"{prefix}nodes.0.{name}"
             if first in state_dict and (prefix + name) not in state_dict:
                 rows = []
@@ -264,6 +313,10 @@ class BaseLUTLayer(ABC, LUTLayerMixin, nn.Module):
                     rows.append(state_dict[key])
                 if rows is not None:
                     state_dict[prefix + name] = torch.stack([r.detach() for r in rows])
+                if self._stacked == "dwn_stable" and f"{prefix}nodes.0.gradient_scale" in state_dict:
+                    state_dict[prefix + "gradient_scale"] = torch.stack(
+                        [state_dict[f"{prefix}nodes.{i}.gradient_scale"].detach().reshape(())
+                         for i in range(self.output_size)])
                 if self._stacked == "dwn" and f"{prefix}nodes.0.alpha" in state_dict:
                     self.alpha = float(state_dict[f"{prefix}nodes.0.alpha"])
                     self.beta = float(state_dict[f"{prefix}nodes.0.beta"])
@@ -341,6 +394,21 @@ class BaseLUTLayer(ABC, LUTLayerMixin, nn.Module):
 
             out = (dwn_mapped_forward(mapped, self.luts, self.alpha, self.beta) if self.training
                    else dwn_mapped_eval(mapped, self.luts))
+            return out.reshape(B, -1)
+        if self._stacked == "dwn_stable":
+            from ..nodes.dwn_node import dwn_mapped_eval
+            from ..nodes.dwn_stable_node import dwn_stable_mapped_forward
+
+            tables = self.stable_tables()
+            out = (dwn_stable_mapped_forward(mapped, tables, self.gradient_scale) if self.training
+                   else dwn_mapped_eval(mapped, tables))
+            return out.reshape(B, -1)
+        if self._stacked == "hybrid":
+            from ..nodes.dwn_node import dwn_mapped_eval
+            from ..nodes.hybrid_node import hybrid_mapped_forward
+
+            tables = self.stable_tables()
+            out = hybrid_mapped_forward(mapped, tables) if self.training else dwn_mapped_eval(mapped, tables)
             return out.reshape(B, -1)
         if self._stacked == "probabilistic":
             from ..nodes.probabilistic_node import prob_mapped_eval, prob_mapped_forward

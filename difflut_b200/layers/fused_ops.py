@@ -66,14 +66,34 @@ def _t_to_rows(t: torch.Tensor, B: int) -> torch.Tensor:
     return rows
 
 
+def _efd_tables(tables, NO, n, alpha, beta, stable_scale):
+    """Per-step backward transform (N*O, n, 32): beta^hamming weights (DWN) or, when `stable_scale` is
+    given, 1/(hamming+1) weights times that scale (gradient-stabilised DWN)."""
+    import ctypes
+
+    efd = torch.empty(NO, n, 32, device=tables.device, dtype=torch.float32)
+    if stable_scale is None:
+        _native.call("dl_dwn_prepare", tables, efd, None, NO, n, alpha, beta)
+    else:
+        w = _native.host_floats([1.0 / (h + 1.0) for h in range(n)])
+        scalar = 1.0 if isinstance(stable_scale, torch.Tensor) else float(stable_scale)
+        _native.call("dl_dwn_prepare_weighted", tables, efd, None, NO, n, scalar, ctypes.addressof(w))
+        if isinstance(stable_scale, torch.Tensor):  # one scale per virtual node
+            efd.mul_(stable_scale.reshape(NO, 1, 1))
+    return efd
+
+
 class DWNLayerFunction(torch.autograd.Function):
     """RandomLayer(+DWN) training forward/backward: x (B, I) rows, tables (N, O, 2^n) -> (B, N*O).
 
     Counterpart of EFDFusedFunction (difflut/nodes/dwn_node.py:232-316) with per-node tables.
+    With `stable_scale` (a float or a per-virtual-node tensor) the backward is the gradient-stabilised
+    variant of difflut/nodes/dwn_stable_node.py:145-205: table gradient times the scale, input gradient
+    with 1/(hamming+1) weights times the scale.
     """
 
     @staticmethod
-    def forward(ctx, x, tables, plan: ConnectionPlan, alpha: float, beta: float):
+    def forward(ctx, x, tables, plan: ConnectionPlan, alpha: float, beta: float, stable_scale=None):
         x = x.contiguous().float()
         tables = tables.contiguous().float()
         B, I = x.shape
@@ -87,6 +107,7 @@ class DWNLayerFunction(torch.autograd.Function):
             out = _t_to_rows(out_t, B)
         ctx.save_for_backward(bits, tables)
         ctx.plan, ctx.alpha, ctx.beta, ctx.B = plan, float(alpha), float(beta), B
+        ctx.stable_scale = stable_scale.detach() if isinstance(stable_scale, torch.Tensor) else stable_scale
         return out
 
     @staticmethod
@@ -103,14 +124,16 @@ class DWNLayerFunction(torch.autograd.Function):
             gt = torch.empty_like(tables)
             # the table-gradient kernel also produces the addresses the input-gradient kernel reads
             _native.call("dl_dwn_bwd_tables_t", bits, plan.map_virtual, g_t, 1, 1.0, gt, addr, NO, n, Bp)
+            if ctx.stable_scale is not None:
+                sc = ctx.stable_scale
+                gt = gt * (sc.reshape(gt.shape[0], gt.shape[1], 1) if isinstance(sc, torch.Tensor) else float(sc))
             if need_x:
-                efd = torch.empty(NO, n, 32, device=g.device, dtype=torch.float32)
-                _native.call("dl_dwn_prepare", tables, efd, None, NO, n, ctx.alpha, ctx.beta)
+                efd = _efd_tables(tables, NO, n, ctx.alpha, ctx.beta, ctx.stable_scale)
                 gx_t = torch.empty(I, Bp, device=g.device, dtype=torch.float32)
                 _native.call("dl_dwn_bwd_input_t", addr, g_t, 1, 1.0, efd, plan.inv_ptr_virtual,
                              plan.inv_ent8_virtual, gx_t, I, n, Bp)
                 gx = _t_to_rows(gx_t, B)
-        return gx, (gt if need_t else None), None, None, None
+        return gx, (gt if need_t else None), None, None, None, None
 
 
 def dwn_layer_eval(x: torch.Tensor, tables: torch.Tensor, plan: ConnectionPlan) -> torch.Tensor:
@@ -186,6 +209,51 @@ class ProbLayerFunction(torch.autograd.Function):
                 _native.call("dl_seg_sum_t", gxm_t, plan.inv_ptr_nodes, plan.inv_ent_nodes, gx_t, I, Bp)
                 gx = _t_to_rows(gx_t, B)
         return gx, (graw if need_r else None), None, None, None, None
+
+
+class HybridLayerFunction(torch.autograd.Function):
+    """RandomLayer(+Hybrid) training forward/backward: x (B, I) rows, tables (N, O, 2^n) -> (B, N*O).
+
+    Forward is the DWN look-up on `x >= 0.5`; backward is the probabilistic one on the real-valued x
+    (HybridFunctionCPU, difflut/nodes/hybrid_node.py:119-224).
+    """
+
+    @staticmethod
+    def forward(ctx, x, tables, plan: ConnectionPlan):
+        x = x.contiguous().float()
+        tables = tables.contiguous().float()
+        B, I = x.shape
+        NO, n = plan.N * plan.O, plan.n
+        Bp = _native.padded_batch(B)
+        with torch.cuda.device(x.device):
+            x_t = _rows_to_t(x, Bp)
+            bits = torch.empty(I, Bp // 32, device=x.device, dtype=torch.int32)
+            _native.call("dl_pack_rows_to_t", x, bits, B, I, Bp, 0.5)
+            out_t = torch.empty(NO, Bp, device=x.device, dtype=torch.float32)
+            _native.call("dl_dwn_fwd_vals_t", bits, plan.map_virtual, tables, out_t, None, NO, n, Bp)
+            out = _t_to_rows(out_t, B)
+        ctx.save_for_backward(x_t, tables)
+        ctx.plan, ctx.B = plan, B
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        x_t, tables = ctx.saved_tensors
+        plan, B = ctx.plan, ctx.B
+        N, n, O, I = plan.N, plan.n, plan.O, plan.input_size
+        Bp = x_t.shape[1]
+        need_x, need_t = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        gx = None
+        with torch.cuda.device(g.device):
+            g_t = _rows_to_t(g.contiguous().float(), Bp)
+            gt = torch.empty_like(tables)
+            gxm_t = torch.empty(N * n, Bp, device=g.device, dtype=torch.float32) if need_x else None
+            _native.call("dl_hybrid_bwd_t", x_t, plan.map_nodes, tables, g_t, 1, 1.0, gt, gxm_t, N, n, O, B, Bp)
+            if need_x:
+                gx_t = torch.empty(I, Bp, device=g.device, dtype=torch.float32)
+                _native.call("dl_seg_sum_t", gxm_t, plan.inv_ptr_nodes, plan.inv_ent_nodes, gx_t, I, Bp)
+                gx = _t_to_rows(gx_t, B)
+        return gx, (gt if need_t else None), None
 
 
 class GatherFunction(torch.autograd.Function):

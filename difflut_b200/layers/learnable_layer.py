@@ -136,6 +136,9 @@ class LearnableLayer(BaseLUTLayer):
         if not self.training and self._stacked == "dwn" and self.n <= FAST_PATH_MAX_N:
             idx = self.mapping.hard_indices().view(self.output_size, self.n)
             return dwn_layer_eval(x, self.luts, self._plan_for(idx, x.device, "hard"))
+        if not self.training and self._stacked in ("dwn_stable", "hybrid"):
+            idx = self.mapping.hard_indices().view(self.output_size, self.n)
+            return dwn_layer_eval(x, self.stable_tables(), self._plan_for(idx, x.device, "hard"))
         return self._run_nodes(self.get_mapping(x))
 
     def get_mapping_matrix(self) -> torch.Tensor:

@@ -105,6 +105,13 @@ int dl_gather_rows_bwd(const float* g, const int32_t* inv_ptr, const int32_t* in
  * Either output pointer may be null. */
 int dl_dwn_prepare(const float* tables, float* efd_t, uint64_t* masks, int64_t N, int64_t n,
                    float alpha, float beta, dl_stream_t stream);
+/* The same outputs with an arbitrary weight per Hamming distance instead of beta^h:
+ * efd_t[j,i,a'] = scale * sum_k sgn(k_i) * tables[j,k] * w[popc((a^k) & ~(1<<i))].
+ * hamming_weights_host is a HOST array of n floats (w[0..n-1]); it is copied at the call.
+ * w[h] = 1/(h+1) gives the gradient-stabilised DWN backward
+ * (difflut/nodes/dwn_stable_node.py:170-202, kernel difflut/nodes/cuda/dwn_stable_cuda_kernel.cu:80-145). */
+int dl_dwn_prepare_weighted(const float* tables, float* efd_t, uint64_t* masks, int64_t N, int64_t n,
+                            float scale, const float* hamming_weights_host, dl_stream_t stream);
 
 /* Hard forward on packed bits: out_bits_t[j] = masks[j] looked up at the address formed from
  * rows map[j,0..n-1] of in_bits_t, 32 samples per word at a time (bit-sliced). */
@@ -193,6 +200,15 @@ int dl_prob_fwd_groupsum_t(const float* x_t, const int32_t* map, const float* ra
 int dl_prob_bwd_t(const float* x_t, const int32_t* map, const float* raw, float temperature,
                   const float* g_t, int64_t gdiv, float gscale, float* graw, float* gxm_t, int64_t N,
                   int64_t n, int64_t O, int64_t B, int64_t Bp, dl_stream_t stream);
+/* Hybrid node backward (difflut/nodes/hybrid_node.py:173-224; replaces hybrid_cuda.backward): the forward
+ * is the DWN look-up (dl_dwn_fwd_vals_t), the backward treats the table as a probabilistic node's
+ * weights.  tables / gtables (N, O, 2^n) fp32 in the DWN layout (the sigmoid of raw_luts and its
+ * chain rule stay with the caller); gtables[j,o,a] = sum_b g * P_a(x_b) (overwritten);
+ * gxm_t [N*n][Bp] = the product-rule input gradient times x(1-x)/(x(1-x)+1e-8), summed over the
+ * node's outputs (overwritten).  x_t [F][Bp] fp32, g as for dl_prob_bwd_t.  n <= DL_MAX_FAST_N. */
+int dl_hybrid_bwd_t(const float* x_t, const int32_t* map, const float* tables, const float* g_t,
+                    int64_t gdiv, float gscale, float* gtables, float* gxm_t, int64_t N, int64_t n,
+                    int64_t O, int64_t B, int64_t Bp, dl_stream_t stream);
 /* gx_t[f][b] = sum over the inverse-map entries e of feature f of src_t[inv_ent[e]][b]: the
  * scatter-add of the gather (difflut/layers/cuda/mapping_cuda_kernel.cu:136-162) as an
  * atomics-free segmented sum in the feature-major layout. */

@@ -218,6 +218,71 @@ def dwn_backward(
     return gxm, gl.float()
 
 
+def stable_transform(luts: torch.Tensor, scale) -> torch.Tensor:
+    """T[j,o,a,i] = scale_j * sum_k sgn(k_i) * luts[j,o,k] / (popc((a^k) & ~(1<<i)) + 1).
+
+    Gradient-stabilised variant, dwn_stable_node.py:170-202, in float64.  `scale` is a float or a
+    per-node tensor (N,).  (N, O, 2^n) -> (N, O, 2^n, n) float64.
+    """
+    N, O, L = luts.shape
+    n = int(math.log2(L))
+    a = torch.arange(L)
+    k = torch.arange(L)
+    out = torch.empty(N, O, L, n, dtype=torch.float64)
+    l64 = luts.double()
+    sc = torch.as_tensor(scale, dtype=torch.float64).reshape(-1, 1, 1) if torch.is_tensor(scale) else float(scale)
+    for i in range(n):
+        mask = (L - 1) & ~(1 << i)
+        x = (a[:, None] ^ k[None, :]) & mask
+        ham = torch.zeros_like(x)
+        for bit in range(n):
+            ham += (x >> bit) & 1
+        sign = torch.where(((k >> i) & 1) == 0, -1.0, 1.0).double()
+        M = sign[None, :] / (ham.double() + 1.0)  # (a, k)
+        out[..., i] = sc * torch.einsum("ak,jok->joa", M, l64)
+    return out
+
+
+def dwn_stable_backward(
+    xm: torch.Tensor, luts: torch.Tensor, g: torch.Tensor, scale
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Gradient-stabilised backward: (gxm (B,N,n) fp32, gluts (N,O,2^n) fp32) w.r.t. the sigmoid-ed tables.
+
+    dwn_stable_node.py:145-205.  gluts[j,o,addr_b] += scale_j * g[b,j,o];
+    gxm[b,j,i] = sum_o g[b,j,o] * T[j,o,addr,i] with T of `stable_transform`.
+    """
+    addr = dwn_addresses(xm)
+    B, N = addr.shape
+    _, O, L = luts.shape
+    T = stable_transform(luts, scale)
+    Tsel = T[torch.arange(N)[None, :].expand(B, N), :, addr]  # (B,N,O,n)
+    gxm = (g.double().unsqueeze(-1) * Tsel).sum(2).float()
+    gl = torch.zeros(N, O, L, dtype=torch.float64)
+    flat = (torch.arange(N)[None, :, None] * O + torch.arange(O)[None, None, :]) * L + addr[:, :, None]
+    gl.view(-1).index_add_(0, flat.reshape(-1), g.double().reshape(-1))
+    sc = torch.as_tensor(scale, dtype=torch.float64).reshape(-1, 1, 1) if torch.is_tensor(scale) else float(scale)
+    return gxm, (gl * sc).float()
+
+
+def hybrid_backward(xm: torch.Tensor, luts: torch.Tensor, g: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Hybrid-node backward: (gxm (B,N,n) fp32, gluts (N,O,2^n) fp32) w.r.t. the sigmoid-ed tables.
+
+    hybrid_node.py:173-224, vectorised over nodes, same fp32 operation order per node:
+    P[b,j,a] = prod_i (x_i a_i + (1-x_i)(1-a_i));  gluts[j,o,a] = sum_b P[b,j,a] g[b,j,o];
+    gxm[b,j,i] = sum_o g[b,j,o] sum_a P[b,j,a] (a_i - x_i) / (x_i (1-x_i) + 1e-8) luts[j,o,a].
+    """
+    n = xm.shape[-1]
+    pats = prob_patterns(n)  # (L, n)
+    xe = xm.unsqueeze(2)  # (B,N,1,n)
+    ae = pats[None, None]  # (1,1,L,n)
+    probs = torch.prod(xe * ae + (1 - xe) * (1 - ae), dim=3)  # (B,N,L)
+    gl = torch.einsum("bjl,bjo->jol", probs, g)
+    deriv = (ae - xe) / (xe * (1 - xe) + 1e-8)  # (B,N,L,n)
+    pw = probs.unsqueeze(-1) * deriv
+    gxm = torch.einsum("bjli,jol,bjo->bji", pw, luts, g)
+    return gxm, gl
+
+
 # ----------------------------------------------------------------------------------
 # Probabilistic node
 # ----------------------------------------------------------------------------------

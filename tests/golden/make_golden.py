@@ -242,6 +242,73 @@ def main():
     out["eval_counts"] = _np(counts.round()).astype(np.int32)
     np.savez_compressed(os.path.join(HERE, "dwn_net3.npz"), **out)
 
+    # ---------------------------------------------------------------- gradient-stabilised DWN layer fwd+bwd
+    from difflut.nodes import DWNStableNode
+
+    out = {}
+    for tag, B, I, N, n, O, seed, scale in (("n6", 20, 40, 18, 6, 1, 3, 1.25), ("n4o2", 10, 16, 6, 4, 2, 6, 0.7),
+                                            ("n3", 9, 8, 5, 3, 1, 8, 2.0)):
+        g = torch.Generator().manual_seed(seed)
+        x = torch.rand(B, I, generator=g, requires_grad=True)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            layer = RandomLayer(I, N, DWNStableNode,
+                                NodeConfig(input_dim=n, output_dim=O, extra_params={"gradient_scale": scale}),
+                                seed=seed, ensure_full_input_coverage=False)
+        raw = torch.randn(N, O, 2**n, generator=g)
+        with torch.no_grad():
+            for j, node in enumerate(layer.nodes):
+                node.raw_luts.copy_(raw[j])
+        layer.train()
+        y = layer(x)
+        gy = torch.randn(y.shape, generator=g)
+        y.backward(gy)
+        out[f"{tag}_x"] = _np(x)
+        out[f"{tag}_map"] = _np(layer._mapping_indices)
+        out[f"{tag}_raw"] = _np(raw)
+        out[f"{tag}_scale"] = np.array([scale], dtype=np.float64)
+        out[f"{tag}_y"] = _np(y)
+        out[f"{tag}_gy"] = _np(gy)
+        out[f"{tag}_gx"] = _np(x.grad)
+        out[f"{tag}_graw"] = _np(torch.stack([nd.raw_luts.grad for nd in layer.nodes]))
+        layer.eval()
+        xb = (x.detach() >= 0.5).float()
+        out[f"{tag}_y_eval"] = _np(layer(xb)).astype(np.uint8)
+    np.savez_compressed(os.path.join(HERE, "dwn_stable_layer.npz"), **out)
+
+    # ---------------------------------------------------------------- hybrid layer fwd+bwd
+    from difflut.nodes import HybridNode
+
+    out = {}
+    for tag, B, I, N, n, O, seed in (("n6", 20, 40, 18, 6, 1, 4), ("n4o2", 10, 16, 6, 4, 2, 7), ("n2", 9, 8, 5, 2, 1, 9)):
+        g = torch.Generator().manual_seed(seed)
+        x = torch.rand(B, I, generator=g)
+        x[0, : I // 2] = (x[0, : I // 2] >= 0.5).float()  # exactly binary inputs: the input gradient is zero there
+        x.requires_grad_(True)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            layer = RandomLayer(I, N, HybridNode, NodeConfig(input_dim=n, output_dim=O), seed=seed,
+                                ensure_full_input_coverage=False)
+        raw = torch.randn(N, O, 2**n, generator=g)
+        with torch.no_grad():
+            for j, node in enumerate(layer.nodes):
+                node.raw_luts.copy_(raw[j])
+        layer.train()
+        y = layer(x)
+        gy = torch.randn(y.shape, generator=g)
+        y.backward(gy)
+        out[f"{tag}_x"] = _np(x)
+        out[f"{tag}_map"] = _np(layer._mapping_indices)
+        out[f"{tag}_raw"] = _np(raw)
+        out[f"{tag}_y"] = _np(y)
+        out[f"{tag}_gy"] = _np(gy)
+        out[f"{tag}_gx"] = _np(x.grad)
+        out[f"{tag}_graw"] = _np(torch.stack([nd.raw_luts.grad for nd in layer.nodes]))
+        layer.eval()
+        xb = (x.detach() >= 0.5).float()
+        out[f"{tag}_y_eval"] = _np(layer(xb)).astype(np.uint8)
+    np.savez_compressed(os.path.join(HERE, "hybrid_layer.npz"), **out)
+
     # ---------------------------------------------------------------- GroupSum known answers
     out = {}
     g = torch.Generator().manual_seed(9)

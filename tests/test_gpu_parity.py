@@ -137,6 +137,137 @@ def test_dwn_layer_matches_reference(golden, dev, tag):
     assert torch.equal(yn, y.detach().reshape(x.shape[0], N, O_)[:, 1, :])
 
 
+@pytest.mark.parametrize("tag", ["n6", "n4o2", "n3"])
+def test_dwn_stable_layer_matches_reference(golden, dev, tag):
+    from difflut_b200.nodes import DWNStableNode
+
+    g = golden("dwn_stable_layer")
+    x, idx, raw = T(g[f"{tag}_x"]), T(g[f"{tag}_map"]), T(g[f"{tag}_raw"])
+    scale = float(g[f"{tag}_scale"][0])
+    N, O_, L = raw.shape
+    n = int(np.log2(L))
+    layer = _layer(dev, x.shape[1], N, n, O_, DWNStableNode, idx, extra={"gradient_scale": scale})
+    assert layer.gradient_scale.shape == (N,) and float(layer.gradient_scale[0]) == pytest.approx(scale)
+    with torch.no_grad():
+        layer.raw_luts.copy_(raw.to(dev))
+    xg = x.to(dev).requires_grad_(True)
+    layer.train()
+    y = layer(xg)
+    torch.testing.assert_close(y.cpu(), T(g[f"{tag}_y"]), rtol=0, atol=2e-7)  # sigmoid on the device
+    y.backward(T(g[f"{tag}_gy"]).to(dev))
+    torch.testing.assert_close(xg.grad.cpu(), T(g[f"{tag}_gx"]), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(layer.raw_luts.grad.cpu(), T(g[f"{tag}_graw"]), rtol=1e-5, atol=1e-6)
+    assert layer.gradient_scale.grad is None  # the reference reads it with .item(): no gradient
+    layer.eval()
+    ye = layer((x >= 0.5).float().to(dev))
+    assert np.array_equal(ye.cpu().numpy().astype(np.uint8), g[f"{tag}_y_eval"])
+    # materialised path and per-node views
+    layer.train()
+    xg2 = x.to(dev).requires_grad_(True)
+    y2 = layer._run_nodes(layer.get_mapping(xg2))
+    assert torch.equal(y2, y)
+    y2.backward(T(g[f"{tag}_gy"]).to(dev))
+    torch.testing.assert_close(xg2.grad.cpu(), T(g[f"{tag}_gx"]), rtol=1e-5, atol=1e-6)
+    node = layer.nodes[1]
+    yn = node(layer.get_mapping(x.to(dev))[:, 1, :])
+    assert torch.equal(yn, y.detach().reshape(x.shape[0], N, O_)[:, 1, :])
+    # reference-format state dict round trip
+    sd = layer.state_dict()
+    assert f"nodes.{N - 1}.raw_luts" in sd and f"nodes.0.gradient_scale" in sd and "raw_luts" not in sd
+    other = _layer(dev, x.shape[1], N, n, O_, DWNStableNode, idx)
+    other.load_state_dict(sd)
+    assert torch.equal(other.raw_luts, layer.raw_luts) and torch.equal(other.gradient_scale, layer.gradient_scale)
+
+
+@pytest.mark.parametrize("tag", ["n6", "n4o2", "n2"])
+def test_hybrid_layer_matches_reference(golden, dev, tag):
+    from difflut_b200.nodes import HybridNode
+
+    g = golden("hybrid_layer")
+    x, idx, raw = T(g[f"{tag}_x"]), T(g[f"{tag}_map"]), T(g[f"{tag}_raw"])
+    N, O_, L = raw.shape
+    n = int(np.log2(L))
+    layer = _layer(dev, x.shape[1], N, n, O_, HybridNode, idx)
+    with torch.no_grad():
+        layer.raw_luts.copy_(raw.to(dev))
+    xg = x.to(dev).requires_grad_(True)
+    layer.train()
+    y = layer(xg)
+    torch.testing.assert_close(y.cpu(), T(g[f"{tag}_y"]), rtol=0, atol=2e-7)  # sigmoid on the device
+    y.backward(T(g[f"{tag}_gy"]).to(dev))
+    gx_ref = T(g[f"{tag}_gx"])
+    torch.testing.assert_close(xg.grad.cpu(), gx_ref, rtol=1e-5, atol=1e-6)
+    assert torch.count_nonzero(xg.grad[0, : x.shape[1] // 2]) == 0  # exactly binary inputs: zero gradient
+    torch.testing.assert_close(layer.raw_luts.grad.cpu(), T(g[f"{tag}_graw"]), rtol=1e-5, atol=1e-6)
+    layer.eval()
+    ye = layer((x >= 0.5).float().to(dev))
+    assert np.array_equal(ye.cpu().numpy().astype(np.uint8), g[f"{tag}_y_eval"])
+    # materialised path and per-node views
+    layer.train()
+    xg2 = x.to(dev).requires_grad_(True)
+    y2 = layer._run_nodes(layer.get_mapping(xg2))
+    assert torch.equal(y2, y)
+    y2.backward(T(g[f"{tag}_gy"]).to(dev))
+    torch.testing.assert_close(xg2.grad.cpu(), gx_ref, rtol=1e-5, atol=1e-6)
+    node = layer.nodes[1]
+    yn = node(layer.get_mapping(x.to(dev))[:, 1, :])
+    assert torch.equal(yn, y.detach().reshape(x.shape[0], N, O_)[:, 1, :])
+    assert node.binary_combinations.shape == (L, n)
+    sd = layer.state_dict()
+    assert f"nodes.{N - 1}.raw_luts" in sd and "nodes.0.binary_combinations" in sd and "raw_luts" not in sd
+    other = _layer(dev, x.shape[1], N, n, O_, HybridNode, idx)
+    other.load_state_dict(sd)
+    assert torch.equal(other.raw_luts, layer.raw_luts)
+
+
+def test_hybrid_standalone_node_vs_oracle(dev):
+    from difflut_b200.nodes import HybridNode
+
+    gen = torch.Generator().manual_seed(31)
+    B, n, O_ = 70, 5, 2
+    x = torch.rand(B, n, generator=gen)
+    node = HybridNode(input_dim=n, output_dim=O_).to(dev)
+    tab = torch.sigmoid(node.raw_luts.detach()).cpu()
+    xg = x.to(dev).requires_grad_(True)
+    y = node.train()(xg)
+    assert torch.equal(y.cpu(), O.dwn_forward(x.unsqueeze(1), tab.unsqueeze(0)).squeeze(1))
+    gy = torch.randn(B, O_, generator=gen)
+    y.backward(gy.to(dev))
+    gxm, gl = O.hybrid_backward(x.unsqueeze(1), tab.unsqueeze(0), gy.unsqueeze(1))
+    torch.testing.assert_close(xg.grad.cpu(), gxm.squeeze(1), rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(node.raw_luts.grad.cpu(), gl.squeeze(0) * tab * (1 - tab), rtol=1e-4, atol=1e-6)
+    with pytest.raises(ValueError):
+        HybridNode(input_dim=7, output_dim=1)
+
+
+@pytest.mark.parametrize("n,O_", [(1, 1), (3, 2), (6, 1)])
+def test_dwn_stable_standalone_node_vs_oracle(dev, n, O_):
+    from difflut_b200.nodes import DWNStableNode
+
+    gen = torch.Generator().manual_seed(20 + n)
+    B = 50
+    x = torch.rand(B, n, generator=gen)
+    node = DWNStableNode(input_dim=n, output_dim=O_, gradient_scale=0.9).to(dev)
+    raw = torch.randn(O_, 2 ** n, generator=gen)
+    with torch.no_grad():
+        node.raw_luts.copy_(raw.to(dev))
+    tab = torch.sigmoid(node.raw_luts.detach()).cpu()  # the device's sigmoid, so look-ups compare exactly
+    xg = x.to(dev).requires_grad_(True)
+    node.train()
+    y = node(xg)
+    assert torch.equal(y.cpu(), O.dwn_forward(x.unsqueeze(1), tab.unsqueeze(0)).squeeze(1))
+    gy = torch.randn(B, O_, generator=gen)
+    y.backward(gy.to(dev))
+    gxm, gl = O.dwn_stable_backward(x.unsqueeze(1), tab.unsqueeze(0), gy.unsqueeze(1), 0.9)
+    torch.testing.assert_close(xg.grad.cpu(), gxm.squeeze(1), rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(node.raw_luts.grad.cpu(), (gl.squeeze(0) * tab * (1 - tab)), rtol=1e-4, atol=1e-6)
+    node.eval()
+    xb = (x >= 0.5).float()
+    assert torch.equal(node(xb.to(dev)).cpu(), O.dwn_forward_eval(xb.unsqueeze(1), tab.unsqueeze(0)).squeeze(1))
+    with pytest.raises(ValueError):
+        DWNStableNode(input_dim=7, output_dim=1)
+
+
 @pytest.mark.parametrize("n,O_", [(1, 1), (3, 2), (6, 1), (8, 1), (10, 2)])
 def test_dwn_standalone_node_vs_oracle(dev, n, O_):
     from difflut_b200.nodes import DWNNode

@@ -59,6 +59,51 @@ def test_dwn_layer_matches_reference(golden):
         assert np.array_equal(ye.reshape(B, -1).numpy().astype(np.uint8), g[f"{tag}_y_eval"])
 
 
+def test_dwn_stable_layer_matches_reference(golden):
+    g = golden("dwn_stable_layer")
+    for tag in ("n6", "n4o2", "n3"):
+        x, idx, raw = T(g[f"{tag}_x"]), T(g[f"{tag}_map"]), T(g[f"{tag}_raw"])
+        scale = float(g[f"{tag}_scale"][0])
+        tab = torch.sigmoid(raw)
+        xm = O.gather_mapping(x, idx)
+        y = O.dwn_forward(xm, tab)
+        B = x.shape[0]
+        # sigmoid of the stacked tensor may differ from the per-node sigmoid by one ulp (vector vs scalar tail)
+        torch.testing.assert_close(y.reshape(B, -1), T(g[f"{tag}_y"]), rtol=0, atol=1e-7)
+        gy = T(g[f"{tag}_gy"]).reshape(y.shape)
+        gxm, gl = O.dwn_stable_backward(xm, tab, gy, scale)
+        gx = O.gather_mapping_backward(gxm, idx, x.shape[1])
+        torch.testing.assert_close(gx, T(g[f"{tag}_gx"]), rtol=1e-5, atol=1e-6)
+        graw = gl * tab * (1.0 - tab)  # chain rule through the sigmoid parameterisation
+        torch.testing.assert_close(graw, T(g[f"{tag}_graw"]), rtol=1e-5, atol=1e-6)
+        ye = O.dwn_forward_eval(O.gather_mapping((x >= 0.5).float(), idx), tab)
+        assert np.array_equal(ye.reshape(B, -1).numpy().astype(np.uint8), g[f"{tag}_y_eval"])
+    # per-node scales equal the scalar form when all nodes share one value
+    a = O.stable_transform(tab, 0.7)
+    b = O.stable_transform(tab, torch.full((tab.shape[0],), 0.7))
+    torch.testing.assert_close(a, b)
+
+
+def test_hybrid_layer_matches_reference(golden):
+    g = golden("hybrid_layer")
+    for tag in ("n6", "n4o2", "n2"):
+        x, idx, raw = T(g[f"{tag}_x"]), T(g[f"{tag}_map"]), T(g[f"{tag}_raw"])
+        tab = torch.sigmoid(raw)
+        xm = O.gather_mapping(x, idx)
+        y = O.dwn_forward(xm, tab)
+        B = x.shape[0]
+        torch.testing.assert_close(y.reshape(B, -1), T(g[f"{tag}_y"]), rtol=0, atol=1e-7)
+        gy = T(g[f"{tag}_gy"]).reshape(y.shape)
+        gxm, gl = O.hybrid_backward(xm, tab, gy)
+        gx = O.gather_mapping_backward(gxm, idx, x.shape[1])
+        gx_ref = T(g[f"{tag}_gx"])
+        torch.testing.assert_close(gx, gx_ref, rtol=1e-5, atol=1e-6)
+        assert torch.count_nonzero(gx_ref[0, : x.shape[1] // 2]) == 0  # binary inputs get no gradient
+        torch.testing.assert_close(gl * tab * (1.0 - tab), T(g[f"{tag}_graw"]), rtol=1e-5, atol=1e-6)
+        ye = O.dwn_forward_eval(O.gather_mapping((x >= 0.5).float(), idx), tab)
+        assert np.array_equal(ye.reshape(B, -1).numpy().astype(np.uint8), g[f"{tag}_y_eval"])
+
+
 def test_dwn_residual_tables_pass_bit0(golden):
     tab = T(golden("dwn_layer")["residual_tables"]).reshape(1, 1, 64)
     a = torch.arange(64)
