@@ -27,6 +27,10 @@ SIGNATURES = {
     "dl_bits_rows_to_t": "ppllll s",
     "dl_gather_rows": "pppllll s",
     "dl_gather_rows_bwd": "ppppllll s",
+    "dl_unfold_rows": "ppllllllllll s",
+    "dl_unfold_pack_t": "ppllllllllllfl s",
+    "dl_fold_rows": "ppllllllllll s",
+    "dl_fold_t": "pplllllllllll s",
     "dl_dwn_prepare": "pppllff s",
     "dl_dwn_prepare_weighted": "pppllfp s",
     "dl_dwn_prepare_full": "ppllff s",
@@ -94,6 +98,8 @@ def lib():
     handle.dl_dwn_bwd_groups.argtypes = [ctypes.c_int64]
     handle.dl_prob_groupsum_splits.restype = ctypes.c_int64
     handle.dl_prob_groupsum_splits.argtypes = [ctypes.c_int64, ctypes.c_int64]
+    handle.dl_unfold_positions.restype = ctypes.c_int64
+    handle.dl_unfold_positions.argtypes = [ctypes.c_int64] * 4
     _lib = handle
     return _lib
 

@@ -1,8 +1,10 @@
 """Layers of the hot path (registered on import)."""
 
 from .base_layer import BaseLUTLayer
-from .layer_config import LayerConfig
+from .convolutional import ConvolutionalLayer, ConvolutionConfig
+from .layer_config import GroupedInputConfig, LayerConfig
 from .learnable_layer import LearnableLayer
 from .random_layer import RandomLayer
 
-__all__ = ["BaseLUTLayer", "RandomLayer", "LearnableLayer", "LayerConfig"]
+__all__ = ["BaseLUTLayer", "RandomLayer", "LearnableLayer", "ConvolutionalLayer", "ConvolutionConfig",
+           "LayerConfig", "GroupedInputConfig"]

@@ -249,10 +249,6 @@ class BaseLUTLayer(ABC, LUTLayerMixin, nn.Module):
         hybrid_node.py:308-314)."""
         return torch.sigmoid(self.raw_luts)
 
-    def stable_scales(self) -> torch.Tensor:
-        """One backward scale per virtual node (N*O,), detached: the reference reads it with .item()."""
-        return self.gradient_scale.detach().float().repeat_interleave(self.output_dim_per_node)
-
     def _init_stacked_prob(self, input_dim=None, output_dim=None, init_fn=None, init_kwargs=None,
                            regularizers=None, temperature=1.0, eval_mode="expectation", use_cuda=True):
         self._common_node_args(input_dim, output_dim, regularizers, init_fn, init_kwargs)
@@ -386,35 +382,79 @@ class BaseLUTLayer(ABC, LUTLayerMixin, nn.Module):
     def get_mapping_indices(self):
         return None
 
-    def _run_nodes(self, mapped: torch.Tensor) -> torch.Tensor:
+    def _own_params(self):
+        """The stacked parameter tensors the node arithmetic of this layer reads, as a tuple."""
+        if self._stacked == "dwn":
+            return (self.luts,)
+        if self._stacked == "dwn_stable":
+            return (self.raw_luts, self.gradient_scale)
+        if self._stacked == "hybrid":
+            return (self.raw_luts,)
+        if self._stacked == "probabilistic":
+            return (self.raw_weights,)
+        return ()
+
+    def _apply_plan(self, x: torch.Tensor, plan: ConnectionPlan, params=None, geom=None) -> torch.Tensor:
+        """Layer arithmetic (B, I) -> (B, N*O) under connection plan `plan` with parameters `params`
+        (default: this layer's own).  Other callers pass the concatenated parameters of several layers
+        of the same configuration together with their combined plan, which runs them as one layer.
+        With `geom` (a PatchGeometry) x is an image batch and the samples are its patches; node types
+        that only look at `x >= 0.5` then never materialise the patches."""
+        from .fused_ops import (DWNLayerFunction, GatherFunction, HybridLayerFunction, PatchFunction,
+                                ProbLayerFunction, dwn_levels_eval)
+
+        params = self._own_params() if params is None else params
+        kind, fast = self._stacked, self.n <= 6
+        if kind == "dwn" and fast:
+            if self.training:
+                return DWNLayerFunction.apply(x, params[0], plan, self.alpha, self.beta, None, geom)
+            return dwn_levels_eval(x, [(params[0], plan)], geom)
+        if kind == "dwn_stable":
+            tables = torch.sigmoid(params[0])
+            if self.training:
+                scales = params[1].detach().float().repeat_interleave(self.output_dim_per_node)
+                return DWNLayerFunction.apply(x, tables, plan, 0.0, 0.0, scales, geom)
+            return dwn_levels_eval(x, [(tables, plan)], geom)
+        if kind == "hybrid" and not self.training:
+            return dwn_levels_eval(x, [(torch.sigmoid(params[0]), plan)], geom)
+        if geom is not None:
+            x = PatchFunction.apply(x, geom)
+        if kind == "hybrid":
+            return HybridLayerFunction.apply(x, torch.sigmoid(params[0]), plan)
+        if kind == "probabilistic" and fast and self.training:
+            return ProbLayerFunction.apply(x, params[0], plan, self.temperature, None, 1.0)
+        return self._run_nodes(GatherFunction.apply(x, plan), params)
+
+    def _run_nodes(self, mapped: torch.Tensor, params=None) -> torch.Tensor:
         """Node arithmetic on materialised inputs (B, N, n) -> (B, N*O)."""
         B = mapped.shape[0]
+        params = self._own_params() if params is None else params
         if self._stacked == "dwn":
             from ..nodes.dwn_node import dwn_mapped_eval, dwn_mapped_forward
 
-            out = (dwn_mapped_forward(mapped, self.luts, self.alpha, self.beta) if self.training
-                   else dwn_mapped_eval(mapped, self.luts))
+            out = (dwn_mapped_forward(mapped, params[0], self.alpha, self.beta) if self.training
+                   else dwn_mapped_eval(mapped, params[0]))
             return out.reshape(B, -1)
         if self._stacked == "dwn_stable":
             from ..nodes.dwn_node import dwn_mapped_eval
             from ..nodes.dwn_stable_node import dwn_stable_mapped_forward
 
-            tables = self.stable_tables()
-            out = (dwn_stable_mapped_forward(mapped, tables, self.gradient_scale) if self.training
+            tables = torch.sigmoid(params[0])
+            out = (dwn_stable_mapped_forward(mapped, tables, params[1]) if self.training
                    else dwn_mapped_eval(mapped, tables))
             return out.reshape(B, -1)
         if self._stacked == "hybrid":
             from ..nodes.dwn_node import dwn_mapped_eval
             from ..nodes.hybrid_node import hybrid_mapped_forward
 
-            tables = self.stable_tables()
+            tables = torch.sigmoid(params[0])
             out = hybrid_mapped_forward(mapped, tables) if self.training else dwn_mapped_eval(mapped, tables)
             return out.reshape(B, -1)
         if self._stacked == "probabilistic":
             from ..nodes.probabilistic_node import prob_mapped_eval, prob_mapped_forward
 
-            out = (prob_mapped_forward(mapped, self.raw_weights, self.temperature) if self.training
-                   else prob_mapped_eval(mapped, self.raw_weights, self.temperature))
+            out = (prob_mapped_forward(mapped, params[0], self.temperature) if self.training
+                   else prob_mapped_eval(mapped, params[0], self.temperature))
             return out.reshape(B, -1)
         outs = [node(mapped[:, i, :]) for i, node in enumerate(self.nodes)]
         return torch.stack(outs, dim=1).reshape(B, -1)

@@ -83,6 +83,54 @@ def _efd_tables(tables, NO, n, alpha, beta, stable_scale):
     return efd
 
 
+class PatchGeometry:
+    """Convolution geometry of an image batch (B, C, H, W): receptive field, stride, zero padding.
+
+    A sample is one patch (b, oy, ox) and a feature one tap (c, ki, kj), in nn.Unfold's order
+    (difflut/layers/convolutional.py:170-173,199-205)."""
+
+    def __init__(self, shape, kernel, stride, padding):
+        self.B, self.C, self.H, self.W = (int(v) for v in shape)
+        self.kh, self.kw = int(kernel[0]), int(kernel[1])
+        self.sh, self.sw = int(stride[0]), int(stride[1])
+        self.ph, self.pw = int(padding[0]), int(padding[1])
+        lib = _native.lib()
+        self.OH = int(lib.dl_unfold_positions(self.H, self.kh, self.sh, self.ph))
+        self.OW = int(lib.dl_unfold_positions(self.W, self.kw, self.sw, self.pw))
+        if self.OH <= 0 or self.OW <= 0:
+            raise ValueError(
+                f"receptive field {(self.kh, self.kw)} does not fit the padded input {(self.H, self.W)} "
+                f"+ 2*{(self.ph, self.pw)}"
+            )
+        self.P = self.OH * self.OW
+        self.S = self.B * self.P  # samples
+        self.F = self.C * self.kh * self.kw  # features per sample
+
+    def args(self):
+        return (self.B, self.C, self.H, self.W, self.kh, self.kw, self.sh, self.sw, self.ph, self.pw)
+
+
+class PatchFunction(torch.autograd.Function):
+    """x (B, C, H, W) -> patches (B*OH*OW, C*kh*kw) fp32 rows; backward folds the gradient back."""
+
+    @staticmethod
+    def forward(ctx, x, geom: PatchGeometry):
+        x = x.contiguous().float()
+        out = torch.empty(geom.S, geom.F, device=x.device, dtype=torch.float32)
+        with torch.cuda.device(x.device):
+            _native.call("dl_unfold_rows", x, out, *geom.args())
+        ctx.geom = geom
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        geom = ctx.geom
+        gx = torch.empty(geom.B, geom.C, geom.H, geom.W, device=g.device, dtype=torch.float32)
+        with torch.cuda.device(g.device):
+            _native.call("dl_fold_rows", g.contiguous().float(), gx, *geom.args())
+        return gx, None
+
+
 class DWNLayerFunction(torch.autograd.Function):
     """RandomLayer(+DWN) training forward/backward: x (B, I) rows, tables (N, O, 2^n) -> (B, N*O).
 
@@ -90,30 +138,40 @@ class DWNLayerFunction(torch.autograd.Function):
     With `stable_scale` (a float or a per-virtual-node tensor) the backward is the gradient-stabilised
     variant of difflut/nodes/dwn_stable_node.py:145-205: table gradient times the scale, input gradient
     with 1/(hamming+1) weights times the scale.
+    With `geom` the input is an image batch (B, C, H, W) and the layer runs on its patches
+    (difflut/layers/convolutional.py:194-205) without materialising them: the patch bits are packed
+    straight from the image and the input gradient is folded straight back into it.
     """
 
     @staticmethod
-    def forward(ctx, x, tables, plan: ConnectionPlan, alpha: float, beta: float, stable_scale=None):
+    def forward(ctx, x, tables, plan: ConnectionPlan, alpha: float, beta: float, stable_scale=None,
+                geom: Optional[PatchGeometry] = None):
         x = x.contiguous().float()
         tables = tables.contiguous().float()
-        B, I = x.shape
+        if geom is None:
+            B, I = x.shape
+        else:
+            B, I = geom.S, geom.F
         NO, n = plan.N * plan.O, plan.n
         Bp = _native.padded_batch(B)
         with torch.cuda.device(x.device):
             bits = torch.empty(I, Bp // 32, device=x.device, dtype=torch.int32)
-            _native.call("dl_pack_rows_to_t", x, bits, B, I, Bp, 0.5)
+            if geom is None:
+                _native.call("dl_pack_rows_to_t", x, bits, B, I, Bp, 0.5)
+            else:
+                _native.call("dl_unfold_pack_t", x, bits, *geom.args(), 0.5, Bp)
             out_t = torch.empty(NO, Bp, device=x.device, dtype=torch.float32)
             _native.call("dl_dwn_fwd_vals_t", bits, plan.map_virtual, tables, out_t, None, NO, n, Bp)
             out = _t_to_rows(out_t, B)
         ctx.save_for_backward(bits, tables)
-        ctx.plan, ctx.alpha, ctx.beta, ctx.B = plan, float(alpha), float(beta), B
+        ctx.plan, ctx.alpha, ctx.beta, ctx.B, ctx.geom = plan, float(alpha), float(beta), B, geom
         ctx.stable_scale = stable_scale.detach() if isinstance(stable_scale, torch.Tensor) else stable_scale
         return out
 
     @staticmethod
     def backward(ctx, g):
         bits, tables = ctx.saved_tensors
-        plan, B = ctx.plan, ctx.B
+        plan, B, geom = ctx.plan, ctx.B, ctx.geom
         NO, n, I = plan.N * plan.O, plan.n, plan.input_size
         Bp = bits.shape[1] * 32
         need_x, need_t = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
@@ -132,27 +190,48 @@ class DWNLayerFunction(torch.autograd.Function):
                 gx_t = torch.empty(I, Bp, device=g.device, dtype=torch.float32)
                 _native.call("dl_dwn_bwd_input_t", addr, g_t, 1, 1.0, efd, plan.inv_ptr_virtual,
                              plan.inv_ent8_virtual, gx_t, I, n, Bp)
-                gx = _t_to_rows(gx_t, B)
-        return gx, (gt if need_t else None), None, None, None, None
+                if geom is None:
+                    gx = _t_to_rows(gx_t, B)
+                else:
+                    gx = torch.empty(geom.B, geom.C, geom.H, geom.W, device=g.device, dtype=torch.float32)
+                    _native.call("dl_fold_t", gx_t, gx, *geom.args(), Bp)
+        return gx, (gt if need_t else None), None, None, None, None, None
+
+
+def dwn_levels_eval(x: torch.Tensor, levels, geom: Optional[PatchGeometry] = None) -> torch.Tensor:
+    """Eval forward of consecutive hard-LUT layers on {0,1} inputs, bit-packed from end to end.
+
+    `levels` is a list of (tables (N, O, 2^n), plan); the output of one level is the input of the next.
+    x is (B, I) rows, or with `geom` an image batch whose patches are the samples.  Returns the last
+    level's fp32 {0,1} rows (dwn_node.py:457-483 applied layer after layer)."""
+    x = x.contiguous().float()
+    if geom is None:
+        B, I = x.shape
+    else:
+        B, I = geom.S, geom.F
+    Bp = _native.padded_batch(B)
+    with torch.cuda.device(x.device):
+        bits = torch.empty(I, Bp // 32, device=x.device, dtype=torch.int32)
+        if geom is None:
+            _native.call("dl_pack_rows_to_t", x, bits, B, I, Bp, 0.5)
+        else:
+            _native.call("dl_unfold_pack_t", x, bits, *geom.args(), 0.5, Bp)
+        for tables, plan in levels:
+            tables = tables.detach().contiguous().float()
+            NO, n = plan.N * plan.O, plan.n
+            masks = torch.empty(NO, device=x.device, dtype=torch.int64)
+            _native.call("dl_dwn_prepare", tables, None, masks, NO, n, 0.0, 0.0)
+            out_bits = torch.empty(NO, Bp // 32, device=x.device, dtype=torch.int32)
+            _native.call("dl_dwn_fwd_bits_t", bits, plan.map_virtual, masks, out_bits, NO, n, Bp)
+            bits = out_bits
+        out = torch.empty(B, NO, device=x.device, dtype=torch.float32)
+        _native.call("dl_bits_t_to_rows", bits, out, B, NO, Bp)
+    return out
 
 
 def dwn_layer_eval(x: torch.Tensor, tables: torch.Tensor, plan: ConnectionPlan) -> torch.Tensor:
     """Eval forward on {0,1} inputs: bit-sliced hard LUTs, fp32 {0,1} rows out (dwn_node.py:457-483)."""
-    x = x.contiguous().float()
-    tables = tables.detach().contiguous().float()
-    B, I = x.shape
-    NO, n = plan.N * plan.O, plan.n
-    Bp = _native.padded_batch(B)
-    with torch.cuda.device(x.device):
-        bits = torch.empty(I, Bp // 32, device=x.device, dtype=torch.int32)
-        _native.call("dl_pack_rows_to_t", x, bits, B, I, Bp, 0.5)
-        masks = torch.empty(NO, device=x.device, dtype=torch.int64)
-        _native.call("dl_dwn_prepare", tables, None, masks, NO, n, 0.0, 0.0)
-        out_bits = torch.empty(NO, Bp // 32, device=x.device, dtype=torch.int32)
-        _native.call("dl_dwn_fwd_bits_t", bits, plan.map_virtual, masks, out_bits, NO, n, Bp)
-        out = torch.empty(B, NO, device=x.device, dtype=torch.float32)
-        _native.call("dl_bits_t_to_rows", out_bits, out, B, NO, Bp)
-    return out
+    return dwn_levels_eval(x, [(tables, plan)])
 
 
 class ProbLayerFunction(torch.autograd.Function):

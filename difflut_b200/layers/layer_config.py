@@ -54,3 +54,44 @@ class LayerConfig:
             if self.grad_subtract_mean:
                 parts.append(f"grad_subtract_mean={self.grad_subtract_mean}")
         return f"LayerConfig({', '.join(parts)})" if parts else "LayerConfig(default)"
+
+
+class GroupedInputConfig:
+    """Index maps in which every node reads from one input group only.
+
+    Mirrors difflut/layers/layer_config.py:141-221: the `input_size` features form `n_groups`
+    consecutive groups (for a convolution: one group per input channel, each of receptive-field size);
+    every node draws `bits_per_node` positions inside a group, then the group's offset is added.  The
+    same torch CPU generator calls in the same order give the reference's maps bit for bit; the global
+    RNG state is saved and restored.
+    """
+
+    def __init__(self, n_groups: int, input_size: int, output_trees: int, luts_per_tree: int,
+                 bits_per_node: int, seed: int, ensure_full_coverage: bool = True) -> None:
+        import torch
+
+        if n_groups < 1:
+            raise ValueError(f"n_groups must be >= 1, got {n_groups}. Example: n_groups=4 for 4 input groups.")
+        self.n_groups = n_groups
+        self.luts_per_tree = luts_per_tree
+        total_nodes = output_trees * luts_per_tree
+        group_size = input_size // n_groups
+        saved = torch.get_rng_state()
+        torch.manual_seed(seed)
+        within = torch.multinomial(torch.ones((total_nodes, group_size)), num_samples=bits_per_node,
+                                   replacement=bits_per_node > group_size)
+        if ensure_full_coverage:
+            # whole permutations of the groups, then a no-replacement draw for what is left
+            cycles, rest = divmod(total_nodes, n_groups)
+            picks = [torch.randperm(n_groups) for _ in range(cycles)]
+            if rest > 0:
+                picks.append(torch.multinomial(torch.ones((n_groups,)), num_samples=rest, replacement=False))
+            group_of_node = torch.cat(picks).unsqueeze(1)
+        else:
+            group_of_node = torch.randint(low=0, high=n_groups, size=(total_nodes, 1))
+        self.mapping_indices = within + group_of_node * group_size
+        torch.set_rng_state(saved)
+
+    def get_mapping_indices(self, chunk_start: int, chunk_end: int):
+        """Rows of the map that belong to trees [chunk_start, chunk_end)."""
+        return self.mapping_indices[chunk_start * self.luts_per_tree:chunk_end * self.luts_per_tree, :]

@@ -14,7 +14,7 @@ import torch.nn as nn
 from ..nodes.node_config import NodeConfig
 from ..registry import register_layer
 from .base_layer import BaseLUTLayer
-from .fused_ops import DWNLayerFunction, GatherFunction, HybridLayerFunction, ProbLayerFunction, dwn_layer_eval
+from .fused_ops import GatherFunction, ProbLayerFunction
 from .layer_config import LayerConfig
 
 DEFAULT_RANDOM_LAYER_SEED: int = 42
@@ -93,24 +93,7 @@ class RandomLayer(BaseLUTLayer):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         self._validate_input_dims(x)
-        if self._stacked == "dwn" and self.n <= FAST_PATH_MAX_N:
-            plan = self._plan(x.device)
-            if self.training:
-                return DWNLayerFunction.apply(x, self.luts, plan, self.alpha, self.beta)
-            return dwn_layer_eval(x, self.luts, plan)
-        if self._stacked == "dwn_stable":
-            plan = self._plan(x.device)
-            if self.training:
-                return DWNLayerFunction.apply(x, self.stable_tables(), plan, 0.0, 0.0, self.stable_scales())
-            return dwn_layer_eval(x, self.stable_tables(), plan)
-        if self._stacked == "hybrid":
-            plan = self._plan(x.device)
-            if self.training:
-                return HybridLayerFunction.apply(x, self.stable_tables(), plan)
-            return dwn_layer_eval(x, self.stable_tables(), plan)
-        if self._stacked == "probabilistic" and self.n <= FAST_PATH_MAX_N and self.training:
-            return ProbLayerFunction.apply(x, self.raw_weights, self._plan(x.device), self.temperature, None, 1.0)
-        return self._run_nodes(self.get_mapping(x))
+        return self._apply_plan(x, self._plan(x.device))
 
     def forward_groupsum(self, x: torch.Tensor, k: int, tau: float = 1.0) -> torch.Tensor:
         """Probabilistic layer fused with the following GroupSum(k, tau): (B, I) -> (B, k) logits,

@@ -92,6 +92,32 @@ int dl_gather_rows(const float* x, const int32_t* map, float* out, int64_t B, in
 int dl_gather_rows_bwd(const float* g, const int32_t* inv_ptr, const int32_t* inv_ent, float* gx,
                        int64_t B, int64_t F, int64_t N, int64_t n, dl_stream_t stream);
 
+/* ------------------------------------------------------------------ ConvolutionalLayer patches
+ * Replaces nn.Unfold + transpose + view of the convolutional LUT layer
+ * (difflut/layers/convolutional.py:170-173,199-205) and its autograd adjoint (fold).
+ * x (B, C, H, W) fp32.  A sample is one patch s = b*OH*OW + oy*OW + ox, a feature is
+ * f = (c*kh + ki)*kw + kj (nn.Unfold's order); taps in the zero padding read 0.
+ * OH = dl_unfold_positions(H, kh, sh, ph), OW likewise (0 = invalid geometry).
+ *   dl_unfold_rows     patches (B*OH*OW, C*kh*kw) fp32 rows
+ *   dl_unfold_pack_t   bits_t [C*kh*kw][Bp/32], bit = tap >= threshold, Bp >= B*OH*OW a multiple of
+ *                      128; samples beyond B*OH*OW pack as 0
+ *   dl_fold_rows       gx (B, C, H, W) = adjoint of dl_unfold_rows applied to gpatches (overwritten)
+ *   dl_fold_t          the same from a feature-major gradient gpatches_t [C*kh*kw][Bp]
+ * The adjoints gather per input pixel (no atomics, fixed summation order).                     */
+int64_t dl_unfold_positions(int64_t size, int64_t k, int64_t stride, int64_t pad);
+int dl_unfold_rows(const float* x, float* patches, int64_t B, int64_t C, int64_t H, int64_t W,
+                   int64_t kh, int64_t kw, int64_t sh, int64_t sw, int64_t ph, int64_t pw,
+                   dl_stream_t stream);
+int dl_unfold_pack_t(const float* x, uint32_t* bits_t, int64_t B, int64_t C, int64_t H, int64_t W,
+                     int64_t kh, int64_t kw, int64_t sh, int64_t sw, int64_t ph, int64_t pw,
+                     float threshold, int64_t Bp, dl_stream_t stream);
+int dl_fold_rows(const float* gpatches, float* gx, int64_t B, int64_t C, int64_t H, int64_t W,
+                 int64_t kh, int64_t kw, int64_t sh, int64_t sw, int64_t ph, int64_t pw,
+                 dl_stream_t stream);
+int dl_fold_t(const float* gpatches_t, float* gx, int64_t B, int64_t C, int64_t H, int64_t W,
+              int64_t kh, int64_t kw, int64_t sh, int64_t sw, int64_t ph, int64_t pw, int64_t Bp,
+              dl_stream_t stream);
+
 /* ------------------------------------------------------------------ DWN node, feature-major path
  * Together these replace the per-node efd_cuda.forward / .backward calls of a whole layer
  * (difflut/nodes/cuda/efd_cuda.cpp:22-45) and the layer-wide efd_fused_cuda.forward /

@@ -356,6 +356,84 @@ def learnable_tau(iteration: int, tau_start: float, tau_min: float, tau_decay_it
 
 
 # ----------------------------------------------------------------------------------
+# Convolutional layer: patches, merged tree levels
+# ----------------------------------------------------------------------------------
+
+
+def conv_unfold(x: torch.Tensor, kernel, stride, padding) -> torch.Tensor:
+    """(B, C, H, W) -> (B*P, C*kh*kw) patch rows.  convolutional.py:170-173,199-205 (nn.Unfold is
+    torch's own op; the transpose + view follow the reference)."""
+    patches = F.unfold(x, kernel_size=kernel, padding=padding, stride=stride)  # (B, F, P)
+    return patches.transpose(1, 2).contiguous().view(-1, patches.shape[1])
+
+
+def conv_fold(gpatches: torch.Tensor, shape, kernel, stride, padding) -> torch.Tensor:
+    """Adjoint of conv_unfold: (B*P, F) -> (B, C, H, W)."""
+    B, C, H, W = shape
+    g = gpatches.view(B, -1, gpatches.shape[1]).transpose(1, 2)
+    return F.fold(g, output_size=(H, W), kernel_size=kernel, padding=padding, stride=stride)
+
+
+def conv_level_maps(maps, hidden_layers, trees: int):
+    """Per-level index maps of all trees as one layer.  `maps[l]` holds the sub-layers' maps of level l
+    one after the other (tree order); for l >= 1 tree t reads its own block of the level below
+    (convolutional.py:225-236), i.e. columns t*hidden[l-1] + index."""
+    out = [maps[0].long()]
+    for l in range(1, len(maps)):
+        m = maps[l].long().view(trees, hidden_layers[l], -1)
+        shift = (torch.arange(trees) * hidden_layers[l - 1]).view(trees, 1, 1)
+        out.append((m + shift).view(trees * hidden_layers[l], -1))
+    return out
+
+
+def conv_output(rows: torch.Tensor, B: int, OH: int, OW: int) -> torch.Tensor:
+    """(B*P, trees) -> (B, trees, OH, OW).  convolutional.py:242-249."""
+    return rows.view(B, OH * OW, -1).transpose(1, 2).reshape(B, -1, OH, OW)
+
+
+def conv_dwn_forward(x, kernel, stride, padding, maps, tables, eval_mode: bool = False):
+    """DWN trees on every patch: returns (rows (B*P, trees), activations per level)."""
+    h = conv_unfold(x, kernel, stride, padding)
+    acts = []
+    for m, t in zip(maps, tables):
+        acts.append(h)
+        xm = gather_mapping(h, m)
+        h = (dwn_forward_eval(xm, t) if eval_mode else dwn_forward(xm, t)).reshape(h.shape[0], -1)
+    return h, acts
+
+
+def conv_dwn_backward(acts, maps, tables, grows, alpha: float, beta: float, shape, kernel, stride, padding):
+    """Backward of conv_dwn_forward: (gx (B,C,H,W), [gtables per level])."""
+    grads = [None] * len(maps)
+    g = grows
+    for l in range(len(maps) - 1, -1, -1):
+        xm = gather_mapping(acts[l], maps[l])
+        gxm, grads[l] = dwn_backward(xm, tables[l], g.reshape(g.shape[0], -1, 1), alpha, beta)
+        g = gather_mapping_backward(gxm, maps[l], acts[l].shape[1])
+    return conv_fold(g, shape, kernel, stride, padding), grads
+
+
+def grouped_mapping(n_groups: int, input_size: int, output_trees: int, luts_per_tree: int, bits_per_node: int,
+                    seed: int, ensure_full_coverage: bool) -> torch.Tensor:
+    """Index map whose rows stay inside one input group.  layer_config.py:157-215, same generator calls."""
+    total = output_trees * luts_per_tree
+    size = input_size // n_groups
+    state = torch.get_rng_state()
+    torch.manual_seed(seed)
+    idx = torch.multinomial(torch.ones((total, size)), num_samples=bits_per_node, replacement=bits_per_node > size)
+    if not ensure_full_coverage:
+        offs = torch.randint(low=0, high=n_groups, size=(total, 1)) * size
+    else:
+        full, rem = divmod(total, n_groups)
+        parts = [torch.randperm(n_groups) for _ in range(full)]
+        if rem > 0:
+            parts.append(torch.multinomial(torch.ones((n_groups,)), num_samples=rem, replacement=False))
+        offs = torch.cat(parts).unsqueeze(1) * size
+    torch.set_rng_state(state)
+    return idx + offs
+
+
+# ----------------------------------------------------------------------------------
 # Whole-network helpers (configs of the benchmark)
 # ----------------------------------------------------------------------------------
 

@@ -309,6 +309,59 @@ def main():
         out[f"{tag}_y_eval"] = _np(layer(xb)).astype(np.uint8)
     np.savez_compressed(os.path.join(HERE, "hybrid_layer.npz"), **out)
 
+    # ---------------------------------------------------------------- convolutional layer fwd+bwd
+    from difflut.layers import ConvolutionalLayer, ConvolutionConfig, GroupedInputConfig
+    from difflut.nodes import ProbabilisticNode as _Prob
+
+    out = {}
+    cases = (
+        # tag, node, B, C, H, W, k, stride, pad, trees, depth, n, chunk, grouped, binary input
+        ("dwn_d2", DWNNode, 2, 2, 6, 6, 3, 1, 0, 3, 2, 3, 2, False, False),
+        ("dwn_s2p1_grouped", DWNNode, 2, 3, 7, 6, 3, 2, 1, 4, 1, 2, 32, True, True),
+        ("prob_d2", _Prob, 2, 2, 5, 5, 2, 1, 0, 3, 2, 2, 2, False, False),
+    )
+    for tag, node_cls, B, C, H, W, k, stride, pad, trees, depth, n, chunk, grouped, binary in cases:
+        g = torch.Generator().manual_seed(len(tag))
+        x = torch.rand(B, C, H, W, generator=g)
+        if binary:
+            x = (x >= 0.5).float()
+        x.requires_grad_(True)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            conv = ConvolutionalLayer(
+                ConvolutionConfig(tree_depth=depth, in_channels=C, out_channels=trees, receptive_field=k,
+                                  stride=stride, padding=pad, chunk_size=chunk, seed=7),
+                node_cls, NodeConfig(input_dim=n, output_dim=1), RandomLayer, n_inputs_per_node=n,
+                grouped_connections=grouped, ensure_full_coverage=grouped)
+        levels = [list(conv.first_layer_chunks)] + [[tree[l] for tree in conv.trees] for l in range(depth)]
+        pname = "luts" if node_cls is DWNNode else "raw_weights"
+        with torch.no_grad():
+            for level in levels:
+                for layer in level:
+                    for node in layer.nodes:
+                        getattr(node, pname).copy_(torch.randn(getattr(node, pname).shape, generator=g))
+        conv.train()
+        y = conv(x)
+        gy = torch.randn(y.shape, generator=g)
+        y.backward(gy)
+        out[f"{tag}_x"] = _np(x)
+        out[f"{tag}_y"] = _np(y)
+        out[f"{tag}_gy"] = _np(gy)
+        out[f"{tag}_gx"] = _np(x.grad)
+        out[f"{tag}_cfg"] = np.array([k, stride, pad, trees, depth, n, chunk, int(grouped)], dtype=np.int64)
+        for li, level in enumerate(levels):
+            out[f"{tag}_map{li}"] = _np(torch.cat([layer._mapping_indices.long() for layer in level]))
+            out[f"{tag}_par{li}"] = _np(torch.stack([getattr(nd, pname) for layer in level for nd in layer.nodes]))
+            out[f"{tag}_gpar{li}"] = _np(torch.stack([getattr(nd, pname).grad for layer in level for nd in layer.nodes]))
+        conv.eval()
+        xb = (x.detach() >= 0.5).float()
+        out[f"{tag}_y_eval"] = _np(conv(xb)).astype(np.uint8)
+    for tag, cover in (("cover", True), ("free", False)):
+        gi = GroupedInputConfig(n_groups=3, input_size=27, output_trees=5, luts_per_tree=6, bits_per_node=4,
+                                seed=11, ensure_full_coverage=cover)
+        out[f"grouped_{tag}"] = _np(gi.mapping_indices)
+    np.savez_compressed(os.path.join(HERE, "conv_layer.npz"), **out)
+
     # ---------------------------------------------------------------- GroupSum known answers
     out = {}
     g = torch.Generator().manual_seed(9)

@@ -221,3 +221,71 @@ def test_thermometer_fit_variants_match_reference(golden):
         assert torch.equal(enc.thresholds, torch.from_numpy(g[f"{tag}_thr"]))
     assert difflut.REGISTRY.get_encoder("gaussian_thermometer") is GaussianThermometerEncoder
     assert difflut.REGISTRY.get_encoder("distributive_thermometer") is DistributiveThermometerEncoder
+
+
+def test_new_node_types_registered_and_stacked():
+    from difflut_b200.nodes import DWNStableNode, HybridNode
+
+    R = difflut.REGISTRY
+    assert R.get_node("dwn_stable") is DWNStableNode and R.get_node("hybrid") is HybridNode
+    stable = RandomLayer(12, 5, DWNStableNode, NodeConfig(input_dim=3, output_dim=2,
+                                                          extra_params={"gradient_scale": 0.8}), seed=1)
+    assert stable.raw_luts.shape == (5, 2, 8) and stable.gradient_scale.shape == (5,)
+    assert float(stable.gradient_scale[3]) == pytest.approx(0.8)
+    assert stable.nodes[2].raw_luts.shape == (2, 8)
+    sd = stable.state_dict()
+    assert {"nodes.4.raw_luts", "nodes.4.gradient_scale", "_mapping_indices"} <= set(sd)
+    assert "raw_luts" not in sd and "gradient_scale" not in sd
+    other = RandomLayer(12, 5, DWNStableNode, NodeConfig(input_dim=3, output_dim=2), seed=1)
+    other.load_state_dict(sd)
+    assert torch.equal(other.raw_luts, stable.raw_luts) and torch.equal(other.gradient_scale, stable.gradient_scale)
+    hybrid = RandomLayer(12, 5, HybridNode, NodeConfig(input_dim=3, output_dim=1), seed=1)
+    assert hybrid.raw_luts.shape == (5, 1, 8)
+    assert hybrid.nodes[0].binary_combinations.tolist()[3] == [1.0, 1.0, 0.0]
+    assert "nodes.0.binary_combinations" in hybrid.state_dict()
+    for cls in (DWNStableNode, HybridNode):
+        with pytest.raises(ValueError):
+            cls(input_dim=7, output_dim=1)
+        node = cls(input_dim=4, output_dim=1)
+        assert node.raw_luts.shape == (1, 16) and float(node.raw_luts.abs().max()) < 1.0  # 0.1 * randn
+
+
+def test_convolutional_layer_structure_matches_reference(golden):
+    from difflut_b200.layers import ConvolutionalLayer, ConvolutionConfig, GroupedInputConfig
+
+    g = golden("conv_layer")
+    assert difflut.REGISTRY.get_convolutional_layer("convolutional") is ConvolutionalLayer
+    for tag, C in (("dwn_d2", 2), ("dwn_s2p1_grouped", 3), ("prob_d2", 2)):
+        k, stride, pad, trees, depth, n, chunk, grouped = (int(v) for v in g[f"{tag}_cfg"])
+        node = ProbabilisticNode if tag.startswith("prob") else DWNNode
+        conv = ConvolutionalLayer(
+            ConvolutionConfig(tree_depth=depth, in_channels=C, out_channels=trees, receptive_field=k,
+                              stride=stride, padding=pad, chunk_size=chunk, seed=7),
+            node, NodeConfig(input_dim=n, output_dim=1), RandomLayer, n_inputs_per_node=n,
+            grouped_connections=bool(grouped), ensure_full_coverage=bool(grouped))
+        assert conv.hidden_layers == [n ** (depth - i) for i in range(depth + 1)]
+        assert len(conv.first_layer_chunks) == -(-trees // min(chunk, trees)) and len(conv.trees) == trees
+        levels = conv._level_layers()
+        for l, level in enumerate(levels):  # the sub-layers' maps are the reference's, bit for bit
+            got = torch.cat([s._mapping_indices.long() for s in level])
+            assert np.array_equal(got.numpy(), g[f"{tag}_map{l}"]), (tag, l)
+        assert conv._mergeable()
+        plans = conv._plans(torch.device("cpu"))
+        assert [p.input_size for p in plans] == [C * k * k] + [h * trees for h in conv.hidden_layers[:-1]]
+        assert int(plans[1].map_nodes[-1].min()) >= (trees - 1) * conv.hidden_layers[0]  # last tree's own block
+        keys = set(conv.state_dict())
+        pname = "raw_weights" if node is ProbabilisticNode else "luts"
+        assert f"first_layer_chunks.0.nodes.0.{pname}" in keys and f"trees.{trees - 1}.0.nodes.0.{pname}" in keys
+    for tag, cover in (("cover", True), ("free", False)):
+        state = torch.get_rng_state()
+        gi = GroupedInputConfig(n_groups=3, input_size=27, output_trees=5, luts_per_tree=6, bits_per_node=4,
+                                seed=11, ensure_full_coverage=cover)
+        assert torch.equal(torch.get_rng_state(), state)
+        assert np.array_equal(gi.mapping_indices.numpy(), g[f"grouped_{tag}"])
+        assert np.array_equal(gi.get_mapping_indices(1, 3).numpy(), g[f"grouped_{tag}"][6:18])
+    with pytest.raises(ValueError):
+        GroupedInputConfig(0, 27, 5, 6, 4, 11)
+    with pytest.raises(AssertionError):
+        ConvolutionConfig(in_channels=None, out_channels=4)
+    with pytest.raises(ValueError):  # wrong rank
+        conv(torch.zeros(2, 5))

@@ -62,7 +62,7 @@ def test_ctypes_signatures_match_header():
     # every compute entry point of the header is bound
     unbound = [n for n in protos if n not in _native.SIGNATURES and n not in (
         "dl_version", "dl_error_string", "dl_padded_batch", "dl_dwn_groupsum_splits", "dl_prob_groupsum_splits",
-        "dl_dwn_bwd_groups")]
+        "dl_dwn_bwd_groups", "dl_unfold_positions")]
     assert not unbound, unbound
 
 
@@ -77,6 +77,10 @@ def test_host_only_helpers(library):
     library.dl_dwn_bwd_groups.restype = ctypes.c_int64
     library.dl_dwn_bwd_groups.argtypes = [ctypes.c_int64]
     assert library.dl_dwn_bwd_groups(8192) == 8 and library.dl_dwn_bwd_groups(128) == 1
+    library.dl_unfold_positions.restype = ctypes.c_int64
+    library.dl_unfold_positions.argtypes = [ctypes.c_int64] * 4
+    assert library.dl_unfold_positions(28, 5, 1, 0) == 24 and library.dl_unfold_positions(28, 3, 2, 1) == 14
+    assert library.dl_unfold_positions(2, 5, 1, 0) == 0
 
 
 def test_missing_library_fails_loudly(monkeypatch):

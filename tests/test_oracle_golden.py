@@ -4,6 +4,7 @@ import hashlib
 import warnings
 
 import numpy as np
+import pytest
 import torch
 
 from oracle import difflut_oracle as O
@@ -102,6 +103,63 @@ def test_hybrid_layer_matches_reference(golden):
         torch.testing.assert_close(gl * tab * (1.0 - tab), T(g[f"{tag}_graw"]), rtol=1e-5, atol=1e-6)
         ye = O.dwn_forward_eval(O.gather_mapping((x >= 0.5).float(), idx), tab)
         assert np.array_equal(ye.reshape(B, -1).numpy().astype(np.uint8), g[f"{tag}_y_eval"])
+
+
+def _conv_case(g, tag):
+    k, stride, pad, trees, depth, n, chunk, grouped = (int(v) for v in g[f"{tag}_cfg"])
+    hidden = [n ** (depth - i) for i in range(depth + 1)]
+    maps = O.conv_level_maps([T(g[f"{tag}_map{l}"]) for l in range(depth + 1)], hidden, trees)
+    pars = [T(g[f"{tag}_par{l}"]) for l in range(depth + 1)]
+    return k, stride, pad, trees, depth, n, chunk, bool(grouped), hidden, maps, pars
+
+
+@pytest.mark.parametrize("tag", ["dwn_d2", "dwn_s2p1_grouped"])
+def test_conv_dwn_matches_reference(golden, tag):
+    g = golden("conv_layer")
+    k, stride, pad, trees, depth, n, _, _, hidden, maps, tables = _conv_case(g, tag)
+    x = T(g[f"{tag}_x"])
+    y_ref = T(g[f"{tag}_y"])
+    B, _, OH, OW = y_ref.shape
+    rows, acts = O.conv_dwn_forward(x, k, stride, pad, maps, tables)
+    assert torch.equal(O.conv_output(rows, B, OH, OW), y_ref)
+    gy = T(g[f"{tag}_gy"])
+    grows = gy.reshape(B, trees, OH * OW).transpose(1, 2).reshape(B * OH * OW, trees)
+    alpha, beta = 0.5 * 0.75 ** (n - 1), 0.25 / 0.75
+    gx, gts = O.conv_dwn_backward(acts, maps, tables, grows, alpha, beta, x.shape, k, stride, pad)
+    torch.testing.assert_close(gx, T(g[f"{tag}_gx"]), rtol=1e-5, atol=1e-6)
+    for l in range(depth + 1):
+        torch.testing.assert_close(gts[l], T(g[f"{tag}_gpar{l}"]), rtol=1e-5, atol=1e-6)
+    rows_e, _ = O.conv_dwn_forward((x >= 0.5).float(), k, stride, pad, maps, tables, eval_mode=True)
+    assert np.array_equal(O.conv_output(rows_e, B, OH, OW).numpy().astype(np.uint8), g[f"{tag}_y_eval"])
+
+
+def test_conv_prob_matches_reference(golden):
+    g = golden("conv_layer")
+    tag = "prob_d2"
+    k, stride, pad, trees, depth, n, _, _, hidden, maps, raws = _conv_case(g, tag)
+    x = T(g[f"{tag}_x"]).requires_grad_(True)
+    raws = [r.clone().requires_grad_(True) for r in raws]
+    y_ref = T(g[f"{tag}_y"])
+    B, _, OH, OW = y_ref.shape
+    h = O.conv_unfold(x, k, stride, pad)
+    for m, r in zip(maps, raws):
+        h = O.prob_forward(O.gather_mapping(h, m), r).reshape(h.shape[0], -1)
+    y = O.conv_output(h, B, OH, OW)
+    torch.testing.assert_close(y, y_ref, rtol=1e-5, atol=1e-6)
+    y.backward(T(g[f"{tag}_gy"]))
+    torch.testing.assert_close(x.grad, T(g[f"{tag}_gx"]), rtol=1e-5, atol=1e-6)
+    for l in range(depth + 1):
+        torch.testing.assert_close(raws[l].grad, T(g[f"{tag}_gpar{l}"]), rtol=1e-5, atol=1e-6)
+
+
+def test_grouped_mapping_exact(golden):
+    g = golden("conv_layer")
+    for tag, cover in (("cover", True), ("free", False)):
+        state = torch.get_rng_state()
+        m = O.grouped_mapping(3, 27, 5, 6, 4, 11, cover)
+        assert torch.equal(torch.get_rng_state(), state)
+        assert np.array_equal(m.numpy(), g[f"grouped_{tag}"])
+        assert bool(((m // 9) == (m[:, :1] // 9)).all())  # a node reads one group only
 
 
 def test_dwn_residual_tables_pass_bit0(golden):
