@@ -244,7 +244,7 @@ def kernel_algorithmic_bytes(net, name):
             total += 4 * g_rows * Bp + I * Bp // 8 + (N * Bp if li > 0 else 0) + 4 * N * 64 + 4 * N * n
         elif name == "dl_dwn_bwd_input_t" and li > 0:
             total += N * Bp + 4 * g_rows * Bp + 4 * N * n * 32 + 4 * I * Bp + 4 * (I + 1) + 4 * N * n
-        elif name == "dl_dwn_bwd_fused_t":
+        elif name in ("dl_dwn_bwd_fused_t", "dl_dwn_bwd_fused_s"):
             G = net.groups
             total += I * Bp // 8 + 4 * N * 64 * G + 4 * N * n  # own input bits, partial table gradients, map
             if li == last:
@@ -257,7 +257,7 @@ def kernel_algorithmic_bytes(net, name):
                     total += 4 * N * Bp + N * Bp  # own output gradient and addresses for the layer below
         elif name == "dl_dwn_fwd_bits_t" and li < last:
             total += I * Bp // 8 + N * Bp // 8 + 8 * N + 4 * N * n
-        elif name == "dl_dwn_fwd_groupsum_t" and li == last:
+        elif name in ("dl_dwn_fwd_groupsum_t", "dl_dwn_fwd_groupsum_s") and li == last:
             total += I * Bp // 8 + 4 * k * Bp + 4 * N * 64 + 4 * N * n
     return total
 
@@ -399,7 +399,7 @@ def run_gpu_arm(args):
             "bound": "hbm", "kernel": top_name, "launches_per_step": top_info["launches"],
             "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
             "frac": achieved / peak,
-            "traffic": (NCU_TRAFFIC_BWD_FUSED_B8192 * B / 8192.0) if top_name == "dl_dwn_bwd_fused_t" else None,
+            "traffic": (NCU_TRAFFIC_BWD_FUSED_B8192 * B / 8192.0) if top_name in ("dl_dwn_bwd_fused_t", "dl_dwn_bwd_fused_s") else None,
             "algorithmic_bytes_per_launch_set": alg, "kernel_ms_per_step": top_info["ms"],
             "step_achieved_gbs": step_alg / (ms_per_step * 1e-3) / 1e9 * (1 if world == 1 else 1),
             "step_algorithmic_bytes": step_alg,

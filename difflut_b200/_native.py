@@ -56,6 +56,9 @@ SIGNATURES = {
     "dl_groupsum_rows_bwd": "pplllf s",
     "dl_groupsum_t": "ppllfl s",
     "dl_dwn_fwd_groupsum_t": "ppppplllfl s",
+    "dl_dwn_fwd_groupsum_s": "ppppplllfl s",
+    "dl_dwn_bwd_fused_s": "pplfplpppppppllll s",
+    "dl_bits_swizzle_t": "ppll s",
     "dl_dwn_fwd_groupsum_noalloc_t": "pppplllfl s",
     "dl_popcount_groupsum_t": "ppllll s",
     "dl_ce_t": "pppppllll s",
@@ -98,6 +101,8 @@ def lib():
     handle.dl_dwn_bwd_groups.argtypes = [ctypes.c_int64]
     handle.dl_prob_groupsum_splits.restype = ctypes.c_int64
     handle.dl_prob_groupsum_splits.argtypes = [ctypes.c_int64, ctypes.c_int64]
+    handle.dl_swizzled_words.restype = ctypes.c_int64
+    handle.dl_swizzled_words.argtypes = [ctypes.c_int64]
     handle.dl_unfold_positions.restype = ctypes.c_int64
     handle.dl_unfold_positions.argtypes = [ctypes.c_int64] * 4
     _lib = handle

@@ -269,13 +269,14 @@ dwn_fwd_vals_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __restr
 // in a fixed order.  For each node lane w loads word w of the node's 6 input rows (coalesced), the 8
 // chunks of the group get their words by shuffle, and 32 running sums (8 chunks x 4 samples) stay
 // in registers; the next node's words are loaded before the current node is consumed.
+// SWZ: chunk-interleaved input bits (see dl_bits_swizzle_t): the lane's own word holds its samples.
+template <bool SWZ>
 __global__ void __launch_bounds__(128)
 dwn_fwd_groupsum_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __restrict__ map,
                         const float* __restrict__ tables, float* __restrict__ partial, int64_t N,
-                        int n, int64_t gsz, int S, int64_t Bp) {
+                        int n, int64_t gsz, int S, int64_t Bp, int64_t Wp) {
     __shared__ float4 red[3][8][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int64_t Wp = Bp >> 5;
     const int L = 1 << n;
     const int64_t grp = blockIdx.x;  // 1024-sample group
     const int64_t cls = blockIdx.y / (unsigned)S, s = blockIdx.y % (unsigned)S;
@@ -311,8 +312,13 @@ dwn_fwd_groupsum_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __r
 #pragma unroll
             for (int i = 0; i < DL_MAX_FAST_N; ++i) {
                 if (i < n) {
-                    const uint32_t t = __shfl_sync(0xffffffffu, words[i], c * 4 + src_lane) >> sh;
-                    a |= dl_spread_nibble(t & 0xFu) << i;
+                    if (SWZ) {
+                        const uint32_t t = c >= i ? words[i] >> (c - i) : words[i] << (i - c);
+                        a |= t & (0x01010101u << i);
+                    } else {
+                        const uint32_t t = __shfl_sync(0xffffffffu, words[i], c * 4 + src_lane) >> sh;
+                        a |= dl_spread_nibble(t & 0xFu) << i;
+                    }
                 }
             }
             acc[c].x += __ldg(tj + (a & 0xFF));
@@ -475,10 +481,13 @@ __device__ __forceinline__ void efd_accumulate(float4& acc, const float4 g, cons
 // Data one chunk needs from the layer above: CNT (address word, gradient float4) pairs, or one
 // gradient float4 in DIRECT mode.  Loads are issued unconditionally (no branch between them) so that
 // they overlap; the next chunk's loads are issued before the current chunk is consumed.
+// CNT = 0..3: exactly that many readers, all in registers; CNT = 4: three in registers plus `extra`
+// more walked through the inverse map; CNT = 5: none in registers, all `extra` readers walked.
 template <int CNT>
 struct ChunkData {
-    uint32_t a[CNT > 0 ? CNT : 1];
-    float4 g[CNT > 0 ? CNT : 1];
+    static constexpr int REG = CNT == 5 ? 0 : (CNT > FUSED_MAX_REG_CONTRIB ? FUSED_MAX_REG_CONTRIB : CNT);
+    uint32_t a[REG > 0 ? REG : 1];
+    float4 g[REG > 0 ? REG : 1];
 };
 
 template <bool DIRECT, int CNT>
@@ -489,7 +498,7 @@ __device__ __forceinline__ void load_chunk(ChunkData<CNT>& d, int c, const float
         d.g[0] = __ldg(reinterpret_cast<const float4*>(gdir + c * 128));
     } else {
 #pragma unroll
-        for (int k = 0; k < CNT; ++k) {
+        for (int k = 0; k < ChunkData<CNT>::REG; ++k) {
             d.a[k] = __ldg(reinterpret_cast<const uint32_t*>(ap[k] + c * 128));
             d.g[k] = __ldg(reinterpret_cast<const float4*>(gp[k] + c * 128));
         }
@@ -498,7 +507,11 @@ __device__ __forceinline__ void load_chunk(ChunkData<CNT>& d, int c, const float
 
 // Everything chunk c does once its data is in registers: output gradient, own addresses, stores,
 // histogram update.  NIN is the compile-time node input count (0 = use the runtime value n).
-template <bool DIRECT, int CNT, int NIN>
+// SWZ: the input bits are in the chunk-interleaved layout (bit c + 8r of word w of a 1024-sample
+// block = sample 128c + 4w + r), so the lane's own word already holds its four samples of chunk c one
+// per byte and an address bit costs a shift and a masked or.  OUTS: bit 0 = store the output gradient,
+// bit 1 = store the addresses (-1: decide at run time from the pointers).
+template <bool DIRECT, int CNT, int NIN, bool SWZ, int OUTS>
 __device__ __forceinline__ void consume_chunk(
     const ChunkData<CNT>& d, int c, int n, int extra, int src_lane, int sh, float gscale,
     const uint32_t (&words)[DL_MAX_FAST_N], const float (&tv)[FUSED_MAX_REG_CONTRIB],
@@ -512,7 +525,8 @@ __device__ __forceinline__ void consume_chunk(
         acc.x *= gscale; acc.y *= gscale; acc.z *= gscale; acc.w *= gscale;
     } else {
 #pragma unroll
-        for (int k = 0; k < CNT; ++k) efd_accumulate(acc, d.g[k], d.a[k], lowm[k], tv[k]);
+        for (int k = 0; k < ChunkData<CNT>::REG; ++k) efd_accumulate(acc, d.g[k], d.a[k], lowm[k], tv[k]);
+        if (CNT > FUSED_MAX_REG_CONTRIB)
         for (int k = 0; k < extra; ++k) {  // rare: more readers than registers
             const int ent = __ldg(&inv_ent[e_tail + k]);
             const int j = ent >> 3, i = ent & 7;
@@ -529,12 +543,17 @@ __device__ __forceinline__ void consume_chunk(
 #pragma unroll
     for (int i = 0; i < DL_MAX_FAST_N; ++i) {
         if (NIN > 0 ? i < NIN : i < n) {
-            const uint32_t t = __shfl_sync(0xffffffffu, words[i], c * 4 + src_lane) >> sh;
-            a |= dl_spread_nibble(t & 0xFu) << i;
+            if (SWZ) {
+                const uint32_t t = c >= i ? words[i] >> (c - i) : words[i] << (i - c);
+                a |= t & (0x01010101u << i);
+            } else {
+                const uint32_t t = __shfl_sync(0xffffffffu, words[i], c * 4 + src_lane) >> sh;
+                a |= dl_spread_nibble(t & 0xFu) << i;
+            }
         }
     }
-    if (go != nullptr) *reinterpret_cast<float4*>(go + c * 128) = acc;
-    if (ao != nullptr) *reinterpret_cast<uint32_t*>(ao + c * 128) = a;
+    if (OUTS < 0 ? go != nullptr : (OUTS & 1) != 0) *reinterpret_cast<float4*>(go + c * 128) = acc;
+    if (OUTS < 0 ? ao != nullptr : (OUTS & 2) != 0) *reinterpret_cast<uint32_t*>(ao + c * 128) = a;
     // bin e of this lane lives at float offset e*32: byte offset e << 7
     char* base = reinterpret_cast<char*>(mine);
     *reinterpret_cast<float*>(base + ((a << 7) & 0x1F80u)) += acc.x;
@@ -549,7 +568,7 @@ __device__ __forceinline__ void consume_chunk(
 // The chunks of one (group, node) item for a node with exactly CNT readers held in registers.
 // FULL: all 8 chunks exist; they are processed as 4 unrolled pairs with two register buffers
 // (ping-pong), so the loads of chunk c+1 fly while chunk c is consumed and nothing is copied.
-template <bool DIRECT, int CNT, int NIN, bool FULL>
+template <bool DIRECT, int CNT, int NIN, bool FULL, bool SWZ, int OUTS>
 __device__ __forceinline__ void fused_chunks(
     int valid_chunks, int n, int extra, int src_lane, int sh, float gscale, const uint32_t (&words)[DL_MAX_FAST_N],
     const float* __restrict__ gdir, const uint8_t* const (&ap)[FUSED_MAX_REG_CONTRIB],
@@ -564,34 +583,35 @@ __device__ __forceinline__ void fused_chunks(
 #pragma unroll
         for (int c = 0; c < FUSED_CG; c += 2) {
             load_chunk<DIRECT, CNT>(odd, c + 1, gdir, ap, gp);
-            consume_chunk<DIRECT, CNT, NIN>(even, c, DL_CONSUME_ARGS);
+            consume_chunk<DIRECT, CNT, NIN, SWZ, OUTS>(even, c, DL_CONSUME_ARGS);
             if (c + 2 < FUSED_CG) load_chunk<DIRECT, CNT>(even, c + 2, gdir, ap, gp);
-            consume_chunk<DIRECT, CNT, NIN>(odd, c + 1, DL_CONSUME_ARGS);
+            consume_chunk<DIRECT, CNT, NIN, SWZ, OUTS>(odd, c + 1, DL_CONSUME_ARGS);
         }
     } else {
         for (int c = 0; c < valid_chunks; ++c) {
             ChunkData<CNT> d;
             load_chunk<DIRECT, CNT>(d, c, gdir, ap, gp);
-            consume_chunk<DIRECT, CNT, NIN>(d, c, DL_CONSUME_ARGS);
+            consume_chunk<DIRECT, CNT, NIN, SWZ, OUTS>(d, c, DL_CONSUME_ARGS);
         }
     }
 }
 #undef DL_CONSUME_ARGS
 
-template <bool DIRECT, int NIN>
+template <bool DIRECT, int NIN, bool SWZ, int OUTS>
 __global__ void __launch_bounds__(HIST_WARPS * 32, 5)
 dwn_bwd_fused_kernel(const uint8_t* __restrict__ addr_up, const float* __restrict__ g_up, int64_t gdiv_up,
                      float gscale_up, const float* __restrict__ efd_up, int n_up,
                      const int32_t* __restrict__ inv_ptr, const int32_t* __restrict__ inv_ent,
                      const uint32_t* __restrict__ in_bits, const int32_t* __restrict__ map,
                      float* __restrict__ g_out, uint8_t* __restrict__ addr_out,
-                     float* __restrict__ gt_partial, int64_t group_stride, int64_t N, int n_rt, int64_t Bp) {
+                     float* __restrict__ gt_partial, int64_t group_stride, int64_t N, int n_rt, int64_t Bp,
+                     int64_t Wp) {
     __shared__ __align__(16) float hist_all[HIST_WARPS][64 * 32];
     const int n = NIN > 0 ? NIN : n_rt;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float* hist = hist_all[warp];      // hist[e * 32 + lane]: bin e, private to the lane
     float* mine = hist + lane;
-    const int64_t C = Bp >> 7, Wp = Bp >> 5;
+    const int64_t C = Bp >> 7;  // Wp: words per input row (Bp/32, or 32 per 1024-sample block when SWZ)
     const int64_t G = (C + FUSED_CG - 1) / FUSED_CG;
     const int L = 1 << n;
     const int64_t nwarps = (int64_t)gridDim.x * HIST_WARPS;
@@ -650,22 +670,25 @@ dwn_bwd_fused_kernel(const uint8_t* __restrict__ addr_up, const float* __restric
                               inv_ent, e0 + FUSED_MAX_REG_CONTRIB, addr_up, g_up, efd_up, n_up, ugdiv, Bp, b0, go, ao, mine
             if (valid_chunks == FUSED_CG) {
                 if (DIRECT) {
-                    fused_chunks<true, 0, NIN, true>(DL_FUSED_ARGS(0));
+                    fused_chunks<true, 0, NIN, true, SWZ, OUTS>(DL_FUSED_ARGS(0));
                 } else {
                     switch (cnt) {  // uniform over the warp
-                        case 0: fused_chunks<false, 0, NIN, true>(DL_FUSED_ARGS(0)); break;
-                        case 1: fused_chunks<false, 1, NIN, true>(DL_FUSED_ARGS(0)); break;
-                        case 2: fused_chunks<false, 2, NIN, true>(DL_FUSED_ARGS(0)); break;
-                        default: fused_chunks<false, 3, NIN, true>(DL_FUSED_ARGS(cnt - FUSED_MAX_REG_CONTRIB)); break;
+                        case 0: fused_chunks<false, 0, NIN, true, SWZ, OUTS>(DL_FUSED_ARGS(0)); break;
+                        case 1: fused_chunks<false, 1, NIN, true, SWZ, OUTS>(DL_FUSED_ARGS(0)); break;
+                        case 2: fused_chunks<false, 2, NIN, true, SWZ, OUTS>(DL_FUSED_ARGS(0)); break;
+                        case 3: fused_chunks<false, 3, NIN, true, SWZ, OUTS>(DL_FUSED_ARGS(0)); break;
+                        default:
+                            fused_chunks<false, 4, NIN, true, SWZ, OUTS>(DL_FUSED_ARGS(cnt - FUSED_MAX_REG_CONTRIB));
+                            break;
                     }
                 }
             } else if (DIRECT) {
-                fused_chunks<true, 0, NIN, false>(DL_FUSED_ARGS(0));
+                fused_chunks<true, 0, NIN, false, SWZ, -1>(DL_FUSED_ARGS(0));
             } else {
                 // ragged last group: one generic body, every reader walked through the inverse map
-                fused_chunks<false, 0, NIN, false>(valid_chunks, n, cnt, src_lane, sh, gscale_up, words, gdir, ap, gp,
-                                                   tv_r, lowm_r, inv_ent, e0, addr_up, g_up, efd_up, n_up, ugdiv, Bp,
-                                                   b0, go, ao, mine);
+                fused_chunks<false, 5, NIN, false, SWZ, -1>(valid_chunks, n, cnt, src_lane, sh, gscale_up, words, gdir,
+                                                            ap, gp, tv_r, lowm_r, inv_ent, e0, addr_up, g_up, efd_up,
+                                                            n_up, ugdiv, Bp, b0, go, ao, mine);
             }
 #undef DL_FUSED_ARGS
             __syncwarp();
@@ -918,10 +941,10 @@ DL_EXPORT int64_t dl_dwn_groupsum_splits(int64_t N, int64_t k) {
     return s;
 }
 
-DL_EXPORT int dl_dwn_fwd_groupsum_t(const uint32_t* in_bits_t, const int32_t* map, const float* tables,
-                                    float* partial, float* logits_t, int64_t N, int64_t n, int64_t k,
-                                    float tau, int64_t Bp, dl_stream_t stream) {
-    DL_REQUIRE(in_bits_t && map && tables && partial && logits_t && N > 0 && k > 0 && tau > 0.f);
+static int fwd_groupsum_entry(bool swz, const uint32_t* in_bits, const int32_t* map, const float* tables,
+                             float* partial, float* logits_t, int64_t N, int64_t n, int64_t k, float tau,
+                             int64_t Bp, dl_stream_t stream) {
+    DL_REQUIRE(in_bits && map && tables && partial && logits_t && N > 0 && k > 0 && tau > 0.f);
     DL_REQUIRE(Bp > 0 && Bp % DL_BATCH_ALIGN == 0);
     DL_REQUIRE_ALIGNED(partial, 16);
     if (n < 1 || n > DL_MAX_FAST_N) return DL_ERR_UNSUPPORTED;
@@ -929,12 +952,28 @@ DL_EXPORT int dl_dwn_fwd_groupsum_t(const uint32_t* in_bits_t, const int32_t* ma
     const int64_t gsz = dl_ceil_div(N, k);
     DL_REQUIRE(k * S <= 65535);
     dim3 grid((unsigned)dl_ceil_div(Bp, 1024), (unsigned)(k * S));
-    dwn_fwd_groupsum_kernel<<<grid, 128, 0, dl_cast(stream)>>>(in_bits_t, map, tables, partial, N, (int)n,
-                                                              gsz, S, Bp);
+    if (swz)
+        dwn_fwd_groupsum_kernel<true><<<grid, 128, 0, dl_cast(stream)>>>(in_bits, map, tables, partial, N, (int)n, gsz,
+                                                                        S, Bp, dl_swizzled_words(Bp));
+    else
+        dwn_fwd_groupsum_kernel<false><<<grid, 128, 0, dl_cast(stream)>>>(in_bits, map, tables, partial, N, (int)n,
+                                                                         gsz, S, Bp, Bp / 32);
     if (cudaPeekAtLastError() != cudaSuccess) return DL_ERR_LAUNCH;
     groupsum_reduce_kernel<<<grid_for(k * Bp, 256), 256, 0, dl_cast(stream)>>>(partial, logits_t, (int)k, S,
                                                                             1.0f / tau, Bp);
     return dl_launch_status();
+}
+
+DL_EXPORT int dl_dwn_fwd_groupsum_t(const uint32_t* in_bits_t, const int32_t* map, const float* tables,
+                                    float* partial, float* logits_t, int64_t N, int64_t n, int64_t k,
+                                    float tau, int64_t Bp, dl_stream_t stream) {
+    return fwd_groupsum_entry(false, in_bits_t, map, tables, partial, logits_t, N, n, k, tau, Bp, stream);
+}
+
+DL_EXPORT int dl_dwn_fwd_groupsum_s(const uint32_t* in_bits_s, const int32_t* map, const float* tables,
+                                    float* partial, float* logits_t, int64_t N, int64_t n, int64_t k,
+                                    float tau, int64_t Bp, dl_stream_t stream) {
+    return fwd_groupsum_entry(true, in_bits_s, map, tables, partial, logits_t, N, n, k, tau, Bp, stream);
 }
 
 DL_EXPORT int dl_dwn_fwd_groupsum_noalloc_t(const uint32_t* in_bits_t, const int32_t* map, const float* tables,
@@ -985,11 +1024,39 @@ DL_EXPORT int64_t dl_dwn_bwd_groups(int64_t Bp) {
     return Bp <= 0 ? 0 : dl_ceil_div(Bp / 128, FUSED_CG);
 }
 
-DL_EXPORT int dl_dwn_bwd_fused_t(const uint8_t* addr_up, const float* g_up, int64_t gdiv_up, float gscale_up,
-                                 const float* efd_up, int64_t n_up, const int32_t* inv_ptr,
-                                 const int32_t* inv_ent, const uint32_t* in_bits_t, const int32_t* map,
-                                 float* g_out, uint8_t* addr_out, float* gt_partial, int64_t group_stride,
-                                 int64_t N, int64_t n, int64_t Bp, dl_stream_t stream) {
+namespace {
+
+template <bool D, int NN, bool SWZ>
+void launch_fused_outs(unsigned blocks, cudaStream_t s, const uint8_t* addr_up, const float* g_up, int64_t gdiv_up,
+                       float gscale_up, const float* efd_up, int n_up, const int32_t* inv_ptr, const int32_t* inv_ent,
+                       const uint32_t* in_bits, const int32_t* map, float* g_out, uint8_t* addr_out, float* gt_partial,
+                       int64_t group_stride, int64_t N, int n, int64_t Bp, int64_t Wp) {
+#define DL_LAUNCH_FUSED(OUTS)                                                                                         \
+    do {                                                                                                              \
+        /* largest shared-memory carve-out, so that 5 CTAs (5 x 32 KB of histograms) fit per SM */                    \
+        cudaFuncSetAttribute(dwn_bwd_fused_kernel<D, NN, SWZ, OUTS>, cudaFuncAttributePreferredSharedMemoryCarveout,  \
+                             100);                                                                                    \
+        dwn_bwd_fused_kernel<D, NN, SWZ, OUTS><<<blocks, HIST_WARPS * 32, 0, s>>>(                                     \
+            addr_up, g_up, gdiv_up, gscale_up, efd_up, n_up, inv_ptr, inv_ent, in_bits, map, g_out, addr_out,         \
+            gt_partial, group_stride, N, n, Bp, Wp);                                                                  \
+    } while (0)
+    if (NN == 0) {  // generic input count: pointers checked at run time
+        DL_LAUNCH_FUSED(-1);
+        return;
+    }
+    switch ((g_out ? 1 : 0) | (addr_out ? 2 : 0)) {
+        case 0: DL_LAUNCH_FUSED(0); break;
+        case 1: DL_LAUNCH_FUSED(1); break;
+        case 2: DL_LAUNCH_FUSED(2); break;
+        default: DL_LAUNCH_FUSED(3); break;
+    }
+#undef DL_LAUNCH_FUSED
+}
+
+int bwd_fused_entry(bool swz, const uint8_t* addr_up, const float* g_up, int64_t gdiv_up, float gscale_up,
+                    const float* efd_up, int64_t n_up, const int32_t* inv_ptr, const int32_t* inv_ent,
+                    const uint32_t* in_bits_t, const int32_t* map, float* g_out, uint8_t* addr_out, float* gt_partial,
+                    int64_t group_stride, int64_t N, int64_t n, int64_t Bp, dl_stream_t stream) {
     DL_REQUIRE(g_up && in_bits_t && map && gt_partial && N > 0 && gdiv_up > 0);
     DL_REQUIRE(Bp > 0 && Bp % DL_BATCH_ALIGN == 0 && group_stride >= N * ((int64_t)1 << n));
     DL_REQUIRE_ALIGNED(g_up, 16);
@@ -1009,22 +1076,40 @@ DL_EXPORT int dl_dwn_bwd_fused_t(const uint8_t* addr_up, const float* g_up, int6
     const int64_t cap = (int64_t)DL_NUM_SMS * 5;
     const int64_t blocks64 = dl_ceil_div(N, HIST_WARPS);
     const unsigned blocks = (unsigned)(blocks64 < cap ? blocks64 : cap);
+    const int64_t Wp = swz ? dl_swizzled_words(Bp) : Bp / 32;
     cudaStream_t s = dl_cast(stream);
-#define DL_LAUNCH_FUSED(D, NN)                                                                                        \
-    do {                                                                                                              \
-        /* largest shared-memory carve-out, so that 5 CTAs (5 x 32 KB of histograms) fit per SM */                    \
-        cudaFuncSetAttribute(dwn_bwd_fused_kernel<D, NN>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);        \
-        dwn_bwd_fused_kernel<D, NN><<<blocks, HIST_WARPS * 32, 0, s>>>(                                                \
-            addr_up, g_up, gdiv_up, gscale_up, efd_up, (int)n_up, inv_ptr, inv_ent, in_bits_t, map, g_out, addr_out,   \
-            gt_partial, group_stride, N, (int)n, Bp);                                                                  \
-    } while (0)
-    if (direct) {
-        if (n == 6) DL_LAUNCH_FUSED(true, 6); else DL_LAUNCH_FUSED(true, 0);
+#define DL_FUSED_CALL(D, NN, SWZ)                                                                                     \
+    launch_fused_outs<D, NN, SWZ>(blocks, s, addr_up, g_up, gdiv_up, gscale_up, efd_up, (int)n_up, inv_ptr, inv_ent,  \
+                                  in_bits_t, map, g_out, addr_out, gt_partial, group_stride, N, (int)n, Bp, Wp)
+    if (swz) {
+        if (direct) { if (n == 6) DL_FUSED_CALL(true, 6, true); else DL_FUSED_CALL(true, 0, true); }
+        else { if (n == 6) DL_FUSED_CALL(false, 6, true); else DL_FUSED_CALL(false, 0, true); }
     } else {
-        if (n == 6) DL_LAUNCH_FUSED(false, 6); else DL_LAUNCH_FUSED(false, 0);
+        if (direct) { if (n == 6) DL_FUSED_CALL(true, 6, false); else DL_FUSED_CALL(true, 0, false); }
+        else { if (n == 6) DL_FUSED_CALL(false, 6, false); else DL_FUSED_CALL(false, 0, false); }
     }
-#undef DL_LAUNCH_FUSED
+#undef DL_FUSED_CALL
     return dl_launch_status();
+}
+
+}  // namespace
+
+DL_EXPORT int dl_dwn_bwd_fused_t(const uint8_t* addr_up, const float* g_up, int64_t gdiv_up, float gscale_up,
+                                 const float* efd_up, int64_t n_up, const int32_t* inv_ptr,
+                                 const int32_t* inv_ent, const uint32_t* in_bits_t, const int32_t* map,
+                                 float* g_out, uint8_t* addr_out, float* gt_partial, int64_t group_stride,
+                                 int64_t N, int64_t n, int64_t Bp, dl_stream_t stream) {
+    return bwd_fused_entry(false, addr_up, g_up, gdiv_up, gscale_up, efd_up, n_up, inv_ptr, inv_ent, in_bits_t, map,
+                           g_out, addr_out, gt_partial, group_stride, N, n, Bp, stream);
+}
+
+DL_EXPORT int dl_dwn_bwd_fused_s(const uint8_t* addr_up, const float* g_up, int64_t gdiv_up, float gscale_up,
+                                 const float* efd_up, int64_t n_up, const int32_t* inv_ptr,
+                                 const int32_t* inv_ent, const uint32_t* in_bits_s, const int32_t* map,
+                                 float* g_out, uint8_t* addr_out, float* gt_partial, int64_t group_stride,
+                                 int64_t N, int64_t n, int64_t Bp, dl_stream_t stream) {
+    return bwd_fused_entry(true, addr_up, g_up, gdiv_up, gscale_up, efd_up, n_up, inv_ptr, inv_ent, in_bits_s, map,
+                           g_out, addr_out, gt_partial, group_stride, N, n, Bp, stream);
 }
 
 DL_EXPORT int dl_sum_groups(const float* partial, float* out, int64_t count, int64_t stride, int64_t groups,

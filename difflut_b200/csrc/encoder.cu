@@ -55,6 +55,30 @@ pack_t_kernel(const float* __restrict__ x, const float* __restrict__ thr, float 
     }
 }
 
+// Natural feature-major bits -> chunk-interleaved layout used by the stack kernels.  Per 1024-sample
+// block a row has 32 words; word w, bit c + 8r holds sample 128c + 4w + r of the block (c = 0..7 the
+// 128-sample chunk, r = 0..3).  A warp owns one (row, block): lane w reads natural word w (coalesced),
+// then collects nibble (w % 8) of natural word 4c + w/8 for every c and spreads it over the bytes.
+__global__ void __launch_bounds__(256)
+bits_swizzle_kernel(const uint32_t* __restrict__ nat, uint32_t* __restrict__ swz, int64_t F, int64_t Wp,
+                    int64_t G) {
+    const int lane = threadIdx.x & 31;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int src = lane >> 3, sh = (lane & 7) * 4;
+    for (int64_t item = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; item < F * G; item += nwarps) {
+        const int64_t f = item / G, g = item - f * G;
+        const int64_t w = g * 32 + lane;
+        const uint32_t mine = w < Wp ? __ldg(nat + f * Wp + w) : 0u;
+        uint32_t out = 0;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const uint32_t t = __shfl_sync(0xffffffffu, mine, c * 4 + src) >> sh;
+            out |= dl_spread_nibble(t & 0xFu) << c;
+        }
+        swz[(f * G + g) * 32 + lane] = out;
+    }
+}
+
 // rows in, fp32 rows out: out[b, f*T+t] = x[b,f] > thr[f,t]
 __global__ void thermo_rows_kernel(const float* __restrict__ x, const float* __restrict__ thr,
                                    float* __restrict__ out, int64_t B, int64_t F, int T) {
@@ -201,6 +225,17 @@ DL_EXPORT int dl_thermo_pack_t(const float* x, const float* thr, uint32_t* bits_
     dim3 grid((unsigned)dl_ceil_div(Bp, TILE_B), (unsigned)dl_ceil_div(F, TILE_F));
     pack_t_kernel<0><<<grid, PACK_THREADS, 0, dl_cast(stream)>>>(x, thr, 0.f, bits_t, B, F, (int)T,
                                                                 Bp / 32);
+    return dl_launch_status();
+}
+
+DL_EXPORT int64_t dl_swizzled_words(int64_t Bp) { return Bp <= 0 ? 0 : dl_ceil_div(Bp, 1024) * 32; }
+
+DL_EXPORT int dl_bits_swizzle_t(const uint32_t* bits_t, uint32_t* bits_s, int64_t F, int64_t Bp,
+                                dl_stream_t stream) {
+    DL_REQUIRE(bits_t && bits_s && bits_t != bits_s && F > 0 && Bp > 0 && Bp % DL_BATCH_ALIGN == 0);
+    const int64_t G = dl_ceil_div(Bp, 1024);
+    const int64_t blocks = dl_min64(dl_ceil_div(F * G, 8), (int64_t)DL_NUM_SMS * 16);
+    bits_swizzle_kernel<<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(bits_t, bits_s, F, Bp / 32, G);
     return dl_launch_status();
 }
 

@@ -49,6 +49,8 @@ class DWNNetwork:
         self.k, self.tau = int(groupsum.k), float(groupsum.tau)
         self.group = process_group
         self.fused_backward = bool(fused_backward)
+        # the fused stack kernels read the activations in the chunk-interleaved bit layout
+        self.swizzle = self.fused_backward
         if distributed is None:
             distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(process_group) > 1
         self.distributed = bool(distributed)
@@ -118,8 +120,13 @@ class DWNNetwork:
         dev = self.device
         if self._B != B:
             Bp = _native.padded_batch(B)
-            Wp = Bp // 32
             self.Bp = Bp
+            # interleaved rows are whole 1024-sample blocks; the natural-layout kernels (hard inference)
+            # use the same buffers with Bp/32 words per row
+            Wp = int(_native.lib().dl_swizzled_words(Bp)) if self.swizzle else Bp // 32
+            self.Bp_bits = Wp * 32
+            self.bits_nat = (torch.empty(self.I[0], Bp // 32, device=dev, dtype=torch.int32)
+                             if self.swizzle else None)
             self.bits = [torch.empty(self.I[0], Wp, device=dev, dtype=torch.int32)]
             for N in self.N[:-1]:
                 self.bits.append(torch.empty(N, Wp, device=dev, dtype=torch.int32))
@@ -162,13 +169,19 @@ class DWNNetwork:
 
     def _forward(self, x: torch.Tensor, B: int) -> None:
         Bp = self.Bp
-        _native.call("dl_thermo_pack_t", x, self.thr, self.bits[0], B, self.F, self.T, Bp)
+        if self.swizzle:
+            _native.call("dl_thermo_pack_t", x, self.thr, self.bits_nat, B, self.F, self.T, Bp)
+            _native.call("dl_bits_swizzle_t", self.bits_nat, self.bits[0], self.I[0], Bp)
+        else:
+            _native.call("dl_thermo_pack_t", x, self.thr, self.bits[0], B, self.F, self.T, Bp)
         last = len(self.layers) - 1
         for li in range(last):
+            # bit-sliced: indifferent to the sample order inside a row, only the row length matters
             _native.call("dl_dwn_fwd_bits_t", self.bits[li], self.plans[li].map_nodes, self.masks[li],
-                         self.bits[li + 1], self.N[li], self.n[li], Bp)
-        _native.call("dl_dwn_fwd_groupsum_t", self.bits[last], self.plans[last].map_nodes, self.tables[last],
-                     self.partial, self.logits_t, self.N[last], self.n[last], self.k, self.tau, Bp)
+                         self.bits[li + 1], self.N[li], self.n[li], self.Bp_bits)
+        _native.call("dl_dwn_fwd_groupsum_s" if self.swizzle else "dl_dwn_fwd_groupsum_t", self.bits[last],
+                     self.plans[last].map_nodes, self.tables[last], self.partial, self.logits_t, self.N[last],
+                     self.n[last], self.k, self.tau, Bp)
 
     def _backward(self) -> None:
         if self.fused_backward:
@@ -196,11 +209,12 @@ class DWNNetwork:
         total = self.flat.numel()
         # with a single group the "partial" gradient is the gradient: write it in place
         direct = self.distributed and self.groups == 1
+        fused = "dl_dwn_bwd_fused_s" if self.swizzle else "dl_dwn_bwd_fused_t"
         self._pending = []
         for li in range(last, -1, -1):
             partial = self.flat_grad[self.offsets[li]:] if direct else self.gt_partial[0, self.offsets[li]:]
             if li == last:
-                _native.call("dl_dwn_bwd_fused_t", None, self.dlogits_t, self.gsz, 1.0 / self.tau, None, 1, None, None,
+                _native.call(fused, None, self.dlogits_t, self.gsz, 1.0 / self.tau, None, 1, None, None,
                              self.bits[li], self.plans[li].map_nodes, None, self.addr[li], partial, total,
                              self.N[li], self.n[li], Bp)
             else:
@@ -209,7 +223,7 @@ class DWNNetwork:
                     g_up, gdiv, gscale = self.dlogits_t, self.gsz, 1.0 / self.tau
                 else:
                     g_up, gdiv, gscale = self.gact[up], 1, 1.0
-                _native.call("dl_dwn_bwd_fused_t", self.addr[up], g_up, gdiv, gscale, self.efd[up], self.n[up],
+                _native.call(fused, self.addr[up], g_up, gdiv, gscale, self.efd[up], self.n[up],
                              self.plans[up].inv_ptr_virtual, self.plans[up].inv_ent8_virtual, self.bits[li],
                              self.plans[li].map_nodes, self.gact[li] if li > 0 else None,
                              self.addr[li] if li > 0 else None, partial, total, self.N[li], self.n[li], Bp)
@@ -263,7 +277,7 @@ class DWNNetwork:
         sums = 0 if (fused_adam or (self.distributed and getattr(self, "groups", 2) == 1)) else (L if self.distributed else 1)
         backward = (L + sums) if self.fused_backward else (L + (L - 1))
         prepare = 2 * (1 if self.uniform else L)
-        return prepare + 1 + (L - 1) + 2 + 2 + backward + 2
+        return prepare + 1 + (1 if self.swizzle else 0) + (L - 1) + 2 + 2 + backward + 2
 
     def train_step(self, x: torch.Tensor, labels: torch.Tensor, use_graph: bool = False) -> torch.Tensor:
         """One optimisation step on this rank's shard (x (B, F) fp32, labels (B,) integer).

@@ -305,6 +305,29 @@ int dl_dwn_fwd_groupsum_noalloc_t(const uint32_t* in_bits_t, const int32_t* map,
                                   float* logits_t, int64_t N, int64_t n, int64_t k, float tau,
                                   int64_t Bp, dl_stream_t stream);
 
+/* ------------------------------------------------------------------ chunk-interleaved bit layout
+ * No counterpart in the reference (it has no packed format).  The bit-sliced hard forward
+ * (dl_dwn_fwd_bits_t) does not care which sample sits at which bit, while the kernels that need a
+ * per-sample table address (dl_dwn_fwd_groupsum_*, dl_dwn_bwd_fused_*) form it for 4 consecutive
+ * samples per lane and 128-sample chunk.  In this layout a row has dl_swizzled_words(Bp) =
+ * 32 * ceil(Bp/1024) words and, inside each 1024-sample block, bit c + 8r of word w holds sample
+ * 128c + 4w + r: a lane's own word then carries its four samples of chunk c one per byte, and an
+ * address bit costs one shift and one masked or instead of a shuffle, a shift, a mask, a multiply
+ * and two logic ops.  dl_bits_swizzle_t converts natural rows [F][Bp/32] (out of place); run
+ * dl_dwn_fwd_bits_t on interleaved rows with Bp rounded up to a multiple of 1024.  The *_s entry
+ * points are the *_t ones reading interleaved input bits; every other argument (gradients,
+ * addresses, logits) keeps the natural sample order. */
+int64_t dl_swizzled_words(int64_t Bp);
+int dl_bits_swizzle_t(const uint32_t* bits_t, uint32_t* bits_s, int64_t F, int64_t Bp, dl_stream_t stream);
+int dl_dwn_fwd_groupsum_s(const uint32_t* in_bits_s, const int32_t* map, const float* tables,
+                          float* partial, float* logits_t, int64_t N, int64_t n, int64_t k, float tau,
+                          int64_t Bp, dl_stream_t stream);
+int dl_dwn_bwd_fused_s(const uint8_t* addr_up, const float* g_up, int64_t gdiv_up, float gscale_up,
+                       const float* efd_up, int64_t n_up, const int32_t* inv_ptr, const int32_t* inv_ent,
+                       const uint32_t* in_bits_s, const int32_t* map, float* g_out, uint8_t* addr_out,
+                       float* gt_partial, int64_t group_stride, int64_t N, int64_t n, int64_t Bp,
+                       dl_stream_t stream);
+
 /* Mean cross-entropy over `B_global` samples of which this call holds B (user code in the
  * reference: nn.CrossEntropyLoss, e.g. tests/test_layers/test_convolutional_learning.py:85-111).
  * logits_t [k][Bp]; labels (B) int32; writes dlogits_t [k][Bp] = (softmax - onehot)/B_global

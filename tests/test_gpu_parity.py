@@ -625,6 +625,33 @@ def test_fused_backward_equals_separate_kernels_multi_group(dev):
         torch.testing.assert_close(a, r, rtol=1e-4, atol=1e-7)
 
 
+@pytest.mark.parametrize("B", [128, 1024, 2500])
+def test_bits_swizzle_layout(dev, B):
+    """Chunk-interleaved layout: bit c + 8r of word w of a 1024-sample block is sample 128c + 4w + r."""
+    from difflut_b200 import _native
+
+    gen = torch.Generator().manual_seed(B)
+    F = 7
+    bits = (torch.rand(B, F, generator=gen) > 0.5).float()
+    Bp = _native.padded_batch(B)
+    nat = torch.from_numpy(O.pack_bits_feature_major(
+        torch.cat([bits, torch.zeros(Bp - B, F)])).view(np.int32)).to(dev)
+    Ws = int(_native.lib().dl_swizzled_words(Bp))
+    assert Ws == 32 * ((Bp + 1023) // 1024)
+    out = torch.full((F, Ws), -1, dtype=torch.int32, device=dev)
+    _native.call("dl_bits_swizzle_t", nat, out, F, Bp)
+    got = out.cpu().numpy().view(np.uint32)
+    padded = np.zeros((Ws * 32, F), dtype=np.uint32)
+    padded[:B] = bits.numpy().astype(np.uint32)
+    want = np.zeros((F, Ws), dtype=np.uint32)
+    for g in range(Ws // 32):
+        blk = padded[g * 1024:(g + 1) * 1024].reshape(8, 32, 4, F)  # [c][w][r][f]
+        for c in range(8):
+            for r in range(4):
+                want[:, g * 32:(g + 1) * 32] |= (blk[c, :, r, :].T << np.uint32(c + 8 * r)).astype(np.uint32)
+    assert np.array_equal(got, want)
+
+
 # ------------------------------------------------------------------------------ tensor-core GEMM
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 320), (300, 500, 200), (1000, 777, 4096)])
 def test_gemm_bf16_tn_matches_fp32_matmul(dev, M, N, K):
