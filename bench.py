@@ -383,6 +383,9 @@ def run_gpu_arm(args):
     # step contains the gradient all-reduce, so every rank runs it
     prof = profile_kernels(net, B, GLOBAL_BATCH)
     trace("kernel profile done")
+    status = net.peer_status()
+    if status != 0:
+        raise SystemExit(f"rank {rank}: a bounded peer wait ran out (rank {status - 1} did not arrive)")
     line = None
     if rank == 0:
         top = max(prof.items(), key=lambda kv: kv[1]["ms"])
@@ -411,7 +414,10 @@ def run_gpu_arm(args):
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": SCALING, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": _config({"per_gpu_batch": B, "parallelism": f"dp{world}", "mode": "bit-packed activations between layers, fp32 gradients",
-                               "cuda_graph": use_graph, "l2": "256 MB flush between timed steps"}),
+                               "cuda_graph": use_graph, "l2": "256 MB flush between timed steps",
+                               "gradient_exchange": ("none" if world == 1 else
+                                                     "peer-memory reduce+Adam+broadcast kernel" if net.peer_optimizer
+                                                     else "NCCL all-reduce per layer")}),
             "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": int(x_pin.numel() * 4 + y_pin.numel() * 4) * world,
                     "d2h_bytes_per_step": 4 * world},
             "gpu_launches": net.kernel_launches_per_step() * args.steps,

@@ -60,6 +60,8 @@ SIGNATURES = {
     "dl_dwn_bwd_fused_s": "pplfplpppppppllll s",
     "dl_bits_swizzle_t": "ppll s",
     "dl_dwn_fwd_groupsum_noalloc_t": "pppplllfl s",
+    "dl_p2p_barrier": "pllpl s",
+    "dl_p2p_reduce_adam": "ppppplllfffff s",
     "dl_popcount_groupsum_t": "ppllll s",
     "dl_ce_t": "pppppllll s",
     "dl_adam_step": "ppppplfffff s",
@@ -101,6 +103,8 @@ def lib():
     handle.dl_dwn_bwd_groups.argtypes = [ctypes.c_int64]
     handle.dl_prob_groupsum_splits.restype = ctypes.c_int64
     handle.dl_prob_groupsum_splits.argtypes = [ctypes.c_int64, ctypes.c_int64]
+    handle.dl_p2p_enable_peer.restype = ctypes.c_int
+    handle.dl_p2p_enable_peer.argtypes = [ctypes.c_int64]
     handle.dl_swizzled_words.restype = ctypes.c_int64
     handle.dl_swizzled_words.argtypes = [ctypes.c_int64]
     handle.dl_unfold_positions.restype = ctypes.c_int64

@@ -36,3 +36,13 @@ constexpr int DL_NUM_SMS = 148;
 __device__ __forceinline__ uint32_t dl_spread_nibble(uint32_t nib) {
     return (nib * 0x00204081u) & 0x01010101u;
 }
+
+// One Adam element update (torch.optim.Adam without weight decay / amsgrad); shared by the local and
+// the peer-to-peer optimiser kernels so that both produce the same bits.
+__device__ __forceinline__ float adam_update(float p, float gi, float& m, float& v, float step_size, float bc2_sqrt,
+                                             float b1, float b2, float eps) {
+    m = m + (gi - m) * (1.0f - b1);
+    v = v * b2 + (1.0f - b2) * gi * gi;
+    const float denom = sqrtf(v) / bc2_sqrt + eps;
+    return p - step_size * (m / denom);
+}

@@ -92,14 +92,6 @@ __global__ void adam_advance_kernel(double* state, double b1, double b2) {
     state[1] *= b2;
 }
 
-__device__ __forceinline__ float adam_update(float p, float gi, float& m, float& v, float step_size, float bc2_sqrt,
-                                             float b1, float b2, float eps) {
-    m = m + (gi - m) * (1.0f - b1);
-    v = v * b2 + (1.0f - b2) * gi * gi;
-    const float denom = sqrtf(v) / bc2_sqrt + eps;
-    return p - step_size * (m / denom);
-}
-
 // four elements per thread (16-byte accesses); the tail is handled element-wise
 __global__ void adam_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
                             float* __restrict__ v, const double* __restrict__ state, int64_t count,

@@ -63,3 +63,54 @@ def max_over_ranks(value: float, device=None) -> float:
     t = torch.tensor([value], dtype=torch.float64, device=device if device is not None else "cpu")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
+
+
+class PeerWindow:
+    """A CUDA tensor of this rank together with the same-shaped tensor of every other rank of the node.
+
+    The ranks exchange CUDA IPC handles (the mechanism torch.multiprocessing uses to pass CUDA tensors
+    between processes) through the process group and every rank opens the others' handles with ITS OWN
+    device current, which is what maps the memory into this GPU's address space and lets the driver set up
+    peer access (opening it under the exporter's device index, as torch.multiprocessing does for a consumer
+    that computes on the exporter's GPU, would leave the mapping in another context of this process, out
+    of reach of this GPU's kernels).  `ptrs` is a host array of `world` device pointers indexed by rank,
+    in the form the `dl_p2p_*` entry points take.  Plain peer mappings only: no multicast object is
+    created.
+    """
+
+    def __init__(self, tensor: torch.Tensor, group=None):
+        import ctypes
+
+        from torch.multiprocessing.reductions import rebuild_cuda_tensor, reduce_tensor
+
+        from . import _native
+
+        if not tensor.is_cuda or not tensor.is_contiguous():
+            raise ValueError("PeerWindow needs a contiguous CUDA tensor")
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > 8:
+            raise ValueError("PeerWindow supports at most 8 ranks (one node)")
+        self.local = tensor
+        _, args = reduce_tensor(tensor)
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, (tensor.device.index, args), group=group)
+        self.tensors = []
+        with torch.cuda.device(tensor.device):
+            for p, (dev, peer_args) in enumerate(gathered):
+                if p == self.rank:
+                    self.tensors.append(tensor)
+                    continue
+                if dev == tensor.device.index:
+                    raise RuntimeError("two ranks share one GPU: peer windows need one GPU per rank")
+                rc = _native.lib().dl_p2p_enable_peer(dev)
+                if rc != 0:
+                    raise RuntimeError(f"no peer access from cuda:{tensor.device.index} to cuda:{dev} (code {rc})")
+                peer_args = list(peer_args)
+                peer_args[6] = tensor.device.index  # storage_device: open the handle on this rank's GPU
+                mapped = rebuild_cuda_tensor(*peer_args)
+                if mapped.numel() != tensor.numel() or mapped.dtype != tensor.dtype:
+                    raise RuntimeError("peer tensor does not match the local one")
+                self.tensors.append(mapped)
+        self._array = (ctypes.c_void_p * self.world)(*[t.data_ptr() for t in self.tensors])
+        self.ptrs = ctypes.addressof(self._array)
+        dist.barrier(group=group)  # every rank has mapped every buffer before anyone uses them

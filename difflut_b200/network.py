@@ -19,6 +19,8 @@ model + loop as in examples/demo_probabilistic_random.py:111-178 with DWN nodes.
 
 from typing import Optional, Sequence
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -33,7 +35,7 @@ class DWNNetwork:
     def __init__(self, encoder: ThermometerEncoder, layers: Sequence[RandomLayer], groupsum: GroupSum,
                  lr: float = 1e-2, betas=(0.9, 0.999), eps: float = 1e-8,
                  process_group: Optional["dist.ProcessGroup"] = None, distributed: Optional[bool] = None,
-                 fused_backward: bool = True):
+                 fused_backward: bool = True, peer_optimizer: Optional[bool] = None):
         if not encoder.is_fitted:
             raise RuntimeError("DWNNetwork needs a fitted encoder")
         if groupsum.use_randperm:
@@ -55,6 +57,14 @@ class DWNNetwork:
             distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(process_group) > 1
         self.distributed = bool(distributed)
         self.world = dist.get_world_size(process_group) if self.distributed else 1
+        self.rank = dist.get_rank(process_group) if self.distributed else 0
+        # gradient all-reduce + Adam + parameter broadcast as one kernel over peer memory (one node, NCCL
+        # process group, at most 8 ranks); DIFFLUT_PEER_OPTIMIZER=0 keeps the NCCL all-reduce path
+        if peer_optimizer is None:
+            peer_optimizer = (self.distributed and self.fused_backward and self.world <= 8
+                              and dist.get_backend(process_group) == "nccl"
+                              and os.environ.get("DIFFLUT_PEER_OPTIMIZER", "1") != "0")
+        self.peer_optimizer = bool(peer_optimizer) and self.distributed
 
         thr = encoder.thresholds.reshape(-1, encoder.num_bits)
         self.thr = thr.to(device=self.device, dtype=torch.float32).contiguous()
@@ -74,10 +84,14 @@ class DWNNetwork:
         for c in counts:
             self.offsets.append(self.offsets[-1] + c)
         total = self.offsets[-1]
-        self.flat = torch.empty(total, device=self.device, dtype=torch.float32)
+        if self.peer_optimizer:  # equal slices of whole 16-byte pieces per rank
+            unit = 4 * self.world
+            total = (total + unit - 1) // unit * unit
+        moments = total // self.world if self.peer_optimizer else total
+        self.flat = torch.zeros(total, device=self.device, dtype=torch.float32)
         self.flat_grad = torch.zeros(total, device=self.device, dtype=torch.float32)
-        self.exp_avg = torch.zeros(total, device=self.device, dtype=torch.float32)
-        self.exp_avg_sq = torch.zeros(total, device=self.device, dtype=torch.float32)
+        self.exp_avg = torch.zeros(moments, device=self.device, dtype=torch.float32)
+        self.exp_avg_sq = torch.zeros(moments, device=self.device, dtype=torch.float32)
         self.adam_state = torch.ones(2, device=self.device, dtype=torch.float64)
         self.tables, self.grads = [], []
         for li, l in enumerate(self.layers):
@@ -89,6 +103,16 @@ class DWNNetwork:
             l.luts.grad = gview
             self.tables.append(view)
             self.grads.append(gview)
+        if self.peer_optimizer:
+            from .distributed import PeerWindow
+
+            self.peer_flags = torch.zeros(8, device=self.device, dtype=torch.int32)
+            self.peer_ctrl = torch.zeros(2, device=self.device, dtype=torch.int32)
+            torch.cuda.synchronize(self.device)
+            self.win_params = PeerWindow(self.flat, process_group)
+            self.win_grads = PeerWindow(self.flat_grad, process_group)
+            self.win_flags = PeerWindow(self.peer_flags, process_group)
+            self.peer_timeout_ms = 5000
         self.plans = [l._plan(self.device) for l in self.layers]
         self.alpha = [l.alpha for l in self.layers]
         self.beta = [l.beta for l in self.layers]
@@ -143,7 +167,8 @@ class DWNNetwork:
             self.gact = [torch.empty(N, Bp, device=dev, dtype=torch.float32)
                          if (li > 0 or not self.fused_backward) else None for li, N in enumerate(self.N[:-1])]
             self.groups = int(_native.lib().dl_dwn_bwd_groups(Bp))
-            self.gt_partial = (torch.empty(self.groups, self.flat.numel(), device=dev, dtype=torch.float32)
+            # zeros: the padding behind the last table (peer mode) is summed with the rest and must stay 0
+            self.gt_partial = (torch.zeros(self.groups, self.flat.numel(), device=dev, dtype=torch.float32)
                                if self.fused_backward else None)
             self.addr = [None] + [torch.empty(N, Bp, device=dev, dtype=torch.uint8) for N in self.N[1:]]
             self.dlogits_t = torch.empty(self.k, Bp, device=dev, dtype=torch.float32)
@@ -230,10 +255,14 @@ class DWNNetwork:
             if self.distributed:
                 lo, hi = self.offsets[li], self.offsets[li + 1]
                 grad = self.flat_grad[lo:hi]
+                if self.peer_optimizer:
+                    continue  # one sum over the whole buffer after the last layer, then the peer step
                 if not direct:
                     _native.call("dl_sum_groups", self.gt_partial[0, lo:], grad, hi - lo, total, self.groups)
                 # sum of per-rank gradients of the GLOBAL-mean loss (dl_ce_t divides by B_global)
                 self._pending.append(allreduce_sum_(grad, self.group, async_op=True))
+        if self.peer_optimizer and not direct:
+            _native.call("dl_sum_groups", self.gt_partial, self.flat_grad, total, total, self.groups)
 
     def _step_body(self, B: int, B_global: int) -> None:
         # the EFD transform is only needed by the backward: it runs on a side stream next to the forward
@@ -259,6 +288,16 @@ class DWNNetwork:
                          self.exp_avg, self.exp_avg_sq, self.adam_state, count, self.lr, self.betas[0], self.betas[1],
                          self.eps, 1.0)
             return
+        if self.peer_optimizer:
+            # every rank's gradients are complete -> each rank reduces and updates its slice and stores the
+            # new parameters everywhere -> every rank's stores have landed
+            barrier = (self.win_flags.ptrs, self.rank, self.world, self.peer_ctrl, self.peer_timeout_ms)
+            _native.call("dl_p2p_barrier", *barrier)
+            _native.call("dl_p2p_reduce_adam", self.win_grads.ptrs, self.win_params.ptrs, self.exp_avg,
+                         self.exp_avg_sq, self.adam_state, count, self.rank, self.world, self.lr, self.betas[0],
+                         self.betas[1], self.eps, 1.0)
+            _native.call("dl_p2p_barrier", *barrier)
+            return
         if self.distributed:
             if self.fused_backward:
                 for work in self._pending:  # the per-layer all-reduces started during the backward
@@ -271,13 +310,21 @@ class DWNNetwork:
                      count, self.lr, self.betas[0], self.betas[1], self.eps, 1.0)
 
     # ------------------------------------------------------------------ public API
+    def peer_status(self) -> int:
+        """0, or 1 + the rank a bounded peer wait gave up on (synchronises; call it between steps)."""
+        return int(self.peer_ctrl[1].item()) if self.peer_optimizer else 0
+
     def kernel_launches_per_step(self) -> int:
         L = len(self.layers)
         fused_adam = self.fused_backward and not self.distributed
-        sums = 0 if (fused_adam or (self.distributed and getattr(self, "groups", 2) == 1)) else (L if self.distributed else 1)
+        if fused_adam or (self.distributed and getattr(self, "groups", 2) == 1):
+            sums = 0
+        else:
+            sums = 1 if (self.peer_optimizer or not self.distributed) else L
         backward = (L + sums) if self.fused_backward else (L + (L - 1))
         prepare = 2 * (1 if self.uniform else L)
-        return prepare + 1 + (1 if self.swizzle else 0) + (L - 1) + 2 + 2 + backward + 2
+        update = 4 if self.peer_optimizer else 2  # barrier, state advance, reduce+Adam+broadcast, barrier
+        return prepare + 1 + (1 if self.swizzle else 0) + (L - 1) + 2 + 2 + backward + update
 
     def train_step(self, x: torch.Tensor, labels: torch.Tensor, use_graph: bool = False) -> torch.Tensor:
         """One optimisation step on this rank's shard (x (B, F) fp32, labels (B,) integer).

@@ -328,6 +328,29 @@ int dl_dwn_bwd_fused_s(const uint8_t* addr_up, const float* g_up, int64_t gdiv_u
                        float* gt_partial, int64_t group_stride, int64_t N, int64_t n, int64_t Bp,
                        dl_stream_t stream);
 
+/* ------------------------------------------------------------------ data-parallel step over peer memory
+ * No counterpart in the reference (it is single-process).  One process per GPU; every rank maps the
+ * other ranks' gradient / parameter / flag buffers (CUDA IPC: plain peer pointers) and passes HOST
+ * arrays of `world` device pointers, indexed by rank (its own buffer at its own index).
+ *   dl_p2p_enable_peer   enable access from the current device to `peer_device` (idempotent)
+ *   dl_p2p_barrier       one barrier among the ranks: flags buffers are int32[DL_MAX_PEERS], zeroed
+ *                        once; ctrl is a local int32[2] {epoch, status}, zeroed once.  Every wait
+ *                        is bounded by timeout_ms; on expiry status becomes 1 + the peer that was
+ *                        missing and the kernel returns (the caller reads ctrl[1] when it likes).
+ *   dl_p2p_reduce_adam   rank r sums slice r (count/world elements) of all ranks' gradients in
+ *                        rank order, applies the Adam step of dl_adam_step to it with its slice-
+ *                        sized moments m, v (count/world floats) and stores the new parameters
+ *                        into every rank's parameter buffer.  count % (4*world) == 0.  Call
+ *                        dl_p2p_barrier before it (gradients complete everywhere) and after it
+ *                        (parameters complete everywhere).                                        */
+#define DL_MAX_PEERS 8
+int dl_p2p_enable_peer(int64_t peer_device);
+int dl_p2p_barrier(const void* const* peer_flags_host, int64_t rank, int64_t world, int32_t* ctrl,
+                   int64_t timeout_ms, dl_stream_t stream);
+int dl_p2p_reduce_adam(const void* const* peer_grads_host, const void* const* peer_params_host, float* m,
+                       float* v, double* state, int64_t count, int64_t rank, int64_t world, float lr,
+                       float beta1, float beta2, float eps, float gscale, dl_stream_t stream);
+
 /* Mean cross-entropy over `B_global` samples of which this call holds B (user code in the
  * reference: nn.CrossEntropyLoss, e.g. tests/test_layers/test_convolutional_learning.py:85-111).
  * logits_t [k][Bp]; labels (B) int32; writes dlogits_t [k][Bp] = (softmax - onehot)/B_global

@@ -1,0 +1,77 @@
+"""Two-GPU test of the peer-memory optimiser step (gradient sum + Adam + parameter broadcast in one
+kernel): two ranks train a small DWN classifier for three steps with it and, separately, with the NCCL
+all-reduce path; tables must agree between the ranks bit for bit and between the two paths to fp32
+rounding.  Needs two GPUs (skipped otherwise); the ranks are child processes."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+WORKER = r"""
+import os, sys, warnings
+warnings.simplefilter("ignore")
+import torch
+import torch.distributed as dist
+sys.path.insert(0, os.environ["DIFFLUT_ROOT"])
+from difflut_b200.distributed import init_from_env, shard_rows
+from difflut_b200.encoder import ThermometerEncoder
+from difflut_b200.layers import RandomLayer
+from difflut_b200.network import DWNNetwork
+from difflut_b200.nodes import DWNNode, NodeConfig
+from difflut_b200.utils import GroupSum
+
+rank, world, local = init_from_env(timeout_s=60)
+dev = torch.device("cuda", local)
+gen = torch.Generator().manual_seed(0)
+B, F, Tb, k = 600, 12, 3, 4
+x = torch.rand(B, F, generator=gen)
+y = torch.randint(0, k, (B,), generator=gen)
+sizes = [70, 40, 20]
+tabs = [torch.randn(N, 1, 64, generator=gen) for N in sizes]
+lo, hi = shard_rows(B, rank, world)
+results = {}
+for peer in (True, False):
+    enc = ThermometerEncoder(num_bits=Tb).fit(x)
+    layers, I = [], F * Tb
+    for li, N in enumerate(sizes):
+        l = RandomLayer(I, N, DWNNode, NodeConfig(input_dim=6, output_dim=1), seed=li).to(dev)
+        with torch.no_grad():
+            l.luts.copy_(tabs[li].to(dev))
+        layers.append(l)
+        I = N
+    net = DWNNetwork(enc, layers, GroupSum(k=k, tau=2.0, use_randperm=False), lr=1e-2, peer_optimizer=peer)
+    assert net.peer_optimizer == peer
+    for step in range(3):
+        net.train_step(x[lo:hi].to(dev), y[lo:hi].to(dev), use_graph=(step > 0))
+    torch.cuda.synchronize()
+    assert net.peer_status() == 0
+    results[peer] = torch.cat([t.reshape(-1) for t in net.tables]).clone()
+mine = results[True]
+both = [torch.empty_like(mine) for _ in range(world)]
+dist.all_gather(both, mine)
+assert torch.equal(both[0], both[1]), "ranks disagree after the peer-memory step"
+torch.testing.assert_close(results[True], results[False], rtol=1e-5, atol=1e-6)
+assert not torch.equal(results[True], torch.cat([t.reshape(-1) for t in tabs]).to(dev)), "tables did not move"
+dist.barrier()
+print(f"rank {rank} ok", flush=True)
+os._exit(0)
+"""
+
+
+def test_peer_optimizer_matches_allreduce_path(tmp_path):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, DIFFLUT_ROOT=root, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+           "--master-addr", "127.0.0.1", "--master-port", "29533", str(script)]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    assert "rank 0 ok" in out.stdout and "rank 1 ok" in out.stdout
