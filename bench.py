@@ -557,6 +557,84 @@ def run_prob(args):
                                    "traffic": None}}), flush=True)
 
 
+def run_conv(args):
+    """ConvolutionalLayer training step (fwd+bwd): 28x28 images in 3 thermometer planes, 5x5 receptive field,
+    32 trees of depth 2 with 6-input nodes, batch 128 -> 73 728 patches through 1152 + 192 + 32 nodes."""
+    import torch
+
+    warnings.simplefilter("ignore")
+    from difflut_b200.layers import ConvolutionalLayer, ConvolutionConfig, RandomLayer
+    from difflut_b200.nodes import DWNNode, DWNStableNode, HybridNode, NodeConfig, ProbabilisticNode
+
+    device = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(0)
+    B, C, H, trees = 128, 3, 28, 32
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    results = {}
+    for name, node in (("dwn", DWNNode), ("dwn_stable", DWNStableNode), ("hybrid", HybridNode),
+                       ("probabilistic", ProbabilisticNode)):
+        conv = ConvolutionalLayer(ConvolutionConfig(tree_depth=2, in_channels=C, out_channels=trees, receptive_field=5,
+                                                    chunk_size=8), node, NodeConfig(input_dim=6, output_dim=1),
+                                  RandomLayer).to(device).train()
+        x = (torch.rand(B, C, H, H, generator=g) > 0.5).float() if name.startswith("dwn") else \
+            torch.rand(B, C, H, H, generator=g).clamp(1e-3, 1 - 1e-3)
+        x = x.to(device).requires_grad_(True)
+        gy = torch.randn(B, trees, 24, 24, generator=g).to(device)
+
+        def step():
+            x.grad = None
+            for p in conv.parameters():
+                p.grad = None
+            conv(x).backward(gy)
+
+        results[name] = _time_gpu(step, args.steps, max(args.warmup, 3), flush)
+    patches = B * 24 * 24
+    ms = results["dwn"]
+    print(json.dumps({"metric": "train patches/s (fwd+bwd) convolutional DWN layer, 32 trees of depth 2, n=6",
+                      "value": patches / (ms * 1e-3), "unit": "patches/s", "n_gpus": 1, "steps": args.steps,
+                      "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+                      "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": "conv_B128_3x28x28_rf5_trees32_depth2_n6", "patches_per_step": patches,
+                                 "l2": "256 MB flush between timed steps"},
+                      "ms_per_step_by_node_type": {k: round(v, 4) for k, v in results.items()}}), flush=True)
+
+
+def run_nodes(args):
+    """RandomLayer(4096 -> 8000, n=6) fwd+bwd at batch 1024 for each stacked node type (layer API)."""
+    import torch
+
+    warnings.simplefilter("ignore")
+    from difflut_b200.layers import RandomLayer
+    from difflut_b200.nodes import DWNNode, DWNStableNode, HybridNode, NodeConfig, ProbabilisticNode
+
+    device = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(0)
+    B, I, N = 1024, 4096, 8000
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    x = torch.rand(B, I, generator=g).clamp(1e-3, 1 - 1e-3).to(device).requires_grad_(True)
+    gy = torch.randn(B, N, generator=g).to(device)
+    results = {}
+    for name, node in (("dwn", DWNNode), ("dwn_stable", DWNStableNode), ("hybrid", HybridNode),
+                       ("probabilistic", ProbabilisticNode)):
+        layer = RandomLayer(I, N, node, NodeConfig(input_dim=6, output_dim=1), seed=0).to(device).train()
+
+        def step():
+            x.grad = None
+            for p in layer.parameters():
+                p.grad = None
+            layer(x).backward(gy)
+
+        results[name] = _time_gpu(step, args.steps, max(args.warmup, 3), flush)
+    ms = results["dwn_stable"]
+    print(json.dumps({"metric": "train samples/s (fwd+bwd) RandomLayer 4096->8000 n=6, DWNStable nodes",
+                      "value": B / (ms * 1e-3), "unit": "samples/s", "n_gpus": 1, "steps": args.steps,
+                      "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+                      "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": "layer_B1024_in4096_N8000_n6_by_node_type",
+                                 "l2": "256 MB flush between timed steps"},
+                      "ms_per_step_by_node_type": {k: round(v, 4) for k, v in results.items()}}), flush=True)
+
+
 def run_learnable(args):
     """BASELINE config 3: LearnableLayer(4096 -> 16000 DWN nodes, n=6), B=4096 binary inputs, loss = sum of outputs."""
     import torch
@@ -641,7 +719,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="train", choices=["train", "train-layers", "infer", "prob", "learnable"],
+    ap.add_argument("--workload", default="train", choices=["train", "train-layers", "infer", "prob", "learnable", "conv", "nodes"],
                     help="train = the benchmark contract's workload; the others are secondary measurements")
     ap.add_argument("--small", action="store_true", help="reduced sizes of the secondary workloads (for ncu captures)")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
@@ -667,6 +745,10 @@ def main():
         run_infer(args)
     elif args.workload == "prob":
         run_prob(args)
+    elif args.workload == "conv":
+        run_conv(args)
+    elif args.workload == "nodes":
+        run_nodes(args)
     elif args.workload == "learnable":
         run_learnable(args)
     elif args.workload == "train-layers":

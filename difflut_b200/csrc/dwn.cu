@@ -235,22 +235,26 @@ __device__ __forceinline__ uint32_t addr4(const uint32_t* __restrict__ in_bits, 
     return packed;
 }
 
-// Training forward, one warp per node; lane = 4 consecutive samples of each 128-sample chunk.
+// Training forward, one warp per (1024-sample slab, node); lane = 4 consecutive samples of each
+// 128-sample chunk.  Slabs are the outer order, so the warps of the grid share one slab of input rows
+// at a time and layers with few nodes still fill the machine.
 __global__ void __launch_bounds__(256)
 dwn_fwd_vals_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __restrict__ map,
                     const float* __restrict__ tables, float* __restrict__ out_t,
                     uint8_t* __restrict__ addr_t, int64_t N, int n, int64_t Bp) {
     const int lane = threadIdx.x & 31;
     const int64_t C = Bp >> 7, Wp = Bp >> 5;
+    const int64_t G = (C + 7) >> 3;
     const int L = 1 << n;
     const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-    // warp w of the grid walks nodes w, w + nwarps, ...; all chunks of a node stay in one warp
-    for (int64_t j = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; j < N; j += nwarps) {
+    for (int64_t item = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; item < G * N; item += nwarps) {
+        const int64_t cg = item / N, j = item - cg * N;
         int32_t rows[DL_MAX_FAST_N];
 #pragma unroll
         for (int i = 0; i < DL_MAX_FAST_N; ++i) rows[i] = i < n ? __ldg(&map[j * n + i]) : 0;
         const float* tj = tables + j * L;
-        for (int64_t c = 0; c < C; ++c) {
+        const int64_t c1 = (cg + 1) * 8 < C ? (cg + 1) * 8 : C;
+        for (int64_t c = cg * 8; c < c1; ++c) {
             const int64_t b = (c << 7) + lane * 4;
             const uint32_t a = addr4(in_bits, rows, n, Wp, b);
             float4 o;
@@ -416,17 +420,21 @@ __global__ void __launch_bounds__(256)
 dwn_bwd_input_kernel(const uint8_t* __restrict__ addr_t, const float* __restrict__ g_t, int64_t gdiv,
                      float gscale, const float* __restrict__ efd_t,
                      const int32_t* __restrict__ inv_ptr, const int32_t* __restrict__ inv_ent,
-                     float* __restrict__ gx_t, int64_t F, int n, int64_t Bp) {
+                     float* __restrict__ gx_t, int64_t F, int n, int64_t Bp, int cps) {
     const int lane = threadIdx.x & 31;
     const int64_t C = Bp >> 7;
     const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-    // all warps sweep the features of one 1024-sample slab before moving on, so the slab of g_t /
-    // addr_t they share stays in L2; within a slab a warp owns a feature (no index division)
-    const int64_t G = (C + 7) >> 3;
+    // The batch is walked in passes of `cps` chunks (a multiple of 8: whole 1024-sample slabs); inside a
+    // pass one warp owns one (feature, chunk) pair and the pairs of a feature go to neighbouring warps.
+    // With many features a pass is one slab, so the slab of g_t / addr_t the warps share stays in L2;
+    // with few features (a convolution's patch taps) the host widens the pass until every warp has work.
     const uint32_t ugdiv = (uint32_t)gdiv;
-    for (int64_t cg = 0; cg < G; ++cg)
-    for (int64_t f = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; f < F; f += nwarps)
-    for (int64_t c = cg << 3; c < ((cg + 1) << 3) && c < C; ++c) {
+    const int64_t items = F * cps;
+    for (int64_t c0 = 0; c0 < C; c0 += cps)
+    for (int64_t it = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; it < items; it += nwarps) {
+        const int64_t f = it / cps;
+        const int64_t c = c0 + (it - f * cps);
+        if (c >= C) continue;  // uniform over the warp
         const int64_t b = (c << 7) + lane * 4;
         const int e0 = __ldg(&inv_ptr[f]), e1 = __ldg(&inv_ptr[f + 1]);
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -926,7 +934,7 @@ DL_EXPORT int dl_dwn_fwd_vals_t(const uint32_t* in_bits_t, const int32_t* map, c
     DL_REQUIRE_ALIGNED(out_t, 16);
     if (addr_t) DL_REQUIRE_ALIGNED(addr_t, 4);
     if (n < 1 || n > DL_MAX_FAST_N) return DL_ERR_UNSUPPORTED;
-    const int blocks = grid_for(N * 32, 256);
+    const int blocks = grid_for(N * dl_ceil_div(Bp, 1024) * 32, 256);
     dwn_fwd_vals_kernel<<<blocks, 256, 0, dl_cast(stream)>>>(in_bits_t, map, tables, out_t, addr_t, N,
                                                             (int)n, Bp);
     return dl_launch_status();
@@ -1013,10 +1021,16 @@ DL_EXPORT int dl_dwn_bwd_input_t(const uint8_t* addr_t, const float* g_t, int64_
     DL_REQUIRE_ALIGNED(g_t, 16);
     DL_REQUIRE_ALIGNED(gx_t, 16);
     if (n < 1 || n > DL_MAX_FAST_N) return DL_ERR_UNSUPPORTED;
-    const int64_t want = dl_ceil_div(F * 32, 256);
+    // chunks per pass: one slab, or as many slabs as it takes to give every resident warp a pair
+    const int64_t resident_warps = (int64_t)DL_NUM_SMS * 5 * 8;
+    int64_t slabs = dl_ceil_div(resident_warps, F * 8);
+    const int64_t all_slabs = dl_ceil_div(Bp / 128, 8);
+    if (slabs > all_slabs) slabs = all_slabs;
+    const int cps = (int)(8 * slabs);
+    const int64_t want = dl_ceil_div(F * cps * 32, 256);
     const int blocks = (int)(want < (int64_t)DL_NUM_SMS * 5 ? want : (int64_t)DL_NUM_SMS * 5);
     dwn_bwd_input_kernel<<<blocks, 256, 0, dl_cast(stream)>>>(addr_t, g_t, gdiv, gscale, efd_t, inv_ptr,
-                                                             inv_ent, gx_t, F, (int)n, Bp);
+                                                             inv_ent, gx_t, F, (int)n, Bp, cps);
     return dl_launch_status();
 }
 

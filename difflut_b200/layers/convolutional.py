@@ -11,8 +11,9 @@ trees of a depth level run as ONE layer: their index maps are merged into one bl
 reads columns t*h .. t*h+h-1 of the level below) and their parameters are concatenated, so a forward is
 `depth + 1` layer kernels instead of `out_channels * depth + chunks` small ones.  For node types that only
 read `x >= 0.5` (DWN, DWNStable; every stacked type in eval mode) the patches are never materialised:
-bits are packed straight from the image (`dl_unfold_pack_t`) and the input gradient is folded straight
-back (`dl_fold_t`).  Any other layer / node class keeps the reference's loop over sub-layers on patches
+bits are packed straight from the image (`dl_unfold_pack_t`), the tree levels exchange one bit per
+activation (`DWNStackFunction`: bit-sliced forward, one fused backward kernel per level) and the input
+gradient is folded straight back (`dl_fold_t`).  Any other layer / node class keeps the reference's loop over sub-layers on patches
 produced by `dl_unfold_rows`.
 """
 
@@ -24,7 +25,7 @@ import torch.nn as nn
 from ..nodes.node_config import NodeConfig
 from ..registry import register_convolutional_layer
 from .base_layer import LUTLayerMixin
-from .fused_ops import ConnectionPlan, PatchFunction, PatchGeometry, dwn_levels_eval
+from .fused_ops import ConnectionPlan, DWNStackFunction, PatchFunction, PatchGeometry, dwn_levels_eval
 from .layer_config import GroupedInputConfig, LayerConfig
 from .random_layer import RandomLayer
 
@@ -184,6 +185,14 @@ class ConvolutionalLayer(LUTLayerMixin, nn.Module):
             geom = None
         else:
             h = x
+        if self.training and proto._stacked in ("dwn", "dwn_stable") and proto.n <= 6:
+            # all levels as one bit-packed pipeline: no fp32 activations between the tree levels
+            stable = proto._stacked == "dwn_stable"
+            params = [self._level_params(level) for level in levels]
+            tables = [torch.sigmoid(p[0]) if stable else p[0] for p in params]
+            spec = [(plan, 0.0 if stable else proto.alpha, 0.0 if stable else proto.beta,
+                     p[1].detach().float() if stable else None) for plan, p in zip(plans, params)]
+            return DWNStackFunction.apply(h, spec, geom, *tables)
         for level, plan in zip(levels, plans):
             h = level[0]._apply_plan(h, plan, self._level_params(level), geom)
             geom = None

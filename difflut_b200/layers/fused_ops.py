@@ -181,7 +181,16 @@ class DWNLayerFunction(torch.autograd.Function):
             addr = torch.empty(NO, Bp, device=g.device, dtype=torch.uint8) if need_x else None
             gt = torch.empty_like(tables)
             # the table-gradient kernel also produces the addresses the input-gradient kernel reads
-            _native.call("dl_dwn_bwd_tables_t", bits, plan.map_virtual, g_t, 1, 1.0, gt, addr, NO, n, Bp)
+            groups = int(_native.lib().dl_dwn_bwd_groups(Bp))
+            if groups == 1:
+                _native.call("dl_dwn_bwd_tables_t", bits, plan.map_virtual, g_t, 1, 1.0, gt, addr, NO, n, Bp)
+            else:
+                # large batches: one warp per (1024-sample group, node) and an ordered sum of the groups, so
+                # that layers with few nodes still fill the machine
+                partial = torch.empty(groups, gt.numel(), device=g.device, dtype=torch.float32)
+                _native.call("dl_dwn_bwd_fused_t", None, g_t, 1, 1.0, None, 1, None, None, bits, plan.map_virtual,
+                             None, addr, partial, gt.numel(), NO, n, Bp)
+                _native.call("dl_sum_groups", partial, gt, gt.numel(), gt.numel(), groups)
             if ctx.stable_scale is not None:
                 sc = ctx.stable_scale
                 gt = gt * (sc.reshape(gt.shape[0], gt.shape[1], 1) if isinstance(sc, torch.Tensor) else float(sc))
@@ -196,6 +205,116 @@ class DWNLayerFunction(torch.autograd.Function):
                     gx = torch.empty(geom.B, geom.C, geom.H, geom.W, device=g.device, dtype=torch.float32)
                     _native.call("dl_fold_t", gx_t, gx, *geom.args(), Bp)
         return gx, (gt if need_t else None), None, None, None, None, None
+
+
+class DWNStackFunction(torch.autograd.Function):
+    """Consecutive DWN layers (output_dim 1, n <= 6) as one autograd node, bit-packed from end to end.
+
+    A DWN layer only looks at `input >= 0.5`, so between the layers one bit per activation is enough:
+    the forward runs the bit-sliced hard-LUT kernel for every level but the last and reads table values
+    only there; the backward runs one fused kernel per level (pull the output gradient from the level
+    above, form the addresses, accumulate the table gradient) and never goes back to rows in between.
+    Same arithmetic as applying DWNLayerFunction level after level (difflut/nodes/dwn_node.py:58-229 per
+    node).  `levels` is a list of (plan, alpha, beta, stable_scale); x is (B, I) rows, or with `geom` an
+    image batch whose patches are the samples; `tables` are the levels' (N, 1, 2^n) tables.
+    """
+
+    @staticmethod
+    def forward(ctx, x, levels, geom, *tables):
+        x = x.contiguous().float()
+        tables = [t.contiguous().float() for t in tables]
+        if geom is None:
+            B, I = x.shape
+        else:
+            B, I = geom.S, geom.F
+        Bp = _native.padded_batch(B)
+        Wp = Bp // 32
+        dev = x.device
+        with torch.cuda.device(dev):
+            bits = [torch.empty(I, Wp, device=dev, dtype=torch.int32)]
+            if geom is None:
+                _native.call("dl_pack_rows_to_t", x, bits[0], B, I, Bp, 0.5)
+            else:
+                _native.call("dl_unfold_pack_t", x, bits[0], *geom.args(), 0.5, Bp)
+            for (plan, _, _, _), tab in zip(levels[:-1], tables[:-1]):
+                masks = torch.empty(plan.N, device=dev, dtype=torch.int64)
+                _native.call("dl_dwn_prepare", tab, None, masks, plan.N, plan.n, 0.0, 0.0)
+                nxt = torch.empty(plan.N, Wp, device=dev, dtype=torch.int32)
+                _native.call("dl_dwn_fwd_bits_t", bits[-1], plan.map_nodes, masks, nxt, plan.N, plan.n, Bp)
+                bits.append(nxt)
+            last = levels[-1][0]
+            out_t = torch.empty(last.N, Bp, device=dev, dtype=torch.float32)
+            _native.call("dl_dwn_fwd_vals_t", bits[-1], last.map_nodes, tables[-1], out_t, None, last.N, last.n, Bp)
+            out = _t_to_rows(out_t, B)
+        ctx.save_for_backward(*bits, *tables)
+        ctx.levels, ctx.geom, ctx.B = levels, geom, B
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        levels, geom, B = ctx.levels, ctx.geom, ctx.B
+        L = len(levels)
+        bits, tables = ctx.saved_tensors[:L], ctx.saved_tensors[L:]
+        Bp = bits[0].shape[1] * 32
+        dev = g.device
+        need_x = ctx.needs_input_grad[0]
+        sizes = [lv[0].N * (1 << lv[0].n) for lv in levels]
+        offs = [0]
+        for sz in sizes:
+            offs.append(offs[-1] + sz)
+        total = offs[-1]
+        with torch.cuda.device(dev):
+            g_t = _rows_to_t(g.contiguous().float(), Bp)
+            groups = int(_native.lib().dl_dwn_bwd_groups(Bp))
+            partial = torch.empty(groups, total, device=dev, dtype=torch.float32)
+            efd = [None] * L
+            for l in range(L):
+                if l > 0 or need_x:
+                    plan, alpha, beta, scale = levels[l]
+                    efd[l] = _efd_tables(tables[l], plan.N, plan.n, alpha, beta, scale)
+            addr = [None] * L
+            gact = [None] * L
+            gact[L - 1] = g_t
+            for l in range(L - 1, -1, -1):
+                plan = levels[l][0]
+                below = l > 0 or need_x  # somebody reads this level's addresses and output gradient
+                if below:
+                    addr[l] = torch.empty(plan.N, Bp, device=dev, dtype=torch.uint8)
+                if l == L - 1:
+                    _native.call("dl_dwn_bwd_fused_t", None, g_t, 1, 1.0, None, 1, None, None, bits[l], plan.map_nodes,
+                                 None, addr[l], partial[0, offs[l]:], total, plan.N, plan.n, Bp)
+                else:
+                    up = levels[l + 1][0]
+                    if below:
+                        gact[l] = torch.empty(plan.N, Bp, device=dev, dtype=torch.float32)
+                    _native.call("dl_dwn_bwd_fused_t", addr[l + 1], gact[l + 1], 1, 1.0, efd[l + 1], up.n,
+                                 up.inv_ptr_virtual, up.inv_ent8_virtual, bits[l], plan.map_nodes, gact[l], addr[l],
+                                 partial[0, offs[l]:], total, plan.N, plan.n, Bp)
+                    gact[l + 1] = None if l + 1 < L - 1 else gact[l + 1]
+            gx = None
+            if need_x:
+                plan = levels[0][0]
+                I = plan.input_size
+                gx_t = torch.empty(I, Bp, device=dev, dtype=torch.float32)
+                _native.call("dl_dwn_bwd_input_t", addr[0], gact[0], 1, 1.0, efd[0], plan.inv_ptr_virtual,
+                             plan.inv_ent8_virtual, gx_t, I, plan.n, Bp)
+                if geom is None:
+                    gx = _t_to_rows(gx_t, B)
+                else:
+                    gx = torch.empty(geom.B, geom.C, geom.H, geom.W, device=dev, dtype=torch.float32)
+                    _native.call("dl_fold_t", gx_t, gx, *geom.args(), Bp)
+            flat = torch.empty(total, device=dev, dtype=torch.float32)
+            _native.call("dl_sum_groups", partial, flat, total, total, groups)
+        grads = []
+        for l in range(L):
+            gt = None
+            if ctx.needs_input_grad[3 + l]:
+                gt = flat[offs[l]:offs[l + 1]].view(tables[l].shape)
+                scale = levels[l][3]
+                if scale is not None:
+                    gt = gt * (scale.reshape(-1, 1, 1) if isinstance(scale, torch.Tensor) else float(scale))
+            grads.append(gt)
+        return (gx, None, None, *grads)
 
 
 def dwn_levels_eval(x: torch.Tensor, levels, geom: Optional[PatchGeometry] = None) -> torch.Tensor:
