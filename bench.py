@@ -705,11 +705,30 @@ def run_train_layers(args):
         loss.backward()
         opt.step()
 
-    ms = _time_gpu(step, args.steps, max(args.warmup, 3), torch.empty(256 << 20, dtype=torch.uint8, device=device))
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    ms = _time_gpu(step, args.steps, max(args.warmup, 3), flush)
+
+    # the same layer objects behind DWNStack: one bit per activation between layers, still torch autograd + Adam
+    from difflut_b200.layers import DWNStack
+
+    head = GroupSum(k=CLASSES, tau=TAU, use_randperm=False)
+    stack = DWNStack(layers, encoder=enc).train()
+    opt2 = torch.optim.Adam(stack.parameters(), lr=LR)
+
+    def step_stack():
+        opt2.zero_grad(set_to_none=True)
+        loss = torch.nn.functional.cross_entropy(head(stack(xd)), labels)
+        loss.backward()
+        opt2.step()
+
+    ms_stack = _time_gpu(step_stack, args.steps, max(args.warmup, 3), flush)
     print(json.dumps({"metric": METRIC + " (per-layer API)", "value": GLOBAL_BATCH / (ms * 1e-3), "unit": "samples/s",
                       "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
                       "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-                      "data": "synthetic", "config": _config({"mode": "layer API: fp32 rows between layers, torch autograd + Adam"})}),
+                      "data": "synthetic", "config": _config({"mode": "layer API: fp32 rows between layers, torch autograd + Adam"}),
+                      "dwn_stack": {"ms_per_step": ms_stack, "value": GLOBAL_BATCH / (ms_stack * 1e-3),
+                                    "mode": "same layers behind DWNStack(layers, encoder): bit-packed between layers, "
+                                            "torch autograd + torch.optim.Adam"}}),
           flush=True)
 
 

@@ -207,6 +207,14 @@ class DWNLayerFunction(torch.autograd.Function):
         return gx, (gt if need_t else None), None, None, None, None, None
 
 
+class PackedInput:
+    """Marks the first argument of DWNStackFunction as already bit-packed feature-major rows
+    (int32 (I, Bp/32), e.g. `ThermometerEncoder.encode_packed_t`) holding `batch` samples."""
+
+    def __init__(self, batch: int):
+        self.B = int(batch)
+
+
 class DWNStackFunction(torch.autograd.Function):
     """Consecutive DWN layers (output_dim 1, n <= 6) as one autograd node, bit-packed from end to end.
 
@@ -215,27 +223,38 @@ class DWNStackFunction(torch.autograd.Function):
     only there; the backward runs one fused kernel per level (pull the output gradient from the level
     above, form the addresses, accumulate the table gradient) and never goes back to rows in between.
     Same arithmetic as applying DWNLayerFunction level after level (difflut/nodes/dwn_node.py:58-229 per
-    node).  `levels` is a list of (plan, alpha, beta, stable_scale); x is (B, I) rows, or with `geom` an
-    image batch whose patches are the samples; `tables` are the levels' (N, 1, 2^n) tables.
+    node).  `levels` is a list of (plan, alpha, beta, stable_scale); x is (B, I) rows, or with a
+    PatchGeometry as `geom` an image batch whose patches are the samples, or with a PackedInput already
+    packed bits (no input gradient then); `tables` are the levels' (N, 1, 2^n) tables.
     """
 
     @staticmethod
     def forward(ctx, x, levels, geom, *tables):
-        x = x.contiguous().float()
         tables = [t.contiguous().float() for t in tables]
-        if geom is None:
+        packed = isinstance(geom, PackedInput)
+        if packed:
+            B, I = geom.B, x.shape[0]
+            geom = None
+        elif geom is None:
+            x = x.contiguous().float()
             B, I = x.shape
         else:
+            x = x.contiguous().float()
             B, I = geom.S, geom.F
         Bp = _native.padded_batch(B)
         Wp = Bp // 32
         dev = x.device
         with torch.cuda.device(dev):
-            bits = [torch.empty(I, Wp, device=dev, dtype=torch.int32)]
-            if geom is None:
-                _native.call("dl_pack_rows_to_t", x, bits[0], B, I, Bp, 0.5)
+            if packed:
+                if x.dtype != torch.int32 or tuple(x.shape) != (I, Wp) or not x.is_contiguous():
+                    raise ValueError(f"packed input must be contiguous int32 ({I}, {Wp})")
+                bits = [x]
             else:
-                _native.call("dl_unfold_pack_t", x, bits[0], *geom.args(), 0.5, Bp)
+                bits = [torch.empty(I, Wp, device=dev, dtype=torch.int32)]
+                if geom is None:
+                    _native.call("dl_pack_rows_to_t", x, bits[0], B, I, Bp, 0.5)
+                else:
+                    _native.call("dl_unfold_pack_t", x, bits[0], *geom.args(), 0.5, Bp)
             for (plan, _, _, _), tab in zip(levels[:-1], tables[:-1]):
                 masks = torch.empty(plan.N, device=dev, dtype=torch.int64)
                 _native.call("dl_dwn_prepare", tab, None, masks, plan.N, plan.n, 0.0, 0.0)
@@ -323,18 +342,27 @@ def dwn_levels_eval(x: torch.Tensor, levels, geom: Optional[PatchGeometry] = Non
     `levels` is a list of (tables (N, O, 2^n), plan); the output of one level is the input of the next.
     x is (B, I) rows, or with `geom` an image batch whose patches are the samples.  Returns the last
     level's fp32 {0,1} rows (dwn_node.py:457-483 applied layer after layer)."""
-    x = x.contiguous().float()
-    if geom is None:
+    packed = isinstance(geom, PackedInput)
+    if packed:
+        B, I = geom.B, x.shape[0]
+    elif geom is None:
+        x = x.contiguous().float()
         B, I = x.shape
     else:
+        x = x.contiguous().float()
         B, I = geom.S, geom.F
     Bp = _native.padded_batch(B)
     with torch.cuda.device(x.device):
-        bits = torch.empty(I, Bp // 32, device=x.device, dtype=torch.int32)
-        if geom is None:
-            _native.call("dl_pack_rows_to_t", x, bits, B, I, Bp, 0.5)
+        if packed:
+            if x.dtype != torch.int32 or tuple(x.shape) != (I, Bp // 32) or not x.is_contiguous():
+                raise ValueError(f"packed input must be contiguous int32 ({I}, {Bp // 32})")
+            bits = x
         else:
-            _native.call("dl_unfold_pack_t", x, bits, *geom.args(), 0.5, Bp)
+            bits = torch.empty(I, Bp // 32, device=x.device, dtype=torch.int32)
+            if geom is None:
+                _native.call("dl_pack_rows_to_t", x, bits, B, I, Bp, 0.5)
+            else:
+                _native.call("dl_unfold_pack_t", x, bits, *geom.args(), 0.5, Bp)
         for tables, plan in levels:
             tables = tables.detach().contiguous().float()
             NO, n = plan.N * plan.O, plan.n

@@ -726,3 +726,57 @@ def test_wide_materialised_path_equals_fused_layer(dev):
     gxm, gl = O.dwn_backward(xm, tab, gy.cpu().reshape(B, N, 2), layer.alpha, layer.beta)
     torch.testing.assert_close(gta.cpu(), gl, rtol=1e-5, atol=1e-6)
     torch.testing.assert_close(ga.cpu(), O.gather_mapping_backward(gxm, layer._mapping_indices.cpu(), I), rtol=1e-4, atol=1e-6)
+
+
+def test_dwn_stack_equals_sequential_layers(dev):
+    """DWNStack(layers) = nn.Sequential(*layers): same outputs and gradients (rows in), also with the
+    encoder folded in, in eval mode, and for DWNStable layers."""
+    from difflut_b200.encoder import ThermometerEncoder
+    from difflut_b200.layers import DWNStack, RandomLayer
+    from difflut_b200.nodes import DWNNode, DWNStableNode, NodeConfig
+
+    gen = torch.Generator().manual_seed(5)
+    B, F, Tb = 1500, 10, 4
+    x = torch.rand(B, F, generator=gen)
+    enc = ThermometerEncoder(num_bits=Tb).fit(x).to(dev)
+    for node in (DWNNode, DWNStableNode):
+        layers, I = [], F * Tb
+        for li, N in enumerate((90, 48, 17)):
+            l = RandomLayer(I, N, node, NodeConfig(input_dim=6, output_dim=1), seed=li).to(dev)
+            with torch.no_grad():
+                for p in l.parameters():
+                    if p.dim() == 3:
+                        p.copy_(torch.randn(p.shape, generator=gen).to(dev))
+            layers.append(l)
+            I = N
+        seq = torch.nn.Sequential(*layers).train()
+        stack = DWNStack(layers).train()
+        rows = enc(x.to(dev))
+        gy = torch.randn(B, 17, generator=gen).to(dev)
+        xa = rows.clone().requires_grad_(True)
+        ya = seq(xa)
+        ya.backward(gy)
+        ref = [p.grad.clone() for p in seq.parameters() if p.dim() == 3]
+        gxa = xa.grad.clone()
+        for p in seq.parameters():
+            p.grad = None
+        xb = rows.clone().requires_grad_(True)
+        yb = stack(xb)
+        assert torch.equal(ya, yb)
+        yb.backward(gy)
+        torch.testing.assert_close(xb.grad, gxa, rtol=1e-4, atol=1e-6)
+        for r, p in zip(ref, [p for p in stack.parameters() if p.dim() == 3]):
+            torch.testing.assert_close(p.grad, r, rtol=1e-4, atol=1e-6)
+            p.grad = None
+        # encoder folded in: raw features in, same outputs and table gradients
+        fused = DWNStack(layers, encoder=enc).train()
+        yc = fused(x.to(dev))
+        assert torch.equal(yc, ya)
+        yc.backward(gy)
+        for r, p in zip(ref, [p for p in fused.parameters() if p.dim() == 3]):
+            torch.testing.assert_close(p.grad, r, rtol=1e-4, atol=1e-6)
+        assert torch.equal(stack.eval()(rows), seq.eval()(rows))
+        assert torch.equal(fused.eval()(x.to(dev)), seq(rows))
+        assert set(stack.state_dict()) == {"layers." + k for k in seq.state_dict()}
+    with pytest.raises(ValueError):
+        DWNStack([])
