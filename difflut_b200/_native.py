@@ -19,6 +19,7 @@ LIB_PATH = os.path.join(_HERE, "_lib", "libdifflut_b200.so")
 SIGNATURES = {
     "dl_thermo_rows": "ppplll s",
     "dl_thermo_pack_t": "pppllll s",
+    "dl_thermo_pack_s": "pppllll s",
     "dl_thermo_pack_rows": "ppplll s",
     "dl_pack_rows_to_t": "pplllf s",
     "dl_f32_rows_to_t": "pplll s",

@@ -79,6 +79,49 @@ bits_swizzle_kernel(const uint32_t* __restrict__ nat, uint32_t* __restrict__ swz
     }
 }
 
+// Thermometer compare-and-pack straight into the chunk-interleaved layout (see bits_swizzle_kernel).
+// A CTA owns one 1024-sample block and 8 features: the block's values go to shared memory feature-major,
+// index s + 4*(s/128) inside a feature row (row pitch 1060), which makes both the fill (lane = 8 features
+// x 4 samples) and the read-out (lane = chunk c + 8r reading sample 128c + 4w + r) bank-conflict free.
+// Warp k then owns feature k: it keeps the 32 values of each word position w in registers and, per
+// threshold, one ballot per w yields word w directly in the interleaved bit order; lane w keeps it and
+// the 32 words of a (feature, threshold) row leave as one coalesced 128-byte store.
+constexpr int SWZ_FEATS = 8, SWZ_PITCH = 1060;
+
+__global__ void __launch_bounds__(256)
+thermo_pack_s_kernel(const float* __restrict__ x, const float* __restrict__ thr, uint32_t* __restrict__ bits_s,
+                     int64_t B, int64_t F, int T, int64_t G) {
+    __shared__ float tile[SWZ_FEATS * SWZ_PITCH];
+    const int64_t g = blockIdx.x;
+    const int64_t f0 = (int64_t)blockIdx.y * SWZ_FEATS;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    {
+        const int fl = threadIdx.x & 7;
+        const float nan = __int_as_float(0x7fc00000);  // compares false: padding packs as 0
+        for (int s = threadIdx.x >> 3; s < 1024; s += 32) {
+            const int64_t b = g * 1024 + s, f = f0 + fl;
+            tile[fl * SWZ_PITCH + s + 4 * (s >> 7)] = (b < B && f < F) ? __ldg(x + b * F + f) : nan;
+        }
+    }
+    __syncthreads();
+    const int64_t f = f0 + warp;
+    if (f >= F) return;
+    const int c = lane & 7, r = lane >> 3;
+    float v[32];
+#pragma unroll
+    for (int w = 0; w < 32; ++w) v[w] = tile[warp * SWZ_PITCH + 132 * c + 4 * w + r];
+    for (int t = 0; t < T; ++t) {
+        const float th = __ldg(&thr[f * T + t]);
+        uint32_t mine = 0;
+#pragma unroll
+        for (int w = 0; w < 32; ++w) {
+            const uint32_t word = __ballot_sync(0xffffffffu, v[w] > th);
+            if (lane == w) mine = word;
+        }
+        bits_s[((f * T + t) * G + g) * 32 + lane] = mine;
+    }
+}
+
 // rows in, fp32 rows out: out[b, f*T+t] = x[b,f] > thr[f,t]
 __global__ void thermo_rows_kernel(const float* __restrict__ x, const float* __restrict__ thr,
                                    float* __restrict__ out, int64_t B, int64_t F, int T) {
@@ -236,6 +279,18 @@ DL_EXPORT int dl_bits_swizzle_t(const uint32_t* bits_t, uint32_t* bits_s, int64_
     const int64_t G = dl_ceil_div(Bp, 1024);
     const int64_t blocks = dl_min64(dl_ceil_div(F * G, 8), (int64_t)DL_NUM_SMS * 16);
     bits_swizzle_kernel<<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(bits_t, bits_s, F, Bp / 32, G);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_thermo_pack_s(const float* x, const float* thr, uint32_t* bits_s, int64_t B, int64_t F,
+                               int64_t T, int64_t Bp, dl_stream_t stream) {
+    DL_REQUIRE(x && thr && bits_s && B > 0 && F > 0 && T > 0);
+    DL_REQUIRE(Bp >= B && Bp % DL_BATCH_ALIGN == 0);
+    const int64_t G = dl_ceil_div(Bp, 1024);
+    const int64_t fy = dl_ceil_div(F, SWZ_FEATS);
+    DL_REQUIRE(fy <= 65535);
+    dim3 grid((unsigned)G, (unsigned)fy);
+    thermo_pack_s_kernel<<<grid, 256, 0, dl_cast(stream)>>>(x, thr, bits_s, B, F, (int)T, G);
     return dl_launch_status();
 }
 

@@ -149,8 +149,6 @@ class DWNNetwork:
             # use the same buffers with Bp/32 words per row
             Wp = int(_native.lib().dl_swizzled_words(Bp)) if self.swizzle else Bp // 32
             self.Bp_bits = Wp * 32
-            self.bits_nat = (torch.empty(self.I[0], Bp // 32, device=dev, dtype=torch.int32)
-                             if self.swizzle else None)
             self.bits = [torch.empty(self.I[0], Wp, device=dev, dtype=torch.int32)]
             for N in self.N[:-1]:
                 self.bits.append(torch.empty(N, Wp, device=dev, dtype=torch.int32))
@@ -195,8 +193,7 @@ class DWNNetwork:
     def _forward(self, x: torch.Tensor, B: int) -> None:
         Bp = self.Bp
         if self.swizzle:
-            _native.call("dl_thermo_pack_t", x, self.thr, self.bits_nat, B, self.F, self.T, Bp)
-            _native.call("dl_bits_swizzle_t", self.bits_nat, self.bits[0], self.I[0], Bp)
+            _native.call("dl_thermo_pack_s", x, self.thr, self.bits[0], B, self.F, self.T, Bp)
         else:
             _native.call("dl_thermo_pack_t", x, self.thr, self.bits[0], B, self.F, self.T, Bp)
         last = len(self.layers) - 1
@@ -324,7 +321,7 @@ class DWNNetwork:
         backward = (L + sums) if self.fused_backward else (L + (L - 1))
         prepare = 2 * (1 if self.uniform else L)
         update = 4 if self.peer_optimizer else 2  # barrier, state advance, reduce+Adam+broadcast, barrier
-        return prepare + 1 + (1 if self.swizzle else 0) + (L - 1) + 2 + 2 + backward + update
+        return prepare + 1 + (L - 1) + 2 + 2 + backward + update
 
     def train_step(self, x: torch.Tensor, labels: torch.Tensor, use_graph: bool = False) -> torch.Tensor:
         """One optimisation step on this rank's shard (x (B, F) fp32, labels (B,) integer).

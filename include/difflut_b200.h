@@ -318,6 +318,10 @@ int dl_dwn_fwd_groupsum_noalloc_t(const uint32_t* in_bits_t, const int32_t* map,
  * points are the *_t ones reading interleaved input bits; every other argument (gradients,
  * addresses, logits) keeps the natural sample order. */
 int64_t dl_swizzled_words(int64_t Bp);
+/* dl_thermo_pack_t (difflut/encoder/thermometer.py:89-116) writing the interleaved layout directly:
+ * bits_s [F*T][dl_swizzled_words(Bp)]. */
+int dl_thermo_pack_s(const float* x, const float* thr, uint32_t* bits_s, int64_t B, int64_t F,
+                     int64_t T, int64_t Bp, dl_stream_t stream);
 int dl_bits_swizzle_t(const uint32_t* bits_t, uint32_t* bits_s, int64_t F, int64_t Bp, dl_stream_t stream);
 int dl_dwn_fwd_groupsum_s(const uint32_t* in_bits_s, const int32_t* map, const float* tables,
                           float* partial, float* logits_t, int64_t N, int64_t n, int64_t k, float tau,

@@ -650,6 +650,17 @@ def test_bits_swizzle_layout(dev, B):
             for r in range(4):
                 want[:, g * 32:(g + 1) * 32] |= (blk[c, :, r, :].T << np.uint32(c + 8 * r)).astype(np.uint32)
     assert np.array_equal(got, want)
+    # the encoder's direct-to-interleaved kernel = natural pack followed by the conversion
+    Fx, Tb = 11, 5
+    x = torch.rand(B, Fx, generator=gen)
+    thr = torch.sort(torch.rand(Fx, Tb, generator=gen), dim=1).values.contiguous()
+    nat2 = torch.empty(Fx * Tb, Bp // 32, dtype=torch.int32, device=dev)
+    _native.call("dl_thermo_pack_t", x.to(dev), thr.to(dev), nat2, B, Fx, Tb, Bp)
+    via = torch.empty(Fx * Tb, Ws, dtype=torch.int32, device=dev)
+    _native.call("dl_bits_swizzle_t", nat2, via, Fx * Tb, Bp)
+    direct = torch.full((Fx * Tb, Ws), -1, dtype=torch.int32, device=dev)
+    _native.call("dl_thermo_pack_s", x.to(dev), thr.to(dev), direct, B, Fx, Tb, Bp)
+    assert torch.equal(direct, via)
 
 
 # ------------------------------------------------------------------------------ tensor-core GEMM
