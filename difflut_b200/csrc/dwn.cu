@@ -165,12 +165,15 @@ dwn_prepare_full_kernel(const float* __restrict__ tables, float* __restrict__ ef
 // A leaf turns two adjacent truth-table bits into all-zero / all-one masks and selects with
 // input 0; every inner node is one select on input LVL.  BASE and LVL are compile-time, so
 // every shift is an immediate and the tree is 2^n - 1 three-input logic ops per word.
-template <int LVL, int BASE>
+// SMEM: the leaf masks come ready-made from shared memory (cm[p] = the all-zero / all-one masks of table
+// bits 2p and 2p+1, expanded once per node by the warp) instead of being re-derived by every thread,
+// which moves about a third of the kernel's logic ops off the integer pipe.
+template <int LVL, int BASE, bool SMEM>
 struct MuxTree {
-    __device__ __forceinline__ static void eval(uint32_t lo, uint32_t hi, const uint4* x, uint4& out) {
+    __device__ __forceinline__ static void eval(uint32_t lo, uint32_t hi, const uint2* cm, const uint4* x, uint4& out) {
         uint4 a, b;
-        MuxTree<LVL - 1, BASE>::eval(lo, hi, x, a);
-        MuxTree<LVL - 1, BASE + (1 << LVL)>::eval(lo, hi, x, b);
+        MuxTree<LVL - 1, BASE, SMEM>::eval(lo, hi, cm, x, a);
+        MuxTree<LVL - 1, BASE + (1 << LVL), SMEM>::eval(lo, hi, cm, x, b);
         const uint4 s = x[LVL];
         out.x = (a.x & ~s.x) | (b.x & s.x);
         out.y = (a.y & ~s.y) | (b.y & s.y);
@@ -178,12 +181,19 @@ struct MuxTree {
         out.w = (a.w & ~s.w) | (b.w & s.w);
     }
 };
-template <int BASE>
-struct MuxTree<0, BASE> {
-    __device__ __forceinline__ static void eval(uint32_t lo, uint32_t hi, const uint4* x, uint4& out) {
-        const uint32_t word = BASE < 32 ? lo : hi;
-        const uint32_t c0 = 0u - ((word >> (BASE & 31)) & 1u);
-        const uint32_t c1 = 0u - ((word >> ((BASE + 1) & 31)) & 1u);
+template <int BASE, bool SMEM>
+struct MuxTree<0, BASE, SMEM> {
+    __device__ __forceinline__ static void eval(uint32_t lo, uint32_t hi, const uint2* cm, const uint4* x, uint4& out) {
+        uint32_t c0, c1;
+        if (SMEM) {
+            const uint2 c = cm[BASE >> 1];
+            c0 = c.x;
+            c1 = c.y;
+        } else {
+            const uint32_t word = BASE < 32 ? lo : hi;
+            c0 = 0u - ((word >> (BASE & 31)) & 1u);
+            c1 = 0u - ((word >> ((BASE + 1) & 31)) & 1u);
+        }
         const uint4 s = x[0];
         out.x = (c0 & ~s.x) | (c1 & s.x);
         out.y = (c0 & ~s.y) | (c1 & s.y);
@@ -196,20 +206,33 @@ struct MuxTree<0, BASE> {
 // input row.  Node tiles are the fast grid dimension and word-group tiles the slow one, so the CTAs
 // resident at any time work on one slab of the batch (its input rows stay in L2 while all nodes
 // gather from them); both are walked with grid-stride loops (no index division).
-template <int NIN>
+// SMEM needs blockDim.x to be a multiple of 32, so that all lanes of a warp work on the same node.
+template <int NIN, bool SMEM>
 __global__ void __launch_bounds__(256, 2)
 dwn_fwd_bits_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __restrict__ map,
                     const uint64_t* __restrict__ masks, uint32_t* __restrict__ out_bits, int N, int Q) {
+    __shared__ uint2 cm_all[SMEM ? 8 : 1][32];
+    const int tid = threadIdx.y * blockDim.x + threadIdx.x;
+    const int lane = tid & 31;
+    uint2* cm = cm_all[SMEM ? (tid >> 5) : 0];
     const int64_t Wp = (int64_t)Q << 2;
-    for (int q = blockIdx.y * blockDim.x + threadIdx.x; q < Q; q += gridDim.y * blockDim.x) {
+    // SMEM: the word-group loop runs to a warp-uniform bound so that whole warps reach the __syncwarp
+    const int qend = SMEM ? ((Q + 31) & ~31) : Q;
+    for (int q = blockIdx.y * blockDim.x + threadIdx.x; q < qend; q += gridDim.y * blockDim.x) {
         for (int j = blockIdx.x * blockDim.y + threadIdx.y; j < N; j += gridDim.x * blockDim.y) {
             const uint64_t m = __ldg(&masks[j]);
+            if (SMEM) {
+                __syncwarp();
+                cm[lane] = make_uint2(0u - (uint32_t)((m >> (2 * lane)) & 1u), 0u - (uint32_t)((m >> (2 * lane + 1)) & 1u));
+                __syncwarp();
+                if (q >= Q) continue;
+            }
             uint4 x[NIN];
 #pragma unroll
             for (int i = 0; i < NIN; ++i)
                 x[i] = __ldg(reinterpret_cast<const uint4*>(in_bits + (int64_t)__ldg(&map[j * NIN + i]) * Wp) + q);
             uint4 o;
-            MuxTree<NIN - 1, 0>::eval((uint32_t)m, (uint32_t)(m >> 32), x, o);
+            MuxTree<NIN - 1, 0, SMEM>::eval((uint32_t)m, (uint32_t)(m >> 32), cm, x, o);
             reinterpret_cast<uint4*>(out_bits + (int64_t)j * Wp)[q] = o;
         }
     }
@@ -916,14 +939,22 @@ DL_EXPORT int dl_dwn_fwd_bits_t(const uint32_t* in_bits_t, const int32_t* map, c
     dim3 grid((unsigned)gn, (unsigned)gq);
     cudaStream_t s = dl_cast(stream);
     const int Ni = (int)N;
+#define DL_FWD_BITS(NN)                                                                                      \
+    do {                                                                                                     \
+        if (bx >= 32)                                                                                        \
+            dwn_fwd_bits_kernel<NN, true><<<grid, block, 0, s>>>(in_bits_t, map, masks, out_bits_t, Ni, Q);  \
+        else                                                                                                 \
+            dwn_fwd_bits_kernel<NN, false><<<grid, block, 0, s>>>(in_bits_t, map, masks, out_bits_t, Ni, Q); \
+    } while (0)
     switch (n) {
-        case 1: dwn_fwd_bits_kernel<1><<<grid, block, 0, s>>>(in_bits_t, map, masks, out_bits_t, Ni, Q); break;
-        case 2: dwn_fwd_bits_kernel<2><<<grid, block, 0, s>>>(in_bits_t, map, masks, out_bits_t, Ni, Q); break;
-        case 3: dwn_fwd_bits_kernel<3><<<grid, block, 0, s>>>(in_bits_t, map, masks, out_bits_t, Ni, Q); break;
-        case 4: dwn_fwd_bits_kernel<4><<<grid, block, 0, s>>>(in_bits_t, map, masks, out_bits_t, Ni, Q); break;
-        case 5: dwn_fwd_bits_kernel<5><<<grid, block, 0, s>>>(in_bits_t, map, masks, out_bits_t, Ni, Q); break;
-        default: dwn_fwd_bits_kernel<6><<<grid, block, 0, s>>>(in_bits_t, map, masks, out_bits_t, Ni, Q); break;
+        case 1: DL_FWD_BITS(1); break;
+        case 2: DL_FWD_BITS(2); break;
+        case 3: DL_FWD_BITS(3); break;
+        case 4: DL_FWD_BITS(4); break;
+        case 5: DL_FWD_BITS(5); break;
+        default: DL_FWD_BITS(6); break;
     }
+#undef DL_FWD_BITS
     return dl_launch_status();
 }
 
