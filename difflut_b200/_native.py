@@ -22,6 +22,7 @@ SIGNATURES = {
     "dl_thermo_pack_s": "pppllll s",
     "dl_thermo_pack_rows": "ppplll s",
     "dl_pack_rows_to_t": "pplllf s",
+    "dl_pack_t_to_t": "ppllllf s",
     "dl_f32_rows_to_t": "pplll s",
     "dl_f32_t_to_rows": "pplll s",
     "dl_bits_t_to_rows": "pplll s",

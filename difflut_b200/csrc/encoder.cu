@@ -122,6 +122,29 @@ thermo_pack_s_kernel(const float* __restrict__ x, const float* __restrict__ thr,
     }
 }
 
+// Feature-major fp32 [F][ld] (B valid samples per row) -> packed feature-major bits [F][Wp], bit = value >=
+// threshold.  A warp takes 128 samples of one row: four coalesced loads, four ballots, lanes 0..3 store.
+__global__ void __launch_bounds__(256)
+pack_t_to_t_kernel(const float* __restrict__ src_t, uint32_t* __restrict__ bits_t, int64_t F, int64_t B,
+                   int64_t ld, int64_t Wp, float threshold) {
+    const int lane = threadIdx.x & 31;
+    const int64_t Q = Wp >> 2;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t item = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; item < F * Q; item += nwarps) {
+        const int64_t f = item / Q, q = item - f * Q;
+        const float* row = src_t + f * ld;
+        uint32_t mine = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int64_t b = (q * 4 + k) * 32 + lane;
+            const bool bit = b < B && __ldg(row + b) >= threshold;
+            const uint32_t word = __ballot_sync(0xffffffffu, bit);
+            if (lane == k) mine = word;
+        }
+        if (lane < 4) bits_t[f * Wp + q * 4 + lane] = mine;
+    }
+}
+
 // rows in, fp32 rows out: out[b, f*T+t] = x[b,f] > thr[f,t]
 __global__ void thermo_rows_kernel(const float* __restrict__ x, const float* __restrict__ thr,
                                    float* __restrict__ out, int64_t B, int64_t F, int T) {
@@ -310,6 +333,16 @@ DL_EXPORT int dl_pack_rows_to_t(const float* x, uint32_t* bits_t, int64_t B, int
     dim3 grid((unsigned)dl_ceil_div(Bp, TILE_B), (unsigned)dl_ceil_div(F, TILE_F));
     pack_t_kernel<1><<<grid, PACK_THREADS, 0, dl_cast(stream)>>>(x, nullptr, threshold, bits_t, B, F,
                                                                 1, Bp / 32);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_pack_t_to_t(const float* src_t, uint32_t* bits_t, int64_t F, int64_t B, int64_t ld, int64_t Bp,
+                             float threshold, dl_stream_t stream) {
+    DL_REQUIRE(src_t && bits_t && F > 0 && B > 0 && ld >= B);
+    DL_REQUIRE(Bp >= B && Bp % DL_BATCH_ALIGN == 0);
+    const int64_t items = F * (Bp / 128);
+    const int64_t blocks = dl_min64(dl_ceil_div(items, 8), (int64_t)DL_NUM_SMS * 16);
+    pack_t_to_t_kernel<<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(src_t, bits_t, F, B, ld, Bp / 32, threshold);
     return dl_launch_status();
 }
 

@@ -399,6 +399,23 @@ to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, _
     }
 }
 
+// The common case without transposition or residual: four elements per thread, 16-byte loads, 8-byte stores.
+__global__ void __launch_bounds__(256)
+to_bf16_vec_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int64_t rows, int64_t cq,
+                   int64_t ld) {
+    const int64_t total = rows * cq;
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total;
+         t += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = t / cq, q = t - r * cq;
+        const float4 v = __ldg(reinterpret_cast<const float4*>(src) + t);
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 out;
+        out.x = *reinterpret_cast<uint32_t*>(&a);
+        out.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(dst + r * ld + q * 4) = out;
+    }
+}
+
 // bf16 (rows, cols) with row pitch ld_src -> transposed bf16 (cols, rows) with row pitch ld_dst
 __global__ void __launch_bounds__(256)
 bf16_transpose_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst, int64_t rows,
@@ -459,6 +476,13 @@ DL_EXPORT int dl_softmax_bwd_rows(const float* W, const float* gS, float tau, fl
 DL_EXPORT int dl_f32_to_bf16(const float* src, void* dst_hi, void* dst_lo, int64_t rows, int64_t cols, int64_t ld,
                              int transpose, dl_stream_t stream) {
     DL_REQUIRE(src && dst_hi && rows > 0 && cols > 0 && ld >= (transpose ? rows : cols));
+    if (!transpose && dst_lo == nullptr && cols % 4 == 0 && ld % 4 == 0 &&
+        reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(dst_hi) % 8 == 0) {
+        const int64_t blocks = dl_min64(dl_ceil_div(rows * (cols / 4), 256), (int64_t)DL_NUM_SMS * 16);
+        to_bf16_vec_kernel<<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(src, static_cast<__nv_bfloat16*>(dst_hi),
+                                                                        rows, cols / 4, ld);
+        return dl_launch_status();
+    }
     dim3 grid((unsigned)dl_ceil_div(cols, 32), (unsigned)dl_ceil_div(rows, 32));
     DL_REQUIRE(grid.y <= 65535);
     to_bf16_kernel<<<grid, 256, 0, dl_cast(stream)>>>(src, static_cast<__nv_bfloat16*>(dst_hi),

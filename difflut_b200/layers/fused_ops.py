@@ -110,6 +110,11 @@ class PatchGeometry:
         return (self.B, self.C, self.H, self.W, self.kh, self.kw, self.sh, self.sw, self.ph, self.pw)
 
 
+class FeatureMajorInput:
+    """Marks the input of DWNLayerFunction as fp32 feature-major (I, B) with B a multiple of 128 (what a
+    contraction with swapped operands produces); the input gradient comes back in the same layout."""
+
+
 class PatchFunction(torch.autograd.Function):
     """x (B, C, H, W) -> patches (B*OH*OW, C*kh*kw) fp32 rows; backward folds the gradient back."""
 
@@ -148,7 +153,12 @@ class DWNLayerFunction(torch.autograd.Function):
                 geom: Optional[PatchGeometry] = None):
         x = x.contiguous().float()
         tables = tables.contiguous().float()
-        if geom is None:
+        feature_major = isinstance(geom, FeatureMajorInput)
+        if feature_major:
+            I, B = x.shape
+            if B % 128 != 0:
+                raise ValueError("feature-major input needs a batch that is a multiple of 128")
+        elif geom is None:
             B, I = x.shape
         else:
             B, I = geom.S, geom.F
@@ -156,7 +166,9 @@ class DWNLayerFunction(torch.autograd.Function):
         Bp = _native.padded_batch(B)
         with torch.cuda.device(x.device):
             bits = torch.empty(I, Bp // 32, device=x.device, dtype=torch.int32)
-            if geom is None:
+            if feature_major:
+                _native.call("dl_pack_t_to_t", x, bits, I, B, B, Bp, 0.5)
+            elif geom is None:
                 _native.call("dl_pack_rows_to_t", x, bits, B, I, Bp, 0.5)
             else:
                 _native.call("dl_unfold_pack_t", x, bits, *geom.args(), 0.5, Bp)
@@ -199,7 +211,9 @@ class DWNLayerFunction(torch.autograd.Function):
                 gx_t = torch.empty(I, Bp, device=g.device, dtype=torch.float32)
                 _native.call("dl_dwn_bwd_input_t", addr, g_t, 1, 1.0, efd, plan.inv_ptr_virtual,
                              plan.inv_ent8_virtual, gx_t, I, n, Bp)
-                if geom is None:
+                if isinstance(geom, FeatureMajorInput):
+                    gx = gx_t  # (I, B): B == Bp
+                elif geom is None:
                     gx = _t_to_rows(gx_t, B)
                 else:
                     gx = torch.empty(geom.B, geom.C, geom.H, geom.W, device=g.device, dtype=torch.float32)

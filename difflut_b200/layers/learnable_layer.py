@@ -139,7 +139,26 @@ class LearnableLayer(BaseLUTLayer):
         if not self.training and self._stacked in ("dwn_stable", "hybrid"):
             idx = self.mapping.hard_indices().view(self.output_size, self.n)
             return dwn_layer_eval(x, self.stable_tables(), self._plan_for(idx, x.device, "hard"))
+        if (self.training and self._stacked in ("dwn", "dwn_stable") and self.n <= FAST_PATH_MAX_N
+                and x.shape[0] % 128 == 0):
+            return self._forward_feature_major(x)
         return self._run_nodes(self.get_mapping(x))
+
+    def _forward_feature_major(self, x: torch.Tensor) -> torch.Tensor:
+        """Training with DWN-type nodes: the soft selection is contracted with swapped operands, so the
+        selected values arrive feature-major (N*n, B), which is what the node kernels read, and their
+        gradient leaves in the layout the weight-gradient contraction reads.  Same arithmetic as
+        `_run_nodes(get_mapping(x))`."""
+        from ..nodes.dwn_node import _identity_plan
+        from .fused_ops import DWNLayerFunction, FeatureMajorInput
+        from .soft_select import soft_select_t
+
+        mapped_t = soft_select_t(x, self.mapping.W, self.mapping.tau)
+        plan = _identity_plan(self.output_size, self.n, self.output_dim_per_node, x.device)
+        if self._stacked == "dwn":
+            return DWNLayerFunction.apply(mapped_t, self.luts, plan, self.alpha, self.beta, None, FeatureMajorInput())
+        scales = self.gradient_scale.detach().float().repeat_interleave(self.output_dim_per_node)
+        return DWNLayerFunction.apply(mapped_t, self.stable_tables(), plan, 0.0, 0.0, scales, FeatureMajorInput())
 
     def get_mapping_matrix(self) -> torch.Tensor:
         with torch.no_grad():

@@ -104,6 +104,96 @@ class SoftSelectFunction(torch.autograd.Function):
         return gx, gW, None, None, None
 
 
+class SoftSelectTFunction(torch.autograd.Function):
+    """The same contraction with the operands swapped: (B, I), (M, I) -> (M, B) feature-major,
+    `softmax(W / tau) @ x.T`, which is the layout the DWN layer kernels read and write.  The backward takes
+    the gradient in that layout, so the gradient of the node inputs goes into the weight-gradient
+    contraction as it leaves the node kernels: no transposes of (B, M) tensors in either direction.
+    B must be a multiple of 128."""
+
+    @staticmethod
+    def forward(ctx, x, W, tau, splits, check):
+        x = x.contiguous().float()
+        W = W.contiguous().float()
+        B, I = x.shape
+        M = W.shape[0]
+        if B % 128 != 0:
+            raise ValueError("soft_select_t needs a batch that is a multiple of 128")
+        Ip = _round_up(I, 8)
+        dev = x.device
+        bf = torch.bfloat16
+        with torch.cuda.device(dev):
+            A = torch.zeros(B, splits * Ip, device=dev, dtype=bf)
+            Bm = torch.zeros(M, splits * Ip, device=dev, dtype=bf)
+            ld = splits * Ip
+            s_lo = Bm.data_ptr() + 2 * Ip if splits >= 2 else None
+            _native.call("dl_softmax_rows_bf16", W, tau, Bm, s_lo, ld, M, I)
+            x_lo = A.data_ptr() + 2 * 2 * Ip if splits >= 3 else None
+            _native.call("dl_f32_to_bf16", x, A, x_lo, B, I, ld, 0)
+            if splits >= 2:
+                A[:, Ip:Ip + I].copy_(A[:, :I])
+            if splits >= 3:
+                Bm[:, 2 * Ip:2 * Ip + I].copy_(Bm[:, :I])
+            out_t = torch.empty(M, B, device=dev, dtype=torch.float32)
+            status = torch.zeros(1, device=dev, dtype=torch.int32)
+            _native.call("dl_gemm_bf16_tn", Bm, A, out_t, M, B, ld, status)
+            if check:
+                _check_status(status, "forward")
+        ctx.save_for_backward(x, W)
+        ctx.tau, ctx.check = float(tau), check
+        return out_t
+
+    @staticmethod
+    def backward(ctx, gy_t):
+        x, W = ctx.saved_tensors
+        B, I = x.shape
+        M = W.shape[0]
+        dev = x.device
+        bf = torch.bfloat16
+        gy_t = gy_t.contiguous().float()  # (M, B)
+        need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        gx = gW = None
+        with torch.cuda.device(dev):
+            status = torch.zeros(1, device=dev, dtype=torch.int32)
+            if need_w:
+                # gS (M, I) = gy_t (M, K=B) @ x (B, I): operands gy_t [M, K=B] as it is and x^T [I, K=B]
+                gyb = torch.empty(M, B, device=dev, dtype=bf)
+                _native.call("dl_f32_to_bf16", gy_t, gyb, None, M, B, B, 0)
+                xt = torch.zeros(I, B, device=dev, dtype=bf)
+                _native.call("dl_f32_to_bf16", x, xt, None, B, I, B, 1)
+                gS = torch.empty(M, I, device=dev, dtype=torch.float32)
+                _native.call("dl_gemm_bf16_tn", gyb, xt, gS, M, I, B, status)
+                del gyb, xt
+                gW = torch.empty(M, I, device=dev, dtype=torch.float32)
+                _native.call("dl_softmax_bwd_rows", W, gS, ctx.tau, gW, M, I)
+            if need_x:
+                # gx (B, I) = gy (B, M) @ S (M, I): operands gy [B, K=M] (a transpose of gy_t) and S^T [I, K=M]
+                Mp = _round_up(M, 8)
+                S = torch.empty(M, I, device=dev, dtype=bf)
+                _native.call("dl_softmax_rows_bf16", W, ctx.tau, S, None, I, M, I)
+                St = torch.zeros(I, Mp, device=dev, dtype=bf)
+                _native.call("dl_bf16_transpose", S, St, M, I, I, Mp)
+                del S
+                gyr = torch.zeros(B, Mp, device=dev, dtype=bf)
+                _native.call("dl_f32_to_bf16", gy_t, gyr, None, M, B, Mp, 1)
+                gx = torch.empty(B, I, device=dev, dtype=torch.float32)
+                _native.call("dl_gemm_bf16_tn", gyr, St, gx, B, I, Mp, status)
+            if ctx.check:
+                _check_status(status, "backward")
+        return gx, gW, None, None, None
+
+
+def soft_select_t(x: torch.Tensor, W: torch.Tensor, tau: float, splits: int = None, check: bool = True) -> torch.Tensor:
+    """(B, I), (M, I) -> (M, B) feature-major with autograd (B a multiple of 128); see soft_select."""
+    if not (x.is_cuda and W.is_cuda):
+        raise RuntimeError("difflut_b200 layers run on CUDA tensors only (no CPU fallback)")
+    if splits is None:
+        splits = FORWARD_SPLITS
+    if splits not in (1, 2, 3):
+        raise ValueError("splits must be 1, 2 or 3")
+    return SoftSelectTFunction.apply(x, W, float(tau), int(splits), bool(check))
+
+
 def soft_select(x: torch.Tensor, W: torch.Tensor, tau: float, splits: int = None, check: bool = True) -> torch.Tensor:
     """(B, I), (M, I) -> (B, M) with autograd.  `check` reads the kernels' status word back (one
     host synchronisation per call); pass False inside a captured or latency-critical region."""

@@ -77,6 +77,10 @@ int dl_f32_t_to_rows(const float* t, float* rows, int64_t B, int64_t F, int64_t 
 /* bits_t [F][Bp/32] -> fp32 rows (B, F) of {0,1}. */
 int dl_bits_t_to_rows(const uint32_t* bits_t, float* rows, int64_t B, int64_t F, int64_t Bp,
                       dl_stream_t stream);
+/* fp32 feature-major [F][ld] (B <= ld valid samples per row) -> bits_t [F][Bp/32], bit = value >=
+ * threshold (what dl_pack_rows_to_t does for rows; difflut/nodes/dwn_node.py:147). */
+int dl_pack_t_to_t(const float* src_t, uint32_t* bits_t, int64_t F, int64_t B, int64_t ld, int64_t Bp,
+                   float threshold, dl_stream_t stream);
 /* packed rows (B, Wr) uint32 (bit c%32 of word c/32 = column c) -> bits_t [F][Bp/32]. */
 int dl_bits_rows_to_t(const uint32_t* bits_rows, uint32_t* bits_t, int64_t B, int64_t F,
                       int64_t Wr, int64_t Bp, dl_stream_t stream);

@@ -445,6 +445,44 @@ def test_learnable_layer_matches_reference(golden, dev):
     assert abs(layer.tau - float(g["tau_500"][0])) < 1e-12
 
 
+def test_learnable_feature_major_path_equals_row_path(dev):
+    """Batches that are a multiple of 128 train through the swapped-operand contraction; same outputs and
+    gradients as the row-major path (bf16 contractions: 1e-2 of the gradient's scale), for DWN and
+    DWNStable nodes, and against the fp32 oracle."""
+    from difflut_b200.layers import LearnableLayer
+    from difflut_b200.nodes import DWNNode, DWNStableNode, NodeConfig
+
+    gen = torch.Generator().manual_seed(9)
+    B, I, N = 256, 72, 40
+    x = torch.bernoulli(torch.full((B, I), 0.5), generator=gen)
+    gy = torch.randn(B, N, generator=gen).to(dev)
+    for node in (DWNNode, DWNStableNode):
+        layer = LearnableLayer(I, N, node, NodeConfig(input_dim=6, output_dim=1)).to(dev).train()
+        with torch.no_grad():
+            layer.mapping.W.copy_((torch.randn(N * 6, I, generator=gen) * 2.0).to(dev))
+        xa = x.to(dev).requires_grad_(True)
+        ya = layer(xa)  # feature-major path
+        ya.backward(gy)
+        grads_a = {k: p.grad.clone() for k, p in layer.named_parameters() if p.grad is not None}
+        gxa = xa.grad.clone()
+        for p in layer.parameters():
+            p.grad = None
+        xb = x.to(dev).requires_grad_(True)
+        yb = layer._run_nodes(layer.get_mapping(xb))  # row-major path
+        assert float((ya != yb).float().mean()) < 1e-3  # same addresses up to selections that sit at 0.5
+        yb.backward(gy)
+        for k, p in layer.named_parameters():
+            if p.grad is None:
+                continue
+            scale = float(p.grad.abs().max())
+            torch.testing.assert_close(grads_a[k], p.grad, rtol=1e-2, atol=1e-2 * scale + 1e-12)
+        torch.testing.assert_close(gxa, xb.grad, rtol=1e-2, atol=1e-2 * float(xb.grad.abs().max()))
+        if node is DWNNode:
+            m = O.learnable_soft_mapping(x, layer.mapping.W.detach().cpu(), layer.tau).view(B, N, 6)
+            y_ref = O.dwn_forward(m, layer.luts.detach().cpu()).reshape(B, N)
+            assert float((ya.cpu() != y_ref).float().mean()) < 1e-3
+
+
 # ------------------------------------------------------------------------------ GroupSum
 def test_groupsum_known_answers(golden, dev):
     from difflut_b200.utils import GroupSum
