@@ -62,6 +62,9 @@ SIGNATURES = {
     "dl_dwn_bwd_fused_s": "pplfplpppppppllll s",
     "dl_bits_swizzle_t": "ppll s",
     "dl_dwn_fwd_groupsum_noalloc_t": "pppplllfl s",
+    "dl_flip_rows": "pplfl s",
+    "dl_bits_flip_t": "plllfl s",
+    "dl_grad_rescale": "ppllififp s",
     "dl_p2p_barrier": "pllpl s",
     "dl_p2p_reduce_adam": "ppppplllfffff s",
     "dl_popcount_groupsum_t": "ppllll s",
@@ -105,6 +108,8 @@ def lib():
     handle.dl_dwn_bwd_groups.argtypes = [ctypes.c_int64]
     handle.dl_prob_groupsum_splits.restype = ctypes.c_int64
     handle.dl_prob_groupsum_splits.argtypes = [ctypes.c_int64, ctypes.c_int64]
+    handle.dl_grad_rescale_scratch_doubles.restype = ctypes.c_int64
+    handle.dl_grad_rescale_scratch_doubles.argtypes = []
     handle.dl_p2p_enable_peer.restype = ctypes.c_int
     handle.dl_p2p_enable_peer.argtypes = [ctypes.c_int64]
     handle.dl_swizzled_words.restype = ctypes.c_int64

@@ -75,10 +75,20 @@ class LUTLayerMixin(nn.Module):
             check_positive("grad_epsilon", self.grad_epsilon, "Used for numerical stability in variance calculation")
         self._flip_mask_buffer = None
 
+    @staticmethod
+    def _draw_seed() -> int:
+        """A fresh 62-bit seed from torch's CPU generator (reproducible under torch.manual_seed)."""
+        return int(torch.randint(0, 2 ** 62, (1,), dtype=torch.int64).item())
+
     def _apply_bit_flip(self, x: torch.Tensor) -> torch.Tensor:
-        """x -> 1-x on a random `flip_probability` fraction; the flip carries no gradient."""
+        """x -> 1-x on a random `flip_probability` fraction; the flip carries no gradient.
+
+        CUDA tensors go through `dl_flip_rows` (Bernoulli per element; the reference draws an exact count
+        when the probability is below 0.05, base_layer.py:189-226 - same expectation)."""
         if self.flip_probability <= 0.0 or not self.training:
             return x
+        if x.is_cuda:
+            return _FlipFunction.apply(x, float(self.flip_probability), self._draw_seed())
         if self.flip_probability < 0.05:
             count = int(x.numel() * self.flip_probability)
             if count == 0:
@@ -92,15 +102,48 @@ class LUTLayerMixin(nn.Module):
         return x + delta
 
     def _apply_gradient_stabilization(self, grad: torch.Tensor) -> torch.Tensor:
-        """(g - mean) * sqrt(target_std / (mean(g^2) + eps)), over the layer or per sample."""
+        """(g - mean) * sqrt(target_std / (mean(g^2) + eps)), over the layer or per sample
+        (`dl_grad_rescale` for CUDA tensors)."""
         if self.grad_stabilization == "none" or not self.training or grad is None:
             return grad
+        if grad.is_cuda and grad.dim() == 2:
+            from .. import _native
+
+            g = grad.contiguous().float()
+            out = torch.empty_like(g)
+            per_row = 0 if self.grad_stabilization == "layerwise" else 1
+            with torch.cuda.device(g.device):
+                scratch = None
+                if not per_row:
+                    scratch = torch.empty(int(_native.lib().dl_grad_rescale_scratch_doubles()), device=g.device,
+                                          dtype=torch.float64)
+                _native.call("dl_grad_rescale", g, out, g.shape[0], g.shape[1], per_row, float(self.grad_target_std),
+                             1 if self.grad_subtract_mean else 0, float(self.grad_epsilon), scratch)
+            return out
         dims = None if self.grad_stabilization == "layerwise" else 1
         g = grad.clone()
         if self.grad_subtract_mean:
             g = g - (g.mean() if dims is None else g.mean(dim=1, keepdim=True))
         var = g.pow(2).mean() if dims is None else g.pow(2).mean(dim=1, keepdim=True)
         return g * torch.sqrt(torch.tensor(self.grad_target_std, device=grad.device) / (var + self.grad_epsilon))
+
+
+class _FlipFunction(torch.autograd.Function):
+    """out = 1 - x on a Bernoulli(p) subset, identity gradient (the reference adds a detached delta)."""
+
+    @staticmethod
+    def forward(ctx, x, probability, seed):
+        from .. import _native
+
+        x = x.contiguous().float()
+        out = torch.empty_like(x)
+        with torch.cuda.device(x.device):
+            _native.call("dl_flip_rows", x, out, x.numel(), probability, seed)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None, None
 
 
 class _NodeViews:

@@ -180,19 +180,25 @@ class ConvolutionalLayer(LUTLayerMixin, nn.Module):
                 p = self._level_params(level)[0]
                 tables.append(p if proto._stacked == "dwn" else torch.sigmoid(p))
             return dwn_levels_eval(x, list(zip(tables, plans)), geom)
-        if flip:
+        bits_only = self.training and proto._stacked in ("dwn", "dwn_stable") and proto.n <= 6
+        source = geom
+        if flip and bits_only:
+            # the nodes only read `patch >= 0.5`: flip the packed patch bits instead of materialising patches
+            source = (geom, self.flip_probability, self._draw_seed())
+            h = x
+        elif flip:
             h = self._apply_bit_flip(PatchFunction.apply(x, geom))
-            geom = None
+            geom = source = None
         else:
             h = x
-        if self.training and proto._stacked in ("dwn", "dwn_stable") and proto.n <= 6:
+        if bits_only:
             # all levels as one bit-packed pipeline: no fp32 activations between the tree levels
             stable = proto._stacked == "dwn_stable"
             params = [self._level_params(level) for level in levels]
             tables = [torch.sigmoid(p[0]) if stable else p[0] for p in params]
             spec = [(plan, 0.0 if stable else proto.alpha, 0.0 if stable else proto.beta,
                      p[1].detach().float() if stable else None) for plan, p in zip(plans, params)]
-            return DWNStackFunction.apply(h, spec, geom, *tables)
+            return DWNStackFunction.apply(h, spec, source, *tables)
         for level, plan in zip(levels, plans):
             h = level[0]._apply_plan(h, plan, self._level_params(level), geom)
             geom = None

@@ -244,6 +244,9 @@ class DWNStackFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, levels, geom, *tables):
+        flip = None
+        if isinstance(geom, tuple):  # (source, flip probability, seed): XOR a Bernoulli mask into the packed input
+            geom, flip = geom[0], (float(geom[1]), int(geom[2]))
         tables = [t.contiguous().float() for t in tables]
         packed = isinstance(geom, PackedInput)
         if packed:
@@ -269,6 +272,10 @@ class DWNStackFunction(torch.autograd.Function):
                     _native.call("dl_pack_rows_to_t", x, bits[0], B, I, Bp, 0.5)
                 else:
                     _native.call("dl_unfold_pack_t", x, bits[0], *geom.args(), 0.5, Bp)
+            if flip is not None and flip[0] > 0.0:
+                if packed:
+                    bits[0] = bits[0].clone()
+                _native.call("dl_bits_flip_t", bits[0], I, B, Bp, flip[0], flip[1])
             for (plan, _, _, _), tab in zip(levels[:-1], tables[:-1]):
                 masks = torch.empty(plan.N, device=dev, dtype=torch.int64)
                 _native.call("dl_dwn_prepare", tab, None, masks, plan.N, plan.n, 0.0, 0.0)

@@ -336,6 +336,26 @@ int dl_dwn_bwd_fused_s(const uint8_t* addr_up, const float* g_up, int64_t gdiv_u
                        float* gt_partial, int64_t group_stride, int64_t N, int64_t n, int64_t Bp,
                        dl_stream_t stream);
 
+/* ------------------------------------------------------------------ layer training options
+ * Replace LUTLayerMixin._apply_bit_flip / _apply_gradient_stabilization
+ * (difflut/layers/base_layer.py:149-264, 266-339; torch code in the reference).
+ *   dl_flip_rows     out[i] = 1 - x[i] with probability p, else x[i] (no gradient: the caller's backward
+ *                    is the identity).  Bernoulli per element from a counter-based generator keyed by
+ *                    (seed, i); the reference's exact-count variant for p < 0.05 is not reproduced.
+ *   dl_bits_flip_t   the same decision per element (f, b) of an (F, B) matrix, applied in place as an XOR to
+ *                    packed feature-major bits [F][Bp/32] (flips `x >= 0.5`; differs from thresholding
+ *                    1 - x only at x == 0.5 exactly).
+ *   dl_grad_rescale  out = (g - mean) * sqrt(target_std / (mean((g - mean)^2) + eps)); mean = 0 unless
+ *                    subtract_mean; statistics over the whole (rows, cols) tensor (per_row = 0, needs
+ *                    `scratch` of dl_grad_rescale_scratch_doubles() doubles) or per row (per_row = 1).  */
+int dl_flip_rows(const float* x, float* out, int64_t count, float probability, int64_t seed,
+                 dl_stream_t stream);
+int dl_bits_flip_t(uint32_t* bits_t, int64_t F, int64_t B, int64_t Bp, float probability, int64_t seed,
+                   dl_stream_t stream);
+int64_t dl_grad_rescale_scratch_doubles(void);
+int dl_grad_rescale(const float* g, float* out, int64_t rows, int64_t cols, int per_row, float target_std,
+                    int subtract_mean, float eps, double* scratch, dl_stream_t stream);
+
 /* ------------------------------------------------------------------ data-parallel step over peer memory
  * No counterpart in the reference (it is single-process).  One process per GPU; every rank maps the
  * other ranks' gradient / parameter / flag buffers (CUDA IPC: plain peer pointers) and passes HOST

@@ -210,3 +210,81 @@ def test_conv_full_size_properties(dev):
         assert p.grad is not None and float(p.grad.abs().sum()) > 0
     total = sum(float(p.grad.sum()) for p in conv.trees[0][1].parameters())
     assert total == pytest.approx(64 * 24 * 24, rel=1e-6)  # the root node's histogram counts every patch once
+
+
+def test_flip_kernels_and_fused_conv_flip(dev):
+    """Bit-flip augmentation: Bernoulli rate, determinism in the seed, identical decisions on fp32 and on
+    packed bits, identity gradient; a convolution with DWN trees flips packed patch bits (no patches)."""
+    from difflut_b200 import _native
+    from difflut_b200.layers import ConvolutionalLayer, ConvolutionConfig, LayerConfig, RandomLayer
+    from difflut_b200.layers.base_layer import _FlipFunction
+    from difflut_b200.nodes import DWNNode, NodeConfig
+
+    F, B = 37, 1000
+    gen = torch.Generator().manual_seed(1)
+    xt = (torch.rand(F, B, generator=gen) > 0.5).float().to(dev)  # feature-major {0,1}
+    out = torch.empty_like(xt)
+    _native.call("dl_flip_rows", xt, out, xt.numel(), 0.25, 1234)
+    flipped = out != xt
+    assert abs(float(flipped.float().mean()) - 0.25) < 0.01
+    assert torch.equal(out[flipped], 1.0 - xt[flipped])
+    out2 = torch.empty_like(xt)
+    _native.call("dl_flip_rows", xt, out2, xt.numel(), 0.25, 1234)
+    assert torch.equal(out, out2)
+    _native.call("dl_flip_rows", xt, out2, xt.numel(), 0.25, 1235)
+    assert not torch.equal(out, out2)
+    # the packed variant flips the same elements
+    Bp = _native.padded_batch(B)
+    bits = torch.from_numpy(O.pack_bits_feature_major(
+        torch.cat([xt.t().cpu(), torch.zeros(Bp - B, F)])).view(np.int32)).to(dev)
+    _native.call("dl_bits_flip_t", bits, F, B, Bp, 0.25, 1234)
+    want = O.pack_bits_feature_major(torch.cat([out.t().cpu(), torch.zeros(Bp - B, F)]))
+    assert np.array_equal(bits.cpu().numpy().view(np.uint32), want)
+    # identity gradient
+    xr = torch.rand(50, 20, device=dev, requires_grad=True)
+    y = _FlipFunction.apply(xr, 0.5, 7)
+    y.backward(torch.ones_like(y))
+    assert torch.equal(xr.grad, torch.ones_like(xr))
+    # convolution: flips change the output, are reproducible under torch.manual_seed, gradients flow
+    conv = ConvolutionalLayer(ConvolutionConfig(tree_depth=1, in_channels=2, out_channels=4, receptive_field=3),
+                              DWNNode, NodeConfig(input_dim=6, output_dim=1), RandomLayer,
+                              layer_config=LayerConfig(flip_probability=0.3)).to(dev).train()
+    x = (torch.rand(8, 2, 10, 10, generator=gen) > 0.5).float().to(dev).requires_grad_(True)
+    torch.manual_seed(5)
+    y1 = conv(x)
+    torch.manual_seed(5)
+    y2 = conv(x)
+    assert torch.equal(y1, y2)
+    y3 = conv(x)
+    assert not torch.equal(y1, y3)
+    conv.flip_probability = 0.0
+    y0 = conv(x)
+    assert not torch.equal(y0, y1)
+    y1.sum().backward()
+    assert x.grad is not None and float(x.grad.abs().sum()) > 0
+    assert torch.equal(conv.eval()(x), conv(x))  # no flips in eval
+
+
+@pytest.mark.parametrize("mode", ["layerwise", "batchwise"])
+@pytest.mark.parametrize("subtract", [False, True])
+def test_gradient_rescale_matches_reference_formula(dev, mode, subtract):
+    """difflut/layers/base_layer.py:266-339 restated with torch ops on the CPU vs dl_grad_rescale."""
+    from difflut_b200.layers import LayerConfig, RandomLayer
+    from difflut_b200.nodes import DWNNode, NodeConfig
+
+    layer = RandomLayer(12, 4, DWNNode, NodeConfig(input_dim=3, output_dim=1),
+                        layer_config=LayerConfig(grad_stabilization=mode, grad_target_std=2.0,
+                                                 grad_subtract_mean=subtract, grad_epsilon=1e-6)).train()
+    gen = torch.Generator().manual_seed(3)
+    for shape in ((5, 7), (300, 1000), (64, 4097)):
+        g = torch.randn(shape, generator=gen) * 3.0 + 0.7
+        w = g.clone()
+        dims = None if mode == "layerwise" else 1
+        if subtract:
+            w = w - (w.mean() if dims is None else w.mean(dim=1, keepdim=True))
+        var = w.pow(2).mean() if dims is None else w.pow(2).mean(dim=1, keepdim=True)
+        ref = w * torch.sqrt(torch.tensor(2.0) / (var + 1e-6))
+        got = layer._apply_gradient_stabilization(g.to(dev))
+        torch.testing.assert_close(got.cpu(), ref, rtol=1e-5, atol=1e-6)
+    layer.eval()
+    assert layer._apply_gradient_stabilization(g.to(dev)) is not None
