@@ -245,8 +245,7 @@ def kernel_algorithmic_bytes(net, name):
         elif name == "dl_dwn_bwd_input_t" and li > 0:
             total += N * Bp + 4 * g_rows * Bp + 4 * N * n * 32 + 4 * I * Bp + 4 * (I + 1) + 4 * N * n
         elif name in ("dl_dwn_bwd_fused_t", "dl_dwn_bwd_fused_s"):
-            G = net.groups
-            total += I * Bp // 8 + 4 * N * 64 * G + 4 * N * n  # own input bits, partial table gradients, map
+            total += I * Bp // 8 + 4 * N * 64 + 4 * N * n  # own input bits, table gradient (accumulated in place), map
             if li == last:
                 total += 4 * k * Bp + N * Bp  # logits gradient in, addresses out
             else:

@@ -723,6 +723,16 @@ dwn_bwd_fused_kernel(const uint8_t* __restrict__ addr_up, const float* __restric
             }
 #undef DL_FUSED_ARGS
             __syncwarp();
+            // group_stride == 0: all groups share one slab.  A node is owned by the same warp in every
+            // group and the groups are walked in order, so adding to what this warp stored for the previous
+            // group is race-free and sums in group order (the order dl_sum_groups uses).  The previous
+            // value is fetched before the reduction below so that its latency hides behind it.
+            float* dst = gt_partial + cg * group_stride + f * L;
+            float p0 = 0.f, p1 = 0.f;
+            if (group_stride == 0 && cg > 0) {
+                if (lane < L) p0 = dst[lane];
+                if (lane + 32 < L) p1 = dst[lane + 32];
+            }
             // sum the 32 lane copies of bins `lane` and `lane + 32`: rotated 16-byte reads, conflict-free
             float s0 = 0.f, s1 = 0.f;
 #pragma unroll
@@ -733,7 +743,8 @@ dwn_bwd_fused_kernel(const uint8_t* __restrict__ addr_up, const float* __restric
                 s0 += (u.x + u.y) + (u.z + u.w);
                 s1 += (v.x + v.y) + (v.z + v.w);
             }
-            float* dst = gt_partial + cg * group_stride + f * L;
+            s0 += p0;
+            s1 += p1;
             if (lane < L) dst[lane] = s0;
             if (lane + 32 < L) dst[lane + 32] = s1;
             __syncwarp();
@@ -1103,7 +1114,8 @@ int bwd_fused_entry(bool swz, const uint8_t* addr_up, const float* g_up, int64_t
                     const uint32_t* in_bits_t, const int32_t* map, float* g_out, uint8_t* addr_out, float* gt_partial,
                     int64_t group_stride, int64_t N, int64_t n, int64_t Bp, dl_stream_t stream) {
     DL_REQUIRE(g_up && in_bits_t && map && gt_partial && N > 0 && gdiv_up > 0);
-    DL_REQUIRE(Bp > 0 && Bp % DL_BATCH_ALIGN == 0 && group_stride >= N * ((int64_t)1 << n));
+    DL_REQUIRE(Bp > 0 && Bp % DL_BATCH_ALIGN == 0);
+    DL_REQUIRE(group_stride == 0 || group_stride >= N * ((int64_t)1 << n));
     DL_REQUIRE_ALIGNED(g_up, 16);
     if (g_out) DL_REQUIRE_ALIGNED(g_out, 16);
     if (addr_out) DL_REQUIRE_ALIGNED(addr_out, 4);

@@ -18,16 +18,19 @@ __device__ __forceinline__ float prob_weight(const float* __restrict__ raw, int6
     return 1.0f / (1.0f + expf(-z));
 }
 
-// Interpolation tree on NIN inputs.  w[] holds 2^NIN weights; x[] the inputs.
+// Interpolation tree on NIN inputs.  w[] holds 2^NIN weights; x[] the inputs.  Every loop has a
+// compile-time trip count so that v[] stays in registers.
 template <int NIN>
 __device__ __forceinline__ float lerp_tree(const float* w, const float* x) {
-    float v[1 << (NIN > 0 ? NIN - 1 : 0)];
+    constexpr int H = 1 << (NIN > 0 ? NIN - 1 : 0);
+    float v[H];
 #pragma unroll
-    for (int k = 0; k < (1 << (NIN - 1)); ++k) v[k] = fmaf(x[0], w[2 * k + 1] - w[2 * k], w[2 * k]);
+    for (int k = 0; k < H; ++k) v[k] = fmaf(x[0], w[2 * k + 1] - w[2 * k], w[2 * k]);
 #pragma unroll
     for (int lvl = 1; lvl < NIN; ++lvl) {
 #pragma unroll
-        for (int k = 0; k < (1 << (NIN - 1 - lvl)); ++k) v[k] = fmaf(x[lvl], v[2 * k + 1] - v[2 * k], v[2 * k]);
+        for (int k = 0; k < H / 2; ++k)
+            if (k < (H >> lvl)) v[k] = fmaf(x[lvl], v[2 * k + 1] - v[2 * k], v[2 * k]);
     }
     return v[0];
 }
@@ -85,22 +88,88 @@ __global__ void prob_groupsum_reduce_kernel(const float* __restrict__ partial, f
     }
 }
 
-// Backward.  One warp per node j; lane = sample, looping over the whole batch so the 2^n table
-// gradient accumulators live in registers.  Phase A expands g top-down into g*P_a (table
-// gradient); phase B runs the tree bottom-up keeping the per-level differences and then walks it
-// top-down for d/dx_i.  gxm_t[(j*n+i)][b] receives the input gradient of slot i (summed over o).
+// Backward.  One warp per node j; lane = sample, looping over the whole batch so the 2^n table gradient
+// accumulators live in registers.  The inputs are split into a low group (NL inputs, address bits 0..NL-1)
+// and a high group (NH inputs): P_a(x) = u[a_hi] * v[a_lo] with u, v the multilinear weights of each
+// group (7 products each for 3 inputs).  Then
+//   table gradient  acc[a_hi][a_lo] += (g u[a_hi]) * v[a_lo]                      (one FMA per entry)
+//   s = W v, t = W^T u                                                           (two 2^n-FMA contractions)
+//   d/dx_i for a high input = the derivative of the 2^NH-entry lerp tree over s, for a low input over t
+// which is about 310 FP32 operations per (sample, node) for n = 6 and needs no per-sample array of 2^n
+// entries besides the accumulators.  The node's table sits in shared memory (16-byte broadcast reads).
+// gxm_t[(j*n+i)][b] receives the input gradient of slot i (summed over o).
 // HYBRID (difflut/nodes/hybrid_node.py:173-224): `raw` holds the table values themselves in the DWN
 // layout (N, O, 2^n), the table gradient is sum_b g*P_a with no sigmoid factor and is written in that
 // layout, and d/dx_i carries the reference's factor x(1-x) / (x(1-x) + 1e-8), which makes the input
 // gradient vanish at x in {0, 1}.
+
+// out[k], k < 2^NB: product over the group's inputs of (bit i of k ? x[i] : 1 - x[i]), times `scale`
+template <int NB>
+__device__ __forceinline__ void group_weights(const float* x, float scale, float* out) {
+    out[0] = scale;
+#pragma unroll
+    for (int i = 0; i < NB; ++i) {
+#pragma unroll
+        for (int k = (1 << i) - 1; k >= 0; --k) {
+            const float hi = out[k] * x[i];
+            out[k + (1 << i)] = hi;
+            out[k] = out[k] - hi;
+        }
+    }
+}
+
+// dx[i] = g * d/dx_i of the multilinear interpolation of tbl (2^NB entries) at x
+template <int NB>
+__device__ __forceinline__ void tree_gradient(const float* tbl, const float* x, float g, float* dx) {
+    constexpr int L = 1 << NB;
+    if (NB == 0) return;
+    float d[L > 1 ? L - 1 : 1];
+    float v[L > 1 ? L / 2 : 1];
+#pragma unroll
+    for (int k = 0; k < L / 2; ++k) {
+        d[k] = tbl[2 * k + 1] - tbl[2 * k];
+        v[k] = fmaf(x[0], d[k], tbl[2 * k]);
+    }
+#pragma unroll
+    for (int lvl = 1; lvl < NB; ++lvl) {
+        const int off = L - (L >> lvl);
+#pragma unroll
+        for (int k = 0; k < (L >> (lvl + 1)); ++k) {
+            d[off + k] = v[2 * k + 1] - v[2 * k];
+            v[k] = fmaf(x[lvl], d[off + k], v[2 * k]);
+        }
+    }
+    float q[L > 1 ? L / 2 : 1];
+    q[0] = g;
+#pragma unroll
+    for (int lvl = NB - 1; lvl >= 0; --lvl) {
+        const int off = L - (L >> lvl);
+        const int cnt = L >> (lvl + 1);
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < cnt; ++k) acc = fmaf(q[k], d[off + k], acc);
+        dx[lvl] = acc;
+        if (lvl > 0) {
+#pragma unroll
+            for (int k = cnt - 1; k >= 0; --k) {
+                const float hi = q[k] * x[lvl];
+                q[2 * k + 1] = hi;
+                q[2 * k] = q[k] - hi;
+            }
+        }
+    }
+}
+
 template <int NIN, bool HYBRID>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 3)
 prob_bwd_kernel(const float* __restrict__ x_t, const int32_t* __restrict__ map,
                 const float* __restrict__ raw, float inv_t, const float* __restrict__ g_t,
                 int64_t gdiv, float gscale, float* __restrict__ graw, float* __restrict__ gxm_t,
                 int64_t N, int O, int64_t B, int64_t Bp) {
     constexpr int L = 1 << NIN;
-    __shared__ float w_all[4][L];
+    constexpr int NL = (NIN + 1) / 2, NH = NIN - NL;
+    constexpr int LL = 1 << NL, LH = 1 << NH;
+    __shared__ __align__(16) float w_all[4][L < 4 ? 4 : L];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float* w = w_all[warp];
     const int64_t nwarps = (int64_t)gridDim.x * 4;
@@ -122,65 +191,40 @@ prob_bwd_kernel(const float* __restrict__ x_t, const int32_t* __restrict__ map,
 #pragma unroll
                 for (int i = 0; i < NIN; ++i) x[i] = __ldg(x_t + (int64_t)rows[i] * Bp + b);
                 const float g = (b < B) ? __ldg(grow + b) * gscale : 0.f;
-                // phase A: p[a] = g * prod_i (a_i ? x_i : 1-x_i), built from the top input down
-                {
-                    float p[L];
-                    p[0] = g;
+                float u[LH], v[LL], gu[LH];
+                group_weights<NL>(x, 1.f, v);
+                group_weights<NH>(x + NL, 1.f, u);
 #pragma unroll
-                    for (int lvl = NIN - 1; lvl >= 0; --lvl) {
-                        // entries currently sit at multiples of 2^(lvl+1); split each on input lvl
+                for (int h = 0; h < LH; ++h) gu[h] = g * u[h];
+                // table gradient and the two contractions in one sweep over the table
+                float s[LH], t[LL];
 #pragma unroll
-                        for (int k = 0; k < L; k += (2 << lvl)) {
-                            const float hi = p[k] * x[lvl];
-                            p[k + (1 << lvl)] = hi;
-                            p[k] = p[k] - hi;
-                        }
+                for (int l = 0; l < LL; ++l) t[l] = 0.f;
+#pragma unroll
+                for (int h = 0; h < LH; ++h) {
+                    float sh = 0.f;
+#pragma unroll
+                    for (int l = 0; l < LL; ++l) {
+                        const float wv = w[h * LL + l];
+                        acc[h * LL + l] = fmaf(gu[h], v[l], acc[h * LL + l]);
+                        sh = fmaf(wv, v[l], sh);
+                        t[l] = fmaf(wv, u[h], t[l]);
                     }
-#pragma unroll
-                    for (int a = 0; a < L; ++a) acc[a] += p[a];
+                    s[h] = sh;
                 }
-                // phase B: input gradients
                 if (gxm_t != nullptr) {
-                    float d[L - 1];  // differences per level: level l starts at offset L - (L >> l)
-                    float v[L / 2];
+                    float dx[NIN];
+                    tree_gradient<NL>(t, x, g, dx);
+                    tree_gradient<NH>(s, x + NL, g, dx + NL);
 #pragma unroll
-                    for (int k = 0; k < L / 2; ++k) {
-                        d[k] = w[2 * k + 1] - w[2 * k];
-                        v[k] = fmaf(x[0], d[k], w[2 * k]);
-                    }
-#pragma unroll
-                    for (int lvl = 1; lvl < NIN; ++lvl) {
-                        const int off = L - (L >> lvl);
-#pragma unroll
-                        for (int k = 0; k < (L >> (lvl + 1)); ++k) {
-                            d[off + k] = v[2 * k + 1] - v[2 * k];
-                            v[k] = fmaf(x[lvl], d[off + k], v[2 * k]);
-                        }
-                    }
-                    float q[L / 2];  // top-down weights of the nodes of the current level
-                    q[0] = g;
-#pragma unroll
-                    for (int lvl = NIN - 1; lvl >= 0; --lvl) {
-                        const int off = L - (L >> lvl);
-                        const int cnt = L >> (lvl + 1);
-                        float dx = 0.f;
-#pragma unroll
-                        for (int k = 0; k < cnt; ++k) dx = fmaf(q[k], d[off + k], dx);
+                    for (int i = 0; i < NIN; ++i) {
+                        float val = dx[i];
                         if (HYBRID) {
-                            const float t = x[lvl] * (1.f - x[lvl]);
-                            dx *= t / (t + 1e-8f);
+                            const float tt = x[i] * (1.f - x[i]);
+                            val *= tt / (tt + 1e-8f);
                         }
-                        float* dst = gxm_t + (j * NIN + lvl) * Bp + b;
-                        if (o == 0) *dst = dx; else *dst += dx;
-                        if (lvl > 0) {
-                            // children of node k at the level below are 2k (weight 1-x) and 2k+1 (weight x)
-#pragma unroll
-                            for (int k = cnt - 1; k >= 0; --k) {
-                                const float hi = q[k] * x[lvl];
-                                q[2 * k + 1] = hi;
-                                q[2 * k] = q[k] - hi;
-                            }
-                        }
+                        float* dst = gxm_t + (j * NIN + i) * Bp + b;
+                        if (o == 0) *dst = val; else *dst += val;
                     }
                 }
             }
@@ -188,15 +232,15 @@ prob_bwd_kernel(const float* __restrict__ x_t, const int32_t* __restrict__ map,
             if (graw != nullptr) {
 #pragma unroll
                 for (int a = 0; a < L; ++a) {
-                    float s = acc[a];
+                    float sum = acc[a];
 #pragma unroll
-                    for (int sh = 16; sh > 0; sh >>= 1) s += __shfl_xor_sync(0xffffffffu, s, sh);
+                    for (int sh = 16; sh > 0; sh >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, sh);
                     if (lane == (a & 31)) {
                         if (HYBRID) {
-                            graw[(j * O + o) * L + a] = s;
+                            graw[(j * O + o) * L + a] = sum;
                         } else {
                             const float sg = w[a];
-                            graw[(j * L + a) * O + o] = s * sg * (1.f - sg) * inv_t;
+                            graw[(j * L + a) * O + o] = sum * sg * (1.f - sg) * inv_t;
                         }
                     }
                 }

@@ -305,8 +305,7 @@ class DWNStackFunction(torch.autograd.Function):
         total = offs[-1]
         with torch.cuda.device(dev):
             g_t = _rows_to_t(g.contiguous().float(), Bp)
-            groups = int(_native.lib().dl_dwn_bwd_groups(Bp))
-            partial = torch.empty(groups, total, device=dev, dtype=torch.float32)
+            flat = torch.empty(total, device=dev, dtype=torch.float32)  # all levels' table gradients
             efd = [None] * L
             for l in range(L):
                 if l > 0 or need_x:
@@ -322,14 +321,14 @@ class DWNStackFunction(torch.autograd.Function):
                     addr[l] = torch.empty(plan.N, Bp, device=dev, dtype=torch.uint8)
                 if l == L - 1:
                     _native.call("dl_dwn_bwd_fused_t", None, g_t, 1, 1.0, None, 1, None, None, bits[l], plan.map_nodes,
-                                 None, addr[l], partial[0, offs[l]:], total, plan.N, plan.n, Bp)
+                                 None, addr[l], flat[offs[l]:], 0, plan.N, plan.n, Bp)
                 else:
                     up = levels[l + 1][0]
                     if below:
                         gact[l] = torch.empty(plan.N, Bp, device=dev, dtype=torch.float32)
                     _native.call("dl_dwn_bwd_fused_t", addr[l + 1], gact[l + 1], 1, 1.0, efd[l + 1], up.n,
                                  up.inv_ptr_virtual, up.inv_ent8_virtual, bits[l], plan.map_nodes, gact[l], addr[l],
-                                 partial[0, offs[l]:], total, plan.N, plan.n, Bp)
+                                 flat[offs[l]:], 0, plan.N, plan.n, Bp)
                     gact[l + 1] = None if l + 1 < L - 1 else gact[l + 1]
             gx = None
             if need_x:
@@ -343,8 +342,6 @@ class DWNStackFunction(torch.autograd.Function):
                 else:
                     gx = torch.empty(geom.B, geom.C, geom.H, geom.W, device=dev, dtype=torch.float32)
                     _native.call("dl_fold_t", gx_t, gx, *geom.args(), Bp)
-            flat = torch.empty(total, device=dev, dtype=torch.float32)
-            _native.call("dl_sum_groups", partial, flat, total, total, groups)
         grads = []
         for l in range(L):
             gt = None

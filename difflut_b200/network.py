@@ -165,9 +165,6 @@ class DWNNetwork:
             self.gact = [torch.empty(N, Bp, device=dev, dtype=torch.float32)
                          if (li > 0 or not self.fused_backward) else None for li, N in enumerate(self.N[:-1])]
             self.groups = int(_native.lib().dl_dwn_bwd_groups(Bp))
-            # zeros: the padding behind the last table (peer mode) is summed with the rest and must stay 0
-            self.gt_partial = (torch.zeros(self.groups, self.flat.numel(), device=dev, dtype=torch.float32)
-                               if self.fused_backward else None)
             self.addr = [None] + [torch.empty(N, Bp, device=dev, dtype=torch.uint8) for N in self.N[1:]]
             self.dlogits_t = torch.empty(self.k, Bp, device=dev, dtype=torch.float32)
             self.loss_rows = torch.empty(Bp, device=dev, dtype=torch.float32)
@@ -223,21 +220,20 @@ class DWNNetwork:
                              self.I[li], self.n[li], Bp)
 
     def _backward_fused(self) -> None:
-        """One kernel per layer (top down).  Each kernel leaves one partial table gradient per 1024-sample
-        group; on one GPU Adam sums them itself, under data parallelism each layer's gradient is summed
-        and its all-reduce started right away, so it travels while the layers below are still computed."""
+        """One kernel per layer (top down).  Each kernel adds the table gradient of one 1024-sample group
+        after the other straight into the flat gradient buffer (group stride 0: a node belongs to the same
+        warp in every group, so the sum has a fixed order and no scratch slabs are needed).  Under NCCL
+        data parallelism each layer's all-reduce is started as soon as its slice is complete, so it travels
+        while the layers below are still computed."""
         Bp = self.Bp
         last = len(self.layers) - 1
-        total = self.flat.numel()
-        # with a single group the "partial" gradient is the gradient: write it in place
-        direct = self.distributed and self.groups == 1
         fused = "dl_dwn_bwd_fused_s" if self.swizzle else "dl_dwn_bwd_fused_t"
         self._pending = []
         for li in range(last, -1, -1):
-            partial = self.flat_grad[self.offsets[li]:] if direct else self.gt_partial[0, self.offsets[li]:]
+            grad_out = self.flat_grad[self.offsets[li]:]
             if li == last:
                 _native.call(fused, None, self.dlogits_t, self.gsz, 1.0 / self.tau, None, 1, None, None,
-                             self.bits[li], self.plans[li].map_nodes, None, self.addr[li], partial, total,
+                             self.bits[li], self.plans[li].map_nodes, None, self.addr[li], grad_out, 0,
                              self.N[li], self.n[li], Bp)
             else:
                 up = li + 1
@@ -248,18 +244,11 @@ class DWNNetwork:
                 _native.call(fused, self.addr[up], g_up, gdiv, gscale, self.efd[up], self.n[up],
                              self.plans[up].inv_ptr_virtual, self.plans[up].inv_ent8_virtual, self.bits[li],
                              self.plans[li].map_nodes, self.gact[li] if li > 0 else None,
-                             self.addr[li] if li > 0 else None, partial, total, self.N[li], self.n[li], Bp)
-            if self.distributed:
-                lo, hi = self.offsets[li], self.offsets[li + 1]
-                grad = self.flat_grad[lo:hi]
-                if self.peer_optimizer:
-                    continue  # one sum over the whole buffer after the last layer, then the peer step
-                if not direct:
-                    _native.call("dl_sum_groups", self.gt_partial[0, lo:], grad, hi - lo, total, self.groups)
+                             self.addr[li] if li > 0 else None, grad_out, 0, self.N[li], self.n[li], Bp)
+            if self.distributed and not self.peer_optimizer:
                 # sum of per-rank gradients of the GLOBAL-mean loss (dl_ce_t divides by B_global)
+                grad = self.flat_grad[self.offsets[li]:self.offsets[li + 1]]
                 self._pending.append(allreduce_sum_(grad, self.group, async_op=True))
-        if self.peer_optimizer and not direct:
-            _native.call("dl_sum_groups", self.gt_partial, self.flat_grad, total, total, self.groups)
 
     def _step_body(self, B: int, B_global: int) -> None:
         # the EFD transform is only needed by the backward: it runs on a side stream next to the forward
@@ -279,12 +268,6 @@ class DWNNetwork:
         main.wait_event(self._join)
         self._backward()
         count = self.flat.numel()
-        if self.fused_backward and not self.distributed:
-            # no exchange between the backward and the update: sum the partial gradients inside Adam
-            _native.call("dl_adam_step_groups", self.flat, self.gt_partial, count, self.groups, self.flat_grad,
-                         self.exp_avg, self.exp_avg_sq, self.adam_state, count, self.lr, self.betas[0], self.betas[1],
-                         self.eps, 1.0)
-            return
         if self.peer_optimizer:
             # every rank's gradients are complete -> each rank reduces and updates its slice and stores the
             # new parameters everywhere -> every rank's stores have landed
@@ -313,12 +296,7 @@ class DWNNetwork:
 
     def kernel_launches_per_step(self) -> int:
         L = len(self.layers)
-        fused_adam = self.fused_backward and not self.distributed
-        if fused_adam or (self.distributed and getattr(self, "groups", 2) == 1):
-            sums = 0
-        else:
-            sums = 1 if (self.peer_optimizer or not self.distributed) else L
-        backward = (L + sums) if self.fused_backward else (L + (L - 1))
+        backward = L if self.fused_backward else (L + (L - 1))
         prepare = 2 * (1 if self.uniform else L)
         update = 4 if self.peer_optimizer else 2  # barrier, state advance, reduce+Adam+broadcast, barrier
         return prepare + 1 + (L - 1) + 2 + 2 + backward + update

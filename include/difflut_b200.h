@@ -182,7 +182,10 @@ int dl_dwn_bwd_input_t(const uint8_t* addr_t, const float* g_t, int64_t gdiv, fl
  * are written only if not NULL (the first layer of a stack needs neither).
  * gt_partial is caller-provided scratch: dl_dwn_bwd_groups(Bp) slabs of `group_stride` floats
  * (slab g holds the table gradient of samples [1024 g, 1024 (g+1)) at offset f*2^n); sum them
- * with dl_sum_groups, which adds the slabs in order (reproducible).                          */
+ * with dl_sum_groups, which adds the slabs in order (reproducible).  group_stride == 0: one
+ * slab; the kernel itself adds the groups into it, in the same order (the same warp owns a node
+ * in every group), so gt_partial then receives the complete table gradient, bit-identical to
+ * the ordered sum of the slabs.                                                              */
 int64_t dl_dwn_bwd_groups(int64_t Bp);
 int dl_dwn_bwd_fused_t(const uint8_t* addr_up, const float* g_up, int64_t gdiv_up, float gscale_up,
                        const float* efd_up, int64_t n_up, const int32_t* inv_ptr,
