@@ -710,13 +710,12 @@ def run_train_layers(args):
     # the same layer objects behind DWNStack: one bit per activation between layers, still torch autograd + Adam
     from difflut_b200.layers import DWNStack
 
-    head = GroupSum(k=CLASSES, tau=TAU, use_randperm=False)
-    stack = DWNStack(layers, encoder=enc).train()
+    stack = DWNStack(layers, encoder=enc, groupsum=GroupSum(k=CLASSES, tau=TAU, use_randperm=False)).train()
     opt2 = torch.optim.Adam(stack.parameters(), lr=LR)
 
     def step_stack():
         opt2.zero_grad(set_to_none=True)
-        loss = torch.nn.functional.cross_entropy(head(stack(xd)), labels)
+        loss = torch.nn.functional.cross_entropy(stack(xd), labels)
         loss.backward()
         opt2.step()
 
@@ -726,7 +725,7 @@ def run_train_layers(args):
                       "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
                       "data": "synthetic", "config": _config({"mode": "layer API: fp32 rows between layers, torch autograd + Adam"}),
                       "dwn_stack": {"ms_per_step": ms_stack, "value": GLOBAL_BATCH / (ms_stack * 1e-3),
-                                    "mode": "same layers behind DWNStack(layers, encoder): bit-packed between layers, "
+                                    "mode": "same layers behind DWNStack(layers, encoder, groupsum): bit-packed between layers, "
                                             "torch autograd + torch.optim.Adam"}}),
           flush=True)
 

@@ -208,7 +208,7 @@ struct MuxTree<0, BASE, SMEM> {
 // gather from them); both are walked with grid-stride loops (no index division).
 // SMEM needs blockDim.x to be a multiple of 32, so that all lanes of a warp work on the same node.
 template <int NIN, bool SMEM>
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(256, 4)
 dwn_fwd_bits_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __restrict__ map,
                     const uint64_t* __restrict__ masks, uint32_t* __restrict__ out_bits, int N, int Q) {
     __shared__ uint2 cm_all[SMEM ? 8 : 1][32];

@@ -25,7 +25,8 @@ import torch.nn as nn
 from ..nodes.node_config import NodeConfig
 from ..registry import register_convolutional_layer
 from .base_layer import LUTLayerMixin
-from .fused_ops import ConnectionPlan, DWNStackFunction, PatchFunction, PatchGeometry, dwn_levels_eval
+from .fused_ops import (ConnectionPlan, DWNStackFunction, PatchFunction, PatchGeometry, StackOptions,
+                        dwn_levels_eval)
 from .layer_config import GroupedInputConfig, LayerConfig
 from .random_layer import RandomLayer
 
@@ -184,7 +185,7 @@ class ConvolutionalLayer(LUTLayerMixin, nn.Module):
         source = geom
         if flip and bits_only:
             # the nodes only read `patch >= 0.5`: flip the packed patch bits instead of materialising patches
-            source = (geom, self.flip_probability, self._draw_seed())
+            source = StackOptions(geom, flip=(float(self.flip_probability), self._draw_seed()))
             h = x
         elif flip:
             h = self._apply_bit_flip(PatchFunction.apply(x, geom))

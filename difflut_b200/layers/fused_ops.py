@@ -229,6 +229,16 @@ class PackedInput:
         self.B = int(batch)
 
 
+class StackOptions:
+    """How a DWNStackFunction reads its input and what it appends: `source` None (fp32 rows), a
+    PatchGeometry (image batch, samples = patches) or a PackedInput (bits already packed); `flip`
+    (probability, seed) XORs a Bernoulli mask into the packed input; `head` (k, tau) fuses a following
+    GroupSum(k, tau) (difflut/utils/modules.py:116-163) so that the function returns (B, k) logits."""
+
+    def __init__(self, source=None, flip=None, head=None):
+        self.source, self.flip, self.head = source, flip, head
+
+
 class DWNStackFunction(torch.autograd.Function):
     """Consecutive DWN layers (output_dim 1, n <= 6) as one autograd node, bit-packed from end to end.
 
@@ -244,9 +254,9 @@ class DWNStackFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, levels, geom, *tables):
-        flip = None
-        if isinstance(geom, tuple):  # (source, flip probability, seed): XOR a Bernoulli mask into the packed input
-            geom, flip = geom[0], (float(geom[1]), int(geom[2]))
+        flip = head = None
+        if isinstance(geom, StackOptions):
+            flip, head, geom = geom.flip, geom.head, geom.source
         tables = [t.contiguous().float() for t in tables]
         packed = isinstance(geom, PackedInput)
         if packed:
@@ -283,11 +293,19 @@ class DWNStackFunction(torch.autograd.Function):
                 _native.call("dl_dwn_fwd_bits_t", bits[-1], plan.map_nodes, masks, nxt, plan.N, plan.n, Bp)
                 bits.append(nxt)
             last = levels[-1][0]
-            out_t = torch.empty(last.N, Bp, device=dev, dtype=torch.float32)
-            _native.call("dl_dwn_fwd_vals_t", bits[-1], last.map_nodes, tables[-1], out_t, None, last.N, last.n, Bp)
+            if head is None:
+                out_t = torch.empty(last.N, Bp, device=dev, dtype=torch.float32)
+                _native.call("dl_dwn_fwd_vals_t", bits[-1], last.map_nodes, tables[-1], out_t, None, last.N, last.n, Bp)
+            else:
+                k, tau = int(head[0]), float(head[1])
+                splits = int(_native.lib().dl_dwn_groupsum_splits(last.N, k))
+                partial = torch.empty(k * splits, Bp, device=dev, dtype=torch.float32)
+                out_t = torch.empty(k, Bp, device=dev, dtype=torch.float32)
+                _native.call("dl_dwn_fwd_groupsum_t", bits[-1], last.map_nodes, tables[-1], partial, out_t, last.N,
+                             last.n, k, tau, Bp)
             out = _t_to_rows(out_t, B)
         ctx.save_for_backward(*bits, *tables)
-        ctx.levels, ctx.geom, ctx.B = levels, geom, B
+        ctx.levels, ctx.geom, ctx.B, ctx.head = levels, geom, B, head
         return out
 
     @staticmethod
@@ -303,6 +321,12 @@ class DWNStackFunction(torch.autograd.Function):
         for sz in sizes:
             offs.append(offs[-1] + sz)
         total = offs[-1]
+        # gradient of the last level's outputs: g itself, or with a fused GroupSum the k class gradients,
+        # read as g_t[node / group size] / tau without materialising their broadcast
+        gdiv, gscale = 1, 1.0
+        if ctx.head is not None:
+            k, tau = int(ctx.head[0]), float(ctx.head[1])
+            gdiv, gscale = (levels[-1][0].N + k - 1) // k, 1.0 / tau
         with torch.cuda.device(dev):
             g_t = _rows_to_t(g.contiguous().float(), Bp)
             flat = torch.empty(total, device=dev, dtype=torch.float32)  # all levels' table gradients
@@ -320,23 +344,24 @@ class DWNStackFunction(torch.autograd.Function):
                 if below:
                     addr[l] = torch.empty(plan.N, Bp, device=dev, dtype=torch.uint8)
                 if l == L - 1:
-                    _native.call("dl_dwn_bwd_fused_t", None, g_t, 1, 1.0, None, 1, None, None, bits[l], plan.map_nodes,
-                                 None, addr[l], flat[offs[l]:], 0, plan.N, plan.n, Bp)
+                    _native.call("dl_dwn_bwd_fused_t", None, g_t, gdiv, gscale, None, 1, None, None, bits[l],
+                                 plan.map_nodes, None, addr[l], flat[offs[l]:], 0, plan.N, plan.n, Bp)
                 else:
                     up = levels[l + 1][0]
                     if below:
                         gact[l] = torch.empty(plan.N, Bp, device=dev, dtype=torch.float32)
-                    _native.call("dl_dwn_bwd_fused_t", addr[l + 1], gact[l + 1], 1, 1.0, efd[l + 1], up.n,
-                                 up.inv_ptr_virtual, up.inv_ent8_virtual, bits[l], plan.map_nodes, gact[l], addr[l],
-                                 flat[offs[l]:], 0, plan.N, plan.n, Bp)
+                    top = l + 1 == L - 1
+                    _native.call("dl_dwn_bwd_fused_t", addr[l + 1], gact[l + 1], gdiv if top else 1,
+                                 gscale if top else 1.0, efd[l + 1], up.n, up.inv_ptr_virtual, up.inv_ent8_virtual,
+                                 bits[l], plan.map_nodes, gact[l], addr[l], flat[offs[l]:], 0, plan.N, plan.n, Bp)
                     gact[l + 1] = None if l + 1 < L - 1 else gact[l + 1]
             gx = None
             if need_x:
                 plan = levels[0][0]
                 I = plan.input_size
                 gx_t = torch.empty(I, Bp, device=dev, dtype=torch.float32)
-                _native.call("dl_dwn_bwd_input_t", addr[0], gact[0], 1, 1.0, efd[0], plan.inv_ptr_virtual,
-                             plan.inv_ent8_virtual, gx_t, I, plan.n, Bp)
+                _native.call("dl_dwn_bwd_input_t", addr[0], gact[0], gdiv if L == 1 else 1, gscale if L == 1 else 1.0,
+                             efd[0], plan.inv_ptr_virtual, plan.inv_ent8_virtual, gx_t, I, plan.n, Bp)
                 if geom is None:
                     gx = _t_to_rows(gx_t, B)
                 else:

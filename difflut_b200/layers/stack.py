@@ -15,7 +15,8 @@ import torch
 import torch.nn as nn
 
 from ..encoder.thermometer import ThermometerEncoder
-from .fused_ops import DWNStackFunction, PackedInput, dwn_levels_eval
+from ..utils.modules import GroupSum
+from .fused_ops import DWNStackFunction, PackedInput, StackOptions, dwn_levels_eval
 from .random_layer import RandomLayer
 
 
@@ -23,9 +24,13 @@ class DWNStack(nn.Module):
     """`DWNStack(layers)(x)` equals `nn.Sequential(*layers)(x)` for RandomLayer layers of DWNNode /
     DWNStableNode with n <= 6 and output_dim 1.  With `encoder`, the module takes raw features and packs
     the thermometer bits itself (`DWNStack(layers, encoder)(x)` equals `Sequential(*layers)(encoder(x))`;
-    the raw features then receive no gradient, as the encoder has none)."""
+    the raw features then receive no gradient, as the encoder has none).  With `groupsum` (a GroupSum
+    without random permutation) the class sums are fused into the last layer's kernels and the module
+    returns the (B, k) logits of `groupsum(Sequential(*layers)(x))` without writing the last layer's
+    (B, N) outputs in training mode."""
 
-    def __init__(self, layers: Sequence[RandomLayer], encoder: Optional[ThermometerEncoder] = None):
+    def __init__(self, layers: Sequence[RandomLayer], encoder: Optional[ThermometerEncoder] = None,
+                 groupsum: Optional[GroupSum] = None):
         super().__init__()
         layers = list(layers)
         if not layers:
@@ -42,6 +47,9 @@ class DWNStack(nn.Module):
             width = l.output_size
         self.layers = nn.ModuleList(layers)
         self.encoder = encoder  # plain attribute, as thresholds are in the reference's encoders
+        if groupsum is not None and groupsum.use_randperm:
+            raise ValueError("DWNStack cannot fuse GroupSum(use_randperm=True)")
+        self.groupsum = groupsum
 
     def _spec(self, device):
         spec, tables = [], []
@@ -67,5 +75,7 @@ class DWNStack(nn.Module):
         else:
             self.layers[0]._validate_input_dims(x)
         if self.training:
-            return DWNStackFunction.apply(x, spec, source, *tables)
-        return dwn_levels_eval(x, [(t, s[0]) for t, s in zip(tables, spec)], source)
+            head = (self.groupsum.k, self.groupsum.tau) if self.groupsum is not None else None
+            return DWNStackFunction.apply(x, spec, StackOptions(source, head=head), *tables)
+        out = dwn_levels_eval(x, [(t, s[0]) for t, s in zip(tables, spec)], source)
+        return out if self.groupsum is None else self.groupsum(out)

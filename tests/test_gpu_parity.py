@@ -824,6 +824,30 @@ def test_dwn_stack_equals_sequential_layers(dev):
         yc.backward(gy)
         for r, p in zip(ref, [p for p in fused.parameters() if p.dim() == 3]):
             torch.testing.assert_close(p.grad, r, rtol=1e-4, atol=1e-6)
+        # GroupSum folded in: logits and gradients of GroupSum(Sequential(...)); 17 nodes in 4 classes is ragged
+        from difflut_b200.utils import GroupSum
+
+        head = GroupSum(k=4, tau=3.0, use_randperm=False)
+        glog = torch.randn(B, 4, generator=gen).to(dev)
+        for p in seq.parameters():
+            p.grad = None
+        xh = rows.clone().requires_grad_(True)
+        seq.train()
+        ref_logits = head(seq(xh))
+        ref_logits.backward(glog)
+        ref_h = [p.grad.clone() for p in seq.parameters() if p.dim() == 3]
+        for p in seq.parameters():
+            p.grad = None
+        with_head = DWNStack(layers, groupsum=head).train()
+        xi = rows.clone().requires_grad_(True)
+        logits = with_head(xi)
+        torch.testing.assert_close(logits, ref_logits, rtol=1e-5, atol=1e-5)
+        logits.backward(glog)
+        torch.testing.assert_close(xi.grad, xh.grad, rtol=1e-4, atol=1e-6)
+        for r, p in zip(ref_h, [p for p in with_head.parameters() if p.dim() == 3]):
+            torch.testing.assert_close(p.grad, r, rtol=1e-4, atol=1e-6)
+            p.grad = None
+        assert torch.equal(with_head.eval()(rows), head(seq.eval()(rows)))
         assert torch.equal(stack.eval()(rows), seq.eval()(rows))
         assert torch.equal(fused.eval()(x.to(dev)), seq(rows))
         assert set(stack.state_dict()) == {"layers." + k for k in seq.state_dict()}
