@@ -354,7 +354,8 @@ class DWNStackFunction(torch.autograd.Function):
                     _native.call("dl_dwn_bwd_fused_t", addr[l + 1], gact[l + 1], gdiv if top else 1,
                                  gscale if top else 1.0, efd[l + 1], up.n, up.inv_ptr_virtual, up.inv_ent8_virtual,
                                  bits[l], plan.map_nodes, gact[l], addr[l], flat[offs[l]:], 0, plan.N, plan.n, Bp)
-                    gact[l + 1] = None if l + 1 < L - 1 else gact[l + 1]
+                    if l + 1 < L - 1:
+                        gact[l + 1] = None  # the gradient of the level above is no longer needed
             gx = None
             if need_x:
                 plan = levels[0][0]

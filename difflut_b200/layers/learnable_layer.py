@@ -16,7 +16,7 @@ from ..nodes.node_config import NodeConfig
 from ..registry import register_layer
 from ..utils.warnings import warn_default_value
 from .base_layer import BaseLUTLayer
-from .fused_ops import GatherFunction, dwn_layer_eval
+from .fused_ops import dwn_layer_eval
 from .layer_config import LayerConfig
 from .soft_select import soft_select
 
