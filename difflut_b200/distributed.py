@@ -91,26 +91,45 @@ class PeerWindow:
         if self.world > 8:
             raise ValueError("PeerWindow supports at most 8 ranks (one node)")
         self.local = tensor
-        _, args = reduce_tensor(tensor)
+        # Every rank takes part in both exchanges whatever happens locally, and all ranks learn whether
+        # every mapping succeeded: either all of them get a window or all of them raise (a caller can then
+        # fall back to another exchange on all ranks at once instead of leaving some waiting in a collective).
+        error = None
+        args = None
+        try:
+            _, args = reduce_tensor(tensor)
+        except Exception as e:  # export failed on this rank
+            error = f"export: {e}"
         gathered = [None] * self.world
         dist.all_gather_object(gathered, (tensor.device.index, args), group=group)
         self.tensors = []
-        with torch.cuda.device(tensor.device):
-            for p, (dev, peer_args) in enumerate(gathered):
-                if p == self.rank:
-                    self.tensors.append(tensor)
-                    continue
-                if dev == tensor.device.index:
-                    raise RuntimeError("two ranks share one GPU: peer windows need one GPU per rank")
-                rc = _native.lib().dl_p2p_enable_peer(dev)
-                if rc != 0:
-                    raise RuntimeError(f"no peer access from cuda:{tensor.device.index} to cuda:{dev} (code {rc})")
-                peer_args = list(peer_args)
-                peer_args[6] = tensor.device.index  # storage_device: open the handle on this rank's GPU
-                mapped = rebuild_cuda_tensor(*peer_args)
-                if mapped.numel() != tensor.numel() or mapped.dtype != tensor.dtype:
-                    raise RuntimeError("peer tensor does not match the local one")
-                self.tensors.append(mapped)
+        if error is None:
+            try:
+                with torch.cuda.device(tensor.device):
+                    for p, (dev, peer_args) in enumerate(gathered):
+                        if p == self.rank:
+                            self.tensors.append(tensor)
+                            continue
+                        if peer_args is None:
+                            raise RuntimeError(f"rank {p} could not export its buffer")
+                        if dev == tensor.device.index:
+                            raise RuntimeError("two ranks share one GPU: peer windows need one GPU per rank")
+                        rc = _native.lib().dl_p2p_enable_peer(dev)
+                        if rc != 0:
+                            raise RuntimeError(f"no peer access from cuda:{tensor.device.index} to cuda:{dev} "
+                                               f"(code {rc})")
+                        peer_args = list(peer_args)
+                        peer_args[6] = tensor.device.index  # storage_device: open the handle on this rank's GPU
+                        mapped = rebuild_cuda_tensor(*peer_args)
+                        if mapped.numel() != tensor.numel() or mapped.dtype != tensor.dtype:
+                            raise RuntimeError("peer tensor does not match the local one")
+                        self.tensors.append(mapped)
+            except Exception as e:
+                error = f"map: {e}"
+        ok = torch.tensor([0 if error else 1], device=tensor.device, dtype=torch.int32)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)  # also: every rank has mapped every buffer
+        if int(ok.item()) == 0:
+            self.tensors = []
+            raise RuntimeError(f"peer window unavailable ({error or 'another rank failed'})")
         self._array = (ctypes.c_void_p * self.world)(*[t.data_ptr() for t in self.tensors])
         self.ptrs = ctypes.addressof(self._array)
-        dist.barrier(group=group)  # every rank has mapped every buffer before anyone uses them

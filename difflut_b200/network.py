@@ -109,10 +109,19 @@ class DWNNetwork:
             self.peer_flags = torch.zeros(8, device=self.device, dtype=torch.int32)
             self.peer_ctrl = torch.zeros(2, device=self.device, dtype=torch.int32)
             torch.cuda.synchronize(self.device)
-            self.win_params = PeerWindow(self.flat, process_group)
-            self.win_grads = PeerWindow(self.flat_grad, process_group)
-            self.win_flags = PeerWindow(self.peer_flags, process_group)
             self.peer_timeout_ms = 5000
+            try:
+                # a window either exists on every rank or raises on every rank
+                self.win_params = PeerWindow(self.flat, process_group)
+                self.win_grads = PeerWindow(self.flat_grad, process_group)
+                self.win_flags = PeerWindow(self.peer_flags, process_group)
+            except RuntimeError as e:
+                import warnings
+
+                warnings.warn(f"DWNNetwork: {e}; exchanging gradients with NCCL all-reduces instead", RuntimeWarning)
+                self.peer_optimizer = False
+                self.exp_avg = torch.zeros(total, device=self.device, dtype=torch.float32)
+                self.exp_avg_sq = torch.zeros(total, device=self.device, dtype=torch.float32)
         self.plans = [l._plan(self.device) for l in self.layers]
         self.alpha = [l.alpha for l in self.layers]
         self.beta = [l.beta for l in self.layers]
