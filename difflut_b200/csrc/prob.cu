@@ -82,8 +82,18 @@ __global__ void prob_groupsum_reduce_kernel(const float* __restrict__ partial, f
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t c = i / Bp, b = i - c * Bp;
+        // eight loads in flight at a time; the additions keep their order, so the sum is unchanged
+        const float* src = partial + c * S * Bp + b;
         float acc = 0.f;
-        for (int s = 0; s < S; ++s) acc += partial[(c * S + s) * Bp + b];
+        int s = 0;
+        for (; s + 8 <= S; s += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = __ldg(src + (int64_t)(s + u) * Bp);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc += v[u];
+        }
+        for (; s < S; ++s) acc += __ldg(src + (int64_t)s * Bp);
         logits_t[i] = acc * inv_tau;
     }
 }
