@@ -720,13 +720,37 @@ def run_train_layers(args):
         opt2.step()
 
     ms_stack = _time_gpu(step_stack, args.steps, max(args.warmup, 3), flush)
+
+    # the eager step above is bound by host launch overhead; the same step captured once in a CUDA graph
+    # (capturable torch Adam) shows the device time
+    ms_graph = None
+    try:
+        opt3 = torch.optim.Adam(stack.parameters(), lr=LR, capturable=True)
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                opt3.zero_grad(set_to_none=True)
+                torch.nn.functional.cross_entropy(stack(xd), labels).backward()
+                opt3.step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        opt3.zero_grad(set_to_none=True)
+        with torch.cuda.graph(graph):
+            torch.nn.functional.cross_entropy(stack(xd), labels).backward()
+            opt3.step()
+        ms_graph = _time_gpu(graph.replay, args.steps, max(args.warmup, 3), flush)
+    except Exception as e:  # report, do not hide
+        print(f"[bench] CUDA-graph capture of the DWNStack step failed: {e}", file=sys.stderr)
     print(json.dumps({"metric": METRIC + " (per-layer API)", "value": GLOBAL_BATCH / (ms * 1e-3), "unit": "samples/s",
                       "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
                       "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
                       "data": "synthetic", "config": _config({"mode": "layer API: fp32 rows between layers, torch autograd + Adam"}),
                       "dwn_stack": {"ms_per_step": ms_stack, "value": GLOBAL_BATCH / (ms_stack * 1e-3),
                                     "mode": "same layers behind DWNStack(layers, encoder, groupsum): bit-packed between layers, "
-                                            "torch autograd + torch.optim.Adam"}}),
+                                            "torch autograd + torch.optim.Adam",
+                                    "ms_per_step_cuda_graph": ms_graph}}),
           flush=True)
 
 

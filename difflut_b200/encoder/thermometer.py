@@ -83,6 +83,19 @@ class ThermometerEncoder(BaseEncoder):
             _native.call("dl_thermo_pack_t", x2, thr, out, B, F, self.num_bits, Bp)
         return out
 
+    def encode_packed_s(self, x: torch.Tensor) -> torch.Tensor:
+        """Bit-packed feature-major encoding in the chunk-interleaved layout the stack kernels read: int32
+        (F*T, 32 * ceil(Bp/1024)); bit c + 8r of word w of a 1024-sample block = sample 128c + 4w + r."""
+        self._check_fitted()
+        x2, thr, _ = self._prepared(x)
+        B, F = x2.shape
+        Bp = _native.padded_batch(B)
+        out = torch.empty(F * self.num_bits, int(_native.lib().dl_swizzled_words(Bp)), device=x.device,
+                          dtype=torch.int32)
+        with torch.cuda.device(x.device):
+            _native.call("dl_thermo_pack_s", x2, thr, out, B, F, self.num_bits, Bp)
+        return out
+
     def encode_packed(self, x: torch.Tensor) -> torch.Tensor:
         """Bit-packed row-major encoding: int32 (B, ceil(F*T/32)), bit c%32 of word c//32 = column c."""
         self._check_fitted()

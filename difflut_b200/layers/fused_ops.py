@@ -225,8 +225,9 @@ class PackedInput:
     """Marks the first argument of DWNStackFunction as already bit-packed feature-major rows
     (int32 (I, Bp/32), e.g. `ThermometerEncoder.encode_packed_t`) holding `batch` samples."""
 
-    def __init__(self, batch: int):
+    def __init__(self, batch: int, interleaved: bool = False):
         self.B = int(batch)
+        self.interleaved = bool(interleaved)  # chunk-interleaved rows (`encode_packed_s`) instead of natural ones
 
 
 class StackOptions:
@@ -259,6 +260,7 @@ class DWNStackFunction(torch.autograd.Function):
             flip, head, geom = geom.flip, geom.head, geom.source
         tables = [t.contiguous().float() for t in tables]
         packed = isinstance(geom, PackedInput)
+        interleaved_in = packed and geom.interleaved
         if packed:
             B, I = geom.B, x.shape[0]
             geom = None
@@ -271,10 +273,17 @@ class DWNStackFunction(torch.autograd.Function):
         Bp = _native.padded_batch(B)
         Wp = Bp // 32
         dev = x.device
+        # with a fused GroupSum every consumer of the activations has a variant for the chunk-interleaved
+        # layout, which saves a fifth of the backward's instructions
+        swz = head is not None
+        Ws = int(_native.lib().dl_swizzled_words(Bp)) if swz else Wp
+        if interleaved_in and (not swz or (flip is not None and flip[0] > 0.0)):
+            raise ValueError("interleaved packed input needs a fused GroupSum head and no bit flip")
         with torch.cuda.device(dev):
             if packed:
-                if x.dtype != torch.int32 or tuple(x.shape) != (I, Wp) or not x.is_contiguous():
-                    raise ValueError(f"packed input must be contiguous int32 ({I}, {Wp})")
+                want = Ws if interleaved_in else Wp
+                if x.dtype != torch.int32 or tuple(x.shape) != (I, want) or not x.is_contiguous():
+                    raise ValueError(f"packed input must be contiguous int32 ({I}, {want})")
                 bits = [x]
             else:
                 bits = [torch.empty(I, Wp, device=dev, dtype=torch.int32)]
@@ -286,11 +295,16 @@ class DWNStackFunction(torch.autograd.Function):
                 if packed:
                     bits[0] = bits[0].clone()
                 _native.call("dl_bits_flip_t", bits[0], I, B, Bp, flip[0], flip[1])
+            if swz and not interleaved_in:
+                natural = bits[0]
+                bits[0] = torch.empty(I, Ws, device=dev, dtype=torch.int32)
+                _native.call("dl_bits_swizzle_t", natural, bits[0], I, Bp)
             for (plan, _, _, _), tab in zip(levels[:-1], tables[:-1]):
                 masks = torch.empty(plan.N, device=dev, dtype=torch.int64)
                 _native.call("dl_dwn_prepare", tab, None, masks, plan.N, plan.n, 0.0, 0.0)
-                nxt = torch.empty(plan.N, Wp, device=dev, dtype=torch.int32)
-                _native.call("dl_dwn_fwd_bits_t", bits[-1], plan.map_nodes, masks, nxt, plan.N, plan.n, Bp)
+                nxt = torch.empty(plan.N, Ws, device=dev, dtype=torch.int32)
+                # bit-sliced: indifferent to where a sample sits in a row, only the row length matters
+                _native.call("dl_dwn_fwd_bits_t", bits[-1], plan.map_nodes, masks, nxt, plan.N, plan.n, Ws * 32)
                 bits.append(nxt)
             last = levels[-1][0]
             if head is None:
@@ -301,11 +315,11 @@ class DWNStackFunction(torch.autograd.Function):
                 splits = int(_native.lib().dl_dwn_groupsum_splits(last.N, k))
                 partial = torch.empty(k * splits, Bp, device=dev, dtype=torch.float32)
                 out_t = torch.empty(k, Bp, device=dev, dtype=torch.float32)
-                _native.call("dl_dwn_fwd_groupsum_t", bits[-1], last.map_nodes, tables[-1], partial, out_t, last.N,
+                _native.call("dl_dwn_fwd_groupsum_s", bits[-1], last.map_nodes, tables[-1], partial, out_t, last.N,
                              last.n, k, tau, Bp)
             out = _t_to_rows(out_t, B)
         ctx.save_for_backward(*bits, *tables)
-        ctx.levels, ctx.geom, ctx.B, ctx.head = levels, geom, B, head
+        ctx.levels, ctx.geom, ctx.B, ctx.head, ctx.Bp = levels, geom, B, head, Bp
         return out
 
     @staticmethod
@@ -313,7 +327,8 @@ class DWNStackFunction(torch.autograd.Function):
         levels, geom, B = ctx.levels, ctx.geom, ctx.B
         L = len(levels)
         bits, tables = ctx.saved_tensors[:L], ctx.saved_tensors[L:]
-        Bp = bits[0].shape[1] * 32
+        Bp = ctx.Bp
+        fused = "dl_dwn_bwd_fused_s" if ctx.head is not None else "dl_dwn_bwd_fused_t"
         dev = g.device
         need_x = ctx.needs_input_grad[0]
         sizes = [lv[0].N * (1 << lv[0].n) for lv in levels]
@@ -344,14 +359,14 @@ class DWNStackFunction(torch.autograd.Function):
                 if below:
                     addr[l] = torch.empty(plan.N, Bp, device=dev, dtype=torch.uint8)
                 if l == L - 1:
-                    _native.call("dl_dwn_bwd_fused_t", None, g_t, gdiv, gscale, None, 1, None, None, bits[l],
+                    _native.call(fused, None, g_t, gdiv, gscale, None, 1, None, None, bits[l],
                                  plan.map_nodes, None, addr[l], flat[offs[l]:], 0, plan.N, plan.n, Bp)
                 else:
                     up = levels[l + 1][0]
                     if below:
                         gact[l] = torch.empty(plan.N, Bp, device=dev, dtype=torch.float32)
                     top = l + 1 == L - 1
-                    _native.call("dl_dwn_bwd_fused_t", addr[l + 1], gact[l + 1], gdiv if top else 1,
+                    _native.call(fused, addr[l + 1], gact[l + 1], gdiv if top else 1,
                                  gscale if top else 1.0, efd[l + 1], up.n, up.inv_ptr_virtual, up.inv_ent8_virtual,
                                  bits[l], plan.map_nodes, gact[l], addr[l], flat[offs[l]:], 0, plan.N, plan.n, Bp)
                     if l + 1 < L - 1:

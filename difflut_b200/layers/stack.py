@@ -70,8 +70,9 @@ class DWNStack(nn.Module):
         source = None
         if self.encoder is not None:
             batch = x.shape[0]
-            x = self.encoder.encode_packed_t(x)
-            source = PackedInput(batch)
+            interleaved = self.training and self.groupsum is not None
+            x = self.encoder.encode_packed_s(x) if interleaved else self.encoder.encode_packed_t(x)
+            source = PackedInput(batch, interleaved)
         else:
             self.layers[0]._validate_input_dims(x)
         if self.training:

@@ -848,6 +848,16 @@ def test_dwn_stack_equals_sequential_layers(dev):
             torch.testing.assert_close(p.grad, r, rtol=1e-4, atol=1e-6)
             p.grad = None
         assert torch.equal(with_head.eval()(rows), head(seq.eval()(rows)))
+        # encoder and GroupSum both folded in: raw features in (packed straight into the interleaved layout), logits out
+        both = DWNStack(layers, encoder=enc, groupsum=head).train()
+        lg2 = both(x.to(dev))
+        torch.testing.assert_close(lg2, ref_logits, rtol=1e-5, atol=1e-5)
+        lg2.backward(glog)
+        for r, p in zip(ref_h, [p for p in both.parameters() if p.dim() == 3]):
+            torch.testing.assert_close(p.grad, r, rtol=1e-4, atol=1e-6)
+            p.grad = None
+        assert torch.equal(both.eval()(x.to(dev)), head(seq.eval()(rows)))
+        seq.train()
         assert torch.equal(stack.eval()(rows), seq.eval()(rows))
         assert torch.equal(fused.eval()(x.to(dev)), seq(rows))
         assert set(stack.state_dict()) == {"layers." + k for k in seq.state_dict()}
