@@ -32,7 +32,7 @@ SCALING = "strong"
 # dram__bytes_read.sum + dram__bytes_write.sum of the three dl_dwn_bwd_fused_s launches of one step at
 # per-GPU batch 8192, from one ncu capture (profiles/dwn_bwd_fused_kernel_c4_B8192.txt); the traffic is
 # proportional to the batch (every term but the 7 MB of tables scales with it), so other batches scale it
-NCU_TRAFFIC_BWD_FUSED_B8192 = 825.4e6
+NCU_TRAFFIC_BWD_FUSED_B8192 = 827.6e6
 WORKLOAD = "dwn3_16000-8000-4000_n6_T8_globalbatch8192_adam"
 
 
