@@ -367,6 +367,114 @@ softmax_bwd_rows_kernel(const float* __restrict__ W, const float* __restrict__ g
     }
 }
 
+// Register-resident variants for rows of up to 256 * 4 * SM_MAXQ elements (a multiple of 4): the row is read
+// once with 16-byte loads, every exponential is evaluated once, outputs leave as 8- / 16-byte stores.
+constexpr int SM_MAXQ = 8;
+
+__device__ __forceinline__ uint2 pack_bf16x4(float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 out;
+    out.x = *reinterpret_cast<uint32_t*>(&lo);
+    out.y = *reinterpret_cast<uint32_t*>(&hi);
+    return out;
+}
+
+__global__ void __launch_bounds__(256)
+softmax_rows_vec_kernel(const float* __restrict__ W, float inv_tau, __nv_bfloat16* __restrict__ S_hi,
+                        __nv_bfloat16* __restrict__ S_lo, int64_t ld_out, int I4) {
+    __shared__ float scratch[8];
+    const int64_t row = blockIdx.x;
+    const float4* w = reinterpret_cast<const float4*>(W + row * (int64_t)I4 * 4);
+    float4 v[SM_MAXQ];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < SM_MAXQ; ++k) {
+        const int q = threadIdx.x + k * 256;
+        if (q < I4) {
+            const float4 t = __ldg(w + q);
+            v[k] = make_float4(t.x * inv_tau, t.y * inv_tau, t.z * inv_tau, t.w * inv_tau);
+            mx = fmaxf(mx, fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w)));
+        } else {
+            v[k] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        }
+    }
+    mx = block_reduce(mx, scratch, true);
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < SM_MAXQ; ++k) {
+        v[k].x = expf(v[k].x - mx); v[k].y = expf(v[k].y - mx);
+        v[k].z = expf(v[k].z - mx); v[k].w = expf(v[k].w - mx);
+        sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+    }
+    sum = block_reduce(sum, scratch, false);
+    const float inv = 1.0f / sum;
+#pragma unroll
+    for (int k = 0; k < SM_MAXQ; ++k) {
+        const int q = threadIdx.x + k * 256;
+        if (q < I4) {
+            const float a = v[k].x * inv, b = v[k].y * inv, c = v[k].z * inv, d = v[k].w * inv;
+            const uint2 hi = pack_bf16x4(a, b, c, d);
+            *reinterpret_cast<uint2*>(S_hi + row * ld_out + 4 * q) = hi;
+            if (S_lo != nullptr) {
+                const __nv_bfloat162 h0 = *reinterpret_cast<const __nv_bfloat162*>(&hi.x);
+                const __nv_bfloat162 h1 = *reinterpret_cast<const __nv_bfloat162*>(&hi.y);
+                *reinterpret_cast<uint2*>(S_lo + row * ld_out + 4 * q) =
+                    pack_bf16x4(a - __low2float(h0), b - __high2float(h0), c - __low2float(h1), d - __high2float(h1));
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256)
+softmax_bwd_rows_vec_kernel(const float* __restrict__ W, const float* __restrict__ gS, float inv_tau,
+                            float* __restrict__ gW, int I4) {
+    __shared__ float scratch[8];
+    const int64_t row = blockIdx.x;
+    const float4* w = reinterpret_cast<const float4*>(W + row * (int64_t)I4 * 4);
+    const float4* g = reinterpret_cast<const float4*>(gS + row * (int64_t)I4 * 4);
+    float4 v[SM_MAXQ], gg[SM_MAXQ];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < SM_MAXQ; ++k) {
+        const int q = threadIdx.x + k * 256;
+        if (q < I4) {
+            const float4 t = __ldg(w + q);
+            gg[k] = __ldg(g + q);
+            v[k] = make_float4(t.x * inv_tau, t.y * inv_tau, t.z * inv_tau, t.w * inv_tau);
+            mx = fmaxf(mx, fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w)));
+        } else {
+            v[k] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            gg[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    mx = block_reduce(mx, scratch, true);
+    float sum = 0.f, dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < SM_MAXQ; ++k) {
+        v[k].x = expf(v[k].x - mx); v[k].y = expf(v[k].y - mx);
+        v[k].z = expf(v[k].z - mx); v[k].w = expf(v[k].w - mx);
+        sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+        dot += (v[k].x * gg[k].x + v[k].y * gg[k].y) + (v[k].z * gg[k].z + v[k].w * gg[k].w);
+    }
+    sum = block_reduce(sum, scratch, false);
+    dot = block_reduce(dot, scratch, false);
+    const float inv = 1.0f / sum;
+    const float mean = dot * inv;
+    float4* out = reinterpret_cast<float4*>(gW + row * (int64_t)I4 * 4);
+#pragma unroll
+    for (int k = 0; k < SM_MAXQ; ++k) {
+        const int q = threadIdx.x + k * 256;
+        if (q < I4) {
+            float4 r;
+            r.x = v[k].x * inv * (gg[k].x - mean) * inv_tau;
+            r.y = v[k].y * inv * (gg[k].y - mean) * inv_tau;
+            r.z = v[k].z * inv * (gg[k].z - mean) * inv_tau;
+            r.w = v[k].w * inv * (gg[k].w - mean) * inv_tau;
+            out[q] = r;
+        }
+    }
+}
+
 // fp32 (rows, cols) -> bf16, written at dst[r * ld + c] (or transposed: dst[c * ld + r]); optional
 // residual lo = bf16(x - hi) written at the same place of dst_lo
 __global__ void __launch_bounds__(256)
@@ -461,6 +569,13 @@ DL_EXPORT int dl_gemm_bf16_tn(const void* A, const void* B, float* C, int64_t M,
 DL_EXPORT int dl_softmax_rows_bf16(const float* W, float tau, void* S_hi, void* S_lo, int64_t ld_out, int64_t M,
                                    int64_t I, dl_stream_t stream) {
     DL_REQUIRE(W && S_hi && M > 0 && I > 0 && tau > 0.f && ld_out >= I);
+    const bool aligned = reinterpret_cast<uintptr_t>(W) % 16 == 0 && reinterpret_cast<uintptr_t>(S_hi) % 8 == 0 &&
+                         (S_lo == nullptr || reinterpret_cast<uintptr_t>(S_lo) % 8 == 0);
+    if (aligned && I % 4 == 0 && ld_out % 4 == 0 && I <= 256 * 4 * SM_MAXQ) {
+        softmax_rows_vec_kernel<<<(unsigned)M, 256, 0, dl_cast(stream)>>>(
+            W, 1.0f / tau, static_cast<__nv_bfloat16*>(S_hi), static_cast<__nv_bfloat16*>(S_lo), ld_out, (int)(I / 4));
+        return dl_launch_status();
+    }
     softmax_rows_kernel<<<(unsigned)M, 256, 0, dl_cast(stream)>>>(W, 1.0f / tau, static_cast<__nv_bfloat16*>(S_hi),
                                                                  static_cast<__nv_bfloat16*>(S_lo), ld_out, I);
     return dl_launch_status();
@@ -469,6 +584,11 @@ DL_EXPORT int dl_softmax_rows_bf16(const float* W, float tau, void* S_hi, void* 
 DL_EXPORT int dl_softmax_bwd_rows(const float* W, const float* gS, float tau, float* gW, int64_t M, int64_t I,
                                   dl_stream_t stream) {
     DL_REQUIRE(W && gS && gW && M > 0 && I > 0 && tau > 0.f);
+    if (I % 4 == 0 && I <= 256 * 4 * SM_MAXQ && reinterpret_cast<uintptr_t>(W) % 16 == 0 &&
+        reinterpret_cast<uintptr_t>(gS) % 16 == 0 && reinterpret_cast<uintptr_t>(gW) % 16 == 0) {
+        softmax_bwd_rows_vec_kernel<<<(unsigned)M, 256, 0, dl_cast(stream)>>>(W, gS, 1.0f / tau, gW, (int)(I / 4));
+        return dl_launch_status();
+    }
     softmax_bwd_rows_kernel<<<(unsigned)M, 256, 0, dl_cast(stream)>>>(W, gS, 1.0f / tau, gW, I);
     return dl_launch_status();
 }
