@@ -863,3 +863,57 @@ def test_dwn_stack_equals_sequential_layers(dev):
         assert set(stack.state_dict()) == {"layers." + k for k in seq.state_dict()}
     with pytest.raises(ValueError):
         DWNStack([])
+
+
+def test_prob_config2_full_size_node_subset_vs_oracle(dev):
+    """Config 2 at full size (B=1024, 4096 -> 8000 probabilistic nodes, n=6, GroupSum 10): forward values,
+    input gradient contributions and table gradients of a random subset of nodes against the oracle
+    (the oracle on all 8000 nodes would hold 2 GB of weights per intermediate)."""
+    from difflut_b200.layers import RandomLayer
+    from difflut_b200.nodes import NodeConfig, ProbabilisticNode
+
+    gen = torch.Generator().manual_seed(2)
+    B, I, N = 1024, 4096, 8000
+    x = torch.rand(B, I, generator=gen).clamp(1e-4, 1 - 1e-4)
+    layer = RandomLayer(I, N, ProbabilisticNode, NodeConfig(input_dim=6, output_dim=1), seed=0).to(dev).train()
+    raw = torch.randn(N, 64, 1, generator=gen)
+    with torch.no_grad():
+        layer.raw_weights.copy_(raw.to(dev))
+    y = layer(x.to(dev))
+    gy = torch.randn(B, N, generator=gen)
+    y.backward(gy.to(dev))
+    pick = torch.randperm(N, generator=gen)[:150]
+    idx = layer._mapping_indices.cpu()[pick]
+    raw_sub = raw[pick].clone().requires_grad_(True)
+    y_ref = O.prob_forward(O.gather_mapping(x, idx), raw_sub).reshape(B, -1)
+    torch.testing.assert_close(y.cpu()[:, pick], y_ref, rtol=1e-5, atol=1e-6)
+    y_ref.backward(gy[:, pick])
+    torch.testing.assert_close(layer.raw_weights.grad.cpu()[pick], raw_sub.grad, rtol=1e-4, atol=1e-5)
+    # fused GroupSum: logits = class sums of the same outputs
+    logits = layer.forward_groupsum(x.to(dev), 10, 1.0)
+    torch.testing.assert_close(logits.cpu(), O.groupsum(y.detach().cpu(), 10, 1.0), rtol=1e-5, atol=1e-3)
+
+
+def test_learnable_config3_width_node_subset_vs_oracle(dev):
+    """Config 3 widths (4096 inputs, 16000 nodes x 6 selections) at batch 256: the soft selection of a random
+    subset of nodes against an fp32 softmax + matmul, and their DWN outputs against the oracle."""
+    from difflut_b200.layers import LearnableLayer
+    from difflut_b200.nodes import DWNNode, NodeConfig
+
+    gen = torch.Generator().manual_seed(4)
+    B, I, N = 256, 4096, 16000
+    x = torch.bernoulli(torch.full((B, I), 0.5), generator=gen)
+    layer = LearnableLayer(I, N, DWNNode, NodeConfig(input_dim=6, output_dim=1)).to(dev).train()
+    with torch.no_grad():
+        layer.mapping.W.copy_((torch.randn(N * 6, I, generator=gen) * 1.5).to(dev))
+    y = layer(x.to(dev))  # feature-major path (batch is a multiple of 128)
+    pick = torch.randperm(N, generator=gen)[:200]
+    rows = (pick[:, None] * 6 + torch.arange(6)[None, :]).reshape(-1)
+    W_sub = layer.mapping.W.detach().cpu()[rows]
+    m_ref = O.learnable_soft_mapping(x, W_sub, layer.tau).view(B, len(pick), 6)
+    y_ref = O.dwn_forward(m_ref, layer.luts.detach().cpu()[pick]).reshape(B, -1)
+    safe = ((m_ref - 0.5).abs() > 1e-3).all(dim=2)  # selections that no rounding can move across 0.5
+    assert float(safe.float().mean()) > 0.5  # the comparison below is not vacuous
+    assert torch.equal(y.cpu()[:, pick][safe], y_ref[safe])
+    m = layer.get_mapping(x.to(dev)).cpu()[:, pick, :]
+    torch.testing.assert_close(m, m_ref, rtol=1e-3, atol=1e-4)
