@@ -12,6 +12,8 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace {
@@ -283,7 +285,8 @@ int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int
     typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    static encode_fn encode = nullptr;
+    static std::atomic<encode_fn> cached{nullptr};  // looked up once; concurrent first calls resolve the same pointer
+    encode_fn encode = cached.load(std::memory_order_acquire);
     if (encode == nullptr) {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult qres;
@@ -291,6 +294,7 @@ int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int
             fn == nullptr)
             return DL_ERR_LAUNCH;
         encode = reinterpret_cast<encode_fn>(fn);
+        cached.store(encode, std::memory_order_release);
     }
     const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
                                estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
