@@ -146,26 +146,27 @@ def host_floats(values):
     return (ctypes.c_float * len(values))(*[float(v) for v in values])
 
 
+_CALL_PLANS = {}
+
+
+def _call_plan(name: str):
+    """(function, argument kinds, takes a stream) of entry `name`, resolved once."""
+    plan = _CALL_PLANS.get(name)
+    if plan is None:
+        sig = SIGNATURES[name].replace(" ", "")
+        plan = (getattr(lib(), name), tuple(c for c in sig if c != "s"), sig.endswith("s"))
+        _CALL_PLANS[name] = plan
+    return plan
+
+
 def call(name: str, *args, stream=None):
     """Invoke C-ABI entry `name`; tensors become device pointers, the stream is appended."""
-    handle = lib()
-    fn = getattr(handle, name)
-    sig = SIGNATURES[name].replace(" ", "")
-    kinds = [c for c in sig if c != "s"]
+    fn, kinds, has_stream = _call_plan(name)
     if len(kinds) != len(args):
         raise TypeError(f"{name}: expected {len(kinds)} arguments, got {len(args)}")
-    conv = []
-    for kind, a in zip(kinds, args):
-        if kind == "p":
-            conv.append(_ptr(a))
-        elif kind in ("l", "i"):
-            conv.append(int(a))
-        else:
-            conv.append(float(a))
-    if sig.endswith("s"):
-        if stream is None:
-            stream = torch.cuda.current_stream().cuda_stream
-        conv.append(stream)
+    conv = [_ptr(a) if kind == "p" else (int(a) if kind in ("l", "i") else float(a)) for kind, a in zip(kinds, args)]
+    if has_stream:
+        conv.append(torch.cuda.current_stream().cuda_stream if stream is None else stream)
     code = fn(*conv)
     if code != 0:
-        raise RuntimeError(f"{name} failed: {handle.dl_error_string(code).decode()} (code {code})")
+        raise RuntimeError(f"{name} failed: {lib().dl_error_string(code).decode()} (code {code})")
