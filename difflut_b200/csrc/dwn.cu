@@ -1099,9 +1099,9 @@ void launch_fused_outs(unsigned blocks, cudaStream_t s, const uint8_t* addr_up, 
                        int64_t group_stride, int64_t N, int n, int64_t Bp, int64_t Wp) {
 #define DL_LAUNCH_FUSED(OUTS)                                                                                         \
     do {                                                                                                              \
-        /* largest shared-memory carve-out, so that 5 CTAs (5 x 32 KB of histograms) fit per SM */                    \
+        /* enough shared memory for 5 CTAs (5 x 33 KB), the rest stays L1 for index and transform rows */            \
         cudaFuncSetAttribute(dwn_bwd_fused_kernel<D, NN, SWZ, OUTS>, cudaFuncAttributePreferredSharedMemoryCarveout,  \
-                             100);                                                                                    \
+                              75);                                                                                    \
         dwn_bwd_fused_kernel<D, NN, SWZ, OUTS><<<blocks, HIST_WARPS * 32, 0, s>>>(                                     \
             addr_up, g_up, gdiv_up, gscale_up, efd_up, n_up, inv_ptr, inv_ent, in_bits, map, g_out, addr_out,         \
             gt_partial, group_stride, N, n, Bp, Wp);                                                                  \
