@@ -55,7 +55,8 @@ __global__ void p2p_barrier_kernel(PeerTable flags, int rank, int world, int* __
         const uint64_t t0 = global_timer_ns();
         uint32_t spins = 0;
         while (load_acquire_sys(mine) < e) {
-            if ((++spins & 0x3FFu) == 0 && global_timer_ns() - t0 > timeout_ns) {
+            // wall-clock limit, checked every 1024 polls, plus an absolute cap on the number of polls
+            if ((++spins & 0x3FFu) == 0 && (global_timer_ns() - t0 > timeout_ns || spins >= 0xFFFFF000u)) {
                 atomicCAS(&ctrl[1], 0, 1 + p);
                 break;
             }
