@@ -75,3 +75,35 @@ def test_peer_optimizer_matches_allreduce_path(tmp_path):
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert "rank 0 ok" in out.stdout and "rank 1 ok" in out.stdout
+
+
+def test_barrier_wait_runs_out_and_reports():
+    """A barrier whose peer never arrives (its flag array is a local buffer nothing writes) gives up after the
+    wall-clock limit, records which rank was missing and leaves the context usable."""
+    import ctypes
+    import time
+
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from difflut_b200 import _native
+
+    dev = torch.device("cuda", 0)
+    mine = torch.zeros(8, dtype=torch.int32, device=dev)
+    absent = torch.zeros(8, dtype=torch.int32, device=dev)  # stands in for rank 1's flag array
+    ctrl = torch.zeros(2, dtype=torch.int32, device=dev)
+    ptrs = (ctypes.c_void_p * 2)(mine.data_ptr(), absent.data_ptr())
+    t0 = time.time()
+    with torch.cuda.device(dev):
+        _native.call("dl_p2p_barrier", ctypes.addressof(ptrs), 0, 2, ctrl, 200)
+    torch.cuda.synchronize()
+    waited = time.time() - t0
+    assert 0.15 < waited < 5.0
+    assert ctrl.tolist() == [1, 2]  # epoch advanced; status = 1 + the missing rank
+    assert int(absent[0]) == 1  # this rank did publish its arrival
+    # a barrier of one rank with itself passes at once and the context still works
+    ctrl.zero_()
+    solo = (ctypes.c_void_p * 1)(mine.data_ptr())
+    with torch.cuda.device(dev):
+        _native.call("dl_p2p_barrier", ctypes.addressof(solo), 0, 1, ctrl, 200)
+    assert ctrl.tolist() == [1, 0]
+    assert float(torch.ones(4, device=dev).sum()) == 4.0
