@@ -514,7 +514,7 @@ def run_infer(args):
                     "h2d_bytes_per_step": best["batch"] * 196 * 4, "d2h_bytes_per_step": best["batch"] * 40},
             "roofline": {"bound": "hbm", "achieved": bytes_per_sample * best["samples_per_s"] / world / 1e9, "peak": 6545.6,
                          "unit": "GB/s", "frac": bytes_per_sample * best["samples_per_s"] / world / 1e9 / 6545.6,
-                         "traffic": None, "note": "ALU (three-input logic op) bound: see DESIGN.md"},
+                         "traffic": None, "note": "bound by the integer pipe: 63 three-input logic operations per node and 32 samples"},
         }), flush=True)
     if world > 1:
         sys.stdout.flush()

@@ -28,7 +28,8 @@ def _np(t):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("DIFFLUT_REFERENCE", "reference"),
+                    help="path of the unmodified difflut checkout (or set DIFFLUT_REFERENCE)")
     args = ap.parse_args()
     sys.path.insert(0, args.ref)
     warnings.filterwarnings("ignore")
