@@ -659,7 +659,9 @@ dwn_bwd_fused_kernel(const uint8_t* __restrict__ addr_up, const float* __restric
     const uint32_t ugdiv = (uint32_t)gdiv_up;
     const int src_lane = lane >> 3;          // which of a chunk's 4 words holds this lane's samples
     const int sh = (lane & 7) * 4;           // bit offset of its 4 samples inside that word
-    for (int64_t cg = 0; cg < G; ++cg) {
+    // gridDim.y > 1 only with one slab per group (group_stride > 0): the groups are then independent and
+    // layers with few nodes spread them over the grid's second dimension
+    for (int64_t cg = blockIdx.y; cg < G; cg += gridDim.y) {
         const int64_t left = C - cg * FUSED_CG;
         const int valid_chunks = left < FUSED_CG ? (int)left : FUSED_CG;
         for (int64_t f = (int64_t)blockIdx.x * HIST_WARPS + warp; f < N; f += nwarps) {
@@ -1093,7 +1095,7 @@ DL_EXPORT int64_t dl_dwn_bwd_groups(int64_t Bp) {
 namespace {
 
 template <bool D, int NN, bool SWZ>
-void launch_fused_outs(unsigned blocks, cudaStream_t s, const uint8_t* addr_up, const float* g_up, int64_t gdiv_up,
+void launch_fused_outs(dim3 grid, cudaStream_t s, const uint8_t* addr_up, const float* g_up, int64_t gdiv_up,
                        float gscale_up, const float* efd_up, int n_up, const int32_t* inv_ptr, const int32_t* inv_ent,
                        const uint32_t* in_bits, const int32_t* map, float* g_out, uint8_t* addr_out, float* gt_partial,
                        int64_t group_stride, int64_t N, int n, int64_t Bp, int64_t Wp) {
@@ -1102,7 +1104,7 @@ void launch_fused_outs(unsigned blocks, cudaStream_t s, const uint8_t* addr_up, 
         /* enough shared memory for 5 CTAs (5 x 33 KB), the rest stays L1 for index and transform rows */            \
         cudaFuncSetAttribute(dwn_bwd_fused_kernel<D, NN, SWZ, OUTS>, cudaFuncAttributePreferredSharedMemoryCarveout,  \
                               75);                                                                                    \
-        dwn_bwd_fused_kernel<D, NN, SWZ, OUTS><<<blocks, HIST_WARPS * 32, 0, s>>>(                                     \
+        dwn_bwd_fused_kernel<D, NN, SWZ, OUTS><<<grid, HIST_WARPS * 32, 0, s>>>(                                       \
             addr_up, g_up, gdiv_up, gscale_up, efd_up, n_up, inv_ptr, inv_ent, in_bits, map, g_out, addr_out,         \
             gt_partial, group_stride, N, n, Bp, Wp);                                                                  \
     } while (0)
@@ -1143,10 +1145,19 @@ int bwd_fused_entry(bool swz, const uint8_t* addr_up, const float* g_up, int64_t
     const int64_t cap = (int64_t)DL_NUM_SMS * 5;
     const int64_t blocks64 = dl_ceil_div(N, HIST_WARPS);
     const unsigned blocks = (unsigned)(blocks64 < cap ? blocks64 : cap);
+    // few nodes and one slab per group: fill the machine with groups in the grid's second dimension
+    int64_t gy = 1;
+    if (group_stride > 0 && blocks64 < cap) {
+        gy = cap / blocks64;
+        const int64_t G = dl_dwn_bwd_groups(Bp);
+        if (gy > G) gy = G;
+        if (gy < 1) gy = 1;
+    }
+    const dim3 grid(blocks, (unsigned)gy);
     const int64_t Wp = swz ? dl_swizzled_words(Bp) : Bp / 32;
     cudaStream_t s = dl_cast(stream);
 #define DL_FUSED_CALL(D, NN, SWZ)                                                                                     \
-    launch_fused_outs<D, NN, SWZ>(blocks, s, addr_up, g_up, gdiv_up, gscale_up, efd_up, (int)n_up, inv_ptr, inv_ent,  \
+    launch_fused_outs<D, NN, SWZ>(grid, s, addr_up, g_up, gdiv_up, gscale_up, efd_up, (int)n_up, inv_ptr, inv_ent,  \
                                   in_bits_t, map, g_out, addr_out, gt_partial, group_stride, N, (int)n, Bp, Wp)
     if (swz) {
         if (direct) { if (n == 6) DL_FUSED_CALL(true, 6, true); else DL_FUSED_CALL(true, 0, true); }

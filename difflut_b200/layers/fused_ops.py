@@ -230,6 +230,9 @@ class PackedInput:
         self.interleaved = bool(interleaved)  # chunk-interleaved rows (`encode_packed_s`) instead of natural ones
 
 
+FEW_NODES = 2960  # fewer nodes than resident warps of the fused backward: parallelise over sample groups as well
+
+
 class StackOptions:
     """How a DWNStackFunction reads its input and what it appends: `source` None (fp32 rows), a
     PatchGeometry (image batch, samples = patches) or a PackedInput (bits already packed); `flip`
@@ -353,14 +356,23 @@ class DWNStackFunction(torch.autograd.Function):
             addr = [None] * L
             gact = [None] * L
             gact[L - 1] = g_t
+            groups = int(_native.lib().dl_dwn_bwd_groups(Bp))
             for l in range(L - 1, -1, -1):
                 plan = levels[l][0]
                 below = l > 0 or need_x  # somebody reads this level's addresses and output gradient
                 if below:
                     addr[l] = torch.empty(plan.N, Bp, device=dev, dtype=torch.uint8)
+                # a level with many nodes adds its sample groups into the gradient in place; one with few nodes
+                # writes one slab per group, so that the groups can run side by side, and sums them afterwards
+                slabs = groups > 1 and plan.N < FEW_NODES
+                if slabs:
+                    dst = torch.empty(groups, sizes[l], device=dev, dtype=torch.float32)
+                    stride = sizes[l]
+                else:
+                    dst, stride = flat[offs[l]:], 0
                 if l == L - 1:
                     _native.call(fused, None, g_t, gdiv, gscale, None, 1, None, None, bits[l],
-                                 plan.map_nodes, None, addr[l], flat[offs[l]:], 0, plan.N, plan.n, Bp)
+                                 plan.map_nodes, None, addr[l], dst, stride, plan.N, plan.n, Bp)
                 else:
                     up = levels[l + 1][0]
                     if below:
@@ -368,7 +380,9 @@ class DWNStackFunction(torch.autograd.Function):
                     top = l + 1 == L - 1
                     _native.call(fused, addr[l + 1], gact[l + 1], gdiv if top else 1,
                                  gscale if top else 1.0, efd[l + 1], up.n, up.inv_ptr_virtual, up.inv_ent8_virtual,
-                                 bits[l], plan.map_nodes, gact[l], addr[l], flat[offs[l]:], 0, plan.N, plan.n, Bp)
+                                 bits[l], plan.map_nodes, gact[l], addr[l], dst, stride, plan.N, plan.n, Bp)
+                if slabs:
+                    _native.call("dl_sum_groups", dst, flat[offs[l]:], sizes[l], sizes[l], groups)
                     if l + 1 < L - 1:
                         gact[l + 1] = None  # the gradient of the level above is no longer needed
             gx = None
