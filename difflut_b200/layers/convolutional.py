@@ -112,6 +112,7 @@ class ConvolutionalLayer(LUTLayerMixin, nn.Module):
                 width = out_width
             self.trees.append(tree)
         self._level_plans = None
+        self._merge_ok = None
 
     @staticmethod
     def _pair(x):
@@ -139,29 +140,39 @@ class ConvolutionalLayer(LUTLayerMixin, nn.Module):
         return levels
 
     def _mergeable(self) -> bool:
-        subs = [layer for level in self._level_layers() for layer in level]
-        return all(type(s) is RandomLayer and s._stacked is not None and s.output_dim_per_node == 1
-                   and s._stacked == subs[0]._stacked for s in subs)
+        """All sub-layers are RandomLayers of one stacked node type (fixed at construction: checked once)."""
+        if self._merge_ok is None:
+            subs = [layer for level in self._level_layers() for layer in level]
+            self._merge_ok = all(type(s) is RandomLayer and s._stacked is not None and s.output_dim_per_node == 1
+                                 and s._stacked == subs[0]._stacked for s in subs)
+        return self._merge_ok
+
+    def _apply(self, fn, *args, **kwargs):
+        self._level_plans = None  # buffers are replaced by .to() / .cuda(): rebuild the merged maps
+        return super()._apply(fn, *args, **kwargs)
+
+    def _load_from_state_dict(self, *args, **kwargs):
+        self._level_plans = None  # the sub-layers' maps may be overwritten
+        return super()._load_from_state_dict(*args, **kwargs)
 
     def _plans(self, device):
         """One ConnectionPlan per depth level: the sub-layers' maps side by side, each tree's map shifted
-        to that tree's block of the level below.  Rebuilt when a sub-layer's map object changes."""
-        levels = self._level_layers()
-        key = (str(device),) + tuple((s._mapping_indices.data_ptr(), s._mapping_indices._version)
-                                     for level in levels for s in level)
-        if self._level_plans is None or self._level_plans[0] != key:
-            plans = []
-            for depth, level in enumerate(levels):
-                if depth == 0:
-                    rows = [s._mapping_indices.long() for s in level]
-                    width = self.input_size
-                else:
-                    below = self.hidden_layers[depth - 1]
-                    rows = [s._mapping_indices.long() + t * below for t, s in enumerate(level)]
-                    width = below * self.out_channels
-                plans.append(ConnectionPlan(torch.cat(rows, dim=0), width, 1, device))
-            self._level_plans = (key, plans)
-        return self._level_plans[1]
+        to that tree's block of the level below.  Built once per device; moving the module or loading a
+        state dict drops it (a map edited in place afterwards needs `conv._level_plans = None`)."""
+        if self._level_plans is not None and self._level_plans[0] == str(device):
+            return self._level_plans[1]
+        plans = []
+        for depth, level in enumerate(self._level_layers()):
+            if depth == 0:
+                rows = [s._mapping_indices.long() for s in level]
+                width = self.input_size
+            else:
+                below = self.hidden_layers[depth - 1]
+                rows = [s._mapping_indices.long() + t * below for t, s in enumerate(level)]
+                width = below * self.out_channels
+            plans.append(ConnectionPlan(torch.cat(rows, dim=0), width, 1, device))
+        self._level_plans = (str(device), plans)
+        return plans
 
     @staticmethod
     def _level_params(level):
