@@ -289,3 +289,26 @@ def test_convolutional_layer_structure_matches_reference(golden):
         ConvolutionConfig(in_channels=None, out_channels=4)
     with pytest.raises(ValueError):  # wrong rank
         conv(torch.zeros(2, 5))
+
+
+def test_dwn_stack_validation():
+    from difflut_b200.layers import DWNStack
+
+    cfg = NodeConfig(input_dim=6, output_dim=1)
+    a = RandomLayer(24, 10, DWNNode, cfg, seed=1)
+    b = RandomLayer(10, 4, DWNNode, cfg, seed=2)
+    stack = DWNStack([a, b])
+    assert list(stack.state_dict()) == ["layers." + k for k in torch.nn.Sequential(a, b).state_dict()]
+    assert [p.data_ptr() for p in stack.parameters()] == [a.luts.data_ptr(), b.luts.data_ptr()]  # same parameters
+    with pytest.raises(ValueError):
+        DWNStack([])
+    with pytest.raises(ValueError, match="does not match"):
+        DWNStack([b, a])
+    with pytest.raises(ValueError):
+        DWNStack([RandomLayer(24, 10, ProbabilisticNode, cfg, seed=1)])
+    with pytest.raises(ValueError):
+        DWNStack([RandomLayer(24, 10, DWNNode, NodeConfig(input_dim=6, output_dim=2), seed=1)])
+    with pytest.raises(ValueError, match="randperm"):
+        DWNStack([a, b], groupsum=GroupSum(k=2, tau=1.0, use_randperm=True))
+    with pytest.raises(RuntimeError):
+        stack(torch.zeros(3, 24))  # CPU tensors are rejected, there is no CPU path
