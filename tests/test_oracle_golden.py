@@ -268,3 +268,40 @@ def test_pack_layouts():
     assert rm.shape == (70, 2)
     for b, f in ((0, 0), (33, 7), (69, 44)):
         assert (rm[b, f // 32] >> (f % 32)) & 1 == int(bits[b, f])
+
+
+def test_oracle_adjoint_and_linearity_properties():
+    """Size-independent properties of the checker itself: the gather backward is the adjoint of the gather,
+    fold is the adjoint of unfold, GroupSum is linear, the two transforms are linear in the table."""
+    gen = torch.Generator().manual_seed(123)
+    x = torch.randn(7, 20, generator=gen, dtype=torch.float64)
+    idx = torch.randint(0, 20, (9, 4), generator=gen)
+    g = torch.randn(7, 9, 4, generator=gen, dtype=torch.float64)
+    lhs = (O.gather_mapping(x, idx) * g).sum()
+    rhs = (x * O.gather_mapping_backward(g, idx, 20).double()).sum()
+    assert abs(float(lhs - rhs)) < 1e-4 * (1 + abs(float(lhs)))
+    img = torch.randn(2, 3, 7, 6, generator=gen)
+    for kernel, stride, pad in (((3, 3), (1, 1), (0, 0)), ((3, 2), (2, 1), (1, 0)), ((4, 4), (3, 2), (0, 3))):
+        p = O.conv_unfold(img, kernel, stride, pad)
+        gp = torch.randn(p.shape, generator=gen)
+        a = (p * gp).sum()
+        b = (img * O.conv_fold(gp, img.shape, kernel, stride, pad)).sum()
+        assert abs(float(a - b)) < 1e-3 * (1 + abs(float(a)))
+    y = torch.randn(5, 23, generator=gen)
+    z = torch.randn(5, 23, generator=gen)
+    torch.testing.assert_close(O.groupsum(y + 2 * z, 4, 3.0), O.groupsum(y, 4, 3.0) + 2 * O.groupsum(z, 4, 3.0),
+                               rtol=1e-5, atol=1e-5)
+    t1 = torch.rand(3, 2, 16, generator=gen, dtype=torch.float64)
+    t2 = torch.rand(3, 2, 16, generator=gen, dtype=torch.float64)
+    torch.testing.assert_close(O.efd_transform(t1 + t2, 0.3, 0.4), O.efd_transform(t1, 0.3, 0.4) + O.efd_transform(t2, 0.3, 0.4))
+    torch.testing.assert_close(O.stable_transform(t1 + t2, 1.25), O.stable_transform(t1, 1.25) + O.stable_transform(t2, 1.25))
+    # the transform does not depend on the value of the differentiated bit of the address
+    T = O.efd_transform(t1, 0.3, 0.4)  # (N, O, L, n)
+    for i in range(4):
+        a = torch.arange(16)
+        assert torch.equal(T[:, :, a, i], T[:, :, a ^ (1 << i), i])
+    # packing round trip
+    bits = (torch.rand(70, 9, generator=gen) > 0.5).float()
+    packed = O.pack_bits_feature_major(bits)
+    unpacked = ((packed[:, :, None] >> np.arange(32, dtype=np.uint32)[None, None, :]) & 1).reshape(9, -1)[:, :70].T
+    assert np.array_equal(unpacked, bits.numpy().astype(np.uint32))
