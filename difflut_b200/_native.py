@@ -40,7 +40,7 @@ SIGNATURES = {
     "dl_dwn_fwd_vals_t": "ppppplll s",
     "dl_dwn_bwd_tables_t": "ppplfpplll s",
     "dl_dwn_bwd_input_t": "pplfpppplll s",
-    "dl_dwn_bwd_fused_t": "pplfplpppppppllll s",
+    "dl_dwn_bwd_fused_t": "pplfpllpppppppllll s",
     "dl_sum_groups": "pplll s",
     "dl_dwn_mapped_fwd": "ppplllli s",
     "dl_dwn_mapped_bwd": "pppppllll s",
@@ -59,7 +59,7 @@ SIGNATURES = {
     "dl_groupsum_t": "ppllfl s",
     "dl_dwn_fwd_groupsum_t": "ppppplllfl s",
     "dl_dwn_fwd_groupsum_s": "ppppplllfl s",
-    "dl_dwn_bwd_fused_s": "pplfplpppppppllll s",
+    "dl_dwn_bwd_fused_s": "pplfpllpppppppllll s",
     "dl_bits_swizzle_t": "ppll s",
     "dl_dwn_fwd_groupsum_noalloc_t": "pppplllfl s",
     "dl_flip_rows": "pplfl s",

@@ -46,3 +46,12 @@ __device__ __forceinline__ float adam_update(float p, float gi, float& m, float&
     const float denom = sqrtf(v) / bc2_sqrt + eps;
     return p - step_size * (m / denom);
 }
+
+// Software-pipelined fused DWN backward for n = 6, chunk-interleaved bits and whole 1024-sample blocks
+// (dwn_bwd_pipelined.cu); arguments as dl_dwn_bwd_fused_s after validation.  Returns DL_ERR_UNSUPPORTED
+// (nothing launched) when a row offset does not fit 32 bits.
+int dl_launch_bwd_pipelined(const uint8_t* addr_up, const float* g_up, int64_t gdiv_up, float gscale_up,
+                            const float* efd_up, int n_up, const int32_t* inv_ptr, const int32_t* inv_ent,
+                            const uint32_t* in_bits, const int32_t* map, float* g_out, uint8_t* addr_out,
+                            float* gt, int64_t group_stride, int64_t N, int64_t N_up, int64_t Bp, int64_t Wp,
+                            int blocks_per_item, cudaStream_t s);

@@ -5,6 +5,7 @@
 // coalesced row segment.  Per sample the EFD backward is one address, one histogram update and
 // n lookups in the per-step transform table `efd_t` instead of the reference's 2^n-term loop
 // (difflut/nodes/dwn_node.py:195-227).
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -1121,8 +1122,25 @@ void launch_fused_outs(dim3 grid, cudaStream_t s, const uint8_t* addr_up, const 
 #undef DL_LAUNCH_FUSED
 }
 
+// Tuning switches read once from the environment (measurement aids; the defaults are the product):
+// DIFFLUT_BWD_GENERAL=1 keeps every call on the general kernel, DIFFLUT_BWD_BLOCKS_PER_ITEM=k fixes the
+// number of 1024-sample blocks one (node, group) item of the pipelined kernel spans.
+struct FusedTuning {
+    bool general_only;
+    int blocks_per_item;
+};
+const FusedTuning& fused_tuning() {
+    static const FusedTuning t = [] {
+        FusedTuning v{false, 0};
+        if (const char* e = getenv("DIFFLUT_BWD_GENERAL")) v.general_only = e[0] == '1';
+        if (const char* e = getenv("DIFFLUT_BWD_BLOCKS_PER_ITEM")) v.blocks_per_item = atoi(e);
+        return v;
+    }();
+    return t;
+}
+
 int bwd_fused_entry(bool swz, const uint8_t* addr_up, const float* g_up, int64_t gdiv_up, float gscale_up,
-                    const float* efd_up, int64_t n_up, const int32_t* inv_ptr, const int32_t* inv_ent,
+                    const float* efd_up, int64_t n_up, int64_t N_up, const int32_t* inv_ptr, const int32_t* inv_ent,
                     const uint32_t* in_bits_t, const int32_t* map, float* g_out, uint8_t* addr_out, float* gt_partial,
                     int64_t group_stride, int64_t N, int64_t n, int64_t Bp, dl_stream_t stream) {
     DL_REQUIRE(g_up && in_bits_t && map && gt_partial && N > 0 && gdiv_up > 0);
@@ -1134,7 +1152,7 @@ int bwd_fused_entry(bool swz, const uint8_t* addr_up, const float* g_up, int64_t
     if (n < 1 || n > DL_MAX_FAST_N) return DL_ERR_UNSUPPORTED;
     const bool direct = (inv_ptr == nullptr);
     if (!direct) {
-        DL_REQUIRE(addr_up && efd_up && inv_ent);
+        DL_REQUIRE(addr_up && efd_up && inv_ent && N_up > 0);
         DL_REQUIRE_ALIGNED(addr_up, 4);
         if (n_up < 1 || n_up > DL_MAX_FAST_N) return DL_ERR_UNSUPPORTED;
     }
@@ -1156,6 +1174,20 @@ int bwd_fused_entry(bool swz, const uint8_t* addr_up, const float* g_up, int64_t
     const dim3 grid(blocks, (unsigned)gy);
     const int64_t Wp = swz ? dl_swizzled_words(Bp) : Bp / 32;
     cudaStream_t s = dl_cast(stream);
+    // the common case (n = 6, interleaved bits, whole 1024-sample blocks) has a software-pipelined kernel
+    if (swz && n == 6 && Bp % 1024 == 0 && Bp < ((int64_t)1 << 31) && !fused_tuning().general_only) {
+        int bpi = fused_tuning().blocks_per_item;
+        if (bpi <= 0) {
+            // two blocks per item halve the histogram clear/reduce work; only while every warp slot of the
+            // persistent grid still gets several items per launch
+            const int64_t items2 = N * (Bp / 2048);
+            bpi = (group_stride == 0 && Bp % 2048 == 0 && items2 >= cap * HIST_WARPS * 4) ? 2 : 1;
+        }
+        const int rc = dl_launch_bwd_pipelined(addr_up, g_up, gdiv_up, gscale_up, efd_up, (int)n_up, inv_ptr, inv_ent,
+                                               in_bits_t, map, g_out, addr_out, gt_partial, group_stride, N,
+                                               direct ? 0 : N_up, Bp, Wp, bpi, s);
+        if (rc != DL_ERR_UNSUPPORTED) return rc;  // else: row offsets beyond 32 bits, general kernel below
+    }
 #define DL_FUSED_CALL(D, NN, SWZ)                                                                                     \
     launch_fused_outs<D, NN, SWZ>(grid, s, addr_up, g_up, gdiv_up, gscale_up, efd_up, (int)n_up, inv_ptr, inv_ent,  \
                                   in_bits_t, map, g_out, addr_out, gt_partial, group_stride, N, (int)n, Bp, Wp)
@@ -1173,20 +1205,20 @@ int bwd_fused_entry(bool swz, const uint8_t* addr_up, const float* g_up, int64_t
 }  // namespace
 
 DL_EXPORT int dl_dwn_bwd_fused_t(const uint8_t* addr_up, const float* g_up, int64_t gdiv_up, float gscale_up,
-                                 const float* efd_up, int64_t n_up, const int32_t* inv_ptr,
+                                 const float* efd_up, int64_t n_up, int64_t N_up, const int32_t* inv_ptr,
                                  const int32_t* inv_ent, const uint32_t* in_bits_t, const int32_t* map,
                                  float* g_out, uint8_t* addr_out, float* gt_partial, int64_t group_stride,
                                  int64_t N, int64_t n, int64_t Bp, dl_stream_t stream) {
-    return bwd_fused_entry(false, addr_up, g_up, gdiv_up, gscale_up, efd_up, n_up, inv_ptr, inv_ent, in_bits_t, map,
+    return bwd_fused_entry(false, addr_up, g_up, gdiv_up, gscale_up, efd_up, n_up, N_up, inv_ptr, inv_ent, in_bits_t, map,
                            g_out, addr_out, gt_partial, group_stride, N, n, Bp, stream);
 }
 
 DL_EXPORT int dl_dwn_bwd_fused_s(const uint8_t* addr_up, const float* g_up, int64_t gdiv_up, float gscale_up,
-                                 const float* efd_up, int64_t n_up, const int32_t* inv_ptr,
+                                 const float* efd_up, int64_t n_up, int64_t N_up, const int32_t* inv_ptr,
                                  const int32_t* inv_ent, const uint32_t* in_bits_s, const int32_t* map,
                                  float* g_out, uint8_t* addr_out, float* gt_partial, int64_t group_stride,
                                  int64_t N, int64_t n, int64_t Bp, dl_stream_t stream) {
-    return bwd_fused_entry(true, addr_up, g_up, gdiv_up, gscale_up, efd_up, n_up, inv_ptr, inv_ent, in_bits_s, map,
+    return bwd_fused_entry(true, addr_up, g_up, gdiv_up, gscale_up, efd_up, n_up, N_up, inv_ptr, inv_ent, in_bits_s, map,
                            g_out, addr_out, gt_partial, group_stride, N, n, Bp, stream);
 }
 

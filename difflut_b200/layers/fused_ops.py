@@ -200,7 +200,7 @@ class DWNLayerFunction(torch.autograd.Function):
                 # large batches: one warp per (1024-sample group, node) and an ordered sum of the groups, so
                 # that layers with few nodes still fill the machine
                 partial = torch.empty(groups, gt.numel(), device=g.device, dtype=torch.float32)
-                _native.call("dl_dwn_bwd_fused_t", None, g_t, 1, 1.0, None, 1, None, None, bits, plan.map_virtual,
+                _native.call("dl_dwn_bwd_fused_t", None, g_t, 1, 1.0, None, 1, 0, None, None, bits, plan.map_virtual,
                              None, addr, partial, gt.numel(), NO, n, Bp)
                 _native.call("dl_sum_groups", partial, gt, gt.numel(), gt.numel(), groups)
             if ctx.stable_scale is not None:
@@ -371,7 +371,7 @@ class DWNStackFunction(torch.autograd.Function):
                 else:
                     dst, stride = flat[offs[l]:], 0
                 if l == L - 1:
-                    _native.call(fused, None, g_t, gdiv, gscale, None, 1, None, None, bits[l],
+                    _native.call(fused, None, g_t, gdiv, gscale, None, 1, 0, None, None, bits[l],
                                  plan.map_nodes, None, addr[l], dst, stride, plan.N, plan.n, Bp)
                 else:
                     up = levels[l + 1][0]
@@ -379,7 +379,7 @@ class DWNStackFunction(torch.autograd.Function):
                         gact[l] = torch.empty(plan.N, Bp, device=dev, dtype=torch.float32)
                     top = l + 1 == L - 1
                     _native.call(fused, addr[l + 1], gact[l + 1], gdiv if top else 1,
-                                 gscale if top else 1.0, efd[l + 1], up.n, up.inv_ptr_virtual, up.inv_ent8_virtual,
+                                 gscale if top else 1.0, efd[l + 1], up.n, up.N, up.inv_ptr_virtual, up.inv_ent8_virtual,
                                  bits[l], plan.map_nodes, gact[l], addr[l], dst, stride, plan.N, plan.n, Bp)
                 if slabs:
                     _native.call("dl_sum_groups", dst, flat[offs[l]:], sizes[l], sizes[l], groups)

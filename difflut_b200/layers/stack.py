@@ -42,6 +42,9 @@ class DWNStack(nn.Module):
             if not ok:
                 raise ValueError("DWNStack takes RandomLayer layers of DWNNode / DWNStableNode with n <= 6 and "
                                  "output_dim 1")
+            if l.flip_probability > 0.0 or l.grad_stabilization != "none":
+                raise ValueError("DWNStack does not apply flip_probability / grad_stabilization between its "
+                                 "bit-packed layers; call such layers one by one")
             if width is not None and l.input_size != width:
                 raise ValueError(f"layer input_size {l.input_size} does not match the {width} outputs feeding it")
             width = l.output_size

@@ -43,6 +43,11 @@ class DWNNetwork:
         for l in layers:
             if l._stacked != "dwn" or l.n > 6 or l.output_dim_per_node != 1:
                 raise ValueError("DWNNetwork takes RandomLayer(DWNNode) layers with n <= 6 and output_dim 1")
+            if l.flip_probability > 0.0 or l.grad_stabilization != "none":
+                # the per-layer API applies these options (layers/base_layer.py); this executor keeps the
+                # activations bit-packed between layers and does not, so it refuses instead of ignoring them
+                raise ValueError("DWNNetwork does not apply flip_probability / grad_stabilization; "
+                                 "use the layer API (or DWNStack without these options) for such layers")
         self.encoder, self.layers, self.groupsum = encoder, list(layers), groupsum
         self.device = self.layers[0].luts.device
         if self.device.type != "cuda":
@@ -241,7 +246,7 @@ class DWNNetwork:
         for li in range(last, -1, -1):
             grad_out = self.flat_grad[self.offsets[li]:]
             if li == last:
-                _native.call(fused, None, self.dlogits_t, self.gsz, 1.0 / self.tau, None, 1, None, None,
+                _native.call(fused, None, self.dlogits_t, self.gsz, 1.0 / self.tau, None, 1, 0, None, None,
                              self.bits[li], self.plans[li].map_nodes, None, self.addr[li], grad_out, 0,
                              self.N[li], self.n[li], Bp)
             else:
@@ -250,7 +255,7 @@ class DWNNetwork:
                     g_up, gdiv, gscale = self.dlogits_t, self.gsz, 1.0 / self.tau
                 else:
                     g_up, gdiv, gscale = self.gact[up], 1, 1.0
-                _native.call(fused, self.addr[up], g_up, gdiv, gscale, self.efd[up], self.n[up],
+                _native.call(fused, self.addr[up], g_up, gdiv, gscale, self.efd[up], self.n[up], self.N[up],
                              self.plans[up].inv_ptr_virtual, self.plans[up].inv_ent8_virtual, self.bits[li],
                              self.plans[li].map_nodes, self.gact[li] if li > 0 else None,
                              self.addr[li] if li > 0 else None, grad_out, 0, self.N[li], self.n[li], Bp)

@@ -183,12 +183,15 @@ int dl_dwn_bwd_input_t(const uint8_t* addr_t, const float* g_t, int64_t gdiv, fl
  * gt_partial is caller-provided scratch: dl_dwn_bwd_groups(Bp) slabs of `group_stride` floats
  * (slab g holds the table gradient of samples [1024 g, 1024 (g+1)) at offset f*2^n); sum them
  * with dl_sum_groups, which adds the slabs in order (reproducible).  group_stride == 0: one
- * slab; the kernel itself adds the groups into it, in the same order (the same warp owns a node
- * in every group), so gt_partial then receives the complete table gradient, bit-identical to
- * the ordered sum of the slabs.                                                              */
+ * slab; the kernel itself adds the groups into it in a fixed order (the same warp owns a node in
+ * every group), so gt_partial then receives the complete table gradient, reproducible from run to
+ * run.  In this mode dl_dwn_bwd_fused_s may keep one histogram over two consecutive 1024-sample
+ * blocks (when n == 6, Bp is a multiple of 2048 and there are enough nodes to fill the GPU), which
+ * changes the rounding order against the ordered slab sum, not the value.
+ * N_up = number of nodes of the layer above (rows of addr_up); ignored when inv_ptr == NULL.   */
 int64_t dl_dwn_bwd_groups(int64_t Bp);
 int dl_dwn_bwd_fused_t(const uint8_t* addr_up, const float* g_up, int64_t gdiv_up, float gscale_up,
-                       const float* efd_up, int64_t n_up, const int32_t* inv_ptr,
+                       const float* efd_up, int64_t n_up, int64_t N_up, const int32_t* inv_ptr,
                        const int32_t* inv_ent, const uint32_t* in_bits_t, const int32_t* map,
                        float* g_out, uint8_t* addr_out, float* gt_partial, int64_t group_stride,
                        int64_t N, int64_t n, int64_t Bp, dl_stream_t stream);
@@ -334,7 +337,7 @@ int dl_dwn_fwd_groupsum_s(const uint32_t* in_bits_s, const int32_t* map, const f
                           float* partial, float* logits_t, int64_t N, int64_t n, int64_t k, float tau,
                           int64_t Bp, dl_stream_t stream);
 int dl_dwn_bwd_fused_s(const uint8_t* addr_up, const float* g_up, int64_t gdiv_up, float gscale_up,
-                       const float* efd_up, int64_t n_up, const int32_t* inv_ptr, const int32_t* inv_ent,
+                       const float* efd_up, int64_t n_up, int64_t N_up, const int32_t* inv_ptr, const int32_t* inv_ent,
                        const uint32_t* in_bits_s, const int32_t* map, float* g_out, uint8_t* addr_out,
                        float* gt_partial, int64_t group_stride, int64_t N, int64_t n, int64_t Bp,
                        dl_stream_t stream);

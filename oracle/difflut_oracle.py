@@ -196,8 +196,9 @@ def efd_transform(luts: torch.Tensor, alpha: float, beta: float) -> torch.Tensor
 
 
 def dwn_backward(
-    xm: torch.Tensor, luts: torch.Tensor, g: torch.Tensor, alpha: float, beta: float
-) -> Tuple[torch.Tensor, torch.Tensor]:
+    xm: torch.Tensor, luts: torch.Tensor, g: torch.Tensor, alpha: float, beta: float,
+    need_input_grad: bool = True, transform: Optional[torch.Tensor] = None,
+) -> Tuple[Optional[torch.Tensor], torch.Tensor]:
     """EFD backward: (gxm (B,N,n) fp32, gluts (N,O,2^n) fp32).
 
     dwn_node.py:167-229.  gluts[j,o,addr_b] += g[b,j,o];  gxm[b,j,i] = sum_o g[b,j,o]*T[j,o,addr,i].
@@ -209,9 +210,11 @@ def dwn_backward(
     B, N = addr.shape
     _, O, L = luts.shape
     n = xm.shape[-1]
-    T = efd_transform(luts, alpha, beta)  # (N,O,L,n)
-    Tsel = T[torch.arange(N)[None, :].expand(B, N), :, addr]  # (B,N,O,n)
-    gxm = (g.double().unsqueeze(-1) * Tsel).sum(2).float()
+    gxm = None
+    if need_input_grad:  # callers that only want the table gradient (first layer) skip this half
+        T = transform if transform is not None else efd_transform(luts, alpha, beta)  # (N,O,L,n)
+        Tsel = T[torch.arange(N)[None, :].expand(B, N), :, addr]  # (B,N,O,n)
+        gxm = (g.double().unsqueeze(-1) * Tsel).sum(2).float()
     gl = torch.zeros(N, O, L, dtype=torch.float64)
     flat = (torch.arange(N)[None, :, None] * O + torch.arange(O)[None, None, :]) * L + addr[:, :, None]
     gl.view(-1).index_add_(0, flat.reshape(-1), g.double().reshape(-1))
@@ -454,15 +457,19 @@ def dwn_network_forward(bits: torch.Tensor, maps, tables, k: int, tau: float):
 
 
 def dwn_network_backward(acts, maps, tables, glogits: torch.Tensor, k: int, tau: float,
-                         alpha: float, beta: float):
-    """Backward of `dwn_network_forward`: list of table grads (N_l,1,2^n), first->last."""
+                         alpha: float, beta: float, transforms=None):
+    """Backward of `dwn_network_forward`: list of table grads (N_l,1,2^n), first->last.
+
+    `transforms` may hold `efd_transform(tables[l], alpha, beta)` per layer (a caller that walks the
+    batch in chunks computes them once); the first layer's input gradient is not formed."""
     N_last = tables[-1].shape[0]
     gsz = (N_last + k - 1) // k
     g = (glogits / tau).repeat_interleave(gsz, dim=1)[:, :N_last]  # (B, N_L)
     grads = [None] * len(tables)
     for l in range(len(tables) - 1, -1, -1):
         xm = gather_mapping(acts[l], maps[l])
-        gxm, gl = dwn_backward(xm, tables[l], g.unsqueeze(-1), alpha, beta)
+        gxm, gl = dwn_backward(xm, tables[l], g.unsqueeze(-1), alpha, beta, need_input_grad=l > 0,
+                               transform=None if transforms is None else transforms[l])
         grads[l] = gl
         if l > 0:
             g = gather_mapping_backward(gxm, maps[l], acts[l].shape[1])
@@ -493,3 +500,31 @@ def adam_step(p, g, m, v, step: int, lr: float, b1: float = 0.9, b2: float = 0.9
     denom = v.sqrt() / math.sqrt(bc2) + eps
     p = p - (lr / bc1) * m / denom
     return p, m, v
+
+
+def dwn_network_train_reference(x: torch.Tensor, labels: torch.Tensor, thresholds: torch.Tensor, maps, tables,
+                                k: int, tau: float, alpha: float, beta: float, chunk_rows: int = 1024):
+    """Encoder -> DWN stack -> GroupSum -> mean cross-entropy, forward and backward, walked in row
+    chunks so that a full-width network at a batch of several thousand fits in host memory.
+
+    The same composition as `dwn_network_forward` / `dwn_network_backward` around
+    `F.cross_entropy(logits, labels)` (mean over ALL rows of x); per-chunk table gradients are added in
+    float64 and rounded once.  Returns (logits (B,k) fp32, loss (scalar fp32 tensor), [table grads]).
+    """
+    B = x.shape[0]
+    logits_all, loss_sum = [], 0.0
+    grads = [torch.zeros(t.shape, dtype=torch.float64) for t in tables]
+    transforms = [None] + [efd_transform(t, alpha, beta) for t in tables[1:]]
+    for lo in range(0, B, chunk_rows):
+        xs, ys = x[lo:lo + chunk_rows], labels[lo:lo + chunk_rows].long()
+        bits = thermometer_encode(xs, thresholds)
+        logits, acts = dwn_network_forward(bits, maps, tables, k, tau)
+        lg = logits.clone().requires_grad_(True)
+        part = F.cross_entropy(lg, ys, reduction="sum")
+        part.backward()
+        loss_sum += float(part.detach().double())
+        for acc, g in zip(grads, dwn_network_backward(acts, maps, tables, lg.grad / B, k, tau, alpha, beta,
+                                                    transforms)):
+            acc += g.double()
+        logits_all.append(logits)
+    return torch.cat(logits_all), torch.tensor(loss_sum / B, dtype=torch.float32), [g.float() for g in grads]

@@ -312,3 +312,20 @@ def test_dwn_stack_validation():
         DWNStack([a, b], groupsum=GroupSum(k=2, tau=1.0, use_randperm=True))
     with pytest.raises(RuntimeError):
         stack(torch.zeros(3, 24))  # CPU tensors are rejected, there is no CPU path
+    # options that only the per-layer API applies are refused, not silently dropped
+    with pytest.raises(ValueError, match="flip_probability"):
+        DWNStack([RandomLayer(24, 10, DWNNode, cfg, seed=1, flip_probability=0.1), b])
+    with pytest.raises(ValueError, match="grad_stabilization"):
+        DWNStack([a, RandomLayer(10, 4, DWNNode, cfg, seed=2, grad_stabilization="layerwise")])
+
+
+def test_dwn_network_refuses_layer_options_it_would_drop():
+    from difflut_b200.encoder import ThermometerEncoder
+    from difflut_b200.network import DWNNetwork
+
+    cfg = NodeConfig(input_dim=6, output_dim=1)
+    enc = ThermometerEncoder(num_bits=2).fit(torch.rand(16, 12))
+    gs = GroupSum(k=2, tau=1.0, use_randperm=False)
+    for kw in ({"flip_probability": 0.2}, {"grad_stabilization": "batchwise"}):
+        with pytest.raises(ValueError, match="flip_probability / grad_stabilization"):
+            DWNNetwork(enc, [RandomLayer(24, 10, DWNNode, cfg, seed=1, **kw)], gs)

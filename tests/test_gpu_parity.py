@@ -13,6 +13,7 @@ import pytest
 import torch
 
 from oracle import difflut_oracle as O
+from parity_util import close_normwise
 
 pytestmark = pytest.mark.gpu
 warnings.simplefilter("ignore")
@@ -234,8 +235,8 @@ def test_hybrid_standalone_node_vs_oracle(dev):
     gy = torch.randn(B, O_, generator=gen)
     y.backward(gy.to(dev))
     gxm, gl = O.hybrid_backward(x.unsqueeze(1), tab.unsqueeze(0), gy.unsqueeze(1))
-    torch.testing.assert_close(xg.grad.cpu(), gxm.squeeze(1), rtol=1e-4, atol=1e-6)
-    torch.testing.assert_close(node.raw_luts.grad.cpu(), gl.squeeze(0) * tab * (1 - tab), rtol=1e-4, atol=1e-6)
+    close_normwise(xg.grad.cpu(), gxm.squeeze(1), "xg.grad.cpu()")
+    close_normwise(node.raw_luts.grad.cpu(), gl.squeeze(0) * tab * (1 - tab), "node.raw_luts.grad.cpu()")
     with pytest.raises(ValueError):
         HybridNode(input_dim=7, output_dim=1)
 
@@ -259,8 +260,8 @@ def test_dwn_stable_standalone_node_vs_oracle(dev, n, O_):
     gy = torch.randn(B, O_, generator=gen)
     y.backward(gy.to(dev))
     gxm, gl = O.dwn_stable_backward(x.unsqueeze(1), tab.unsqueeze(0), gy.unsqueeze(1), 0.9)
-    torch.testing.assert_close(xg.grad.cpu(), gxm.squeeze(1), rtol=1e-4, atol=1e-6)
-    torch.testing.assert_close(node.raw_luts.grad.cpu(), (gl.squeeze(0) * tab * (1 - tab)), rtol=1e-4, atol=1e-6)
+    close_normwise(xg.grad.cpu(), gxm.squeeze(1), "xg.grad.cpu()")
+    close_normwise(node.raw_luts.grad.cpu(), (gl.squeeze(0) * tab * (1 - tab)), "node.raw_luts.grad.cpu()")
     node.eval()
     xb = (x >= 0.5).float()
     assert torch.equal(node(xb.to(dev)).cpu(), O.dwn_forward_eval(xb.unsqueeze(1), tab.unsqueeze(0)).squeeze(1))
@@ -288,7 +289,7 @@ def test_dwn_standalone_node_vs_oracle(dev, n, O_):
     y.backward(gy.to(dev))
     alpha, beta = 0.5 * 0.75 ** (n - 1), 0.25 / 0.75
     gxm, gl = O.dwn_backward(x.unsqueeze(1), tab.unsqueeze(0), gy.unsqueeze(1), alpha, beta)
-    torch.testing.assert_close(xg.grad.cpu(), gxm.squeeze(1), rtol=1e-4, atol=1e-6)
+    close_normwise(xg.grad.cpu(), gxm.squeeze(1), "xg.grad.cpu()")
     torch.testing.assert_close(node.luts.grad.cpu(), gl.squeeze(0), rtol=1e-5, atol=1e-6)
     node.eval()
     xb = (x >= 0.5).float()
@@ -336,7 +337,7 @@ def test_dwn_config1_full_size_vs_oracle(dev):
     y.sum().backward()
     gxm, gl = O.dwn_backward(xm, tab, torch.ones(256, 2000, 1), 0.5 * 0.75 ** 5, 0.25 / 0.75)
     torch.testing.assert_close(layer.luts.grad.cpu(), gl, rtol=1e-5, atol=1e-6)
-    torch.testing.assert_close(bg.grad.cpu(), O.gather_mapping_backward(gxm, idx, 2352), rtol=1e-4, atol=1e-6)
+    close_normwise(bg.grad.cpu(), O.gather_mapping_backward(gxm, idx, 2352), "bg.grad.cpu()")
 
 
 # ------------------------------------------------------------------------------ probabilistic
@@ -358,16 +359,16 @@ def test_prob_layer_matches_reference(golden, dev):
     loss = torch.nn.functional.cross_entropy(logits, T(g["labels"]).to(dev))
     loss.backward()
     torch.testing.assert_close(loss.detach().cpu(), T(g["loss"]), rtol=1e-5, atol=1e-6)
-    torch.testing.assert_close(xg.grad.cpu(), T(g["gx"]), rtol=1e-4, atol=1e-7)
-    torch.testing.assert_close(layer.raw_weights.grad.cpu(), T(g["graw"]), rtol=1e-4, atol=1e-7)
+    close_normwise(xg.grad.cpu(), T(g["gx"]), "xg.grad.cpu()")
+    close_normwise(layer.raw_weights.grad.cpu(), T(g["graw"]), "layer.raw_weights.grad.cpu()")
     # fused with GroupSum: same logits and gradients without the (B, N) tensor
     layer.raw_weights.grad = None
     xg2 = x.to(dev).requires_grad_(True)
     logits2 = layer.forward_groupsum(xg2, 10, 1.0)
     torch.testing.assert_close(logits2.cpu(), T(g["logits"]), rtol=1e-5, atol=1e-5)
     torch.nn.functional.cross_entropy(logits2, T(g["labels"]).to(dev)).backward()
-    torch.testing.assert_close(xg2.grad.cpu(), T(g["gx"]), rtol=1e-4, atol=1e-7)
-    torch.testing.assert_close(layer.raw_weights.grad.cpu(), T(g["graw"]), rtol=1e-4, atol=1e-7)
+    close_normwise(xg2.grad.cpu(), T(g["gx"]), "xg2.grad.cpu()")
+    close_normwise(layer.raw_weights.grad.cpu(), T(g["graw"]), "layer.raw_weights.grad.cpu()")
     layer.eval()
     ye = layer((x >= 0.5).float().to(dev))
     assert np.array_equal(ye.cpu().numpy().astype(np.uint8), g["y_eval"])
@@ -386,8 +387,8 @@ def test_prob_layer_temperature_multi_output(golden, dev):
     y = layer(xg)
     torch.testing.assert_close(y.cpu(), T(g["t_y"]), rtol=1e-5, atol=1e-6)
     y.backward(T(g["t_gy"]).to(dev))
-    torch.testing.assert_close(xg.grad.cpu(), T(g["t_gx"]), rtol=1e-4, atol=1e-6)
-    torch.testing.assert_close(layer.raw_weights.grad.cpu(), T(g["t_graw"]), rtol=1e-4, atol=1e-6)
+    close_normwise(xg.grad.cpu(), T(g["t_gx"]), "xg.grad.cpu()")
+    close_normwise(layer.raw_weights.grad.cpu(), T(g["t_graw"]), "layer.raw_weights.grad.cpu()")
     # standalone node on mapped inputs
     node = ProbabilisticNode(input_dim=3, output_dim=2, temperature=0.5).to(dev)
     with torch.no_grad():
@@ -410,7 +411,7 @@ def test_prob_edge_inputs_finite(dev):
     yr.sum().backward()
     assert torch.isfinite(x.grad).all()
     torch.testing.assert_close(y.detach().cpu(), yr.detach().reshape(3, 1), rtol=1e-5, atol=1e-6)
-    torch.testing.assert_close(x.grad.cpu(), xr.grad, rtol=1e-4, atol=1e-6)
+    close_normwise(x.grad.cpu(), xr.grad, "x.grad.cpu()")
 
 
 # ------------------------------------------------------------------------------ learnable
@@ -535,7 +536,7 @@ def test_dwn_net3_two_adam_steps_match_reference(golden, dev, use_graph, fused):
         loss = net.train_step(x, labels, use_graph=use_graph)
         torch.testing.assert_close(loss.cpu()[0], T(g[f"loss_step{step}"]), rtol=1e-5, atol=1e-6)
         for li in range(3):
-            torch.testing.assert_close(layers[li].luts.grad.cpu(), T(g[f"gtables{li}_step{step}"]), rtol=1e-4, atol=1e-7)
+            close_normwise(layers[li].luts.grad.cpu(), T(g[f"gtables{li}_step{step}"]), "layers[li].luts.grad.cpu()")
             torch.testing.assert_close(layers[li].luts.detach().cpu(), T(g[f"tables{li}_after{step}"]), rtol=1e-5, atol=2e-6)
     counts = net.hard_counts(x)
     assert np.array_equal(counts.cpu().numpy(), g["eval_counts"])
@@ -560,7 +561,7 @@ def test_layer_api_equals_fused_network(golden, dev):
     torch.testing.assert_close(logits.cpu(), T(g["logits_step0"]), rtol=1e-5, atol=1e-5)
     torch.nn.functional.cross_entropy(logits, labels).backward()
     for li in range(3):
-        torch.testing.assert_close(layers[li].luts.grad.cpu(), T(g[f"gtables{li}_step0"]), rtol=1e-4, atol=1e-7)
+        close_normwise(layers[li].luts.grad.cpu(), T(g[f"gtables{li}_step0"]), "layers[li].luts.grad.cpu()")
 
 
 def test_full_size_properties(dev):
@@ -660,7 +661,7 @@ def test_fused_backward_equals_separate_kernels_multi_group(dev):
     torch.nn.functional.cross_entropy(lg, labels).backward()
     ref = O.dwn_network_backward(acts, maps, tabs0, lg.grad, k, tau, 0.5 * 0.75 ** 5, 0.25 / 0.75)
     for a, r in zip(grads[True], ref):
-        torch.testing.assert_close(a, r, rtol=1e-4, atol=1e-7)
+        close_normwise(a, r, "a")
 
 
 @pytest.mark.parametrize("B", [128, 1024, 2500])
@@ -774,7 +775,7 @@ def test_wide_materialised_path_equals_fused_layer(dev):
     xm = O.gather_mapping(x, layer._mapping_indices.cpu())
     gxm, gl = O.dwn_backward(xm, tab, gy.cpu().reshape(B, N, 2), layer.alpha, layer.beta)
     torch.testing.assert_close(gta.cpu(), gl, rtol=1e-5, atol=1e-6)
-    torch.testing.assert_close(ga.cpu(), O.gather_mapping_backward(gxm, layer._mapping_indices.cpu(), I), rtol=1e-4, atol=1e-6)
+    close_normwise(ga.cpu(), O.gather_mapping_backward(gxm, layer._mapping_indices.cpu(), I), "ga.cpu()")
 
 
 def test_dwn_stack_equals_sequential_layers(dev):
@@ -813,9 +814,9 @@ def test_dwn_stack_equals_sequential_layers(dev):
         yb = stack(xb)
         assert torch.equal(ya, yb)
         yb.backward(gy)
-        torch.testing.assert_close(xb.grad, gxa, rtol=1e-4, atol=1e-6)
+        close_normwise(xb.grad, gxa, "xb.grad")
         for r, p in zip(ref, [p for p in stack.parameters() if p.dim() == 3]):
-            torch.testing.assert_close(p.grad, r, rtol=1e-4, atol=1e-6)
+            close_normwise(p.grad, r, "p.grad")
             p.grad = None
         # encoder folded in: raw features in, same outputs and table gradients
         fused = DWNStack(layers, encoder=enc).train()
@@ -823,7 +824,7 @@ def test_dwn_stack_equals_sequential_layers(dev):
         assert torch.equal(yc, ya)
         yc.backward(gy)
         for r, p in zip(ref, [p for p in fused.parameters() if p.dim() == 3]):
-            torch.testing.assert_close(p.grad, r, rtol=1e-4, atol=1e-6)
+            close_normwise(p.grad, r, "p.grad")
         # GroupSum folded in: logits and gradients of GroupSum(Sequential(...)); 17 nodes in 4 classes is ragged
         from difflut_b200.utils import GroupSum
 
@@ -843,9 +844,9 @@ def test_dwn_stack_equals_sequential_layers(dev):
         logits = with_head(xi)
         torch.testing.assert_close(logits, ref_logits, rtol=1e-5, atol=1e-5)
         logits.backward(glog)
-        torch.testing.assert_close(xi.grad, xh.grad, rtol=1e-4, atol=1e-6)
+        close_normwise(xi.grad, xh.grad, "xi.grad")
         for r, p in zip(ref_h, [p for p in with_head.parameters() if p.dim() == 3]):
-            torch.testing.assert_close(p.grad, r, rtol=1e-4, atol=1e-6)
+            close_normwise(p.grad, r, "p.grad")
             p.grad = None
         assert torch.equal(with_head.eval()(rows), head(seq.eval()(rows)))
         # encoder and GroupSum both folded in: raw features in (packed straight into the interleaved layout), logits out
@@ -854,7 +855,7 @@ def test_dwn_stack_equals_sequential_layers(dev):
         torch.testing.assert_close(lg2, ref_logits, rtol=1e-5, atol=1e-5)
         lg2.backward(glog)
         for r, p in zip(ref_h, [p for p in both.parameters() if p.dim() == 3]):
-            torch.testing.assert_close(p.grad, r, rtol=1e-4, atol=1e-6)
+            close_normwise(p.grad, r, "p.grad")
             p.grad = None
         assert torch.equal(both.eval()(x.to(dev)), head(seq.eval()(rows)))
         seq.train()
@@ -888,7 +889,7 @@ def test_prob_config2_full_size_node_subset_vs_oracle(dev):
     y_ref = O.prob_forward(O.gather_mapping(x, idx), raw_sub).reshape(B, -1)
     torch.testing.assert_close(y.cpu()[:, pick], y_ref, rtol=1e-5, atol=1e-6)
     y_ref.backward(gy[:, pick])
-    torch.testing.assert_close(layer.raw_weights.grad.cpu()[pick], raw_sub.grad, rtol=1e-4, atol=1e-5)
+    close_normwise(layer.raw_weights.grad.cpu()[pick], raw_sub.grad, "layer.raw_weights.grad.cpu()[pick]")
     # fused GroupSum: logits = class sums of the same outputs
     logits = layer.forward_groupsum(x.to(dev), 10, 1.0)
     torch.testing.assert_close(logits.cpu(), O.groupsum(y.detach().cpu(), 10, 1.0), rtol=1e-5, atol=1e-3)
