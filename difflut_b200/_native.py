@@ -66,9 +66,11 @@ SIGNATURES = {
     "dl_bits_flip_t": "plllfl s",
     "dl_grad_rescale": "ppllififp s",
     "dl_p2p_barrier": "pllpl s",
-    "dl_p2p_reduce_adam": "ppppplllfffff s",
+    "dl_p2p_reduce_adam": "pppppplllfffff s",
+    "dl_p2p_exchange_adam": "pppppppllllllfffffl s",
     "dl_popcount_groupsum_t": "ppllll s",
     "dl_ce_t": "pppppllll s",
+    "dl_loss_sum": "ppll s",
     "dl_adam_step": "ppppplfffff s",
     "dl_adam_step_groups": "ppllpppplfffff s",
 }

@@ -80,25 +80,49 @@ bits_swizzle_kernel(const uint32_t* __restrict__ nat, uint32_t* __restrict__ swz
 }
 
 // Thermometer compare-and-pack straight into the chunk-interleaved layout (see bits_swizzle_kernel).
-// A CTA owns one 1024-sample block and 8 features: the block's values go to shared memory feature-major,
-// index s + 4*(s/128) inside a feature row (row pitch 1060), which makes both the fill (lane = 8 features
-// x 4 samples) and the read-out (lane = chunk c + 8r reading sample 128c + 4w + r) bank-conflict free.
-// Warp k then owns feature k: it keeps the 32 values of each word position w in registers and, per
-// threshold, one ballot per w yields word w directly in the interleaved bit order; lane w keeps it and
-// the 32 words of a (feature, threshold) row leave as one coalesced 128-byte store.
-constexpr int SWZ_FEATS = 8, SWZ_PITCH = 1060;
+// A CTA owns one 1024-sample block and FEATS features (one warp per feature): the block's values go to
+// shared memory feature-major, index s + 4*(s/128) inside a feature row (row pitch 1060), which makes both
+// the fill and the read-out (lane = chunk c + 8r reading sample 128c + 4w + r) bank-conflict free.
+// Fill: with 16-byte-aligned rows (VEC4) a thread fetches four features of a sample per load and has all
+// of its eight loads in flight before the first value is stored; otherwise 4-byte loads.  Warp k then keeps
+// the 32 values of each word position w of feature k in registers and, per threshold, one ballot per w
+// yields word w directly in the interleaved bit order; lane w keeps it and the 32 words of a
+// (feature, threshold) row leave as one coalesced 128-byte store.
+constexpr int SWZ_PITCH = 1060;
 
-__global__ void __launch_bounds__(256)
+template <int FEATS, bool VEC4>
+__global__ void __launch_bounds__(FEATS * 32)
 thermo_pack_s_kernel(const float* __restrict__ x, const float* __restrict__ thr, uint32_t* __restrict__ bits_s,
                      int64_t B, int64_t F, int T, int64_t G) {
-    __shared__ float tile[SWZ_FEATS * SWZ_PITCH];
+    __shared__ float tile[FEATS * SWZ_PITCH];
     const int64_t g = blockIdx.x;
-    const int64_t f0 = (int64_t)blockIdx.y * SWZ_FEATS;
+    const int64_t f0 = (int64_t)blockIdx.y * FEATS;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    {
-        const int fl = threadIdx.x & 7;
-        const float nan = __int_as_float(0x7fc00000);  // compares false: padding packs as 0
-        for (int s = threadIdx.x >> 3; s < 1024; s += 32) {
+    const float nan = __int_as_float(0x7fc00000);  // compares false: padding packs as 0
+    if (VEC4) {
+        constexpr int QUADS = FEATS / 4;               // 16-byte pieces per sample
+        constexpr int ROWS = FEATS * 32 / QUADS;       // samples per pass
+        constexpr int PASSES = 1024 / ROWS;
+        const int h = threadIdx.x % QUADS, s0 = threadIdx.x / QUADS;
+        const int64_t f = f0 + 4 * h;
+        float4 v[PASSES];
+#pragma unroll
+        for (int k = 0; k < PASSES; ++k) {
+            const int64_t b = g * 1024 + s0 + k * ROWS;
+            v[k] = (b < B && f < F) ? __ldg(reinterpret_cast<const float4*>(x + b * F + f)) : make_float4(nan, nan, nan, nan);
+        }
+#pragma unroll
+        for (int k = 0; k < PASSES; ++k) {
+            const int s = s0 + k * ROWS;
+            float* dst = tile + (4 * h) * SWZ_PITCH + s + 4 * (s >> 7);
+            dst[0] = v[k].x;
+            dst[SWZ_PITCH] = v[k].y;
+            dst[2 * SWZ_PITCH] = v[k].z;
+            dst[3 * SWZ_PITCH] = v[k].w;
+        }
+    } else {
+        const int fl = threadIdx.x % FEATS;
+        for (int s = threadIdx.x / FEATS; s < 1024; s += 32) {
             const int64_t b = g * 1024 + s, f = f0 + fl;
             tile[fl * SWZ_PITCH + s + 4 * (s >> 7)] = (b < B && f < F) ? __ldg(x + b * F + f) : nan;
         }
@@ -310,10 +334,21 @@ DL_EXPORT int dl_thermo_pack_s(const float* x, const float* thr, uint32_t* bits_
     DL_REQUIRE(x && thr && bits_s && B > 0 && F > 0 && T > 0);
     DL_REQUIRE(Bp >= B && Bp % DL_BATCH_ALIGN == 0);
     const int64_t G = dl_ceil_div(Bp, 1024);
-    const int64_t fy = dl_ceil_div(F, SWZ_FEATS);
-    DL_REQUIRE(fy <= 65535);
-    dim3 grid((unsigned)G, (unsigned)fy);
-    thermo_pack_s_kernel<<<grid, 256, 0, dl_cast(stream)>>>(x, thr, bits_s, B, F, (int)T, G);
+    DL_REQUIRE(G <= 0x7fffffff && dl_ceil_div(F, 4) <= 65535);
+    // 16-byte loads need whole quads of features per row and aligned rows
+    const bool vec4 = F % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0;
+    // small batches: four features per CTA so that the grid still covers the GPU about twice
+    const bool narrow = G * dl_ceil_div(F, 8) < 2 * DL_NUM_SMS;
+    cudaStream_t s = dl_cast(stream);
+    if (narrow) {
+        dim3 grid((unsigned)G, (unsigned)dl_ceil_div(F, 4));
+        if (vec4) thermo_pack_s_kernel<4, true><<<grid, 128, 0, s>>>(x, thr, bits_s, B, F, (int)T, G);
+        else thermo_pack_s_kernel<4, false><<<grid, 128, 0, s>>>(x, thr, bits_s, B, F, (int)T, G);
+    } else {
+        dim3 grid((unsigned)G, (unsigned)dl_ceil_div(F, 8));
+        if (vec4) thermo_pack_s_kernel<8, true><<<grid, 256, 0, s>>>(x, thr, bits_s, B, F, (int)T, G);
+        else thermo_pack_s_kernel<8, false><<<grid, 256, 0, s>>>(x, thr, bits_s, B, F, (int)T, G);
+    }
     return dl_launch_status();
 }
 

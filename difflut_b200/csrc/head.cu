@@ -63,6 +63,13 @@ __global__ void ce_t_kernel(const float* __restrict__ logits_t, const int32_t* _
         for (int c = 0; c < k; ++c) sum += expf(logits_t[c * Bp + b] - mx);
         const float lse = mx + logf(sum);
         const int y = labels[b];
+        if (y < 0 || y >= k) {
+            // no such class (torch's cross_entropy raises for it): the row gets no gradient and a NaN loss,
+            // which shows in the step's loss instead of reading outside the logits
+            for (int c = 0; c < k; ++c) dlogits_t[c * Bp + b] = 0.f;
+            loss_rows[b] = __int_as_float(0x7fc00000);
+            continue;
+        }
         const float inv = 1.0f / sum;
         for (int c = 0; c < k; ++c) {
             const float p = expf(logits_t[c * Bp + b] - mx) * inv;
@@ -179,14 +186,20 @@ DL_EXPORT int dl_groupsum_t(const float* vals_t, float* logits_t, int64_t F, int
 DL_EXPORT int dl_ce_t(const float* logits_t, const int32_t* labels, float* dlogits_t, float* loss_rows,
                       float* loss, int64_t B, int64_t B_global, int64_t k, int64_t Bp,
                       dl_stream_t stream) {
-    DL_REQUIRE(logits_t && labels && dlogits_t && loss_rows && loss);
+    DL_REQUIRE(logits_t && labels && dlogits_t && loss_rows);
     DL_REQUIRE(B > 0 && B_global >= B && k > 0 && Bp >= B);
     const float inv_bg = (float)(1.0 / (double)B_global);
     const int64_t blocks = dl_min64(dl_ceil_div(Bp, 128), (int64_t)DL_NUM_SMS * 8);
     ce_t_kernel<<<(unsigned)blocks, 128, 0, dl_cast(stream)>>>(logits_t, labels, dlogits_t, loss_rows, B,
                                                              inv_bg, (int)k, Bp);
     if (cudaPeekAtLastError() != cudaSuccess) return DL_ERR_LAUNCH;
-    loss_sum_kernel<<<1, 1024, 0, dl_cast(stream)>>>(loss_rows, loss, Bp, inv_bg);
+    if (loss != nullptr) loss_sum_kernel<<<1, 1024, 0, dl_cast(stream)>>>(loss_rows, loss, Bp, inv_bg);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_loss_sum(const float* loss_rows, float* loss, int64_t B_global, int64_t Bp, dl_stream_t stream) {
+    DL_REQUIRE(loss_rows && loss && B_global > 0 && Bp > 0);
+    loss_sum_kernel<<<1, 1024, 0, dl_cast(stream)>>>(loss_rows, loss, Bp, (float)(1.0 / (double)B_global));
     return dl_launch_status();
 }
 

@@ -68,8 +68,10 @@ __global__ void p2p_barrier_kernel(PeerTable flags, int rank, int world, int* __
 
 __global__ void __launch_bounds__(256)
 p2p_reduce_adam_kernel(PeerTable grads, PeerTable params, float* __restrict__ m, float* __restrict__ v,
-                       const double* __restrict__ state, int64_t lo, int64_t hi, int world, float lr, float b1,
-                       float b2, float eps, float gscale) {
+                       const double* __restrict__ state, const int* __restrict__ ctrl, int64_t lo, int64_t hi,
+                       int world, float lr, float b1, float b2, float eps, float gscale) {
+    // a barrier that gave up means some rank's gradients may be missing or still changing: touch nothing
+    if (ctrl != nullptr && ctrl[1] != 0) return;
     const double bc1 = 1.0 - state[0];
     const double bc2 = 1.0 - state[1];
     const float step_size = (float)((double)lr / bc1);
@@ -99,9 +101,119 @@ p2p_reduce_adam_kernel(PeerTable grads, PeerTable params, float* __restrict__ m,
     }
 }
 
-__global__ void adam_state_advance_kernel(double* state, double b1, double b2) {
+__global__ void adam_state_advance_kernel(double* state, const int* __restrict__ ctrl, double b1, double b2) {
+    if (ctrl != nullptr && ctrl[1] != 0) return;
     state[0] *= b1;
     state[1] *= b2;
+}
+
+// ------------------------------------------------------------------------------------------
+// one kernel per exchange: arrive -> reduce + Adam + broadcast -> done
+// ------------------------------------------------------------------------------------------
+//
+// flags of rank q: int32 [DL_P2P_CHANNELS][2][DL_MAX_PEERS]; entry [ch][0][p] is the epoch in which rank p's
+// gradients of channel ch became complete ("arrive"), [ch][1][p] the epoch in which rank p finished reading
+// everybody's gradients and storing its parameter slice everywhere ("done").  Slot p is written by rank p
+// only.  ctrl (local): [0] = status (0 = fine, else 1 + the first peer a bounded wait gave up on; sticky),
+// [1 + 2 ch] = epoch of channel ch, [2 + 2 ch] = number of CTAs of the running launch that have finished.
+//
+// Every CTA waits for the arrive flags itself (they live in this GPU's memory, so polling is local); no CTA
+// waits for another CTA of the grid, so the grid need not be resident at once and may share the GPU with
+// the backward kernels of the layers below.  The CTA that finishes last publishes "done" to the peers,
+// waits for theirs and only then lets the kernel end: whatever follows it in stream order sees every rank's
+// parameter stores, and no rank overwrites its gradients while another still reads them.
+__device__ __forceinline__ bool wait_flag(const int* flag, int epoch, uint64_t timeout_ns) {
+    const uint64_t t0 = global_timer_ns();
+    uint32_t spins = 0;
+    while (load_acquire_sys(flag) < epoch) {
+        // wall-clock limit, checked every 1024 polls, plus an absolute cap on the number of polls
+        if ((++spins & 0x3FFu) == 0 && (global_timer_ns() - t0 > timeout_ns || spins >= 0xFFFFF000u)) return false;
+    }
+    return true;
+}
+
+__global__ void __launch_bounds__(256)
+p2p_exchange_adam_kernel(PeerTable grads, PeerTable params, PeerTable flags, float* __restrict__ m,
+                         float* __restrict__ v, double* __restrict__ state, int* __restrict__ ctrl, int64_t lo,
+                         int64_t hi, int64_t mlo, int ch, int advance, int rank, int world, float lr, float b1,
+                         float b2, float eps, float gscale, uint64_t timeout_ns) {
+    __shared__ int last_cta;
+    int* const my_epoch = ctrl + 1 + 2 * ch;
+    int* const my_done = ctrl + 2 + 2 * ch;
+    if (ctrl[0] != 0) return;  // an earlier wait gave up: the state is invalid until the host has looked at it
+    // read before any CTA can finish: the epoch word is advanced by the LAST CTA to finish
+    const int e = *my_epoch + 1;
+    const int arrive = (ch * 2 + 0) * DL_MAX_PEERS, done = (ch * 2 + 1) * DL_MAX_PEERS;
+    bool ok = true;
+    if (threadIdx.x < world) {
+        const int p = threadIdx.x;
+        if (blockIdx.x == 0) {
+            __threadfence_system();  // the gradients earlier kernels of this GPU wrote are visible to the peers first
+            store_release_sys(static_cast<int*>(flags.ptr[p]) + arrive + rank, e);
+        }
+        if (!wait_flag(static_cast<const int*>(flags.ptr[rank]) + arrive + p, e, timeout_ns)) {
+            atomicCAS(&ctrl[0], 0, 1 + p);
+            ok = false;
+        }
+    }
+    if (!__syncthreads_and(ok)) return;  // parameters, moments and optimiser state stay untouched
+
+    // bias corrections of THIS step: state holds beta^(t-1) until the step's last exchange advances it
+    // (the products are rounded on their own, as the stored state of the next step will be: no fused multiply-add)
+    const double bc1 = 1.0 - __dmul_rn(state[0], (double)b1);
+    const double bc2 = 1.0 - __dmul_rn(state[1], (double)b2);
+    const float step_size = (float)((double)lr / bc1);
+    const float bc2_sqrt = (float)sqrt(bc2);
+    // [lo, hi) in float4 units of the flat vector; this rank's moments of the slice start at mlo
+    for (int64_t i = lo + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < hi;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int p = 0; p < DL_MAX_PEERS; ++p) {
+            if (p < world) {
+                const float4 t = __ldcg(static_cast<const float4*>(grads.ptr[p]) + i);
+                g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
+            }
+        }
+        float4 pp = static_cast<const float4*>(params.ptr[rank])[i];  // every rank's copy holds the same bits
+        float4 mm = reinterpret_cast<float4*>(m)[mlo + i - lo], vv = reinterpret_cast<float4*>(v)[mlo + i - lo];
+        pp.x = adam_update(pp.x, g.x * gscale, mm.x, vv.x, step_size, bc2_sqrt, b1, b2, eps);
+        pp.y = adam_update(pp.y, g.y * gscale, mm.y, vv.y, step_size, bc2_sqrt, b1, b2, eps);
+        pp.z = adam_update(pp.z, g.z * gscale, mm.z, vv.z, step_size, bc2_sqrt, b1, b2, eps);
+        pp.w = adam_update(pp.w, g.w * gscale, mm.w, vv.w, step_size, bc2_sqrt, b1, b2, eps);
+        reinterpret_cast<float4*>(m)[mlo + i - lo] = mm;
+        reinterpret_cast<float4*>(v)[mlo + i - lo] = vv;
+#pragma unroll
+        for (int p = 0; p < DL_MAX_PEERS; ++p)
+            if (p < world) static_cast<float4*>(params.ptr[p])[i] = pp;
+    }
+
+    __syncthreads();  // every thread's parameter stores are ordered before thread 0's fence
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        last_cta = atomicAdd(my_done, 1) == (int)gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!last_cta) return;
+    __threadfence_system();  // the other CTAs' stores, observed through the counter, before the flag below
+    ok = true;
+    if (threadIdx.x < world) {
+        const int p = threadIdx.x;
+        store_release_sys(static_cast<int*>(flags.ptr[p]) + done + rank, e);
+        if (!wait_flag(static_cast<const int*>(flags.ptr[rank]) + done + p, e, timeout_ns)) {
+            atomicCAS(&ctrl[0], 0, 1 + p);
+            ok = false;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        *my_done = 0;
+        *my_epoch = e;
+        if (advance) {
+            state[0] *= (double)b1;
+            state[1] *= (double)b2;
+        }
+    }
 }
 
 int fill_table(PeerTable& t, const void* const* host_ptrs, int64_t world) {
@@ -142,8 +254,9 @@ DL_EXPORT int dl_p2p_barrier(const void* const* peer_flags_host, int64_t rank, i
 }
 
 DL_EXPORT int dl_p2p_reduce_adam(const void* const* peer_grads_host, const void* const* peer_params_host, float* m,
-                                 float* v, double* state, int64_t count, int64_t rank, int64_t world, float lr,
-                                 float beta1, float beta2, float eps, float gscale, dl_stream_t stream) {
+                                 float* v, double* state, const int32_t* ctrl, int64_t count, int64_t rank,
+                                 int64_t world, float lr, float beta1, float beta2, float eps, float gscale,
+                                 dl_stream_t stream) {
     DL_REQUIRE(peer_grads_host && peer_params_host && m && v && state && count > 0);
     DL_REQUIRE(world >= 1 && world <= DL_MAX_PEERS && rank >= 0 && rank < world);
     DL_REQUIRE(count % (4 * world) == 0);  // equal slices of whole float4s: the caller pads the flat vector
@@ -162,10 +275,45 @@ DL_EXPORT int dl_p2p_reduce_adam(const void* const* peer_grads_host, const void*
     void* t = params.ptr[0]; params.ptr[0] = params.ptr[rank]; params.ptr[rank] = t;
     const int64_t quads = count / 4, per = quads / world;
     const int64_t lo = rank * per, hi = lo + per;
-    adam_state_advance_kernel<<<1, 1, 0, dl_cast(stream)>>>(state, (double)beta1, (double)beta2);
+    adam_state_advance_kernel<<<1, 1, 0, dl_cast(stream)>>>(state, ctrl, (double)beta1, (double)beta2);
     if (cudaPeekAtLastError() != cudaSuccess) return DL_ERR_LAUNCH;
     const int64_t blocks = dl_min64(dl_ceil_div(per, 256), (int64_t)DL_NUM_SMS * 4);
-    p2p_reduce_adam_kernel<<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(grads, params, m, v, state, lo, hi,
+    p2p_reduce_adam_kernel<<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(grads, params, m, v, state, ctrl, lo, hi,
                                                                        (int)world, lr, beta1, beta2, eps, gscale);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_p2p_exchange_adam(const void* const* peer_grads_host, const void* const* peer_params_host,
+                                   const void* const* peer_flags_host, float* m, float* v, double* state,
+                                   int32_t* ctrl, int64_t offset, int64_t count, int64_t channel, int64_t advance_state,
+                                   int64_t rank, int64_t world, float lr, float beta1, float beta2, float eps,
+                                   float gscale, int64_t timeout_ms, dl_stream_t stream) {
+    DL_REQUIRE(peer_grads_host && peer_params_host && peer_flags_host && m && v && state && ctrl);
+    DL_REQUIRE(world >= 1 && world <= DL_MAX_PEERS && rank >= 0 && rank < world);
+    DL_REQUIRE(channel >= 0 && channel < DL_P2P_CHANNELS && timeout_ms > 0 && timeout_ms <= 60000);
+    // the slice and every rank's share of it are whole float4s: the caller pads the flat vector
+    DL_REQUIRE(count > 0 && offset >= 0 && count % (4 * world) == 0 && offset % (4 * world) == 0);
+    PeerTable grads, params, flags;
+    int rc = fill_table(grads, peer_grads_host, world);
+    if (rc != DL_OK) return rc;
+    rc = fill_table(params, peer_params_host, world);
+    if (rc != DL_OK) return rc;
+    rc = fill_table(flags, peer_flags_host, world);
+    if (rc != DL_OK) return rc;
+    for (int64_t p = 0; p < world; ++p) {
+        DL_REQUIRE_ALIGNED(grads.ptr[p], 16);
+        DL_REQUIRE_ALIGNED(params.ptr[p], 16);
+        DL_REQUIRE_ALIGNED(flags.ptr[p], 4);
+    }
+    DL_REQUIRE_ALIGNED(m, 16);
+    DL_REQUIRE_ALIGNED(v, 16);
+    const int64_t per = count / 4 / world;           // float4s this rank owns of the slice
+    const int64_t lo = offset / 4 + rank * per;
+    const int64_t mlo = offset / 4 / world;          // the moments hold only this rank's share of every slice
+    // few CTAs: the kernel shares the GPU with the backward kernels of the layers below
+    const int64_t blocks = dl_min64(dl_ceil_div(per, 256 * 2), (int64_t)DL_NUM_SMS);
+    p2p_exchange_adam_kernel<<<(unsigned)(blocks < 1 ? 1 : blocks), 256, 0, dl_cast(stream)>>>(
+        grads, params, flags, m, v, state, ctrl, lo, lo + per, mlo, (int)channel, advance_state != 0, (int)rank,
+        (int)world, lr, beta1, beta2, eps, gscale, (uint64_t)timeout_ms * 1000000ull);
     return dl_launch_status();
 }

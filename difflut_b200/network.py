@@ -35,7 +35,7 @@ class DWNNetwork:
     def __init__(self, encoder: ThermometerEncoder, layers: Sequence[RandomLayer], groupsum: GroupSum,
                  lr: float = 1e-2, betas=(0.9, 0.999), eps: float = 1e-8,
                  process_group: Optional["dist.ProcessGroup"] = None, distributed: Optional[bool] = None,
-                 fused_backward: bool = True, peer_optimizer: Optional[bool] = None):
+                 fused_backward: bool = True, peer_optimizer: Optional[bool] = None, peer_status_every: int = 0):
         if not encoder.is_fitted:
             raise RuntimeError("DWNNetwork needs a fitted encoder")
         if groupsum.use_randperm:
@@ -70,6 +70,9 @@ class DWNNetwork:
                               and dist.get_backend(process_group) == "nccl"
                               and os.environ.get("DIFFLUT_PEER_OPTIMIZER", "1") != "0")
         self.peer_optimizer = bool(peer_optimizer) and self.distributed
+        # > 0: train_step reads the peer status word every that many steps (a host synchronisation) and raises
+        # when a bounded wait has given up; 0 leaves the polling to the caller (peer_status())
+        self.peer_status_every = int(peer_status_every)
 
         thr = encoder.thresholds.reshape(-1, encoder.num_bits)
         self.thr = thr.to(device=self.device, dtype=torch.float32).contiguous()
@@ -84,15 +87,18 @@ class DWNNetwork:
         self.L = [2 ** n for n in self.n]
 
         # one flat buffer for all tables / gradients / Adam moments; the layers' parameters view it
-        counts = [N * L for N, L in zip(self.N, self.L)]
-        self.offsets = [0]
-        for c in counts:
-            self.offsets.append(self.offsets[-1] + c)
+        self.counts = [N * L for N, L in zip(self.N, self.L)]
+        # with the peer optimiser every layer's slice splits into `world` equal runs of whole 16-byte pieces
+        unit = 4 * self.world if self.peer_optimizer else 1
+        self.offsets, self.padded = [0], []
+        for c in self.counts:
+            self.padded.append((c + unit - 1) // unit * unit)
+            self.offsets.append(self.offsets[-1] + self.padded[-1])
         total = self.offsets[-1]
-        if self.peer_optimizer:  # equal slices of whole 16-byte pieces per rank
-            unit = 4 * self.world
-            total = (total + unit - 1) // unit * unit
         moments = total // self.world if self.peer_optimizer else total
+        # one exchange kernel per layer (its own flag channel) unless there are more layers than channels
+        self.peer_fused = os.environ.get("DIFFLUT_PEER_FUSED", "1") != "0"
+        self.peer_per_layer = len(self.layers) <= 8
         self.flat = torch.zeros(total, device=self.device, dtype=torch.float32)
         self.flat_grad = torch.zeros(total, device=self.device, dtype=torch.float32)
         self.exp_avg = torch.zeros(moments, device=self.device, dtype=torch.float32)
@@ -100,7 +106,7 @@ class DWNNetwork:
         self.adam_state = torch.ones(2, device=self.device, dtype=torch.float64)
         self.tables, self.grads = [], []
         for li, l in enumerate(self.layers):
-            sl = slice(self.offsets[li], self.offsets[li + 1])
+            sl = slice(self.offsets[li], self.offsets[li] + self.counts[li])
             view = self.flat[sl].view(self.N[li], 1, self.L[li])
             view.copy_(l.luts.data)
             l.luts.data = view
@@ -111,8 +117,11 @@ class DWNNetwork:
         if self.peer_optimizer:
             from .distributed import PeerWindow
 
-            self.peer_flags = torch.zeros(8, device=self.device, dtype=torch.int32)
-            self.peer_ctrl = torch.zeros(2, device=self.device, dtype=torch.int32)
+            # flag words per rank: an "arrive" and a "done" epoch per channel and peer (the separate barrier
+            # kernel of the unfused path uses the first 8); ctrl: status + (epoch, CTA counter) per channel
+            self.peer_flags = torch.zeros(8 * 2 * 8, device=self.device, dtype=torch.int32)
+            self.peer_ctrl = torch.zeros(1 + 2 * 8, device=self.device, dtype=torch.int32)
+            self.peer_ctrl_barrier = torch.zeros(2, device=self.device, dtype=torch.int32)
             torch.cuda.synchronize(self.device)
             self.peer_timeout_ms = 5000
             try:
@@ -148,7 +157,9 @@ class DWNNetwork:
         self._B = None
         self._train_B = None
         self._graph = None
+        self._graph_B_global = None
         self._side = None
+        self._comm = None
         self.step_count = 0
         self.infer_chunk = 1 << 18  # hard inference walks large batches in pieces of this many samples
 
@@ -202,11 +213,17 @@ class DWNNetwork:
                          self.masks[li] if need_masks else None, self.N[li], self.n[li], self.alpha[li], self.beta[li])
 
     def _forward(self, x: torch.Tensor, B: int) -> None:
-        Bp = self.Bp
+        self._encode(x, B)
+        self._forward_layers()
+
+    def _encode(self, x: torch.Tensor, B: int) -> None:
         if self.swizzle:
-            _native.call("dl_thermo_pack_s", x, self.thr, self.bits[0], B, self.F, self.T, Bp)
+            _native.call("dl_thermo_pack_s", x, self.thr, self.bits[0], B, self.F, self.T, self.Bp)
         else:
-            _native.call("dl_thermo_pack_t", x, self.thr, self.bits[0], B, self.F, self.T, Bp)
+            _native.call("dl_thermo_pack_t", x, self.thr, self.bits[0], B, self.F, self.T, self.Bp)
+
+    def _forward_layers(self) -> None:
+        Bp = self.Bp
         last = len(self.layers) - 1
         for li in range(last):
             # bit-sliced: indifferent to the sample order inside a row, only the row length matters
@@ -261,73 +278,133 @@ class DWNNetwork:
                              self.addr[li] if li > 0 else None, grad_out, 0, self.N[li], self.n[li], Bp)
             if self.distributed and not self.peer_optimizer:
                 # sum of per-rank gradients of the GLOBAL-mean loss (dl_ce_t divides by B_global)
-                grad = self.flat_grad[self.offsets[li]:self.offsets[li + 1]]
+                grad = self.flat_grad[self.offsets[li]:self.offsets[li] + self.counts[li]]
                 self._pending.append(allreduce_sum_(grad, self.group, async_op=True))
+            elif self.peer_optimizer and self.peer_fused and self.peer_per_layer:
+                # this layer's gradient is complete on this rank: its exchange (all ranks arrive -> reduce + Adam
+                # on the owner -> store everywhere -> all ranks done) runs on the communication stream under
+                # the backward of the layers below; the first layer's exchange also advances the Adam state
+                main = torch.cuda.current_stream()
+                self._comm_events[li].record(main)
+                self._comm.wait_event(self._comm_events[li])
+                with torch.cuda.stream(self._comm):
+                    self._exchange(self.offsets[li], self.padded[li], channel=li, advance=(li == 0))
+
+    def _exchange(self, offset: int, count: int, channel: int, advance: bool) -> None:
+        _native.call("dl_p2p_exchange_adam", self.win_grads.ptrs, self.win_params.ptrs, self.win_flags.ptrs,
+                     self.exp_avg, self.exp_avg_sq, self.adam_state, self.peer_ctrl, offset, count, channel,
+                     1 if advance else 0, self.rank, self.world, self.lr, self.betas[0], self.betas[1], self.eps,
+                     1.0, self.peer_timeout_ms)
 
     def _step_body(self, B: int, B_global: int) -> None:
-        # the EFD transform is only needed by the backward: it runs on a side stream next to the forward
+        """One step as a small dependency graph over three streams (captured as such into the CUDA graph):
+        the table preparation (hard masks for the forward, then the EFD transform for the backward) and
+        the loss sum run on a side stream next to the encoder / forward / backward chain, and with the peer
+        optimiser each layer's gradient exchange runs on a communication stream under the backward of the
+        layers below."""
         main = torch.cuda.current_stream()
         if self._side is None:
             self._side = torch.cuda.Stream(device=self.device)
-            self._fork, self._join = torch.cuda.Event(), torch.cuda.Event()
+            self._comm = torch.cuda.Stream(device=self.device)
+            self._fork, self._masks_ready, self._efd_ready = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
+            self._ce_done, self._side_done, self._comm_done = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
+            self._comm_events = [torch.cuda.Event() for _ in self.layers]
         self._fork.record(main)
         self._side.wait_event(self._fork)
         with torch.cuda.stream(self._side):
+            self._prepare_tables(need_efd=False, need_masks=True)
+            self._masks_ready.record(self._side)
             self._prepare_tables(need_efd=True, need_masks=False)
-            self._join.record(self._side)
-        self._prepare_tables(need_efd=False, need_masks=True)
-        self._forward(self.x_static, B)
-        _native.call("dl_ce_t", self.logits_t, self.y_static, self.dlogits_t, self.loss_rows, self.loss,
+            self._efd_ready.record(self._side)
+        self._encode(self.x_static, B)
+        main.wait_event(self._masks_ready)
+        self._forward_layers()
+        _native.call("dl_ce_t", self.logits_t, self.y_static, self.dlogits_t, self.loss_rows, None,
                      B, B_global, self.k, self.Bp)
-        main.wait_event(self._join)
+        self._ce_done.record(main)
+        with torch.cuda.stream(self._side):
+            self._side.wait_event(self._ce_done)
+            _native.call("dl_loss_sum", self.loss_rows, self.loss, B_global, self.Bp)
+            self._side_done.record(self._side)
+        main.wait_event(self._efd_ready)
+        fused_exchange = self.peer_optimizer and self.peer_fused and self.peer_per_layer and self.fused_backward
+        if fused_exchange:
+            self._comm.wait_event(self._fork)
         self._backward()
         count = self.flat.numel()
         if self.peer_optimizer:
-            # every rank's gradients are complete -> each rank reduces and updates its slice and stores the
-            # new parameters everywhere -> every rank's stores have landed
-            barrier = (self.win_flags.ptrs, self.rank, self.world, self.peer_ctrl, self.peer_timeout_ms)
-            _native.call("dl_p2p_barrier", *barrier)
-            _native.call("dl_p2p_reduce_adam", self.win_grads.ptrs, self.win_params.ptrs, self.exp_avg,
-                         self.exp_avg_sq, self.adam_state, count, self.rank, self.world, self.lr, self.betas[0],
-                         self.betas[1], self.eps, 1.0)
-            _native.call("dl_p2p_barrier", *barrier)
-            return
-        if self.distributed:
-            if self.fused_backward:
-                for work in self._pending:  # the per-layer all-reduces started during the backward
-                    if work is not None:
-                        work.wait()
-                self._pending = []
+            if fused_exchange:
+                self._comm_done.record(self._comm)
+                main.wait_event(self._comm_done)
+            elif self.peer_fused:
+                self._exchange(0, count, channel=0, advance=True)
             else:
-                allreduce_sum_(self.flat_grad, self.group)
-        _native.call("dl_adam_step", self.flat, self.flat_grad, self.exp_avg, self.exp_avg_sq, self.adam_state,
-                     count, self.lr, self.betas[0], self.betas[1], self.eps, 1.0)
+                # three-kernel form: every rank's gradients are complete -> each rank reduces and updates its
+                # slice and stores the new parameters everywhere -> every rank's stores have landed
+                barrier = (self.win_flags.ptrs, self.rank, self.world, self.peer_ctrl_barrier, self.peer_timeout_ms)
+                _native.call("dl_p2p_barrier", *barrier)
+                _native.call("dl_p2p_reduce_adam", self.win_grads.ptrs, self.win_params.ptrs, self.exp_avg,
+                             self.exp_avg_sq, self.adam_state, self.peer_ctrl_barrier, count, self.rank, self.world,
+                             self.lr, self.betas[0], self.betas[1], self.eps, 1.0)
+                _native.call("dl_p2p_barrier", *barrier)
+        else:
+            if self.distributed:
+                if self.fused_backward:
+                    for work in self._pending:  # the per-layer all-reduces started during the backward
+                        if work is not None:
+                            work.wait()
+                    self._pending = []
+                else:
+                    allreduce_sum_(self.flat_grad, self.group)
+            _native.call("dl_adam_step", self.flat, self.flat_grad, self.exp_avg, self.exp_avg_sq, self.adam_state,
+                         count, self.lr, self.betas[0], self.betas[1], self.eps, 1.0)
+        main.wait_event(self._side_done)
 
     # ------------------------------------------------------------------ public API
     def peer_status(self) -> int:
         """0, or 1 + the rank a bounded peer wait gave up on (synchronises; call it between steps)."""
-        return int(self.peer_ctrl[1].item()) if self.peer_optimizer else 0
+        if not self.peer_optimizer:
+            return 0
+        return int(self.peer_ctrl[0].item()) if self.peer_fused else int(self.peer_ctrl_barrier[1].item())
 
     def kernel_launches_per_step(self) -> int:
         L = len(self.layers)
         backward = L if self.fused_backward else (L + (L - 1))
         prepare = 2 * (1 if self.uniform else L)
-        update = 4 if self.peer_optimizer else 2  # barrier, state advance, reduce+Adam+broadcast, barrier
+        if not self.peer_optimizer:
+            update = 2  # state advance, Adam
+        elif self.peer_fused:
+            update = L if self.peer_per_layer else 1  # one exchange kernel per layer
+        else:
+            update = 4  # barrier, state advance, reduce+Adam+broadcast, barrier
         return prepare + 1 + (L - 1) + 2 + 2 + backward + update
 
-    def train_step(self, x: torch.Tensor, labels: torch.Tensor, use_graph: bool = False) -> torch.Tensor:
-        """One optimisation step on this rank's shard (x (B, F) fp32, labels (B,) integer).
+    def train_step(self, x: torch.Tensor, labels: torch.Tensor, use_graph: bool = False,
+                   global_batch: Optional[int] = None) -> torch.Tensor:
+        """One optimisation step on this rank's shard (x (B, F) fp32, labels (B,) integer in [0, k)).
 
         Returns the 1-element device tensor holding this rank's share of the global mean loss
         (sum over ranks = global mean).  With `use_graph` the step is captured once per batch
-        size into a CUDA graph and replayed.
+        size into a CUDA graph and replayed.  `global_batch` is the number of rows all ranks hold
+        together (the denominator of the mean loss); it defaults to B * world, which is only right
+        when every rank holds the same number of rows: pass it when the shards are uneven.
+
+        With the peer optimiser a non-zero `peer_status()` means a rank did not arrive within the
+        limit; the tables are invalid from the step in which that happened (later steps change
+        nothing), so poll it at every host synchronisation point of the training loop.
         """
         B = int(x.shape[0])
+        if not labels.is_cuda and labels.numel() > 0 and (int(labels.min()) < 0 or int(labels.max()) >= self.k):
+            raise ValueError(f"labels must lie in [0, {self.k})")
         with torch.cuda.device(self.device):
             self._ensure_buffers(B)
             self.x_static.copy_(x, non_blocking=True)
             self.y_static.copy_(labels, non_blocking=True)
-            B_global = B * self.world
+            B_global = B * self.world if global_batch is None else int(global_batch)
+            if B_global < B:
+                raise ValueError("global_batch is smaller than this rank's batch")
+            if self._graph is not None and self._graph_B_global != B_global:
+                self._graph = None  # the denominator is baked into the captured launches
             if not use_graph:
                 self._step_body(B, B_global)
             else:
@@ -335,6 +412,11 @@ class DWNNetwork:
                     self._capture(B, B_global)
                 self._graph.replay()
         self.step_count += 1
+        if self.peer_optimizer and self.peer_status_every > 0 and self.step_count % self.peer_status_every == 0:
+            status = self.peer_status()
+            if status != 0:
+                raise RuntimeError(f"peer exchange: rank {status - 1} did not arrive within {self.peer_timeout_ms} ms; "
+                                   "the tables are invalid since the last successful poll")
         return self.loss
 
     def _capture(self, B: int, B_global: int) -> None:
@@ -352,6 +434,7 @@ class DWNNetwork:
         with torch.cuda.graph(graph):
             self._step_body(B, B_global)
         self._graph = graph
+        self._graph_B_global = B_global
 
     @torch.no_grad()
     def logits(self, x: torch.Tensor) -> torch.Tensor:

@@ -376,21 +376,50 @@ int dl_grad_rescale(const float* g, float* out, int64_t rows, int64_t cols, int 
  *                        sized moments m, v (count/world floats) and stores the new parameters
  *                        into every rank's parameter buffer.  count % (4*world) == 0.  Call
  *                        dl_p2p_barrier before it (gradients complete everywhere) and after it
- *                        (parameters complete everywhere).                                        */
+ *                        (parameters complete everywhere).  ctrl = the barriers' ctrl (or NULL): when
+ *                        its status word is non-zero the call changes nothing.                     */
 #define DL_MAX_PEERS 8
+#define DL_P2P_CHANNELS 8
+/*   dl_p2p_exchange_adam the three steps above as ONE kernel, for a slice [offset, offset + count) of the
+ *                        flat vector (one layer's tables), so that a layer's exchange can start on a side
+ *                        stream as soon as its gradient is complete and travel under the backward of the
+ *                        layers below.  flags buffers are int32[DL_P2P_CHANNELS * 2 * DL_MAX_PEERS] (an
+ *                        "arrive" and a "done" epoch per channel and peer), ctrl is a local
+ *                        int32[1 + 2 * DL_P2P_CHANNELS] {status, then epoch and a CTA counter per channel};
+ *                        both zeroed once.  Calls that may overlap in time use different channels.  Rank r
+ *                        owns the r-th of `world` equal parts of the slice; its moments m, v hold only its
+ *                        parts, the part of this slice at float offset/world (offset and count are
+ *                        multiples of 4 * world).  The kernel waits (bounded by timeout_ms) until every
+ *                        rank has arrived, reduces, updates and stores its part into every rank's parameter
+ *                        buffer, and returns once every rank has done so.  The bias corrections use
+ *                        state * beta (this step's powers); with advance_state != 0 the call multiplies
+ *                        state by the betas at its end: pass it on the step's last exchange only.  If a
+ *                        wait gives up, status becomes 1 + the missing peer and stays so: later calls
+ *                        return without touching anything until the host has reset ctrl[0].  A CTA decides
+ *                        for itself whether everybody arrived, so a peer that arrives exactly at the limit
+ *                        can leave a slice partly updated: a non-zero status invalidates the parameters.  */
+int dl_p2p_exchange_adam(const void* const* peer_grads_host, const void* const* peer_params_host,
+                         const void* const* peer_flags_host, float* m, float* v, double* state, int32_t* ctrl,
+                         int64_t offset, int64_t count, int64_t channel, int64_t advance_state, int64_t rank,
+                         int64_t world, float lr, float beta1, float beta2, float eps, float gscale,
+                         int64_t timeout_ms, dl_stream_t stream);
 int dl_p2p_enable_peer(int64_t peer_device);
 int dl_p2p_barrier(const void* const* peer_flags_host, int64_t rank, int64_t world, int32_t* ctrl,
                    int64_t timeout_ms, dl_stream_t stream);
 int dl_p2p_reduce_adam(const void* const* peer_grads_host, const void* const* peer_params_host, float* m,
-                       float* v, double* state, int64_t count, int64_t rank, int64_t world, float lr,
-                       float beta1, float beta2, float eps, float gscale, dl_stream_t stream);
+                       float* v, double* state, const int32_t* ctrl, int64_t count, int64_t rank, int64_t world,
+                       float lr, float beta1, float beta2, float eps, float gscale, dl_stream_t stream);
 
 /* Mean cross-entropy over `B_global` samples of which this call holds B (user code in the
  * reference: nn.CrossEntropyLoss, e.g. tests/test_layers/test_convolutional_learning.py:85-111).
  * logits_t [k][Bp]; labels (B) int32; writes dlogits_t [k][Bp] = (softmax - onehot)/B_global
- * (0 in padding), loss_rows [Bp] per-sample losses and loss[0] = sum(loss_rows)/B_global. */
+ * (0 in padding), loss_rows [Bp] per-sample losses and loss[0] = sum(loss_rows)/B_global.
+ * loss == NULL skips the sum: dl_loss_sum then forms it from loss_rows, e.g. on another stream, off
+ * the path to the backward kernels.  A label outside [0, k) gives that row a zero gradient and a NaN
+ * loss (torch's cross_entropy raises for such a label; nothing is read outside the logits here). */
 int dl_ce_t(const float* logits_t, const int32_t* labels, float* dlogits_t, float* loss_rows,
             float* loss, int64_t B, int64_t B_global, int64_t k, int64_t Bp, dl_stream_t stream);
+int dl_loss_sum(const float* loss_rows, float* loss, int64_t B_global, int64_t Bp, dl_stream_t stream);
 
 /* torch.optim.Adam step (no weight decay / amsgrad) over a flat fp32 tensor.  `state` is a
  * device array of 2 doubles {beta1^t, beta2^t}, initialised to {1, 1}; every call multiplies

@@ -2,8 +2,9 @@
 golden fixtures produced by the reference and against the CPU oracle on seeded inputs.
 
 Bars: bit-exact for bits, addresses (observable through exact table values), index maps and hard
-outputs; rtol 1e-5 (+ small atol for near-zero sums) for fp32 outputs; rtol 1e-4 where fp32
-summation order differs over long reductions (gradients summed over the batch).
+outputs; rtol 1e-5 (+ small atol for near-zero sums) for fp32 outputs; gradients that are long sums
+over the batch (different summation order than the reference) are held to 1e-5 norm-wise:
+max|got - ref| <= 1e-5 * max|ref|, with the measured ratio recorded (tests/parity_util.py).
 """
 
 import warnings
@@ -624,9 +625,15 @@ def test_error_codes(dev):
         _native.call("dl_f32_rows_to_t", torch.zeros(4), a, 1, 4, 128)
 
 
-def test_fused_backward_equals_separate_kernels_multi_group(dev):
-    """B = 2500 (three 1024-sample groups, ragged tail): the fused per-layer backward and the separate
-    table / input gradient kernels give the same table gradients; both match the oracle."""
+@pytest.mark.parametrize("B,sizes", [
+    (2500, [96, 50, 33]),        # ragged tail: general fused kernel; 33 is not a multiple of k
+    (2048, [96, 50, 33]),        # whole blocks: pipelined kernel, nodes with 3 and 4 readers (extra-reader path)
+    (4096, [6200, 1500, 333]),   # pipelined kernel, first layer with two blocks per item, nodes with 0-2 readers
+])
+def test_fused_backward_equals_separate_kernels_multi_group(dev, B, sizes):
+    """Several 1024-sample groups: the fused per-layer backward (general kernel for a ragged batch, the
+    software-pipelined one for whole blocks) and the separate table / input gradient kernels give the same
+    table gradients; both match the oracle."""
     from difflut_b200.encoder import ThermometerEncoder
     from difflut_b200.layers import RandomLayer
     from difflut_b200.network import DWNNetwork
@@ -634,8 +641,7 @@ def test_fused_backward_equals_separate_kernels_multi_group(dev):
     from difflut_b200.utils import GroupSum
 
     gen = torch.Generator().manual_seed(3)
-    B, F, Tb, k, tau = 2500, 16, 4, 5, 2.0
-    sizes = [96, 50, 33]  # 33 is not a multiple of k: the last class is short
+    F, Tb, k, tau = 16, 4, 5, 2.0
     x = torch.rand(B, F, generator=gen)
     labels = torch.randint(0, k, (B,), generator=gen)
     grads = {}
@@ -653,15 +659,15 @@ def test_fused_backward_equals_separate_kernels_multi_group(dev):
         net.train_step(x.to(dev), labels.to(dev))
         grads[fused] = [gr.cpu().clone() for gr in net.grads]
         maps = [l._mapping_indices.cpu() for l in layers]
-    for a, b in zip(grads[True], grads[False]):
-        torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-7)
+    for li, (a, b) in enumerate(zip(grads[True], grads[False])):
+        close_normwise(a, b, f"fused vs separate kernels, table gradient of layer {li + 1}", tol=2e-6)
     bits = O.thermometer_encode(x, O.thermometer_thresholds(x, Tb))
     logits, acts = O.dwn_network_forward(bits, maps, tabs0, k, tau)
     lg = logits.clone().requires_grad_(True)
     torch.nn.functional.cross_entropy(lg, labels).backward()
     ref = O.dwn_network_backward(acts, maps, tabs0, lg.grad, k, tau, 0.5 * 0.75 ** 5, 0.25 / 0.75)
-    for a, r in zip(grads[True], ref):
-        close_normwise(a, r, "a")
+    for li, (a, r) in enumerate(zip(grads[True], ref)):
+        close_normwise(a, r, f"fused backward vs oracle, table gradient of layer {li + 1}")
 
 
 @pytest.mark.parametrize("B", [128, 1024, 2500])
@@ -699,6 +705,32 @@ def test_bits_swizzle_layout(dev, B):
     _native.call("dl_bits_swizzle_t", nat2, via, Fx * Tb, Bp)
     direct = torch.full((Fx * Tb, Ws), -1, dtype=torch.int32, device=dev)
     _native.call("dl_thermo_pack_s", x.to(dev), thr.to(dev), direct, B, Fx, Tb, Bp)
+    assert torch.equal(direct, via)
+
+
+@pytest.mark.parametrize("B,F", [(1024, 12), (3000, 784), (8192, 296), (8192, 298), (1000, 7)])
+def test_thermo_pack_interleaved_all_kernel_variants(dev, B, F):
+    """dl_thermo_pack_s picks 16-byte or 4-byte loads (whole quads of features per row or not) and 8 or 4
+    features per CTA (large or small grids): every variant = natural pack followed by the layout conversion,
+    and the natural pack equals the oracle's bits."""
+    from difflut_b200 import _native
+
+    gen = torch.Generator().manual_seed(B + F)
+    Tb = 3
+    x = torch.rand(B, F, generator=gen)
+    thr = torch.sort(torch.rand(F, Tb, generator=gen), dim=1).values.contiguous()
+    x[0, :] = thr[:, 0]  # equality with a threshold encodes as 0 (strict comparison)
+    Bp = _native.padded_batch(B)
+    Ws = int(_native.lib().dl_swizzled_words(Bp))
+    nat = torch.empty(F * Tb, Bp // 32, dtype=torch.int32, device=dev)
+    _native.call("dl_thermo_pack_t", x.to(dev), thr.to(dev), nat, B, F, Tb, Bp)
+    ref = O.pack_bits_feature_major(O.thermometer_encode(x, thr))
+    got = nat.cpu().numpy().view(np.uint32)
+    assert np.array_equal(got[:, : ref.shape[1]], ref) and not got[:, ref.shape[1]:].any()
+    via = torch.empty(F * Tb, Ws, dtype=torch.int32, device=dev)
+    _native.call("dl_bits_swizzle_t", nat, via, F * Tb, Bp)
+    direct = torch.full((F * Tb, Ws), -1, dtype=torch.int32, device=dev)
+    _native.call("dl_thermo_pack_s", x.to(dev), thr.to(dev), direct, B, F, Tb, Bp)
     assert torch.equal(direct, via)
 
 

@@ -1,7 +1,12 @@
-"""Two-GPU test of the peer-memory optimiser step (gradient sum + Adam + parameter broadcast in one
-kernel): two ranks train a small DWN classifier for three steps with it and, separately, with the NCCL
-all-reduce path; tables must agree between the ranks bit for bit and between the two paths to fp32
-rounding.  Needs two GPUs (skipped otherwise); the ranks are child processes."""
+"""The peer-memory optimiser step (gradient sum + Adam + parameter broadcast in one kernel per layer).
+
+Two GPUs (skipped otherwise; the ranks are child processes): two ranks train a small DWN classifier for
+three steps with it and, separately, with the NCCL all-reduce path and as ONE process on the whole batch;
+tables must agree between the ranks bit for bit, and with the other two runs to fp32 rounding.
+
+One GPU: the exchange kernel with a world of one rank must reproduce dl_adam_step bit for bit (slices,
+channels, state advance), and with a peer whose flags nothing writes it must give up after the limit,
+report the peer and leave parameters, moments and optimiser state untouched."""
 
 import os
 import subprocess
@@ -51,6 +56,21 @@ for peer in (True, False):
     torch.cuda.synchronize()
     assert net.peer_status() == 0
     results[peer] = torch.cat([t.reshape(-1) for t in net.tables]).clone()
+# the same three steps in one process on the whole batch (no exchange at all)
+enc = ThermometerEncoder(num_bits=Tb).fit(x)
+layers, I = [], F * Tb
+for li, N in enumerate(sizes):
+    l = RandomLayer(I, N, DWNNode, NodeConfig(input_dim=6, output_dim=1), seed=li).to(dev)
+    with torch.no_grad():
+        l.luts.copy_(tabs[li].to(dev))
+    layers.append(l)
+    I = N
+solo = DWNNetwork(enc, layers, GroupSum(k=k, tau=2.0, use_randperm=False), lr=1e-2, distributed=False)
+for step in range(3):
+    solo.train_step(x.to(dev), y.to(dev))
+torch.cuda.synchronize()
+single = torch.cat([t.reshape(-1) for t in solo.tables]).clone()
+torch.testing.assert_close(results[True], single, rtol=1e-5, atol=2e-6)
 mine = results[True]
 both = [torch.empty_like(mine) for _ in range(world)]
 dist.all_gather(both, mine)
@@ -107,3 +127,101 @@ def test_barrier_wait_runs_out_and_reports():
         _native.call("dl_p2p_barrier", ctypes.addressof(solo), 0, 1, ctrl, 200)
     assert ctrl.tolist() == [1, 0]
     assert float(torch.ones(4, device=dev).sum()) == 4.0
+
+
+def _exchange_args(dev, count, world):
+    import ctypes
+
+    g = torch.Generator().manual_seed(11)
+    grads = torch.randn(count, generator=g).to(dev) * 1e-3
+    params = torch.randn(count, generator=g).to(dev)
+    flags = torch.zeros(8 * 2 * 8, dtype=torch.int32, device=dev)
+    absent = torch.zeros(8 * 2 * 8, dtype=torch.int32, device=dev)  # stands in for a rank that never runs
+    m = torch.zeros(count // world, device=dev)
+    v = torch.zeros(count // world, device=dev)
+    state = torch.ones(2, dtype=torch.float64, device=dev)
+    ctrl = torch.zeros(17, dtype=torch.int32, device=dev)
+
+    def table(*tensors):
+        arr = (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+        return arr
+
+    return grads, params, flags, absent, m, v, state, ctrl, table
+
+
+def test_exchange_kernel_with_one_rank_equals_adam_step():
+    import ctypes
+
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from difflut_b200 import _native
+
+    dev = torch.device("cuda", 0)
+    count = 3 * 4096 + 512  # two "layers": slices of 4096*2 and the rest
+    grads, params, flags, _, m, v, state, ctrl, table = _exchange_args(dev, count, 1)
+    ref_p, ref_m, ref_v = params.clone(), m.clone(), v.clone()
+    ref_state = state.clone()
+    tg, tp, tf = table(grads), table(params), table(flags)
+    split = 8192
+    with torch.cuda.device(dev):
+        for step in range(3):
+            grads.mul_(-0.7).add_(1e-4)  # a different gradient every step
+            _native.call("dl_adam_step", ref_p, grads, ref_m, ref_v, ref_state, count, 1e-2, 0.9, 0.999, 1e-8, 1.0)
+            # upper slice first on channel 1, lower slice last on channel 0 (it advances the state)
+            _native.call("dl_p2p_exchange_adam", ctypes.addressof(tg), ctypes.addressof(tp), ctypes.addressof(tf),
+                         m, v, state, ctrl, split, count - split, 1, 0, 0, 1, 1e-2, 0.9, 0.999, 1e-8, 1.0, 200)
+            _native.call("dl_p2p_exchange_adam", ctypes.addressof(tg), ctypes.addressof(tp), ctypes.addressof(tf),
+                         m, v, state, ctrl, 0, split, 0, 1, 0, 1, 1e-2, 0.9, 0.999, 1e-8, 1.0, 200)
+            torch.cuda.synchronize()
+            assert torch.equal(params, ref_p) and torch.equal(m, ref_m) and torch.equal(v, ref_v)
+            assert torch.equal(state, ref_state)
+    c = ctrl.tolist()
+    assert c[0] == 0 and c[1] == 3 and c[3] == 3 and c[2] == 0 and c[4] == 0  # status, epochs, counters reset
+
+
+def test_exchange_kernel_gives_up_and_touches_nothing():
+    import ctypes
+    import time
+
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from difflut_b200 import _native
+
+    dev = torch.device("cuda", 0)
+    count = 8 * 1024
+    grads, params, flags, absent, m, v, state, ctrl, table = _exchange_args(dev, count, 2)
+    m.fill_(0.25)
+    v.fill_(0.5)
+    before = (params.clone(), m.clone(), v.clone(), state.clone())
+    peer_grads, peer_params = torch.zeros_like(grads), params.clone()
+    tg, tp, tf = table(grads, peer_grads), table(params, peer_params), table(flags, absent)
+    args = (ctypes.addressof(tg), ctypes.addressof(tp), ctypes.addressof(tf), m, v, state, ctrl, 0, count, 0, 1, 0, 2,
+            1e-2, 0.9, 0.999, 1e-8, 1.0, 200)
+    t0 = time.time()
+    with torch.cuda.device(dev):
+        _native.call("dl_p2p_exchange_adam", *args)
+    torch.cuda.synchronize()
+    waited = time.time() - t0
+    assert 0.15 < waited < 5.0
+    assert int(ctrl[0]) == 2  # 1 + the rank that never arrived
+    assert int(absent[0]) == 1  # this rank did publish its arrival (channel 0, "arrive", slot of rank 0)
+    for now, was in zip((params, m, v, state), before):
+        assert torch.equal(now, was)
+    assert torch.equal(peer_params, before[0])
+    # the status is sticky: the next call returns at once and still changes nothing
+    t0 = time.time()
+    with torch.cuda.device(dev):
+        _native.call("dl_p2p_exchange_adam", *args)
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 0.15
+    for now, was in zip((params, m, v, state), before):
+        assert torch.equal(now, was)
+    # the three-kernel form: a status left by a barrier stops the reduce + Adam kernel as well
+    bctrl = torch.tensor([1, 2], dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _native.call("dl_p2p_reduce_adam", ctypes.addressof(tg), ctypes.addressof(tp), m, v, state, bctrl, count, 0, 2,
+                     1e-2, 0.9, 0.999, 1e-8, 1.0)
+    torch.cuda.synchronize()
+    for now, was in zip((params, m, v, state), before):
+        assert torch.equal(now, was)
+    assert float(torch.ones(4, device=dev).sum()) == 4.0  # the context is still usable
