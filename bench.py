@@ -36,6 +36,16 @@ NCU_TRAFFIC_BWD_FUSED_B8192 = 827.6e6
 WORKLOAD = "dwn3_16000-8000-4000_n6_T8_globalbatch8192_adam"
 
 
+def _peaks():
+    """Measured roofline denominators of this pool's B200s (driver-written file), else the stated fallback."""
+    try:
+        d = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
 def _config(extra=None):
     cfg = {"workload": WORKLOAD, "global_batch": GLOBAL_BATCH, "features": FEATURES, "thermometer_bits": THERMO_BITS,
            "layers": list(SIZES), "n": 6, "classes": CLASSES, "tau": TAU, "optimizer": "adam lr=1e-2"}
@@ -145,15 +155,15 @@ def run_reference_arm(args):
     import torch
 
     threads = min(os.cpu_count() or 1, 64)
-    rows = 512
-    for _ in range(min(args.warmup, 1)):
+    rows = 512  # per step: about half a second on 16 cores, so the requested steps and warm-up fit in a few minutes
+    for _ in range(args.warmup):
         _oracle_step_time(rows, threads)
-    times = [_oracle_step_time(rows, threads) for _ in range(max(1, min(args.steps, 10)))]
+    times = [_oracle_step_time(rows, threads) for _ in range(max(1, args.steps))]
     dt = sum(times) / len(times)
     value = rows / dt
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": args.gpus,
-        "steps": len(times), "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "steps": len(times), "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": _config({"sample_rows_per_step": rows}),
         "cpu_baseline": {"value": value, "unit": "samples/s", "cores": threads, "kind": "port",
@@ -424,6 +434,11 @@ def run_gpu_arm(args):
         }
         if cpu is not None:
             line["cpu_baseline"] = cpu
+    if world == 1 and not args.no_secondary:
+        del net, flush, x_dev, in_bufs
+        torch.cuda.empty_cache()
+        line["secondary"] = collect_secondary(args)
+    if rank == 0:
         guard.emit(json.dumps(line))
     barrier()
     trace("finished")
@@ -438,6 +453,37 @@ def run_gpu_arm(args):
 
 
 # ------------------------------------------------------------------------------ secondary workloads
+def collect_secondary(args):
+    """The other BASELINE configurations, measured in the same process after the main line (one GPU only) and
+    attached to it under "secondary": config 2 (probabilistic layer), config 3 (LearnableLayer), config 5
+    (hard-LUT inference sweep) and the config-4 step through the per-layer API.  Fewer steps than the main line."""
+    import copy
+
+    import torch
+
+    sub = copy.copy(args)
+    sub.steps, sub.warmup, sub.small = min(args.steps, 10), 3, False
+    out = {}
+    for key, fn in (("prob", measure_prob), ("learnable", measure_learnable), ("infer", measure_infer),
+                    ("train_layers", measure_train_layers)):
+        t0 = time.perf_counter()
+        try:
+            line = fn(sub)
+            keep = {k: line[k] for k in ("metric", "value", "unit", "ms_per_step", "dtype", "roofline", "e2e", "dwn_stack")
+                    if k in line}
+            keep["workload"] = line["config"]["workload"]
+            if key == "infer":
+                keep["sweep"] = line["config"]["sweep"]
+            if key == "train_layers":
+                keep["mode"] = line["config"]["mode"]
+        except Exception as e:  # a secondary measurement must not take the main line down; report it
+            keep = {"error": repr(e)}
+        keep["wall_s"] = round(time.perf_counter() - t0, 1)
+        out[key] = keep
+        torch.cuda.empty_cache()
+    return out
+
+
 def _time_gpu(fn, steps, warmup, flush):
     import torch
 
@@ -457,7 +503,7 @@ def _time_gpu(fn, steps, warmup, flush):
     return total / steps
 
 
-def run_infer(args):
+def measure_infer(args):
     """BASELINE config 5: bit-packed hard-LUT inference sweep, rows sharded over the ranks, no communication."""
     import torch
 
@@ -499,12 +545,13 @@ def run_infer(args):
                         "checksum": int(out.sum().item())})
         del packed, host, host_out, dev_in, out
         torch.cuda.empty_cache()
+    line = None
     if rank == 0:
         best = max(results, key=lambda r: r["samples_per_s"])
         # algorithmic bytes per sample of the per-layer kernels: packed input 784 B, layer outputs 2000+1000+500 B
         # written and read once each, 40 B of counts
         bytes_per_sample = 784 + 2 * (784 + 2000 + 1000) + 500 + 40
-        print(json.dumps({
+        line = {
             "metric": "hard-LUT inference samples/s, bit-packed 3-layer n=6 DWN", "value": best["samples_per_s"],
             "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": best["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32",
@@ -512,16 +559,14 @@ def run_infer(args):
                                                     "l2": "256 MB flush between timed passes"}),
             "e2e": {"value": best["e2e_samples_per_s"], "unit": "samples/s",
                     "h2d_bytes_per_step": best["batch"] * 196 * 4, "d2h_bytes_per_step": best["batch"] * 40},
-            "roofline": {"bound": "hbm", "achieved": bytes_per_sample * best["samples_per_s"] / world / 1e9, "peak": 6545.6,
-                         "unit": "GB/s", "frac": bytes_per_sample * best["samples_per_s"] / world / 1e9 / 6545.6,
+            "roofline": {"bound": "hbm", "achieved": bytes_per_sample * best["samples_per_s"] / world / 1e9, "peak": _peaks()["hbm_gbs"],
+                         "peak_source": _peaks()["source"], "unit": "GB/s", "frac": bytes_per_sample * best["samples_per_s"] / world / 1e9 / _peaks()["hbm_gbs"],
                          "traffic": None, "note": "bound by the integer pipe: 63 three-input logic operations per node and 32 samples"},
-        }), flush=True)
-    if world > 1:
-        sys.stdout.flush()
-        os._exit(0)
+        }
+    return line
 
 
-def run_prob(args):
+def measure_prob(args):
     """BASELINE config 2: RandomLayer(4096 -> 8000, n=6, ProbabilisticNode) fused with GroupSum(10), CE, fwd+bwd."""
     import torch
 
@@ -546,17 +591,17 @@ def run_prob(args):
 
     ms = _time_gpu(step, args.steps, max(args.warmup, 3), torch.empty(256 << 20, dtype=torch.uint8, device=device))
     flops = 1276.0 * B * N
-    print(json.dumps({"metric": "train samples/s (fwd+bwd) probabilistic layer 8000 nodes n=6 + GroupSum + CE",
+    return {"metric": "train samples/s (fwd+bwd) probabilistic layer 8000 nodes n=6 + GroupSum + CE",
                       "value": B / (ms * 1e-3), "unit": "samples/s", "n_gpus": 1, "steps": args.steps,
                       "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
                       "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                       "config": {"workload": "prob_layer_B1024_in4096_N8000_n6_k10"},
                       "roofline": {"bound": "fp32", "achieved": flops / (ms * 1e-3) / 1e12, "peak": 148 * 128 * 2 * 1.965e9 / 1e12,
                                    "unit": "TFLOP/s", "frac": flops / (ms * 1e-3) / (148 * 128 * 2 * 1.965e9),
-                                   "traffic": None}}), flush=True)
+                                   "traffic": None}}
 
 
-def run_conv(args):
+def measure_conv(args):
     """ConvolutionalLayer training step (fwd+bwd): 28x28 images in 3 thermometer planes, 5x5 receptive field,
     32 trees of depth 2 with 6-input nodes, batch 128 -> 73 728 patches through 1152 + 192 + 32 nodes."""
     import torch
@@ -589,16 +634,16 @@ def run_conv(args):
         results[name] = _time_gpu(step, args.steps, max(args.warmup, 3), flush)
     patches = B * 24 * 24
     ms = results["dwn"]
-    print(json.dumps({"metric": "train patches/s (fwd+bwd) convolutional DWN layer, 32 trees of depth 2, n=6",
+    return {"metric": "train patches/s (fwd+bwd) convolutional DWN layer, 32 trees of depth 2, n=6",
                       "value": patches / (ms * 1e-3), "unit": "patches/s", "n_gpus": 1, "steps": args.steps,
                       "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
                       "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                       "config": {"workload": "conv_B128_3x28x28_rf5_trees32_depth2_n6", "patches_per_step": patches,
                                  "l2": "256 MB flush between timed steps"},
-                      "ms_per_step_by_node_type": {k: round(v, 4) for k, v in results.items()}}), flush=True)
+                      "ms_per_step_by_node_type": {k: round(v, 4) for k, v in results.items()}}
 
 
-def run_nodes(args):
+def measure_nodes(args):
     """RandomLayer(4096 -> 8000, n=6) fwd+bwd at batch 1024 for each stacked node type (layer API)."""
     import torch
 
@@ -625,16 +670,16 @@ def run_nodes(args):
 
         results[name] = _time_gpu(step, args.steps, max(args.warmup, 3), flush)
     ms = results["dwn_stable"]
-    print(json.dumps({"metric": "train samples/s (fwd+bwd) RandomLayer 4096->8000 n=6, DWNStable nodes",
+    return {"metric": "train samples/s (fwd+bwd) RandomLayer 4096->8000 n=6, DWNStable nodes",
                       "value": B / (ms * 1e-3), "unit": "samples/s", "n_gpus": 1, "steps": args.steps,
                       "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
                       "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                       "config": {"workload": "layer_B1024_in4096_N8000_n6_by_node_type",
                                  "l2": "256 MB flush between timed steps"},
-                      "ms_per_step_by_node_type": {k: round(v, 4) for k, v in results.items()}}), flush=True)
+                      "ms_per_step_by_node_type": {k: round(v, 4) for k, v in results.items()}}
 
 
-def run_learnable(args):
+def measure_learnable(args):
     """BASELINE config 3: LearnableLayer(4096 -> 16000 DWN nodes, n=6), B=4096 binary inputs, loss = sum of outputs."""
     import torch
 
@@ -661,17 +706,18 @@ def run_learnable(args):
 
     ms = _time_gpu(step, max(2, args.steps // 4), 2, None)
     gemm_flops = 2.0 * B * I * (N * 6) * (2 + 1)  # forward with K doubled by the split, one backward GEMM (x needs no grad)
-    print(json.dumps({"metric": "train samples/s (fwd+bwd) LearnableLayer 4096 -> 16000 DWN n=6",
+    return {"metric": "train samples/s (fwd+bwd) LearnableLayer 4096 -> 16000 DWN n=6",
                       "value": B / (ms * 1e-3), "unit": "samples/s", "n_gpus": 1, "steps": max(2, args.steps // 4),
                       "warmup": 2, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                       "dtype": "bf16", "data": "synthetic", "config": {"workload": f"learnable_B{B}_in{I}_N{N}_n6"},
-                      "roofline": {"bound": "tensor", "achieved": gemm_flops / (ms * 1e-3) / 1e12, "peak": 1643.8,
-                                   "unit": "TFLOP/s", "frac": gemm_flops / (ms * 1e-3) / 1e12 / 1643.8, "traffic": None,
-                                   "note": "whole step (softmax, conversions, DWN kernels included) against the GEMM flops"}}),
-          flush=True)
+                      "roofline": {"bound": "tensor", "achieved": gemm_flops / (ms * 1e-3) / 1e12,
+                                   "peak": _peaks()["bf16_tflops_sustained"], "peak_source": _peaks()["source"] + " (sustained cuBLAS bf16)",
+                                   "unit": "TFLOP/s", "frac": gemm_flops / (ms * 1e-3) / 1e12 / _peaks()["bf16_tflops_sustained"],
+                                   "traffic": None,
+                                   "note": "whole step (softmax, conversions, DWN kernels included) against the GEMM flops"}}
 
 
-def run_train_layers(args):
+def measure_train_layers(args):
     """The same 3-layer DWN training step through the per-layer drop-in API: ThermometerEncoder ->
     RandomLayer x3 -> GroupSum -> torch cross-entropy -> autograd -> torch.optim.Adam (fp32 rows between layers)."""
     import torch
@@ -743,15 +789,14 @@ def run_train_layers(args):
         ms_graph = _time_gpu(graph.replay, args.steps, max(args.warmup, 3), flush)
     except Exception as e:  # report, do not hide
         print(f"[bench] CUDA-graph capture of the DWNStack step failed: {e}", file=sys.stderr)
-    print(json.dumps({"metric": METRIC + " (per-layer API)", "value": GLOBAL_BATCH / (ms * 1e-3), "unit": "samples/s",
+    return {"metric": METRIC + " (per-layer API)", "value": GLOBAL_BATCH / (ms * 1e-3), "unit": "samples/s",
                       "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
                       "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
                       "data": "synthetic", "config": _config({"mode": "layer API: fp32 rows between layers, torch autograd + Adam"}),
                       "dwn_stack": {"ms_per_step": ms_stack, "value": GLOBAL_BATCH / (ms_stack * 1e-3),
                                     "mode": "same layers behind DWNStack(layers, encoder, groupsum): bit-packed between layers, "
                                             "torch autograd + torch.optim.Adam",
-                                    "ms_per_step_cuda_graph": ms_graph}}),
-          flush=True)
+                                    "ms_per_step_cuda_graph": ms_graph}}
 
 
 def main():
@@ -765,6 +810,8 @@ def main():
     ap.add_argument("--small", action="store_true", help="reduced sizes of the secondary workloads (for ncu captures)")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="skip the secondary workloads that a one-GPU run attaches to its line")
     ap.add_argument("--global-batch", type=int, default=8192,
                     help="override the global batch (profiling on a small case; the default is the benchmark workload)")
     ap.add_argument("--per-gpu-batch", type=int, default=0,
@@ -782,20 +829,17 @@ def main():
                "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29511"),
                os.path.abspath(__file__)] + sys.argv[1:]
         raise SystemExit(subprocess.call(cmd))
-    if args.workload == "infer":
-        run_infer(args)
-    elif args.workload == "prob":
-        run_prob(args)
-    elif args.workload == "conv":
-        run_conv(args)
-    elif args.workload == "nodes":
-        run_nodes(args)
-    elif args.workload == "learnable":
-        run_learnable(args)
-    elif args.workload == "train-layers":
-        run_train_layers(args)
-    else:
+    measure = {"infer": measure_infer, "prob": measure_prob, "conv": measure_conv, "nodes": measure_nodes,
+               "learnable": measure_learnable, "train-layers": measure_train_layers}.get(args.workload)
+    if measure is None:
         run_gpu_arm(args)
+        return
+    line = measure(args)
+    if line is not None:
+        print(json.dumps(line), flush=True)
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        sys.stdout.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -44,6 +44,8 @@ SIGNATURES = {
     "dl_sum_groups": "pplll s",
     "dl_dwn_mapped_fwd": "ppplllli s",
     "dl_dwn_mapped_bwd": "pppppllll s",
+    "dl_dwn_stable_mapped_bwd_input": "ppppfpllll s",
+    "dl_hybrid_mapped_bwd": "pppppllll s",
     "dl_prob_fwd_t": "pppfpllll s",
     "dl_prob_fwd_groupsum_t": "pppfpppllllfl s",
     "dl_prob_bwd_t": "pppfplfpplllll s",
@@ -64,6 +66,8 @@ SIGNATURES = {
     "dl_dwn_fwd_groupsum_noalloc_t": "pppplllfl s",
     "dl_flip_rows": "pplfl s",
     "dl_bits_flip_t": "plllfl s",
+    "dl_flip_at": "pppll s",
+    "dl_bits_flip_at_t": "ppllll s",
     "dl_grad_rescale": "ppllififp s",
     "dl_p2p_barrier": "pllpl s",
     "dl_p2p_reduce_adam": "pppppplllfffff s",

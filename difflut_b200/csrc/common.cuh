@@ -37,14 +37,17 @@ __device__ __forceinline__ uint32_t dl_spread_nibble(uint32_t nib) {
     return (nib * 0x00204081u) & 0x01010101u;
 }
 
-// One Adam element update (torch.optim.Adam without weight decay / amsgrad); shared by the local and
-// the peer-to-peer optimiser kernels so that both produce the same bits.
-__device__ __forceinline__ float adam_update(float p, float gi, float& m, float& v, float step_size, float bc2_sqrt,
-                                             float b1, float b2, float eps) {
-    m = m + (gi - m) * (1.0f - b1);
-    v = v * b2 + (1.0f - b2) * gi * gi;
-    const float denom = sqrtf(v) / bc2_sqrt + eps;
-    return p - step_size * (m / denom);
+// One Adam element update (torch.optim.Adam without weight decay / amsgrad): m <- lerp(m, g, 1-b1),
+// v <- v*b2 + (1-b2)*g*g, p <- p - step_size * m / (sqrt(v)/sqrt(bc2) + eps), g = g_raw * gscale.  Every
+// operation is written with its rounding spelled out, so that the compiler cannot contract it differently
+// in different kernels: the local and the peer-to-peer optimiser kernels produce the same bits.
+__device__ __forceinline__ float adam_update(float p, float g_raw, float gscale, float& m, float& v, float step_size,
+                                             float bc2_sqrt, float b1, float b2, float eps) {
+    const float gi = __fmul_rn(g_raw, gscale);
+    m = __fmaf_rn(__fsub_rn(gi, m), __fsub_rn(1.0f, b1), m);
+    v = __fmaf_rn(__fmul_rn(__fsub_rn(1.0f, b2), gi), gi, __fmul_rn(v, b2));
+    const float denom = __fadd_rn(__fdiv_rn(__fsqrt_rn(v), bc2_sqrt), eps);
+    return __fmaf_rn(-step_size, __fdiv_rn(m, denom), p);
 }
 
 // Software-pipelined fused DWN backward for n = 6, chunk-interleaved bits and whole 1024-sample blocks
@@ -54,4 +57,4 @@ int dl_launch_bwd_pipelined(const uint8_t* addr_up, const float* g_up, int64_t g
                             const float* efd_up, int n_up, const int32_t* inv_ptr, const int32_t* inv_ent,
                             const uint32_t* in_bits, const int32_t* map, float* g_out, uint8_t* addr_out,
                             float* gt, int64_t group_stride, int64_t N, int64_t N_up, int64_t Bp, int64_t Wp,
-                            int blocks_per_item, cudaStream_t s);
+                            int blocks_per_item, int min_ctas, cudaStream_t s);

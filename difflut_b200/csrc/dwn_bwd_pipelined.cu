@@ -3,7 +3,7 @@
 //
 // What limits this kernel is the SM's load/store data pipe (shuffles, shared-memory and global
 // accesses all pass through it, one 128-byte wavefront per cycle), then the latency of the dependent
-// loads at the start of every (node, sample group) item.  Two changes against the general kernel:
+// loads at the start of every (node, sample group) item.  Three changes against the general kernel:
 //
 //  * An item may span several 1024-sample blocks (`bpi`): the lane-private histogram is cleared and
 //    reduced once per item instead of once per block (128 of the ~450 wavefronts of a one-block item),
@@ -11,12 +11,17 @@
 //    after it is read).
 //  * The index data of the NEXT item travels while the current item is computed: its map row and
 //    inverse-map bounds are loaded one item ahead (one value per lane, handed out by shuffles), its
-//    inverse-map entries half an item ahead, and its input words, EFD values and first chunk of
-//    gradients/addresses are requested before the current item's histogram is reduced.  An item start
-//    therefore waits for one memory round trip (overlapped with the reduction) instead of four.
+//    inverse-map entries at the start of the item's last block, and its input words, EFD values and first two
+//    chunks of gradients/addresses are requested before the current item's histogram is reduced.  An item
+//    start therefore waits for one memory round trip (overlapped with the reduction) instead of four.
+//  * Inside a block the gradients/addresses of chunk c + 2 are requested as soon as chunk c's have been
+//    used (reader by reader, into the registers just freed): two chunks are in flight with two buffers,
+//    which is what a load that misses L2 needs.
 //
 // The arithmetic and its order are those of dwn_bwd_fused_kernel: with bpi = 1 both kernels give the
 // same bits.  Reference semantics: EFDFunctionCPU.backward, difflut/nodes/dwn_node.py:167-229.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace {
@@ -59,6 +64,19 @@ __device__ __forceinline__ void load_chunk(Chunk& d, int c, const uint8_t* __res
     }
 }
 
+// one reader's share of a chunk (DIRECT: the node's own gradient row)
+template <bool DIRECT, bool GSAME>
+__device__ __forceinline__ void load_reader(Chunk& d, int k, int c, const uint8_t* __restrict__ addr_up,
+                                            const float* __restrict__ g_up, const uint32_t (&oa)[MAXR],
+                                            const uint32_t (&og)[MAXR]) {
+    if (DIRECT) {
+        d.g[0] = __ldg(reinterpret_cast<const float4*>(g_up + (size_t)og[0] + c * 128));
+    } else {
+        d.a[k] = __ldg(reinterpret_cast<const uint32_t*>(addr_up + (size_t)oa[k] + c * 128));
+        d.g[k] = __ldg(reinterpret_cast<const float4*>(g_up + (size_t)(GSAME ? oa[k] : og[k]) + c * 128));
+    }
+}
+
 __device__ __forceinline__ void efd_lookup(float4& acc, const float4 g, const uint32_t a, const uint32_t lowm,
                                            const float tv) {
     // lane index of each shuffle = the sample's address without the slot's bit (a shuffle takes its
@@ -78,8 +96,8 @@ __device__ __forceinline__ void hist_add(uint32_t mine, uint32_t a, float v) {
     sts_f32(at, lds_f32(at) + v);
 }
 
-template <bool DIRECT, bool GSAME, int OUTS>
-__global__ void __launch_bounds__(PW * 32, 5)
+template <bool DIRECT, bool GSAME, int OUTS, int MINB>
+__global__ void __launch_bounds__(PW * 32, MINB)
 dwn_bwd_pipelined_kernel(const uint8_t* __restrict__ addr_up, const float* __restrict__ g_up, uint32_t ugdiv,
                          float gscale, const float* __restrict__ efd_up, int n_up,
                          const int32_t* __restrict__ inv_ptr, const int32_t* __restrict__ inv_ent,
@@ -156,7 +174,7 @@ dwn_bwd_pipelined_kernel(const uint8_t* __restrict__ addr_up, const float* __res
             }
         }
         if (OUTS != 0) oo = (uint32_t)node * Bp + b0;
-        load_chunk<DIRECT, GSAME>(even, 0, addr_up, g_up, oa, og);
+        load_chunk<DIRECT, GSAME>(even, 0, addr_up, g_up, oa, og);  // chunk 1 follows once the caller has registers for it
     };
 
     // the next 1024-sample block of the same node
@@ -177,17 +195,27 @@ dwn_bwd_pipelined_kernel(const uint8_t* __restrict__ addr_up, const float* __res
         }
         if (OUTS != 0) oo += 1024u;
         load_chunk<DIRECT, GSAME>(even, 0, addr_up, g_up, oa, og);
+        load_chunk<DIRECT, GSAME>(odd, 1, addr_up, g_up, oa, og);
     };
 
-    auto consume = [&](const Chunk& d, int c, int blk, int m1cur) {
+    // Chunk c of the current block.  As soon as a reader's address word and gradients have been used, the
+    // same registers receive that reader's data of chunk c + 2: two chunks are in flight with two buffers.
+    // EXTRA: the node has more readers than registers (rare); they are walked through the inverse map.
+    auto consume = [&](Chunk& d, int c, int blk, int m1cur, auto extra_tag) {
+        constexpr bool EXTRA = decltype(extra_tag)::value;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         if (DIRECT) {
             acc = d.g[0];
             acc.x *= gscale; acc.y *= gscale; acc.z *= gscale; acc.w *= gscale;
+            if (c + 2 < 8) load_reader<DIRECT, GSAME>(d, 0, c + 2, addr_up, g_up, oa, og);
         } else {
 #pragma unroll
-            for (int k = 0; k < MAXR; ++k) efd_lookup(acc, d.g[k], d.a[k], lowm[k], tv[k]);
-            for (int k = 0; k < extra; ++k) {  // rare: more readers than registers
+            for (int k = 0; k < MAXR; ++k) {
+                efd_lookup(acc, d.g[k], d.a[k], lowm[k], tv[k]);
+                if (c + 2 < 8) load_reader<DIRECT, GSAME>(d, k, c + 2, addr_up, g_up, oa, og);
+            }
+            if (EXTRA)
+            for (int k = 0; k < extra; ++k) {
                 const int ent = __ldg(&inv_ent[__shfl_sync(0xffffffffu, m1cur, 6) + MAXR + k]);
                 const uint32_t j = (uint32_t)ent >> 3, i = (uint32_t)ent & 7u;
                 const float t = gscale * __ldg(efd_up + ((size_t)j * n_up + i) * 32 + lane);
@@ -224,19 +252,26 @@ dwn_bwd_pipelined_kernel(const uint8_t* __restrict__ addr_up, const float* __res
         const int m2 = load_meta2(m1);
         setup(f, cg, m1, m2);
     }
+    load_chunk<DIRECT, GSAME>(odd, 1, addr_up, g_up, oa, og);
 
     while (true) {
         const int blk_first = cg * bpi;
         const int blk_end = blk_first + bpi < NB ? blk_first + bpi : NB;
         for (int blk = blk_first; blk < blk_end; ++blk) {
             const bool last_blk = blk + 1 == blk_end;
+            if (last_blk && nvalid) m2n = load_meta2(m1n);  // uniform over the warp; used at the item's end
+            if (extra == 0) {
 #pragma unroll
-            for (int c = 0; c < 8; c += 2) {
-                load_chunk<DIRECT, GSAME>(odd, c + 1, addr_up, g_up, oa, og);
-                if (c == 2 && last_blk && nvalid) m2n = load_meta2(m1n);  // uniform over the warp
-                consume(even, c, blk, m1);
-                if (c + 2 < 8) load_chunk<DIRECT, GSAME>(even, c + 2, addr_up, g_up, oa, og);
-                consume(odd, c + 1, blk, m1);
+                for (int c = 0; c < 8; c += 2) {
+                    consume(even, c, blk, m1, std::false_type{});
+                    consume(odd, c + 1, blk, m1, std::false_type{});
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 8; c += 2) {
+                    consume(even, c, blk, m1, std::true_type{});
+                    consume(odd, c + 1, blk, m1, std::true_type{});
+                }
             }
             if (!last_blk) next_block(m1, blk + 1);
         }
@@ -283,6 +318,7 @@ dwn_bwd_pipelined_kernel(const uint8_t* __restrict__ addr_up, const float* __res
         dst[lane + 32] = s1;
         __syncwarp();
         if (!more) break;
+        load_chunk<DIRECT, GSAME>(odd, 1, addr_up, g_up, oa, og);  // the reduction's registers are free again
     }
 }
 
@@ -295,7 +331,7 @@ int dl_launch_bwd_pipelined(const uint8_t* addr_up, const float* g_up, int64_t g
                             const float* efd_up, int n_up, const int32_t* inv_ptr, const int32_t* inv_ent,
                             const uint32_t* in_bits, const int32_t* map, float* g_out, uint8_t* addr_out,
                             float* gt, int64_t group_stride, int64_t N, int64_t N_up, int64_t Bp, int64_t Wp,
-                            int blocks_per_item, cudaStream_t s) {
+                            int blocks_per_item, int min_ctas, cudaStream_t s) {
     const int64_t rows = N > N_up ? N : N_up;
     if (rows * Bp >= ((int64_t)1 << 32) || Wp >= ((int64_t)1 << 31)) return DL_ERR_UNSUPPORTED;
     const int NB = (int)(Bp / 1024);
@@ -303,7 +339,8 @@ int dl_launch_bwd_pipelined(const uint8_t* addr_up, const float* g_up, int64_t g
     if (group_stride > 0) bpi = 1;  // one slab per 1024-sample group: items cannot span blocks
     if (bpi > NB) bpi = NB;
     const int G = (NB + bpi - 1) / bpi;
-    const int64_t cap = (int64_t)DL_NUM_SMS * 5;
+    if (min_ctas != 4) min_ctas = 5;
+    const int64_t cap = (int64_t)DL_NUM_SMS * min_ctas;  // persistent grid: the CTAs resident at once
     const int64_t blocks64 = dl_ceil_div(N, PW);
     const unsigned blocks = (unsigned)(blocks64 < cap ? blocks64 : cap);
     int64_t gy = 1;
@@ -316,12 +353,19 @@ int dl_launch_bwd_pipelined(const uint8_t* addr_up, const float* g_up, int64_t g
     const bool direct = inv_ptr == nullptr;
     const bool gsame = gdiv_up == 1;
     const int outs = (g_out ? 1 : 0) | (addr_out ? 2 : 0);
-#define DL_PIPE(D, S, O)                                                                                            \
-    do {                                                                                                            \
-        cudaFuncSetAttribute(dwn_bwd_pipelined_kernel<D, S, O>, cudaFuncAttributePreferredSharedMemoryCarveout, 75); \
-        dwn_bwd_pipelined_kernel<D, S, O><<<grid, PW * 32, 0, s>>>(                                                 \
-            addr_up, g_up, (uint32_t)gdiv_up, gscale_up, efd_up, n_up, inv_ptr, inv_ent, in_bits, map, g_out,       \
-            addr_out, gt, group_stride, (int)N, (uint32_t)Bp, (uint32_t)Wp, NB, bpi);                               \
+#define DL_PIPE(D, S, O)                                                                                             \
+    do {                                                                                                             \
+        if (min_ctas == 4) {                                                                                         \
+            cudaFuncSetAttribute(dwn_bwd_pipelined_kernel<D, S, O, 4>, cudaFuncAttributePreferredSharedMemoryCarveout, 60); \
+            dwn_bwd_pipelined_kernel<D, S, O, 4><<<grid, PW * 32, 0, s>>>(                                           \
+                addr_up, g_up, (uint32_t)gdiv_up, gscale_up, efd_up, n_up, inv_ptr, inv_ent, in_bits, map, g_out,    \
+                addr_out, gt, group_stride, (int)N, (uint32_t)Bp, (uint32_t)Wp, NB, bpi);                            \
+        } else {                                                                                                     \
+            cudaFuncSetAttribute(dwn_bwd_pipelined_kernel<D, S, O, 5>, cudaFuncAttributePreferredSharedMemoryCarveout, 75); \
+            dwn_bwd_pipelined_kernel<D, S, O, 5><<<grid, PW * 32, 0, s>>>(                                           \
+                addr_up, g_up, (uint32_t)gdiv_up, gscale_up, efd_up, n_up, inv_ptr, inv_ent, in_bits, map, g_out,    \
+                addr_out, gt, group_stride, (int)N, (uint32_t)Bp, (uint32_t)Wp, NB, bpi);                            \
+        }                                                                                                            \
     } while (0)
 #define DL_PIPE_OUTS(D, S)                    \
     switch (outs) {                           \

@@ -80,25 +80,31 @@ bits_swizzle_kernel(const uint32_t* __restrict__ nat, uint32_t* __restrict__ swz
 }
 
 // Thermometer compare-and-pack straight into the chunk-interleaved layout (see bits_swizzle_kernel).
-// A CTA owns one 1024-sample block and FEATS features (one warp per feature): the block's values go to
-// shared memory feature-major, index s + 4*(s/128) inside a feature row (row pitch 1060), which makes both
-// the fill and the read-out (lane = chunk c + 8r reading sample 128c + 4w + r) bank-conflict free.
+// A CTA owns one 1024-sample block and FEATS features (one warp per feature).  The block's values go to
+// shared memory as tile[feature][q][w] with q = c + 8r the bit position and w the word of sample
+// 128c + 4w + r (row pitch 33, feature pitch 1057: fill and read-out are both bank-conflict free).
 // Fill: with 16-byte-aligned rows (VEC4) a thread fetches four features of a sample per load and has all
-// of its eight loads in flight before the first value is stored; otherwise 4-byte loads.  Warp k then keeps
-// the 32 values of each word position w of feature k in registers and, per threshold, one ballot per w
-// yields word w directly in the interleaved bit order; lane w keeps it and the 32 words of a
-// (feature, threshold) row leave as one coalesced 128-byte store.
-constexpr int SWZ_PITCH = 1060;
+// of its eight loads in flight before the first value is stored; otherwise 4-byte loads.  Lane w of warp k
+// then holds the 32 values of word w of feature k in registers, in bit order, and builds each threshold's
+// word with two instructions per bit: the sign of (threshold - value) is exactly the strict comparison
+// value > threshold for finite thresholds (the difference of two floats is zero only when they are equal,
+// and a NaN, which is what padding samples hold, keeps its positive sign), and a funnel shift moves it into
+// the word.  The 32 words of a (feature, threshold) row leave as one coalesced 128-byte store.
+constexpr int SWZ_ROW = 33, SWZ_FEAT = 32 * SWZ_ROW + 1;
+
+__device__ __forceinline__ int swz_slot(int s) {  // sample s of the block -> q * SWZ_ROW + w
+    return (((s >> 7) + 8 * (s & 3)) * SWZ_ROW) + ((s >> 2) & 31);
+}
 
 template <int FEATS, bool VEC4>
 __global__ void __launch_bounds__(FEATS * 32)
 thermo_pack_s_kernel(const float* __restrict__ x, const float* __restrict__ thr, uint32_t* __restrict__ bits_s,
                      int64_t B, int64_t F, int T, int64_t G) {
-    __shared__ float tile[FEATS * SWZ_PITCH];
+    __shared__ float tile[FEATS * SWZ_FEAT];
     const int64_t g = blockIdx.x;
     const int64_t f0 = (int64_t)blockIdx.y * FEATS;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const float nan = __int_as_float(0x7fc00000);  // compares false: padding packs as 0
+    const float nan = __int_as_float(0x7fc00000);  // (threshold - NaN) keeps the positive sign: padding packs as 0
     if (VEC4) {
         constexpr int QUADS = FEATS / 4;               // 16-byte pieces per sample
         constexpr int ROWS = FEATS * 32 / QUADS;       // samples per pass
@@ -113,36 +119,32 @@ thermo_pack_s_kernel(const float* __restrict__ x, const float* __restrict__ thr,
         }
 #pragma unroll
         for (int k = 0; k < PASSES; ++k) {
-            const int s = s0 + k * ROWS;
-            float* dst = tile + (4 * h) * SWZ_PITCH + s + 4 * (s >> 7);
+            float* dst = tile + (4 * h) * SWZ_FEAT + swz_slot(s0 + k * ROWS);
             dst[0] = v[k].x;
-            dst[SWZ_PITCH] = v[k].y;
-            dst[2 * SWZ_PITCH] = v[k].z;
-            dst[3 * SWZ_PITCH] = v[k].w;
+            dst[SWZ_FEAT] = v[k].y;
+            dst[2 * SWZ_FEAT] = v[k].z;
+            dst[3 * SWZ_FEAT] = v[k].w;
         }
     } else {
         const int fl = threadIdx.x % FEATS;
         for (int s = threadIdx.x / FEATS; s < 1024; s += 32) {
             const int64_t b = g * 1024 + s, f = f0 + fl;
-            tile[fl * SWZ_PITCH + s + 4 * (s >> 7)] = (b < B && f < F) ? __ldg(x + b * F + f) : nan;
+            tile[fl * SWZ_FEAT + swz_slot(s)] = (b < B && f < F) ? __ldg(x + b * F + f) : nan;
         }
     }
     __syncthreads();
     const int64_t f = f0 + warp;
     if (f >= F) return;
-    const int c = lane & 7, r = lane >> 3;
     float v[32];
 #pragma unroll
-    for (int w = 0; w < 32; ++w) v[w] = tile[warp * SWZ_PITCH + 132 * c + 4 * w + r];
+    for (int q = 0; q < 32; ++q) v[q] = tile[warp * SWZ_FEAT + q * SWZ_ROW + lane];
     for (int t = 0; t < T; ++t) {
-        const float th = __ldg(&thr[f * T + t]);
-        uint32_t mine = 0;
+        const float th = __fadd_rn(__ldg(&thr[f * T + t]), 0.0f);  // a threshold of -0 counts as +0
+        uint32_t word = 0;
 #pragma unroll
-        for (int w = 0; w < 32; ++w) {
-            const uint32_t word = __ballot_sync(0xffffffffu, v[w] > th);
-            if (lane == w) mine = word;
-        }
-        bits_s[((f * T + t) * G + g) * 32 + lane] = mine;
+        for (int q = 31; q >= 0; --q)  // (word << 1) | sign bit of (th - v[q])
+            word = __funnelshift_l(__float_as_uint(__fsub_rn(th, v[q])), word, 1);
+        bits_s[((f * T + t) * G + g) * 32 + lane] = word;
     }
 }
 

@@ -114,17 +114,17 @@ __global__ void adam_kernel(float* __restrict__ p, const float* __restrict__ g, 
         float4 pp = reinterpret_cast<float4*>(p)[i], mm = reinterpret_cast<float4*>(m)[i];
         float4 vv = reinterpret_cast<float4*>(v)[i];
         const float4 gg = reinterpret_cast<const float4*>(g)[i];
-        pp.x = adam_update(pp.x, gg.x * gscale, mm.x, vv.x, step_size, bc2_sqrt, b1, b2, eps);
-        pp.y = adam_update(pp.y, gg.y * gscale, mm.y, vv.y, step_size, bc2_sqrt, b1, b2, eps);
-        pp.z = adam_update(pp.z, gg.z * gscale, mm.z, vv.z, step_size, bc2_sqrt, b1, b2, eps);
-        pp.w = adam_update(pp.w, gg.w * gscale, mm.w, vv.w, step_size, bc2_sqrt, b1, b2, eps);
+        pp.x = adam_update(pp.x, gg.x, gscale, mm.x, vv.x, step_size, bc2_sqrt, b1, b2, eps);
+        pp.y = adam_update(pp.y, gg.y, gscale, mm.y, vv.y, step_size, bc2_sqrt, b1, b2, eps);
+        pp.z = adam_update(pp.z, gg.z, gscale, mm.z, vv.z, step_size, bc2_sqrt, b1, b2, eps);
+        pp.w = adam_update(pp.w, gg.w, gscale, mm.w, vv.w, step_size, bc2_sqrt, b1, b2, eps);
         reinterpret_cast<float4*>(p)[i] = pp;
         reinterpret_cast<float4*>(m)[i] = mm;
         reinterpret_cast<float4*>(v)[i] = vv;
     }
     for (int64_t i = (quads << 2) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count;
          i += (int64_t)gridDim.x * blockDim.x)
-        p[i] = adam_update(p[i], g[i] * gscale, m[i], v[i], step_size, bc2_sqrt, b1, b2, eps);
+        p[i] = adam_update(p[i], g[i], gscale, m[i], v[i], step_size, bc2_sqrt, b1, b2, eps);
 }
 
 // Adam step whose gradient is the ordered sum of `groups` partial-gradient slabs; the summed
@@ -142,13 +142,10 @@ __global__ void adam_groups_kernel(float* __restrict__ p, const float* __restric
         float acc = 0.f;
         for (int g = 0; g < groups; ++g) acc += partial[(int64_t)g * stride + i];
         g_out[i] = acc;
-        const float gi = acc * gscale;
-        const float mi = m[i] + (gi - m[i]) * (1.0f - b1);
-        const float vi = v[i] * b2 + (1.0f - b2) * gi * gi;
+        float mi = m[i], vi = v[i];
+        p[i] = adam_update(p[i], acc, gscale, mi, vi, step_size, bc2_sqrt, b1, b2, eps);
         m[i] = mi;
         v[i] = vi;
-        const float denom = sqrtf(vi) / bc2_sqrt + eps;
-        p[i] = p[i] - step_size * (mi / denom);
     }
 }
 

@@ -45,6 +45,35 @@ __global__ void bits_flip_t_kernel(uint32_t* __restrict__ bits_t, int64_t F, int
     }
 }
 
+// Exact-count variant (the reference's choice below p = 0.05, base_layer.py:226-262): the caller draws the
+// positions (a random permutation's first `flips` entries, so they are distinct) and these kernels apply them.
+__global__ void copy_f32_kernel(const float* __restrict__ x, float* __restrict__ out, int64_t count) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count;
+         i += (int64_t)gridDim.x * blockDim.x)
+        out[i] = x[i];
+}
+
+__global__ void flip_at_kernel(const float* __restrict__ x, float* __restrict__ out, const int64_t* __restrict__ idx,
+                               int64_t count, int64_t flips) {
+    for (int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k < flips;
+         k += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t i = idx[k];
+        if (i >= 0 && i < count) out[i] = 1.0f - x[i];
+    }
+}
+
+// position e of the row-major (B, F) matrix = sample e / F, feature e % F; two positions can share a word
+__global__ void bits_flip_at_t_kernel(uint32_t* __restrict__ bits_t, const int64_t* __restrict__ idx, int64_t flips,
+                                      int64_t F, int64_t B, int64_t Wp) {
+    for (int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; k < flips;
+         k += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t e = idx[k];
+        if (e < 0 || e >= F * B) continue;
+        const int64_t b = e / F, f = e - b * F;
+        atomicXor(bits_t + f * Wp + (b >> 5), 1u << (b & 31));
+    }
+}
+
 __device__ __forceinline__ double block_sum(double v, double* shared) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
@@ -143,6 +172,27 @@ DL_EXPORT int dl_bits_flip_t(uint32_t* bits_t, int64_t F, int64_t B, int64_t Bp,
     const int64_t blocks = dl_min64(dl_ceil_div(F * (Bp / 32), 256), (int64_t)DL_NUM_SMS * 16);
     bits_flip_t_kernel<<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(bits_t, F, B, Bp / 32,
                                                                      flip_threshold(probability), (uint64_t)seed);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_flip_at(const float* x, float* out, const int64_t* positions, int64_t count, int64_t flips,
+                         dl_stream_t stream) {
+    DL_REQUIRE(x && out && x != out && count > 0 && flips >= 0 && (positions || flips == 0));
+    cudaStream_t s = dl_cast(stream);
+    copy_f32_kernel<<<(unsigned)dl_min64(dl_ceil_div(count, 256), (int64_t)DL_NUM_SMS * 16), 256, 0, s>>>(x, out, count);
+    if (cudaPeekAtLastError() != cudaSuccess) return DL_ERR_LAUNCH;
+    if (flips > 0)
+        flip_at_kernel<<<(unsigned)dl_min64(dl_ceil_div(flips, 256), (int64_t)DL_NUM_SMS * 16), 256, 0, s>>>(
+            x, out, positions, count, flips);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_bits_flip_at_t(uint32_t* bits_t, const int64_t* positions, int64_t flips, int64_t F, int64_t B,
+                                int64_t Bp, dl_stream_t stream) {
+    DL_REQUIRE(bits_t && F > 0 && B > 0 && Bp >= B && Bp % DL_BATCH_ALIGN == 0 && flips >= 0 && (positions || flips == 0));
+    if (flips > 0)
+        bits_flip_at_t_kernel<<<(unsigned)dl_min64(dl_ceil_div(flips, 256), (int64_t)DL_NUM_SMS * 16), 256, 0,
+                                dl_cast(stream)>>>(bits_t, positions, flips, F, B, Bp / 32);
     return dl_launch_status();
 }
 

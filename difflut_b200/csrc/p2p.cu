@@ -89,10 +89,10 @@ p2p_reduce_adam_kernel(PeerTable grads, PeerTable params, float* __restrict__ m,
         }
         float4 pp = static_cast<const float4*>(params.ptr[0])[i];  // every rank's copy holds the same bits
         float4 mm = reinterpret_cast<float4*>(m)[i - lo], vv = reinterpret_cast<float4*>(v)[i - lo];
-        pp.x = adam_update(pp.x, g.x * gscale, mm.x, vv.x, step_size, bc2_sqrt, b1, b2, eps);
-        pp.y = adam_update(pp.y, g.y * gscale, mm.y, vv.y, step_size, bc2_sqrt, b1, b2, eps);
-        pp.z = adam_update(pp.z, g.z * gscale, mm.z, vv.z, step_size, bc2_sqrt, b1, b2, eps);
-        pp.w = adam_update(pp.w, g.w * gscale, mm.w, vv.w, step_size, bc2_sqrt, b1, b2, eps);
+        pp.x = adam_update(pp.x, g.x, gscale, mm.x, vv.x, step_size, bc2_sqrt, b1, b2, eps);
+        pp.y = adam_update(pp.y, g.y, gscale, mm.y, vv.y, step_size, bc2_sqrt, b1, b2, eps);
+        pp.z = adam_update(pp.z, g.z, gscale, mm.z, vv.z, step_size, bc2_sqrt, b1, b2, eps);
+        pp.w = adam_update(pp.w, g.w, gscale, mm.w, vv.w, step_size, bc2_sqrt, b1, b2, eps);
         reinterpret_cast<float4*>(m)[i - lo] = mm;
         reinterpret_cast<float4*>(v)[i - lo] = vv;
 #pragma unroll
@@ -177,10 +177,10 @@ p2p_exchange_adam_kernel(PeerTable grads, PeerTable params, PeerTable flags, flo
         }
         float4 pp = static_cast<const float4*>(params.ptr[rank])[i];  // every rank's copy holds the same bits
         float4 mm = reinterpret_cast<float4*>(m)[mlo + i - lo], vv = reinterpret_cast<float4*>(v)[mlo + i - lo];
-        pp.x = adam_update(pp.x, g.x * gscale, mm.x, vv.x, step_size, bc2_sqrt, b1, b2, eps);
-        pp.y = adam_update(pp.y, g.y * gscale, mm.y, vv.y, step_size, bc2_sqrt, b1, b2, eps);
-        pp.z = adam_update(pp.z, g.z * gscale, mm.z, vv.z, step_size, bc2_sqrt, b1, b2, eps);
-        pp.w = adam_update(pp.w, g.w * gscale, mm.w, vv.w, step_size, bc2_sqrt, b1, b2, eps);
+        pp.x = adam_update(pp.x, g.x, gscale, mm.x, vv.x, step_size, bc2_sqrt, b1, b2, eps);
+        pp.y = adam_update(pp.y, g.y, gscale, mm.y, vv.y, step_size, bc2_sqrt, b1, b2, eps);
+        pp.z = adam_update(pp.z, g.z, gscale, mm.z, vv.z, step_size, bc2_sqrt, b1, b2, eps);
+        pp.w = adam_update(pp.w, g.w, gscale, mm.w, vv.w, step_size, bc2_sqrt, b1, b2, eps);
         reinterpret_cast<float4*>(m)[mlo + i - lo] = mm;
         reinterpret_cast<float4*>(v)[mlo + i - lo] = vv;
 #pragma unroll

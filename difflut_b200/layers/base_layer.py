@@ -83,11 +83,15 @@ class LUTLayerMixin(nn.Module):
     def _apply_bit_flip(self, x: torch.Tensor) -> torch.Tensor:
         """x -> 1-x on a random `flip_probability` fraction; the flip carries no gradient.
 
-        CUDA tensors go through `dl_flip_rows` (Bernoulli per element; the reference draws an exact count
-        when the probability is below 0.05, base_layer.py:189-226 - same expectation)."""
+        As in the reference (base_layer.py:189-262): below a probability of 0.05 exactly
+        int(numel * p) distinct positions flip, the first entries of `torch.randperm(numel)` on the tensor's
+        device (`dl_flip_at`); from 0.05 on every element flips independently (`dl_flip_rows`)."""
         if self.flip_probability <= 0.0 or not self.training:
             return x
         if x.is_cuda:
+            if self.flip_probability < 0.05:
+                positions = self._draw_flip_positions(x.numel(), x.device)
+                return x if positions is None else _FlipAtFunction.apply(x, positions)
             return _FlipFunction.apply(x, float(self.flip_probability), self._draw_seed())
         if self.flip_probability < 0.05:
             count = int(x.numel() * self.flip_probability)
@@ -97,9 +101,16 @@ class LUTLayerMixin(nn.Module):
             mask[torch.randperm(x.numel(), device=x.device)[:count]] = True
             mask = mask.view_as(x)
         else:
-            mask = torch.rand(x.shape, device=x.device) < self.flip_probability
+            mask = torch.bernoulli(torch.full(x.shape, float(self.flip_probability), device=x.device)).bool()
         delta = torch.where(mask, 1.0 - 2.0 * x.detach(), torch.zeros_like(x))
         return x + delta
+
+    def _draw_flip_positions(self, numel: int, device) -> Optional[torch.Tensor]:
+        """The positions the reference's sparse rule flips (base_layer.py:242-254), or None when there are none."""
+        count = int(numel * self.flip_probability)
+        if count == 0:
+            return None
+        return torch.randperm(numel, device=device)[:count].contiguous()
 
     def _apply_gradient_stabilization(self, grad: torch.Tensor) -> torch.Tensor:
         """(g - mean) * sqrt(target_std / (mean(g^2) + eps)), over the layer or per sample
@@ -144,6 +155,24 @@ class _FlipFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         return g, None, None
+
+
+class _FlipAtFunction(torch.autograd.Function):
+    """out = 1 - x at the given positions, identity gradient (the reference adds a detached delta)."""
+
+    @staticmethod
+    def forward(ctx, x, positions):
+        from .. import _native
+
+        x = x.contiguous().float()
+        out = torch.empty_like(x)
+        with torch.cuda.device(x.device):
+            _native.call("dl_flip_at", x, out, positions, x.numel(), positions.numel())
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
 
 
 class _NodeViews:
@@ -452,17 +481,17 @@ class BaseLUTLayer(ABC, LUTLayerMixin, nn.Module):
             if self.training:
                 return DWNLayerFunction.apply(x, params[0], plan, self.alpha, self.beta, None, geom)
             return dwn_levels_eval(x, [(params[0], plan)], geom)
-        if kind == "dwn_stable":
+        if kind == "dwn_stable" and fast:
             tables = torch.sigmoid(params[0])
             if self.training:
                 scales = params[1].detach().float().repeat_interleave(self.output_dim_per_node)
                 return DWNLayerFunction.apply(x, tables, plan, 0.0, 0.0, scales, geom)
             return dwn_levels_eval(x, [(tables, plan)], geom)
-        if kind == "hybrid" and not self.training:
+        if kind == "hybrid" and fast and not self.training:
             return dwn_levels_eval(x, [(torch.sigmoid(params[0]), plan)], geom)
         if geom is not None:
             x = PatchFunction.apply(x, geom)
-        if kind == "hybrid":
+        if kind == "hybrid" and fast:
             return HybridLayerFunction.apply(x, torch.sigmoid(params[0]), plan)
         if kind == "probabilistic" and fast and self.training:
             return ProbLayerFunction.apply(x, params[0], plan, self.temperature, None, 1.0)

@@ -196,7 +196,13 @@ class ConvolutionalLayer(LUTLayerMixin, nn.Module):
         source = geom
         if flip and bits_only:
             # the nodes only read `patch >= 0.5`: flip the packed patch bits instead of materialising patches
-            source = StackOptions(geom, flip=(float(self.flip_probability), self._draw_seed()))
+            if self.flip_probability < 0.05:
+                # the reference's sparse rule: an exact number of the B*P x (C*kh*kw) patch entries flips
+                numel = geom.S * geom.F
+                flip_spec = (float(self.flip_probability), 0, self._draw_flip_positions(numel, x.device))
+            else:
+                flip_spec = (float(self.flip_probability), self._draw_seed())
+            source = StackOptions(geom, flip=flip_spec)
             h = x
         elif flip:
             h = self._apply_bit_flip(PatchFunction.apply(x, geom))

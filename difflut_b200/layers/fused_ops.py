@@ -236,7 +236,8 @@ FEW_NODES = 2960  # fewer nodes than resident warps of the fused backward: paral
 class StackOptions:
     """How a DWNStackFunction reads its input and what it appends: `source` None (fp32 rows), a
     PatchGeometry (image batch, samples = patches) or a PackedInput (bits already packed); `flip`
-    (probability, seed) XORs a Bernoulli mask into the packed input; `head` (k, tau) fuses a following
+    (probability, seed) XORs a Bernoulli mask into the packed input, (probability, 0, positions) flips exactly
+    the given positions of the row-major (samples, features) matrix (None: nothing); `head` (k, tau) fuses a following
     GroupSum(k, tau) (difflut/utils/modules.py:116-163) so that the function returns (B, k) logits."""
 
     def __init__(self, source=None, flip=None, head=None):
@@ -297,7 +298,11 @@ class DWNStackFunction(torch.autograd.Function):
             if flip is not None and flip[0] > 0.0:
                 if packed:
                     bits[0] = bits[0].clone()
-                _native.call("dl_bits_flip_t", bits[0], I, B, Bp, flip[0], flip[1])
+                if len(flip) > 2:  # exact count: flip[2] holds the positions in the row-major (B, I) matrix
+                    if flip[2] is not None:
+                        _native.call("dl_bits_flip_at_t", bits[0], flip[2], flip[2].numel(), I, B, Bp)
+                else:
+                    _native.call("dl_bits_flip_t", bits[0], I, B, Bp, flip[0], flip[1])
             if swz and not interleaved_in:
                 natural = bits[0]
                 bits[0] = torch.empty(I, Ws, device=dev, dtype=torch.int32)

@@ -23,14 +23,61 @@ from .dwn_node import _check_cuda, dwn_mapped_eval
 
 DEFAULT_DWN_STABLE_GRADIENT_SCALE: float = 1.0
 DEFAULT_DWN_STABLE_USE_CUDA: bool = True
-MAX_DWN_STABLE_INPUT_DIM: int = 6  # the weighted transform is kept in the 32-value-per-slot layout
+MAX_DWN_STABLE_INPUT_DIM: int = 16
+FAST_DWN_STABLE_INPUT_DIM: int = 6  # up to here the weighted transform fits the 32-value-per-slot layer kernels
+
+
+class DWNStableWideFunction(torch.autograd.Function):
+    """N nodes with more than 6 inputs on mapped inputs xm (B, N, n), tables (N, O, 2^n) -> (B, N, O).
+
+    Forward: table look-up (`dl_dwn_mapped_fwd`).  Backward: the reference's per-sample sums
+    (dwn_stable_node.py:145-205) as `dl_dwn_stable_mapped_bwd_input` and the address histogram of the
+    output gradient times `gradient_scale`."""
+
+    @staticmethod
+    def forward(ctx, xm, tables, scale):
+        from .. import _native
+
+        xm = xm.contiguous().float()
+        tables = tables.contiguous().float()
+        B, N, n = xm.shape
+        O = tables.shape[1]
+        out = torch.empty(B, N, O, device=xm.device, dtype=torch.float32)
+        with torch.cuda.device(xm.device):
+            _native.call("dl_dwn_mapped_fwd", xm, tables, out, B, N, n, O, 0)
+        ctx.save_for_backward(xm, tables)
+        ctx.scale = scale
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        from .. import _native
+
+        xm, tables = ctx.saved_tensors
+        B, N, n = xm.shape
+        O = tables.shape[1]
+        g = g.contiguous().float()
+        scale = ctx.scale
+        per_node = scale.detach().float().reshape(N).contiguous() if isinstance(scale, torch.Tensor) else None
+        gxm = gt = None
+        with torch.cuda.device(xm.device):
+            if ctx.needs_input_grad[0]:
+                gxm = torch.empty_like(xm)
+                _native.call("dl_dwn_stable_mapped_bwd_input", xm, tables, g, per_node,
+                             1.0 if per_node is not None else float(scale), gxm, B, N, n, O)
+            if ctx.needs_input_grad[1]:
+                gt = torch.empty_like(tables)
+                _native.call("dl_dwn_mapped_bwd", xm, g, None, None, gt, B, N, n, O)
+                gt = gt * (per_node.reshape(N, 1, 1) if per_node is not None else float(scale))
+        return gxm, gt, None
 
 
 def dwn_stable_mapped_forward(xm, tables, gradient_scale):
     """Training forward of N nodes on mapped inputs xm (B, N, n), tables (N, O, 2^n) -> (B, N, O).
 
-    `gradient_scale` is a float or a tensor with one value per node.  Every size runs the feature-major
-    layer kernels under the identity connection map (node j reads columns j*n .. j*n+n-1)."""
+    `gradient_scale` is a float or a tensor with one value per node.  Up to 6 inputs per node the
+    feature-major layer kernels run under the identity connection map (node j reads columns
+    j*n .. j*n+n-1); wider nodes take the per-sample kernels of `DWNStableWideFunction`."""
     from ..layers.fused_ops import DWNLayerFunction
     from .dwn_node import _identity_plan
 
@@ -39,6 +86,8 @@ def dwn_stable_mapped_forward(xm, tables, gradient_scale):
     O = tables.shape[1]
     if n > MAX_DWN_STABLE_INPUT_DIM:
         raise ValueError(f"DWNStableNode supports input_dim <= {MAX_DWN_STABLE_INPUT_DIM}, got {n}")
+    if n > FAST_DWN_STABLE_INPUT_DIM:
+        return DWNStableWideFunction.apply(xm, tables, gradient_scale)
     if isinstance(gradient_scale, torch.Tensor):
         gradient_scale = gradient_scale.detach().float().reshape(N).repeat_interleave(O)
     plan = _identity_plan(N, n, O, xm.device)

@@ -21,7 +21,44 @@ from .base_node import BaseNode
 from .dwn_node import _check_cuda, dwn_mapped_eval
 
 DEFAULT_HYBRID_USE_CUDA: bool = True
-MAX_HYBRID_INPUT_DIM: int = 6  # the backward keeps the 2^n table gradient of a node in registers
+MAX_HYBRID_INPUT_DIM: int = 16
+FAST_HYBRID_INPUT_DIM: int = 6  # up to here the layer kernel keeps a node's 2^n table gradient in registers
+
+
+class HybridWideFunction(torch.autograd.Function):
+    """N hybrid nodes with more than 6 inputs on mapped inputs xm (B, N, n), tables (N, O, 2^n) -> (B, N, O).
+
+    Forward: table look-up (`dl_dwn_mapped_fwd`); backward: the probabilistic gradient of
+    hybrid_node.py:160-224 as `dl_hybrid_mapped_bwd`."""
+
+    @staticmethod
+    def forward(ctx, xm, tables):
+        from .. import _native
+
+        xm = xm.contiguous().float()
+        tables = tables.contiguous().float()
+        B, N, n = xm.shape
+        O = tables.shape[1]
+        out = torch.empty(B, N, O, device=xm.device, dtype=torch.float32)
+        with torch.cuda.device(xm.device):
+            _native.call("dl_dwn_mapped_fwd", xm, tables, out, B, N, n, O, 0)
+        ctx.save_for_backward(xm, tables)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        from .. import _native
+
+        xm, tables = ctx.saved_tensors
+        B, N, n = xm.shape
+        O = tables.shape[1]
+        g = g.contiguous().float()
+        gxm = torch.empty_like(xm) if ctx.needs_input_grad[0] else None
+        gt = torch.empty_like(tables) if ctx.needs_input_grad[1] else None
+        if gxm is not None or gt is not None:
+            with torch.cuda.device(xm.device):
+                _native.call("dl_hybrid_mapped_bwd", xm, tables, g, gxm, gt, B, N, n, O)
+        return gxm, gt
 
 
 def hybrid_mapped_forward(xm, tables):
@@ -34,6 +71,8 @@ def hybrid_mapped_forward(xm, tables):
     O = tables.shape[1]
     if n > MAX_HYBRID_INPUT_DIM:
         raise ValueError(f"HybridNode supports input_dim <= {MAX_HYBRID_INPUT_DIM}, got {n}")
+    if n > FAST_HYBRID_INPUT_DIM:
+        return HybridWideFunction.apply(xm, tables)
     plan = _identity_plan(N, n, O, xm.device)
     return HybridLayerFunction.apply(xm.reshape(B, N * n), tables, plan).reshape(B, N, O)
 

@@ -213,6 +213,25 @@ int dl_dwn_prepare_full(const float* tables, float* efd_full, int64_t NO, int64_
 int dl_dwn_mapped_bwd(const float* xm, const float* g, const float* efd_full, float* gxm,
                       float* gt, int64_t B, int64_t N, int64_t n, int64_t O, dl_stream_t stream);
 
+/* ------------------------------------------------------------------ DWNStable / Hybrid nodes, 6 < n <= 16
+ * The n <= 6 forms of these nodes run in the layer kernels (dl_dwn_prepare_weighted + dl_dwn_bwd_*,
+ * dl_hybrid_bwd_t).  For wider nodes the forward is dl_dwn_mapped_fwd on the sigmoid-ed tables and the
+ * backward restates the reference's per-sample sums on materialised inputs xm (B, N, n):
+ *   dl_dwn_stable_mapped_bwd_input  gxm[b,j,i] = scale_j * sum_o g[b,j,o] * sum_k (+-1) table[j,o,k] /
+ *                                   (hamming(addr, k without bit i) + 1), sign by bit i of k
+ *                                   (difflut/nodes/dwn_stable_node.py:170-202); scale_per_node (N) or NULL
+ *                                   and the scalar.  The table gradient is dl_dwn_mapped_bwd's histogram
+ *                                   times the scale.
+ *   dl_hybrid_mapped_bwd            P[a] = prod_i (a_i ? x_i : 1 - x_i); gt[j,o,a] = sum_b P[a] g[b,j,o];
+ *                                   gxm[b,j,i] = sum_o g sum_a table[j,o,a] P[a] (a_i - x_i) /
+ *                                   (x_i (1 - x_i) + 1e-8)  (difflut/nodes/hybrid_node.py:160-224).
+ *                                   gt (N, O, 2^n) is overwritten (fp32 atomics: not bit-reproducible).    */
+int dl_dwn_stable_mapped_bwd_input(const float* xm, const float* tables, const float* g,
+                                   const float* scale_per_node, float scale, float* gxm, int64_t B, int64_t N,
+                                   int64_t n, int64_t O, dl_stream_t stream);
+int dl_hybrid_mapped_bwd(const float* xm, const float* tables, const float* g, float* gxm, float* gt, int64_t B,
+                         int64_t N, int64_t n, int64_t O, dl_stream_t stream);
+
 /* ------------------------------------------------------------------ Probabilistic node
  * Replaces probabilistic_cuda.forward(input, raw_weights, temperature) / .backward(...)
  * (difflut/nodes/cuda/probabilistic_cuda.cpp:44-49) for a whole layer, fused with the
@@ -347,7 +366,12 @@ int dl_dwn_bwd_fused_s(const uint8_t* addr_up, const float* g_up, int64_t gdiv_u
  * (difflut/layers/base_layer.py:149-264, 266-339; torch code in the reference).
  *   dl_flip_rows     out[i] = 1 - x[i] with probability p, else x[i] (no gradient: the caller's backward
  *                    is the identity).  Bernoulli per element from a counter-based generator keyed by
- *                    (seed, i); the reference's exact-count variant for p < 0.05 is not reproduced.
+ *                    (seed, i).  This is the reference's rule for p >= 0.05 (base_layer.py:189-224).
+ *   dl_flip_at       the reference's rule below p = 0.05 (base_layer.py:226-262): exactly `flips` positions
+ *                    flip, given by the caller (the first int(count * p) entries of a random permutation of
+ *                    the `count` positions, int64, distinct); out = x elsewhere.  out must not alias x.
+ *   dl_bits_flip_at_t the same on packed feature-major bits: position e of the row-major (B, F) matrix is
+ *                    sample e / F, feature e % F; applied in place with atomic XORs.
  *   dl_bits_flip_t   the same decision per element (f, b) of an (F, B) matrix, applied in place as an XOR to
  *                    packed feature-major bits [F][Bp/32] (flips `x >= 0.5`; differs from thresholding
  *                    1 - x only at x == 0.5 exactly).
@@ -358,6 +382,10 @@ int dl_flip_rows(const float* x, float* out, int64_t count, float probability, i
                  dl_stream_t stream);
 int dl_bits_flip_t(uint32_t* bits_t, int64_t F, int64_t B, int64_t Bp, float probability, int64_t seed,
                    dl_stream_t stream);
+int dl_flip_at(const float* x, float* out, const int64_t* positions, int64_t count, int64_t flips,
+               dl_stream_t stream);
+int dl_bits_flip_at_t(uint32_t* bits_t, const int64_t* positions, int64_t flips, int64_t F, int64_t B, int64_t Bp,
+                      dl_stream_t stream);
 int64_t dl_grad_rescale_scratch_doubles(void);
 int dl_grad_rescale(const float* g, float* out, int64_t rows, int64_t cols, int per_row, float target_std,
                     int subtract_mean, float eps, double* scratch, dl_stream_t stream);

@@ -437,6 +437,36 @@ def grouped_mapping(n_groups: int, input_size: int, output_trees: int, luts_per_
 
 
 # ----------------------------------------------------------------------------------
+# Layer training options (LUTLayerMixin)
+# ----------------------------------------------------------------------------------
+
+
+def grad_rescale(g: torch.Tensor, mode: str, target_std: float, subtract_mean: bool, eps: float) -> torch.Tensor:
+    """Gradient stabilisation, difflut/layers/base_layer.py:266-339: optionally subtract the mean, then
+    multiply by sqrt(target_std / (mean(g^2) + eps)); statistics over the whole tensor ("layerwise") or per
+    row ("batchwise")."""
+    w = g.clone()
+    dims = None if mode == "layerwise" else 1
+    if subtract_mean:
+        w = w - (w.mean() if dims is None else w.mean(dim=1, keepdim=True))
+    var = w.pow(2).mean() if dims is None else w.pow(2).mean(dim=1, keepdim=True)
+    return w * torch.sqrt(torch.tensor(float(target_std)) / (var + eps))
+
+
+def flip_positions_sparse(numel: int, probability: float) -> torch.Tensor:
+    """The positions the reference flips when the probability is below 0.05 (base_layer.py:226-262): the first
+    int(numel * p) entries of torch.randperm(numel), drawn from the global generator of the calling device."""
+    return torch.randperm(numel)[: int(numel * probability)]
+
+
+def flip_apply(x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+    """x with 1 - x at `positions` of its flattened view (base_layer.py:249-260)."""
+    out = x.clone().reshape(-1)
+    out[positions] = 1.0 - out[positions]
+    return out.view_as(x)
+
+
+# ----------------------------------------------------------------------------------
 # Whole-network helpers (configs of the benchmark)
 # ----------------------------------------------------------------------------------
 

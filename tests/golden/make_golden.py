@@ -373,6 +373,34 @@ def main():
         out["k4_tau2"] = _np(GroupSum(k=4, tau=2.0, use_randperm=False)(xg))  # padded: 23 -> 24
         out["k1_tau1"] = _np(GroupSum(k=1, tau=1.0, use_randperm=False)(xg))
     np.savez_compressed(os.path.join(HERE, "groupsum.npz"), **out)
+
+    # ---------------------------------------------------------------- layer training options (LUTLayerMixin)
+    # gradient rescaling (base_layer.py:266-339) on fixed gradients, and the two bit-flip rules
+    # (base_layer.py:149-264) under a fixed CPU generator seed
+    from difflut.layers import LayerConfig
+
+    out = {}
+    g = torch.Generator().manual_seed(21)
+    grads = {"small": torch.randn(5, 7, generator=g) * 3.0 + 0.7, "wide": torch.randn(12, 515, generator=g) * 0.02 - 0.01}
+    for name, gr in grads.items():
+        out[f"g_{name}"] = _np(gr)
+    out["rescale_params"] = np.array([2.0, 1e-6])  # target_std, epsilon
+    for mode in ("layerwise", "batchwise"):
+        for subtract in (False, True):
+            layer = RandomLayer(12, 4, DWNNode, NodeConfig(input_dim=3, output_dim=1),
+                                layer_config=LayerConfig(grad_stabilization=mode, grad_target_std=2.0,
+                                                         grad_subtract_mean=subtract, grad_epsilon=1e-6)).train()
+            for name, gr in grads.items():
+                out[f"rescaled_{mode}_{int(subtract)}_{name}"] = _np(layer._apply_gradient_stabilization(gr.clone()))
+    xf = torch.rand(40, 50, generator=g)
+    out["flip_x"] = _np(xf)
+    for tag, p in (("sparse", 0.03), ("dense", 0.3)):
+        layer = RandomLayer(50, 4, DWNNode, NodeConfig(input_dim=3, output_dim=1),
+                            layer_config=LayerConfig(flip_probability=p)).train()
+        torch.manual_seed(77)
+        out[f"flip_{tag}_out"] = _np(layer._apply_bit_flip(xf.clone()))
+        out[f"flip_{tag}_p"] = np.array([p])
+    np.savez_compressed(os.path.join(HERE, "layer_options.npz"), **out)
     print("golden fixtures written to", HERE)
 
 

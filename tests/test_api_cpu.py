@@ -245,7 +245,8 @@ def test_new_node_types_registered_and_stacked():
     assert "nodes.0.binary_combinations" in hybrid.state_dict()
     for cls in (DWNStableNode, HybridNode):
         with pytest.raises(ValueError):
-            cls(input_dim=7, output_dim=1)
+            cls(input_dim=17, output_dim=1)
+        assert cls(input_dim=9, output_dim=2).raw_luts.shape == (2, 512)  # wider than the layer kernels' 6 inputs
         node = cls(input_dim=4, output_dim=1)
         assert node.raw_luts.shape == (1, 16) and float(node.raw_luts.abs().max()) < 1.0  # 0.1 * randn
 
@@ -329,3 +330,25 @@ def test_dwn_network_refuses_layer_options_it_would_drop():
     for kw in ({"flip_probability": 0.2}, {"grad_stabilization": "batchwise"}):
         with pytest.raises(ValueError, match="flip_probability / grad_stabilization"):
             DWNNetwork(enc, [RandomLayer(24, 10, DWNNode, cfg, seed=1, **kw)], gs)
+
+
+def test_layer_option_host_paths_match_reference(golden):
+    """The mixin's host-side branches (CPU tensors) reproduce the reference's outputs: both flip rules under the
+    same generator seed, bit for bit, and the gradient rescaling."""
+    from difflut_b200.layers import LayerConfig
+
+    g = golden("layer_options")
+    x = torch.from_numpy(g["flip_x"])
+    cfg = NodeConfig(input_dim=3, output_dim=1)
+    for tag in ("sparse", "dense"):
+        layer = RandomLayer(50, 4, DWNNode, cfg, layer_config=LayerConfig(flip_probability=float(g[f"flip_{tag}_p"][0]))).train()
+        torch.manual_seed(77)
+        assert torch.equal(layer._apply_bit_flip(x.clone()), torch.from_numpy(g[f"flip_{tag}_out"])), tag
+    for mode in ("layerwise", "batchwise"):
+        for subtract in (0, 1):
+            layer = RandomLayer(12, 4, DWNNode, cfg,
+                                layer_config=LayerConfig(grad_stabilization=mode, grad_target_std=2.0,
+                                                         grad_subtract_mean=bool(subtract), grad_epsilon=1e-6)).train()
+            for name in ("small", "wide"):
+                got = layer._apply_gradient_stabilization(torch.from_numpy(g[f"g_{name}"]))
+                torch.testing.assert_close(got, torch.from_numpy(g[f"rescaled_{mode}_{subtract}_{name}"]), rtol=1e-6, atol=1e-7)

@@ -267,24 +267,61 @@ def test_flip_kernels_and_fused_conv_flip(dev):
 
 @pytest.mark.parametrize("mode", ["layerwise", "batchwise"])
 @pytest.mark.parametrize("subtract", [False, True])
-def test_gradient_rescale_matches_reference_formula(dev, mode, subtract):
-    """difflut/layers/base_layer.py:266-339 restated with torch ops on the CPU vs dl_grad_rescale."""
+def test_gradient_rescale_matches_reference(golden, dev, mode, subtract):
+    """dl_grad_rescale against outputs of the reference's _apply_gradient_stabilization
+    (difflut/layers/base_layer.py:266-339) and, on larger shapes, against the oracle's restatement of it."""
     from difflut_b200.layers import LayerConfig, RandomLayer
     from difflut_b200.nodes import DWNNode, NodeConfig
 
+    fx = golden("layer_options")
+    target, eps = (float(v) for v in fx["rescale_params"])
     layer = RandomLayer(12, 4, DWNNode, NodeConfig(input_dim=3, output_dim=1),
-                        layer_config=LayerConfig(grad_stabilization=mode, grad_target_std=2.0,
-                                                 grad_subtract_mean=subtract, grad_epsilon=1e-6)).train()
+                        layer_config=LayerConfig(grad_stabilization=mode, grad_target_std=target,
+                                                 grad_subtract_mean=subtract, grad_epsilon=eps)).train()
+    for name in ("small", "wide"):
+        got = layer._apply_gradient_stabilization(T(fx[f"g_{name}"]).to(dev))
+        torch.testing.assert_close(got.cpu(), T(fx[f"rescaled_{mode}_{int(subtract)}_{name}"]), rtol=1e-5, atol=1e-7)
     gen = torch.Generator().manual_seed(3)
-    for shape in ((5, 7), (300, 1000), (64, 4097)):
+    for shape in ((300, 1000), (64, 4097)):
         g = torch.randn(shape, generator=gen) * 3.0 + 0.7
-        w = g.clone()
-        dims = None if mode == "layerwise" else 1
-        if subtract:
-            w = w - (w.mean() if dims is None else w.mean(dim=1, keepdim=True))
-        var = w.pow(2).mean() if dims is None else w.pow(2).mean(dim=1, keepdim=True)
-        ref = w * torch.sqrt(torch.tensor(2.0) / (var + 1e-6))
+        ref = O.grad_rescale(g, mode, target, subtract, eps)
         got = layer._apply_gradient_stabilization(g.to(dev))
         torch.testing.assert_close(got.cpu(), ref, rtol=1e-5, atol=1e-6)
     layer.eval()
     assert layer._apply_gradient_stabilization(g.to(dev)) is not None
+
+
+def test_exact_count_flip_below_five_percent(dev):
+    """Below p = 0.05 the reference flips exactly int(numel * p) distinct positions, the head of a random
+    permutation drawn on the tensor's device (difflut/layers/base_layer.py:226-262): the layer draws the same
+    permutation from torch's CUDA generator, so the flipped positions can be re-derived from the seed."""
+    from difflut_b200 import _native
+    from difflut_b200.layers import LayerConfig, RandomLayer
+    from difflut_b200.nodes import DWNNode, NodeConfig
+
+    gen = torch.Generator().manual_seed(5)
+    x = torch.rand(300, 77, generator=gen).to(dev)
+    p = 0.03
+    layer = RandomLayer(77, 4, DWNNode, NodeConfig(input_dim=3, output_dim=1),
+                        layer_config=LayerConfig(flip_probability=p)).to(dev).train()
+    torch.manual_seed(123)
+    xg = x.clone().requires_grad_(True)
+    out = layer._apply_bit_flip(xg)
+    torch.manual_seed(123)
+    want = torch.randperm(x.numel(), device=dev)[: int(x.numel() * p)]
+    assert torch.equal(out.detach().cpu(), O.flip_apply(x.cpu(), want.cpu()))
+    assert int((out.detach() != x).sum()) == int(x.numel() * p)
+    out.sum().backward()
+    assert torch.equal(xg.grad, torch.ones_like(x))  # the flip carries no gradient
+    # too few elements for a single flip: the input comes back untouched
+    tiny = torch.rand(2, 7, device=dev)
+    assert layer._apply_bit_flip(tiny) is tiny
+    # packed variant: the same positions of the row-major (B, F) matrix, applied to feature-major bits
+    B, F = 300, 77
+    Bp = _native.padded_batch(B)
+    bits = torch.empty(F, Bp // 32, dtype=torch.int32, device=dev)
+    _native.call("dl_pack_rows_to_t", x, bits, B, F, Bp, 0.5)
+    _native.call("dl_bits_flip_at_t", bits, want, want.numel(), F, B, Bp)
+    ref_bits = torch.empty_like(bits)
+    _native.call("dl_pack_rows_to_t", out.detach().contiguous(), ref_bits, B, F, Bp, 0.5)
+    assert torch.equal(bits, ref_bits)

@@ -222,12 +222,15 @@ def test_hybrid_layer_matches_reference(golden, dev, tag):
     assert torch.equal(other.raw_luts, layer.raw_luts)
 
 
-def test_hybrid_standalone_node_vs_oracle(dev):
+@pytest.mark.parametrize("n,O_", [(5, 2), (8, 1), (9, 2)])
+def test_hybrid_standalone_node_vs_oracle(dev, n, O_):
+    """n <= 6: the layer kernel; wider nodes: the per-sample kernel on materialised inputs."""
     from difflut_b200.nodes import HybridNode
 
     gen = torch.Generator().manual_seed(31)
-    B, n, O_ = 70, 5, 2
+    B = 70
     x = torch.rand(B, n, generator=gen)
+    x[0, :] = (torch.rand(n, generator=gen) > 0.5).float()  # exactly binary inputs: the 1e-8 guard decides
     node = HybridNode(input_dim=n, output_dim=O_).to(dev)
     tab = torch.sigmoid(node.raw_luts.detach()).cpu()
     xg = x.to(dev).requires_grad_(True)
@@ -239,10 +242,10 @@ def test_hybrid_standalone_node_vs_oracle(dev):
     close_normwise(xg.grad.cpu(), gxm.squeeze(1), "xg.grad.cpu()")
     close_normwise(node.raw_luts.grad.cpu(), gl.squeeze(0) * tab * (1 - tab), "node.raw_luts.grad.cpu()")
     with pytest.raises(ValueError):
-        HybridNode(input_dim=7, output_dim=1)
+        HybridNode(input_dim=17, output_dim=1)
 
 
-@pytest.mark.parametrize("n,O_", [(1, 1), (3, 2), (6, 1)])
+@pytest.mark.parametrize("n,O_", [(1, 1), (3, 2), (6, 1), (8, 1), (10, 2)])
 def test_dwn_stable_standalone_node_vs_oracle(dev, n, O_):
     from difflut_b200.nodes import DWNStableNode
 
@@ -267,7 +270,39 @@ def test_dwn_stable_standalone_node_vs_oracle(dev, n, O_):
     xb = (x >= 0.5).float()
     assert torch.equal(node(xb.to(dev)).cpu(), O.dwn_forward_eval(xb.unsqueeze(1), tab.unsqueeze(0)).squeeze(1))
     with pytest.raises(ValueError):
-        DWNStableNode(input_dim=7, output_dim=1)
+        DWNStableNode(input_dim=17, output_dim=1)
+
+
+@pytest.mark.parametrize("kind", ["dwn_stable", "hybrid"])
+def test_wide_node_layers_vs_oracle(dev, kind):
+    """RandomLayer with 8-input DWNStable / Hybrid nodes (beyond the 6 inputs of the layer kernels): forward,
+    eval and both gradients through the gather against the oracle."""
+    from difflut_b200.nodes import DWNStableNode, HybridNode
+
+    gen = torch.Generator().manual_seed(77)
+    B, I, N, n, O_ = 40, 30, 9, 8, 2
+    node = DWNStableNode if kind == "dwn_stable" else HybridNode
+    extra = {"gradient_scale": 1.1} if kind == "dwn_stable" else None
+    layer = _layer(dev, I, N, n, O_, node, None, extra)
+    idx = layer._mapping_indices.cpu()
+    x = torch.rand(B, I, generator=gen)
+    tab = torch.sigmoid(layer.raw_luts.detach()).cpu()
+    xg = x.to(dev).requires_grad_(True)
+    layer.train()
+    y = layer(xg)
+    xm = O.gather_mapping(x, idx)
+    assert torch.equal(y.cpu(), O.dwn_forward(xm, tab).reshape(B, -1))
+    gy = torch.randn(B, N * O_, generator=gen)
+    y.backward(gy.to(dev))
+    if kind == "dwn_stable":
+        gxm, gl = O.dwn_stable_backward(xm, tab, gy.view(B, N, O_), 1.1)
+    else:
+        gxm, gl = O.hybrid_backward(xm, tab, gy.view(B, N, O_))
+    close_normwise(xg.grad.cpu(), O.gather_mapping_backward(gxm, idx, I), f"{kind} n=8 layer: input gradient")
+    close_normwise(layer.raw_luts.grad.cpu(), gl * tab * (1 - tab), f"{kind} n=8 layer: table gradient")
+    layer.eval()
+    xb = (x >= 0.5).float()
+    assert torch.equal(layer(xb.to(dev)).cpu(), O.dwn_forward_eval(O.gather_mapping(xb, idx), tab).reshape(B, -1))
 
 
 @pytest.mark.parametrize("n,O_", [(1, 1), (3, 2), (6, 1), (8, 1), (10, 2)])
@@ -720,6 +755,10 @@ def test_thermo_pack_interleaved_all_kernel_variants(dev, B, F):
     x = torch.rand(B, F, generator=gen)
     thr = torch.sort(torch.rand(F, Tb, generator=gen), dim=1).values.contiguous()
     x[0, :] = thr[:, 0]  # equality with a threshold encodes as 0 (strict comparison)
+    # values for which a comparison and a subtraction's sign could disagree if handled carelessly
+    thr[0, 0] = -0.0
+    x[1, 0], x[2, 0], x[3, 0], x[4, 0] = 0.0, -0.0, float("nan"), float("inf")
+    x[5, 0], x[6, 0] = -float("inf"), 1e-42  # a denormal above zero
     Bp = _native.padded_batch(B)
     Ws = int(_native.lib().dl_swizzled_words(Bp))
     nat = torch.empty(F * Tb, Bp // 32, dtype=torch.int32, device=dev)

@@ -173,8 +173,11 @@ def test_exchange_kernel_with_one_rank_equals_adam_step():
             _native.call("dl_p2p_exchange_adam", ctypes.addressof(tg), ctypes.addressof(tp), ctypes.addressof(tf),
                          m, v, state, ctrl, 0, split, 0, 1, 0, 1, 1e-2, 0.9, 0.999, 1e-8, 1.0, 200)
             torch.cuda.synchronize()
-            assert torch.equal(params, ref_p) and torch.equal(m, ref_m) and torch.equal(v, ref_v)
-            assert torch.equal(state, ref_state)
+            assert torch.equal(state, ref_state), (step, state.tolist(), ref_state.tolist())
+            for name, got, want in (("m", m, ref_m), ("v", v, ref_v), ("params", params, ref_p)):
+                bad = (got != want).nonzero().flatten()
+                assert bad.numel() == 0, (f"step {step}: {name} differs at {bad.numel()} places, first {int(bad[0])}: "
+                                          f"{float(got[bad[0]])!r} vs {float(want[bad[0]])!r}")
     c = ctrl.tolist()
     assert c[0] == 0 and c[1] == 3 and c[3] == 3 and c[2] == 0 and c[4] == 0  # status, epochs, counters reset
 

@@ -306,3 +306,24 @@ def test_oracle_adjoint_and_linearity_properties():
     packed = O.pack_bits_feature_major(bits)
     unpacked = ((packed[:, :, None] >> np.arange(32, dtype=np.uint32)[None, None, :]) & 1).reshape(9, -1)[:, :70].T
     assert np.array_equal(unpacked, bits.numpy().astype(np.uint32))
+
+
+def test_layer_options_match_reference(golden):
+    """Gradient rescaling and the two bit-flip rules against outputs of the reference's LUTLayerMixin."""
+    g = golden("layer_options")
+    target, eps = (float(v) for v in g["rescale_params"])
+    for mode in ("layerwise", "batchwise"):
+        for subtract in (0, 1):
+            for name in ("small", "wide"):
+                got = O.grad_rescale(T(g[f"g_{name}"]), mode, target, bool(subtract), eps)
+                torch.testing.assert_close(got, T(g[f"rescaled_{mode}_{subtract}_{name}"]), rtol=1e-6, atol=1e-7)
+    x = T(g["flip_x"])
+    torch.manual_seed(77)
+    pos = O.flip_positions_sparse(x.numel(), float(g["flip_sparse_p"][0]))
+    assert pos.numel() == int(x.numel() * 0.03)
+    assert torch.equal(O.flip_apply(x, pos), T(g["flip_sparse_out"]))
+    # dense rule: about p of the entries flip, and a flipped entry holds exactly 1 - x
+    dense = T(g["flip_dense_out"])
+    changed = dense != x
+    assert 0.2 < float(changed.float().mean()) < 0.4
+    assert torch.equal(dense[changed], (x + (1.0 - 2.0 * x))[changed])
