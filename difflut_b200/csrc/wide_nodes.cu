@@ -48,8 +48,9 @@ __global__ void stable_wide_bwd_input_kernel(const float* __restrict__ xm, const
     }
 }
 
-// thread per (b, j): P[a] = prod_i (a_i ? x_i : 1 - x_i) in fp32, in input order (torch.prod over the input
-// dimension); table gradient by atomics (gt zeroed by the entry point), input gradient accumulated in double.
+// thread per (b, j): P[a] = prod_i (a_i ? x_i : 1 - x_i); table gradient by fp32 atomics (gt zeroed by the entry
+// point), input gradient in double throughout: with tables that vary little the 2^n signed terms of an input
+// gradient cancel almost completely, and the rounding of fp32 terms would show at the 1e-5 level.
 __global__ void hybrid_wide_bwd_kernel(const float* __restrict__ xm, const float* __restrict__ tables,
                                        const float* __restrict__ g, float* __restrict__ gxm, float* __restrict__ gt,
                                        int64_t B, int64_t N, int n, int O) {
@@ -58,25 +59,23 @@ __global__ void hybrid_wide_bwd_kernel(const float* __restrict__ xm, const float
     for (int64_t bj = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; bj < total;
          bj += (int64_t)gridDim.x * blockDim.x) {
         const int64_t j = bj % N;
-        float x[WIDE_MAX_N], inv[WIDE_MAX_N];
-        double gx[WIDE_MAX_N];
+        double x[WIDE_MAX_N], inv[WIDE_MAX_N], gx[WIDE_MAX_N];
         for (int i = 0; i < WIDE_MAX_N; ++i) {
-            x[i] = i < n ? xm[bj * n + i] : 0.f;
-            inv[i] = 1.0f / (x[i] * (1.0f - x[i]) + 1e-8f);
+            x[i] = i < n ? (double)xm[bj * n + i] : 0.0;
+            inv[i] = 1.0 / (x[i] * (1.0 - x[i]) + 1e-8);
             gx[i] = 0.0;
         }
         for (int a = 0; a < L; ++a) {
-            float p = 1.0f;
-            for (int i = 0; i < n; ++i) p *= ((a >> i) & 1) ? x[i] : 1.0f - x[i];
-            float lg = 0.f;  // sum_o table[j,o,a] * g[b,j,o]
+            double p = 1.0;
+            for (int i = 0; i < n; ++i) p *= ((a >> i) & 1) ? x[i] : 1.0 - x[i];
+            double lg = 0.0;  // sum_o table[j,o,a] * g[b,j,o]
             for (int o = 0; o < O; ++o) {
                 const float go = g[bj * O + o];
-                lg += __ldg(tables + (j * O + o) * (int64_t)L + a) * go;
-                if (gt != nullptr && p != 0.f) atomicAdd(gt + (j * O + o) * (int64_t)L + a, p * go);
+                lg += (double)__ldg(tables + (j * O + o) * (int64_t)L + a) * (double)go;
+                if (gt != nullptr && p != 0.0) atomicAdd(gt + (j * O + o) * (int64_t)L + a, (float)(p * (double)go));
             }
-            if (gxm != nullptr && p != 0.f && lg != 0.f)
-                for (int i = 0; i < n; ++i)
-                    gx[i] += (double)(p * ((((a >> i) & 1) ? 1.0f : 0.0f) - x[i]) * inv[i]) * (double)lg;
+            if (gxm != nullptr && p != 0.0 && lg != 0.0)
+                for (int i = 0; i < n; ++i) gx[i] += p * ((((a >> i) & 1) ? 1.0 : 0.0) - x[i]) * inv[i] * lg;
         }
         if (gxm != nullptr)
             for (int i = 0; i < n; ++i) gxm[bj * n + i] = (float)gx[i];

@@ -238,9 +238,15 @@ def test_hybrid_standalone_node_vs_oracle(dev, n, O_):
     assert torch.equal(y.cpu(), O.dwn_forward(x.unsqueeze(1), tab.unsqueeze(0)).squeeze(1))
     gy = torch.randn(B, O_, generator=gen)
     y.backward(gy.to(dev))
-    gxm, gl = O.hybrid_backward(x.unsqueeze(1), tab.unsqueeze(0), gy.unsqueeze(1))
-    close_normwise(xg.grad.cpu(), gxm.squeeze(1), "xg.grad.cpu()")
-    close_normwise(node.raw_luts.grad.cpu(), gl.squeeze(0) * tab * (1 - tab), "node.raw_luts.grad.cpu()")
+    if n <= 6:
+        gxm, gl = O.hybrid_backward(x.unsqueeze(1), tab.unsqueeze(0), gy.unsqueeze(1))
+    else:
+        # 2^n terms of mixed sign per input gradient: in fp32 the reference's own sum is only good to about 1e-5
+        # here, so the wide kernel (double accumulation) is held to the formula evaluated in float64
+        gxm, gl = O.hybrid_backward(x.double().unsqueeze(1), tab.double().unsqueeze(0), gy.double().unsqueeze(1))
+        gxm, gl = gxm.float(), gl.float()
+    close_normwise(xg.grad.cpu(), gxm.squeeze(1), f"hybrid node n={n}: input gradient")
+    close_normwise(node.raw_luts.grad.cpu(), gl.squeeze(0) * tab * (1 - tab), f"hybrid node n={n}: table gradient")
     with pytest.raises(ValueError):
         HybridNode(input_dim=17, output_dim=1)
 
@@ -296,8 +302,9 @@ def test_wide_node_layers_vs_oracle(dev, kind):
     y.backward(gy.to(dev))
     if kind == "dwn_stable":
         gxm, gl = O.dwn_stable_backward(xm, tab, gy.view(B, N, O_), 1.1)
-    else:
-        gxm, gl = O.hybrid_backward(xm, tab, gy.view(B, N, O_))
+    else:  # the formula in float64 (see test_hybrid_standalone_node_vs_oracle)
+        gxm, gl = O.hybrid_backward(xm.double(), tab.double(), gy.view(B, N, O_).double())
+        gxm, gl = gxm.float(), gl.float()
     close_normwise(xg.grad.cpu(), O.gather_mapping_backward(gxm, idx, I), f"{kind} n=8 layer: input gradient")
     close_normwise(layer.raw_luts.grad.cpu(), gl * tab * (1 - tab), f"{kind} n=8 layer: table gradient")
     layer.eval()
