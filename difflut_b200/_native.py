@@ -71,11 +71,13 @@ SIGNATURES = {
     "dl_grad_rescale": "ppllififp s",
     "dl_p2p_barrier": "pllpl s",
     "dl_p2p_reduce_adam": "pppppplllfffff s",
-    "dl_p2p_exchange_adam": "pppppppllllllfffffl s",
+    "dl_p2p_exchange_adam": "ppppppplllllllfffffl s",
     "dl_popcount_groupsum_t": "ppllll s",
     "dl_ce_t": "pppppllll s",
     "dl_loss_sum": "ppll s",
     "dl_adam_step": "ppppplfffff s",
+    "dl_adam_advance": "pff s",
+    "dl_adam_apply": "ppppplfffff s",
     "dl_adam_step_groups": "ppllpppplfffff s",
 }
 

@@ -216,6 +216,25 @@ DL_EXPORT int dl_adam_step(float* p, const float* g, float* m, float* v, double*
     return dl_launch_status();
 }
 
+DL_EXPORT int dl_adam_advance(double* state, float beta1, float beta2, dl_stream_t stream) {
+    DL_REQUIRE(state);
+    adam_advance_kernel<<<1, 1, 0, dl_cast(stream)>>>(state, (double)beta1, (double)beta2);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_adam_apply(float* p, const float* g, float* m, float* v, const double* state, int64_t count,
+                            float lr, float beta1, float beta2, float eps, float gscale, dl_stream_t stream) {
+    DL_REQUIRE(p && g && m && v && state && count > 0);
+    DL_REQUIRE_ALIGNED(p, 16);
+    DL_REQUIRE_ALIGNED(g, 16);
+    DL_REQUIRE_ALIGNED(m, 16);
+    DL_REQUIRE_ALIGNED(v, 16);
+    const int64_t blocks = dl_min64(dl_ceil_div(dl_ceil_div(count, 4), 256), (int64_t)DL_NUM_SMS * 16);
+    adam_kernel<<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(p, g, m, v, state, count, lr, beta1, beta2,
+                                                             eps, gscale);
+    return dl_launch_status();
+}
+
 DL_EXPORT int dl_adam_step_groups(float* p, const float* partial, int64_t stride, int64_t groups, float* g_out,
                                   float* m, float* v, double* state, int64_t count, float lr, float beta1,
                                   float beta2, float eps, float gscale, dl_stream_t stream) {

@@ -132,7 +132,13 @@ __device__ __forceinline__ bool wait_flag(const int* flag, int epoch, uint64_t t
     return true;
 }
 
-__global__ void __launch_bounds__(256)
+// THREADS = 64: a CTA of two warps with at most 64 registers per thread fits into what five resident CTAs of
+// the fused backward kernel leave free on an SM (4096 registers), so an exchange that overlaps a backward
+// kernel gets its CTAs scheduled at once instead of waiting for that kernel to end.  THREADS = 256: for an
+// exchange that has the GPU to itself.  Two 16-byte pieces per thread and iteration keep several peer loads
+// in flight per thread.
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS, THREADS == 64 ? 16 : 2)
 p2p_exchange_adam_kernel(PeerTable grads, PeerTable params, PeerTable flags, float* __restrict__ m,
                          float* __restrict__ v, double* __restrict__ state, int* __restrict__ ctrl, int64_t lo,
                          int64_t hi, int64_t mlo, int ch, int advance, int rank, int world, float lr, float b1,
@@ -165,27 +171,37 @@ p2p_exchange_adam_kernel(PeerTable grads, PeerTable params, PeerTable flags, flo
     const float step_size = (float)((double)lr / bc1);
     const float bc2_sqrt = (float)sqrt(bc2);
     // [lo, hi) in float4 units of the flat vector; this rank's moments of the slice start at mlo
-    for (int64_t i = lo + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < hi;
-         i += (int64_t)gridDim.x * blockDim.x) {
-        float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int64_t stride = (int64_t)gridDim.x * THREADS;
+    for (int64_t i0 = lo + (int64_t)blockIdx.x * THREADS + threadIdx.x; i0 < hi; i0 += 2 * stride) {
+        const int64_t i1 = i0 + stride;
+        const bool two = i1 < hi;
+        float4 g0 = make_float4(0.f, 0.f, 0.f, 0.f), g1 = g0;
 #pragma unroll
         for (int p = 0; p < DL_MAX_PEERS; ++p) {
-            if (p < world) {
-                const float4 t = __ldcg(static_cast<const float4*>(grads.ptr[p]) + i);
-                g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
+            if (p < world) {  // rank order: every rank forms the same sum, bit for bit
+                const float4 t0 = __ldcg(static_cast<const float4*>(grads.ptr[p]) + i0);
+                const float4 t1 = two ? __ldcg(static_cast<const float4*>(grads.ptr[p]) + i1) : make_float4(0.f, 0.f, 0.f, 0.f);
+                g0.x += t0.x; g0.y += t0.y; g0.z += t0.z; g0.w += t0.w;
+                g1.x += t1.x; g1.y += t1.y; g1.z += t1.z; g1.w += t1.w;
             }
         }
-        float4 pp = static_cast<const float4*>(params.ptr[rank])[i];  // every rank's copy holds the same bits
-        float4 mm = reinterpret_cast<float4*>(m)[mlo + i - lo], vv = reinterpret_cast<float4*>(v)[mlo + i - lo];
-        pp.x = adam_update(pp.x, g.x, gscale, mm.x, vv.x, step_size, bc2_sqrt, b1, b2, eps);
-        pp.y = adam_update(pp.y, g.y, gscale, mm.y, vv.y, step_size, bc2_sqrt, b1, b2, eps);
-        pp.z = adam_update(pp.z, g.z, gscale, mm.z, vv.z, step_size, bc2_sqrt, b1, b2, eps);
-        pp.w = adam_update(pp.w, g.w, gscale, mm.w, vv.w, step_size, bc2_sqrt, b1, b2, eps);
-        reinterpret_cast<float4*>(m)[mlo + i - lo] = mm;
-        reinterpret_cast<float4*>(v)[mlo + i - lo] = vv;
 #pragma unroll
-        for (int p = 0; p < DL_MAX_PEERS; ++p)
-            if (p < world) static_cast<float4*>(params.ptr[p])[i] = pp;
+        for (int h = 0; h < 2; ++h) {
+            if (h == 1 && !two) break;
+            const int64_t i = h == 0 ? i0 : i1;
+            const float4 g = h == 0 ? g0 : g1;
+            float4 pp = static_cast<const float4*>(params.ptr[rank])[i];  // every rank's copy holds the same bits
+            float4 mm = reinterpret_cast<float4*>(m)[mlo + i - lo], vv = reinterpret_cast<float4*>(v)[mlo + i - lo];
+            pp.x = adam_update(pp.x, g.x, gscale, mm.x, vv.x, step_size, bc2_sqrt, b1, b2, eps);
+            pp.y = adam_update(pp.y, g.y, gscale, mm.y, vv.y, step_size, bc2_sqrt, b1, b2, eps);
+            pp.z = adam_update(pp.z, g.z, gscale, mm.z, vv.z, step_size, bc2_sqrt, b1, b2, eps);
+            pp.w = adam_update(pp.w, g.w, gscale, mm.w, vv.w, step_size, bc2_sqrt, b1, b2, eps);
+            reinterpret_cast<float4*>(m)[mlo + i - lo] = mm;
+            reinterpret_cast<float4*>(v)[mlo + i - lo] = vv;
+#pragma unroll
+            for (int p = 0; p < DL_MAX_PEERS; ++p)
+                if (p < world) static_cast<float4*>(params.ptr[p])[i] = pp;
+        }
     }
 
     __syncthreads();  // every thread's parameter stores are ordered before thread 0's fence
@@ -196,14 +212,10 @@ p2p_exchange_adam_kernel(PeerTable grads, PeerTable params, PeerTable flags, flo
     __syncthreads();
     if (!last_cta) return;
     __threadfence_system();  // the other CTAs' stores, observed through the counter, before the flag below
-    ok = true;
     if (threadIdx.x < world) {
         const int p = threadIdx.x;
         store_release_sys(static_cast<int*>(flags.ptr[p]) + done + rank, e);
-        if (!wait_flag(static_cast<const int*>(flags.ptr[rank]) + done + p, e, timeout_ns)) {
-            atomicCAS(&ctrl[0], 0, 1 + p);
-            ok = false;
-        }
+        if (!wait_flag(static_cast<const int*>(flags.ptr[rank]) + done + p, e, timeout_ns)) atomicCAS(&ctrl[0], 0, 1 + p);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -286,8 +298,8 @@ DL_EXPORT int dl_p2p_reduce_adam(const void* const* peer_grads_host, const void*
 DL_EXPORT int dl_p2p_exchange_adam(const void* const* peer_grads_host, const void* const* peer_params_host,
                                    const void* const* peer_flags_host, float* m, float* v, double* state,
                                    int32_t* ctrl, int64_t offset, int64_t count, int64_t channel, int64_t advance_state,
-                                   int64_t rank, int64_t world, float lr, float beta1, float beta2, float eps,
-                                   float gscale, int64_t timeout_ms, dl_stream_t stream) {
+                                   int64_t overlapped, int64_t rank, int64_t world, float lr, float beta1, float beta2,
+                                   float eps, float gscale, int64_t timeout_ms, dl_stream_t stream) {
     DL_REQUIRE(peer_grads_host && peer_params_host && peer_flags_host && m && v && state && ctrl);
     DL_REQUIRE(world >= 1 && world <= DL_MAX_PEERS && rank >= 0 && rank < world);
     DL_REQUIRE(channel >= 0 && channel < DL_P2P_CHANNELS && timeout_ms > 0 && timeout_ms <= 60000);
@@ -310,10 +322,20 @@ DL_EXPORT int dl_p2p_exchange_adam(const void* const* peer_grads_host, const voi
     const int64_t per = count / 4 / world;           // float4s this rank owns of the slice
     const int64_t lo = offset / 4 + rank * per;
     const int64_t mlo = offset / 4 / world;          // the moments hold only this rank's share of every slice
-    // few CTAs: the kernel shares the GPU with the backward kernels of the layers below
-    const int64_t blocks = dl_min64(dl_ceil_div(per, 256 * 2), (int64_t)DL_NUM_SMS);
-    p2p_exchange_adam_kernel<<<(unsigned)(blocks < 1 ? 1 : blocks), 256, 0, dl_cast(stream)>>>(
-        grads, params, flags, m, v, state, ctrl, lo, lo + per, mlo, (int)channel, advance_state != 0, (int)rank,
-        (int)world, lr, beta1, beta2, eps, gscale, (uint64_t)timeout_ms * 1000000ull);
+    const uint64_t timeout_ns = (uint64_t)timeout_ms * 1000000ull;
+    if (overlapped) {
+        // one small CTA per SM, next to the resident CTAs of a backward kernel on the caller's other stream
+        int64_t blocks = dl_min64(dl_ceil_div(per, 64 * 2), (int64_t)DL_NUM_SMS);
+        if (blocks < 1) blocks = 1;
+        p2p_exchange_adam_kernel<64><<<(unsigned)blocks, 64, 0, dl_cast(stream)>>>(
+            grads, params, flags, m, v, state, ctrl, lo, lo + per, mlo, (int)channel, advance_state != 0, (int)rank,
+            (int)world, lr, beta1, beta2, eps, gscale, timeout_ns);
+    } else {
+        int64_t blocks = dl_min64(dl_ceil_div(per, 256 * 2), (int64_t)DL_NUM_SMS * 2);
+        if (blocks < 1) blocks = 1;
+        p2p_exchange_adam_kernel<256><<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(
+            grads, params, flags, m, v, state, ctrl, lo, lo + per, mlo, (int)channel, advance_state != 0, (int)rank,
+            (int)world, lr, beta1, beta2, eps, gscale, timeout_ns);
+    }
     return dl_launch_status();
 }

@@ -425,11 +425,15 @@ int dl_grad_rescale(const float* g, float* out, int64_t rows, int64_t cols, int 
  *                        wait gives up, status becomes 1 + the missing peer and stays so: later calls
  *                        return without touching anything until the host has reset ctrl[0].  A CTA decides
  *                        for itself whether everybody arrived, so a peer that arrives exactly at the limit
- *                        can leave a slice partly updated: a non-zero status invalidates the parameters.  */
+ *                        can leave a slice partly updated: a non-zero status invalidates the parameters.
+ *                        overlapped != 0: the call runs while a fused backward kernel occupies the GPU on
+ *                        another stream; it then launches two-warp CTAs of at most 64 registers per thread,
+ *                        which fit beside that kernel's resident CTAs (otherwise they would wait for it to
+ *                        end).  overlapped == 0: 256-thread CTAs for a call that has the GPU to itself.      */
 int dl_p2p_exchange_adam(const void* const* peer_grads_host, const void* const* peer_params_host,
                          const void* const* peer_flags_host, float* m, float* v, double* state, int32_t* ctrl,
-                         int64_t offset, int64_t count, int64_t channel, int64_t advance_state, int64_t rank,
-                         int64_t world, float lr, float beta1, float beta2, float eps, float gscale,
+                         int64_t offset, int64_t count, int64_t channel, int64_t advance_state, int64_t overlapped,
+                         int64_t rank, int64_t world, float lr, float beta1, float beta2, float eps, float gscale,
                          int64_t timeout_ms, dl_stream_t stream);
 int dl_p2p_enable_peer(int64_t peer_device);
 int dl_p2p_barrier(const void* const* peer_flags_host, int64_t rank, int64_t world, int32_t* ctrl,
@@ -455,6 +459,13 @@ int dl_loss_sum(const float* loss_rows, float* loss, int64_t B_global, int64_t B
  * g is multiplied by gscale before use (1/world after a sum all-reduce). */
 int dl_adam_step(float* p, const float* g, float* m, float* v, double* state, int64_t count,
                  float lr, float beta1, float beta2, float eps, float gscale, dl_stream_t stream);
+/* The two halves of dl_adam_step on their own, for a caller that updates slices of the flat vector at
+ * different times of a step (each layer's tables as soon as its gradient is complete): dl_adam_advance
+ * multiplies the state by the betas (once per step, before the first slice), dl_adam_apply updates one
+ * slice with the state as it stands. */
+int dl_adam_advance(double* state, float beta1, float beta2, dl_stream_t stream);
+int dl_adam_apply(float* p, const float* g, float* m, float* v, const double* state, int64_t count, float lr,
+                  float beta1, float beta2, float eps, float gscale, dl_stream_t stream);
 /* The same step with the gradient given as `groups` partial slabs of `stride` floats (what
  * dl_dwn_bwd_fused_t writes): g = sum of the slabs in order, also stored to g_out.  Replaces
  * dl_sum_groups + dl_adam_step when no all-reduce sits between them. */

@@ -169,9 +169,9 @@ def test_exchange_kernel_with_one_rank_equals_adam_step():
             _native.call("dl_adam_step", ref_p, grads, ref_m, ref_v, ref_state, count, 1e-2, 0.9, 0.999, 1e-8, 1.0)
             # upper slice first on channel 1, lower slice last on channel 0 (it advances the state)
             _native.call("dl_p2p_exchange_adam", ctypes.addressof(tg), ctypes.addressof(tp), ctypes.addressof(tf),
-                         m, v, state, ctrl, split, count - split, 1, 0, 0, 1, 1e-2, 0.9, 0.999, 1e-8, 1.0, 200)
+                         m, v, state, ctrl, split, count - split, 1, 0, 1, 0, 1, 1e-2, 0.9, 0.999, 1e-8, 1.0, 200)
             _native.call("dl_p2p_exchange_adam", ctypes.addressof(tg), ctypes.addressof(tp), ctypes.addressof(tf),
-                         m, v, state, ctrl, 0, split, 0, 1, 0, 1, 1e-2, 0.9, 0.999, 1e-8, 1.0, 200)
+                         m, v, state, ctrl, 0, split, 0, 1, 0, 0, 1, 1e-2, 0.9, 0.999, 1e-8, 1.0, 200)
             torch.cuda.synchronize()
             assert torch.equal(state, ref_state), (step, state.tolist(), ref_state.tolist())
             for name, got, want in (("m", m, ref_m), ("v", v, ref_v), ("params", params, ref_p)):
@@ -198,7 +198,7 @@ def test_exchange_kernel_gives_up_and_touches_nothing():
     before = (params.clone(), m.clone(), v.clone(), state.clone())
     peer_grads, peer_params = torch.zeros_like(grads), params.clone()
     tg, tp, tf = table(grads, peer_grads), table(params, peer_params), table(flags, absent)
-    args = (ctypes.addressof(tg), ctypes.addressof(tp), ctypes.addressof(tf), m, v, state, ctrl, 0, count, 0, 1, 0, 2,
+    args = (ctypes.addressof(tg), ctypes.addressof(tp), ctypes.addressof(tf), m, v, state, ctrl, 0, count, 0, 1, 0, 0, 2,
             1e-2, 0.9, 0.999, 1e-8, 1.0, 200)
     t0 = time.time()
     with torch.cuda.device(dev):
