@@ -71,7 +71,8 @@ SIGNATURES = {
     "dl_grad_rescale": "ppllififp s",
     "dl_p2p_barrier": "pllpl s",
     "dl_p2p_reduce_adam": "pppppplllfffff s",
-    "dl_p2p_exchange_adam": "ppppppplllllllfffffl s",
+    "dl_p2p_exchange_adam": "pppppppllllllllfffffl s",
+    "dl_p2p_wait_done": "ppllll s",
     "dl_popcount_groupsum_t": "ppllll s",
     "dl_ce_t": "pppppllll s",
     "dl_loss_sum": "ppll s",

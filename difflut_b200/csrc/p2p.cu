@@ -132,47 +132,107 @@ __device__ __forceinline__ bool wait_flag(const int* flag, int epoch, uint64_t t
     return true;
 }
 
-// THREADS = 64: a CTA of two warps with at most 64 registers per thread fits into what five resident CTAs of
-// the fused backward kernel leave free on an SM (4096 registers), so an exchange that overlaps a backward
-// kernel gets its CTAs scheduled at once instead of waiting for that kernel to end.  THREADS = 256: for an
-// exchange that has the GPU to itself.  Two 16-byte pieces per thread and iteration keep several peer loads
-// in flight per thread.
-template <int THREADS>
-__global__ void __launch_bounds__(THREADS, THREADS == 64 ? 16 : 2)
-p2p_exchange_adam_kernel(PeerTable grads, PeerTable params, PeerTable flags, float* __restrict__ m,
-                         float* __restrict__ v, double* __restrict__ state, int* __restrict__ ctrl, int64_t lo,
-                         int64_t hi, int64_t mlo, int ch, int advance, int rank, int world, float lr, float b1,
-                         float b2, float eps, float gscale, uint64_t timeout_ns) {
-    __shared__ int last_cta;
-    int* const my_epoch = ctrl + 1 + 2 * ch;
-    int* const my_done = ctrl + 2 + 2 * ch;
-    if (ctrl[0] != 0) return;  // an earlier wait gave up: the state is invalid until the host has looked at it
+struct ExchangeCtl {       // what the head of an exchange kernel hands to its body and tail
+    int epoch;
+    bool ok;
+};
+
+// Arrive: CTA 0 publishes this rank's arrival to every peer; every CTA waits until all peers have arrived.
+__device__ __forceinline__ ExchangeCtl exchange_head(const PeerTable& flags, int* __restrict__ own_flags,
+                                                     int* __restrict__ ctrl, int ch, int rank, int world,
+                                                     uint64_t timeout_ns) {
+    ExchangeCtl c;
+    c.ok = ctrl[0] == 0;  // an earlier wait gave up: the state is invalid until the host has looked at it
     // read before any CTA can finish: the epoch word is advanced by the LAST CTA to finish
-    const int e = *my_epoch + 1;
-    const int arrive = (ch * 2 + 0) * DL_MAX_PEERS, done = (ch * 2 + 1) * DL_MAX_PEERS;
+    c.epoch = ctrl[1 + 2 * ch] + 1;
+    if (!c.ok) return c;
+    const int arrive = (ch * 2 + 0) * DL_MAX_PEERS;
     bool ok = true;
     if (threadIdx.x < world) {
         const int p = threadIdx.x;
         if (blockIdx.x == 0) {
             __threadfence_system();  // the gradients earlier kernels of this GPU wrote are visible to the peers first
-            store_release_sys(static_cast<int*>(flags.ptr[p]) + arrive + rank, e);
+            store_release_sys(static_cast<int*>(flags.ptr[p]) + arrive + rank, c.epoch);
         }
-        if (!wait_flag(static_cast<const int*>(flags.ptr[rank]) + arrive + p, e, timeout_ns)) {
+        if (!wait_flag(own_flags + arrive + p, c.epoch, timeout_ns)) {
             atomicCAS(&ctrl[0], 0, 1 + p);
             ok = false;
         }
     }
-    if (!__syncthreads_and(ok)) return;  // parameters, moments and optimiser state stay untouched
+    c.ok = __syncthreads_and(ok);
+    return c;
+}
 
-    // bias corrections of THIS step: state holds beta^(t-1) until the step's last exchange advances it
-    // (the products are rounded on their own, as the stored state of the next step will be: no fused multiply-add)
+// Done: the CTA that finishes last tells the peers, waits for theirs, then advances the epoch (and, on the
+// step's last exchange, the optimiser state).
+__device__ __forceinline__ void exchange_tail(const PeerTable& flags, int* __restrict__ own_flags,
+                                              int* __restrict__ ctrl, double* __restrict__ state, int ch, int rank,
+                                              int world, int epoch, int advance, bool wait_peers, float b1, float b2,
+                                              uint64_t timeout_ns) {
+    __shared__ int last_cta;
+    int* const my_done = ctrl + 2 + 2 * ch;
+    __syncthreads();  // every thread's parameter stores are ordered before thread 0's fence
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        last_cta = atomicAdd(my_done, 1) == (int)gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!last_cta) return;
+    __threadfence_system();  // the other CTAs' stores, observed through the counter, before the flag below
+    const int done = (ch * 2 + 1) * DL_MAX_PEERS;
+    if (threadIdx.x < world) {
+        const int p = threadIdx.x;
+        store_release_sys(static_cast<int*>(flags.ptr[p]) + done + rank, epoch);
+        // without the wait the caller runs dl_p2p_wait_done before anything reads the parameters or
+        // overwrites the gradients: the second rendezvous then costs nothing on the step's critical path
+        if (wait_peers && !wait_flag(own_flags + done + p, epoch, timeout_ns)) atomicCAS(&ctrl[0], 0, 1 + p);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        *my_done = 0;
+        ctrl[1 + 2 * ch] = epoch;
+        if (advance) {
+            state[0] *= (double)b1;
+            state[1] *= (double)b2;
+        }
+    }
+}
+
+// Bias corrections of THIS step: state holds beta^(t-1) until the step's last exchange advances it (the
+// products are rounded on their own, as the stored state of the next step will be: no fused multiply-add).
+__device__ __forceinline__ void exchange_step_sizes(const double* __restrict__ state, float lr, float b1, float b2,
+                                                    float& step_size, float& bc2_sqrt) {
     const double bc1 = 1.0 - __dmul_rn(state[0], (double)b1);
     const double bc2 = 1.0 - __dmul_rn(state[1], (double)b2);
-    const float step_size = (float)((double)lr / bc1);
-    const float bc2_sqrt = (float)sqrt(bc2);
-    // [lo, hi) in float4 units of the flat vector; this rank's moments of the slice start at mlo
-    const int64_t stride = (int64_t)gridDim.x * THREADS;
-    for (int64_t i0 = lo + (int64_t)blockIdx.x * THREADS + threadIdx.x; i0 < hi; i0 += 2 * stride) {
+    step_size = (float)((double)lr / bc1);
+    bc2_sqrt = (float)sqrt(bc2);
+}
+
+// Second half of a deferred rendezvous: wait until every peer has published "done" for the channel's latest epoch.
+__global__ void p2p_wait_done_kernel(const int* __restrict__ own_flags, int* __restrict__ ctrl, int ch, int world,
+                                     uint64_t timeout_ns) {
+    if (ctrl[0] != 0) return;
+    const int epoch = ctrl[1 + 2 * ch];
+    const int p = threadIdx.x;
+    if (p < world && !wait_flag(own_flags + (ch * 2 + 1) * DL_MAX_PEERS + p, epoch, timeout_ns))
+        atomicCAS(&ctrl[0], 0, 1 + p);
+}
+
+// For an exchange that has the GPU to itself: 256-thread CTAs, two 16-byte pieces per thread and iteration
+// (several peer loads in flight per thread).  [lo, hi) in float4 units of the flat vector; this rank's moments
+// of the slice start at mlo.
+__global__ void __launch_bounds__(256, 2)
+p2p_exchange_adam_kernel(PeerTable grads, PeerTable params, PeerTable flags, int* __restrict__ own_flags,
+                         const float4* __restrict__ own_params, float4* __restrict__ m, float4* __restrict__ v,
+                         double* __restrict__ state, int* __restrict__ ctrl, int64_t lo, int64_t hi, int64_t mlo,
+                         int ch, int advance, int wait_peers, int rank, int world, float lr, float b1, float b2,
+                         float eps, float gscale, uint64_t timeout_ns) {
+    const ExchangeCtl c = exchange_head(flags, own_flags, ctrl, ch, rank, world, timeout_ns);
+    if (!c.ok) return;  // parameters, moments and optimiser state stay untouched
+    float step_size, bc2_sqrt;
+    exchange_step_sizes(state, lr, b1, b2, step_size, bc2_sqrt);
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i0 = lo + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < hi; i0 += 2 * stride) {
         const int64_t i1 = i0 + stride;
         const bool two = i1 < hi;
         float4 g0 = make_float4(0.f, 0.f, 0.f, 0.f), g1 = g0;
@@ -190,42 +250,66 @@ p2p_exchange_adam_kernel(PeerTable grads, PeerTable params, PeerTable flags, flo
             if (h == 1 && !two) break;
             const int64_t i = h == 0 ? i0 : i1;
             const float4 g = h == 0 ? g0 : g1;
-            float4 pp = static_cast<const float4*>(params.ptr[rank])[i];  // every rank's copy holds the same bits
-            float4 mm = reinterpret_cast<float4*>(m)[mlo + i - lo], vv = reinterpret_cast<float4*>(v)[mlo + i - lo];
+            float4 pp = own_params[i];  // every rank's copy holds the same bits
+            float4 mm = m[mlo + i - lo], vv = v[mlo + i - lo];
             pp.x = adam_update(pp.x, g.x, gscale, mm.x, vv.x, step_size, bc2_sqrt, b1, b2, eps);
             pp.y = adam_update(pp.y, g.y, gscale, mm.y, vv.y, step_size, bc2_sqrt, b1, b2, eps);
             pp.z = adam_update(pp.z, g.z, gscale, mm.z, vv.z, step_size, bc2_sqrt, b1, b2, eps);
             pp.w = adam_update(pp.w, g.w, gscale, mm.w, vv.w, step_size, bc2_sqrt, b1, b2, eps);
-            reinterpret_cast<float4*>(m)[mlo + i - lo] = mm;
-            reinterpret_cast<float4*>(v)[mlo + i - lo] = vv;
+            m[mlo + i - lo] = mm;
+            v[mlo + i - lo] = vv;
 #pragma unroll
             for (int p = 0; p < DL_MAX_PEERS; ++p)
                 if (p < world) static_cast<float4*>(params.ptr[p])[i] = pp;
         }
     }
+    exchange_tail(flags, own_flags, ctrl, state, ch, rank, world, c.epoch, advance, wait_peers != 0, b1, b2, timeout_ns);
+}
 
-    __syncthreads();  // every thread's parameter stores are ordered before thread 0's fence
-    if (threadIdx.x == 0) {
-        __threadfence_system();
-        last_cta = atomicAdd(my_done, 1) == (int)gridDim.x - 1;
-    }
-    __syncthreads();
-    if (!last_cta) return;
-    __threadfence_system();  // the other CTAs' stores, observed through the counter, before the flag below
-    if (threadIdx.x < world) {
-        const int p = threadIdx.x;
-        store_release_sys(static_cast<int*>(flags.ptr[p]) + done + rank, e);
-        if (!wait_flag(static_cast<const int*>(flags.ptr[rank]) + done + p, e, timeout_ns)) atomicCAS(&ctrl[0], 0, 1 + p);
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        *my_done = 0;
-        *my_epoch = e;
-        if (advance) {
-            state[0] *= (double)b1;
-            state[1] *= (double)b2;
+// For an exchange that runs while a fused backward kernel fills the GPU from another stream.  Five resident
+// CTAs of that kernel (20 warps of 96 registers) leave 1024 registers free in each of an SM's four register
+// partitions: one warp of at most 32 registers per partition.  This variant is built for exactly that hole
+// (four warps, 32 registers, no shared-memory arrays), so its CTAs are scheduled beside the backward kernel
+// instead of after it.  It works on single floats, four per thread and iteration, a warp always on 128
+// consecutive bytes.  [lo, hi) and mlo in floats here.
+__global__ void __launch_bounds__(128, 16)
+p2p_exchange_adam_lean_kernel(PeerTable grads, PeerTable params, PeerTable flags, int* __restrict__ own_flags,
+                              const float* __restrict__ own_params, float* __restrict__ m, float* __restrict__ v,
+                              double* __restrict__ state, int* __restrict__ ctrl, int64_t lo, int64_t hi,
+                              int64_t mlo, int ch, int advance, int wait_peers, int rank, int world, float lr, float b1,
+                              float b2, float eps, float gscale, uint64_t timeout_ns) {
+    const ExchangeCtl c = exchange_head(flags, own_flags, ctrl, ch, rank, world, timeout_ns);
+    if (!c.ok) return;
+    float step_size, bc2_sqrt;
+    exchange_step_sizes(state, lr, b1, b2, step_size, bc2_sqrt);
+    const int64_t stride = (int64_t)gridDim.x * 128 * 4;
+    for (int64_t base = lo + (int64_t)blockIdx.x * 128 * 4 + threadIdx.x; base < hi; base += stride) {
+        float g[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int p = 0; p < DL_MAX_PEERS; ++p) {
+            if (p < world) {  // rank order: every rank forms the same sum, bit for bit
+                const float* src = static_cast<const float*>(grads.ptr[p]);
+                float t[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) t[k] = base + k * 128 < hi ? __ldcg(src + base + k * 128) : 0.f;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) g[k] += t[k];
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int64_t i = base + k * 128;
+            if (i >= hi) break;
+            float mm = m[mlo + i - lo], vv = v[mlo + i - lo];
+            const float pp = adam_update(own_params[i], g[k], gscale, mm, vv, step_size, bc2_sqrt, b1, b2, eps);
+            m[mlo + i - lo] = mm;
+            v[mlo + i - lo] = vv;
+#pragma unroll
+            for (int p = 0; p < DL_MAX_PEERS; ++p)
+                if (p < world) static_cast<float*>(params.ptr[p])[i] = pp;
         }
     }
+    exchange_tail(flags, own_flags, ctrl, state, ch, rank, world, c.epoch, advance, wait_peers != 0, b1, b2, timeout_ns);
 }
 
 int fill_table(PeerTable& t, const void* const* host_ptrs, int64_t world) {
@@ -298,8 +382,9 @@ DL_EXPORT int dl_p2p_reduce_adam(const void* const* peer_grads_host, const void*
 DL_EXPORT int dl_p2p_exchange_adam(const void* const* peer_grads_host, const void* const* peer_params_host,
                                    const void* const* peer_flags_host, float* m, float* v, double* state,
                                    int32_t* ctrl, int64_t offset, int64_t count, int64_t channel, int64_t advance_state,
-                                   int64_t overlapped, int64_t rank, int64_t world, float lr, float beta1, float beta2,
-                                   float eps, float gscale, int64_t timeout_ms, dl_stream_t stream) {
+                                   int64_t overlapped, int64_t defer_done, int64_t rank, int64_t world, float lr,
+                                   float beta1, float beta2, float eps, float gscale, int64_t timeout_ms,
+                                   dl_stream_t stream) {
     DL_REQUIRE(peer_grads_host && peer_params_host && peer_flags_host && m && v && state && ctrl);
     DL_REQUIRE(world >= 1 && world <= DL_MAX_PEERS && rank >= 0 && rank < world);
     DL_REQUIRE(channel >= 0 && channel < DL_P2P_CHANNELS && timeout_ms > 0 && timeout_ms <= 60000);
@@ -323,19 +408,32 @@ DL_EXPORT int dl_p2p_exchange_adam(const void* const* peer_grads_host, const voi
     const int64_t lo = offset / 4 + rank * per;
     const int64_t mlo = offset / 4 / world;          // the moments hold only this rank's share of every slice
     const uint64_t timeout_ns = (uint64_t)timeout_ms * 1000000ull;
+    int* own_flags = static_cast<int*>(flags.ptr[rank]);
     if (overlapped) {
-        // one small CTA per SM, next to the resident CTAs of a backward kernel on the caller's other stream
-        int64_t blocks = dl_min64(dl_ceil_div(per, 64 * 2), (int64_t)DL_NUM_SMS);
+        // one four-warp CTA per SM, beside the resident CTAs of a backward kernel on the caller's other stream
+        int64_t blocks = dl_min64(dl_ceil_div(per * 4, 128 * 4), (int64_t)DL_NUM_SMS);
         if (blocks < 1) blocks = 1;
-        p2p_exchange_adam_kernel<64><<<(unsigned)blocks, 64, 0, dl_cast(stream)>>>(
-            grads, params, flags, m, v, state, ctrl, lo, lo + per, mlo, (int)channel, advance_state != 0, (int)rank,
-            (int)world, lr, beta1, beta2, eps, gscale, timeout_ns);
+        p2p_exchange_adam_lean_kernel<<<(unsigned)blocks, 128, 0, dl_cast(stream)>>>(
+            grads, params, flags, own_flags, static_cast<const float*>(params.ptr[rank]), m, v, state, ctrl, lo * 4,
+            (lo + per) * 4, mlo * 4, (int)channel, advance_state != 0, defer_done == 0, (int)rank, (int)world, lr, beta1,
+            beta2, eps, gscale, timeout_ns);
     } else {
         int64_t blocks = dl_min64(dl_ceil_div(per, 256 * 2), (int64_t)DL_NUM_SMS * 2);
         if (blocks < 1) blocks = 1;
-        p2p_exchange_adam_kernel<256><<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(
-            grads, params, flags, m, v, state, ctrl, lo, lo + per, mlo, (int)channel, advance_state != 0, (int)rank,
-            (int)world, lr, beta1, beta2, eps, gscale, timeout_ns);
+        p2p_exchange_adam_kernel<<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(
+            grads, params, flags, own_flags, static_cast<const float4*>(params.ptr[rank]),
+            reinterpret_cast<float4*>(m), reinterpret_cast<float4*>(v), state, ctrl, lo, lo + per, mlo, (int)channel,
+            advance_state != 0, defer_done == 0, (int)rank, (int)world, lr, beta1, beta2, eps, gscale, timeout_ns);
     }
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_p2p_wait_done(const void* const* peer_flags_host, int32_t* ctrl, int64_t channel, int64_t rank,
+                               int64_t world, int64_t timeout_ms, dl_stream_t stream) {
+    DL_REQUIRE(peer_flags_host && ctrl && world >= 1 && world <= DL_MAX_PEERS && rank >= 0 && rank < world);
+    DL_REQUIRE(channel >= 0 && channel < DL_P2P_CHANNELS && timeout_ms > 0 && timeout_ms <= 60000);
+    DL_REQUIRE(peer_flags_host[rank] != nullptr);
+    p2p_wait_done_kernel<<<1, 32, 0, dl_cast(stream)>>>(static_cast<const int*>(peer_flags_host[rank]), ctrl, (int)channel,
+                                                       (int)world, (uint64_t)timeout_ms * 1000000ull);
     return dl_launch_status();
 }

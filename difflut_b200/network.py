@@ -97,8 +97,12 @@ class DWNNetwork:
         total = self.offsets[-1]
         moments = total // self.world if self.peer_optimizer else total
         # one exchange kernel per layer (its own flag channel) unless there are more layers than channels
+        # (DIFFLUT_PEER_PER_LAYER=1 starts it per layer under the backward of the layers below: measured slower,
+        # every exchange is a rendezvous of all ranks)
         self.peer_fused = os.environ.get("DIFFLUT_PEER_FUSED", "1") != "0"
-        self.peer_per_layer = len(self.layers) <= 8
+        self.peer_per_layer = len(self.layers) <= 8 and os.environ.get("DIFFLUT_PEER_PER_LAYER", "0") == "1"
+        # the exchange does not wait for the peers' "done": the next step (or any read of the tables) does
+        self.peer_defer_done = os.environ.get("DIFFLUT_PEER_DEFER_DONE", "1") != "0"
         self.flat = torch.zeros(total, device=self.device, dtype=torch.float32)
         self.flat_grad = torch.zeros(total, device=self.device, dtype=torch.float32)
         self.exp_avg = torch.zeros(moments, device=self.device, dtype=torch.float32)
@@ -160,6 +164,7 @@ class DWNNetwork:
         self._graph_B_global = None
         self._side = None
         self._comm = None
+        self._peer_channels = set()
         self.step_count = 0
         self.infer_chunk = 1 << 18  # hard inference walks large batches in pieces of this many samples
 
@@ -305,8 +310,17 @@ class DWNNetwork:
     def _exchange(self, offset: int, count: int, channel: int, advance: bool, overlapped: bool = False) -> None:
         _native.call("dl_p2p_exchange_adam", self.win_grads.ptrs, self.win_params.ptrs, self.win_flags.ptrs,
                      self.exp_avg, self.exp_avg_sq, self.adam_state, self.peer_ctrl, offset, count, channel,
-                     1 if advance else 0, 1 if overlapped else 0, self.rank, self.world, self.lr, self.betas[0],
-                     self.betas[1], self.eps, 1.0, self.peer_timeout_ms)
+                     1 if advance else 0, 1 if overlapped else 0, 1 if self.peer_defer_done else 0, self.rank,
+                     self.world, self.lr, self.betas[0], self.betas[1], self.eps, 1.0, self.peer_timeout_ms)
+        self._peer_channels.add(channel)
+
+    def _peer_wait_done(self) -> None:
+        """Every rank's parameter stores of the latest exchange have landed here and every rank has finished
+        reading this rank's gradients (second half of the exchange's rendezvous, see `peer_defer_done`)."""
+        if self.peer_optimizer and self.peer_fused and self.peer_defer_done:
+            for ch in sorted(self._peer_channels):
+                _native.call("dl_p2p_wait_done", self.win_flags.ptrs, self.peer_ctrl, ch, self.rank, self.world,
+                             self.peer_timeout_ms)
 
     def _step_body(self, B: int, B_global: int) -> None:
         """One step as a small dependency graph over three streams (captured as such into the CUDA graph):
@@ -324,6 +338,7 @@ class DWNNetwork:
         self._fork.record(main)
         self._side.wait_event(self._fork)
         with torch.cuda.stream(self._side):
+            self._peer_wait_done()  # the previous step's exchange, before the tables are read again
             self._prepare_tables(need_efd=False, need_masks=True)
             self._masks_ready.record(self._side)
             self._prepare_tables(need_efd=True, need_masks=False)
@@ -380,6 +395,8 @@ class DWNNetwork:
         """0, or 1 + the rank a bounded peer wait gave up on (synchronises; call it between steps)."""
         if not self.peer_optimizer:
             return 0
+        with torch.cuda.device(self.device):
+            self._peer_wait_done()  # after this the tables are complete on this rank
         return int(self.peer_ctrl[0].item()) if self.peer_fused else int(self.peer_ctrl_barrier[1].item())
 
     def kernel_launches_per_step(self) -> int:
@@ -441,6 +458,7 @@ class DWNNetwork:
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
             self._step_body(B, B_global)
+            self._peer_wait_done()  # no peer may still be storing into the tables that are restored below
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize(self.device)
         self.flat.copy_(snap[0]); self.exp_avg.copy_(snap[1]); self.exp_avg_sq.copy_(snap[2])
@@ -457,6 +475,7 @@ class DWNNetwork:
         B = int(x.shape[0])
         with torch.cuda.device(self.device):
             self._ensure_buffers(B, training=False)
+            self._peer_wait_done()
             self._prepare_tables(need_efd=False)
             self._forward(x.contiguous().float(), B)
             out = torch.empty(B, self.k, device=self.device, dtype=torch.float32)
@@ -476,6 +495,7 @@ class DWNNetwork:
         with torch.cuda.device(self.device):
             if out is None:
                 out = torch.empty(B_total, self.k, device=self.device, dtype=torch.int32)
+            self._peer_wait_done()
             self._prepare_tables(need_efd=False)
             for lo in range(0, B_total, self.infer_chunk):
                 hi = min(lo + self.infer_chunk, B_total)

@@ -427,14 +427,22 @@ int dl_grad_rescale(const float* g, float* out, int64_t rows, int64_t cols, int 
  *                        for itself whether everybody arrived, so a peer that arrives exactly at the limit
  *                        can leave a slice partly updated: a non-zero status invalidates the parameters.
  *                        overlapped != 0: the call runs while a fused backward kernel occupies the GPU on
- *                        another stream; it then launches two-warp CTAs of at most 64 registers per thread,
+ *                        another stream; it then launches four-warp CTAs of at most 32 registers per thread,
  *                        which fit beside that kernel's resident CTAs (otherwise they would wait for it to
- *                        end).  overlapped == 0: 256-thread CTAs for a call that has the GPU to itself.      */
+ *                        end).  overlapped == 0: 256-thread CTAs for a call that has the GPU to itself.
+ *                        defer_done != 0: the kernel publishes "done" but does not wait for the peers'; the
+ *                        caller then runs dl_p2p_wait_done on the same channel before anything reads the
+ *                        parameters or overwrites the gradients again (the start of the next step), which
+ *                        takes the second rendezvous off the step's critical path.
+ *   dl_p2p_wait_done     waits (bounded) until every peer has published "done" for the channel's latest
+ *                        exchange; returns at once before the first exchange.                                */
 int dl_p2p_exchange_adam(const void* const* peer_grads_host, const void* const* peer_params_host,
                          const void* const* peer_flags_host, float* m, float* v, double* state, int32_t* ctrl,
                          int64_t offset, int64_t count, int64_t channel, int64_t advance_state, int64_t overlapped,
-                         int64_t rank, int64_t world, float lr, float beta1, float beta2, float eps, float gscale,
-                         int64_t timeout_ms, dl_stream_t stream);
+                         int64_t defer_done, int64_t rank, int64_t world, float lr, float beta1, float beta2, float eps,
+                         float gscale, int64_t timeout_ms, dl_stream_t stream);
+int dl_p2p_wait_done(const void* const* peer_flags_host, int32_t* ctrl, int64_t channel, int64_t rank, int64_t world,
+                     int64_t timeout_ms, dl_stream_t stream);
 int dl_p2p_enable_peer(int64_t peer_device);
 int dl_p2p_barrier(const void* const* peer_flags_host, int64_t rank, int64_t world, int32_t* ctrl,
                    int64_t timeout_ms, dl_stream_t stream);

@@ -169,15 +169,18 @@ def test_exchange_kernel_with_one_rank_equals_adam_step():
             _native.call("dl_adam_step", ref_p, grads, ref_m, ref_v, ref_state, count, 1e-2, 0.9, 0.999, 1e-8, 1.0)
             # upper slice first on channel 1, lower slice last on channel 0 (it advances the state)
             _native.call("dl_p2p_exchange_adam", ctypes.addressof(tg), ctypes.addressof(tp), ctypes.addressof(tf),
-                         m, v, state, ctrl, split, count - split, 1, 0, 1, 0, 1, 1e-2, 0.9, 0.999, 1e-8, 1.0, 200)
+                         m, v, state, ctrl, split, count - split, 1, 0, 1, 1, 0, 1, 1e-2, 0.9, 0.999, 1e-8, 1.0, 200)
             _native.call("dl_p2p_exchange_adam", ctypes.addressof(tg), ctypes.addressof(tp), ctypes.addressof(tf),
-                         m, v, state, ctrl, 0, split, 0, 1, 0, 0, 1, 1e-2, 0.9, 0.999, 1e-8, 1.0, 200)
+                         m, v, state, ctrl, 0, split, 0, 1, 0, 0, 0, 1, 1e-2, 0.9, 0.999, 1e-8, 1.0, 200)
             torch.cuda.synchronize()
             assert torch.equal(state, ref_state), (step, state.tolist(), ref_state.tolist())
             for name, got, want in (("m", m, ref_m), ("v", v, ref_v), ("params", params, ref_p)):
                 bad = (got != want).nonzero().flatten()
                 assert bad.numel() == 0, (f"step {step}: {name} differs at {bad.numel()} places, first {int(bad[0])}: "
                                           f"{float(got[bad[0]])!r} vs {float(want[bad[0]])!r}")
+    with torch.cuda.device(dev):  # the deferred half of channel 1's rendezvous: every rank (this one) is done
+        _native.call("dl_p2p_wait_done", ctypes.addressof(tf), ctrl, 1, 0, 1, 200)
+    torch.cuda.synchronize()
     c = ctrl.tolist()
     assert c[0] == 0 and c[1] == 3 and c[3] == 3 and c[2] == 0 and c[4] == 0  # status, epochs, counters reset
 
@@ -198,7 +201,7 @@ def test_exchange_kernel_gives_up_and_touches_nothing():
     before = (params.clone(), m.clone(), v.clone(), state.clone())
     peer_grads, peer_params = torch.zeros_like(grads), params.clone()
     tg, tp, tf = table(grads, peer_grads), table(params, peer_params), table(flags, absent)
-    args = (ctypes.addressof(tg), ctypes.addressof(tp), ctypes.addressof(tf), m, v, state, ctrl, 0, count, 0, 1, 0, 0, 2,
+    args = (ctypes.addressof(tg), ctypes.addressof(tp), ctypes.addressof(tf), m, v, state, ctrl, 0, count, 0, 1, 0, 0, 0, 2,
             1e-2, 0.9, 0.999, 1e-8, 1.0, 200)
     t0 = time.time()
     with torch.cuda.device(dev):
@@ -227,4 +230,16 @@ def test_exchange_kernel_gives_up_and_touches_nothing():
     torch.cuda.synchronize()
     for now, was in zip((params, m, v, state), before):
         assert torch.equal(now, was)
+    # the deferred wait gives up the same way: an epoch nobody has reported "done" for
+    ctrl2 = torch.zeros(17, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _native.call("dl_p2p_wait_done", ctypes.addressof(tf), ctrl2, 3, 0, 2, 200)  # before any exchange: returns at once
+    torch.cuda.synchronize()
+    assert int(ctrl2[0]) == 0
+    ctrl2[1 + 2 * 3] = 1
+    t0 = time.time()
+    with torch.cuda.device(dev):
+        _native.call("dl_p2p_wait_done", ctypes.addressof(tf), ctrl2, 3, 0, 2, 200)
+    torch.cuda.synchronize()
+    assert 0.15 < time.time() - t0 < 5.0 and int(ctrl2[0]) in (1, 2)
     assert float(torch.ones(4, device=dev).sum()) == 4.0  # the context is still usable
