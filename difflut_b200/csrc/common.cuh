@@ -57,4 +57,4 @@ int dl_launch_bwd_pipelined(const uint8_t* addr_up, const float* g_up, int64_t g
                             const float* efd_up, int n_up, const int32_t* inv_ptr, const int32_t* inv_ent,
                             const uint32_t* in_bits, const int32_t* map, float* g_out, uint8_t* addr_out,
                             float* gt, int64_t group_stride, int64_t N, int64_t N_up, int64_t Bp, int64_t Wp,
-                            int blocks_per_item, int min_ctas, cudaStream_t s);
+                            int blocks_per_item, cudaStream_t s);

@@ -1124,19 +1124,16 @@ void launch_fused_outs(dim3 grid, cudaStream_t s, const uint8_t* addr_up, const 
 
 // Tuning switches read once from the environment (measurement aids; the defaults are the product):
 // DIFFLUT_BWD_GENERAL=1 keeps every call on the general kernel, DIFFLUT_BWD_BLOCKS_PER_ITEM=k fixes the
-// number of 1024-sample blocks one (node, group) item of the pipelined kernel spans, DIFFLUT_BWD_MIN_CTAS=4
-// selects its 128-register build (4 CTAs per SM instead of 5).
+// number of 1024-sample blocks one (node, group) item of the pipelined kernel spans.
 struct FusedTuning {
     bool general_only;
     int blocks_per_item;
-    int min_ctas;
 };
 const FusedTuning& fused_tuning() {
     static const FusedTuning t = [] {
-        FusedTuning v{false, 0, 5};
+        FusedTuning v{false, 0};
         if (const char* e = getenv("DIFFLUT_BWD_GENERAL")) v.general_only = e[0] == '1';
         if (const char* e = getenv("DIFFLUT_BWD_BLOCKS_PER_ITEM")) v.blocks_per_item = atoi(e);
-        if (const char* e = getenv("DIFFLUT_BWD_MIN_CTAS")) v.min_ctas = atoi(e);
         return v;
     }();
     return t;
@@ -1188,7 +1185,7 @@ int bwd_fused_entry(bool swz, const uint8_t* addr_up, const float* g_up, int64_t
         }
         const int rc = dl_launch_bwd_pipelined(addr_up, g_up, gdiv_up, gscale_up, efd_up, (int)n_up, inv_ptr, inv_ent,
                                                in_bits_t, map, g_out, addr_out, gt_partial, group_stride, N,
-                                               direct ? 0 : N_up, Bp, Wp, bpi, fused_tuning().min_ctas, s);
+                                               direct ? 0 : N_up, Bp, Wp, bpi, s);
         if (rc != DL_ERR_UNSUPPORTED) return rc;  // else: row offsets beyond 32 bits, general kernel below
     }
 #define DL_FUSED_CALL(D, NN, SWZ)                                                                                     \

@@ -96,8 +96,8 @@ __device__ __forceinline__ void hist_add(uint32_t mine, uint32_t a, float v) {
     sts_f32(at, lds_f32(at) + v);
 }
 
-template <bool DIRECT, bool GSAME, int OUTS, int MINB>
-__global__ void __launch_bounds__(PW * 32, MINB)
+template <bool DIRECT, bool GSAME, int OUTS>
+__global__ void __launch_bounds__(PW * 32, 5)
 dwn_bwd_pipelined_kernel(const uint8_t* __restrict__ addr_up, const float* __restrict__ g_up, uint32_t ugdiv,
                          float gscale, const float* __restrict__ efd_up, int n_up,
                          const int32_t* __restrict__ inv_ptr, const int32_t* __restrict__ inv_ent,
@@ -331,7 +331,7 @@ int dl_launch_bwd_pipelined(const uint8_t* addr_up, const float* g_up, int64_t g
                             const float* efd_up, int n_up, const int32_t* inv_ptr, const int32_t* inv_ent,
                             const uint32_t* in_bits, const int32_t* map, float* g_out, uint8_t* addr_out,
                             float* gt, int64_t group_stride, int64_t N, int64_t N_up, int64_t Bp, int64_t Wp,
-                            int blocks_per_item, int min_ctas, cudaStream_t s) {
+                            int blocks_per_item, cudaStream_t s) {
     const int64_t rows = N > N_up ? N : N_up;
     if (rows * Bp >= ((int64_t)1 << 32) || Wp >= ((int64_t)1 << 31)) return DL_ERR_UNSUPPORTED;
     const int NB = (int)(Bp / 1024);
@@ -339,8 +339,7 @@ int dl_launch_bwd_pipelined(const uint8_t* addr_up, const float* g_up, int64_t g
     if (group_stride > 0) bpi = 1;  // one slab per 1024-sample group: items cannot span blocks
     if (bpi > NB) bpi = NB;
     const int G = (NB + bpi - 1) / bpi;
-    if (min_ctas != 4) min_ctas = 5;
-    const int64_t cap = (int64_t)DL_NUM_SMS * min_ctas;  // persistent grid: the CTAs resident at once
+    const int64_t cap = (int64_t)DL_NUM_SMS * 5;  // persistent grid: the CTAs resident at once
     const int64_t blocks64 = dl_ceil_div(N, PW);
     const unsigned blocks = (unsigned)(blocks64 < cap ? blocks64 : cap);
     int64_t gy = 1;
@@ -353,19 +352,13 @@ int dl_launch_bwd_pipelined(const uint8_t* addr_up, const float* g_up, int64_t g
     const bool direct = inv_ptr == nullptr;
     const bool gsame = gdiv_up == 1;
     const int outs = (g_out ? 1 : 0) | (addr_out ? 2 : 0);
-#define DL_PIPE(D, S, O)                                                                                             \
-    do {                                                                                                             \
-        if (min_ctas == 4) {                                                                                         \
-            cudaFuncSetAttribute(dwn_bwd_pipelined_kernel<D, S, O, 4>, cudaFuncAttributePreferredSharedMemoryCarveout, 60); \
-            dwn_bwd_pipelined_kernel<D, S, O, 4><<<grid, PW * 32, 0, s>>>(                                           \
-                addr_up, g_up, (uint32_t)gdiv_up, gscale_up, efd_up, n_up, inv_ptr, inv_ent, in_bits, map, g_out,    \
-                addr_out, gt, group_stride, (int)N, (uint32_t)Bp, (uint32_t)Wp, NB, bpi);                            \
-        } else {                                                                                                     \
-            cudaFuncSetAttribute(dwn_bwd_pipelined_kernel<D, S, O, 5>, cudaFuncAttributePreferredSharedMemoryCarveout, 75); \
-            dwn_bwd_pipelined_kernel<D, S, O, 5><<<grid, PW * 32, 0, s>>>(                                           \
-                addr_up, g_up, (uint32_t)gdiv_up, gscale_up, efd_up, n_up, inv_ptr, inv_ent, in_bits, map, g_out,    \
-                addr_out, gt, group_stride, (int)N, (uint32_t)Bp, (uint32_t)Wp, NB, bpi);                            \
-        }                                                                                                            \
+#define DL_PIPE(D, S, O)                                                                                            \
+    do {                                                                                                            \
+        /* enough shared memory for 5 CTAs (5 x 33 KB), the rest stays L1 for index and transform rows */           \
+        cudaFuncSetAttribute(dwn_bwd_pipelined_kernel<D, S, O>, cudaFuncAttributePreferredSharedMemoryCarveout, 75); \
+        dwn_bwd_pipelined_kernel<D, S, O><<<grid, PW * 32, 0, s>>>(                                                 \
+            addr_up, g_up, (uint32_t)gdiv_up, gscale_up, efd_up, n_up, inv_ptr, inv_ent, in_bits, map, g_out,       \
+            addr_out, gt, group_stride, (int)N, (uint32_t)Bp, (uint32_t)Wp, NB, bpi);                               \
     } while (0)
 #define DL_PIPE_OUTS(D, S)                    \
     switch (outs) {                           \

@@ -285,17 +285,6 @@ class DWNNetwork:
                 # sum of per-rank gradients of the GLOBAL-mean loss (dl_ce_t divides by B_global)
                 grad = self.flat_grad[self.offsets[li]:self.offsets[li] + self.counts[li]]
                 self._pending.append(allreduce_sum_(grad, self.group, async_op=True))
-            elif not self.distributed:
-                # single process: this layer's Adam update runs on the side stream under the backward of the
-                # layers below (nothing reads the tables any more in this step)
-                main = torch.cuda.current_stream()
-                self._comm_events[li].record(main)
-                self._side.wait_event(self._comm_events[li])
-                with torch.cuda.stream(self._side):
-                    lo, n_el = self.offsets[li], self.counts[li]
-                    _native.call("dl_adam_apply", self.flat[lo:lo + n_el], self.flat_grad[lo:lo + n_el],
-                                 self.exp_avg[lo:lo + n_el], self.exp_avg_sq[lo:lo + n_el], self.adam_state, n_el,
-                                 self.lr, self.betas[0], self.betas[1], self.eps, 1.0)
             elif self.peer_optimizer and self.peer_fused and self.peer_per_layer:
                 # this layer's gradient is complete on this rank: its exchange (all ranks arrive -> reduce + Adam
                 # on the owner -> store everywhere -> all ranks done) runs on the communication stream under
@@ -349,12 +338,10 @@ class DWNNetwork:
         _native.call("dl_ce_t", self.logits_t, self.y_static, self.dlogits_t, self.loss_rows, None,
                      B, B_global, self.k, self.Bp)
         self._ce_done.record(main)
-        layerwise_adam = self.fused_backward and not self.distributed
         with torch.cuda.stream(self._side):
             self._side.wait_event(self._ce_done)
             _native.call("dl_loss_sum", self.loss_rows, self.loss, B_global, self.Bp)
-            if layerwise_adam:
-                _native.call("dl_adam_advance", self.adam_state, self.betas[0], self.betas[1])
+            self._side_done.record(self._side)
         main.wait_event(self._efd_ready)
         fused_exchange = self.peer_optimizer and self.peer_fused and self.peer_per_layer and self.fused_backward
         if fused_exchange:
@@ -376,7 +363,10 @@ class DWNNetwork:
                              self.exp_avg_sq, self.adam_state, self.peer_ctrl_barrier, count, self.rank, self.world,
                              self.lr, self.betas[0], self.betas[1], self.eps, 1.0)
                 _native.call("dl_p2p_barrier", *barrier)
-        elif not layerwise_adam:
+        else:
+            # (the update of a layer's tables could start as soon as that layer's gradient is complete, under the
+            # backward of the layers below; measured, that is slower: the backward kernels divide their work
+            # statically over a grid that fills the GPU, and any CTA that has to start late ends the kernel late)
             if self.distributed:
                 if self.fused_backward:
                     for work in self._pending:  # the per-layer all-reduces started during the backward
@@ -387,7 +377,6 @@ class DWNNetwork:
                     allreduce_sum_(self.flat_grad, self.group)
             _native.call("dl_adam_step", self.flat, self.flat_grad, self.exp_avg, self.exp_avg_sq, self.adam_state,
                          count, self.lr, self.betas[0], self.betas[1], self.eps, 1.0)
-        self._side_done.record(self._side)
         main.wait_event(self._side_done)
 
     # ------------------------------------------------------------------ public API
@@ -404,7 +393,7 @@ class DWNNetwork:
         backward = L if self.fused_backward else (L + (L - 1))
         prepare = 2 * (1 if self.uniform else L)
         if not self.peer_optimizer:
-            update = 1 + L if (self.fused_backward and not self.distributed) else 2  # state advance, Adam (per layer)
+            update = 2  # state advance, Adam
         elif self.peer_fused:
             update = L if self.peer_per_layer else 1  # one exchange kernel per layer
         else:
