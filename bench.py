@@ -465,11 +465,12 @@ def collect_secondary(args):
     sub.steps, sub.warmup, sub.small = min(args.steps, 10), 3, False
     out = {}
     for key, fn in (("prob", measure_prob), ("learnable", measure_learnable), ("infer", measure_infer),
-                    ("train_layers", measure_train_layers)):
+                    ("train_layers", measure_train_layers), ("gather", measure_gather)):
         t0 = time.perf_counter()
         try:
             line = fn(sub)
-            keep = {k: line[k] for k in ("metric", "value", "unit", "ms_per_step", "dtype", "roofline", "e2e", "dwn_stack")
+            keep = {k: line[k] for k in ("metric", "value", "unit", "ms_per_step", "dtype", "roofline", "e2e", "dwn_stack",
+                                         "backward_ms")
                     if k in line}
             keep["workload"] = line["config"]["workload"]
             if key == "infer":
@@ -679,6 +680,42 @@ def measure_nodes(args):
                       "ms_per_step_by_node_type": {k: round(v, 4) for k, v in results.items()}}
 
 
+def measure_gather(args):
+    """RandomLayer.get_mapping and its backward at the first layer's width (6272 -> 16000 nodes x 6 inputs):
+    `dl_gather_rows` / `dl_gather_rows_bwd` on fp32 rows, the API-exact materialised path
+    (difflut/layers/random_layer.py:258-304).  Algorithmic bytes: input read once, output written once."""
+    import torch
+
+    warnings.simplefilter("ignore")
+    from difflut_b200 import _native
+    from difflut_b200.layers.fused_ops import ConnectionPlan
+    from difflut_b200.layers.random_layer import draw_random_mapping
+
+    device = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(0)
+    B, I, N, n = 2048, FEATURES * THERMO_BITS, SIZES[0], 6
+    plan = ConnectionPlan(draw_random_mapping(I, N, n, 0, True), I, 1, device)
+    x = torch.rand(B, I, generator=g).to(device)
+    out = torch.empty(B, N, n, device=device)
+    gy = torch.randn(B, N, n, generator=g).to(device)
+    gx = torch.empty(B, I, device=device)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    fwd = _time_gpu(lambda: _native.call("dl_gather_rows", x, plan.map_nodes, out, B, I, N, n), args.steps, 3, flush)
+    bwd = _time_gpu(lambda: _native.call("dl_gather_rows_bwd", gy, plan.inv_ptr_nodes, plan.inv_ent_nodes, gx, B, I,
+                                          N, n), args.steps, 3, flush)
+    bytes_each = 4.0 * B * (I + N * n)
+    peak = _peaks()
+    return {"metric": "gather rows/s (forward), RandomLayer map 6272 -> 16000 x 6 on fp32 rows", "value": B / (fwd * 1e-3),
+            "unit": "rows/s", "n_gpus": 1, "steps": args.steps, "warmup": 3, "ms_per_step": fwd,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"gather_B{B}_in{I}_N{N}_n{n}", "l2": "256 MB flush between timed calls"},
+            "backward_ms": bwd,
+            "roofline": {"bound": "hbm", "achieved": bytes_each / (fwd * 1e-3) / 1e9, "peak": peak["hbm_gbs"],
+                         "peak_source": peak["source"], "unit": "GB/s", "frac": bytes_each / (fwd * 1e-3) / 1e9 / peak["hbm_gbs"],
+                         "traffic": None, "backward_achieved": bytes_each / (bwd * 1e-3) / 1e9,
+                         "backward_frac": bytes_each / (bwd * 1e-3) / 1e9 / peak["hbm_gbs"]}}
+
+
 def measure_learnable(args):
     """BASELINE config 3: LearnableLayer(4096 -> 16000 DWN nodes, n=6), B=4096 binary inputs, loss = sum of outputs."""
     import torch
@@ -805,7 +842,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="train", choices=["train", "train-layers", "infer", "prob", "learnable", "conv", "nodes"],
+    ap.add_argument("--workload", default="train", choices=["train", "train-layers", "infer", "prob", "learnable", "conv", "nodes", "gather"],
                     help="train = the benchmark contract's workload; the others are secondary measurements")
     ap.add_argument("--small", action="store_true", help="reduced sizes of the secondary workloads (for ncu captures)")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
@@ -830,7 +867,8 @@ def main():
                os.path.abspath(__file__)] + sys.argv[1:]
         raise SystemExit(subprocess.call(cmd))
     measure = {"infer": measure_infer, "prob": measure_prob, "conv": measure_conv, "nodes": measure_nodes,
-               "learnable": measure_learnable, "train-layers": measure_train_layers}.get(args.workload)
+               "learnable": measure_learnable, "train-layers": measure_train_layers,
+               "gather": measure_gather}.get(args.workload)
     if measure is None:
         run_gpu_arm(args)
         return

@@ -780,6 +780,25 @@ def test_thermo_pack_interleaved_all_kernel_variants(dev, B, F):
     assert torch.equal(direct, via)
 
 
+@pytest.mark.parametrize("B,I,N,n", [(70, 300, 1000, 6), (33, 301, 1001, 5), (5, 6272, 2000, 6)])
+def test_gather_staged_kernels_vs_oracle(dev, B, I, N, n):
+    """`get_mapping` at sizes that take the shared-memory staged gather kernels (wide rows, with and without
+    16-byte alignment of the rows): the forward is an exact copy, the backward a segmented sum."""
+    from difflut_b200.layers.fused_ops import ConnectionPlan, GatherFunction
+
+    gen = torch.Generator().manual_seed(B + N)
+    idx = torch.randint(0, I, (N, n), generator=gen)
+    idx[:, 0] = torch.arange(N) % I  # every feature is read at least once when N >= I
+    plan = ConnectionPlan(idx, I, 1, dev)
+    x = torch.rand(B, I, generator=gen)
+    xg = x.to(dev).requires_grad_(True)
+    out = GatherFunction.apply(xg, plan)
+    assert torch.equal(out.cpu(), O.gather_mapping(x, idx))
+    g = torch.randn(B, N, n, generator=gen)
+    out.backward(g.to(dev))
+    close_normwise(xg.grad.cpu(), O.gather_mapping_backward(g, idx, I), "staged gather backward", tol=2e-6)
+
+
 # ------------------------------------------------------------------------------ tensor-core GEMM
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 320), (300, 500, 200), (1000, 777, 4096)])
 def test_gemm_bf16_tn_matches_fp32_matmul(dev, M, N, K):
