@@ -30,9 +30,12 @@ FEATURES, THERMO_BITS, CLASSES, TAU, GLOBAL_BATCH, LR = 784, 8, 10, 33.0, 8192, 
 METRIC = "train samples/s (fwd+bwd) 3-layer n=6 DWN"
 SCALING = "strong"
 # dram__bytes_read.sum + dram__bytes_write.sum of the three dl_dwn_bwd_fused_s launches of one step at
-# per-GPU batch 8192, from one ncu capture (profiles/dwn_bwd_fused_kernel_c4_B8192.txt); the traffic is
-# proportional to the batch (every term but the 7 MB of tables scales with it), so other batches scale it
-NCU_TRAFFIC_BWD_FUSED_B8192 = 827.6e6
+# per-GPU batch 8192, from one ncu capture (profiles/dwn_bwd_pipelined_kernel_c4_B8192.txt: two 1024-sample
+# blocks per item, which costs L2 hits: 1.41 x the algorithmic bytes; 827.6e6 = 1.07 x with one block per
+# item, the rule for batches that are not multiples of 2048).  The traffic is proportional to the batch
+# (every term but the 7 MB of tables scales with it), so other batches scale it
+NCU_TRAFFIC_BWD_FUSED_B8192 = 1087.4e6
+NCU_TRAFFIC_BWD_FUSED_B8192_ONE_BLOCK = 827.6e6
 WORKLOAD = "dwn3_16000-8000-4000_n6_T8_globalbatch8192_adam"
 
 
@@ -411,7 +414,11 @@ def run_gpu_arm(args):
             "bound": "hbm", "kernel": top_name, "launches_per_step": top_info["launches"],
             "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
             "frac": achieved / peak,
-            "traffic": (NCU_TRAFFIC_BWD_FUSED_B8192 * B / 8192.0) if top_name in ("dl_dwn_bwd_fused_t", "dl_dwn_bwd_fused_s") else None,
+            "traffic": ((NCU_TRAFFIC_BWD_FUSED_B8192 if B % 2048 == 0 and B >= 4096 else NCU_TRAFFIC_BWD_FUSED_B8192_ONE_BLOCK)
+                        * B / 8192.0) if top_name in ("dl_dwn_bwd_fused_t", "dl_dwn_bwd_fused_s") else None,
+            "lsu_pipe": {"what": "load/store data pipe of the SM (shuffles, shared memory, global loads): the resource "
+                                 "that bounds this kernel, from the ncu capture in profiles/",
+                         "busy_frac_largest_launch": 0.773, "wavefronts_per_node_and_1024_samples": 390},
             "algorithmic_bytes_per_launch_set": alg, "kernel_ms_per_step": top_info["ms"],
             "step_achieved_gbs": step_alg / (ms_per_step * 1e-3) / 1e9 * (1 if world == 1 else 1),
             "step_algorithmic_bytes": step_alg,
@@ -465,7 +472,7 @@ def collect_secondary(args):
     sub.steps, sub.warmup, sub.small = min(args.steps, 10), 3, False
     out = {}
     for key, fn in (("prob", measure_prob), ("learnable", measure_learnable), ("infer", measure_infer),
-                    ("train_layers", measure_train_layers), ("gather", measure_gather)):
+                    ("train_layers", measure_train_layers), ("gather", measure_gather), ("gemm", measure_gemm)):
         t0 = time.perf_counter()
         try:
             line = fn(sub)
@@ -716,6 +723,35 @@ def measure_gather(args):
                          "backward_frac": bytes_each / (bwd * 1e-3) / 1e9 / peak["hbm_gbs"]}}
 
 
+def measure_gemm(args):
+    """`dl_gemm_bf16_tn` alone (the tcgen05 + TMA contraction of the LearnableLayer path): C (4096 x 8192) fp32 =
+    A (4096 x 4096) * B (8192 x 4096)^T, bf16 operands; timed in isolation, so the burst cuBLAS figure is the peak."""
+    import torch
+
+    from difflut_b200 import _native
+
+    device = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(0)
+    M, N, K = 4096, 8192, 4096
+    A = torch.randn(M, K, generator=g).to(device).to(torch.bfloat16)
+    Bm = torch.randn(N, K, generator=g).to(device).to(torch.bfloat16)
+    C = torch.empty(M, N, device=device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    ms = _time_gpu(lambda: _native.call("dl_gemm_bf16_tn", A, Bm, C, M, N, K, status), args.steps, 3, flush)
+    if int(status.item()) != 0:
+        raise RuntimeError("a bounded wait inside dl_gemm_bf16_tn ran out")
+    tflops = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+    peak = _peaks()
+    return {"metric": "dl_gemm_bf16_tn TFLOP/s, 4096 x 8192 x 4096", "value": tflops, "unit": "TFLOP/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": 3, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"gemm_bf16_tn_{M}x{N}x{K}", "l2": "256 MB flush between timed calls"},
+            "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak["bf16_tflops"],
+                         "peak_source": peak["source"] + " (burst cuBLAS bf16)", "unit": "TFLOP/s",
+                         "frac": tflops / peak["bf16_tflops"], "traffic": None}}
+
+
 def measure_learnable(args):
     """BASELINE config 3: LearnableLayer(4096 -> 16000 DWN nodes, n=6), B=4096 binary inputs, loss = sum of outputs."""
     import torch
@@ -842,7 +878,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="train", choices=["train", "train-layers", "infer", "prob", "learnable", "conv", "nodes", "gather"],
+    ap.add_argument("--workload", default="train", choices=["train", "train-layers", "infer", "prob", "learnable", "conv", "nodes", "gather", "gemm"],
                     help="train = the benchmark contract's workload; the others are secondary measurements")
     ap.add_argument("--small", action="store_true", help="reduced sizes of the secondary workloads (for ncu captures)")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels eagerly instead of replaying a CUDA graph")
@@ -868,7 +904,7 @@ def main():
         raise SystemExit(subprocess.call(cmd))
     measure = {"infer": measure_infer, "prob": measure_prob, "conv": measure_conv, "nodes": measure_nodes,
                "learnable": measure_learnable, "train-layers": measure_train_layers,
-               "gather": measure_gather}.get(args.workload)
+               "gather": measure_gather, "gemm": measure_gemm}.get(args.workload)
     if measure is None:
         run_gpu_arm(args)
         return
