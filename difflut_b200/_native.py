@@ -61,6 +61,7 @@ SIGNATURES = {
     "dl_groupsum_t": "ppllfl s",
     "dl_dwn_fwd_groupsum_t": "ppppplllfl s",
     "dl_dwn_fwd_groupsum_s": "ppppplllfl s",
+    "dl_dwn_fwd_groupsum_ce_s": "pppppppplllflll s",
     "dl_dwn_bwd_fused_s": "pplfpllpppppppllll s",
     "dl_bits_swizzle_t": "ppll s",
     "dl_dwn_fwd_groupsum_noalloc_t": "pppplllfl s",

@@ -396,6 +396,67 @@ __global__ void groupsum_reduce_kernel(const float* __restrict__ partial, float*
     }
 }
 
+// The same reduction followed at once by the mean cross-entropy of the logits (the arithmetic of ce_t_kernel in
+// head.cu, same order: identical bits), one launch instead of two on the path from the last layer to the
+// backward kernels.  A CTA takes 32 samples; thread (class lane cl, sample lane) reduces the partial sums of
+// the classes cl, cl + 8, ... and leaves the logits in shared memory; the first warp then does the softmax
+// of its 32 samples.  k <= CE_MAX_CLASSES.
+constexpr int CE_MAX_CLASSES = 128;
+
+__global__ void __launch_bounds__(256)
+groupsum_reduce_ce_kernel(const float* __restrict__ partial, float* __restrict__ logits_t,
+                          const int32_t* __restrict__ labels, float* __restrict__ dlogits_t,
+                          float* __restrict__ loss_rows, int k, int S, float inv_tau, int64_t B, float inv_bg,
+                          int64_t Bp) {
+    extern __shared__ float lg[];  // [k][32]
+    const int lane = threadIdx.x & 31, cl = threadIdx.x >> 5;
+    for (int64_t b0 = (int64_t)blockIdx.x * 32; b0 < Bp; b0 += (int64_t)gridDim.x * 32) {
+        const int64_t b = b0 + lane;
+        __syncthreads();  // the previous 32 samples' logits are no longer read
+        for (int c = cl; c < k; c += 8) {
+            // eight loads in flight at a time; the additions keep their order, so the sum is unchanged
+            const float* src = partial + (int64_t)c * S * Bp + b;
+            float acc = 0.f;
+            int s = 0;
+            for (; s + 8 <= S; s += 8) {
+                float v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) v[u] = __ldg(src + (int64_t)(s + u) * Bp);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) acc += v[u];
+            }
+            for (; s < S; ++s) acc += __ldg(src + (int64_t)s * Bp);
+            const float logit = acc * inv_tau;
+            logits_t[(int64_t)c * Bp + b] = logit;
+            lg[c * 32 + lane] = logit;
+        }
+        __syncthreads();
+        if (cl != 0) continue;
+        if (b >= B) {
+            for (int c = 0; c < k; ++c) dlogits_t[(int64_t)c * Bp + b] = 0.f;
+            loss_rows[b] = 0.f;
+            continue;
+        }
+        float mx = -INFINITY;
+        for (int c = 0; c < k; ++c) mx = fmaxf(mx, lg[c * 32 + lane]);
+        float sum = 0.f;
+        for (int c = 0; c < k; ++c) sum += expf(lg[c * 32 + lane] - mx);
+        const float lse = mx + logf(sum);
+        const int y = labels[b];
+        if (y < 0 || y >= k) {  // no such class: no gradient, NaN loss (see dl_ce_t)
+            for (int c = 0; c < k; ++c) dlogits_t[(int64_t)c * Bp + b] = 0.f;
+            loss_rows[b] = __int_as_float(0x7fc00000);
+            continue;
+        }
+        const float inv = 1.0f / sum;
+        for (int c = 0; c < k; ++c) {
+            const float p = expf(lg[c * 32 + lane] - mx) * inv;
+            dlogits_t[(int64_t)c * Bp + b] = (p - (c == y ? 1.f : 0.f)) * inv_bg;
+        }
+        loss_rows[b] = lse - lg[y * 32 + lane];
+    }
+}
+
 // ------------------------------------------------------------------------------------------
 // backward: table gradient (histogram) and input gradient (segmented pull)
 // ------------------------------------------------------------------------------------------
@@ -1037,6 +1098,27 @@ DL_EXPORT int dl_dwn_fwd_groupsum_s(const uint32_t* in_bits_s, const int32_t* ma
                                     float* partial, float* logits_t, int64_t N, int64_t n, int64_t k,
                                     float tau, int64_t Bp, dl_stream_t stream) {
     return fwd_groupsum_entry(true, in_bits_s, map, tables, partial, logits_t, N, n, k, tau, Bp, stream);
+}
+
+DL_EXPORT int dl_dwn_fwd_groupsum_ce_s(const uint32_t* in_bits_s, const int32_t* map, const float* tables,
+                                       float* partial, float* logits_t, const int32_t* labels, float* dlogits_t,
+                                       float* loss_rows, int64_t N, int64_t n, int64_t k, float tau, int64_t B,
+                                       int64_t B_global, int64_t Bp, dl_stream_t stream) {
+    DL_REQUIRE(in_bits_s && map && tables && partial && logits_t && labels && dlogits_t && loss_rows);
+    DL_REQUIRE(N > 0 && k > 0 && tau > 0.f && B > 0 && B_global >= B && Bp >= B && Bp % DL_BATCH_ALIGN == 0);
+    DL_REQUIRE_ALIGNED(partial, 16);
+    if (n < 1 || n > DL_MAX_FAST_N || k > CE_MAX_CLASSES) return DL_ERR_UNSUPPORTED;
+    const int S = (int)dl_dwn_groupsum_splits(N, k);
+    const int64_t gsz = dl_ceil_div(N, k);
+    DL_REQUIRE(k * S <= 65535);
+    dim3 grid((unsigned)dl_ceil_div(Bp, 1024), (unsigned)(k * S));
+    dwn_fwd_groupsum_kernel<true><<<grid, 128, 0, dl_cast(stream)>>>(in_bits_s, map, tables, partial, N, (int)n, gsz, S,
+                                                                    Bp, dl_swizzled_words(Bp));
+    if (cudaPeekAtLastError() != cudaSuccess) return DL_ERR_LAUNCH;
+    const int64_t blocks = dl_min64(Bp / 32, (int64_t)DL_NUM_SMS * 8);
+    groupsum_reduce_ce_kernel<<<(unsigned)blocks, 256, (size_t)k * 32 * sizeof(float), dl_cast(stream)>>>(
+        partial, logits_t, labels, dlogits_t, loss_rows, (int)k, S, 1.0f / tau, B, (float)(1.0 / (double)B_global), Bp);
+    return dl_launch_status();
 }
 
 DL_EXPORT int dl_dwn_fwd_groupsum_noalloc_t(const uint32_t* in_bits_t, const int32_t* map, const float* tables,

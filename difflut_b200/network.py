@@ -227,16 +227,27 @@ class DWNNetwork:
         else:
             _native.call("dl_thermo_pack_t", x, self.thr, self.bits[0], B, self.F, self.T, self.Bp)
 
-    def _forward_layers(self) -> None:
+    def _forward_layers(self, with_loss=None) -> None:
+        """Hidden layers (bit-sliced) and the last layer fused with GroupSum; with `with_loss` = (B, B_global)
+        the kernel that reduces the class sums also does the cross-entropy (gradient of the logits and
+        per-sample losses), one launch fewer on the way to the backward."""
         Bp = self.Bp
         last = len(self.layers) - 1
         for li in range(last):
             # bit-sliced: indifferent to the sample order inside a row, only the row length matters
             _native.call("dl_dwn_fwd_bits_t", self.bits[li], self.plans[li].map_nodes, self.masks[li],
                          self.bits[li + 1], self.N[li], self.n[li], self.Bp_bits)
+        if with_loss is not None and self.swizzle and self.k <= 128:
+            _native.call("dl_dwn_fwd_groupsum_ce_s", self.bits[last], self.plans[last].map_nodes, self.tables[last],
+                         self.partial, self.logits_t, self.y_static, self.dlogits_t, self.loss_rows, self.N[last],
+                         self.n[last], self.k, self.tau, with_loss[0], with_loss[1], Bp)
+            return
         _native.call("dl_dwn_fwd_groupsum_s" if self.swizzle else "dl_dwn_fwd_groupsum_t", self.bits[last],
                      self.plans[last].map_nodes, self.tables[last], self.partial, self.logits_t, self.N[last],
                      self.n[last], self.k, self.tau, Bp)
+        if with_loss is not None:
+            _native.call("dl_ce_t", self.logits_t, self.y_static, self.dlogits_t, self.loss_rows, None,
+                         with_loss[0], with_loss[1], self.k, Bp)
 
     def _backward(self) -> None:
         if self.fused_backward:
@@ -334,9 +345,7 @@ class DWNNetwork:
             self._efd_ready.record(self._side)
         self._encode(self.x_static, B)
         main.wait_event(self._masks_ready)
-        self._forward_layers()
-        _native.call("dl_ce_t", self.logits_t, self.y_static, self.dlogits_t, self.loss_rows, None,
-                     B, B_global, self.k, self.Bp)
+        self._forward_layers(with_loss=(B, B_global))
         self._ce_done.record(main)
         with torch.cuda.stream(self._side):
             self._side.wait_event(self._ce_done)
@@ -398,7 +407,8 @@ class DWNNetwork:
             update = L if self.peer_per_layer else 1  # one exchange kernel per layer
         else:
             update = 4  # barrier, state advance, reduce+Adam+broadcast, barrier
-        return prepare + 1 + (L - 1) + 2 + 2 + backward + update
+        head = 3 if (self.swizzle and self.k <= 128) else 4  # last layer, reduce (+ cross-entropy), loss sum
+        return prepare + 1 + (L - 1) + head + backward + update
 
     def train_step(self, x: torch.Tensor, labels: torch.Tensor, use_graph: bool = False,
                    global_batch: Optional[int] = None) -> torch.Tensor:

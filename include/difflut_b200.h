@@ -355,6 +355,13 @@ int dl_bits_swizzle_t(const uint32_t* bits_t, uint32_t* bits_s, int64_t F, int64
 int dl_dwn_fwd_groupsum_s(const uint32_t* in_bits_s, const int32_t* map, const float* tables,
                           float* partial, float* logits_t, int64_t N, int64_t n, int64_t k, float tau,
                           int64_t Bp, dl_stream_t stream);
+/* dl_dwn_fwd_groupsum_s followed by dl_ce_t (loss == NULL) with one launch fewer: the kernel that reduces the
+ * partial class sums goes on to the softmax cross-entropy of the 32 samples it holds.  Same bits as the two
+ * calls.  k <= 128, else DL_ERR_UNSUPPORTED (nothing launched).  Form the scalar loss with dl_loss_sum. */
+int dl_dwn_fwd_groupsum_ce_s(const uint32_t* in_bits_s, const int32_t* map, const float* tables, float* partial,
+                             float* logits_t, const int32_t* labels, float* dlogits_t, float* loss_rows, int64_t N,
+                             int64_t n, int64_t k, float tau, int64_t B, int64_t B_global, int64_t Bp,
+                             dl_stream_t stream);
 int dl_dwn_bwd_fused_s(const uint8_t* addr_up, const float* g_up, int64_t gdiv_up, float gscale_up,
                        const float* efd_up, int64_t n_up, int64_t N_up, const int32_t* inv_ptr, const int32_t* inv_ent,
                        const uint32_t* in_bits_s, const int32_t* map, float* g_out, uint8_t* addr_out,

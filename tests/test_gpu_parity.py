@@ -712,6 +712,48 @@ def test_fused_backward_equals_separate_kernels_multi_group(dev, B, sizes):
         close_normwise(a, r, f"fused backward vs oracle, table gradient of layer {li + 1}")
 
 
+@pytest.mark.parametrize("B,k", [(1024, 10), (2500, 7), (200, 3)])
+def test_groupsum_ce_fused_entry_equals_separate_calls(dev, B, k):
+    """dl_dwn_fwd_groupsum_ce_s = dl_dwn_fwd_groupsum_s + dl_ce_t, bit for bit (logits, their gradient, per-sample
+    losses), with a ragged batch, a class count that does not divide the nodes and an out-of-range label."""
+    from difflut_b200 import _native
+    from difflut_b200.layers.fused_ops import ConnectionPlan
+    from difflut_b200.layers.random_layer import draw_random_mapping
+
+    gen = torch.Generator().manual_seed(B + k)
+    I, N, n, tau = 90, 101, 6, 2.5
+    Bp = _native.padded_batch(B)
+    Ws = int(_native.lib().dl_swizzled_words(Bp))
+    x = torch.rand(B, I, generator=gen).to(dev)
+    nat = torch.empty(I, Bp // 32, dtype=torch.int32, device=dev)
+    _native.call("dl_pack_rows_to_t", x, nat, B, I, Bp, 0.5)
+    bits = torch.empty(I, Ws, dtype=torch.int32, device=dev)
+    _native.call("dl_bits_swizzle_t", nat, bits, I, Bp)
+    plan = ConnectionPlan(draw_random_mapping(I, N, n, 3, True), I, 1, dev)
+    tab = torch.randn(N, 64, generator=gen).to(dev)
+    labels = torch.randint(0, k, (B,), generator=gen, dtype=torch.int32)
+    labels[1] = k + 5  # no such class
+    labels = labels.to(dev)
+    S = int(_native.lib().dl_dwn_groupsum_splits(N, k))
+    outs = []
+    for fused in (False, True):
+        partial = torch.empty(k * S, Bp, device=dev)
+        logits = torch.full((k, Bp), 7.0, device=dev)
+        dlog = torch.full((k, Bp), 7.0, device=dev)
+        rows = torch.full((Bp,), 7.0, device=dev)
+        if fused:
+            _native.call("dl_dwn_fwd_groupsum_ce_s", bits, plan.map_nodes, tab, partial, logits, labels, dlog, rows, N, n, k,
+                         tau, B, 3 * B, Bp)
+        else:
+            _native.call("dl_dwn_fwd_groupsum_s", bits, plan.map_nodes, tab, partial, logits, N, n, k, tau, Bp)
+            _native.call("dl_ce_t", logits, labels, dlog, rows, None, B, 3 * B, k, Bp)
+        outs.append((logits, dlog, rows))
+    for a, b in zip(outs[0], outs[1]):
+        assert torch.equal(torch.nan_to_num(a, nan=-1.0), torch.nan_to_num(b, nan=-1.0))
+    assert bool(torch.isnan(outs[1][2][1])) and not bool(outs[1][1][:, 1].any())  # the bad label: NaN loss, no gradient
+    assert not bool(outs[1][1][:, B:].any()) and not bool(outs[1][2][B:].any())  # padding: zeros
+
+
 @pytest.mark.parametrize("B", [128, 1024, 2500])
 def test_bits_swizzle_layout(dev, B):
     """Chunk-interleaved layout: bit c + 8r of word w of a 1024-sample block is sample 128c + 4w + r."""
