@@ -162,13 +162,21 @@ dwn_prepare_full_kernel(const float* __restrict__ tables, float* __restrict__ ef
 // bit-sliced hard forward
 // ------------------------------------------------------------------------------------------
 
+// The multiplier and addend of leaf `p` of a node's multiplexer tree (see MuxTree): (t1 - t0, -t0).
+__device__ __forceinline__ uint2 leaf_pair(uint64_t m, int p) {
+    const uint32_t t0 = (uint32_t)(m >> (2 * p)) & 1u, t1 = (uint32_t)(m >> (2 * p + 1)) & 1u;
+    return make_uint2(t1 - t0, 0u - t0);
+}
+
 // Depth-first evaluation of the 2^n -> 1 multiplexer tree on 4 words (128 samples) at once.
 // A leaf turns two adjacent truth-table bits into all-zero / all-one masks and selects with
 // input 0; every inner node is one select on input LVL.  BASE and LVL are compile-time, so
 // every shift is an immediate and the tree is 2^n - 1 three-input logic ops per word.
-// SMEM: the leaf masks come ready-made from shared memory (cm[p] = the all-zero / all-one masks of table
-// bits 2p and 2p+1, expanded once per node by the warp) instead of being re-derived by every thread,
-// which moves about a third of the kernel's logic ops off the integer pipe.
+// SMEM: the leaves come ready-made from shared memory, expanded once per node by the warp, and they are
+// evaluated as integer multiply-adds instead of logic ops: with table bits (t0, t1) a leaf is 0, s, ~s or
+// ~0, which is s * (t1 - t0) - t0 in 32-bit arithmetic (~s = -s - 1), so cm[p] = (t1 - t0, -t0) for table bits
+// 2p and 2p+1.  The kernels are bound by the integer-logic pipe (measured 78-81 % busy with all 63 selects of
+// a word on it); the 32 leaves of a word now go to the multiply-add pipe and 31 selects stay.
 template <int LVL, int BASE, bool SMEM>
 struct MuxTree {
     __device__ __forceinline__ static void eval(uint32_t lo, uint32_t hi, const uint2* cm, const uint4* x, uint4& out) {
@@ -185,17 +193,18 @@ struct MuxTree {
 template <int BASE, bool SMEM>
 struct MuxTree<0, BASE, SMEM> {
     __device__ __forceinline__ static void eval(uint32_t lo, uint32_t hi, const uint2* cm, const uint4* x, uint4& out) {
-        uint32_t c0, c1;
+        const uint4 s = x[0];
         if (SMEM) {
             const uint2 c = cm[BASE >> 1];
-            c0 = c.x;
-            c1 = c.y;
-        } else {
-            const uint32_t word = BASE < 32 ? lo : hi;
-            c0 = 0u - ((word >> (BASE & 31)) & 1u);
-            c1 = 0u - ((word >> ((BASE + 1) & 31)) & 1u);
+            out.x = s.x * c.x + c.y;
+            out.y = s.y * c.x + c.y;
+            out.z = s.z * c.x + c.y;
+            out.w = s.w * c.x + c.y;
+            return;
         }
-        const uint4 s = x[0];
+        const uint32_t word = BASE < 32 ? lo : hi;
+        const uint32_t c0 = 0u - ((word >> (BASE & 31)) & 1u);
+        const uint32_t c1 = 0u - ((word >> ((BASE + 1) & 31)) & 1u);
         out.x = (c0 & ~s.x) | (c1 & s.x);
         out.y = (c0 & ~s.y) | (c1 & s.y);
         out.z = (c0 & ~s.z) | (c1 & s.z);
@@ -224,7 +233,7 @@ dwn_fwd_bits_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __restr
             const uint64_t m = __ldg(&masks[j]);
             if (SMEM) {
                 __syncwarp();
-                cm[lane] = make_uint2(0u - (uint32_t)((m >> (2 * lane)) & 1u), 0u - (uint32_t)((m >> (2 * lane + 1)) & 1u));
+                cm[lane] = leaf_pair(m, lane);
                 __syncwarp();
                 if (q >= Q) continue;
             }
@@ -236,6 +245,52 @@ dwn_fwd_bits_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __restr
             MuxTree<NIN - 1, 0, SMEM>::eval((uint32_t)m, (uint32_t)(m >> 32), cm, x, o);
             reinterpret_cast<uint4*>(out_bits + (int64_t)j * Wp)[q] = o;
         }
+    }
+}
+
+// The same layer as a persistent kernel for batches of whole 4096-sample tiles.  A warp walks items
+// (tile of 32 word groups, node), tile-major so that the warps of the grid share one slab of input rows; while
+// the multiplexer tree of one item runs (252 logic ops per thread) the index row, the leaf mask and the six
+// 16-byte pieces of the next item are already on their way, so the integer pipe does not wait for L2.
+constexpr int FWD_STREAM_WARPS = 8;
+
+template <int NIN>
+__global__ void __launch_bounds__(FWD_STREAM_WARPS * 32, 2)
+dwn_fwd_bits_stream_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __restrict__ map,
+                           const uint64_t* __restrict__ masks, uint32_t* __restrict__ out_bits, int N, int Q) {
+    __shared__ uint2 cm_all[FWD_STREAM_WARPS][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint2* cm = cm_all[warp];
+    const int64_t Wp = (int64_t)Q << 2;
+    const uint32_t total = (uint32_t)(Q >> 5) * (uint32_t)N;
+    const uint32_t stride = gridDim.x * FWD_STREAM_WARPS;
+    uint32_t item = blockIdx.x * FWD_STREAM_WARPS + warp;
+    uint4 xn[NIN];
+    uint64_t mn = 0;
+    uint32_t jn = 0, qn = 0;
+    auto fetch = [&](uint32_t it) {
+        const uint32_t tile = it / (uint32_t)N;
+        jn = it - tile * (uint32_t)N;
+        qn = tile * 32 + lane;
+        mn = __ldg(&masks[jn]);
+#pragma unroll
+        for (int i = 0; i < NIN; ++i)
+            xn[i] = __ldg(reinterpret_cast<const uint4*>(in_bits + (int64_t)__ldg(&map[jn * NIN + i]) * Wp) + qn);
+    };
+    if (item < total) fetch(item);
+    for (; item < total; item += stride) {
+        uint4 x[NIN];
+#pragma unroll
+        for (int i = 0; i < NIN; ++i) x[i] = xn[i];
+        const uint64_t m = mn;
+        const uint32_t j = jn, q = qn;
+        if (item + stride < total) fetch(item + stride);
+        __syncwarp();  // the previous item's masks are no longer read
+        cm[lane] = leaf_pair(m, lane);
+        __syncwarp();
+        uint4 o;
+        MuxTree<NIN - 1, 0, true>::eval((uint32_t)m, (uint32_t)(m >> 32), cm, x, o);
+        reinterpret_cast<uint4*>(out_bits + (int64_t)j * Wp)[q] = o;
     }
 }
 
@@ -1004,6 +1059,15 @@ DL_EXPORT int dl_dwn_prepare_full(const float* tables, float* efd_full, int64_t 
     return dl_launch_status();
 }
 
+// DIFFLUT_FWD_STREAM=0 keeps the bit-sliced forward on the one-item-per-thread kernel (a measurement aid).
+static bool fwd_stream_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("DIFFLUT_FWD_STREAM");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 DL_EXPORT int dl_dwn_fwd_bits_t(const uint32_t* in_bits_t, const int32_t* map, const uint64_t* masks,
                                 uint32_t* out_bits_t, int64_t N, int64_t n, int64_t Bp,
                                 dl_stream_t stream) {
@@ -1024,6 +1088,14 @@ DL_EXPORT int dl_dwn_fwd_bits_t(const uint32_t* in_bits_t, const int32_t* map, c
     dim3 grid((unsigned)gn, (unsigned)gq);
     cudaStream_t s = dl_cast(stream);
     const int Ni = (int)N;
+    if (n == 6 && Q % 32 == 0 && (int64_t)(Q / 32) * N < ((int64_t)1 << 31) && fwd_stream_enabled()) {
+        // whole 4096-sample tiles: the persistent, software-pipelined kernel, two CTAs per SM
+        const int64_t items = (int64_t)(Q / 32) * N;
+        const int64_t blocks = dl_min64(dl_ceil_div(items, FWD_STREAM_WARPS), (int64_t)DL_NUM_SMS * 2);
+        dwn_fwd_bits_stream_kernel<6><<<(unsigned)blocks, FWD_STREAM_WARPS * 32, 0, s>>>(in_bits_t, map, masks, out_bits_t,
+                                                                                       Ni, Q);
+        return dl_launch_status();
+    }
 #define DL_FWD_BITS(NN)                                                                                      \
     do {                                                                                                     \
         if (bx >= 32)                                                                                        \
@@ -1065,6 +1137,23 @@ DL_EXPORT int64_t dl_dwn_groupsum_splits(int64_t N, int64_t k) {
     return s;
 }
 
+// Slices per class that a call really uses (<= dl_dwn_groupsum_splits, which sizes the caller's buffer): with
+// several 1024-sample groups fewer slices fill the GPU, and every slice costs a cross-warp reduction, 4 KB of
+// partial sums per group and one more term in the reduction pass.  DIFFLUT_GROUPSUM_SLICES fixes the count
+// (a measurement aid).
+static int groupsum_slices_used(int64_t N, int64_t k, int64_t Bp) {
+    static const int forced = [] {
+        const char* e = getenv("DIFFLUT_GROUPSUM_SLICES");
+        return e ? atoi(e) : 0;
+    }();
+    const int64_t cap = dl_dwn_groupsum_splits(N, k);
+    const int64_t groups = dl_ceil_div(Bp, 1024);
+    int64_t s = forced > 0 ? forced : dl_ceil_div((int64_t)DL_NUM_SMS * 16, groups * k);
+    if (s < 1) s = 1;
+    if (s > cap) s = cap;
+    return (int)s;
+}
+
 static int fwd_groupsum_entry(bool swz, const uint32_t* in_bits, const int32_t* map, const float* tables,
                              float* partial, float* logits_t, int64_t N, int64_t n, int64_t k, float tau,
                              int64_t Bp, dl_stream_t stream) {
@@ -1072,7 +1161,7 @@ static int fwd_groupsum_entry(bool swz, const uint32_t* in_bits, const int32_t* 
     DL_REQUIRE(Bp > 0 && Bp % DL_BATCH_ALIGN == 0);
     DL_REQUIRE_ALIGNED(partial, 16);
     if (n < 1 || n > DL_MAX_FAST_N) return DL_ERR_UNSUPPORTED;
-    const int S = (int)dl_dwn_groupsum_splits(N, k);
+    const int S = groupsum_slices_used(N, k, Bp);
     const int64_t gsz = dl_ceil_div(N, k);
     DL_REQUIRE(k * S <= 65535);
     dim3 grid((unsigned)dl_ceil_div(Bp, 1024), (unsigned)(k * S));
@@ -1108,7 +1197,7 @@ DL_EXPORT int dl_dwn_fwd_groupsum_ce_s(const uint32_t* in_bits_s, const int32_t*
     DL_REQUIRE(N > 0 && k > 0 && tau > 0.f && B > 0 && B_global >= B && Bp >= B && Bp % DL_BATCH_ALIGN == 0);
     DL_REQUIRE_ALIGNED(partial, 16);
     if (n < 1 || n > DL_MAX_FAST_N || k > CE_MAX_CLASSES) return DL_ERR_UNSUPPORTED;
-    const int S = (int)dl_dwn_groupsum_splits(N, k);
+    const int S = groupsum_slices_used(N, k, Bp);
     const int64_t gsz = dl_ceil_div(N, k);
     DL_REQUIRE(k * S <= 65535);
     dim3 grid((unsigned)dl_ceil_div(Bp, 1024), (unsigned)(k * S));

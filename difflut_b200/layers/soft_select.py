@@ -42,8 +42,10 @@ class SoftSelectFunction(torch.autograd.Function):
         bf = torch.bfloat16
         with torch.cuda.device(dev):
             # operands concatenated along K: A = [x_hi | x_hi | x_lo], Bm = [S_hi | S_lo | S_hi]
-            A = torch.zeros(B, splits * Ip, device=dev, dtype=bf)
-            Bm = torch.zeros(M, splits * Ip, device=dev, dtype=bf)
+            # with no K padding every element of both operands is written below: no 3 GB memset for config 3
+            alloc = torch.empty if Ip == I else torch.zeros
+            A = alloc(B, splits * Ip, device=dev, dtype=bf)
+            Bm = alloc(M, splits * Ip, device=dev, dtype=bf)
             ld = splits * Ip
             s_lo = Bm.data_ptr() + 2 * Ip if splits >= 2 else None
             _native.call("dl_softmax_rows_bf16", W, tau, Bm, s_lo, ld, M, I)
@@ -123,8 +125,10 @@ class SoftSelectTFunction(torch.autograd.Function):
         dev = x.device
         bf = torch.bfloat16
         with torch.cuda.device(dev):
-            A = torch.zeros(B, splits * Ip, device=dev, dtype=bf)
-            Bm = torch.zeros(M, splits * Ip, device=dev, dtype=bf)
+            # with no K padding every element of both operands is written below: no 3 GB memset for config 3
+            alloc = torch.empty if Ip == I else torch.zeros
+            A = alloc(B, splits * Ip, device=dev, dtype=bf)
+            Bm = alloc(M, splits * Ip, device=dev, dtype=bf)
             ld = splits * Ip
             s_lo = Bm.data_ptr() + 2 * Ip if splits >= 2 else None
             _native.call("dl_softmax_rows_bf16", W, tau, Bm, s_lo, ld, M, I)

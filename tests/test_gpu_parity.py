@@ -655,6 +655,32 @@ def test_full_size_properties(dev):
     assert torch.equal(outs[0][2][sl, :B].t().cpu().long(), ref_addr)
 
 
+@pytest.mark.parametrize("B", [4096, 12288, 5000])
+def test_bit_sliced_forward_whole_tiles_equals_oracle(dev, B):
+    """Batches of one and three whole 4096-sample tiles take the persistent kernel of dl_dwn_fwd_bits_t, the
+    ragged one the one-item-per-thread kernel: both against the oracle's eval forward (dwn_node.py:457-483),
+    bit for bit, with a node count that is no multiple of the grid's warp count."""
+    from difflut_b200 import _native
+    from difflut_b200.layers.random_layer import draw_random_mapping
+
+    gen = torch.Generator().manual_seed(B)
+    I, N = 100, 777
+    Bp = _native.padded_batch(B)
+    rows = (torch.rand(B, I, generator=gen) > 0.5).float()
+    idx = draw_random_mapping(I, N, 6, 3, True)
+    tab = torch.randn(N, 64, generator=gen)
+    bits = torch.empty(I, Bp // 32, device=dev, dtype=torch.int32)
+    _native.call("dl_pack_rows_to_t", rows.to(dev), bits, B, I, Bp, 0.5)
+    masks = torch.empty(N, device=dev, dtype=torch.int64)
+    _native.call("dl_dwn_prepare", tab.to(dev), None, masks, N, 6, 0.0, 0.0)
+    hard = torch.full((N, Bp // 32), -1, device=dev, dtype=torch.int32)
+    _native.call("dl_dwn_fwd_bits_t", bits, idx.to(device=dev, dtype=torch.int32).contiguous(), masks, hard, N, 6, Bp)
+    got = torch.empty(B, N, device=dev)
+    _native.call("dl_bits_t_to_rows", hard, got, B, N, Bp)
+    want = O.dwn_forward_eval(O.gather_mapping(rows, idx), tab.unsqueeze(1)).reshape(B, N)
+    assert torch.equal(got.cpu(), want)
+
+
 def test_error_codes(dev):
     from difflut_b200 import _native
 
