@@ -249,48 +249,84 @@ dwn_fwd_bits_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __restr
 }
 
 // The same layer as a persistent kernel for batches of whole 4096-sample tiles.  A warp walks items
-// (tile of 32 word groups, node), tile-major so that the warps of the grid share one slab of input rows; while
-// the multiplexer tree of one item runs (252 logic ops per thread) the index row, the leaf mask and the six
-// 16-byte pieces of the next item are already on their way, so the integer pipe does not wait for L2.
+// (tile of 32 word groups, node), tile-major so that the warps of the grid share one slab of input rows.
+// Two stages of loads run ahead of the multiplexer tree: the index row and leaf mask of the item after next
+// (one value per lane, handed out by shuffles) and the six 16-byte pieces of the next item, so the tree of
+// one item (128 multiply-adds and 124 selects per thread) never waits for a dependent pair of L2 round trips.
+// The two register sets swap roles every item (the loop body is written out twice), so nothing is copied.
 constexpr int FWD_STREAM_WARPS = 8;
 
-template <int NIN>
-__global__ void __launch_bounds__(FWD_STREAM_WARPS * 32, 2)
+template <int NIN, int CTAS>
+__global__ void __launch_bounds__(FWD_STREAM_WARPS * 32, CTAS)
 dwn_fwd_bits_stream_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __restrict__ map,
                            const uint64_t* __restrict__ masks, uint32_t* __restrict__ out_bits, int N, int Q) {
     __shared__ uint2 cm_all[FWD_STREAM_WARPS][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     uint2* cm = cm_all[warp];
     const int64_t Wp = (int64_t)Q << 2;
-    const uint32_t total = (uint32_t)(Q >> 5) * (uint32_t)N;
+    const uint32_t tiles = (uint32_t)Q >> 5, nodes = (uint32_t)N;
     const uint32_t stride = gridDim.x * FWD_STREAM_WARPS;
-    uint32_t item = blockIdx.x * FWD_STREAM_WARPS + warp;
-    uint4 xn[NIN];
-    uint64_t mn = 0;
-    uint32_t jn = 0, qn = 0;
-    auto fetch = [&](uint32_t it) {
-        const uint32_t tile = it / (uint32_t)N;
-        jn = it - tile * (uint32_t)N;
-        qn = tile * 32 + lane;
-        mn = __ldg(&masks[jn]);
-#pragma unroll
-        for (int i = 0; i < NIN; ++i)
-            xn[i] = __ldg(reinterpret_cast<const uint4*>(in_bits + (int64_t)__ldg(&map[jn * NIN + i]) * Wp) + qn);
+    const uint32_t* masks32 = reinterpret_cast<const uint32_t*>(masks);
+
+    // the frontier of the item sequence of this warp: (tile tf, node jf)
+    uint32_t tf, jf;
+    {
+        const uint32_t first = blockIdx.x * FWD_STREAM_WARPS + warp;
+        tf = first / nodes;
+        jf = first - tf * nodes;
+    }
+    // index data of the frontier item, one value per lane (lanes 0..NIN-1 the input rows, then the two halves
+    // of the leaf mask); afterwards the frontier moves on by one stride
+    auto take = [&](uint32_t& j, uint32_t& q, uint32_t& meta) -> bool {
+        const bool ok = tf < tiles;
+        j = jf;
+        q = tf * 32 + lane;
+        meta = 0;
+        if (ok) {
+            if (lane < NIN) meta = (uint32_t)__ldg(&map[jf * NIN + lane]);
+            else if (lane < NIN + 2) meta = __ldg(&masks32[2 * jf + (lane - NIN)]);
+        }
+        jf += stride;
+        while (jf >= nodes) {
+            jf -= nodes;
+            ++tf;
+        }
+        return ok;
     };
-    if (item < total) fetch(item);
-    for (; item < total; item += stride) {
-        uint4 x[NIN];
+    auto load_x = [&](uint4 (&x)[NIN], uint32_t meta, uint32_t q) {
 #pragma unroll
-        for (int i = 0; i < NIN; ++i) x[i] = xn[i];
-        const uint64_t m = mn;
-        const uint32_t j = jn, q = qn;
-        if (item + stride < total) fetch(item + stride);
-        __syncwarp();  // the previous item's masks are no longer read
-        cm[lane] = leaf_pair(m, lane);
+        for (int i = 0; i < NIN; ++i) {
+            const uint32_t row = __shfl_sync(0xffffffffu, meta, i);
+            x[i] = __ldg(reinterpret_cast<const uint4*>(in_bits + (int64_t)row * Wp) + q);
+        }
+    };
+    auto compute = [&](const uint4 (&x)[NIN], uint32_t meta, uint32_t j, uint32_t q) {
+        const uint32_t lo = __shfl_sync(0xffffffffu, meta, NIN), hi = __shfl_sync(0xffffffffu, meta, NIN + 1);
+        __syncwarp();  // the previous item's leaves are no longer read
+        cm[lane] = leaf_pair(((uint64_t)hi << 32) | lo, lane);
         __syncwarp();
         uint4 o;
-        MuxTree<NIN - 1, 0, true>::eval((uint32_t)m, (uint32_t)(m >> 32), cm, x, o);
+        MuxTree<NIN - 1, 0, true>::eval(lo, hi, cm, x, o);
         reinterpret_cast<uint4*>(out_bits + (int64_t)j * Wp)[q] = o;
+    };
+
+    uint4 xa[NIN], xb[NIN];
+    uint32_t ja, qa, ma, jb, qb, mb, jc, qc, mc;
+    if (!take(ja, qa, ma)) return;
+    bool okb = take(jb, qb, mb);
+    load_x(xa, ma, qa);
+    while (true) {
+        bool okc = take(jc, qc, mc);           // two items ahead: index data
+        if (okb) load_x(xb, mb, qb);           // one item ahead: input words
+        compute(xa, ma, ja, qa);
+        if (!okb) break;
+        okb = take(ja, qa, ma);
+        if (okc) load_x(xa, mc, qc);
+        compute(xb, mb, jb, qb);
+        if (!okc) break;
+        // roles for the next round: a = the item whose words were just requested, b = the one whose index data was
+        jb = ja; qb = qa; mb = ma;
+        ja = jc; qa = qc; ma = mc;
     }
 }
 
@@ -353,13 +389,16 @@ dwn_fwd_vals_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __restr
 // chunks of the group get their words by shuffle, and 32 running sums (8 chunks x 4 samples) stay
 // in registers; the next node's words are loaded before the current node is consumed.
 // SWZ: chunk-interleaved input bits (see dl_bits_swizzle_t): the lane's own word holds its samples.
-template <bool SWZ>
+// NFIX: the node width as a compile-time constant (0 = read it from `n_arg`), which removes the per-input
+// predicates from the address formation.
+template <bool SWZ, int NFIX>
 __global__ void __launch_bounds__(128)
 dwn_fwd_groupsum_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __restrict__ map,
                         const float* __restrict__ tables, float* __restrict__ partial, int64_t N,
-                        int n, int64_t gsz, int S, int64_t Bp, int64_t Wp) {
+                        int n_arg, int64_t gsz, int S, int64_t Bp, int64_t Wp) {
     __shared__ float4 red[3][8][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n = NFIX > 0 ? NFIX : n_arg;
     const int L = 1 << n;
     const int64_t grp = blockIdx.x;  // 1024-sample group
     const int64_t cls = blockIdx.y / (unsigned)S, s = blockIdx.y % (unsigned)S;
@@ -388,26 +427,28 @@ dwn_fwd_groupsum_kernel(const uint32_t* __restrict__ in_bits, const int32_t* __r
             for (int i = 0; i < DL_MAX_FAST_N; ++i)
                 nxt[i] = (i < n && wvalid) ? __ldg(in_bits + (int64_t)__ldg(&map[(j + 4) * n + i]) * Wp + w) : 0u;
         }
-        const float* tj = tables + j * L;
+        const char* tj = reinterpret_cast<const char*>(tables + j * L);
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
+            // four table offsets in bytes, one per byte of `a` (addresses < 64, so address * 4 stays inside its byte)
             uint32_t a = 0;
 #pragma unroll
             for (int i = 0; i < DL_MAX_FAST_N; ++i) {
                 if (i < n) {
                     if (SWZ) {
-                        const uint32_t t = c >= i ? words[i] >> (c - i) : words[i] << (i - c);
-                        a |= t & (0x01010101u << i);
+                        const uint32_t t = c >= i + 2 ? words[i] >> (c - i - 2) : words[i] << (i + 2 - c);
+                        a |= t & (0x04040404u << i);
                     } else {
                         const uint32_t t = __shfl_sync(0xffffffffu, words[i], c * 4 + src_lane) >> sh;
-                        a |= dl_spread_nibble(t & 0xFu) << i;
+                        a |= dl_spread_nibble(t & 0xFu) << (i + 2);
                     }
                 }
             }
-            acc[c].x += __ldg(tj + (a & 0xFF));
-            acc[c].y += __ldg(tj + ((a >> 8) & 0xFF));
-            acc[c].z += __ldg(tj + ((a >> 16) & 0xFF));
-            acc[c].w += __ldg(tj + (a >> 24));
+            // one byte extract and one 64-bit add per look-up
+            acc[c].x += __ldg(reinterpret_cast<const float*>(tj + __byte_perm(a, 0, 0x4440)));
+            acc[c].y += __ldg(reinterpret_cast<const float*>(tj + __byte_perm(a, 0, 0x4441)));
+            acc[c].z += __ldg(reinterpret_cast<const float*>(tj + __byte_perm(a, 0, 0x4442)));
+            acc[c].w += __ldg(reinterpret_cast<const float*>(tj + __byte_perm(a, 0, 0x4443)));
         }
     }
     if (warp > 0) {
@@ -1059,13 +1100,16 @@ DL_EXPORT int dl_dwn_prepare_full(const float* tables, float* efd_full, int64_t 
     return dl_launch_status();
 }
 
-// DIFFLUT_FWD_STREAM=0 keeps the bit-sliced forward on the one-item-per-thread kernel (a measurement aid).
-static bool fwd_stream_enabled() {
-    static const bool on = [] {
+// Resident CTAs per SM of the persistent bit-sliced forward kernel.  DIFFLUT_FWD_STREAM=0 keeps the layer on the
+// one-item-per-thread kernel, =2 / =3 pick the build (measurement aids).
+static int fwd_stream_ctas() {
+    static const int ctas = [] {
         const char* e = getenv("DIFFLUT_FWD_STREAM");
-        return !(e && e[0] == '0');
+        if (e && e[0] == '0') return 0;
+        if (e && e[0] == '3') return 3;
+        return 2;
     }();
-    return on;
+    return ctas;
 }
 
 DL_EXPORT int dl_dwn_fwd_bits_t(const uint32_t* in_bits_t, const int32_t* map, const uint64_t* masks,
@@ -1088,12 +1132,17 @@ DL_EXPORT int dl_dwn_fwd_bits_t(const uint32_t* in_bits_t, const int32_t* map, c
     dim3 grid((unsigned)gn, (unsigned)gq);
     cudaStream_t s = dl_cast(stream);
     const int Ni = (int)N;
-    if (n == 6 && Q % 32 == 0 && (int64_t)(Q / 32) * N < ((int64_t)1 << 31) && fwd_stream_enabled()) {
-        // whole 4096-sample tiles: the persistent, software-pipelined kernel, two CTAs per SM
+    if (n == 6 && Q % 32 == 0 && (int64_t)(Q / 32) * N < ((int64_t)1 << 31) && fwd_stream_ctas() > 0) {
+        // whole 4096-sample tiles: the persistent, software-pipelined kernel
         const int64_t items = (int64_t)(Q / 32) * N;
-        const int64_t blocks = dl_min64(dl_ceil_div(items, FWD_STREAM_WARPS), (int64_t)DL_NUM_SMS * 2);
-        dwn_fwd_bits_stream_kernel<6><<<(unsigned)blocks, FWD_STREAM_WARPS * 32, 0, s>>>(in_bits_t, map, masks, out_bits_t,
-                                                                                       Ni, Q);
+        const int ctas = fwd_stream_ctas();
+        const int64_t blocks = dl_min64(dl_ceil_div(items, FWD_STREAM_WARPS), (int64_t)DL_NUM_SMS * ctas);
+        if (ctas == 3)
+            dwn_fwd_bits_stream_kernel<6, 3><<<(unsigned)blocks, FWD_STREAM_WARPS * 32, 0, s>>>(in_bits_t, map, masks,
+                                                                                              out_bits_t, Ni, Q);
+        else
+            dwn_fwd_bits_stream_kernel<6, 2><<<(unsigned)blocks, FWD_STREAM_WARPS * 32, 0, s>>>(in_bits_t, map, masks,
+                                                                                              out_bits_t, Ni, Q);
         return dl_launch_status();
     }
 #define DL_FWD_BITS(NN)                                                                                      \
@@ -1154,6 +1203,9 @@ static int groupsum_slices_used(int64_t N, int64_t k, int64_t Bp) {
     return (int)s;
 }
 
+// the six-input build of the kernel when it applies, else the one that reads n at run time
+#define DL_GROUPSUM_LAUNCH(SWZ) (n == 6 ? dwn_fwd_groupsum_kernel<SWZ, 6> : dwn_fwd_groupsum_kernel<SWZ, 0>)
+
 static int fwd_groupsum_entry(bool swz, const uint32_t* in_bits, const int32_t* map, const float* tables,
                              float* partial, float* logits_t, int64_t N, int64_t n, int64_t k, float tau,
                              int64_t Bp, dl_stream_t stream) {
@@ -1166,10 +1218,10 @@ static int fwd_groupsum_entry(bool swz, const uint32_t* in_bits, const int32_t* 
     DL_REQUIRE(k * S <= 65535);
     dim3 grid((unsigned)dl_ceil_div(Bp, 1024), (unsigned)(k * S));
     if (swz)
-        dwn_fwd_groupsum_kernel<true><<<grid, 128, 0, dl_cast(stream)>>>(in_bits, map, tables, partial, N, (int)n, gsz,
+        DL_GROUPSUM_LAUNCH(true)<<<grid, 128, 0, dl_cast(stream)>>>(in_bits, map, tables, partial, N, (int)n, gsz,
                                                                         S, Bp, dl_swizzled_words(Bp));
     else
-        dwn_fwd_groupsum_kernel<false><<<grid, 128, 0, dl_cast(stream)>>>(in_bits, map, tables, partial, N, (int)n,
+        DL_GROUPSUM_LAUNCH(false)<<<grid, 128, 0, dl_cast(stream)>>>(in_bits, map, tables, partial, N, (int)n,
                                                                          gsz, S, Bp, Bp / 32);
     if (cudaPeekAtLastError() != cudaSuccess) return DL_ERR_LAUNCH;
     groupsum_reduce_kernel<<<grid_for(k * Bp, 256), 256, 0, dl_cast(stream)>>>(partial, logits_t, (int)k, S,
@@ -1201,7 +1253,7 @@ DL_EXPORT int dl_dwn_fwd_groupsum_ce_s(const uint32_t* in_bits_s, const int32_t*
     const int64_t gsz = dl_ceil_div(N, k);
     DL_REQUIRE(k * S <= 65535);
     dim3 grid((unsigned)dl_ceil_div(Bp, 1024), (unsigned)(k * S));
-    dwn_fwd_groupsum_kernel<true><<<grid, 128, 0, dl_cast(stream)>>>(in_bits_s, map, tables, partial, N, (int)n, gsz, S,
+    DL_GROUPSUM_LAUNCH(true)<<<grid, 128, 0, dl_cast(stream)>>>(in_bits_s, map, tables, partial, N, (int)n, gsz, S,
                                                                     Bp, dl_swizzled_words(Bp));
     if (cudaPeekAtLastError() != cudaSuccess) return DL_ERR_LAUNCH;
     const int64_t blocks = dl_min64(Bp / 32, (int64_t)DL_NUM_SMS * 8);
