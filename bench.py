@@ -477,7 +477,7 @@ def collect_secondary(args):
         try:
             line = fn(sub)
             keep = {k: line[k] for k in ("metric", "value", "unit", "ms_per_step", "dtype", "roofline", "e2e", "dwn_stack",
-                                         "backward_ms")
+                                         "backward_ms", "two_piece_split")
                     if k in line}
             keep["workload"] = line["config"]["workload"]
             if key == "infer":
@@ -770,15 +770,22 @@ def measure_learnable(args):
     with torch.no_grad():
         layer.mapping.W.copy_((torch.randn(N * 6, I, generator=g) * 0.01).to(device))
         layer.luts.copy_(torch.randn(N, 1, 64, generator=g).to(device))
-    ss.FORWARD_SPLITS = 2  # binary inputs are exact in bf16: head + residual of the softmax only
-
+    # Forward precision.  The headline uses the centred single pass (bf16 of softmax - 1/I, the rank-one term
+    # sum(x)/I exact through three extra K columns): for this workload (binary inputs, weights N(0, 0.01), i.e.
+    # a near-uniform selection whose results sit at the nodes' 0.5 threshold) its error against float64 is
+    # 3e-6, against 9e-7 for the two-piece split and 2e-4 for plain bf16.  The two-piece split (K doubled) is
+    # timed beside it.
     def step():
         layer.mapping.W.grad = None
         layer.luts.grad = None
         layer(x).sum().backward()
 
+    ss.FORWARD_SPLITS = "centered"
     ms = _time_gpu(step, max(2, args.steps // 4), 2, None)
-    gemm_flops = 2.0 * B * I * (N * 6) * (2 + 1)  # forward with K doubled by the split, one backward GEMM (x needs no grad)
+    ss.FORWARD_SPLITS = 2
+    ms_split = _time_gpu(step, max(2, args.steps // 4), 2, None)
+    ss.FORWARD_SPLITS = "centered"
+    gemm_flops = 2.0 * B * (N * 6) * ((I + 64) + I)  # forward over I + 64 columns, one backward GEMM (x needs no grad)
     return {"metric": "train samples/s (fwd+bwd) LearnableLayer 4096 -> 16000 DWN n=6",
                       "value": B / (ms * 1e-3), "unit": "samples/s", "n_gpus": 1, "steps": max(2, args.steps // 4),
                       "warmup": 2, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -787,7 +794,10 @@ def measure_learnable(args):
                                    "peak": _peaks()["bf16_tflops_sustained"], "peak_source": _peaks()["source"] + " (sustained cuBLAS bf16)",
                                    "unit": "TFLOP/s", "frac": gemm_flops / (ms * 1e-3) / 1e12 / _peaks()["bf16_tflops_sustained"],
                                    "traffic": None,
-                                   "note": "whole step (softmax, conversions, DWN kernels included) against the GEMM flops"}}
+                                   "note": "whole step (softmax, conversions, DWN kernels included) against the GEMM flops; "
+                                           "forward = centred single bf16 pass"},
+            "two_piece_split": {"ms_per_step": ms_split, "value": B / (ms_split * 1e-3),
+                                "note": "forward with the softmax split into bf16 head + residual (K doubled)"}}
 
 
 def measure_train_layers(args):

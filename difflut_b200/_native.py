@@ -40,6 +40,7 @@ SIGNATURES = {
     "dl_dwn_fwd_vals_t": "ppppplll s",
     "dl_dwn_bwd_tables_t": "ppplfpplll s",
     "dl_dwn_bwd_input_t": "pplfpppplll s",
+    "dl_dwn_bwd_input_disjoint_t": "pplfpppllll s",
     "dl_dwn_bwd_fused_t": "pplfpllpppppppllll s",
     "dl_sum_groups": "pplll s",
     "dl_dwn_mapped_fwd": "ppplllli s",
@@ -53,6 +54,8 @@ SIGNATURES = {
     "dl_seg_sum_t": "ppppll s",
     "dl_gemm_bf16_tn": "ppplllp s",
     "dl_softmax_rows_bf16": "pfpplll s",
+    "dl_softmax_rows_centered_bf16": "pfplllll s",
+    "dl_row_sum_split_bf16": "pllllfl s",
     "dl_softmax_bwd_rows": "ppfpll s",
     "dl_f32_to_bf16": "pppllli s",
     "dl_bf16_transpose": "ppllll s",

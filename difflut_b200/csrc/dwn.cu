@@ -8,6 +8,8 @@
 #include <cstdlib>
 #include <mutex>
 
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 
 namespace {
@@ -647,6 +649,60 @@ dwn_bwd_input_kernel(const uint8_t* __restrict__ addr_t, const float* __restrict
         }
         acc.x *= gscale; acc.y *= gscale; acc.z *= gscale; acc.w *= gscale;
         *reinterpret_cast<float4*>(gx_t + f * Bp + b) = acc;
+    }
+}
+
+// The same input gradient for a connection map in which no input feature has more than one reader (the
+// identity map a LearnableLayer's soft selection feeds: node j reads features j*n .. j*n+n-1).  Nothing has to
+// be summed, so the work is turned around: one warp per (node, 1024-sample slab) loads the node's gradient and
+// addresses once and writes its n input-gradient rows, instead of one warp per (feature, chunk) chasing the
+// inverse map through four dependent loads.  BF16: the rows leave as bf16 (round to nearest), which is what the
+// weight-gradient contraction of the soft selection reads.
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+dwn_bwd_input_disjoint_kernel(const uint8_t* __restrict__ addr_t, const float* __restrict__ g_t, uint32_t ugdiv,
+                              float gscale, const float* __restrict__ efd_t, const int32_t* __restrict__ map,
+                              void* __restrict__ out, int64_t NO, int n, int64_t Bp) {
+    const int lane = threadIdx.x & 31;
+    const int64_t C = Bp >> 7, G = (C + 7) >> 3;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t item = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; item < G * NO; item += nwarps) {
+        const int64_t cg = item / NO, j = item - cg * NO;
+        float tv[DL_MAX_FAST_N];
+        int64_t row[DL_MAX_FAST_N];
+#pragma unroll
+        for (int i = 0; i < DL_MAX_FAST_N; ++i) {
+            tv[i] = i < n ? gscale * __ldg(efd_t + (j * n + i) * 32 + lane) : 0.f;
+            row[i] = i < n ? (int64_t)__ldg(map + j * n + i) : 0;
+        }
+        const int64_t grow = ugdiv == 1 ? j : (int64_t)((uint32_t)j / ugdiv);
+        const int64_t c1 = (cg + 1) * 8 < C ? (cg + 1) * 8 : C;
+        for (int64_t c = cg * 8; c < c1; ++c) {
+            const int64_t b = (c << 7) + lane * 4;
+            const uint32_t a = __ldg(reinterpret_cast<const uint32_t*>(addr_t + j * Bp + b));
+            const float4 g = __ldg(reinterpret_cast<const float4*>(g_t + grow * Bp + b));
+#pragma unroll
+            for (int i = 0; i < DL_MAX_FAST_N; ++i) {
+                if (i < n) {
+                    const uint32_t lowm = ((1u << i) - 1u) * 0x01010101u;
+                    const uint32_t a5 = (a & lowm) | ((a >> 1) & ~lowm & 0x7F7F7F7Fu);
+                    float4 r;
+                    r.x = g.x * __shfl_sync(0xffffffffu, tv[i], a5);
+                    r.y = g.y * __shfl_sync(0xffffffffu, tv[i], a5 >> 8);
+                    r.z = g.z * __shfl_sync(0xffffffffu, tv[i], a5 >> 16);
+                    r.w = g.w * __shfl_sync(0xffffffffu, tv[i], a5 >> 24);
+                    if (BF16) {
+                        const __nv_bfloat162 lo = __floats2bfloat162_rn(r.x, r.y), hi = __floats2bfloat162_rn(r.z, r.w);
+                        uint2 pk;
+                        pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+                        pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+                        *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(out) + row[i] * Bp + b) = pk;
+                    } else {
+                        *reinterpret_cast<float4*>(static_cast<float*>(out) + row[i] * Bp + b) = r;
+                    }
+                }
+            }
+        }
     }
 }
 
@@ -1309,6 +1365,26 @@ DL_EXPORT int dl_dwn_bwd_input_t(const uint8_t* addr_t, const float* g_t, int64_
     const int blocks = (int)(want < (int64_t)DL_NUM_SMS * 5 ? want : (int64_t)DL_NUM_SMS * 5);
     dwn_bwd_input_kernel<<<blocks, 256, 0, dl_cast(stream)>>>(addr_t, g_t, gdiv, gscale, efd_t, inv_ptr,
                                                              inv_ent, gx_t, F, (int)n, Bp, cps);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_dwn_bwd_input_disjoint_t(const uint8_t* addr_t, const float* g_t, int64_t gdiv, float gscale,
+                                          const float* efd_t, const int32_t* map, void* gx_t, int64_t out_bf16,
+                                          int64_t NO, int64_t n, int64_t Bp, dl_stream_t stream) {
+    DL_REQUIRE(addr_t && g_t && efd_t && map && gx_t && NO > 0 && gdiv > 0 && gdiv < ((int64_t)1 << 31));
+    DL_REQUIRE(Bp > 0 && Bp % DL_BATCH_ALIGN == 0);
+    DL_REQUIRE_ALIGNED(addr_t, 4);
+    DL_REQUIRE_ALIGNED(g_t, 16);
+    DL_REQUIRE_ALIGNED(gx_t, 16);
+    if (n < 1 || n > DL_MAX_FAST_N) return DL_ERR_UNSUPPORTED;
+    const int64_t items = NO * dl_ceil_div(Bp / 128, 8);
+    const int64_t blocks = dl_min64(dl_ceil_div(items, 8), (int64_t)DL_NUM_SMS * 32);
+    if (out_bf16)
+        dwn_bwd_input_disjoint_kernel<true><<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(
+            addr_t, g_t, (uint32_t)gdiv, gscale, efd_t, map, gx_t, NO, (int)n, Bp);
+    else
+        dwn_bwd_input_disjoint_kernel<false><<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(
+            addr_t, g_t, (uint32_t)gdiv, gscale, efd_t, map, gx_t, NO, (int)n, Bp);
     return dl_launch_status();
 }
 

@@ -322,9 +322,9 @@ __device__ __forceinline__ float block_reduce(float v, float* scratch, bool is_m
     return r;
 }
 
-// one CTA per row: S = softmax(W / tau) written as bf16 hi (+ optional lo = bf16(S - hi))
+// one CTA per row: S = softmax(W / tau) - center written as bf16 hi (+ optional lo = bf16(S - hi))
 __global__ void __launch_bounds__(256)
-softmax_rows_kernel(const float* __restrict__ W, float inv_tau, __nv_bfloat16* __restrict__ S_hi,
+softmax_rows_kernel(const float* __restrict__ W, float inv_tau, float center, __nv_bfloat16* __restrict__ S_hi,
                     __nv_bfloat16* __restrict__ S_lo, int64_t ld_out, int64_t I) {
     __shared__ float scratch[8];
     const int64_t row = blockIdx.x;
@@ -337,7 +337,7 @@ softmax_rows_kernel(const float* __restrict__ W, float inv_tau, __nv_bfloat16* _
     sum = block_reduce(sum, scratch, false);
     const float inv = 1.0f / sum;
     for (int64_t i = threadIdx.x; i < I; i += blockDim.x) {
-        const float s = expf(w[i] * inv_tau - mx) * inv;
+        const float s = expf(w[i] * inv_tau - mx) * inv - center;
         const __nv_bfloat16 hi = __float2bfloat16(s);
         S_hi[row * ld_out + i] = hi;
         if (S_lo != nullptr) S_lo[row * ld_out + i] = __float2bfloat16(s - __bfloat162float(hi));
@@ -384,7 +384,7 @@ __device__ __forceinline__ uint2 pack_bf16x4(float a, float b, float c, float d)
 }
 
 __global__ void __launch_bounds__(256)
-softmax_rows_vec_kernel(const float* __restrict__ W, float inv_tau, __nv_bfloat16* __restrict__ S_hi,
+softmax_rows_vec_kernel(const float* __restrict__ W, float inv_tau, float center, __nv_bfloat16* __restrict__ S_hi,
                         __nv_bfloat16* __restrict__ S_lo, int64_t ld_out, int I4) {
     __shared__ float scratch[8];
     const int64_t row = blockIdx.x;
@@ -416,7 +416,8 @@ softmax_rows_vec_kernel(const float* __restrict__ W, float inv_tau, __nv_bfloat1
     for (int k = 0; k < SM_MAXQ; ++k) {
         const int q = threadIdx.x + k * 256;
         if (q < I4) {
-            const float a = v[k].x * inv, b = v[k].y * inv, c = v[k].z * inv, d = v[k].w * inv;
+            const float a = v[k].x * inv - center, b = v[k].y * inv - center, c = v[k].z * inv - center,
+                        d = v[k].w * inv - center;
             const uint2 hi = pack_bf16x4(a, b, c, d);
             *reinterpret_cast<uint2*>(S_hi + row * ld_out + 4 * q) = hi;
             if (S_lo != nullptr) {
@@ -570,18 +571,90 @@ DL_EXPORT int dl_gemm_bf16_tn(const void* A, const void* B, float* C, int64_t M,
     return dl_launch_status();
 }
 
-DL_EXPORT int dl_softmax_rows_bf16(const float* W, float tau, void* S_hi, void* S_lo, int64_t ld_out, int64_t M,
-                                   int64_t I, dl_stream_t stream) {
-    DL_REQUIRE(W && S_hi && M > 0 && I > 0 && tau > 0.f && ld_out >= I);
+static int softmax_rows_launch(const float* W, float tau, float center, void* S_hi, void* S_lo, int64_t ld_out,
+                               int64_t M, int64_t I, dl_stream_t stream) {
     const bool aligned = reinterpret_cast<uintptr_t>(W) % 16 == 0 && reinterpret_cast<uintptr_t>(S_hi) % 8 == 0 &&
                          (S_lo == nullptr || reinterpret_cast<uintptr_t>(S_lo) % 8 == 0);
     if (aligned && I % 4 == 0 && ld_out % 4 == 0 && I <= 256 * 4 * SM_MAXQ) {
-        softmax_rows_vec_kernel<<<(unsigned)M, 256, 0, dl_cast(stream)>>>(
-            W, 1.0f / tau, static_cast<__nv_bfloat16*>(S_hi), static_cast<__nv_bfloat16*>(S_lo), ld_out, (int)(I / 4));
+        softmax_rows_vec_kernel<<<(unsigned)M, 256, 0, dl_cast(stream)>>>(W, 1.0f / tau, center,
+                                                                        static_cast<__nv_bfloat16*>(S_hi),
+                                                                        static_cast<__nv_bfloat16*>(S_lo), ld_out,
+                                                                        (int)(I / 4));
         return dl_launch_status();
     }
-    softmax_rows_kernel<<<(unsigned)M, 256, 0, dl_cast(stream)>>>(W, 1.0f / tau, static_cast<__nv_bfloat16*>(S_hi),
+    softmax_rows_kernel<<<(unsigned)M, 256, 0, dl_cast(stream)>>>(W, 1.0f / tau, center,
+                                                                 static_cast<__nv_bfloat16*>(S_hi),
                                                                  static_cast<__nv_bfloat16*>(S_lo), ld_out, I);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_softmax_rows_bf16(const float* W, float tau, void* S_hi, void* S_lo, int64_t ld_out, int64_t M,
+                                   int64_t I, dl_stream_t stream) {
+    DL_REQUIRE(W && S_hi && M > 0 && I > 0 && tau > 0.f && ld_out >= I);
+    return softmax_rows_launch(W, tau, 0.f, S_hi, S_lo, ld_out, M, I, stream);
+}
+
+// Centred single-pass operands.  A softmax row sums to one, so S = 1/I + D with small D when the selection is
+// close to uniform, which is when the contraction's result sits near the 0.5 threshold of the nodes that read it:
+//   x . S^T = (sum_i x_i) / I + x . D^T.
+// D is what bf16 rounds (its error is relative to D, not to S), and the first term enters the same GEMM
+// through three extra K columns: the row of D carries 1, 1, 1 there and the row of x its own sum / I as a
+// three-piece bf16 split (24 bits).  The two entry points below write those columns.
+__global__ void fill_ones_cols_kernel(__nv_bfloat16* __restrict__ S, int64_t ld, int64_t M, int64_t col0, int ones,
+                                      int ext) {
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < M * ext;
+         t += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = t / ext;
+        const int c = (int)(t - row * ext);
+        S[row * ld + col0 + c] = __float2bfloat16(c < ones ? 1.0f : 0.0f);
+    }
+}
+
+// one warp per row: fixed-order sum of the row's bf16 values, times `scale`, split into three bf16 pieces
+__global__ void __launch_bounds__(256)
+row_sum_split_kernel(__nv_bfloat16* __restrict__ A, int64_t ld, int64_t rows, int64_t cols, int64_t col0, float scale,
+                     int ext) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (row >= rows) return;
+    const __nv_bfloat16* a = A + row * ld;
+    float acc = 0.f;
+    for (int64_t i = lane; i < cols; i += 32) acc += __bfloat162float(a[i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    const float t = acc * scale;
+    const __nv_bfloat16 p0 = __float2bfloat16(t);
+    const float r1 = t - __bfloat162float(p0);
+    const __nv_bfloat16 p1 = __float2bfloat16(r1);
+    const __nv_bfloat16 p2 = __float2bfloat16(r1 - __bfloat162float(p1));
+    for (int c = lane; c < ext; c += 32) {
+        __nv_bfloat16 v = __float2bfloat16(0.f);
+        if (c == 0) v = p0;
+        else if (c == 1) v = p1;
+        else if (c == 2) v = p2;
+        A[row * ld + col0 + c] = v;
+    }
+}
+
+DL_EXPORT int dl_softmax_rows_centered_bf16(const float* W, float tau, void* S_c, int64_t ld_out, int64_t M, int64_t I,
+                                            int64_t ext_col, int64_t ext, dl_stream_t stream) {
+    DL_REQUIRE(W && S_c && M > 0 && I > 0 && tau > 0.f && ext >= 3 && ext <= 1024 && ext_col >= I &&
+               ld_out >= ext_col + ext);
+    const int rc = softmax_rows_launch(W, tau, 1.0f / (float)I, S_c, nullptr, ld_out, M, I, stream);
+    if (rc != DL_OK) return rc;
+    const int64_t blocks = dl_min64(dl_ceil_div(M * ext, 256), (int64_t)DL_NUM_SMS * 8);
+    fill_ones_cols_kernel<<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(static_cast<__nv_bfloat16*>(S_c), ld_out, M,
+                                                                       ext_col, 3, (int)ext);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_row_sum_split_bf16(void* A, int64_t ld, int64_t rows, int64_t cols, int64_t ext_col, float scale,
+                                    int64_t ext, dl_stream_t stream) {
+    DL_REQUIRE(A && rows > 0 && cols > 0 && ext >= 3 && ext <= 1024 && ext_col >= cols && ld >= ext_col + ext);
+    const int64_t blocks = dl_ceil_div(rows * 32, 256);
+    DL_REQUIRE(blocks < ((int64_t)1 << 31));
+    row_sum_split_kernel<<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(static_cast<__nv_bfloat16*>(A), ld, rows, cols,
+                                                                      ext_col, scale, (int)ext);
     return dl_launch_status();
 }
 

@@ -112,7 +112,18 @@ class PatchGeometry:
 
 class FeatureMajorInput:
     """Marks the input of DWNLayerFunction as fp32 feature-major (I, B) with B a multiple of 128 (what a
-    contraction with swapped operands produces); the input gradient comes back in the same layout."""
+    contraction with swapped operands produces); the input gradient comes back in the same layout.
+
+    The marker doubles as a private channel between the two autograd functions of a LearnableLayer: when the
+    producer of the input (soft_select_t) sets `want_bf16`, the layer function leaves the input gradient as a
+    bf16 (I, B) tensor in `grad_bf16` (the dtype the weight-gradient contraction reads, written once by the
+    node kernel instead of fp32 + a conversion pass) and hands autograd a zero-stride placeholder of the right
+    shape, which the producer's backward ignores.  Only for disjoint connection plans (`disjoint`)."""
+
+    def __init__(self, disjoint: bool = False):
+        self.disjoint = disjoint
+        self.want_bf16 = False
+        self.grad_bf16 = None
 
 
 class PatchFunction(torch.autograd.Function):
@@ -208,6 +219,17 @@ class DWNLayerFunction(torch.autograd.Function):
                 gt = gt * (sc.reshape(gt.shape[0], gt.shape[1], 1) if isinstance(sc, torch.Tensor) else float(sc))
             if need_x:
                 efd = _efd_tables(tables, NO, n, ctx.alpha, ctx.beta, ctx.stable_scale)
+                if isinstance(geom, FeatureMajorInput) and geom.disjoint:
+                    # every feature has one reader: node-major kernel, bf16 rows if the producer asked for them
+                    as_bf16 = geom.want_bf16
+                    gx_t = torch.empty(I, Bp, device=g.device, dtype=torch.bfloat16 if as_bf16 else torch.float32)
+                    _native.call("dl_dwn_bwd_input_disjoint_t", addr, g_t, 1, 1.0, efd, plan.map_virtual, gx_t,
+                                 1 if as_bf16 else 0, NO, n, Bp)
+                    if as_bf16:
+                        geom.grad_bf16 = gx_t
+                        return (torch.zeros(1, 1, device=g.device).expand(I, Bp), (gt if need_t else None),
+                                None, None, None, None, None)
+                    return gx_t, (gt if need_t else None), None, None, None, None, None
                 gx_t = torch.empty(I, Bp, device=g.device, dtype=torch.float32)
                 _native.call("dl_dwn_bwd_input_t", addr, g_t, 1, 1.0, efd, plan.inv_ptr_virtual,
                              plan.inv_ent8_virtual, gx_t, I, n, Bp)

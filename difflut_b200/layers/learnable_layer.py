@@ -153,12 +153,15 @@ class LearnableLayer(BaseLUTLayer):
         from .fused_ops import DWNLayerFunction, FeatureMajorInput
         from .soft_select import soft_select_t
 
-        mapped_t = soft_select_t(x, self.mapping.W, self.mapping.tau)
+        # the identity plan is disjoint (one reader per selected value) and with one output per node the plan's
+        # virtual nodes are its nodes: the node kernel can then hand the gradient over as bf16 (see FeatureMajorInput)
+        channel = FeatureMajorInput(disjoint=self.output_dim_per_node == 1)
+        mapped_t = soft_select_t(x, self.mapping.W, self.mapping.tau, grad_channel=channel if channel.disjoint else None)
         plan = _identity_plan(self.output_size, self.n, self.output_dim_per_node, x.device)
         if self._stacked == "dwn":
-            return DWNLayerFunction.apply(mapped_t, self.luts, plan, self.alpha, self.beta, None, FeatureMajorInput())
+            return DWNLayerFunction.apply(mapped_t, self.luts, plan, self.alpha, self.beta, None, channel)
         scales = self.gradient_scale.detach().float().repeat_interleave(self.output_dim_per_node)
-        return DWNLayerFunction.apply(mapped_t, self.stable_tables(), plan, 0.0, 0.0, scales, FeatureMajorInput())
+        return DWNLayerFunction.apply(mapped_t, self.stable_tables(), plan, 0.0, 0.0, scales, channel)
 
     def get_mapping_matrix(self) -> torch.Tensor:
         with torch.no_grad():

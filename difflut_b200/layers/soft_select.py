@@ -11,6 +11,14 @@ bf16 head and a bf16 residual and the products head*head + head*residual (+ resi
 summed by concatenating the pieces along K of one GEMM.  `FORWARD_SPLITS` picks the number of
 pieces: 1 = plain bf16, 2 = split the softmax only (exact when x is exactly representable in bf16,
 e.g. binary inputs), 3 = split both (default).  The backward GEMMs use plain bf16 (1e-2 bar).
+
+`FORWARD_SPLITS = "centered"` is a single-pass alternative for the regime that matters for the threshold:
+a softmax row sums to one, so `S = 1/I + D` and `x @ S.T = sum(x)/I + x @ D.T`; bf16 rounds D (error
+relative to the deviation from a uniform selection, tiny while the selection is soft and the node inputs
+sit near 0.5), and `sum(x)/I` enters the same GEMM exactly through three extra K columns
+(`dl_softmax_rows_centered_bf16`, `dl_row_sum_split_bf16`).  Half the forward tensor-core work of 2; x
+itself is rounded to bf16 (exact for binary inputs); once the selection is sharp its error is that of plain
+bf16, where the selected values are far from the threshold.
 """
 
 import torch
@@ -18,6 +26,7 @@ import torch
 from .. import _native
 
 FORWARD_SPLITS = 3
+_CENTER_EXT = 64  # extra K columns of the centred form (three used): one K block, so the row pitch stays a multiple of 128 bytes
 
 
 def _round_up(v: int, m: int) -> int:
@@ -28,6 +37,40 @@ def _check_status(status: torch.Tensor, what: str) -> None:
     code = int(status.item())
     if code != 0:
         raise RuntimeError(f"dl_gemm_bf16_tn ({what}): a bounded wait inside the kernel ran out (status {code:#x})")
+
+
+def _forward_operands(x, W, tau, splits):
+    """bf16 operands of the forward contraction, pieces concatenated along K: A (B, ld) from x and Bm (M, ld) from
+    softmax(W / tau).  splits 1..3: A = [x_hi | x_hi | x_lo], Bm = [S_hi | S_lo | S_hi]; 0 (centred):
+    A = [x | split(sum(x)/I), 0...], Bm = [S - 1/I | 1, 1, 1, 0...]."""
+    B, I = x.shape
+    M = W.shape[0]
+    Ip = _round_up(I, 8)
+    dev, bf = x.device, torch.bfloat16
+    # with no K padding every element of both operands is written below: no 3 GB memset for config 3
+    alloc = torch.empty if Ip == I else torch.zeros
+    if splits == 0:
+        Ic = _round_up(I, _CENTER_EXT)  # the extension starts on a K-block boundary
+        ld = Ic + _CENTER_EXT
+        alloc = torch.empty if Ic == I else torch.zeros
+        A = alloc(B, ld, device=dev, dtype=bf)
+        Bm = alloc(M, ld, device=dev, dtype=bf)
+        _native.call("dl_softmax_rows_centered_bf16", W, tau, Bm, ld, M, I, Ic, _CENTER_EXT)
+        _native.call("dl_f32_to_bf16", x, A, None, B, I, ld, 0)
+        _native.call("dl_row_sum_split_bf16", A, ld, B, I, Ic, 1.0 / I, _CENTER_EXT)
+        return A, Bm, ld
+    ld = splits * Ip
+    A = alloc(B, ld, device=dev, dtype=bf)
+    Bm = alloc(M, ld, device=dev, dtype=bf)
+    s_lo = Bm.data_ptr() + 2 * Ip if splits >= 2 else None
+    _native.call("dl_softmax_rows_bf16", W, tau, Bm, s_lo, ld, M, I)
+    x_lo = A.data_ptr() + 2 * 2 * Ip if splits >= 3 else None
+    _native.call("dl_f32_to_bf16", x, A, x_lo, B, I, ld, 0)
+    if splits >= 2:
+        A[:, Ip:Ip + I].copy_(A[:, :I])
+    if splits >= 3:
+        Bm[:, 2 * Ip:2 * Ip + I].copy_(Bm[:, :I])
+    return A, Bm, ld
 
 
 class SoftSelectFunction(torch.autograd.Function):
@@ -42,19 +85,7 @@ class SoftSelectFunction(torch.autograd.Function):
         bf = torch.bfloat16
         with torch.cuda.device(dev):
             # operands concatenated along K: A = [x_hi | x_hi | x_lo], Bm = [S_hi | S_lo | S_hi]
-            # with no K padding every element of both operands is written below: no 3 GB memset for config 3
-            alloc = torch.empty if Ip == I else torch.zeros
-            A = alloc(B, splits * Ip, device=dev, dtype=bf)
-            Bm = alloc(M, splits * Ip, device=dev, dtype=bf)
-            ld = splits * Ip
-            s_lo = Bm.data_ptr() + 2 * Ip if splits >= 2 else None
-            _native.call("dl_softmax_rows_bf16", W, tau, Bm, s_lo, ld, M, I)
-            x_lo = A.data_ptr() + 2 * 2 * Ip if splits >= 3 else None
-            _native.call("dl_f32_to_bf16", x, A, x_lo, B, I, ld, 0)
-            if splits >= 2:
-                A[:, Ip:Ip + I].copy_(A[:, :I])
-            if splits >= 3:
-                Bm[:, 2 * Ip:2 * Ip + I].copy_(Bm[:, :I])
+            A, Bm, ld = _forward_operands(x, W, tau, splits)
             out = torch.empty(B, M, device=dev, dtype=torch.float32)
             status = torch.zeros(1, device=dev, dtype=torch.int32)
             _native.call("dl_gemm_bf16_tn", A, Bm, out, B, M, ld, status)
@@ -114,30 +145,22 @@ class SoftSelectTFunction(torch.autograd.Function):
     B must be a multiple of 128."""
 
     @staticmethod
-    def forward(ctx, x, W, tau, splits, check):
+    def forward(ctx, x, W, tau, splits, check, grad_channel=None):
         x = x.contiguous().float()
         W = W.contiguous().float()
         B, I = x.shape
         M = W.shape[0]
         if B % 128 != 0:
             raise ValueError("soft_select_t needs a batch that is a multiple of 128")
+        # a consumer that can write its input gradient as bf16 (M, B) leaves it in the channel (FeatureMajorInput)
+        ctx.grad_channel = grad_channel
+        if grad_channel is not None:
+            grad_channel.want_bf16 = True
         Ip = _round_up(I, 8)
         dev = x.device
         bf = torch.bfloat16
         with torch.cuda.device(dev):
-            # with no K padding every element of both operands is written below: no 3 GB memset for config 3
-            alloc = torch.empty if Ip == I else torch.zeros
-            A = alloc(B, splits * Ip, device=dev, dtype=bf)
-            Bm = alloc(M, splits * Ip, device=dev, dtype=bf)
-            ld = splits * Ip
-            s_lo = Bm.data_ptr() + 2 * Ip if splits >= 2 else None
-            _native.call("dl_softmax_rows_bf16", W, tau, Bm, s_lo, ld, M, I)
-            x_lo = A.data_ptr() + 2 * 2 * Ip if splits >= 3 else None
-            _native.call("dl_f32_to_bf16", x, A, x_lo, B, I, ld, 0)
-            if splits >= 2:
-                A[:, Ip:Ip + I].copy_(A[:, :I])
-            if splits >= 3:
-                Bm[:, 2 * Ip:2 * Ip + I].copy_(Bm[:, :I])
+            A, Bm, ld = _forward_operands(x, W, tau, splits)
             out_t = torch.empty(M, B, device=dev, dtype=torch.float32)
             status = torch.zeros(1, device=dev, dtype=torch.int32)
             _native.call("dl_gemm_bf16_tn", Bm, A, out_t, M, B, ld, status)
@@ -154,20 +177,27 @@ class SoftSelectTFunction(torch.autograd.Function):
         M = W.shape[0]
         dev = x.device
         bf = torch.bfloat16
-        gy_t = gy_t.contiguous().float()  # (M, B)
+        channel = ctx.grad_channel
+        gyb = None
+        from_channel = channel is not None and channel.grad_bf16 is not None
+        if from_channel:
+            gyb, channel.grad_bf16 = channel.grad_bf16, None  # (M, B) bf16 from the consumer; gy_t is a placeholder
+        else:
+            gy_t = gy_t.contiguous().float()  # (M, B)
         need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         gx = gW = None
         with torch.cuda.device(dev):
             status = torch.zeros(1, device=dev, dtype=torch.int32)
             if need_w:
                 # gS (M, I) = gy_t (M, K=B) @ x (B, I): operands gy_t [M, K=B] as it is and x^T [I, K=B]
-                gyb = torch.empty(M, B, device=dev, dtype=bf)
-                _native.call("dl_f32_to_bf16", gy_t, gyb, None, M, B, B, 0)
+                if gyb is None:
+                    gyb = torch.empty(M, B, device=dev, dtype=bf)
+                    _native.call("dl_f32_to_bf16", gy_t, gyb, None, M, B, B, 0)
                 xt = torch.zeros(I, B, device=dev, dtype=bf)
                 _native.call("dl_f32_to_bf16", x, xt, None, B, I, B, 1)
                 gS = torch.empty(M, I, device=dev, dtype=torch.float32)
                 _native.call("dl_gemm_bf16_tn", gyb, xt, gS, M, I, B, status)
-                del gyb, xt
+                del xt
                 gW = torch.empty(M, I, device=dev, dtype=torch.float32)
                 _native.call("dl_softmax_bwd_rows", W, gS, ctx.tau, gW, M, I)
             if need_x:
@@ -179,23 +209,36 @@ class SoftSelectTFunction(torch.autograd.Function):
                 _native.call("dl_bf16_transpose", S, St, M, I, I, Mp)
                 del S
                 gyr = torch.zeros(B, Mp, device=dev, dtype=bf)
-                _native.call("dl_f32_to_bf16", gy_t, gyr, None, M, B, Mp, 1)
+                if from_channel:
+                    _native.call("dl_bf16_transpose", gyb, gyr, M, B, B, Mp)
+                else:
+                    _native.call("dl_f32_to_bf16", gy_t, gyr, None, M, B, Mp, 1)
                 gx = torch.empty(B, I, device=dev, dtype=torch.float32)
                 _native.call("dl_gemm_bf16_tn", gyr, St, gx, B, I, Mp, status)
             if ctx.check:
                 _check_status(status, "backward")
-        return gx, gW, None, None, None
+        return gx, gW, None, None, None, None
 
 
-def soft_select_t(x: torch.Tensor, W: torch.Tensor, tau: float, splits: int = None, check: bool = True) -> torch.Tensor:
-    """(B, I), (M, I) -> (M, B) feature-major with autograd (B a multiple of 128); see soft_select."""
-    if not (x.is_cuda and W.is_cuda):
-        raise RuntimeError("difflut_b200 layers run on CUDA tensors only (no CPU fallback)")
+def _splits_code(splits) -> int:
     if splits is None:
         splits = FORWARD_SPLITS
+    if splits == "centered":
+        return 0
     if splits not in (1, 2, 3):
-        raise ValueError("splits must be 1, 2 or 3")
-    return SoftSelectTFunction.apply(x, W, float(tau), int(splits), bool(check))
+        raise ValueError('splits must be 1, 2, 3 or "centered"')
+    return int(splits)
+
+
+def soft_select_t(x: torch.Tensor, W: torch.Tensor, tau: float, splits: int = None, check: bool = True,
+                  grad_channel=None) -> torch.Tensor:
+    """(B, I), (M, I) -> (M, B) feature-major with autograd (B a multiple of 128); see soft_select.
+    `grad_channel`: a `fused_ops.FeatureMajorInput` shared with the one consumer of the result, through which
+    that consumer may hand its input gradient over as bf16."""
+    if not (x.is_cuda and W.is_cuda):
+        raise RuntimeError("difflut_b200 layers run on CUDA tensors only (no CPU fallback)")
+    splits = _splits_code(splits)
+    return SoftSelectTFunction.apply(x, W, float(tau), int(splits), bool(check), grad_channel)
 
 
 def soft_select(x: torch.Tensor, W: torch.Tensor, tau: float, splits: int = None, check: bool = True) -> torch.Tensor:
@@ -203,8 +246,5 @@ def soft_select(x: torch.Tensor, W: torch.Tensor, tau: float, splits: int = None
     host synchronisation per call); pass False inside a captured or latency-critical region."""
     if not (x.is_cuda and W.is_cuda):
         raise RuntimeError("difflut_b200 layers run on CUDA tensors only (no CPU fallback)")
-    if splits is None:
-        splits = FORWARD_SPLITS
-    if splits not in (1, 2, 3):
-        raise ValueError("splits must be 1, 2 or 3")
+    splits = _splits_code(splits)
     return SoftSelectFunction.apply(x, W, float(tau), int(splits), bool(check))

@@ -350,6 +350,9 @@ class DWNNetwork:
         with torch.cuda.stream(self._side):
             self._side.wait_event(self._ce_done)
             _native.call("dl_loss_sum", self.loss_rows, self.loss, B_global, self.Bp)
+            if not self.peer_optimizer:
+                # the optimiser's step counter and bias corrections advance here, off the critical path
+                _native.call("dl_adam_advance", self.adam_state, self.betas[0], self.betas[1])
             self._side_done.record(self._side)
         main.wait_event(self._efd_ready)
         fused_exchange = self.peer_optimizer and self.peer_fused and self.peer_per_layer and self.fused_backward
@@ -384,7 +387,8 @@ class DWNNetwork:
                     self._pending = []
                 else:
                     allreduce_sum_(self.flat_grad, self.group)
-            _native.call("dl_adam_step", self.flat, self.flat_grad, self.exp_avg, self.exp_avg_sq, self.adam_state,
+            main.wait_event(self._side_done)
+            _native.call("dl_adam_apply", self.flat, self.flat_grad, self.exp_avg, self.exp_avg_sq, self.adam_state,
                          count, self.lr, self.betas[0], self.betas[1], self.eps, 1.0)
         main.wait_event(self._side_done)
 

@@ -171,6 +171,14 @@ int dl_dwn_bwd_tables_t(const uint32_t* in_bits_t, const int32_t* map, const flo
 int dl_dwn_bwd_input_t(const uint8_t* addr_t, const float* g_t, int64_t gdiv, float gscale,
                        const float* efd_t, const int32_t* inv_ptr, const int32_t* inv_ent,
                        float* gx_t, int64_t F, int64_t n, int64_t Bp, dl_stream_t stream);
+/* The same gradient for a connection map in which every input feature has at most one reader (e.g. the
+ * identity map behind a LearnableLayer's soft selection: node j reads features j*n .. j*n+n-1): one warp per
+ * (node, 1024 samples) writes the node's n input-gradient rows, gx_t[map[j*n+i]][b]; rows that no node reads
+ * are not written.  out_bf16 != 0: gx_t is bf16 [F][Bp] (round to nearest) instead of fp32.  The caller
+ * guarantees that the map is disjoint. */
+int dl_dwn_bwd_input_disjoint_t(const uint8_t* addr_t, const float* g_t, int64_t gdiv, float gscale,
+                                const float* efd_t, const int32_t* map, void* gx_t, int64_t out_bf16, int64_t NO,
+                                int64_t n, int64_t Bp, dl_stream_t stream);
 
 /* Fused backward of one layer of a stack (same arithmetic as dl_dwn_bwd_input_t of the layer
  * above followed by dl_dwn_bwd_tables_t of this layer, in one pass).  One warp handles 1024
@@ -285,6 +293,17 @@ int dl_gemm_bf16_tn(const void* A, const void* B, float* C, int64_t M, int64_t N
  * receives bf16(S - S_hi) so that S_hi + S_lo carries 16 mantissa bits. */
 int dl_softmax_rows_bf16(const float* W, float tau, void* S_hi, void* S_lo, int64_t ld_out, int64_t M,
                          int64_t I, dl_stream_t stream);
+
+/* Centred single-pass operands of the same contraction: S_c[row, 0..I) = bf16(softmax(W/tau) - 1/I) and
+ * S_c[row, ext_col .. ext_col+ext) = 1, 1, 1, 0, ...; dl_row_sum_split_bf16 writes the matching columns of the
+ * other operand: A[row, ext_col .. ext_col+ext) = the three-piece bf16 split of scale * sum(A[row, 0..cols)),
+ * then zeros (scale = 1/I).  With both, dl_gemm_bf16_tn over K = ext_col + ext gives x . softmax^T with the
+ * rounding error of bf16 relative to the deviation from a uniform selection instead of to the weights
+ * themselves.  3 <= ext <= 1024; a row pitch that is a multiple of 128 bytes keeps the GEMM's tile loads aligned.  Same reference lines as dl_softmax_rows_bf16. */
+int dl_softmax_rows_centered_bf16(const float* W, float tau, void* S_c, int64_t ld_out, int64_t M, int64_t I,
+                                  int64_t ext_col, int64_t ext, dl_stream_t stream);
+int dl_row_sum_split_bf16(void* A, int64_t ld, int64_t rows, int64_t cols, int64_t ext_col, float scale, int64_t ext,
+                          dl_stream_t stream);
 /* gW = S * (gS - rowsum(gS * S)) / tau, S recomputed from W in fp32. */
 int dl_softmax_bwd_rows(const float* W, const float* gS, float tau, float* gW, int64_t M, int64_t I,
                         dl_stream_t stream);

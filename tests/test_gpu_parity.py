@@ -912,6 +912,72 @@ def test_soft_select_matches_fp32_reference(dev):
     torch.testing.assert_close(out2, xb @ torch.softmax(W.detach(), -1).t(), rtol=2e-5, atol=2e-5)
 
 
+def test_input_gradient_for_a_disjoint_map_equals_the_general_kernel(dev):
+    """dl_dwn_bwd_input_disjoint_t (one warp per node and 1024 samples, for maps in which every feature has one
+    reader) against dl_dwn_bwd_input_t on the identity map: the same bits in fp32, and its bf16 output is the
+    fp32 result rounded to nearest.  Ragged last slab (B = 1408 = 11 chunks)."""
+    from difflut_b200 import _native
+    from difflut_b200.layers.fused_ops import ConnectionPlan
+
+    gen = torch.Generator().manual_seed(21)
+    B, N, n = 1408, 333, 6
+    I = N * n
+    Bp = _native.padded_batch(B)
+    plan = ConnectionPlan(torch.arange(I).view(N, n), I, 1, dev)
+    tab = torch.randn(N, 64, generator=gen).to(dev)
+    efd = torch.empty(N, n, 32, device=dev)
+    _native.call("dl_dwn_prepare", tab, efd, None, N, n, 0.1, 1 / 3)
+    addr = torch.randint(0, 64, (N, Bp), generator=gen, dtype=torch.uint8).to(dev)
+    g_t = torch.randn(N, Bp, generator=gen).to(dev)
+    want = torch.empty(I, Bp, device=dev)
+    _native.call("dl_dwn_bwd_input_t", addr, g_t, 1, 1.0, efd, plan.inv_ptr_virtual, plan.inv_ent8_virtual, want, I, n, Bp)
+    got = torch.full((I, Bp), float("nan"), device=dev)
+    _native.call("dl_dwn_bwd_input_disjoint_t", addr, g_t, 1, 1.0, efd, plan.map_virtual, got, 0, N, n, Bp)
+    assert torch.equal(got, want)
+    got16 = torch.empty(I, Bp, device=dev, dtype=torch.bfloat16)
+    _native.call("dl_dwn_bwd_input_disjoint_t", addr, g_t, 1, 1.0, efd, plan.map_virtual, got16, 1, N, n, Bp)
+    assert torch.equal(got16, want.to(torch.bfloat16))
+
+
+def test_soft_select_centred_single_pass(dev):
+    """The centred single-pass form of the soft selection (`splits="centered"`): inside the 1e-2 bar of the
+    tensor-core contraction for any weights, and for a near-uniform selection (weights N(0, 0.01), binary
+    inputs: the regime of the LearnableLayer benchmark, where the result sits near the nodes' 0.5 threshold)
+    within a small factor of the two-piece split's distance to a float64 reference and far closer than plain
+    bf16.  Gradients are
+    those of the other modes.  Sizes with and without K padding."""
+    from difflut_b200.layers.soft_select import soft_select, soft_select_t
+
+    gen = torch.Generator().manual_seed(3)
+    for B, I, M in ((256, 1024, 192), (200, 300, 90)):
+        xb = (torch.rand(B, I, generator=gen) > 0.5).float()
+        W = torch.randn(M, I, generator=gen) * 0.01
+        ref = xb.double() @ torch.softmax(W.double(), -1).t()
+        err = {}
+        for mode in (1, 2, "centered"):
+            out = soft_select(xb.to(dev), W.to(dev), 1.0, splits=mode)
+            err[mode] = float((out.cpu().double() - ref).abs().max())
+        assert err["centered"] <= 1e-5, err            # values are about 0.5 (measured 3e-6; the split 9e-7)
+        assert err["centered"] <= 8 * err[2], err
+        assert err["centered"] * 20 <= err[1], err     # plain bf16 is more than an order of magnitude worse (2e-4)
+        if B % 128 == 0:
+            out_t = soft_select_t(xb.to(dev), W.to(dev), 1.0, splits="centered")
+            assert torch.equal(out_t.t().contiguous(), soft_select(xb.to(dev), W.to(dev), 1.0, splits="centered"))
+    # general inputs and sharp weights: the 1e-2 bar, forward and backward
+    B, I, M = 200, 300, 90
+    x = torch.rand(B, I, generator=gen).to(dev).requires_grad_(True)
+    W = (torch.randn(M, I, generator=gen) * 2.0).to(dev).requires_grad_(True)
+    gy = torch.randn(B, M, generator=gen).to(dev)
+    xr, Wr = x.detach().clone().requires_grad_(True), W.detach().clone().requires_grad_(True)
+    ref = torch.matmul(xr, torch.softmax(Wr / 0.5, dim=-1).t())
+    ref.backward(gy)
+    out = soft_select(x, W, 0.5, splits="centered")
+    torch.testing.assert_close(out, ref.detach(), rtol=1e-2, atol=1e-2)
+    out.backward(gy)
+    torch.testing.assert_close(x.grad, xr.grad, rtol=1e-2, atol=1e-2 * float(xr.grad.abs().max()))
+    torch.testing.assert_close(W.grad, Wr.grad, rtol=1e-2, atol=1e-2 * float(Wr.grad.abs().max()))
+
+
 def test_wide_materialised_path_equals_fused_layer(dev):
     """(B, N, n) mapped inputs with N >= 64 go through the feature-major kernels under the identity map:
     same outputs and gradients as the fused layer forward, and as the oracle."""
