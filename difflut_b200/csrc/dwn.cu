@@ -614,41 +614,61 @@ dwn_bwd_input_kernel(const uint8_t* __restrict__ addr_t, const float* __restrict
                      float gscale, const float* __restrict__ efd_t,
                      const int32_t* __restrict__ inv_ptr, const int32_t* __restrict__ inv_ent,
                      float* __restrict__ gx_t, int64_t F, int n, int64_t Bp, int cps) {
+    constexpr int CH = 4;  // chunks per work item: a reader's index data is loaded once per 512 samples
     const int lane = threadIdx.x & 31;
     const int64_t C = Bp >> 7;
     const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     // The batch is walked in passes of `cps` chunks (a multiple of 8: whole 1024-sample slabs); inside a
-    // pass one warp owns one (feature, chunk) pair and the pairs of a feature go to neighbouring warps.
+    // pass one warp owns one (feature, 4 chunks) item and the items of a feature go to neighbouring warps.
     // With many features a pass is one slab, so the slab of g_t / addr_t the warps share stays in L2;
     // with few features (a convolution's patch taps) the host widens the pass until every warp has work.
+    // Per reader the item's four address words and gradient pieces are requested together.
     const uint32_t ugdiv = (uint32_t)gdiv;
-    const int64_t items = F * cps;
+    const int ipp = cps / CH;  // items of a feature per pass
+    const int64_t items = F * ipp;
     for (int64_t c0 = 0; c0 < C; c0 += cps)
     for (int64_t it = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; it < items; it += nwarps) {
-        const int64_t f = it / cps;
-        const int64_t c = c0 + (it - f * cps);
-        if (c >= C) continue;  // uniform over the warp
-        const int64_t b = (c << 7) + lane * 4;
+        const int64_t f = it / ipp;
+        const int64_t cb = c0 + (it - f * ipp) * CH;
+        if (cb >= C) continue;  // uniform over the warp
+        const int64_t b = (cb << 7) + lane * 4;
         const int e0 = __ldg(&inv_ptr[f]), e1 = __ldg(&inv_ptr[f + 1]);
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 acc[CH];
+#pragma unroll
+        for (int c = 0; c < CH; ++c) acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int e = e0; e < e1; ++e) {
             const int ent = __ldg(&inv_ent[e]);
             const int j = ent >> 3, i = ent & 7;
             const float tv = __ldg(efd_t + ((int64_t)j * n + i) * 32 + lane);
-            const uint32_t a = __ldg(reinterpret_cast<const uint32_t*>(addr_t + (int64_t)j * Bp + b));
             const int64_t grow = ugdiv == 1 ? j : (int64_t)((uint32_t)j / ugdiv);
-            const float4 g = __ldg(reinterpret_cast<const float4*>(g_t + grow * Bp + b));
+            uint32_t a[CH];
+            float4 g[CH];
+#pragma unroll
+            for (int c = 0; c < CH; ++c) {
+                const bool live = cb + c < C;
+                a[c] = live ? __ldg(reinterpret_cast<const uint32_t*>(addr_t + (int64_t)j * Bp + b + c * 128)) : 0u;
+                g[c] = live ? __ldg(reinterpret_cast<const float4*>(g_t + grow * Bp + b + c * 128))
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
             const uint32_t low = (1u << i) - 1u;
             // drop bit i of every byte: keep the bits below i, shift the bits above i down by one
             const uint32_t lowm = low * 0x01010101u;
-            const uint32_t a5 = (a & lowm) | ((a >> 1) & ~lowm & 0x7F7F7F7Fu);
-            acc.x += g.x * __shfl_sync(0xffffffffu, tv, a5 & 31);
-            acc.y += g.y * __shfl_sync(0xffffffffu, tv, (a5 >> 8) & 31);
-            acc.z += g.z * __shfl_sync(0xffffffffu, tv, (a5 >> 16) & 31);
-            acc.w += g.w * __shfl_sync(0xffffffffu, tv, (a5 >> 24) & 31);
+#pragma unroll
+            for (int c = 0; c < CH; ++c) {
+                const uint32_t a5 = (a[c] & lowm) | ((a[c] >> 1) & ~lowm & 0x7F7F7F7Fu);
+                acc[c].x += g[c].x * __shfl_sync(0xffffffffu, tv, a5 & 31);
+                acc[c].y += g[c].y * __shfl_sync(0xffffffffu, tv, (a5 >> 8) & 31);
+                acc[c].z += g[c].z * __shfl_sync(0xffffffffu, tv, (a5 >> 16) & 31);
+                acc[c].w += g[c].w * __shfl_sync(0xffffffffu, tv, (a5 >> 24) & 31);
+            }
         }
-        acc.x *= gscale; acc.y *= gscale; acc.z *= gscale; acc.w *= gscale;
-        *reinterpret_cast<float4*>(gx_t + f * Bp + b) = acc;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            if (cb + c < C) {
+                acc[c].x *= gscale; acc[c].y *= gscale; acc[c].z *= gscale; acc[c].w *= gscale;
+                *reinterpret_cast<float4*>(gx_t + f * Bp + b + c * 128) = acc[c];
+            }
+        }
     }
 }
 
@@ -1355,13 +1375,14 @@ DL_EXPORT int dl_dwn_bwd_input_t(const uint8_t* addr_t, const float* g_t, int64_
     DL_REQUIRE_ALIGNED(g_t, 16);
     DL_REQUIRE_ALIGNED(gx_t, 16);
     if (n < 1 || n > DL_MAX_FAST_N) return DL_ERR_UNSUPPORTED;
-    // chunks per pass: one slab, or as many slabs as it takes to give every resident warp a pair
+    // chunks per pass: one slab, or as many slabs as it takes to give every resident warp an item (a slab is
+    // two items per feature)
     const int64_t resident_warps = (int64_t)DL_NUM_SMS * 5 * 8;
-    int64_t slabs = dl_ceil_div(resident_warps, F * 8);
+    int64_t slabs = dl_ceil_div(resident_warps, F * 2);
     const int64_t all_slabs = dl_ceil_div(Bp / 128, 8);
     if (slabs > all_slabs) slabs = all_slabs;
     const int cps = (int)(8 * slabs);
-    const int64_t want = dl_ceil_div(F * cps * 32, 256);
+    const int64_t want = dl_ceil_div(F * (cps / 4) * 32, 256);  // one warp per (feature, 4 chunks)
     const int blocks = (int)(want < (int64_t)DL_NUM_SMS * 5 ? want : (int64_t)DL_NUM_SMS * 5);
     dwn_bwd_input_kernel<<<blocks, 256, 0, dl_cast(stream)>>>(addr_t, g_t, gdiv, gscale, efd_t, inv_ptr,
                                                              inv_ent, gx_t, F, (int)n, Bp, cps);

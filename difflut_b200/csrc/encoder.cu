@@ -234,6 +234,43 @@ t_to_rows_kernel(const float* __restrict__ t, float* __restrict__ rows, int64_t 
     }
 }
 
+// 64 x 64 tiles with 16-byte accesses on both sides, for shapes whose row lengths are multiples of 4 and
+// whose pointers are 16-byte aligned: dst[c][r] = src[r][c].  Source rows r >= R read as zero; source columns are
+// loaded while c < c_load and stored (as destination rows) while c < C; destination columns are written up to
+// r_store.  Twice the bytes in flight per thread of the 32 x 32 form above.
+__global__ void __launch_bounds__(256)
+transpose64_kernel(const float* __restrict__ src, float* __restrict__ dst, int64_t R, int64_t C, int64_t c_load,
+                   int64_t r_store, int64_t ld_src, int64_t ld_dst) {
+    __shared__ float tile[64][65];
+    const int64_t r0 = (int64_t)blockIdx.x * 64, c0 = (int64_t)blockIdx.y * 64;
+    const int q = threadIdx.x & 15, p = threadIdx.x >> 4;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int r = p + 16 * k;
+        const int64_t gr = r0 + r, gc = c0 + 4 * q;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (gr < R && gc < c_load) v = __ldg(reinterpret_cast<const float4*>(src + gr * ld_src + gc));
+        tile[r][4 * q + 0] = v.x;
+        tile[r][4 * q + 1] = v.y;
+        tile[r][4 * q + 2] = v.z;
+        tile[r][4 * q + 3] = v.w;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int c = p + 16 * k;
+        const int64_t gc = c0 + c, gr = r0 + 4 * q;
+        if (gc < C && gr < r_store)
+            *reinterpret_cast<float4*>(dst + gc * ld_dst + gr) =
+                make_float4(tile[4 * q + 0][c], tile[4 * q + 1][c], tile[4 * q + 2][c], tile[4 * q + 3][c]);
+    }
+}
+
+static bool transpose64_ok(const void* a, const void* b, int64_t n0, int64_t n1) {
+    return reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(b) % 16 == 0 && n0 % 4 == 0 &&
+           n1 % 4 == 0;
+}
+
 // bits_t [F][Wp] -> fp32 rows (B,F) of {0,1}: CTA tile = 32 features x 32 samples (one word each)
 __global__ void __launch_bounds__(256)
 bits_t_to_rows_kernel(const uint32_t* __restrict__ bits_t, float* __restrict__ rows, int64_t B,
@@ -386,6 +423,12 @@ DL_EXPORT int dl_pack_t_to_t(const float* src_t, uint32_t* bits_t, int64_t F, in
 DL_EXPORT int dl_f32_rows_to_t(const float* rows, float* t, int64_t B, int64_t F, int64_t Bp,
                                dl_stream_t stream) {
     DL_REQUIRE(rows && t && B > 0 && F > 0 && Bp >= B && Bp % DL_BATCH_ALIGN == 0);
+    if (transpose64_ok(rows, t, F, Bp) && dl_ceil_div(F, 64) <= 65535) {
+        // source = rows (B x F), destination = t (F x Bp); samples B..Bp-1 are written as zeros
+        dim3 grid64((unsigned)(Bp / 64 + (Bp % 64 != 0)), (unsigned)dl_ceil_div(F, 64));
+        transpose64_kernel<<<grid64, 256, 0, dl_cast(stream)>>>(rows, t, B, F, F, Bp, F, Bp);
+        return dl_launch_status();
+    }
     dim3 grid((unsigned)(Bp / 32), (unsigned)dl_ceil_div(F, 32));
     rows_to_t_kernel<<<grid, 256, 0, dl_cast(stream)>>>(rows, t, B, F, Bp);
     return dl_launch_status();
@@ -394,6 +437,12 @@ DL_EXPORT int dl_f32_rows_to_t(const float* rows, float* t, int64_t B, int64_t F
 DL_EXPORT int dl_f32_t_to_rows(const float* t, float* rows, int64_t B, int64_t F, int64_t Bp,
                                dl_stream_t stream) {
     DL_REQUIRE(rows && t && B > 0 && F > 0 && Bp >= B && Bp % DL_BATCH_ALIGN == 0);
+    if (transpose64_ok(rows, t, F, Bp) && dl_ceil_div(B, 64) <= 65535) {
+        // source = t (F x Bp), destination = rows (B x F): only the B real samples become rows
+        dim3 grid64((unsigned)dl_ceil_div(F, 64), (unsigned)dl_ceil_div(B, 64));
+        transpose64_kernel<<<grid64, 256, 0, dl_cast(stream)>>>(t, rows, F, B, Bp, F, Bp, F);
+        return dl_launch_status();
+    }
     dim3 grid((unsigned)dl_ceil_div(B, 32), (unsigned)dl_ceil_div(F, 32));
     t_to_rows_kernel<<<grid, 256, 0, dl_cast(stream)>>>(t, rows, B, F, Bp);
     return dl_launch_status();
