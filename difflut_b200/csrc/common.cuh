@@ -27,6 +27,7 @@ static inline cudaStream_t dl_cast(dl_stream_t s) { return reinterpret_cast<cuda
 
 static inline int64_t dl_ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 static inline int64_t dl_min64(int64_t a, int64_t b) { return a < b ? a : b; }
+static inline int64_t dl_max64(int64_t a, int64_t b) { return a > b ? a : b; }
 
 // Number of streaming multiprocessors the grids are sized for (B200: 148).
 constexpr int DL_NUM_SMS = 148;

@@ -183,6 +183,26 @@ __global__ void thermo_rows_kernel(const float* __restrict__ x, const float* __r
     }
 }
 
+// The same for row lengths F*T that are multiples of 4: a thread owns four adjacent output columns, looks their
+// features and thresholds up once, and then walks the samples of its grid row with one 16-byte store each
+// (no division inside the loop).
+__global__ void __launch_bounds__(256)
+thermo_rows_vec_kernel(const float* __restrict__ x, const float* __restrict__ thr, float* __restrict__ out,
+                       int64_t B, int64_t F, int T, int C4) {
+    const int c4 = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c4 >= C4) return;
+    const int c = c4 * 4;
+    const int f0 = c / T, f1 = (c + 1) / T, f2 = (c + 2) / T, f3 = (c + 3) / T;
+    const float4 th = __ldg(reinterpret_cast<const float4*>(thr) + c4);
+    const int64_t C = (int64_t)C4 * 4;
+    for (int64_t b = blockIdx.y; b < B; b += gridDim.y) {
+        const float* xr = x + b * F;
+        const float v0 = __ldg(xr + f0), v1 = __ldg(xr + f1), v2 = __ldg(xr + f2), v3 = __ldg(xr + f3);
+        *reinterpret_cast<float4*>(out + b * C + c) =
+            make_float4(v0 > th.x ? 1.0f : 0.0f, v1 > th.y ? 1.0f : 0.0f, v2 > th.z ? 1.0f : 0.0f, v3 > th.w ? 1.0f : 0.0f);
+    }
+}
+
 // rows in, packed rows out: one warp per (sample, word); lane = column inside the word
 __global__ void thermo_pack_rows_kernel(const float* __restrict__ x, const float* __restrict__ thr,
                                         uint32_t* __restrict__ bits, int64_t B, int64_t F, int T,
@@ -342,6 +362,14 @@ DL_EXPORT int dl_thermo_rows(const float* x, const float* thr, float* out, int64
                              int64_t T, dl_stream_t stream) {
     DL_REQUIRE(x && thr && out && B > 0 && F > 0 && T > 0);
     const int64_t total = B * F * T;
+    if ((F * T) % 4 == 0 && F * T < ((int64_t)1 << 31) && reinterpret_cast<uintptr_t>(thr) % 16 == 0 &&
+        reinterpret_cast<uintptr_t>(out) % 16 == 0) {
+        const int C4 = (int)(F * T / 4);
+        const unsigned gx = (unsigned)dl_ceil_div(C4, 256);
+        const int64_t gy = dl_min64(B, dl_max64(1, (int64_t)DL_NUM_SMS * 16 / gx));
+        thermo_rows_vec_kernel<<<dim3(gx, (unsigned)gy), 256, 0, dl_cast(stream)>>>(x, thr, out, B, F, (int)T, C4);
+        return dl_launch_status();
+    }
     const int blocks = (int)dl_min64(dl_ceil_div(total, 256), (int64_t)DL_NUM_SMS * 16);
     thermo_rows_kernel<<<blocks, 256, 0, dl_cast(stream)>>>(x, thr, out, B, F, (int)T);
     return dl_launch_status();
