@@ -171,6 +171,48 @@ pack_t_to_t_kernel(const float* __restrict__ src_t, uint32_t* __restrict__ bits_
     }
 }
 
+// The same with 16-byte loads: a warp item is 512 samples of one feature; a lane reads four float4 (one per
+// 128-sample chunk, all in flight together), turns each into a nibble, and the eight nibbles of a word are
+// combined with a warp OR.  Needs ld % 4 == 0 and a 16-byte aligned source.
+__global__ void __launch_bounds__(256)
+pack_t_to_t_vec_kernel(const float* __restrict__ src_t, uint32_t* __restrict__ bits_t, int64_t F, int64_t B,
+                       int64_t ld, int64_t Wp, float threshold) {
+    const int lane = threadIdx.x & 31;
+    const int64_t C = Wp >> 2;             // 128-sample chunks per row
+    const int64_t Q = (C + 3) >> 2;        // items per row
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t item = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; item < F * Q; item += nwarps) {
+        const int64_t f = item / Q, q = item - f * Q;
+        const float* row = src_t + f * ld;
+        float4 v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int64_t c = q * 4 + k;
+            v[k] = c < C ? __ldg(reinterpret_cast<const float4*>(row + c * 128) + lane)
+                         : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int64_t c = q * 4 + k;
+            if (c >= C) break;  // uniform over the warp
+            const int64_t b = c * 128 + lane * 4;
+            uint32_t nib = 0;
+            nib |= (b + 0 < B && v[k].x >= threshold) ? 1u : 0u;
+            nib |= (b + 1 < B && v[k].y >= threshold) ? 2u : 0u;
+            nib |= (b + 2 < B && v[k].z >= threshold) ? 4u : 0u;
+            nib |= (b + 3 < B && v[k].w >= threshold) ? 8u : 0u;
+            const uint32_t part = nib << ((lane & 7) * 4);
+            uint32_t mine = 0;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const uint32_t word = __reduce_or_sync(0xffffffffu, (lane >> 3) == w ? part : 0u);
+                if (lane == w) mine = word;
+            }
+            if (lane < 4) bits_t[f * Wp + c * 4 + lane] = mine;
+        }
+    }
+}
+
 // rows in, fp32 rows out: out[b, f*T+t] = x[b,f] > thr[f,t]
 __global__ void thermo_rows_kernel(const float* __restrict__ x, const float* __restrict__ thr,
                                    float* __restrict__ out, int64_t B, int64_t F, int T) {
@@ -315,23 +357,33 @@ bits_t_to_rows_kernel(const uint32_t* __restrict__ bits_t, float* __restrict__ r
 __global__ void __launch_bounds__(256)
 bits_rows_to_t_kernel(const uint32_t* __restrict__ bits_rows, uint32_t* __restrict__ bits_t,
                       int64_t B, int64_t F, int64_t Wr, int64_t Wp) {
-    __shared__ uint32_t in_tile[512][9];     // +1 word padding: a warp reads one column conflict-free
-    __shared__ uint32_t out_tile[256][17];
+    // one buffer for both directions (18 KB: eight CTAs per SM): the input tile [512][9] (+1 word padding: a warp
+    // reads one column conflict-free) is overwritten by the output tile [256][17] once every warp holds its words
+    __shared__ uint32_t tile_buf[512 * 9];
+    uint32_t (*in_tile)[9] = reinterpret_cast<uint32_t (*)[9]>(tile_buf);
+    uint32_t (*out_tile)[17] = reinterpret_cast<uint32_t (*)[17]>(tile_buf);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t wc0 = (int64_t)blockIdx.y * 8;      // first column word
     const int64_t b0 = (int64_t)blockIdx.x * 512;     // first sample
-    for (int idx = threadIdx.x; idx < 512 * 8; idx += 256) {
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+        const int idx = threadIdx.x + k * 256;
         const int r = idx >> 3, cw = idx & 7;
         const int64_t b = b0 + r, wc = wc0 + cw;
         in_tile[r][cw] = (b < B && wc < Wr) ? __ldg(bits_rows + b * Wr + wc) : 0u;
     }
     __syncthreads();
     // 8 column words x 16 sample words = 128 tiles; warp w takes column word w
+    uint32_t held[16];
+#pragma unroll
+    for (int sw = 0; sw < 16; ++sw) held[sw] = in_tile[sw * 32 + lane][warp];
+    __syncthreads();  // the input tile may be overwritten now
+#pragma unroll
     for (int sw = 0; sw < 16; ++sw) {
         // 32x32 bit transpose across the warp: five rounds of swapping off-diagonal blocks with the
         // lane that differs in bit j of its index (lane r starts with sample r's word and ends with
         // the 32 samples of feature r)
-        uint32_t v = in_tile[sw * 32 + lane][warp];
+        uint32_t v = held[sw];
         uint32_t m = 0x0000FFFFu;
 #pragma unroll
         for (int j = 16; j > 0; j >>= 1) {
@@ -345,8 +397,7 @@ bits_rows_to_t_kernel(const uint32_t* __restrict__ bits_rows, uint32_t* __restri
             }
             m ^= m << (j >> 1);
         }
-        const uint32_t outw = v;
-        out_tile[warp * 32 + lane][sw] = outw;
+        out_tile[warp * 32 + lane][sw] = v;
     }
     __syncthreads();
     const int64_t wb0 = b0 >> 5;
@@ -443,6 +494,12 @@ DL_EXPORT int dl_pack_t_to_t(const float* src_t, uint32_t* bits_t, int64_t F, in
     DL_REQUIRE(src_t && bits_t && F > 0 && B > 0 && ld >= B);
     DL_REQUIRE(Bp >= B && Bp % DL_BATCH_ALIGN == 0);
     const int64_t items = F * (Bp / 128);
+    if (ld % 4 == 0 && reinterpret_cast<uintptr_t>(src_t) % 16 == 0 && ld >= Bp) {
+        const int64_t blocks4 = dl_min64(dl_ceil_div(F * dl_ceil_div(Bp / 128, 4), 8), (int64_t)DL_NUM_SMS * 16);
+        pack_t_to_t_vec_kernel<<<(unsigned)blocks4, 256, 0, dl_cast(stream)>>>(src_t, bits_t, F, B, ld, Bp / 32,
+                                                                            threshold);
+        return dl_launch_status();
+    }
     const int64_t blocks = dl_min64(dl_ceil_div(items, 8), (int64_t)DL_NUM_SMS * 16);
     pack_t_to_t_kernel<<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(src_t, bits_t, F, B, ld, Bp / 32, threshold);
     return dl_launch_status();
