@@ -44,8 +44,9 @@ prob_fwd_kernel(const float* __restrict__ x_t, const int32_t* __restrict__ map,
                 float* __restrict__ partial, int64_t NO, int O, int64_t gsz, int S, int64_t per,
                 int64_t Bp) {
     constexpr int L = 1 << NIN;
-    __shared__ float w[L];
-    __shared__ int32_t rows[NIN];
+    // two buffers: node v + 1 is staged while node v is evaluated, one barrier per node
+    __shared__ float w_all[2][L];
+    __shared__ int32_t rows_all[2][NIN];
     const int64_t b = (int64_t)blockIdx.x * PROB_TILE + threadIdx.x;
     int64_t v0, v1;
     if (GROUPSUM) {
@@ -62,9 +63,11 @@ prob_fwd_kernel(const float* __restrict__ x_t, const int32_t* __restrict__ map,
     for (int64_t v = v0; v < v1; ++v) {
         const int64_t j = v / O;
         const int o = (int)(v - j * O);
-        __syncthreads();
+        float* w = w_all[(v - v0) & 1];
+        int32_t* rows = rows_all[(v - v0) & 1];
         if (threadIdx.x < L) w[threadIdx.x] = prob_weight(raw, j, o, O, L, threadIdx.x, inv_t);
         if (threadIdx.x < NIN) rows[threadIdx.x] = __ldg(map + j * NIN + threadIdx.x);
+        // after this barrier the buffer is complete, and the other buffer (read for node v - 1) is free for v + 1
         __syncthreads();
         float x[NIN];
 #pragma unroll
