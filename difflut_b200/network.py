@@ -162,6 +162,11 @@ class DWNNetwork:
         self._train_B = None
         self._graph = None
         self._graph_B_global = None
+        # graphs captured on a caller's own input tensor (no copy into the static buffer), by input address
+        self._direct_graphs = {}
+        self._direct_seen = {}
+        self._x_src = None
+        self.max_direct_graphs = 4
         self._side = None
         self._comm = None
         self._peer_channels = set()
@@ -188,6 +193,7 @@ class DWNNetwork:
             self._B = B
             self._train_B = None
             self._graph = None
+            self._direct_graphs, self._direct_seen = {}, {}
         if training and self._train_B != B:
             Bp = self.Bp
             # gradient w.r.t. the output of layer li (li < last), produced by layer li+1's backward; the
@@ -203,6 +209,7 @@ class DWNNetwork:
             self.y_static = torch.empty(B, device=dev, dtype=torch.int32)
             self._train_B = B
             self._graph = None
+            self._direct_graphs, self._direct_seen = {}, {}
 
     # ------------------------------------------------------------------ kernels
     def _prepare_tables(self, need_efd: bool, need_masks: bool = True) -> None:
@@ -343,7 +350,7 @@ class DWNNetwork:
             self._masks_ready.record(self._side)
             self._prepare_tables(need_efd=True, need_masks=False)
             self._efd_ready.record(self._side)
-        self._encode(self.x_static, B)
+        self._encode(self.x_static if self._x_src is None else self._x_src, B)
         main.wait_event(self._masks_ready)
         self._forward_layers(with_loss=(B, B_global))
         self._ce_done.record(main)
@@ -433,19 +440,42 @@ class DWNNetwork:
             raise ValueError(f"labels must lie in [0, {self.k})")
         with torch.cuda.device(self.device):
             self._ensure_buffers(B)
-            self.x_static.copy_(x, non_blocking=True)
-            self.y_static.copy_(labels, non_blocking=True)
             B_global = B * self.world if global_batch is None else int(global_batch)
             if B_global < B:
                 raise ValueError("global_batch is smaller than this rank's batch")
-            if self._graph is not None and self._graph_B_global != B_global:
-                self._graph = None  # the denominator is baked into the captured launches
-            if not use_graph:
-                self._step_body(B, B_global)
+            self.y_static.copy_(labels, non_blocking=True)
+            # An input tensor that comes back (a training loop's own device buffer) gets a graph captured on its
+            # address from its second appearance on: the encoder then reads it in place.  Any other input is
+            # copied into the static buffer the general graph reads.
+            key = None
+            if (use_graph and x.is_cuda and x.device == self.device and x.dtype == torch.float32
+                    and x.is_contiguous() and x.data_ptr() % 16 == 0 and tuple(x.shape) == (B, self.F)):
+                key = (x.data_ptr(), B, B_global)
+            direct = self._direct_graphs.get(key) if key is not None else None
+            if direct is None and key is not None and self._direct_seen.get(key, 0) >= 1 \
+                    and len(self._direct_graphs) < self.max_direct_graphs and self._graph is not None:
+                self._x_src = x
+                try:
+                    direct = (self._capture_graph(B, B_global), x)  # the tensor is kept alive with its graph
+                finally:
+                    self._x_src = None
+                self._direct_graphs[key] = direct
+            if direct is not None:
+                direct[0].replay()
             else:
-                if self._graph is None:
-                    self._capture(B, B_global)
-                self._graph.replay()
+                if key is not None:
+                    if len(self._direct_seen) > 64:
+                        self._direct_seen = {}
+                    self._direct_seen[key] = self._direct_seen.get(key, 0) + 1
+                self.x_static.copy_(x, non_blocking=True)
+                if self._graph is not None and self._graph_B_global != B_global:
+                    self._graph = None  # the denominator is baked into the captured launches
+                if not use_graph:
+                    self._step_body(B, B_global)
+                else:
+                    if self._graph is None:
+                        self._capture(B, B_global)
+                    self._graph.replay()
         self.step_count += 1
         if self.peer_optimizer and self.peer_status_every > 0 and self.step_count % self.peer_status_every == 0:
             status = self.peer_status()
@@ -466,11 +496,14 @@ class DWNNetwork:
         torch.cuda.synchronize(self.device)
         self.flat.copy_(snap[0]); self.exp_avg.copy_(snap[1]); self.exp_avg_sq.copy_(snap[2])
         self.adam_state.copy_(snap[3])
+        self._graph = self._capture_graph(B, B_global)
+        self._graph_B_global = B_global
+
+    def _capture_graph(self, B: int, B_global: int):
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             self._step_body(B, B_global)
-        self._graph = graph
-        self._graph_B_global = B_global
+        return graph
 
     @torch.no_grad()
     def logits(self, x: torch.Tensor) -> torch.Tensor:

@@ -587,6 +587,31 @@ def test_dwn_net3_two_adam_steps_match_reference(golden, dev, use_graph, fused):
     assert torch.equal(net.hard_counts(packed_rows=packed), counts)
 
 
+def test_graph_on_a_recurring_input_tensor_reads_it_in_place(golden, dev):
+    """From its second appearance on, an input tensor gets a graph captured on its own address (no copy into the
+    static buffer).  Five graph steps on one tensor whose CONTENT changes between steps must leave the same
+    tables, bit for bit, as five eager steps on the same inputs; a fresh tensor afterwards takes the general
+    graph again."""
+    g = golden("dwn_net3")
+    net_a, layers_a, _ = _build_net3(g, dev)
+    net_b, layers_b, _ = _build_net3(g, dev)
+    x0, labels = T(g["x"]).to(dev), T(g["labels"]).to(dev)
+    gen = torch.Generator().manual_seed(7)
+    inputs = [x0.clone()] + [torch.rand(x0.shape, generator=gen).to(dev) for _ in range(4)]
+    buf = torch.empty_like(x0)
+    for step, xi in enumerate(inputs):
+        buf.copy_(xi)
+        la = net_a.train_step(buf, labels, use_graph=True).clone()
+        lb = net_b.train_step(xi, labels, use_graph=False).clone()
+        assert torch.equal(la, lb), step
+    assert len(net_a._direct_graphs) == 1
+    for la_, lb_ in zip(layers_a, layers_b):
+        assert torch.equal(la_.luts.detach(), lb_.luts.detach())
+    extra = torch.rand(x0.shape, generator=gen).to(dev)
+    assert torch.equal(net_a.train_step(extra, labels, use_graph=True), net_b.train_step(extra, labels, use_graph=False))
+    assert len(net_a._direct_graphs) == 1
+
+
 def test_layer_api_equals_fused_network(golden, dev):
     """The per-layer fp32 API and the bit-packed executor compute the same logits and table gradients."""
     from difflut_b200.utils import GroupSum
