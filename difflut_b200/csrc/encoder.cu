@@ -379,24 +379,28 @@ bits_rows_to_t_kernel(const uint32_t* __restrict__ bits_rows, uint32_t* __restri
     for (int sw = 0; sw < 16; ++sw) held[sw] = in_tile[sw * 32 + lane][warp];
     __syncthreads();  // the input tile may be overwritten now
 #pragma unroll
-    for (int sw = 0; sw < 16; ++sw) {
-        // 32x32 bit transpose across the warp: five rounds of swapping off-diagonal blocks with the
-        // lane that differs in bit j of its index (lane r starts with sample r's word and ends with
-        // the 32 samples of feature r)
-        uint32_t v = held[sw];
-        uint32_t m = 0x0000FFFFu;
+    // 32x32 bit transpose across the warp: five rounds of swapping off-diagonal blocks with the lane that
+    // differs in bit j of its index (lane r starts with sample r's word and ends with the 32 samples of
+    // feature r).  A lane with bit j clear keeps its low halves and takes the partner's low halves shifted up;
+    // a lane with bit j set keeps its high halves and takes the partner's high halves shifted down.  For
+    // j = 16 and 8 that is one byte permute; for j = 4, 2, 1 one rotate of the partner's word and one
+    // three-input select, with the selector / rotate amount / keep mask of each lane prepared once.
+    const uint32_t sel16 = (lane & 16) ? 0x3276u : 0x5410u;
+    const uint32_t sel8 = (lane & 8) ? 0x3715u : 0x6240u;
+    const uint32_t rot4 = (lane & 4) ? 28u : 4u, keep4 = (lane & 4) ? 0xF0F0F0F0u : 0x0F0F0F0Fu;
+    const uint32_t rot2 = (lane & 2) ? 30u : 2u, keep2 = (lane & 2) ? 0xCCCCCCCCu : 0x33333333u;
+    const uint32_t rot1 = (lane & 1) ? 31u : 1u, keep1 = (lane & 1) ? 0xAAAAAAAAu : 0x55555555u;
 #pragma unroll
-        for (int j = 16; j > 0; j >>= 1) {
-            const uint32_t p = __shfl_xor_sync(0xffffffffu, v, j);
-            if ((lane & j) == 0) {
-                const uint32_t t = ((v >> j) ^ p) & m;
-                v ^= t << j;
-            } else {
-                const uint32_t t = ((p >> j) ^ v) & m;
-                v ^= t;
-            }
-            m ^= m << (j >> 1);
-        }
+    for (int sw = 0; sw < 16; ++sw) {
+        uint32_t v = held[sw];
+        v = __byte_perm(v, __shfl_xor_sync(0xffffffffu, v, 16), sel16);
+        v = __byte_perm(v, __shfl_xor_sync(0xffffffffu, v, 8), sel8);
+        uint32_t p = __shfl_xor_sync(0xffffffffu, v, 4);
+        v = (v & keep4) | (__funnelshift_l(p, p, rot4) & ~keep4);
+        p = __shfl_xor_sync(0xffffffffu, v, 2);
+        v = (v & keep2) | (__funnelshift_l(p, p, rot2) & ~keep2);
+        p = __shfl_xor_sync(0xffffffffu, v, 1);
+        v = (v & keep1) | (__funnelshift_l(p, p, rot1) & ~keep1);
         out_tile[warp * 32 + lane][sw] = v;
     }
     __syncthreads();
