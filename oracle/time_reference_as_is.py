@@ -1,9 +1,9 @@
 """Times the UNMODIFIED reference (pure-PyTorch CPU path) on config 1 at reduced node counts.
 
-    PYTHONDONTWRITEBYTECODE=1 python oracle/time_reference_as_is.py [--ref /path/to/difflut/checkout]
+    PYTHONDONTWRITEBYTECODE=1 python oracle/time_reference_as_is.py --ref /path/to/difflut/checkout
 
 Run it where the reference checkout exists; the reference is a Python package that does not travel with
-this repository, so the numbers it prints are recorded in BASELINE.md / DESIGN.md by hand and the
+this repository, so the numbers it prints are recorded in the project's notes by hand and the
 benchmark's `cpu_baseline` stays the oracle port.  Config 1: batch 256 x 784 features, 3-threshold
 thermometer (2352 bits), RandomLayer of N six-input DWN nodes (uniform without replacement per node),
 loss = sum of outputs, forward + backward.  The reference's cost is linear in the number of nodes (a Python
@@ -22,7 +22,8 @@ import torch
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default=os.environ.get("DIFFLUT_REFERENCE", "/root/reference"))
+    ap.add_argument("--ref", default=os.environ.get("DIFFLUT_REFERENCE"), required="DIFFLUT_REFERENCE" not in os.environ,
+                    help="path of the reference checkout (or set DIFFLUT_REFERENCE)")
     ap.add_argument("--nodes", type=int, nargs="+", default=[10, 40])
     args = ap.parse_args()
     sys.path.insert(0, args.ref)
