@@ -708,15 +708,18 @@ def measure_gather(args):
     gx = torch.empty(B, I, device=device)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     fwd = _time_gpu(lambda: _native.call("dl_gather_rows", x, plan.map_nodes, out, B, I, N, n), args.steps, 3, flush)
-    bwd = _time_gpu(lambda: _native.call("dl_gather_rows_bwd", gy, plan.inv_ptr_nodes, plan.inv_ent_nodes, gx, B, I,
-                                          N, n), args.steps, 3, flush)
+    bwd_csr = _time_gpu(lambda: _native.call("dl_gather_rows_bwd", gy, plan.inv_ptr_nodes, plan.inv_ent_nodes, gx, B, I,
+                                              N, n), args.steps, 3, flush)
+    ell, max_deg = plan.ell_nodes()
+    # what the autograd function of get_mapping calls for rows this wide: the feature-interleaved entry table
+    bwd = _time_gpu(lambda: _native.call("dl_gather_rows_bwd_ell", gy, ell, max_deg, gx, B, I, N, n), args.steps, 3, flush)
     bytes_each = 4.0 * B * (I + N * n)
     peak = _peaks()
     return {"metric": "gather rows/s (forward), RandomLayer map 6272 -> 16000 x 6 on fp32 rows", "value": B / (fwd * 1e-3),
             "unit": "rows/s", "n_gpus": 1, "steps": args.steps, "warmup": 3, "ms_per_step": fwd,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"gather_B{B}_in{I}_N{N}_n{n}", "l2": "256 MB flush between timed calls"},
-            "backward_ms": bwd,
+            "backward_ms": bwd, "backward_csr_ms": bwd_csr,
             "roofline": {"bound": "hbm", "achieved": bytes_each / (fwd * 1e-3) / 1e9, "peak": peak["hbm_gbs"],
                          "peak_source": peak["source"], "unit": "GB/s", "frac": bytes_each / (fwd * 1e-3) / 1e9 / peak["hbm_gbs"],
                          "traffic": None, "backward_achieved": bytes_each / (bwd * 1e-3) / 1e9,

@@ -29,6 +29,7 @@ SIGNATURES = {
     "dl_bits_rows_to_t": "ppllll s",
     "dl_gather_rows": "pppllll s",
     "dl_gather_rows_bwd": "ppppllll s",
+    "dl_gather_rows_bwd_ell": "pplpllll s",
     "dl_unfold_rows": "ppllllllllll s",
     "dl_unfold_pack_t": "ppllllllllllfl s",
     "dl_fold_rows": "ppllllllllll s",

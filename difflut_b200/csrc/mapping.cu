@@ -4,8 +4,11 @@
 // (difflut/layers/cuda/mapping_cuda_kernel.cu:136-162) by a segmented sum over the inverse map:
 // the owner of (b, f) adds the gradient columns listed for feature f in a fixed order.  The forward has a plain
 // form (one thread per element) and a shared-memory staged form that the entry point prefers when a row fits;
-// both are exact copies.  A staged backward (gradient row walked in shared-memory tiles) was measured slower
-// than the plain one at the first layer's width (0.92 vs 0.78 ms for 2048 rows) and is not kept.
+// both are exact copies.  The backward has two forms as well.  dl_gather_rows_bwd takes the inverse map as CSR
+// and gives one thread a feature and four rows; it fetches a 32-byte sector for every 4-byte gradient AND for
+// every 4-byte entry (neighbouring features' lists lie 60 bytes apart), and staging the gradient row in shared
+// memory alone did not help it (0.59 - 0.92 ms against 0.71 ms at the first layer's width, 2048 rows).
+// dl_gather_rows_bwd_ell takes the entries interleaved by feature and stages the gradient: both streams coalesced.
 #include "common.cuh"
 
 namespace {
@@ -83,6 +86,97 @@ gather_rows_staged_kernel(const float* __restrict__ x, const int32_t* __restrict
 
 constexpr int64_t STAGE_SMEM_BUDGET = 220 * 1024;  // bytes of dynamic shared memory a staged kernel may ask for
 
+// Column-tiled backward over an entry table interleaved by feature: ell[j * F + f] = the j-th column that
+// feature f collects (ascending), -1 when f has fewer.  A CTA takes one gradient row at a time and walks it in
+// tiles of TB_COLS columns: the tile is copied into shared memory in coalesced 16-byte pieces; a thread owns
+// TB_FEATS features (f = tid + k * TB_THREADS, so the lanes of a warp read neighbouring table entries) and, in
+// rounds over all of them, consumes the pending entry of every feature whose column lies in the tile and
+// requests that feature's next entry.  Every gradient and every entry is read once per pass, coalesced; a
+// feature's gradients are added in ascending column order, as in the plain kernel: same bits.
+constexpr int TB_THREADS = 512, TB_FEATS = 13, TB_COLS = 10240;
+
+__device__ __forceinline__ void cp_async16(float* smem_dst, const float* gmem_src) {
+    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+
+// The tile of the step after the current one is copied global -> shared asynchronously (cp.async, two tile
+// buffers) while the current tile is consumed, across row boundaries too, so a CTA's loads and look-ups overlap.
+__global__ void __launch_bounds__(TB_THREADS, 2)
+gather_rows_bwd_ell_kernel(const float* __restrict__ g, const int32_t* __restrict__ ell, int max_deg,
+                           float* __restrict__ gx, int64_t B, int64_t F, int64_t M, int64_t f_base) {
+    extern __shared__ float tile_s[];  // [2][TB_COLS] gradient tiles, then [TB_FEATS][TB_THREADS] running sums
+    const int tid = threadIdx.x;
+    float* acc_s = tile_s + 2 * TB_COLS + tid;  // acc_s[k * TB_THREADS]: private to the thread (registers are short)
+    // entries are addressed as ellf[off]: off = j * F + k * TB_THREADS in 32 bits (the launcher checks the range)
+    const int32_t* ellf = ell + f_base + tid;
+    const uint32_t F32 = (uint32_t)F, limit = (uint32_t)max_deg * (uint32_t)F;
+    const int tiles = (int)((M + TB_COLS - 1) / TB_COLS);
+
+    auto issue = [&](int buf, int64_t b, int t) {  // request tile t of row b into buffer buf (one commit group)
+        if (b < B) {
+            const int64_t c0 = (int64_t)t * TB_COLS;
+            const int64_t c1 = c0 + TB_COLS < M ? c0 + TB_COLS : M;
+            const float* src = g + b * M + c0;   // M % 4 == 0 and c0 % 4 == 0: 16-byte aligned
+            float* dst = tile_s + buf * TB_COLS;
+            const int quads = (int)((c1 - c0) >> 2);
+            for (int q = tid; q < quads; q += TB_THREADS) cp_async16(dst + 4 * q, src + 4 * q);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    int64_t b = blockIdx.x;
+    int t = 0, buf = 0;
+    issue(0, b, 0);
+    uint32_t off[TB_FEATS];  // offset of the feature's pending entry
+    int c[TB_FEATS];         // its column, -1 = the feature has no more entries
+    while (b < B) {
+        // the step after this one
+        int64_t nb = b;
+        int nt = t + 1;
+        if (nt == tiles) { nt = 0; nb = b + gridDim.x; }
+        issue(buf ^ 1, nb, nt);
+        if (t == 0) {
+#pragma unroll
+            for (int k = 0; k < TB_FEATS; ++k) {
+                acc_s[k * TB_THREADS] = 0.f;
+                off[k] = (uint32_t)k * TB_THREADS;
+                c[k] = (f_base + tid + (int64_t)k * TB_THREADS < F && max_deg > 0) ? __ldg(ellf + off[k]) : -1;
+            }
+        }
+        asm volatile("cp.async.wait_group 1;" ::: "memory");  // everything but the newest group has landed
+        __syncthreads();
+        const float* tile = tile_s + buf * TB_COLS;
+        const int lo = t * TB_COLS;
+        const int hi = lo + TB_COLS < (int)M ? lo + TB_COLS : (int)M;
+        bool more = true;
+        while (more) {
+            more = false;
+#pragma unroll
+            for (int k = 0; k < TB_FEATS; ++k) {
+                if (c[k] >= 0 && c[k] < hi) {
+                    acc_s[k * TB_THREADS] += tile[c[k] - lo];
+                    off[k] += F32;
+                    c[k] = off[k] < limit ? __ldg(ellf + off[k]) : -1;
+                    more = true;
+                }
+            }
+        }
+        if (nt == 0) {  // the row is complete
+#pragma unroll
+            for (int k = 0; k < TB_FEATS; ++k) {
+                const int64_t f = f_base + tid + (int64_t)k * TB_THREADS;
+                if (f < F) gx[b * F + f] = acc_s[k * TB_THREADS];
+            }
+        }
+        __syncthreads();  // this buffer is requested again two steps from now
+        b = nb;
+        t = nt;
+        buf ^= 1;
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
 }  // namespace
 
 DL_EXPORT int dl_gather_rows(const float* x, const int32_t* map, float* out, int64_t B, int64_t F,
@@ -115,5 +209,23 @@ DL_EXPORT int dl_gather_rows_bwd(const float* g, const int32_t* inv_ptr, const i
     const int64_t M = N * n;
     const int64_t blocks = dl_min64(dl_ceil_div(dl_ceil_div(B, BWD_ROWS) * F, 256), (int64_t)DL_NUM_SMS * 32);
     gather_rows_bwd_kernel<<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(g, inv_ptr, inv_ent, gx, B, F, M);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_gather_rows_bwd_ell(const float* g, const int32_t* ell, int64_t max_deg, float* gx, int64_t B,
+                                     int64_t F, int64_t N, int64_t n, dl_stream_t stream) {
+    DL_REQUIRE(g && ell && gx && B > 0 && F > 0 && N > 0 && n > 0 && max_deg >= 0 && max_deg < ((int64_t)1 << 20));
+    const int64_t M = N * n;
+    DL_REQUIRE(M % 4 == 0 && M < ((int64_t)1 << 31) && (max_deg + 1) * F < ((int64_t)1 << 31));
+    DL_REQUIRE_ALIGNED(g, 16);
+    const size_t smem = (2 * (size_t)TB_COLS + (size_t)TB_FEATS * TB_THREADS) * sizeof(float);
+    if (cudaFuncSetAttribute(gather_rows_bwd_ell_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+        return DL_ERR_LAUNCH;
+    const int64_t per_pass = (int64_t)TB_THREADS * TB_FEATS;
+    const int64_t blocks = dl_min64(B, (int64_t)DL_NUM_SMS * 2);
+    for (int64_t f_base = 0; f_base < F; f_base += per_pass)
+        gather_rows_bwd_ell_kernel<<<(unsigned)blocks, TB_THREADS, smem, dl_cast(stream)>>>(g, ell, (int)max_deg, gx, B,
+                                                                                          F, M, f_base);
     return dl_launch_status();
 }

@@ -41,6 +41,22 @@ class ConnectionPlan:
         else:
             self.inv_ptr_nodes, self.inv_ent_nodes = self.inv_ptr_virtual, self.inv_ent_virtual
         self.device = device
+        self._ell_nodes = None
+
+    def ell_nodes(self):
+        """The inverse map of the nodes as a table interleaved by feature, (max_deg, F) int32: row j holds the
+        j-th column (ascending) that each feature collects, -1 where a feature has fewer (built on first use)."""
+        if self._ell_nodes is None:
+            ptr = self.inv_ptr_nodes.long()
+            deg = ptr[1:] - ptr[:-1]
+            max_deg = int(deg.max()) if deg.numel() else 0
+            F = self.input_size
+            ell = torch.full((max(max_deg, 1), F), -1, dtype=torch.int32, device=ptr.device)
+            f_of = torch.repeat_interleave(torch.arange(F, device=ptr.device), deg)
+            j_of = torch.arange(f_of.numel(), device=ptr.device) - ptr[:-1][f_of]
+            ell[j_of, f_of] = self.inv_ent_nodes
+            self._ell_nodes = (ell.contiguous(), max_deg)
+        return self._ell_nodes
 
     @staticmethod
     def _invert(m: torch.Tensor, input_size: int):
@@ -605,6 +621,12 @@ class GatherFunction(torch.autograd.Function):
         g = g.contiguous().float()
         gx = torch.empty(B, plan.input_size, device=g.device, dtype=torch.float32)
         with torch.cuda.device(g.device):
-            _native.call("dl_gather_rows_bwd", g, plan.inv_ptr_nodes, plan.inv_ent_nodes, gx, B,
-                         plan.input_size, plan.N, plan.n)
+            M = plan.N * plan.n
+            if M % 4 == 0 and M >= 16384 and B >= 64:
+                # wide gradient rows: shared-memory staged rows and the feature-interleaved entry table
+                ell, max_deg = plan.ell_nodes()
+                _native.call("dl_gather_rows_bwd_ell", g, ell, max_deg, gx, B, plan.input_size, plan.N, plan.n)
+            else:
+                _native.call("dl_gather_rows_bwd", g, plan.inv_ptr_nodes, plan.inv_ent_nodes, gx, B,
+                             plan.input_size, plan.N, plan.n)
         return gx, None

@@ -95,6 +95,12 @@ int dl_gather_rows(const float* x, const int32_t* map, float* out, int64_t B, in
                    int64_t n, dl_stream_t stream);
 int dl_gather_rows_bwd(const float* g, const int32_t* inv_ptr, const int32_t* inv_ent, float* gx,
                        int64_t B, int64_t F, int64_t N, int64_t n, dl_stream_t stream);
+/* The same sum with the inverse map as a table interleaved by feature: ell[j*F + f] = the j-th column (in
+ * ascending order) that feature f collects, -1 once f has no more; max_deg rows.  Gradient rows are staged in
+ * shared memory and both streams are read coalesced; N*n must be a multiple of 4 and g 16-byte aligned.  Same
+ * order of additions as dl_gather_rows_bwd: same bits. */
+int dl_gather_rows_bwd_ell(const float* g, const int32_t* ell, int64_t max_deg, float* gx, int64_t B, int64_t F,
+                           int64_t N, int64_t n, dl_stream_t stream);
 
 /* ------------------------------------------------------------------ ConvolutionalLayer patches
  * Replaces nn.Unfold + transpose + view of the convolutional LUT layer

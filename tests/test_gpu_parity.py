@@ -964,6 +964,33 @@ def test_input_gradient_for_a_disjoint_map_equals_the_general_kernel(dev):
     assert torch.equal(got16, want.to(torch.bfloat16))
 
 
+def test_gather_backward_with_interleaved_entry_table(dev):
+    """dl_gather_rows_bwd_ell (gradient rows staged in shared memory, inverse map interleaved by feature) against
+    dl_gather_rows_bwd (CSR): the same bits, and both match the scatter-add of
+    difflut/layers/random_layer.py:258-304 computed with index_add in float64.  7001 features: two passes of
+    the kernel, the second one ragged; 36000 columns: two column tiles."""
+    from difflut_b200 import _native
+    from difflut_b200.layers.fused_ops import ConnectionPlan, GatherFunction
+    from difflut_b200.layers.random_layer import draw_random_mapping
+
+    gen = torch.Generator().manual_seed(9)
+    B, I, N, n = 301, 7001, 6000, 6
+    plan = ConnectionPlan(draw_random_mapping(I, N, n, 4, True), I, 1, dev)
+    g = torch.randn(B, N * n, generator=gen).to(dev)
+    want = torch.full((B, I), float("nan"), device=dev)
+    _native.call("dl_gather_rows_bwd", g, plan.inv_ptr_nodes, plan.inv_ent_nodes, want, B, I, N, n)
+    ell, max_deg = plan.ell_nodes()
+    got = torch.full((B, I), float("nan"), device=dev)
+    _native.call("dl_gather_rows_bwd_ell", g, ell, max_deg, got, B, I, N, n)
+    assert torch.equal(got, want)
+    ref = torch.zeros(B, I, dtype=torch.float64).index_add_(1, plan.map_nodes.cpu().reshape(-1).long(), g.cpu().double())
+    torch.testing.assert_close(got.cpu().double(), ref, rtol=1e-5, atol=1e-5)
+    # and through autograd (get_mapping's backward picks the interleaved form for rows this wide)
+    x = torch.rand(B, I, generator=gen).to(dev).requires_grad_(True)
+    GatherFunction.apply(x, plan).backward(g.view(B, N, n))
+    assert torch.equal(x.grad, want)
+
+
 def test_soft_select_centred_single_pass(dev):
     """The centred single-pass form of the soft selection (`splits="centered"`): inside the 1e-2 bar of the
     tensor-core contraction for any weights, and for a near-uniform selection (weights N(0, 0.01), binary
