@@ -54,6 +54,7 @@ SIGNATURES = {
     "dl_hybrid_bwd_t": "pppplfpplllll s",
     "dl_seg_sum_t": "ppppll s",
     "dl_gemm_bf16_tn": "ppplllp s",
+    "dl_gemm_bf16_tn_bits": "pppllllfp s",
     "dl_softmax_rows_bf16": "pfpplll s",
     "dl_softmax_rows_centered_bf16": "pfplllll s",
     "dl_row_sum_split_bf16": "pllllfl s",

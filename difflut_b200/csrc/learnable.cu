@@ -107,7 +107,8 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 // status[0] = 0 ok, otherwise (role << 8 | stage) of the wait that gave up.
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    float* __restrict__ C, int M, int N, int K, int* __restrict__ status) {
+                    float* __restrict__ C, uint32_t* __restrict__ Cbits, int64_t Wp, float threshold, int M, int N,
+                    int K, int* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     // the swizzled tiles need 1024-byte alignment
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -244,7 +245,17 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     : "r"(taddr)
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (grow < M) {
+                if (grow < M && Cbits != nullptr) {
+                    // packed result: the thread holds 32 consecutive columns of its row = one word of that row
+                    const int64_t gcol = (int64_t)tile_n * BN + c0;
+                    if (gcol < N) {
+                        uint32_t word = 0;
+#pragma unroll
+                        for (int q = 0; q < 32; ++q)
+                            word |= (gcol + q < N && __uint_as_float(r[q]) >= threshold) ? (1u << q) : 0u;
+                        Cbits[grow * Wp + (gcol >> 5)] = word;
+                    }
+                } else if (grow < M) {
                     const int64_t gcol = (int64_t)tile_n * BN + c0;
                     float* dst = C + grow * N + gcol;
                     if (gcol + 32 <= N && (N & 3) == 0) {
@@ -566,8 +577,29 @@ DL_EXPORT int dl_gemm_bf16_tn(const void* A, const void* B, float* C, int64_t M,
     const int64_t gx = dl_ceil_div(N, BN), gy = dl_ceil_div(M, BM);
     DL_REQUIRE(gx * gy < ((int64_t)1 << 31));
     dim3 grid((unsigned)dl_min64(gx * gy, DL_NUM_SMS));
-    gemm_bf16_tn_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, dl_cast(stream)>>>(map_a, map_b, C, (int)M, (int)N, (int)K,
-                                                                           status);
+    gemm_bf16_tn_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, dl_cast(stream)>>>(map_a, map_b, C, nullptr, 0, 0.f, (int)M,
+                                                                           (int)N, (int)K, status);
+    return dl_launch_status();
+}
+
+DL_EXPORT int dl_gemm_bf16_tn_bits(const void* A, const void* B, uint32_t* bits, int64_t M, int64_t N, int64_t K,
+                                   int64_t Wp, float threshold, int* status, dl_stream_t stream) {
+    DL_REQUIRE(A && B && bits && status && M > 0 && N > 0 && K > 0 && Wp * 32 >= N);
+    DL_REQUIRE(M < ((int64_t)1 << 31) && N < ((int64_t)1 << 31) && K < ((int64_t)1 << 31));
+    DL_REQUIRE_ALIGNED(A, 16);
+    DL_REQUIRE_ALIGNED(B, 16);
+    if (K % 8 != 0) return DL_ERR_ALIGN;  // tensor-map row pitch must be a multiple of 16 bytes
+    CUtensorMap map_a, map_b;
+    int rc = make_map(&map_a, A, M, K, BM);
+    if (rc != DL_OK) return rc;
+    rc = make_map(&map_b, B, N, K, BN);
+    if (rc != DL_OK) return rc;
+    cudaFuncSetAttribute(gemm_bf16_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    const int64_t gx = dl_ceil_div(N, BN), gy = dl_ceil_div(M, BM);
+    DL_REQUIRE(gx * gy < ((int64_t)1 << 31));
+    dim3 grid((unsigned)dl_min64(gx * gy, DL_NUM_SMS));
+    gemm_bf16_tn_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, dl_cast(stream)>>>(map_a, map_b, nullptr, bits, Wp, threshold,
+                                                                           (int)M, (int)N, (int)K, status);
     return dl_launch_status();
 }
 

@@ -134,12 +134,17 @@ class FeatureMajorInput:
     producer of the input (soft_select_t) sets `want_bf16`, the layer function leaves the input gradient as a
     bf16 (I, B) tensor in `grad_bf16` (the dtype the weight-gradient contraction reads, written once by the
     node kernel instead of fp32 + a conversion pass) and hands autograd a zero-stride placeholder of the right
-    shape, which the producer's backward ignores.  Only for disjoint connection plans (`disjoint`)."""
+    shape, which the producer's backward ignores.  Only for disjoint connection plans (`disjoint`).  The same
+    channel carries the forward hand-over of packed bits (`want_bits` / `bits_t`)."""
 
-    def __init__(self, disjoint: bool = False):
+    def __init__(self, disjoint: bool = False, want_bits: bool = False):
         self.disjoint = disjoint
         self.want_bf16 = False
         self.grad_bf16 = None
+        # forward direction: the consumer only reads `value >= 0.5`, so the producer may leave the packed bits
+        # (I, B / 32) int32 here, written by its contraction's epilogue, and return a zero-stride placeholder
+        self.want_bits = want_bits
+        self.bits_t = None
 
 
 class PatchFunction(torch.autograd.Function):
@@ -178,9 +183,13 @@ class DWNLayerFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, tables, plan: ConnectionPlan, alpha: float, beta: float, stable_scale=None,
                 geom: Optional[PatchGeometry] = None):
-        x = x.contiguous().float()
         tables = tables.contiguous().float()
         feature_major = isinstance(geom, FeatureMajorInput)
+        handed_bits = None
+        if feature_major and geom.bits_t is not None:
+            handed_bits, geom.bits_t = geom.bits_t, None  # x is a placeholder of the right shape: do not touch it
+        else:
+            x = x.contiguous().float()
         if feature_major:
             I, B = x.shape
             if B % 128 != 0:
@@ -192,8 +201,10 @@ class DWNLayerFunction(torch.autograd.Function):
         NO, n = plan.N * plan.O, plan.n
         Bp = _native.padded_batch(B)
         with torch.cuda.device(x.device):
-            bits = torch.empty(I, Bp // 32, device=x.device, dtype=torch.int32)
-            if feature_major:
+            bits = handed_bits if handed_bits is not None else torch.empty(I, Bp // 32, device=x.device, dtype=torch.int32)
+            if handed_bits is not None:
+                pass
+            elif feature_major:
                 _native.call("dl_pack_t_to_t", x, bits, I, B, B, Bp, 0.5)
             elif geom is None:
                 _native.call("dl_pack_rows_to_t", x, bits, B, I, Bp, 0.5)

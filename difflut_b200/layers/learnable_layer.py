@@ -155,8 +155,9 @@ class LearnableLayer(BaseLUTLayer):
 
         # the identity plan is disjoint (one reader per selected value) and with one output per node the plan's
         # virtual nodes are its nodes: the node kernel can then hand the gradient over as bf16 (see FeatureMajorInput)
-        channel = FeatureMajorInput(disjoint=self.output_dim_per_node == 1)
-        mapped_t = soft_select_t(x, self.mapping.W, self.mapping.tau, grad_channel=channel if channel.disjoint else None)
+        # the node kernels only read `selected value >= 0.5`: the contraction's epilogue packs those bits itself
+        channel = FeatureMajorInput(disjoint=self.output_dim_per_node == 1, want_bits=True)
+        mapped_t = soft_select_t(x, self.mapping.W, self.mapping.tau, grad_channel=channel)
         plan = _identity_plan(self.output_size, self.n, self.output_dim_per_node, x.device)
         if self._stacked == "dwn":
             return DWNLayerFunction.apply(mapped_t, self.luts, plan, self.alpha, self.beta, None, channel)

@@ -153,17 +153,26 @@ class SoftSelectTFunction(torch.autograd.Function):
         if B % 128 != 0:
             raise ValueError("soft_select_t needs a batch that is a multiple of 128")
         # a consumer that can write its input gradient as bf16 (M, B) leaves it in the channel (FeatureMajorInput)
-        ctx.grad_channel = grad_channel
-        if grad_channel is not None:
+        ctx.grad_channel = grad_channel if (grad_channel is not None and grad_channel.disjoint) else None
+        if ctx.grad_channel is not None:
             grad_channel.want_bf16 = True
+        want_bits = grad_channel is not None and grad_channel.want_bits
         Ip = _round_up(I, 8)
         dev = x.device
         bf = torch.bfloat16
         with torch.cuda.device(dev):
             A, Bm, ld = _forward_operands(x, W, tau, splits)
-            out_t = torch.empty(M, B, device=dev, dtype=torch.float32)
             status = torch.zeros(1, device=dev, dtype=torch.int32)
-            _native.call("dl_gemm_bf16_tn", Bm, A, out_t, M, B, ld, status)
+            if want_bits:
+                # the consumer reads only `value >= 0.5`: packed in the epilogue, nothing else is stored; what
+                # autograd sees is a placeholder of the result's shape
+                bits = torch.empty(M, B // 32, device=dev, dtype=torch.int32)
+                _native.call("dl_gemm_bf16_tn_bits", Bm, A, bits, M, B, ld, B // 32, 0.5, status)
+                grad_channel.bits_t = bits
+                out_t = torch.zeros(1, 1, device=dev, dtype=torch.float32).expand(M, B)
+            else:
+                out_t = torch.empty(M, B, device=dev, dtype=torch.float32)
+                _native.call("dl_gemm_bf16_tn", Bm, A, out_t, M, B, ld, status)
             if check:
                 _check_status(status, "forward")
         ctx.save_for_backward(x, W)

@@ -295,6 +295,12 @@ int dl_seg_sum_t(const float* src_t, const int32_t* inv_ptr, const int32_t* inv_
  * stage) means a bounded wait inside the kernel ran out and C is not valid. */
 int dl_gemm_bf16_tn(const void* A, const void* B, float* C, int64_t M, int64_t N, int64_t K, int* status,
                     dl_stream_t stream);
+/* The same contraction with the result thresholded and bit-packed in the epilogue instead of stored:
+ * bits[m*Wp + n/32] bit n%32 = (C[m][n] >= threshold), the layout and rule of dl_pack_t_to_t applied to the
+ * same accumulators (words past N / 32 are not written; Wp*32 >= N).  For consumers that only read
+ * "selected value >= 0.5" (DWN nodes behind a LearnableLayer): no fp32 result reaches memory. */
+int dl_gemm_bf16_tn_bits(const void* A, const void* B, uint32_t* bits, int64_t M, int64_t N, int64_t K, int64_t Wp,
+                         float threshold, int* status, dl_stream_t stream);
 /* S = softmax(W / tau) per row of W (M, I), written as bf16 at S_hi[r*ld_out + i]; S_lo (optional)
  * receives bf16(S - S_hi) so that S_hi + S_lo carries 16 mantissa bits. */
 int dl_softmax_rows_bf16(const float* W, float tau, void* S_hi, void* S_lo, int64_t ld_out, int64_t M,

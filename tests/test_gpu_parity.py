@@ -911,6 +911,28 @@ def test_gemm_bf16_tn_matches_fp32_matmul(dev, M, N, K):
     torch.testing.assert_close(C, ref, rtol=1e-4, atol=1e-4 * float(K) ** 0.5)
 
 
+def test_gemm_with_packing_epilogue_equals_gemm_then_pack(dev):
+    """dl_gemm_bf16_tn_bits thresholds and packs its accumulators in the epilogue: the same bits as
+    dl_gemm_bf16_tn followed by dl_pack_t_to_t, on a shape with ragged tiles in both directions and values
+    centred on the threshold."""
+    from difflut_b200 import _native
+
+    gen = torch.Generator().manual_seed(2)
+    M, N, K = 333, 640, 264
+    A = (torch.randn(M, K, generator=gen) * 0.05).to(dev).to(torch.bfloat16)
+    B = torch.randn(N, K, generator=gen).to(dev).to(torch.bfloat16)
+    status = torch.zeros(1, device=dev, dtype=torch.int32)
+    C = torch.empty(M, N, device=dev)
+    _native.call("dl_gemm_bf16_tn", A, B, C, M, N, K, status)
+    want = torch.empty(M, N // 32, device=dev, dtype=torch.int32)
+    _native.call("dl_pack_t_to_t", C, want, M, N, N, N, 0.1)
+    got = torch.full((M, N // 32), -1, device=dev, dtype=torch.int32)
+    _native.call("dl_gemm_bf16_tn_bits", A, B, got, M, N, K, N // 32, 0.1, status)
+    assert int(status.item()) == 0
+    assert torch.equal(got, want)
+    assert 0.2 < float((C >= 0.1).float().mean()) < 0.8  # the threshold cuts through the values
+
+
 def test_soft_select_matches_fp32_reference(dev):
     from difflut_b200.layers.soft_select import soft_select
 
