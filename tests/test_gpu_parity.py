@@ -499,9 +499,11 @@ def test_learnable_feature_major_path_equals_row_path(dev):
     gen = torch.Generator().manual_seed(9)
     B, I, N = 256, 72, 40
     x = torch.bernoulli(torch.full((B, I), 0.5), generator=gen)
-    gy = torch.randn(B, N, generator=gen).to(dev)
-    for node in (DWNNode, DWNStableNode):
-        layer = LearnableLayer(I, N, node, NodeConfig(input_dim=6, output_dim=1)).to(dev).train()
+    # two outputs per node: the connection plan is no longer disjoint per virtual node, so the input gradient
+    # takes the general kernel and the fp32 hand-over while the forward still receives packed bits
+    for node, out_dim in ((DWNNode, 1), (DWNStableNode, 1), (DWNNode, 2)):
+        gy = torch.randn(B, N * out_dim, generator=gen).to(dev)
+        layer = LearnableLayer(I, N, node, NodeConfig(input_dim=6, output_dim=out_dim)).to(dev).train()
         with torch.no_grad():
             layer.mapping.W.copy_((torch.randn(N * 6, I, generator=gen) * 2.0).to(dev))
         xa = x.to(dev).requires_grad_(True)
@@ -523,7 +525,7 @@ def test_learnable_feature_major_path_equals_row_path(dev):
         torch.testing.assert_close(gxa, xb.grad, rtol=1e-2, atol=1e-2 * float(xb.grad.abs().max()))
         if node is DWNNode:
             m = O.learnable_soft_mapping(x, layer.mapping.W.detach().cpu(), layer.tau).view(B, N, 6)
-            y_ref = O.dwn_forward(m, layer.luts.detach().cpu()).reshape(B, N)
+            y_ref = O.dwn_forward(m, layer.luts.detach().cpu()).reshape(B, N * out_dim)
             assert float((ya.cpu() != y_ref).float().mean()) < 1e-3
 
 
