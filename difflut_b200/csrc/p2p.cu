@@ -15,6 +15,8 @@
 // publishes this rank's epoch into rank p's flag array (system-scope release) and waits until rank p's
 // epoch shows up in its own array.  Every wait is bounded by a wall-clock limit; on expiry the kernel
 // records it in a status word and returns, so a missing peer can never hang the GPU.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace {
@@ -379,6 +381,16 @@ DL_EXPORT int dl_p2p_reduce_adam(const void* const* peer_grads_host, const void*
     return dl_launch_status();
 }
 
+// DIFFLUT_PEER_BLOCKS=k caps the grid of the whole-vector exchange kernel (a measurement aid: fewer CTAs walk the
+// slice in several iterations, so that one iteration's stores overlap the next one's loads).
+static int64_t exchange_blocks_override() {
+    static const int64_t v = [] {
+        const char* e = getenv("DIFFLUT_PEER_BLOCKS");
+        return e ? (int64_t)atoi(e) : (int64_t)0;
+    }();
+    return v;
+}
+
 DL_EXPORT int dl_p2p_exchange_adam(const void* const* peer_grads_host, const void* const* peer_params_host,
                                    const void* const* peer_flags_host, float* m, float* v, double* state,
                                    int32_t* ctrl, int64_t offset, int64_t count, int64_t channel, int64_t advance_state,
@@ -419,6 +431,7 @@ DL_EXPORT int dl_p2p_exchange_adam(const void* const* peer_grads_host, const voi
             beta2, eps, gscale, timeout_ns);
     } else {
         int64_t blocks = dl_min64(dl_ceil_div(per, 256 * 2), (int64_t)DL_NUM_SMS * 2);
+        if (exchange_blocks_override() > 0) blocks = dl_min64(blocks, exchange_blocks_override());
         if (blocks < 1) blocks = 1;
         p2p_exchange_adam_kernel<<<(unsigned)blocks, 256, 0, dl_cast(stream)>>>(
             grads, params, flags, own_flags, static_cast<const float4*>(params.ptr[rank]),
