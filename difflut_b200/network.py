@@ -166,6 +166,7 @@ class DWNNetwork:
         self._direct_graphs = {}
         self._direct_seen = {}
         self._x_src = None
+        self._y_src = None
         self.max_direct_graphs = 4
         self._side = None
         self._comm = None
@@ -246,15 +247,18 @@ class DWNNetwork:
                          self.bits[li + 1], self.N[li], self.n[li], self.Bp_bits)
         if with_loss is not None and self.swizzle and self.k <= 128:
             _native.call("dl_dwn_fwd_groupsum_ce_s", self.bits[last], self.plans[last].map_nodes, self.tables[last],
-                         self.partial, self.logits_t, self.y_static, self.dlogits_t, self.loss_rows, self.N[last],
+                         self.partial, self.logits_t, self._labels(), self.dlogits_t, self.loss_rows, self.N[last],
                          self.n[last], self.k, self.tau, with_loss[0], with_loss[1], Bp)
             return
         _native.call("dl_dwn_fwd_groupsum_s" if self.swizzle else "dl_dwn_fwd_groupsum_t", self.bits[last],
                      self.plans[last].map_nodes, self.tables[last], self.partial, self.logits_t, self.N[last],
                      self.n[last], self.k, self.tau, Bp)
         if with_loss is not None:
-            _native.call("dl_ce_t", self.logits_t, self.y_static, self.dlogits_t, self.loss_rows, None,
+            _native.call("dl_ce_t", self.logits_t, self._labels(), self.dlogits_t, self.loss_rows, None,
                          with_loss[0], with_loss[1], self.k, Bp)
+
+    def _labels(self) -> torch.Tensor:
+        return self.y_static if self._y_src is None else self._y_src
 
     def _backward(self) -> None:
         if self.fused_backward:
@@ -407,6 +411,14 @@ class DWNNetwork:
         with torch.cuda.device(self.device):
             self._peer_wait_done()  # after this the tables are complete on this rank
         return int(self.peer_ctrl[0].item()) if self.peer_fused else int(self.peer_ctrl_barrier[1].item())
+
+    def host_pipeline(self, x_pinned: torch.Tensor, labels_pinned: torch.Tensor,
+                      loss_pinned: Optional[torch.Tensor] = None, global_batch: Optional[int] = None):
+        """A training loop whose batches arrive in pinned host memory: returns an object whose `step()` is ONE
+        graph launch that trains on the batch copied to the device during the previous step, copies the batch
+        now in the pinned buffers to the other device slot meanwhile, and writes the step's loss to pinned
+        memory.  See `HostPipeline`."""
+        return HostPipeline(self, x_pinned, labels_pinned, loss_pinned, global_batch)
 
     def kernel_launches_per_step(self) -> int:
         L = len(self.layers)
@@ -574,3 +586,76 @@ class DWNNetwork:
         table_bytes = 4 * self.flat.numel()
         per_step = 3 * table_bytes + 7 * table_bytes + sum(2 * 4 * N * n for N, n in zip(self.N, self.n))
         return int(per_sample * B + per_step)
+
+
+
+class HostPipeline:
+    """Double-buffered training steps fed from pinned host memory, one CUDA graph launch per step.
+
+    `x_pinned` (B, F) fp32 and `labels_pinned` (B,) int32 are the caller's staging buffers.  The constructor
+    copies their current content to device slot 0.  Every `step()` replays a graph that (a) trains on the slot
+    filled last, (b) on a parallel branch copies the CURRENT content of the pinned buffers into the other slot,
+    (c) copies the step's loss into `loss` (pinned, 1 element).  So the caller writes batch k + 1 into the pinned
+    buffers, calls `step()` (which trains on batch k and fetches k + 1), and must not overwrite the pinned
+    buffers again before that step has finished (synchronise, or read `loss` after an event).  The host's share
+    of a step is a single launch, which matters when the device step is short (many GPUs, small per-rank
+    batches).  With the peer optimiser `step()` polls the exchange status as `train_step` does.
+    """
+
+    def __init__(self, net: DWNNetwork, x_pinned, labels_pinned, loss_pinned=None, global_batch=None):
+        if not (x_pinned.is_pinned() and labels_pinned.is_pinned()):
+            raise ValueError("host_pipeline needs pinned host tensors")
+        if x_pinned.dtype != torch.float32 or labels_pinned.dtype != torch.int32:
+            raise ValueError("host_pipeline takes fp32 inputs and int32 labels")
+        B = int(x_pinned.shape[0])
+        if tuple(x_pinned.shape) != (B, net.F) or tuple(labels_pinned.shape) != (B,):
+            raise ValueError("host_pipeline: inputs (B, F) and labels (B,) expected")
+        if int(labels_pinned.min()) < 0 or int(labels_pinned.max()) >= net.k:
+            raise ValueError(f"labels must lie in [0, {net.k})")
+        self.net, self.x_pinned, self.labels_pinned = net, x_pinned, labels_pinned
+        self.loss = loss_pinned if loss_pinned is not None else torch.zeros(1).pin_memory()
+        self.B = B
+        self.B_global = B * net.world if global_batch is None else int(global_batch)
+        dev = net.device
+        with torch.cuda.device(dev):
+            net._ensure_buffers(B)
+            if net._graph is None or net._graph_B_global != self.B_global:
+                net._capture(B, self.B_global)  # the eager warm-up step (state restored afterwards) and the general graph
+            self.slots = [(torch.empty(B, net.F, device=dev, dtype=torch.float32),
+                           torch.empty(B, device=dev, dtype=torch.int32)) for _ in range(2)]
+            self.copy_stream = torch.cuda.Stream(device=dev)
+            self.slots[0][0].copy_(x_pinned, non_blocking=True)
+            self.slots[0][1].copy_(labels_pinned, non_blocking=True)
+            self.graphs = [self._capture(0), self._capture(1)]
+        self.cur = 0
+
+    def _capture(self, s: int):
+        net = self.net
+        net._x_src, net._y_src = self.slots[s]
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                main = torch.cuda.current_stream()
+                self.copy_stream.wait_stream(main)
+                with torch.cuda.stream(self.copy_stream):
+                    self.slots[s ^ 1][0].copy_(self.x_pinned, non_blocking=True)
+                    self.slots[s ^ 1][1].copy_(self.labels_pinned, non_blocking=True)
+                net._step_body(self.B, self.B_global)
+                self.loss.copy_(net.loss, non_blocking=True)
+                main.wait_stream(self.copy_stream)
+        finally:
+            net._x_src = net._y_src = None
+        return graph
+
+    def step(self) -> torch.Tensor:
+        net = self.net
+        with torch.cuda.device(net.device):
+            self.graphs[self.cur].replay()
+        self.cur ^= 1
+        net.step_count += 1
+        if net.peer_optimizer and net.peer_status_every > 0 and net.step_count % net.peer_status_every == 0:
+            status = net.peer_status()
+            if status != 0:
+                raise RuntimeError(f"peer exchange: rank {status - 1} did not arrive within {net.peer_timeout_ms} ms; "
+                                   "the tables are invalid since the last successful poll")
+        return self.loss

@@ -614,6 +614,30 @@ def test_graph_on_a_recurring_input_tensor_reads_it_in_place(golden, dev):
     assert len(net_a._direct_graphs) == 1
 
 
+def test_host_pipeline_trains_on_the_batches_in_order(golden, dev):
+    """DWNNetwork.host_pipeline: every step() is one graph launch that trains on the batch fetched during the
+    previous step and fetches the batch now in the pinned buffers.  Four batches written one step ahead must
+    give the same losses and tables, bit for bit, as four train_step calls on the same batches."""
+    g = golden("dwn_net3")
+    net_a, layers_a, _ = _build_net3(g, dev)
+    net_b, layers_b, _ = _build_net3(g, dev)
+    x0, labels = T(g["x"]), T(g["labels"]).to(torch.int32)
+    gen = torch.Generator().manual_seed(11)
+    batches = [x0] + [torch.rand(x0.shape, generator=gen) for _ in range(3)]
+    x_pin, y_pin = torch.empty_like(x0).pin_memory(), labels.clone().pin_memory()
+    x_pin.copy_(batches[0])
+    pipe = net_a.host_pipeline(x_pin, y_pin)
+    for k in range(4):
+        if k + 1 < len(batches):
+            x_pin.copy_(batches[k + 1])  # the next batch goes into the staging buffer before the step that fetches it
+        loss = pipe.step()
+        torch.cuda.synchronize()
+        want = net_b.train_step(batches[k].to(dev), labels.to(dev)).cpu()
+        assert torch.equal(loss.clone(), want), k
+    for la, lb in zip(layers_a, layers_b):
+        assert torch.equal(la.luts.detach(), lb.luts.detach())
+
+
 def test_layer_api_equals_fused_network(golden, dev):
     """The per-layer fp32 API and the bit-packed executor compute the same logits and table gradients."""
     from difflut_b200.utils import GroupSum
