@@ -352,3 +352,28 @@ def test_layer_option_host_paths_match_reference(golden):
             for name in ("small", "wide"):
                 got = layer._apply_gradient_stabilization(torch.from_numpy(g[f"g_{name}"]))
                 torch.testing.assert_close(got, torch.from_numpy(g[f"rescaled_{mode}_{subtract}_{name}"]), rtol=1e-6, atol=1e-7)
+
+
+def test_connection_plan_inverse_maps_agree():
+    """ConnectionPlan's two forms of the inverse map (CSR, and the table interleaved by feature that
+    dl_gather_rows_bwd_ell reads) list the same columns for every feature, in ascending order, and every
+    listed column really maps to that feature (difflut/layers/random_layer.py:258-304 scatters by the same map)."""
+    import torch
+
+    from difflut_b200.layers.fused_ops import ConnectionPlan
+    from difflut_b200.layers.random_layer import draw_random_mapping
+
+    I, N, n = 50, 40, 6
+    mapping = draw_random_mapping(I, N, n, 3, True)
+    plan = ConnectionPlan(mapping, I, 1, torch.device("cpu"))
+    ell, max_deg = plan.ell_nodes()
+    ptr, ent = plan.inv_ptr_nodes.long(), plan.inv_ent_nodes
+    assert ell.shape == (max_deg, I) and int((ell >= 0).sum()) == N * n
+    flat = mapping.reshape(-1)
+    for f in range(I):
+        seg = ent[ptr[f]:ptr[f + 1]].tolist()
+        col = [int(v) for v in ell[:, f].tolist() if v >= 0]
+        assert seg == col == sorted(seg)
+        assert all(int(flat[c]) == f for c in seg)
+        assert (ell[len(seg):, f] == -1).all()
+
