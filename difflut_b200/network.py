@@ -428,6 +428,8 @@ class DWNNetwork:
             update = 2  # state advance, Adam
         elif self.peer_fused:
             update = L if self.peer_per_layer else 1  # one exchange kernel per layer
+            if self.peer_defer_done:
+                update += 1  # the deferred second rendezvous, waited for at the next step's start
         else:
             update = 4  # barrier, state advance, reduce+Adam+broadcast, barrier
         head = 3 if (self.swizzle and self.k <= 128) else 4  # last layer, reduce (+ cross-entropy), loss sum
