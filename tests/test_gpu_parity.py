@@ -831,6 +831,35 @@ def test_groupsum_ce_fused_entry_equals_separate_calls(dev, B, k):
     assert not bool(outs[1][1][:, B:].any()) and not bool(outs[1][2][B:].any())  # padding: zeros
 
 
+@pytest.mark.parametrize("n", [2, 4, 5, 6])
+def test_last_layer_groupsum_for_every_node_width_vs_oracle(dev, n):
+    """dl_dwn_fwd_groupsum_t / _s for n = 2, 4, 5 (the build of the kernel that reads n at run time) and n = 6
+    (the compile-time build), natural and chunk-interleaved bits, ragged batch: logits against the oracle's
+    table look-up (difflut/nodes/dwn_node.py:138-165) + GroupSum (difflut/utils/modules.py:116-163)."""
+    from difflut_b200 import _native
+    from difflut_b200.layers.random_layer import draw_random_mapping
+
+    gen = torch.Generator().manual_seed(40 + n)
+    B, I, N, k, tau = 1300, 80, 123, 5, 1.7
+    Bp = _native.padded_batch(B)
+    x = torch.rand(B, I, generator=gen)
+    idx = draw_random_mapping(I, N, n, 2, True)
+    tab = torch.randn(N, 1 << n, generator=gen)
+    nat = torch.empty(I, Bp // 32, dtype=torch.int32, device=dev)
+    _native.call("dl_pack_rows_to_t", x.to(dev), nat, B, I, Bp, 0.5)
+    swz = torch.empty(I, int(_native.lib().dl_swizzled_words(Bp)), dtype=torch.int32, device=dev)
+    _native.call("dl_bits_swizzle_t", nat, swz, I, Bp)
+    xm = O.gather_mapping((x >= 0.5).float(), idx)
+    want = O.groupsum(O.dwn_forward(xm, tab.unsqueeze(1)).reshape(B, N), k, tau)
+    S = int(_native.lib().dl_dwn_groupsum_splits(N, k))
+    mp = idx.to(device=dev, dtype=torch.int32).contiguous()
+    for entry, bits in (("dl_dwn_fwd_groupsum_t", nat), ("dl_dwn_fwd_groupsum_s", swz)):
+        partial = torch.empty(k * S, Bp, device=dev)
+        logits = torch.full((k, Bp), float("nan"), device=dev)
+        _native.call(entry, bits, mp, tab.to(dev), partial, logits, N, n, k, tau, Bp)
+        torch.testing.assert_close(logits[:, :B].t().cpu(), want, rtol=1e-5, atol=1e-5)
+
+
 @pytest.mark.parametrize("B", [128, 1024, 2500])
 def test_bits_swizzle_layout(dev, B):
     """Chunk-interleaved layout: bit c + 8r of word w of a 1024-sample block is sample 128c + 4w + r."""
