@@ -394,16 +394,19 @@ __device__ __forceinline__ uint2 pack_bf16x4(float a, float b, float c, float d)
     return out;
 }
 
+// QN: 16-byte pieces per thread (the row has at most 256 * QN of them); the launcher picks the smallest that fits,
+// so a 4096-wide row holds 16 values per thread instead of 32 and more rows are resident per SM.
+template <int QN>
 __global__ void __launch_bounds__(256)
 softmax_rows_vec_kernel(const float* __restrict__ W, float inv_tau, float center, __nv_bfloat16* __restrict__ S_hi,
                         __nv_bfloat16* __restrict__ S_lo, int64_t ld_out, int I4) {
     __shared__ float scratch[8];
     const int64_t row = blockIdx.x;
     const float4* w = reinterpret_cast<const float4*>(W + row * (int64_t)I4 * 4);
-    float4 v[SM_MAXQ];
+    float4 v[QN];
     float mx = -INFINITY;
 #pragma unroll
-    for (int k = 0; k < SM_MAXQ; ++k) {
+    for (int k = 0; k < QN; ++k) {
         const int q = threadIdx.x + k * 256;
         if (q < I4) {
             const float4 t = __ldg(w + q);
@@ -416,7 +419,7 @@ softmax_rows_vec_kernel(const float* __restrict__ W, float inv_tau, float center
     mx = block_reduce(mx, scratch, true);
     float sum = 0.f;
 #pragma unroll
-    for (int k = 0; k < SM_MAXQ; ++k) {
+    for (int k = 0; k < QN; ++k) {
         v[k].x = expf(v[k].x - mx); v[k].y = expf(v[k].y - mx);
         v[k].z = expf(v[k].z - mx); v[k].w = expf(v[k].w - mx);
         sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
@@ -424,7 +427,7 @@ softmax_rows_vec_kernel(const float* __restrict__ W, float inv_tau, float center
     sum = block_reduce(sum, scratch, false);
     const float inv = 1.0f / sum;
 #pragma unroll
-    for (int k = 0; k < SM_MAXQ; ++k) {
+    for (int k = 0; k < QN; ++k) {
         const int q = threadIdx.x + k * 256;
         if (q < I4) {
             const float a = v[k].x * inv - center, b = v[k].y * inv - center, c = v[k].z * inv - center,
@@ -441,6 +444,7 @@ softmax_rows_vec_kernel(const float* __restrict__ W, float inv_tau, float center
     }
 }
 
+template <int QN>
 __global__ void __launch_bounds__(256)
 softmax_bwd_rows_vec_kernel(const float* __restrict__ W, const float* __restrict__ gS, float inv_tau,
                             float* __restrict__ gW, int I4) {
@@ -448,10 +452,10 @@ softmax_bwd_rows_vec_kernel(const float* __restrict__ W, const float* __restrict
     const int64_t row = blockIdx.x;
     const float4* w = reinterpret_cast<const float4*>(W + row * (int64_t)I4 * 4);
     const float4* g = reinterpret_cast<const float4*>(gS + row * (int64_t)I4 * 4);
-    float4 v[SM_MAXQ], gg[SM_MAXQ];
+    float4 v[QN], gg[QN];
     float mx = -INFINITY;
 #pragma unroll
-    for (int k = 0; k < SM_MAXQ; ++k) {
+    for (int k = 0; k < QN; ++k) {
         const int q = threadIdx.x + k * 256;
         if (q < I4) {
             const float4 t = __ldg(w + q);
@@ -466,7 +470,7 @@ softmax_bwd_rows_vec_kernel(const float* __restrict__ W, const float* __restrict
     mx = block_reduce(mx, scratch, true);
     float sum = 0.f, dot = 0.f;
 #pragma unroll
-    for (int k = 0; k < SM_MAXQ; ++k) {
+    for (int k = 0; k < QN; ++k) {
         v[k].x = expf(v[k].x - mx); v[k].y = expf(v[k].y - mx);
         v[k].z = expf(v[k].z - mx); v[k].w = expf(v[k].w - mx);
         sum += (v[k].x + v[k].y) + (v[k].z + v[k].w);
@@ -478,7 +482,7 @@ softmax_bwd_rows_vec_kernel(const float* __restrict__ W, const float* __restrict
     const float mean = dot * inv;
     float4* out = reinterpret_cast<float4*>(gW + row * (int64_t)I4 * 4);
 #pragma unroll
-    for (int k = 0; k < SM_MAXQ; ++k) {
+    for (int k = 0; k < QN; ++k) {
         const int q = threadIdx.x + k * 256;
         if (q < I4) {
             float4 r;
@@ -608,10 +612,15 @@ static int softmax_rows_launch(const float* W, float tau, float center, void* S_
     const bool aligned = reinterpret_cast<uintptr_t>(W) % 16 == 0 && reinterpret_cast<uintptr_t>(S_hi) % 8 == 0 &&
                          (S_lo == nullptr || reinterpret_cast<uintptr_t>(S_lo) % 8 == 0);
     if (aligned && I % 4 == 0 && ld_out % 4 == 0 && I <= 256 * 4 * SM_MAXQ) {
-        softmax_rows_vec_kernel<<<(unsigned)M, 256, 0, dl_cast(stream)>>>(W, 1.0f / tau, center,
-                                                                        static_cast<__nv_bfloat16*>(S_hi),
-                                                                        static_cast<__nv_bfloat16*>(S_lo), ld_out,
-                                                                        (int)(I / 4));
+        __nv_bfloat16* hi = static_cast<__nv_bfloat16*>(S_hi);
+        __nv_bfloat16* lo = static_cast<__nv_bfloat16*>(S_lo);
+        const int I4 = (int)(I / 4);
+        const unsigned rows = (unsigned)M;
+        cudaStream_t st = dl_cast(stream);
+        if (I4 <= 256) softmax_rows_vec_kernel<1><<<rows, 256, 0, st>>>(W, 1.0f / tau, center, hi, lo, ld_out, I4);
+        else if (I4 <= 512) softmax_rows_vec_kernel<2><<<rows, 256, 0, st>>>(W, 1.0f / tau, center, hi, lo, ld_out, I4);
+        else if (I4 <= 1024) softmax_rows_vec_kernel<4><<<rows, 256, 0, st>>>(W, 1.0f / tau, center, hi, lo, ld_out, I4);
+        else softmax_rows_vec_kernel<SM_MAXQ><<<rows, 256, 0, st>>>(W, 1.0f / tau, center, hi, lo, ld_out, I4);
         return dl_launch_status();
     }
     softmax_rows_kernel<<<(unsigned)M, 256, 0, dl_cast(stream)>>>(W, 1.0f / tau, center,
@@ -695,7 +704,13 @@ DL_EXPORT int dl_softmax_bwd_rows(const float* W, const float* gS, float tau, fl
     DL_REQUIRE(W && gS && gW && M > 0 && I > 0 && tau > 0.f);
     if (I % 4 == 0 && I <= 256 * 4 * SM_MAXQ && reinterpret_cast<uintptr_t>(W) % 16 == 0 &&
         reinterpret_cast<uintptr_t>(gS) % 16 == 0 && reinterpret_cast<uintptr_t>(gW) % 16 == 0) {
-        softmax_bwd_rows_vec_kernel<<<(unsigned)M, 256, 0, dl_cast(stream)>>>(W, gS, 1.0f / tau, gW, (int)(I / 4));
+        const int I4 = (int)(I / 4);
+        const unsigned rows = (unsigned)M;
+        cudaStream_t st = dl_cast(stream);
+        if (I4 <= 256) softmax_bwd_rows_vec_kernel<1><<<rows, 256, 0, st>>>(W, gS, 1.0f / tau, gW, I4);
+        else if (I4 <= 512) softmax_bwd_rows_vec_kernel<2><<<rows, 256, 0, st>>>(W, gS, 1.0f / tau, gW, I4);
+        else if (I4 <= 1024) softmax_bwd_rows_vec_kernel<4><<<rows, 256, 0, st>>>(W, gS, 1.0f / tau, gW, I4);
+        else softmax_bwd_rows_vec_kernel<SM_MAXQ><<<rows, 256, 0, st>>>(W, gS, 1.0f / tau, gW, I4);
         return dl_launch_status();
     }
     softmax_bwd_rows_kernel<<<(unsigned)M, 256, 0, dl_cast(stream)>>>(W, gS, 1.0f / tau, gW, I);
